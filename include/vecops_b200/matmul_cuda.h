@@ -1,0 +1,139 @@
+/*
+ * Thin C ABI over the sm_100a matmul kernels.
+ *
+ * This is what a vecops build binds in place of its CPU matmul backends.  The
+ * semantic is vecops' own (include/vecops/ops/Matmul.h:13-17, :530-570):
+ *
+ *     C[M,N] = A[M,K] . B[N,K]^T        (B is always addressed as [N,K]; a
+ *                                        row-major [K,N] matrix is the view
+ *                                        with strides (1, N))
+ *
+ * with the memory dtype of each operand separate from the compute dtype
+ * (docs/Tensor.md:218-231) and an optional per-output-column scale applied in
+ * accumulator space before the store conversion
+ * (tests/ops/MatmulConversionTestCommon.h:664-671).  The dtype combinations
+ * served, and the vecops atoms they stand for (include/vecops/matmul/details/
+ * kernel/amx/Atoms.h:51-86):
+ *
+ *     A      B      C      scale   accumulate   vecops atom
+ *     f32    f32    f32    -       f32          (AVX-512 fmadd leaf, amx/Backend.h:767-901)
+ *     bf16   bf16   bf16   opt.    f32          AMX_BF16F32 with output<float>(bf16 C)
+ *     bf16   bf16   f32    opt.    f32          AMX_BF16F32
+ *     i8/u8  i8/u8  i32    -       i32 (wraps)  AMX_I8I32<A,B>
+ *     bf16   i8     bf16   opt.    f32          AMX_BF16F32 with input<bfloat16_t>(int8 W)
+ *
+ * All pointers are DEVICE pointers on `device_index`; strides count elements.
+ * Nothing here allocates device memory: scratch is passed in by the caller
+ * after asking vecops_b200_matmul_workspace (the device counterpart of
+ * Matmul::required_workspace, include/vecops/ops/Matmul.h:504-526).  There is
+ * no CPU fallback: every entry point that needs a GPU fails with
+ * VECOPS_STATUS_EXECUTION_ERROR when none is usable.
+ */
+#ifndef VECOPS_B200_MATMUL_CUDA_H
+#define VECOPS_B200_MATMUL_CUDA_H
+
+#include "vecops_b200/call_abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Kernel variants.  AUTO lets the shape/dtype rules decide; the rules are the
+ * device counterpart of vecops' runtime_*_profitable predicates
+ * (include/vecops/matmul/details/kernel/RuntimeDispatch.h:24-101,
+ * src/MatmulRuntimeDispatch.cpp:12-32). */
+typedef enum VecopsB200MatmulKernel {
+  VECOPS_B200_KERNEL_AUTO = 0,
+  VECOPS_B200_KERNEL_GENERIC = 1,      /* strided SIMT; every dtype row above, any shape */
+  VECOPS_B200_KERNEL_F32_SIMT = 2,     /* tiled FP32 FMA GEMM */
+  VECOPS_B200_KERNEL_BF16_TCGEN05 = 3, /* tcgen05 kind::f16, TMEM f32 accumulators, TMA pipeline */
+  VECOPS_B200_KERNEL_I8_TCGEN05 = 4,   /* tcgen05 kind::i8, TMEM i32 accumulators, TMA pipeline */
+  VECOPS_B200_KERNEL_W8_SMALL_M = 5,   /* weight-only int8, M <= 32: 128-bit loads, in-register dequant, split-K */
+  VECOPS_B200_KERNEL_W8_TCGEN05 = 6,   /* weight-only int8, larger M: dequant into swizzled smem, tcgen05 with W as the M operand */
+  VECOPS_B200_KERNEL_COUNT_ = 7
+} VecopsB200MatmulKernel;
+
+#define VECOPS_B200_MATMUL_FLAG_ASYNC (1u << 0) /* enqueue only; caller synchronises the stream */
+
+typedef struct VecopsB200Matmul {
+  uint32_t struct_size;
+  uint32_t kernel;      /* VecopsB200MatmulKernel; AUTO = pick by rules */
+  int64_t m, n, k;
+  const void* a;        /* [M,K] */
+  int64_t a_stride_m, a_stride_k;
+  const void* b;        /* [N,K] */
+  int64_t b_stride_n, b_stride_k;
+  void* c;              /* [M,N] */
+  int64_t c_stride_m, c_stride_n;
+  const float* column_scale; /* optional [N] f32 factor on the accumulator, NULL = none */
+  void* workspace;      /* device scratch, may be NULL when the query returns 0 */
+  uint64_t workspace_size;
+  void* stream;         /* cudaStream_t; NULL = default stream */
+  uint32_t a_dtype, b_dtype, c_dtype; /* VecopsDType */
+  int32_t device_index; /* CUDA ordinal; -1 = the calling thread's current device */
+  uint32_t flags;
+  uint32_t reserved;
+} VecopsB200Matmul;
+
+/* Pure host logic, no GPU needed: which kernel the rules choose for this
+ * problem (replaces vecops' MatmulRuntimeDispatch for the device path).
+ * Fails with INVALID_ARGUMENT on an unsupported dtype row or negative extent,
+ * NOT_APPLICABLE when `kernel` was forced to a variant that cannot serve it. */
+VECOPS_B200_EXPORT int32_t vecops_b200_matmul_select(const VecopsB200Matmul* problem, uint32_t* kernel,
+                                                     VecopsError* error);
+
+/* Bytes of device scratch the chosen kernel needs (split-K partials).  Pure
+ * host logic.  Replaces Matmul::required_workspace (ops/Matmul.h:504-526). */
+VECOPS_B200_EXPORT int32_t vecops_b200_matmul_workspace(const VecopsB200Matmul* problem, uint64_t* bytes,
+                                                        VecopsError* error);
+
+/* Launch.  Synchronous unless VECOPS_B200_MATMUL_FLAG_ASYNC is set.  Replaces
+ * Matmul::operator() (ops/Matmul.h:530-570) / kernel::matmul_bound
+ * (include/vecops/matmul/details/kernel/Kernel.h:97-133).  M, N or K == 0 are
+ * legal: K == 0 stores zeros (ops/Matmul.h:41-43). */
+VECOPS_B200_EXPORT int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* error);
+
+/* Stable short name of a variant ("bf16_tcgen05", ...), NULL if out of range. */
+VECOPS_B200_EXPORT const char* vecops_b200_kernel_name(uint32_t kernel);
+
+/* Number of usable CUDA devices; 0 when there is no driver or no GPU. */
+VECOPS_B200_EXPORT int32_t vecops_b200_device_count(void);
+
+typedef struct VecopsB200DeviceInfo {
+  uint32_t struct_size;
+  int32_t sm_major, sm_minor;
+  int32_t sm_count;
+  uint64_t l2_bytes;
+  uint64_t hbm_bytes;
+  uint64_t smem_per_block_optin;
+  char name[64];
+} VecopsB200DeviceInfo;
+
+VECOPS_B200_EXPORT int32_t vecops_b200_device_info(int32_t device_index, VecopsB200DeviceInfo* info,
+                                                   VecopsError* error);
+
+/* Kernels launched by this library since load (all devices, all threads). */
+VECOPS_B200_EXPORT uint64_t vecops_b200_launch_count(void);
+
+/* Device-side wait diagnostics.  Every mbarrier wait in the tensor-core
+ * kernels is bounded; a wait that runs out records where it gave up and the
+ * kernel returns.  Synchronous runs check this themselves and report
+ * EXECUTION_ERROR; after asynchronous runs call this once the stream is
+ * idle.  Returns OK and *status == 0 when no wait ever ran out; reading
+ * clears the record. */
+VECOPS_B200_EXPORT int32_t vecops_b200_take_device_status(int32_t device_index, uint32_t* status,
+                                                          VecopsError* error);
+
+/* Strided gather of column slabs: dst[M, ldd] columns [col0, col0+cols) <-
+ * src[M, cols] (row pitch lds), `elem_size` bytes per element.  Used after the
+ * all-gather of a column-sharded GEMM to place peers' slabs into the row-major
+ * full matrix. */
+VECOPS_B200_EXPORT int32_t vecops_b200_place_columns(void* dst, int64_t ldd, int64_t col0, const void* src,
+                                                     int64_t lds, int64_t rows, int64_t cols, uint32_t elem_size,
+                                                     void* stream, VecopsError* error);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* VECOPS_B200_MATMUL_CUDA_H */

@@ -1,0 +1,136 @@
+/*
+ * TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+ *
+ * CPU restatement of the vecops matmul semantic, used only as the checker in
+ * tests/, in __graft_entry__.smoke() and as the "port" CPU baseline of
+ * bench.py.  Nothing the library ships calls into this file.
+ *
+ * What it restates (paths are inside the vecops repository):
+ *   - C[M,N] = A[M,K] . B[N,K]^T, B always addressed [N,K]
+ *       include/vecops/ops/Matmul.h:13-17
+ *   - the form the reference's own tests use as their expected value: a naive
+ *     triple loop accumulating in the accumulator type
+ *       tests/ops/MatmulTest.cpp:82-97
+ *       tests/ops/MatmulConversionTestCommon.h:126-141
+ *   - memory dtype != compute dtype: load converts to the compute type, the
+ *     store converts from the accumulator type
+ *       docs/Tensor.md:218-231
+ *   - float -> bfloat16 is round-to-nearest-even on the bit pattern, NaN maps
+ *     to 0x7fc0
+ *       include/vecops/util/BFloat16.h:25-37
+ *   - 8-bit products accumulate in int32 and wrap modulo 2^32
+ *       include/vecops/vec/WideningDot.h:100-103, tests/ops/MatmulTest.cpp:1025-1055
+ *   - per-output-column scale applied to the fp32 accumulator before the
+ *     store conversion
+ *       tests/ops/MatmulConversionTestCommon.h:664-671
+ *
+ * Floating-point sums are taken in double and rounded once to float: the
+ * reference fixes no summation order (AMX TMUL, AVX-512 lanes and the scalar
+ * test loop all differ), so the checker uses the order-free value that every
+ * fp32 order approximates, and the tests carry the tolerance.
+ *
+ * Pinned against the reference itself: oracle/_ref (the reference's own
+ * ops::matmul built from its headers) on the fixtures under tests/golden/.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <string.h>
+
+static inline float bf16_to_f32(uint16_t bits) {
+  uint32_t wide = (uint32_t)bits << 16;
+  float out;
+  memcpy(&out, &wide, sizeof(out));
+  return out;
+}
+
+static inline uint16_t f32_to_bf16(float value) {
+  if (isnan(value)) return 0x7fc0;
+  uint32_t bits;
+  memcpy(&bits, &value, sizeof(bits));
+  const uint32_t bias = ((bits >> 16) & 1u) + 0x7fffu;
+  return (uint16_t)((bits + bias) >> 16);
+}
+
+/* exported so that tests can pin the rounding rule on its own */
+uint16_t oracle_f32_to_bf16(float value) { return f32_to_bf16(value); }
+float oracle_bf16_to_f32(uint16_t bits) { return bf16_to_f32(bits); }
+
+/* fp32 x fp32 -> fp32.  Element strides on every tensor. */
+void oracle_matmul_f32(int64_t m, int64_t n, int64_t k, const float* a, int64_t sam, int64_t sak, const float* b,
+                       int64_t sbn, int64_t sbk, float* c, int64_t scm, int64_t scn) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t i = 0; i < m; ++i) {
+    for (int64_t j = 0; j < n; ++j) {
+      double sum = 0.0;
+      for (int64_t kk = 0; kk < k; ++kk) sum += (double)a[i * sam + kk * sak] * (double)b[j * sbn + kk * sbk];
+      c[i * scm + j * scn] = (float)sum;
+    }
+  }
+}
+
+/* bf16 x bf16 -> fp32 accumulate -> (optional column scale) -> bf16 or fp32.
+ * c_is_bf16 selects the store type. */
+void oracle_matmul_bf16(int64_t m, int64_t n, int64_t k, const uint16_t* a, int64_t sam, int64_t sak,
+                        const uint16_t* b, int64_t sbn, int64_t sbk, const float* column_scale, void* c, int64_t scm,
+                        int64_t scn, int c_is_bf16) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t i = 0; i < m; ++i) {
+    for (int64_t j = 0; j < n; ++j) {
+      double sum = 0.0;
+      for (int64_t kk = 0; kk < k; ++kk)
+        sum += (double)bf16_to_f32(a[i * sam + kk * sak]) * (double)bf16_to_f32(b[j * sbn + kk * sbk]);
+      float acc = (float)sum;
+      if (column_scale) acc *= column_scale[j];
+      if (c_is_bf16) ((uint16_t*)c)[i * scm + j * scn] = f32_to_bf16(acc);
+      else ((float*)c)[i * scm + j * scn] = acc;
+    }
+  }
+}
+
+/* 8-bit x 8-bit -> int32, wrapping.  a_signed / b_signed select int8 or uint8. */
+void oracle_matmul_i8(int64_t m, int64_t n, int64_t k, const void* a, int64_t sam, int64_t sak, int a_signed,
+                      const void* b, int64_t sbn, int64_t sbk, int b_signed, int32_t* c, int64_t scm, int64_t scn) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t i = 0; i < m; ++i) {
+    for (int64_t j = 0; j < n; ++j) {
+      uint32_t sum = 0;
+      for (int64_t kk = 0; kk < k; ++kk) {
+        const int32_t av = a_signed ? (int32_t)((const int8_t*)a)[i * sam + kk * sak]
+                                    : (int32_t)((const uint8_t*)a)[i * sam + kk * sak];
+        const int32_t bv = b_signed ? (int32_t)((const int8_t*)b)[j * sbn + kk * sbk]
+                                    : (int32_t)((const uint8_t*)b)[j * sbn + kk * sbk];
+        sum += (uint32_t)av * (uint32_t)bv;
+      }
+      int32_t out;
+      memcpy(&out, &sum, sizeof(out));
+      c[i * scm + j * scn] = out;
+    }
+  }
+}
+
+/* Weight-only int8: bf16 activations x int8 weights (widened exactly to the
+ * bf16 compute type) -> fp32 accumulate -> column scale -> bf16 or fp32. */
+void oracle_matmul_w8(int64_t m, int64_t n, int64_t k, const uint16_t* a, int64_t sam, int64_t sak, const int8_t* w,
+                      int64_t swn, int64_t swk, const float* column_scale, void* c, int64_t scm, int64_t scn,
+                      int c_is_bf16) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t i = 0; i < m; ++i) {
+    for (int64_t j = 0; j < n; ++j) {
+      double sum = 0.0;
+      for (int64_t kk = 0; kk < k; ++kk)
+        sum += (double)bf16_to_f32(a[i * sam + kk * sak]) * (double)w[j * swn + kk * swk];
+      float acc = (float)sum;
+      if (column_scale) acc *= column_scale[j];
+      if (c_is_bf16) ((uint16_t*)c)[i * scm + j * scn] = f32_to_bf16(acc);
+      else ((float*)c)[i * scm + j * scn] = acc;
+    }
+  }
+}
+
+/* How many threads the loops above use (1 when built without OpenMP). */
+#ifdef _OPENMP
+#include <omp.h>
+int oracle_threads(void) { return omp_get_max_threads(); }
+#else
+int oracle_threads(void) { return 1; }
+#endif

@@ -1,0 +1,151 @@
+// TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+//
+// A C-callable door to the reference's own CPU matmul, compiled from the
+// reference's headers where they lie (never copied into this repository) by
+// oracle/build_oracle.py into oracle/_ref/libvecops_ref.so.  It validates the
+// C restatement in matmul_oracle.c, generates the fixtures under tests/golden/
+// and serves as the timed "reference" CPU baseline of bench.py.
+//
+// API usage follows the reference's own tests: tests/ops/MatmulTest.cpp:60-81
+// (make_tensor / ops::matmul / required_workspace / kernel::Workspace) and
+// tests/ops/MatmulConversionTestCommon.h:105-124, 664-677 (input<Compute>(t),
+// output<Acc>(t, epilogue), per-column scale as a lane-local vec transform).
+// AMX needs a per-thread permission request first, as in
+// tests/ops/MatmulTestArch.h:22-27.
+#include <sys/syscall.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <thread>
+#include <vector>
+
+#include "vecops/ops/Matmul.h"
+
+using namespace vecops;
+using namespace vecops::meta;
+using namespace vecops::tensor;
+
+namespace {
+
+bool request_amx() {
+  return syscall(SYS_arch_prctl, 0x1023 /* ARCH_REQ_XCOMP_PERM */, 18 /* XFEATURE_XTILEDATA */) == 0;
+}
+
+template <class Atom, class MA, class MB, class MC, class... Epilogue>
+void ref_matmul(nint_t m, nint_t n, nint_t k, const MA* a, nint_t lda, const MB* b, nint_t ldb, MC* c, nint_t ldc,
+                Epilogue... epilogue) {
+  auto at = make_tensor(a, make_layout(make_shape(Any{m}, Any{k}), make_strides(Any{lda}, cint<1>)));
+  auto bt = make_tensor(b, make_layout(make_shape(Any{n}, Any{k}), make_strides(Any{ldb}, cint<1>)));
+  auto ct = make_tensor(c, make_layout(make_shape(Any{m}, Any{n}), make_strides(Any{ldc}, cint<1>)));
+  auto ai = input<typename Atom::TA>(at);
+  auto bi = input<typename Atom::TB>(bt);
+  auto co = output<typename Atom::TAcc>(ct, epilogue...);
+  auto op = ops::matmul(ops::MatmulConfig<Atom>{});
+  kernel::Workspace storage(op.required_workspace(Any{m}, Any{n}, Any{k}, ai, bi, co));
+  auto view = storage.view();
+  op(view, Any{m}, Any{n}, Any{k}, ai, bi, co);
+}
+
+// Run `body(n0, n1)` over [0, n) split across `threads` workers in multiples
+// of 16 columns (the AMX tile width), each worker with its own AMX permission:
+// the way the reference means callers to use all cores (one matmul per lane on
+// a sub-view, docs/WorkspacePlanning.md:96-110).
+template <class Body>
+void over_columns(nint_t n, int threads, Body body) {
+  threads = std::max(1, threads);
+  if (threads == 1) {
+    body(nint_t{0}, n);
+    return;
+  }
+  const nint_t blocks = (n + 15) / 16;
+  std::vector<std::thread> pool;
+  for (int t = 0; t < threads; ++t) {
+    const nint_t n0 = std::min(n, (blocks * t / threads) * 16);
+    const nint_t n1 = std::min(n, (blocks * (t + 1) / threads) * 16);
+    if (n1 <= n0) continue;
+    pool.emplace_back([=] {
+      request_amx();
+      body(n0, n1);
+    });
+  }
+  for (auto& worker : pool) worker.join();
+}
+
+}  // namespace
+
+extern "C" {
+
+int ref_available(void) { return request_amx() ? 1 : 0; }
+
+// bf16 x bf16 -> f32 accumulate -> bf16 (c_is_bf16) or f32.  AMX_BF16F32.
+int ref_matmul_bf16(int64_t m, int64_t n, int64_t k, const uint16_t* a, int64_t lda, const uint16_t* b, int64_t ldb,
+                    void* c, int64_t ldc, int c_is_bf16, int threads) {
+  if (!request_amx()) return 1;
+  over_columns(n, threads, [=](nint_t n0, nint_t n1) {
+    const auto* ap = reinterpret_cast<const bfloat16_t*>(a);
+    const auto* bp = reinterpret_cast<const bfloat16_t*>(b) + n0 * ldb;
+    if (c_is_bf16)
+      ref_matmul<matmul::AMX_BF16F32>(m, n1 - n0, k, ap, lda, bp, ldb, reinterpret_cast<bfloat16_t*>(c) + n0, ldc);
+    else
+      ref_matmul<matmul::AMX_BF16F32>(m, n1 - n0, k, ap, lda, bp, ldb, reinterpret_cast<float*>(c) + n0, ldc);
+  });
+  return 0;
+}
+
+// 8-bit x 8-bit -> int32.  AMX_I8I32<A,B> for the four signedness pairs.
+int ref_matmul_i8(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int a_signed, const void* b, int64_t ldb,
+                  int b_signed, int32_t* c, int64_t ldc, int threads) {
+  if (!request_amx()) return 1;
+  over_columns(n, threads, [=](nint_t n0, nint_t n1) {
+    int32_t* cp = c + n0;
+    if (a_signed && b_signed)
+      ref_matmul<matmul::AMX_I8I32<int8_t, int8_t>>(m, n1 - n0, k, static_cast<const int8_t*>(a), lda,
+                                                    static_cast<const int8_t*>(b) + n0 * ldb, ldb, cp, ldc);
+    else if (a_signed)
+      ref_matmul<matmul::AMX_I8I32<int8_t, uint8_t>>(m, n1 - n0, k, static_cast<const int8_t*>(a), lda,
+                                                     static_cast<const uint8_t*>(b) + n0 * ldb, ldb, cp, ldc);
+    else if (b_signed)
+      ref_matmul<matmul::AMX_I8I32<uint8_t, int8_t>>(m, n1 - n0, k, static_cast<const uint8_t*>(a), lda,
+                                                     static_cast<const int8_t*>(b) + n0 * ldb, ldb, cp, ldc);
+    else
+      ref_matmul<matmul::AMX_I8I32<uint8_t, uint8_t>>(m, n1 - n0, k, static_cast<const uint8_t*>(a), lda,
+                                                      static_cast<const uint8_t*>(b) + n0 * ldb, ldb, cp, ldc);
+  });
+  return 0;
+}
+
+// Weight-only int8: bf16 activations, int8 weights read as the bf16 compute
+// type, per-column f32 scale in the epilogue, bf16 store.  `scale` must have
+// 64 readable floats past n (the epilogue loads whole vectors, as the
+// reference tests allocate n + 64: MatmulConversionTestCommon.h:636-646).
+int ref_matmul_w8(int64_t m, int64_t n, int64_t k, const uint16_t* a, int64_t lda, const int8_t* w, int64_t ldw,
+                  const float* scale, uint16_t* c, int64_t ldc, int threads) {
+  if (!request_amx()) return 1;
+  over_columns(n, threads, [=](nint_t n0, nint_t n1) {
+    const float* scales = scale + n0;
+    auto epilogue = make_lane_local_vec_transform<float32_t, float32_t>(
+        [scales](auto tag, auto value, const auto& context) VECOPS_KERNEL_LAMBDA {
+          const auto coordinate = context.lane_coord(0);
+          const nint_t column = coordinate[coordinate.size() - 1];
+          return vec::mul(tag, value, vec::load(tag, scales + column));
+        });
+    ref_matmul<matmul::AMX_BF16F32>(m, n1 - n0, k, reinterpret_cast<const bfloat16_t*>(a), lda, w + n0 * ldw, ldw,
+                                    reinterpret_cast<bfloat16_t*>(c) + n0, ldc, epilogue);
+  });
+  return 0;
+}
+
+// fp32: the reference has no fp32 matmul atom on x86; its only fp32 x fp32
+// product code is the AVX-512 vector leaf (amx/Backend.h:767-901) instantiated
+// with equal types.  B is [N,K] here.
+int ref_matmul_f32_leaf(int64_t m, int64_t n, int64_t k, const float* a, int64_t lda, const float* b, int64_t ldb,
+                        float* c, int64_t ldc, int threads) {
+  over_columns(n, threads, [=](nint_t n0, nint_t n1) {
+    kernel::matmul_details::amx::small_vector_dense_matmul<false, float, float, float>(a, lda, b + n0 * ldb, ldb, c + n0,
+                                                                                       ldc, m, n1 - n0, k);
+  });
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,128 @@
+"""ctypes view of the C ABI in ``include/vecops_b200/*.h``.
+
+The host side of this project is C++ (as in vecops); Python appears only as the
+test and benchmark harness, and it reaches the kernels through the same
+``extern "C"`` entry points a vecops build would bind.  Loading fails loudly
+when the library has not been built: there is no fallback path.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import (POINTER, Structure, Union, byref, c_char, c_char_p, c_int32, c_int64, c_size_t, c_uint16, c_uint32,
+                    c_uint64, c_void_p)
+from pathlib import Path
+
+LIBRARY_PATH = Path(__file__).resolve().parent / "lib" / "libvecops_b200.so"
+
+# VecopsStatusCode
+OK, INVALID_ARGUMENT, NOT_APPLICABLE, NOT_FOUND, ABI_MISMATCH, LOAD_ERROR, EXECUTION_ERROR, INTERNAL_ERROR = range(8)
+STATUS_NAMES = ["OK", "INVALID_ARGUMENT", "NOT_APPLICABLE", "NOT_FOUND", "ABI_MISMATCH", "LOAD_ERROR", "EXECUTION_ERROR",
+                "INTERNAL_ERROR"]
+# VecopsDType
+DTYPE_I8, DTYPE_U8, DTYPE_I32, DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 2, 3, 6, 10, 11, 12
+DEVICE_CPU, DEVICE_CUDA = 1, 2
+VALUE_NONE, VALUE_TENSOR, VALUE_SCALAR = 0, 1, 2
+TENSOR_READ, TENSOR_WRITE = 1, 2
+# VecopsB200MatmulKernel
+KERNEL_AUTO, KERNEL_GENERIC, KERNEL_F32_SIMT, KERNEL_BF16_TCGEN05, KERNEL_I8_TCGEN05, KERNEL_W8_SMALL_M, KERNEL_W8_TCGEN05 = range(7)
+MATMUL_FLAG_ASYNC = 1
+CONTEXT_FLAG_ASYNC = 1 << 32
+
+
+class VecopsError(Structure):
+    _fields_ = [("struct_size", c_uint32), ("code", c_int32), ("message", c_void_p), ("message_capacity", c_size_t),
+                ("message_required", c_size_t)]
+
+
+class VecopsTensorView(Structure):
+    _fields_ = [("struct_size", c_uint32), ("data", c_void_p), ("byte_offset", c_uint64), ("device_type", c_uint32),
+                ("device_index", c_int32), ("dtype", c_uint32), ("rank", c_uint32), ("sizes", POINTER(c_int64)),
+                ("strides", POINTER(c_int64)), ("flags", c_uint64)]
+
+
+class VecopsScalarStorage(Union):
+    _fields_ = [("i64", c_int64), ("u64", c_uint64), ("f64", ctypes.c_double)]
+
+
+class VecopsScalar(Structure):
+    _fields_ = [("struct_size", c_uint32), ("dtype", c_uint32), ("value", VecopsScalarStorage)]
+
+
+class _ValueUnion(Union):
+    _fields_ = [("tensor", VecopsTensorView), ("scalar", VecopsScalar)]
+
+
+class VecopsValue(Structure):
+    _fields_ = [("struct_size", c_uint32), ("kind", c_uint32), ("value", _ValueUnion)]
+
+
+class VecopsExecutionContext(Structure):
+    _fields_ = [("struct_size", c_uint32), ("requested_threads", c_uint32), ("stream", c_void_p), ("user_data", c_void_p),
+                ("flags", c_uint64), ("workspace_provider", c_void_p), ("thread_pool", c_void_p),
+                ("allocation_observer", c_void_p)]
+
+
+class VecopsCall(Structure):
+    _fields_ = [("struct_size", c_uint32), ("num_values", c_uint32), ("values", POINTER(VecopsValue)),
+                ("workspace", c_void_p), ("workspace_size", c_uint64), ("context", POINTER(VecopsExecutionContext))]
+
+
+class VecopsB200Matmul(Structure):
+    _fields_ = [("struct_size", c_uint32), ("kernel", c_uint32), ("m", c_int64), ("n", c_int64), ("k", c_int64),
+                ("a", c_void_p), ("a_stride_m", c_int64), ("a_stride_k", c_int64),
+                ("b", c_void_p), ("b_stride_n", c_int64), ("b_stride_k", c_int64),
+                ("c", c_void_p), ("c_stride_m", c_int64), ("c_stride_n", c_int64),
+                ("column_scale", c_void_p), ("workspace", c_void_p), ("workspace_size", c_uint64), ("stream", c_void_p),
+                ("a_dtype", c_uint32), ("b_dtype", c_uint32), ("c_dtype", c_uint32), ("device_index", c_int32),
+                ("flags", c_uint32), ("reserved", c_uint32)]
+
+
+class VecopsB200DeviceInfo(Structure):
+    _fields_ = [("struct_size", c_uint32), ("sm_major", c_int32), ("sm_minor", c_int32), ("sm_count", c_int32),
+                ("l2_bytes", c_uint64), ("hbm_bytes", c_uint64), ("smem_per_block_optin", c_uint64), ("name", c_char * 64)]
+
+
+class VecopsB200Error(RuntimeError):
+    def __init__(self, code: int, message: str) -> None:
+        super().__init__(f"{STATUS_NAMES[code] if 0 <= code < len(STATUS_NAMES) else code}: {message}")
+        self.code = code
+        self.message = message
+
+
+class ErrorBuffer:
+    """Caller-owned VecopsError with a 1 KiB message buffer (the size vecops' runtime uses)."""
+
+    def __init__(self) -> None:
+        self.text = ctypes.create_string_buffer(1024)
+        self.record = VecopsError(ctypes.sizeof(VecopsError), 0, ctypes.cast(self.text, c_void_p), 1024, 0)
+
+    def raise_for(self, code: int) -> None:
+        if code != OK:
+            raise VecopsB200Error(code, self.text.value.decode(errors="replace"))
+
+
+_LIB = None
+
+
+def library() -> ctypes.CDLL:
+    """Load libvecops_b200.so once; raise if it has not been built."""
+    global _LIB
+    if _LIB is None:
+        if not LIBRARY_PATH.exists():
+            raise RuntimeError(f"{LIBRARY_PATH} is missing: build it with `python -m vecops_b200._build` "
+                               "(there is no fallback path)")
+        lib = ctypes.CDLL(str(LIBRARY_PATH))
+        e = POINTER(VecopsError)
+        lib.vecops_b200_matmul_select.argtypes = [POINTER(VecopsB200Matmul), POINTER(c_uint32), e]
+        lib.vecops_b200_matmul_workspace.argtypes = [POINTER(VecopsB200Matmul), POINTER(c_uint64), e]
+        lib.vecops_b200_matmul_run.argtypes = [POINTER(VecopsB200Matmul), e]
+        lib.vecops_b200_kernel_name.argtypes = [c_uint32]
+        lib.vecops_b200_kernel_name.restype = c_char_p
+        lib.vecops_b200_device_count.restype = c_int32
+        lib.vecops_b200_device_info.argtypes = [c_int32, POINTER(VecopsB200DeviceInfo), e]
+        lib.vecops_b200_launch_count.restype = c_uint64
+        lib.vecops_b200_take_device_status.argtypes = [c_int32, POINTER(c_uint32), e]
+        lib.vecops_b200_place_columns.argtypes = [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
+                                                  c_uint32, c_void_p, e]
+        _LIB = lib
+    return _LIB

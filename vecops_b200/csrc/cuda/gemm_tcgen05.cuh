@@ -1,0 +1,328 @@
+// Dense GEMM C[M,N] = A[M,K] . B[N,K]^T on the 5th-generation tensor cores.
+//
+// One persistent CTA per SM walks 128x256 output tiles.  Roles:
+//   warp 0    TMA producer: A (128 x 128 B) and B (256 x 128 B) k-blocks into a
+//             4-stage shared-memory ring, 128-byte swizzle, mbarrier full/empty
+//   warp 1    owns TMEM (512 columns = two 128x256 fp32/int32 accumulators) and
+//             issues tcgen05.mma from one thread; tcgen05.commit releases smem
+//             stages and publishes finished accumulators
+//   warps 2-5 epilogue: tcgen05.ld their TMEM lane quarter, convert, and either
+//             stage 32-row x 128-byte slabs in swizzled smem for TMA stores or
+//             store straight to global (ragged / unaligned C)
+// The second accumulator lets the epilogue of tile i overlap the main loop of
+// tile i+1.  kind::f16 (bf16 in, fp32 accumulate) and kind::i8 (8-bit in, int32
+// accumulate) share this file; the operand formats arrive in the instruction
+// descriptor.
+//
+// Algorithmic traffic per launch: (M*K + N*K) * sizeof(in) + M*N * sizeof(out).
+#pragma once
+
+#include "ptx.cuh"
+
+namespace vb200 {
+
+struct GemmTc {
+  static constexpr int kBlockM = 128;
+  static constexpr int kBlockN = 256;
+  static constexpr int kBlockKBytes = 128;  // one swizzle atom along K
+  static constexpr int kStages = 4;
+  static constexpr int kABytes = kBlockM * kBlockKBytes;
+  static constexpr int kBBytes = kBlockN * kBlockKBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kEpiWarps = 4;
+  static constexpr int kEpiBufBytes = 32 * 128;  // 32 rows x 128 bytes
+  static constexpr int kEpiBytes = kEpiWarps * 2 * kEpiBufBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarrierBytes + 1024;  // + alignment slack
+  static constexpr int kThreads = 32 * (2 + kEpiWarps);
+  static constexpr int kTmemColumns = 512;
+  static constexpr int kGroupM = 16;  // raster: 16 row-tiles share each sweep over N
+};
+
+// Device status codes ORed into the status word by a wait that ran out.
+enum : uint32_t {
+  kStatusProducerWait = 1u << 0,
+  kStatusMmaWaitFull = 1u << 1,
+  kStatusMmaWaitTmem = 1u << 2,
+  kStatusEpilogueWait = 1u << 3,
+  kStatusW8Wait = 1u << 4,
+};
+
+// The status word lives in pinned host memory mapped into the device: a plain
+// system-scope store is enough, it only ever happens when a wait ran out.
+__device__ __forceinline__ void report_status(uint32_t* status, uint32_t code) {
+  *reinterpret_cast<volatile uint32_t*>(status) = code;
+  __threadfence_system();
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_group = GemmTc::kGroupM * tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * GemmTc::kGroupM;
+  const int group_rows = min(tiles_m - first_m, GemmTc::kGroupM);
+  const int in_group = tile - group * per_group;
+  tm = first_m + in_group % group_rows;
+  tn = in_group / group_rows;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// OutT: __nv_bfloat16 or float for kind::f16, int32_t for kind::i8.
+template <bool kInt8, typename OutT>
+__global__ void __launch_bounds__(GemmTc::kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const __grid_constant__ CUtensorMap tma_c, OutT* __restrict__ c, long long ldc, int M, int N,
+                    int K, const float* __restrict__ column_scale, uint32_t idesc, int use_tma_store,
+                    uint32_t* __restrict__ status) {
+  using G = GemmTc;
+  constexpr int kElemBytes = kInt8 ? 1 : 2;
+  constexpr int kBlockK = G::kBlockKBytes / kElemBytes;  // elements per k-block
+  constexpr int kOutCols = 128 / static_cast<int>(sizeof(OutT));  // columns per 128-byte slab row
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t epi_base = smem_base + G::kStages * G::kStageBytes;
+  uint8_t* bar_gen = smem_gen + G::kStages * G::kStageBytes + G::kEpiBytes;
+  const uint32_t bar_base = epi_base + G::kEpiBytes;
+  // barrier block: full[4] empty[4] tmem_full[2] tmem_empty[2] | tmem slot | abort flag
+  const uint32_t full_bar = bar_base;
+  const uint32_t empty_bar = bar_base + 8 * G::kStages;
+  const uint32_t tmem_full_bar = bar_base + 16 * G::kStages;
+  const uint32_t tmem_empty_bar = tmem_full_bar + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_gen + 16 * G::kStages + 32);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bar_gen + 16 * G::kStages + 36);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (M + G::kBlockM - 1) / G::kBlockM;
+  const int tiles_n = (N + G::kBlockN - 1) / G::kBlockN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + kBlockK - 1) / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < G::kStages; ++s) {
+      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(empty_bar + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar + 8 * a, 1);
+      mbar_init(tmem_empty_bar + 8 * a, G::kEpiWarps * 32);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_descriptor(&tma_a);
+    tma_prefetch_descriptor(&tma_b);
+    if (use_tma_store) tma_prefetch_descriptor(&tma_c);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), G::kTmemColumns);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag)) {
+            report_status(status, kStatusProducerWait);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * G::kStageBytes;
+          const uint32_t b_dst = a_dst + G::kABytes;
+          mbar_arrive_expect_tx(full_bar + 8 * stage, G::kStageBytes);
+          tma_load_2d(a_dst, &tma_a, full_bar + 8 * stage, kb * kBlockK, tm * G::kBlockM);
+          tma_load_2d(b_dst, &tma_b, full_bar + 8 * stage, kb * kBlockK, tn * G::kBlockN);
+          if (++stage == G::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag)) {
+          report_status(status, kStatusMmaWaitTmem);
+          *abort_flag = 1;
+          break;
+        }
+        tcgen05_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * G::kBlockN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag)) {
+            report_status(status, kStatusMmaWaitFull);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after_sync();
+          const uint32_t a_src = smem_base + stage * G::kStageBytes;
+          const uint64_t a_desc = umma_smem_desc_sw128(a_src);
+          const uint64_t b_desc = umma_smem_desc_sw128(a_src + G::kABytes);
+#pragma unroll
+          for (int kk = 0; kk < G::kBlockKBytes / 32; ++kk) {
+            // +32 bytes along K inside the swizzle atom = +2 in the address field
+            const uint32_t accumulate = (kb | kk) != 0 ? 1u : 0u;
+            if (kInt8) umma_i8(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accumulate);
+            else umma_f16(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accumulate);
+          }
+          umma_commit(empty_bar + 8 * stage);
+          if (++stage == G::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(tmem_full_bar + 8 * acc);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
+    const int epi_warp = warp - 2;
+    const uint32_t my_buf = epi_base + epi_warp * 2 * G::kEpiBufBytes;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int buf_sel = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag)) {
+        report_status(status, kStatusEpilogueWait);
+        *abort_flag = 1;
+        break;
+      }
+      tcgen05_fence_after_sync();
+      const int row0 = tm * G::kBlockM + quarter * 32;
+      const int row = row0 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * G::kBlockN;
+#pragma unroll 1
+      for (int slab = 0; slab < G::kBlockN / kOutCols; ++slab) {
+        const int col0 = tn * G::kBlockN + slab * kOutCols;
+        if (col0 >= N) break;  // uniform across the warp
+        uint32_t words[32];    // 128 bytes of converted output for this thread's row
+        if constexpr (sizeof(OutT) == 4) {
+          tmem_load_32x32(taddr + slab * 32, words);
+          tmem_load_wait();
+          if constexpr (!kInt8) {
+            if (column_scale != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float s = (col0 + j < N) ? __ldg(column_scale + col0 + j) : 0.f;
+                words[j] = __float_as_uint(__uint_as_float(words[j]) * s);
+              }
+            }
+          }
+        } else {
+          uint32_t v0[32], v1[32];
+          tmem_load_32x32(taddr + slab * 64, v0);
+          tmem_load_32x32(taddr + slab * 64 + 32, v1);
+          tmem_load_wait();
+          if (column_scale != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float s0 = (col0 + j < N) ? __ldg(column_scale + col0 + j) : 0.f;
+              const float s1 = (col0 + 32 + j < N) ? __ldg(column_scale + col0 + 32 + j) : 0.f;
+              v0[j] = __float_as_uint(__uint_as_float(v0[j]) * s0);
+              v1[j] = __float_as_uint(__uint_as_float(v1[j]) * s1);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            words[j] = pack_bf16x2(__uint_as_float(v0[2 * j]), __uint_as_float(v0[2 * j + 1]));
+            words[16 + j] = pack_bf16x2(__uint_as_float(v1[2 * j]), __uint_as_float(v1[2 * j + 1]));
+          }
+        }
+        if (use_tma_store) {
+          const uint32_t buf = my_buf + buf_sel * G::kEpiBufBytes;
+          // the store issued two slabs ago from this buffer must have read it
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t dst = buf + lane * 128 + ((j ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(words[4 * j]),
+                         "r"(words[4 * j + 1]), "r"(words[4 * j + 2]), "r"(words[4 * j + 3])
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tma_c, buf, col0, row0);
+            tma_store_commit();
+          }
+          buf_sel ^= 1;
+        } else if (row < M) {
+          OutT* dst = c + static_cast<long long>(row) * ldc + col0;
+          const int valid = min(kOutCols, N - col0);
+          const bool vec = valid == kOutCols && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+          if (vec) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              reinterpret_cast<uint4*>(dst)[j] =
+                  make_uint4(words[4 * j], words[4 * j + 1], words[4 * j + 2], words[4 * j + 3]);
+          } else {
+            // ragged or unaligned edge: element stores, indices kept static so
+            // that `words` stays in registers
+#pragma unroll
+            for (int j = 0; j < kOutCols; ++j) {
+              if (j < valid) {
+                if constexpr (sizeof(OutT) == 4) {
+                  reinterpret_cast<uint32_t*>(dst)[j] = words[j];
+                } else {
+                  reinterpret_cast<uint16_t*>(dst)[j] = static_cast<uint16_t>(words[j >> 1] >> (16 * (j & 1)));
+                }
+              }
+            }
+          }
+        }
+      }
+      tcgen05_fence_before_sync();
+      mbar_arrive(tmem_empty_bar + 8 * acc);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    if (use_tma_store && lane == 0) tma_store_wait_all<0>();
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncthreads();
+  if (*abort_flag != 0) {
+    // A wait ran out: give copies and MMAs still in flight time to land
+    // before shared memory and TMEM go back to the SM.
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc(tmem_base, G::kTmemColumns);
+  }
+}
+
+}  // namespace vb200

@@ -1,0 +1,582 @@
+// Host side of the thin C ABI over the sm_100a matmul kernels: argument
+// checks, the shape/dtype dispatch rules, tensor-map construction and the
+// launches.  No CPU arithmetic lives here: a problem either runs on the GPU
+// or the call fails.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <type_traits>
+#include <unordered_map>
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_runtime.h>
+
+#include "vecops_b200/matmul_cuda.h"
+
+#include "gemm_tcgen05.cuh"
+#include "simt_kernels.cuh"
+#include "w8_small_m.cuh"
+#include "shim_util.h"
+
+namespace vb200 {
+
+std::atomic<uint64_t> g_launches{0};
+
+int32_t set_error(VecopsError* error, int32_t code, const char* format, ...) {
+  char text[512];
+  va_list args;
+  va_start(args, format);
+  const int wanted = vsnprintf(text, sizeof(text), format, args);
+  va_end(args);
+  if (error != nullptr && error->struct_size >= sizeof(VecopsError)) {
+    error->code = code;
+    error->message_required = static_cast<size_t>(wanted < 0 ? 0 : wanted) + 1;
+    if (error->message != nullptr && error->message_capacity > 0) {
+      snprintf(error->message, error->message_capacity, "%s", text);
+    }
+  }
+  return code;
+}
+
+namespace {
+
+// ------------------------------------------------------------------ device bookkeeping
+
+struct DeviceState {
+  bool known = false;
+  cudaDeviceProp prop{};
+};
+
+std::mutex g_mutex;
+DeviceState g_devices[64];
+uint32_t* g_status_host = nullptr;  // pinned, mapped; kernels write here only when a wait ran out
+PFN_cuTensorMapEncodeTiled_v12000 g_encode_tiled = nullptr;
+
+int32_t cuda_fail(VecopsError* error, cudaError_t status, const char* what) {
+  return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "%s: %s", what, cudaGetErrorString(status));
+}
+
+int32_t device_state(int device, const DeviceState** out, VecopsError* error) {
+  if (device < 0 || device >= 64) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "device index %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState& state = g_devices[device];
+  if (!state.known) {
+    cudaError_t status = cudaGetDeviceProperties(&state.prop, device);
+    if (status != cudaSuccess) return cuda_fail(error, status, "cudaGetDeviceProperties");
+    state.known = true;
+  }
+  if (g_status_host == nullptr) {
+    void* p = nullptr;
+    cudaError_t status = cudaHostAlloc(&p, 64, cudaHostAllocMapped | cudaHostAllocPortable);
+    if (status != cudaSuccess) return cuda_fail(error, status, "cudaHostAlloc(status word)");
+    memset(p, 0, 64);
+    g_status_host = static_cast<uint32_t*>(p);
+  }
+  if (g_encode_tiled == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    cudaError_t status = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &query);
+    if (status != cudaSuccess || fn == nullptr || query != cudaDriverEntryPointSuccess)
+      return set_error(error, VECOPS_STATUS_LOAD_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
+    g_encode_tiled = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  }
+  *out = &state;
+  return VECOPS_STATUS_OK;
+}
+
+int32_t current_device(const VecopsB200Matmul& p, int* device, VecopsError* error) {
+  int count = 0;
+  cudaError_t status = cudaGetDeviceCount(&count);
+  if (status != cudaSuccess || count == 0) {
+    (void)cudaGetLastError();
+    return set_error(error, VECOPS_STATUS_EXECUTION_ERROR,
+                     "no usable CUDA device (%s); the B200 matmul path has no CPU fallback",
+                     status == cudaSuccess ? "device count is 0" : cudaGetErrorString(status));
+  }
+  if (p.device_index >= 0) {
+    if (p.device_index >= count)
+      return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "device index %d but only %d devices", p.device_index, count);
+    *device = p.device_index;
+    return VECOPS_STATUS_OK;
+  }
+  status = cudaGetDevice(device);
+  if (status != cudaSuccess) return cuda_fail(error, status, "cudaGetDevice");
+  return VECOPS_STATUS_OK;
+}
+
+// ------------------------------------------------------------------ problem classification
+
+enum class Row { Invalid, F32, BF16, I8, W8 };
+
+size_t dtype_size(uint32_t dtype) {
+  switch (dtype) {
+    case VECOPS_DTYPE_I8: case VECOPS_DTYPE_U8: return 1;
+    case VECOPS_DTYPE_BF16: case VECOPS_DTYPE_F16: return 2;
+    case VECOPS_DTYPE_F32: case VECOPS_DTYPE_I32: return 4;
+    default: return 0;
+  }
+}
+
+Row classify(const VecopsB200Matmul& p) {
+  const uint32_t a = p.a_dtype, b = p.b_dtype, c = p.c_dtype;
+  const bool a8 = a == VECOPS_DTYPE_I8 || a == VECOPS_DTYPE_U8;
+  const bool b8 = b == VECOPS_DTYPE_I8 || b == VECOPS_DTYPE_U8;
+  if (a == VECOPS_DTYPE_F32 && b == VECOPS_DTYPE_F32 && c == VECOPS_DTYPE_F32) return Row::F32;
+  if (a == VECOPS_DTYPE_BF16 && b == VECOPS_DTYPE_BF16 && (c == VECOPS_DTYPE_BF16 || c == VECOPS_DTYPE_F32)) return Row::BF16;
+  if (a8 && b8 && c == VECOPS_DTYPE_I32) return Row::I8;
+  if (a == VECOPS_DTYPE_BF16 && b == VECOPS_DTYPE_I8 && (c == VECOPS_DTYPE_BF16 || c == VECOPS_DTYPE_F32)) return Row::W8;
+  return Row::Invalid;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Can the TMA-fed tensor-core kernel address these operands?  Both operands
+// K-contiguous, 16-byte aligned bases and row pitches (TMA's rules), and
+// extents inside the tensor-map limits.
+bool tma_operands_ok(const VecopsB200Matmul& p, size_t elem) {
+  return p.a_stride_k == 1 && p.b_stride_k == 1 && p.c_stride_n == 1 && p.k > 0 && aligned16(p.a) && aligned16(p.b) &&
+         (p.a_stride_m * static_cast<int64_t>(elem)) % 16 == 0 && (p.b_stride_n * static_cast<int64_t>(elem)) % 16 == 0 &&
+         p.a_stride_m >= p.k && p.b_stride_n >= p.k && p.c_stride_m >= p.n && p.m < (INT64_C(1) << 31) &&
+         p.n < (INT64_C(1) << 31) && p.k < (INT64_C(1) << 31);
+}
+
+// Device counterpart of vecops' small-problem predicate
+// (RuntimeDispatch.h:24-27 `area_at_most`): tiny outputs are not worth a
+// 128x256 tensor-core tile.
+bool area_at_most(int64_t m, int64_t n, int64_t limit) { return m > 0 && n > 0 && n <= limit / m; }
+
+bool applicable(const VecopsB200Matmul& p, Row row, uint32_t kernel) {
+  switch (kernel) {
+    case VECOPS_B200_KERNEL_GENERIC:
+      return true;
+    case VECOPS_B200_KERNEL_F32_SIMT:
+      return row == Row::F32 && p.a_stride_k == 1 && p.c_stride_n == 1 && (p.b_stride_k == 1 || p.b_stride_n == 1) &&
+             p.column_scale == nullptr;
+    case VECOPS_B200_KERNEL_BF16_TCGEN05:
+      return row == Row::BF16 && tma_operands_ok(p, 2);
+    case VECOPS_B200_KERNEL_I8_TCGEN05:
+      return row == Row::I8 && tma_operands_ok(p, 1) && p.column_scale == nullptr;
+    case VECOPS_B200_KERNEL_W8_SMALL_M:
+      return row == Row::W8 && p.a_stride_k == 1 && p.b_stride_k == 1 && p.k > 0 && p.k % 32 == 0 && aligned16(p.a) &&
+             aligned16(p.b) && p.a_stride_m % 8 == 0 && p.b_stride_n % 16 == 0 && p.n < (INT64_C(1) << 31) &&
+             p.m < (INT64_C(1) << 31) && p.k < (INT64_C(1) << 31);
+    case VECOPS_B200_KERNEL_W8_TCGEN05:
+      return false;  // reserved: selected nowhere until the kernel exists
+    default:
+      return false;
+  }
+}
+
+const char* const kKernelNames[VECOPS_B200_KERNEL_COUNT_] = {
+    "auto", "generic", "f32_simt", "bf16_tcgen05", "i8_tcgen05", "w8_small_m", "w8_tcgen05"};
+
+uint32_t forced_by_environment() {
+  const char* text = getenv("VECOPS_B200_FORCE_KERNEL");
+  if (text == nullptr || text[0] == '\0') return VECOPS_B200_KERNEL_AUTO;
+  for (uint32_t k = 1; k < VECOPS_B200_KERNEL_COUNT_; ++k)
+    if (strcmp(text, kKernelNames[k]) == 0) return k;
+  return VECOPS_B200_KERNEL_AUTO;
+}
+
+int32_t check_problem(const VecopsB200Matmul* p, Row* row, VecopsError* error) {
+  if (p == nullptr) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "problem record is null");
+  if (p->struct_size < sizeof(VecopsB200Matmul))
+    return set_error(error, VECOPS_STATUS_ABI_MISMATCH, "problem record is %u bytes, this library needs %zu", p->struct_size,
+                     sizeof(VecopsB200Matmul));
+  if (p->m < 0 || p->n < 0 || p->k < 0) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "negative extent m=%lld n=%lld k=%lld",
+                                                          (long long)p->m, (long long)p->n, (long long)p->k);
+  *row = classify(*p);
+  if (*row == Row::Invalid)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "unsupported dtype combination a=%u b=%u c=%u", p->a_dtype, p->b_dtype,
+                     p->c_dtype);
+  if (p->column_scale != nullptr && *row == Row::I8)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "column_scale applies to f32 accumulators only");
+  if (p->kernel >= VECOPS_B200_KERNEL_COUNT_) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "unknown kernel id %u", p->kernel);
+  return VECOPS_STATUS_OK;
+}
+
+int32_t select_kernel(const VecopsB200Matmul& p, Row row, uint32_t* kernel, VecopsError* error) {
+  uint32_t wanted = p.kernel != VECOPS_B200_KERNEL_AUTO ? p.kernel : forced_by_environment();
+  if (wanted != VECOPS_B200_KERNEL_AUTO) {
+    if (!applicable(p, row, wanted))
+      return set_error(error, VECOPS_STATUS_NOT_APPLICABLE, "kernel '%s' cannot serve this problem (dtypes, strides or alignment)",
+                       kKernelNames[wanted]);
+    *kernel = wanted;
+    return VECOPS_STATUS_OK;
+  }
+  uint32_t pick = VECOPS_B200_KERNEL_GENERIC;
+  const bool tiny = p.m == 0 || p.n == 0 || p.k == 0 || area_at_most(p.m, p.n, 1024);
+  switch (row) {
+    case Row::F32:
+      if (!tiny && applicable(p, row, VECOPS_B200_KERNEL_F32_SIMT)) pick = VECOPS_B200_KERNEL_F32_SIMT;
+      break;
+    case Row::BF16:
+      if (!tiny && applicable(p, row, VECOPS_B200_KERNEL_BF16_TCGEN05)) pick = VECOPS_B200_KERNEL_BF16_TCGEN05;
+      break;
+    case Row::I8:
+      // int32 accumulators must wrap modulo 2^32 (vecops semantic); the tensor
+      // pipe is used where |sum| < 2^31 is guaranteed: K * 2^16 < 2^31.
+      if (!tiny && p.k <= 32767 && applicable(p, row, VECOPS_B200_KERNEL_I8_TCGEN05)) pick = VECOPS_B200_KERNEL_I8_TCGEN05;
+      break;
+    case Row::W8:
+      if (p.m > 0 && p.n >= 16 && applicable(p, row, VECOPS_B200_KERNEL_W8_SMALL_M)) pick = VECOPS_B200_KERNEL_W8_SMALL_M;
+      break;
+    default:
+      break;
+  }
+  *kernel = pick;
+  return VECOPS_STATUS_OK;
+}
+
+// ------------------------------------------------------------------ tensor maps
+
+struct MapKey {
+  const void* base;
+  uint64_t dim0, dim1, pitch;
+  uint32_t box0, box1, dtype, swizzle;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && dim0 == o.dim0 && dim1 == o.dim1 && pitch == o.pitch && box0 == o.box0 && box1 == o.box1 &&
+           dtype == o.dtype && swizzle == o.swizzle;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base);
+    auto mix = [&](uint64_t v) { h = (h ^ v) * UINT64_C(0x9E3779B97F4A7C15); h ^= h >> 29; };
+    mix(k.dim0); mix(k.dim1); mix(k.pitch); mix(k.box0); mix(k.box1); mix(k.dtype); mix(k.swizzle);
+    return static_cast<size_t>(h);
+  }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+
+// 2-D row-major tensor [dim1 rows][dim0 contiguous elements], row pitch in bytes.
+int32_t make_map_2d(CUtensorMap* out, CUtensorMapDataType dtype, size_t elem, const void* base, uint64_t dim0, uint64_t dim1,
+                    uint64_t pitch_bytes, uint32_t box0, uint32_t box1, VecopsError* error) {
+  const MapKey key{base, dim0, dim1, pitch_bytes, box0, box1, static_cast<uint32_t>(dtype), 128};
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    auto found = g_map_cache.find(key);
+    if (found != g_map_cache.end()) {
+      *out = found->second;
+      return VECOPS_STATUS_OK;
+    }
+  }
+  cuuint64_t dims[2] = {dim0, dim1};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box0, box1};
+  cuuint32_t elem_strides[2] = {1, 1};
+  (void)elem;
+  CUresult result = g_encode_tiled(out, dtype, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (result != CUDA_SUCCESS)
+    return set_error(error, VECOPS_STATUS_EXECUTION_ERROR,
+                     "cuTensorMapEncodeTiled failed (%d) for dims=(%llu,%llu) pitch=%llu box=(%u,%u)", static_cast<int>(result),
+                     (unsigned long long)dim0, (unsigned long long)dim1, (unsigned long long)pitch_bytes, box0, box1);
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_map_cache.size() > 512) g_map_cache.clear();
+  g_map_cache.emplace(key, *out);
+  return VECOPS_STATUS_OK;
+}
+
+bool direct_epilogue_forced() {
+  const char* text = getenv("VECOPS_B200_EPILOGUE");
+  return text != nullptr && strcmp(text, "direct") == 0;
+}
+
+// ------------------------------------------------------------------ launches
+
+template <typename Kernel>
+int32_t raise_smem_limit(Kernel kernel, int bytes, VecopsError* error) {
+  cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (status != cudaSuccess) return cuda_fail(error, status, "cudaFuncSetAttribute(max dynamic shared memory)");
+  return VECOPS_STATUS_OK;
+}
+
+template <bool kInt8, typename OutT>
+int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaStream_t stream, VecopsError* error) {
+  using G = GemmTc;
+  if (dev.prop.major != 10)
+    return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "tcgen05 kernels need an sm_100 device, found sm_%d%d", dev.prop.major,
+                     dev.prop.minor);
+  constexpr size_t elem = kInt8 ? 1 : 2;
+  const CUtensorMapDataType in_type = kInt8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const uint32_t box_k = G::kBlockKBytes / elem;
+  CUtensorMap map_a, map_b, map_c;
+  int32_t rc = make_map_2d(&map_a, in_type, elem, p.a, p.k, p.m, p.a_stride_m * elem, box_k, G::kBlockM, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  rc = make_map_2d(&map_b, in_type, elem, p.b, p.k, p.n, p.b_stride_n * elem, box_k, G::kBlockN, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  const bool tma_store = !direct_epilogue_forced() && aligned16(p.c) && (p.c_stride_m * sizeof(OutT)) % 16 == 0;
+  if (tma_store) {
+    const CUtensorMapDataType out_type = std::is_same<OutT, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                         : std::is_same<OutT, float>::value       ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                                                  : CU_TENSOR_MAP_DATA_TYPE_INT32;
+    rc = make_map_2d(&map_c, out_type, sizeof(OutT), p.c, p.n, p.m, p.c_stride_m * sizeof(OutT), 128 / sizeof(OutT), 32, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+  } else {
+    map_c = map_a;  // never dereferenced
+  }
+  uint32_t idesc;
+  if (kInt8) {
+    idesc = umma_instr_desc(kUmmaAccS32, p.a_dtype == VECOPS_DTYPE_I8 ? kUmmaS8 : kUmmaU8,
+                            p.b_dtype == VECOPS_DTYPE_I8 ? kUmmaS8 : kUmmaU8, G::kBlockM, G::kBlockN);
+  } else {
+    idesc = umma_instr_desc(kUmmaAccF32, kUmmaBF16, kUmmaBF16, G::kBlockM, G::kBlockN);
+  }
+  auto kernel = gemm_tcgen05_kernel<kInt8, OutT>;
+  static std::atomic<bool> raised[64];
+  int device = 0;
+  cudaGetDevice(&device);
+  if (!raised[device].load()) {
+    rc = raise_smem_limit(kernel, G::kSmemBytes, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+    raised[device].store(true);
+  }
+  const long long tiles = ((p.m + G::kBlockM - 1) / G::kBlockM) * ((p.n + G::kBlockN - 1) / G::kBlockN);
+  const int grid = static_cast<int>(tiles < dev.prop.multiProcessorCount ? tiles : dev.prop.multiProcessorCount);
+  kernel<<<grid, G::kThreads, G::kSmemBytes, stream>>>(map_a, map_b, map_c, static_cast<OutT*>(p.c), p.c_stride_m,
+                                                       static_cast<int>(p.m), static_cast<int>(p.n), static_cast<int>(p.k),
+                                                       kInt8 ? nullptr : p.column_scale, idesc, tma_store ? 1 : 0, g_status_host);
+  g_launches.fetch_add(1);
+  return VECOPS_STATUS_OK;
+}
+
+template <typename TA, typename TB, typename TC, typename Acc>
+void launch_generic_typed(const VecopsB200Matmul& p, cudaStream_t stream) {
+  dim3 grid(static_cast<unsigned>((p.n + 31) / 32), static_cast<unsigned>((p.m + 31) / 32));
+  gemm_generic_kernel<TA, TB, TC, Acc><<<grid, 256, 0, stream>>>(
+      static_cast<const TA*>(p.a), p.a_stride_m, p.a_stride_k, static_cast<const TB*>(p.b), p.b_stride_n, p.b_stride_k,
+      static_cast<TC*>(p.c), p.c_stride_m, p.c_stride_n, static_cast<int>(p.m), static_cast<int>(p.n), static_cast<int>(p.k),
+      p.column_scale);
+  g_launches.fetch_add(1);
+}
+
+int32_t launch_generic(const VecopsB200Matmul& p, Row row, cudaStream_t stream, VecopsError* error) {
+  if (p.m >= (INT64_C(1) << 31) || p.n >= (INT64_C(1) << 31) || p.k >= (INT64_C(1) << 31) || (p.m + 31) / 32 > 65535)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "extent too large for the strided kernel");
+  using bf16 = __nv_bfloat16;
+  const bool c_bf16 = p.c_dtype == VECOPS_DTYPE_BF16;
+  switch (row) {
+    case Row::F32: launch_generic_typed<float, float, float, float>(p, stream); break;
+    case Row::BF16:
+      if (c_bf16) launch_generic_typed<bf16, bf16, bf16, float>(p, stream);
+      else launch_generic_typed<bf16, bf16, float, float>(p, stream);
+      break;
+    case Row::W8:
+      if (c_bf16) launch_generic_typed<bf16, int8_t, bf16, float>(p, stream);
+      else launch_generic_typed<bf16, int8_t, float, float>(p, stream);
+      break;
+    case Row::I8: {
+      const bool as = p.a_dtype == VECOPS_DTYPE_I8, bs = p.b_dtype == VECOPS_DTYPE_I8;
+      if (as && bs) launch_generic_typed<int8_t, int8_t, int32_t, uint32_t>(p, stream);
+      else if (as) launch_generic_typed<int8_t, uint8_t, int32_t, uint32_t>(p, stream);
+      else if (bs) launch_generic_typed<uint8_t, int8_t, int32_t, uint32_t>(p, stream);
+      else launch_generic_typed<uint8_t, uint8_t, int32_t, uint32_t>(p, stream);
+      break;
+    }
+    default: return set_error(error, VECOPS_STATUS_INTERNAL_ERROR, "unclassified problem reached the strided kernel");
+  }
+  return VECOPS_STATUS_OK;
+}
+
+template <int kMTiles, typename OutT>
+void launch_w8_small_typed(const VecopsB200Matmul& p, cudaStream_t stream) {
+  using G = W8SmallM;
+  dim3 grid(static_cast<unsigned>((p.n + G::kRowsPerCta - 1) / G::kRowsPerCta),
+            static_cast<unsigned>((p.m + 8 * kMTiles - 1) / (8 * kMTiles)));
+  w8_small_m_kernel<kMTiles, OutT><<<grid, G::kThreads, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(p.a), p.a_stride_m, static_cast<const int8_t*>(p.b), p.b_stride_n, p.column_scale,
+      static_cast<OutT*>(p.c), p.c_stride_m, static_cast<int>(p.m), static_cast<int>(p.n), static_cast<int>(p.k));
+  g_launches.fetch_add(1);
+}
+
+int32_t launch_w8_small(const VecopsB200Matmul& p, cudaStream_t stream, VecopsError* error) {
+  if (p.c_stride_n != 1) return set_error(error, VECOPS_STATUS_NOT_APPLICABLE, "w8_small_m needs a row-major C");
+  if ((p.m + 31) / 32 > 65535) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "M too large for w8_small_m");
+  const bool c_bf16 = p.c_dtype == VECOPS_DTYPE_BF16;
+  if (p.m <= 8) {
+    if (c_bf16) launch_w8_small_typed<1, __nv_bfloat16>(p, stream); else launch_w8_small_typed<1, float>(p, stream);
+  } else if (p.m <= 16) {
+    if (c_bf16) launch_w8_small_typed<2, __nv_bfloat16>(p, stream); else launch_w8_small_typed<2, float>(p, stream);
+  } else {
+    if (c_bf16) launch_w8_small_typed<4, __nv_bfloat16>(p, stream); else launch_w8_small_typed<4, float>(p, stream);
+  }
+  return VECOPS_STATUS_OK;
+}
+
+int32_t launch_f32(const VecopsB200Matmul& p, cudaStream_t stream, VecopsError* error) {
+  if ((p.m + 63) / 64 > 65535) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "M too large for f32_simt");
+  dim3 grid(static_cast<unsigned>((p.n + 63) / 64), static_cast<unsigned>((p.m + 63) / 64));
+  gemm_f32_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(p.a), p.a_stride_m, static_cast<const float*>(p.b), p.b_stride_n,
+                                            p.b_stride_k, static_cast<float*>(p.c), p.c_stride_m, static_cast<int>(p.m),
+                                            static_cast<int>(p.n), static_cast<int>(p.k));
+  g_launches.fetch_add(1);
+  return VECOPS_STATUS_OK;
+}
+
+}  // namespace
+}  // namespace vb200
+
+using namespace vb200;
+
+extern "C" {
+
+int32_t vecops_b200_matmul_select(const VecopsB200Matmul* problem, uint32_t* kernel, VecopsError* error) {
+  Row row;
+  int32_t rc = check_problem(problem, &row, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  if (kernel == nullptr) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "kernel output pointer is null");
+  return select_kernel(*problem, row, kernel, error);
+}
+
+int32_t vecops_b200_matmul_workspace(const VecopsB200Matmul* problem, uint64_t* bytes, VecopsError* error) {
+  Row row;
+  int32_t rc = check_problem(problem, &row, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  if (bytes == nullptr) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "bytes output pointer is null");
+  uint32_t kernel;
+  rc = select_kernel(*problem, row, &kernel, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  // Split-K of the kernels built so far meets in shared memory; none needs device scratch.
+  *bytes = 0;
+  return VECOPS_STATUS_OK;
+}
+
+int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* error) {
+  Row row;
+  int32_t rc = check_problem(problem, &row, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  const VecopsB200Matmul& p = *problem;
+  uint32_t kernel;
+  rc = select_kernel(p, row, &kernel, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  if (p.m == 0 || p.n == 0) return VECOPS_STATUS_OK;
+  if (p.c == nullptr || (p.k > 0 && (p.a == nullptr || p.b == nullptr)))
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "a, b or c is null for a non-empty problem");
+
+  int device = 0;
+  rc = current_device(p, &device, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  int previous = -1;
+  cudaGetDevice(&previous);
+  if (previous != device) {
+    cudaError_t status = cudaSetDevice(device);
+    if (status != cudaSuccess) return cuda_fail(error, status, "cudaSetDevice");
+  }
+  const DeviceState* dev = nullptr;
+  rc = device_state(device, &dev, error);
+  cudaStream_t stream = static_cast<cudaStream_t>(p.stream);
+
+  if (rc == VECOPS_STATUS_OK) {
+    if (p.k == 0) {
+      // empty reduction: C = 0 (include/vecops/ops/Matmul.h:41-43)
+      const size_t esz = dtype_size(p.c_dtype);
+      const long long total = p.m * p.n;
+      const int blocks = static_cast<int>(total / 256 + 1 < 4096 ? total / 256 + 1 : 4096);
+      fill_zero_kernel<<<blocks, 256, 0, stream>>>(static_cast<uint8_t*>(p.c), p.c_stride_m * esz, p.c_stride_n * esz,
+                                                   static_cast<int>(esz), p.m, p.n);
+      g_launches.fetch_add(1);
+    } else {
+      switch (kernel) {
+        case VECOPS_B200_KERNEL_GENERIC: rc = launch_generic(p, row, stream, error); break;
+        case VECOPS_B200_KERNEL_F32_SIMT: rc = launch_f32(p, stream, error); break;
+        case VECOPS_B200_KERNEL_BF16_TCGEN05:
+          rc = p.c_dtype == VECOPS_DTYPE_BF16 ? launch_tcgen05<false, __nv_bfloat16>(p, *dev, stream, error)
+                                              : launch_tcgen05<false, float>(p, *dev, stream, error);
+          break;
+        case VECOPS_B200_KERNEL_I8_TCGEN05: rc = launch_tcgen05<true, int32_t>(p, *dev, stream, error); break;
+        case VECOPS_B200_KERNEL_W8_SMALL_M: rc = launch_w8_small(p, stream, error); break;
+        default: rc = set_error(error, VECOPS_STATUS_INTERNAL_ERROR, "kernel id %u has no launcher", kernel);
+      }
+    }
+  }
+  if (rc == VECOPS_STATUS_OK) {
+    cudaError_t status = cudaGetLastError();
+    if (status != cudaSuccess) rc = cuda_fail(error, status, "kernel launch");
+  }
+  if (rc == VECOPS_STATUS_OK && (p.flags & VECOPS_B200_MATMUL_FLAG_ASYNC) == 0) {
+    cudaError_t status = cudaStreamSynchronize(stream);
+    if (status != cudaSuccess) {
+      rc = cuda_fail(error, status, "cudaStreamSynchronize");
+    } else if (g_status_host != nullptr && *reinterpret_cast<volatile uint32_t*>(g_status_host) != 0) {
+      const uint32_t word = *reinterpret_cast<volatile uint32_t*>(g_status_host);
+      *reinterpret_cast<volatile uint32_t*>(g_status_host) = 0;
+      rc = set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "kernel '%s': a bounded device wait ran out (status 0x%x)",
+                     kKernelNames[kernel], word);
+    }
+  }
+  if (previous >= 0 && previous != device) cudaSetDevice(previous);
+  return rc;
+}
+
+const char* vecops_b200_kernel_name(uint32_t kernel) {
+  return kernel < VECOPS_B200_KERNEL_COUNT_ ? kKernelNames[kernel] : nullptr;
+}
+
+int32_t vecops_b200_device_count(void) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return count;
+}
+
+int32_t vecops_b200_device_info(int32_t device_index, VecopsB200DeviceInfo* info, VecopsError* error) {
+  if (info == nullptr || info->struct_size < sizeof(VecopsB200DeviceInfo))
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "device info record is null or too small");
+  if (device_index < 0 || device_index >= vecops_b200_device_count())
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "no CUDA device %d", device_index);
+  cudaDeviceProp prop;
+  cudaError_t status = cudaGetDeviceProperties(&prop, device_index);
+  if (status != cudaSuccess) return cuda_fail(error, status, "cudaGetDeviceProperties");
+  info->sm_major = prop.major;
+  info->sm_minor = prop.minor;
+  info->sm_count = prop.multiProcessorCount;
+  info->l2_bytes = static_cast<uint64_t>(prop.l2CacheSize);
+  info->hbm_bytes = static_cast<uint64_t>(prop.totalGlobalMem);
+  info->smem_per_block_optin = static_cast<uint64_t>(prop.sharedMemPerBlockOptin);
+  snprintf(info->name, sizeof(info->name), "%.63s", prop.name);
+  return VECOPS_STATUS_OK;
+}
+
+uint64_t vecops_b200_launch_count(void) { return g_launches.load(); }
+
+int32_t vecops_b200_take_device_status(int32_t device_index, uint32_t* status, VecopsError* error) {
+  (void)device_index;
+  if (status == nullptr) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "status output pointer is null");
+  *status = 0;
+  if (g_status_host != nullptr) {
+    *status = *reinterpret_cast<volatile uint32_t*>(g_status_host);
+    *reinterpret_cast<volatile uint32_t*>(g_status_host) = 0;
+  }
+  return VECOPS_STATUS_OK;
+}
+
+int32_t vecops_b200_place_columns(void* dst, int64_t ldd, int64_t col0, const void* src, int64_t lds, int64_t rows,
+                                  int64_t cols, uint32_t elem_size, void* stream, VecopsError* error) {
+  if (rows == 0 || cols == 0) return VECOPS_STATUS_OK;
+  if (dst == nullptr || src == nullptr || rows < 0 || cols < 0 || elem_size == 0)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "place_columns: null pointer or negative extent");
+  if (vecops_b200_device_count() == 0)
+    return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "no usable CUDA device; there is no CPU fallback");
+  const int64_t e = elem_size;
+  if (!aligned16(dst) || !aligned16(src) || (ldd * e) % 16 || (lds * e) % 16 || (col0 * e) % 16 || (cols * e) % 16)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "place_columns needs 16-byte aligned slabs and pitches");
+  const long long total = rows * (cols * e / 16);
+  const int blocks = static_cast<int>(total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
+  place_columns_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint4*>(dst), ldd * e / 16, col0 * e / 16, static_cast<const uint4*>(src), lds * e / 16, rows, cols * e / 16);
+  g_launches.fetch_add(1);
+  cudaError_t status = cudaGetLastError();
+  if (status != cudaSuccess) return cuda_fail(error, status, "place_columns launch");
+  return VECOPS_STATUS_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,224 @@
+// CUDA-core kernels: the strided any-dtype GEMM that serves ragged and
+// unaligned problems, and the tiled FP32 FMA GEMM.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace vb200 {
+
+// ------------------------------------------------------------------ element conversion
+
+template <typename Acc, typename T>
+__device__ __forceinline__ Acc load_as(const T* p) {
+  return static_cast<Acc>(*p);
+}
+template <>
+__device__ __forceinline__ float load_as<float, __nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat162float(*p);
+}
+// 8-bit operands widen to 32-bit and accumulate modulo 2^32 (the vecops
+// int32 accumulator wraps: include/vecops/vec/WideningDot.h:100-103).
+template <>
+__device__ __forceinline__ uint32_t load_as<uint32_t, int8_t>(const int8_t* p) {
+  return static_cast<uint32_t>(static_cast<int32_t>(*p));
+}
+template <>
+__device__ __forceinline__ uint32_t load_as<uint32_t, uint8_t>(const uint8_t* p) {
+  return static_cast<uint32_t>(*p);
+}
+
+template <typename Out, typename Acc>
+__device__ __forceinline__ void store_from(Out* p, Acc v) {
+  *p = static_cast<Out>(v);
+}
+template <>
+__device__ __forceinline__ void store_from<__nv_bfloat16, float>(__nv_bfloat16* p, float v) {
+  *p = __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ void store_from<int32_t, uint32_t>(int32_t* p, uint32_t v) {
+  *p = static_cast<int32_t>(v);
+}
+
+// ------------------------------------------------------------------ strided any-dtype GEMM
+
+// C[m,n] = convert( (sum_k A[m,k] * B[n,k]) * scale[n] ), arbitrary element
+// strides on all three tensors.  32x32 output tile, 32-deep k-blocks staged in
+// shared memory in accumulator type, 4 outputs per thread.
+template <typename TA, typename TB, typename TC, typename Acc>
+__global__ void __launch_bounds__(256)
+gemm_generic_kernel(const TA* __restrict__ a, long long sam, long long sak, const TB* __restrict__ b, long long sbn,
+                    long long sbk, TC* __restrict__ c, long long scm, long long scn, int M, int N, int K,
+                    const float* __restrict__ column_scale) {
+  constexpr int T = 32;
+  __shared__ Acc as[T][T + 1];
+  __shared__ Acc bs[T][T + 1];
+  const int tx = threadIdx.x & 31;
+  const int ty = threadIdx.x >> 5;  // 0..7
+  const int m0 = blockIdx.y * T;
+  const int n0 = blockIdx.x * T;
+  Acc acc[4] = {Acc(0), Acc(0), Acc(0), Acc(0)};
+  for (int k0 = 0; k0 < K; k0 += T) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int r = ty + 8 * j;
+      const int kk = k0 + tx;
+      const int m = m0 + r;
+      const int n = n0 + r;
+      as[r][tx] = (m < M && kk < K) ? load_as<Acc, TA>(a + m * sam + kk * sak) : Acc(0);
+      bs[r][tx] = (n < N && kk < K) ? load_as<Acc, TB>(b + n * sbn + kk * sbk) : Acc(0);
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < T; ++kk) {
+      const Acc bv = bs[tx][kk];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[j] += as[ty + 8 * j][kk] * bv;
+    }
+    __syncthreads();
+  }
+  const int n = n0 + tx;
+  if (n >= N) return;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int m = m0 + ty + 8 * j;
+    if (m >= M) continue;
+    Acc v = acc[j];
+    if constexpr (sizeof(Acc) == 4 && !std::is_same<Acc, uint32_t>::value) {
+      if (column_scale != nullptr) v *= column_scale[n];
+    }
+    store_from<TC, Acc>(c + m * scm + n * scn, v);
+  }
+}
+
+// ------------------------------------------------------------------ FP32 FMA GEMM
+
+// C[M,N] = A[M,K] . B[N,K]^T in FP32 with FP32 FMA accumulation (no tensor
+// cores, so FP32 semantics are kept exactly: every product is an fp32 product
+// and every sum an fp32 sum).  64x64 tile, 16-deep k-blocks, 4x4 outputs per
+// thread.  A must be k-contiguous; B is either k-contiguous ([N,K] rows) or
+// n-contiguous (a row-major [K,N] matrix viewed as [N,K]).
+struct GemmF32 {
+  static constexpr int kTile = 64;
+  static constexpr int kDepth = 16;
+  static constexpr int kPad = 4;
+};
+
+__global__ void __launch_bounds__(256)
+gemm_f32_kernel(const float* __restrict__ a, long long lda, const float* __restrict__ b, long long sbn,
+                long long sbk, float* __restrict__ c, long long ldc, int M, int N, int K) {
+  using G = GemmF32;
+  __shared__ __align__(16) float as[2][G::kDepth][G::kTile + G::kPad];
+  __shared__ __align__(16) float bs[2][G::kDepth][G::kTile + G::kPad];
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * G::kTile;
+  const int n0 = blockIdx.x * G::kTile;
+  const int tx = tid & 15;   // 4 columns each
+  const int ty = tid >> 4;   // 4 rows each
+  const bool b_k_contig = (sbk == 1);
+
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+  float ra[4], rb[4];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      // A: 16 consecutive k per row, 16 rows per pass
+      const int kk = tid & 15, r = (tid >> 4) + 16 * j;
+      const int m = m0 + r, k = k0 + kk;
+      ra[j] = (m < M && k < K) ? __ldg(a + static_cast<long long>(m) * lda + k) : 0.f;
+      if (b_k_contig) {
+        const int n = n0 + r;
+        rb[j] = (n < N && k < K) ? __ldg(b + static_cast<long long>(n) * sbn + k) : 0.f;
+      } else {
+        // B n-contiguous: 64 consecutive n per k, 4 k per pass
+        const int nn = tid & 63, kq = (tid >> 6) + 4 * j;
+        const int n = n0 + nn, k2 = k0 + kq;
+        rb[j] = (n < N && k2 < K) ? __ldg(b + static_cast<long long>(n) * sbn + static_cast<long long>(k2) * sbk) : 0.f;
+      }
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int kk = tid & 15, r = (tid >> 4) + 16 * j;
+      as[buf][kk][r] = ra[j];
+      if (b_k_contig) {
+        bs[buf][kk][r] = rb[j];
+      } else {
+        const int nn = tid & 63, kq = (tid >> 6) + 4 * j;
+        bs[buf][kq][nn] = rb[j];
+      }
+    }
+  };
+
+  const int num_kb = (K + G::kDepth - 1) / G::kDepth;
+  if (num_kb > 0) {
+    fetch(0);
+    stash(0);
+  }
+  __syncthreads();
+  for (int kb = 0; kb < num_kb; ++kb) {
+    const int buf = kb & 1;
+    if (kb + 1 < num_kb) fetch((kb + 1) * G::kDepth);
+#pragma unroll
+    for (int kk = 0; kk < G::kDepth; ++kk) {
+      const float4 av = *reinterpret_cast<const float4*>(&as[buf][kk][ty * 4]);
+      const float4 bv = *reinterpret_cast<const float4*>(&bs[buf][kk][tx * 4]);
+      const float avs[4] = {av.x, av.y, av.z, av.w};
+      const float bvs[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(avs[i], bvs[j], acc[i][j]);
+    }
+    if (kb + 1 < num_kb) stash(buf ^ 1);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+    float* dst = c + static_cast<long long>(m) * ldc + n0 + tx * 4;
+    const int n = n0 + tx * 4;
+    if (n + 3 < N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+      *reinterpret_cast<float4*>(dst) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (n + j < N) dst[j] = acc[i][j];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ fills and slab placement
+
+__global__ void fill_zero_kernel(uint8_t* __restrict__ c, long long row_pitch_bytes, long long col_pitch_bytes,
+                                 int elem_bytes, long long M, long long N) {
+  const long long total = M * N;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    uint8_t* p = c + (i / N) * row_pitch_bytes + (i % N) * col_pitch_bytes;
+    for (int e = 0; e < elem_bytes; ++e) p[e] = 0;
+  }
+}
+
+// dst[r, col0 + j] = src[r, j] in 16-byte units (caller guarantees alignment).
+__global__ void place_columns_kernel(uint4* __restrict__ dst, long long dst_pitch16, long long col0_16,
+                                     const uint4* __restrict__ src, long long src_pitch16, long long rows,
+                                     long long cols16) {
+  const long long total = rows * cols16;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cols16, j = i % cols16;
+    dst[r * dst_pitch16 + col0_16 + j] = src[r * src_pitch16 + j];
+  }
+}
+
+}  // namespace vb200

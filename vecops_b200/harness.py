@@ -1,0 +1,73 @@
+"""Test/benchmark harness over the C ABI: torch tensors in, ``vecops_b200_matmul_run`` underneath.
+
+torch is used for device memory and streams only; all arithmetic happens in the
+library's own kernels.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import byref, c_uint32, c_uint64
+
+from . import capi
+
+
+def torch_dtype_code(dtype) -> int:
+    import torch
+    table = {torch.float32: capi.DTYPE_F32, torch.bfloat16: capi.DTYPE_BF16, torch.int8: capi.DTYPE_I8,
+             torch.uint8: capi.DTYPE_U8, torch.int32: capi.DTYPE_I32, torch.float16: capi.DTYPE_F16}
+    if dtype not in table:
+        raise ValueError(f"dtype {dtype} has no vecops code on this path")
+    return table[dtype]
+
+
+def matmul_problem(a, b_nk, c, scale=None, kernel: int = capi.KERNEL_AUTO, stream=None, asynchronous: bool = False,
+                   workspace=None) -> capi.VecopsB200Matmul:
+    """Describe C[M,N] = A[M,K] . B[N,K]^T over 2-D torch tensors (any strides)."""
+    if a.dim() != 2 or b_nk.dim() != 2 or c.dim() != 2:
+        raise ValueError("a, b and c must be 2-D")
+    m, k = a.shape
+    n, kb = b_nk.shape
+    if kb != k or tuple(c.shape) != (m, n):
+        raise ValueError(f"shape mismatch: a{tuple(a.shape)} b{tuple(b_nk.shape)} c{tuple(c.shape)}")
+    p = capi.VecopsB200Matmul()
+    p.struct_size = ctypes.sizeof(capi.VecopsB200Matmul)
+    p.kernel = kernel
+    p.m, p.n, p.k = m, n, k
+    p.a, p.a_stride_m, p.a_stride_k = a.data_ptr(), a.stride(0), a.stride(1)
+    p.b, p.b_stride_n, p.b_stride_k = b_nk.data_ptr(), b_nk.stride(0), b_nk.stride(1)
+    p.c, p.c_stride_m, p.c_stride_n = c.data_ptr(), c.stride(0), c.stride(1)
+    p.column_scale = scale.data_ptr() if scale is not None else None
+    if workspace is not None:
+        p.workspace, p.workspace_size = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    p.stream = stream.cuda_stream if stream is not None else None
+    p.a_dtype, p.b_dtype, p.c_dtype = torch_dtype_code(a.dtype), torch_dtype_code(b_nk.dtype), torch_dtype_code(c.dtype)
+    p.device_index = a.device.index if a.is_cuda and a.device.index is not None else -1
+    p.flags = capi.MATMUL_FLAG_ASYNC if asynchronous else 0
+    return p
+
+
+def select_kernel(problem: capi.VecopsB200Matmul) -> int:
+    error = capi.ErrorBuffer()
+    out = c_uint32(0)
+    error.raise_for(capi.library().vecops_b200_matmul_select(byref(problem), byref(out), byref(error.record)))
+    return out.value
+
+
+def workspace_bytes(problem: capi.VecopsB200Matmul) -> int:
+    error = capi.ErrorBuffer()
+    out = c_uint64(0)
+    error.raise_for(capi.library().vecops_b200_matmul_workspace(byref(problem), byref(out), byref(error.record)))
+    return out.value
+
+
+def run(problem: capi.VecopsB200Matmul) -> None:
+    error = capi.ErrorBuffer()
+    error.raise_for(capi.library().vecops_b200_matmul_run(byref(problem), byref(error.record)))
+
+
+def matmul(a, b_nk, c, scale=None, kernel: int = capi.KERNEL_AUTO, stream=None, asynchronous: bool = False) -> None:
+    """Run C = A . B^T on the GPU through the C ABI; raises VecopsB200Error on any failure."""
+    import torch
+    if stream is None and a.is_cuda:
+        stream = torch.cuda.current_stream(a.device)
+    run(matmul_problem(a, b_nk, c, scale, kernel, stream, asynchronous))
