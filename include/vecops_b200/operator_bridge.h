@@ -1,0 +1,65 @@
+/*
+ * C door to the matmul Operator, for embeddings that cannot include C++.
+ *
+ * vecops_operator_bridge_invoke_v1 has the signature and meaning of vecops'
+ * process-local bridge (include/vecops/runtime/OperatorBridgeAbi.h:23-158): a
+ * generated framework adapter hands over a positional VecopsCall plus named
+ * specialization values, and the runtime validates, resolves and runs.  The
+ * handle comes from vecops_b200_matmul_operator() instead of a Python-owned
+ * registry.
+ */
+#ifndef VECOPS_B200_OPERATOR_BRIDGE_H
+#define VECOPS_B200_OPERATOR_BRIDGE_H
+
+#include "vecops_b200/kernel_abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef VECOPS_RUNTIME_OPERATOR_BRIDGE_ABI_H
+typedef enum VecopsSpecializationValueKind {
+  VECOPS_SPECIALIZATION_CONST_INT = 1,
+  VECOPS_SPECIALIZATION_DTYPE = 2
+} VecopsSpecializationValueKind;
+
+typedef struct VecopsSpecializationArgument {
+  uint32_t struct_size;
+  uint32_t kind;
+  const char* name;
+  union {
+    int64_t integer;
+    uint32_t dtype;
+  } value;
+} VecopsSpecializationArgument;
+#endif
+
+/* Handle of the process-wide CUDA matmul operator (created on first use). */
+VECOPS_B200_EXPORT uint64_t vecops_b200_matmul_operator(void);
+
+/* Validate, resolve and run one call: values = {a, b, c[, column_scale]}.
+ * Replaces vecops_operator_bridge_invoke_v1 (OperatorBridgeAbi.h:156-158). */
+VECOPS_B200_EXPORT int32_t vecops_operator_bridge_invoke_v1(uint64_t handle, const VecopsCall* call,
+                                                            uint32_t num_specialization_values,
+                                                            const VecopsSpecializationArgument* specialization_values,
+                                                            VecopsError* error);
+
+/* Resolve only: which specialization key would serve this call.  The key is
+ * written NUL-terminated (truncated to `capacity`) into `key`. */
+VECOPS_B200_EXPORT int32_t vecops_b200_operator_resolve(uint64_t handle, const VecopsCall* call, char* key,
+                                                        size_t capacity, VecopsError* error);
+
+/* Device scratch in bytes the resolved executable wants for this call. */
+VECOPS_B200_EXPORT int32_t vecops_b200_operator_workspace(uint64_t handle, const VecopsCall* call, uint64_t* bytes,
+                                                          VecopsError* error);
+
+/* Descriptor template of one kernel variant (VecopsB200MatmulKernel id): what
+ * a one-specialization artifact's vecops_kernel_query_v1 would return, with an
+ * empty specialization key.  NULL for AUTO or an id out of range. */
+VECOPS_B200_EXPORT const VecopsKernelDescriptorV1* vecops_b200_matmul_descriptor(uint32_t kernel);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* VECOPS_B200_OPERATOR_BRIDGE_H */

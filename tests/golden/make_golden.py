@@ -1,0 +1,97 @@
+"""Generate tests/golden/*.npz by running the reference's own CPU matmul.
+
+Needs the reference checkout (to build oracle/_ref) and a CPU with AMX; the
+fixtures it writes are committed, so neither is needed to run the tests.
+
+Inputs follow the reference tests' own deterministic patterns:
+  value<T>(i, modulus)        tests/ops/MatmulTest.cpp:36-41   (a: modulus 13, b: modulus 11, :63-64)
+  conversion_value<T>(i, s)   tests/ops/MatmulConversionTestCommon.h:62-70
+on shapes the reference tests use (K tails, ragged M/N, all int8 signedness
+pairs, GEMV orientations: MatmulTest.cpp:434-452, :1005-1023).
+
+    python tests/golden/make_golden.py
+"""
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+
+from oracle.checker import Ref, f32_to_bf16_bits  # noqa: E402
+
+HERE = Path(__file__).resolve().parent
+
+
+def value_pattern(count: int, modulus: int, dtype) -> np.ndarray:
+    """value<T>(index, modulus): (index % modulus) - modulus / 2, scaled by 1/modulus for floats."""
+    x = (np.arange(count, dtype=np.int64) % modulus) - modulus // 2
+    if np.issubdtype(dtype, np.integer):
+        return x.astype(dtype)
+    return (x.astype(np.float32) / np.float32(modulus)).astype(np.float32)
+
+
+def conversion_pattern(count: int, seed: int, dtype) -> np.ndarray:
+    """conversion_value<T>(index, seed)."""
+    index = np.arange(count, dtype=np.int64)
+    if np.issubdtype(dtype, np.integer):
+        low = 0 if np.issubdtype(dtype, np.unsignedinteger) else -3
+        return (low + (index * 5 + seed) % 7).astype(dtype)
+    return (((index * 7 + seed) % 17 - 8).astype(np.float32) / np.float32(16.0)).astype(np.float32)
+
+
+def main() -> None:
+    ref, why = Ref.load()
+    if ref is None:
+        raise SystemExit(f"reference matmul unavailable here: {why}")
+    cases = {}
+
+    # AMX_BF16F32, bf16 in / f32 out and bf16 out, microkernel shapes with K tails
+    for m, n, k in [(16, 16, 35), (37, 51, 79), (1, 128, 65), (48, 16, 65), (64, 96, 256)]:
+        a = f32_to_bf16_bits(value_pattern(m * k, 13, np.float32)).reshape(m, k)
+        b = f32_to_bf16_bits(value_pattern(n * k, 11, np.float32)).reshape(n, k)
+        cases[f"bf16_{m}x{n}x{k}"] = dict(kind="bf16", a=a, b=b, c_f32=ref.matmul_bf16(a, b, out_bf16=False),
+                                          c_bf16=ref.matmul_bf16(a, b, out_bf16=True))
+
+    # AMX_I8I32<A,B>, all four signedness pairs
+    for (m, n, k), (ta, tb) in [((19, 21, 69), (np.int8, np.int8)), ((19, 21, 69), (np.int8, np.uint8)),
+                                ((19, 21, 69), (np.uint8, np.int8)), ((19, 21, 69), (np.uint8, np.uint8)),
+                                ((1, 128, 65), (np.int8, np.int8)), ((16, 1, 129), (np.uint8, np.int8)),
+                                ((40, 48, 192), (np.int8, np.int8))]:
+        a = value_pattern(m * k, 13, np.int16).astype(ta).reshape(m, k)
+        b = value_pattern(n * k, 11, np.int16).astype(tb).reshape(n, k)
+        name = f"i8_{np.dtype(ta).name}_{np.dtype(tb).name}_{m}x{n}x{k}"
+        cases[name] = dict(kind="i8", a=a, b=b, c=ref.matmul_i8(a, b))
+
+    # full-range int8 at one bigger shape (random, seeded)
+    rng = np.random.default_rng(2)
+    a = rng.integers(-128, 128, (33, 256), dtype=np.int8)
+    b = rng.integers(-128, 128, (47, 256), dtype=np.int8)
+    cases["i8_full_range_33x47x256"] = dict(kind="i8", a=a, b=b, c=ref.matmul_i8(a, b))
+
+    # weight-only int8: bf16 activations, int8 weights, per-column scale, bf16 out
+    rng = np.random.default_rng(3)
+    for m, n, k in [(1, 48, 128), (16, 64, 256), (5, 33, 96)]:
+        a = f32_to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32))
+        w = rng.integers(-127, 128, (n, k), dtype=np.int8)
+        s = rng.uniform(0.001, 0.02, n).astype(np.float32)
+        cases[f"w8_{m}x{n}x{k}"] = dict(kind="w8", a=a, b=w, scale=s, c_bf16=ref.matmul_w8(a, w, s))
+
+    # fp32: the AVX-512 fmadd leaf (B as [N,K])
+    for m, n, k in [(33, 40, 64), (7, 19, 50)]:
+        a = conversion_pattern(m * k, 3, np.float32).reshape(m, k)
+        b = conversion_pattern(n * k, 5, np.float32).reshape(n, k)
+        cases[f"f32_{m}x{n}x{k}"] = dict(kind="f32", a=a, b=b, c=ref.matmul_f32_leaf(a, b))
+
+    for name, arrays in cases.items():
+        kind = arrays.pop("kind")
+        np.savez_compressed(HERE / f"{name}.npz", kind=np.array(kind), **arrays)
+    total = sum(p.stat().st_size for p in HERE.glob("*.npz"))
+    print(f"wrote {len(cases)} fixtures, {total / 1024:.1f} KiB")
+
+
+if __name__ == "__main__":
+    main()

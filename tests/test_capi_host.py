@@ -1,0 +1,121 @@
+"""Host-only checks of the C ABI: the library loads without a GPU, exports every
+declared symbol, and the dispatch rules / argument checks behave."""
+import ctypes
+import re
+from ctypes import byref, c_uint32, c_uint64
+from pathlib import Path
+
+import pytest
+import torch
+
+import vecops_b200
+from vecops_b200 import capi, harness
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def declared_symbols():
+    names = set()
+    for header in (ROOT / "include" / "vecops_b200").glob("*.h"):
+        text = header.read_text()
+        names.update(re.findall(r"VECOPS_B200_EXPORT[^;{]*?\b(vecops_[a-z0-9_]+)\s*\(", text, flags=re.S))
+    return names
+
+
+def test_library_exports_every_declared_symbol(library):
+    names = declared_symbols()
+    assert {"vecops_b200_matmul_run", "vecops_b200_matmul_select", "vecops_b200_matmul_workspace",
+            "vecops_operator_bridge_invoke_v1", "vecops_b200_matmul_operator"} <= names
+    for name in sorted(names):
+        assert hasattr(library, name), f"{name} is declared in include/ but not exported"
+
+
+def test_record_sizes_match_the_c_layout():
+    # 64-bit layouts of the vecops records the artifact exchanges with its caller
+    assert ctypes.sizeof(capi.VecopsError) == 32
+    assert ctypes.sizeof(capi.VecopsTensorView) == 64
+    assert ctypes.sizeof(capi.VecopsScalar) == 16
+    assert ctypes.sizeof(capi.VecopsValue) == 72
+    assert ctypes.sizeof(capi.VecopsExecutionContext) == 56
+    assert ctypes.sizeof(capi.VecopsCall) == 40
+
+
+def _problem(m, n, k, a_dtype, b_dtype, c_dtype, **kw):
+    a = torch.empty((m, k), dtype=a_dtype)
+    b = torch.empty((n, k), dtype=b_dtype)
+    c = torch.empty((m, n), dtype=c_dtype)
+    keep = (a, b, c)
+    p = vecops_b200.matmul_problem(a, b, c, **kw)
+    p._keep = keep
+    return p
+
+
+def _name(kernel):
+    return capi.library().vecops_b200_kernel_name(kernel).decode()
+
+
+def test_dispatch_rules_pick_the_tensor_core_kernels_for_the_benchmark_shapes(library):
+    assert _name(vecops_b200.select_kernel(_problem(4096, 4096, 4096, torch.bfloat16, torch.bfloat16, torch.bfloat16))) == "bf16_tcgen05"
+    assert _name(vecops_b200.select_kernel(_problem(4096, 14336, 4096, torch.int8, torch.int8, torch.int32))) == "i8_tcgen05"
+    assert _name(vecops_b200.select_kernel(_problem(4096, 256, 512, torch.uint8, torch.int8, torch.int32))) == "i8_tcgen05"
+    for m in (1, 16):
+        assert _name(vecops_b200.select_kernel(_problem(m, 14336, 4096, torch.bfloat16, torch.int8, torch.bfloat16))) == "w8_small_m"
+    assert _name(vecops_b200.select_kernel(_problem(1024, 1024, 1024, torch.float32, torch.float32, torch.float32))) == "f32_simt"
+
+
+def test_dispatch_rules_route_ragged_and_tiny_problems_to_the_strided_kernel(library):
+    # K = 35 bf16 rows are 70 bytes apart: not addressable by TMA
+    assert _name(vecops_b200.select_kernel(_problem(16, 16, 35, torch.bfloat16, torch.bfloat16, torch.float32))) == "generic"
+    # tiny outputs (area rule), as vecops sends them to its small-vector leaves
+    assert _name(vecops_b200.select_kernel(_problem(4, 8, 4096, torch.bfloat16, torch.bfloat16, torch.bfloat16))) == "generic"
+    # int32 wrap semantic: very long K stays on the wrapping integer kernel
+    assert _name(vecops_b200.select_kernel(_problem(256, 256, 262144, torch.int8, torch.int8, torch.int32))) == "generic"
+    # weight-only with K not a multiple of 32
+    assert _name(vecops_b200.select_kernel(_problem(4, 64, 72, torch.bfloat16, torch.int8, torch.bfloat16))) == "generic"
+
+
+def test_forced_kernel_that_cannot_serve_is_not_applicable(library):
+    p = _problem(16, 16, 35, torch.bfloat16, torch.bfloat16, torch.float32, kernel=capi.KERNEL_BF16_TCGEN05)
+    with pytest.raises(capi.VecopsB200Error) as info:
+        vecops_b200.select_kernel(p)
+    assert info.value.code == capi.NOT_APPLICABLE
+
+
+def test_unsupported_dtype_row_is_invalid_argument(library):
+    p = _problem(8, 8, 8, torch.float32, torch.bfloat16, torch.float32)
+    with pytest.raises(capi.VecopsB200Error) as info:
+        vecops_b200.select_kernel(p)
+    assert info.value.code == capi.INVALID_ARGUMENT
+
+
+def test_short_record_is_an_abi_mismatch(library):
+    p = _problem(8, 8, 8, torch.float32, torch.float32, torch.float32)
+    p.struct_size = 16
+    with pytest.raises(capi.VecopsB200Error) as info:
+        vecops_b200.select_kernel(p)
+    assert info.value.code == capi.ABI_MISMATCH
+
+
+def test_error_text_is_truncated_to_the_callers_buffer(library):
+    p = _problem(8, 8, 8, torch.float32, torch.bfloat16, torch.float32)
+    text = ctypes.create_string_buffer(12)
+    record = capi.VecopsError(ctypes.sizeof(capi.VecopsError), 0, ctypes.cast(text, ctypes.c_void_p), 12, 0)
+    out = c_uint32(0)
+    rc = library.vecops_b200_matmul_select(byref(p), byref(out), byref(record))
+    assert rc == capi.INVALID_ARGUMENT and record.code == capi.INVALID_ARGUMENT
+    assert len(text.value) == 11 and record.message_required > 12
+
+
+def test_workspace_query_is_pure_host_logic(library):
+    p = _problem(16, 14336, 4096, torch.bfloat16, torch.int8, torch.bfloat16)
+    assert harness.workspace_bytes(p) == 0
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU failure mode")
+def test_run_without_a_gpu_fails_loudly_instead_of_falling_back(library):
+    assert library.vecops_b200_device_count() == 0
+    p = _problem(64, 64, 64, torch.float32, torch.float32, torch.float32)
+    with pytest.raises(capi.VecopsB200Error) as info:
+        harness.run(p)
+    assert info.value.code == capi.EXECUTION_ERROR
+    assert "no CPU fallback" in info.value.message

@@ -1,0 +1,85 @@
+"""The CPU checker against the reference: committed fixtures (outputs of the
+reference's own ops::matmul) and, where this host can run it, the reference
+library itself."""
+import numpy as np
+import pytest
+
+from oracle.checker import Ref, bf16_bits_to_f32, f32_to_bf16_bits, rel_frobenius
+from tests.helpers import TOL_BF16, TOL_F32
+
+
+def test_bf16_rounding_rule(port):
+    # round-to-nearest-even on the bit pattern, NaN -> 0x7fc0 (util/BFloat16.h:25-37)
+    samples = np.array([0.0, -0.0, 1.0, 1.00390625, 1.005859375, 3.14159265, -2.5e-40, 6.5e4, 3.38e38, np.inf, -np.inf],
+                       dtype=np.float32)
+    bits = f32_to_bf16_bits(samples)
+    for value, got in zip(samples, bits):
+        assert port.lib.oracle_f32_to_bf16(float(value)) == int(got)
+    assert f32_to_bf16_bits(np.array([np.nan], dtype=np.float32))[0] == 0x7FC0
+    assert port.lib.oracle_f32_to_bf16(float("nan")) == 0x7FC0
+    # ties go to even: 1 + 2^-8 is exactly between 1.0 and 1 + 2^-7
+    assert f32_to_bf16_bits(np.array([1.00390625], dtype=np.float32))[0] == 0x3F80
+    assert f32_to_bf16_bits(np.array([1.01171875], dtype=np.float32))[0] == 0x3F82
+
+
+def test_port_matches_golden_fixtures(port, golden):
+    checked = 0
+    for name, case in golden.items():
+        kind = str(case["kind"])
+        a, b = case["a"], case["b"]
+        if kind == "i8":
+            assert np.array_equal(port.matmul_i8(a, b), case["c"]), name
+        elif kind == "f32":
+            assert rel_frobenius(port.matmul_f32(a, b), case["c"]) <= TOL_F32, name
+        elif kind == "bf16":
+            assert rel_frobenius(port.matmul_bf16(a, b, None, False), case["c_f32"]) <= 1e-6, name
+            got = bf16_bits_to_f32(port.matmul_bf16(a, b, None, True))
+            assert rel_frobenius(got, bf16_bits_to_f32(case["c_bf16"])) <= TOL_BF16, name
+        elif kind == "w8":
+            got = bf16_bits_to_f32(port.matmul_w8(a, b, case["scale"], True))
+            assert rel_frobenius(got, bf16_bits_to_f32(case["c_bf16"])) <= TOL_BF16, name
+        else:
+            raise AssertionError(f"unknown fixture kind {kind}")
+        checked += 1
+    assert checked >= 15
+
+
+def test_int32_accumulator_wraps(port):
+    # K = 262145 of 127*127 overflows int32 and must wrap (tests/ops/MatmulTest.cpp:1025-1055)
+    k = 262145
+    for dtype, value in ((np.int8, 127), (np.uint8, 255)):
+        a = np.full((1, k), value, dtype=dtype)
+        expected = np.uint32((value * value * k) % (1 << 32)).astype(np.int32)
+        assert port.matmul_i8(a, a)[0, 0] == expected
+
+
+def test_empty_and_degenerate_shapes(port):
+    a = np.zeros((3, 0), dtype=np.float32)
+    b = np.zeros((5, 0), dtype=np.float32)
+    assert np.array_equal(port.matmul_f32(a, b), np.zeros((3, 5), dtype=np.float32))  # K = 0 -> zeros
+    assert port.matmul_i8(np.zeros((0, 4), np.int8), np.zeros((2, 4), np.int8)).shape == (0, 2)
+
+
+def test_strided_b_is_the_nk_view_of_a_kn_matrix(port):
+    rng = np.random.default_rng(0)
+    a = rng.uniform(-1, 1, (9, 20)).astype(np.float32)
+    b_kn = rng.uniform(-1, 1, (20, 13)).astype(np.float32)
+    want = (a.astype(np.float64) @ b_kn.astype(np.float64)).astype(np.float32)
+    assert rel_frobenius(port.matmul_f32(a, b_kn.T), want) <= 1e-7
+
+
+def test_port_against_reference_library_live(port):
+    ref, why = Ref.load()
+    if ref is None:
+        pytest.skip(f"reference matmul cannot run on this host: {why}")
+    rng = np.random.default_rng(11)
+    a = f32_to_bf16_bits(rng.standard_normal((96, 320), dtype=np.float32))
+    b = f32_to_bf16_bits(rng.standard_normal((80, 320), dtype=np.float32))
+    assert rel_frobenius(bf16_bits_to_f32(port.matmul_bf16(a, b)), bf16_bits_to_f32(ref.matmul_bf16(a, b, threads=2))) <= TOL_BF16
+    ai = rng.integers(-128, 128, (70, 448), dtype=np.int8)
+    bi = rng.integers(-128, 128, (50, 448), dtype=np.int8)
+    assert np.array_equal(port.matmul_i8(ai, bi), ref.matmul_i8(ai, bi, threads=2))
+    w = rng.integers(-127, 128, (64, 320), dtype=np.int8)
+    s = rng.uniform(0.001, 0.02, 64).astype(np.float32)
+    got = bf16_bits_to_f32(port.matmul_w8(a[:16], w, s))
+    assert rel_frobenius(got, bf16_bits_to_f32(ref.matmul_w8(a[:16], w, s))) <= TOL_BF16

@@ -20,7 +20,7 @@ LIBRARY = LIB_DIR / "libvecops_b200.so"
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden"]
-CXX_FLAGS = ["-std=c++20", "-O2", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wextra"]
+CXX_FLAGS = ["-std=c++20", "-O2", "-fPIC", "-Wall", "-Wextra"]  # default visibility: the C++ runtime classes are part of the library's API
 
 
 def _nvcc() -> str:
@@ -33,7 +33,8 @@ def _nvcc() -> str:
 def _sources() -> tuple[list[Path], list[Path], list[Path]]:
     cuda = sorted((CSRC / "cuda").glob("*.cu"))
     host = sorted((CSRC / "runtime").glob("*.cpp"))
-    headers = sorted(CSRC.rglob("*.h")) + sorted(CSRC.rglob("*.cuh")) + sorted(INCLUDE.rglob("*.h"))
+    # this file counts as an input: a change of flags rebuilds everything
+    headers = sorted(CSRC.rglob("*.h")) + sorted(CSRC.rglob("*.cuh")) + sorted(INCLUDE.rglob("*.h")) + [Path(__file__)]
     return cuda, host, headers
 
 

@@ -1,0 +1,465 @@
+// CUDA matmul operator: KernelDef, recipes, dispatch policy, provider,
+// descriptors and the C bridge.
+#include "vecops_b200/runtime/matmul_operator.h"
+
+#include <array>
+#include <cstddef>
+#include <cstring>
+
+#include "vecops_b200/operator_bridge.h"
+
+namespace vecops::runtime {
+namespace {
+
+constexpr const char* kOperatorName = "vecops::matmul";
+constexpr std::uint32_t kVariants[] = {VECOPS_B200_KERNEL_BF16_TCGEN05, VECOPS_B200_KERNEL_I8_TCGEN05,
+                                       VECOPS_B200_KERNEL_W8_SMALL_M,   VECOPS_B200_KERNEL_W8_TCGEN05,
+                                       VECOPS_B200_KERNEL_F32_SIMT,     VECOPS_B200_KERNEL_GENERIC};
+
+struct ErrorText {
+  std::array<char, 1024> text{};
+  VecopsError record{};
+  ErrorText() {
+    record.struct_size = sizeof(VecopsError);
+    record.message = text.data();
+    record.message_capacity = text.size();
+  }
+  [[nodiscard]] Status status(std::int32_t rc) const {
+    if (rc == VECOPS_STATUS_OK) return Status::success();
+    return Status(static_cast<StatusCode>(rc), text.data());
+  }
+};
+
+std::shared_ptr<const KernelDef> shared_definition() {
+  static const auto definition = std::make_shared<const KernelDef>(matmul_kernel_def());
+  return definition;
+}
+
+// ---------------------------------------------------------------- descriptors
+
+constexpr std::uint64_t bit(std::uint32_t dtype) { return std::uint64_t{1} << (dtype - 1); }
+constexpr VecopsDimensionConstraint any_dim() { return {sizeof(VecopsDimensionConstraint), VECOPS_DIM_ANY, 0, 0, 0, 1}; }
+constexpr VecopsDimensionConstraint const_dim(std::int64_t v) { return {sizeof(VecopsDimensionConstraint), VECOPS_DIM_CONST, v, 0, 0, 1}; }
+constexpr VecopsDimensionConstraint aligned_dim(std::int64_t alignment) {
+  return {sizeof(VecopsDimensionConstraint), VECOPS_DIM_DYNAMIC, 0, 0, INT64_MAX, alignment};
+}
+
+struct VariantDescriptor {
+  VecopsDimensionConstraint a_sizes[2], a_strides[2], b_sizes[2], b_strides[2], c_sizes[2], c_strides[2], s_sizes[1], s_strides[1];
+  VecopsParameterDescriptor parameters[4];
+  VecopsKernelDescriptorV1 descriptor;
+};
+
+VecopsParameterDescriptor tensor_parameter(const char* name, std::uint64_t dtype_mask, std::int32_t rank,
+                                           const VecopsDimensionConstraint* sizes, const VecopsDimensionConstraint* strides,
+                                           bool optional, bool output) {
+  VecopsParameterDescriptor p{};
+  p.struct_size = sizeof(VecopsParameterDescriptor);
+  p.kind = VECOPS_VALUE_TENSOR;
+  p.name = name;
+  auto& t = p.constraint.tensor;
+  t.struct_size = sizeof(VecopsTensorParameter);
+  t.dtype_mask = dtype_mask;
+  t.device_type = VECOPS_DEVICE_CUDA;
+  t.device_index = -1;
+  t.rank = rank;
+  t.optional = optional ? 1u : 0u;
+  t.dimension_constraint_stride = sizeof(VecopsDimensionConstraint);
+  t.sizes = sizes;
+  t.strides = strides;
+  t.required_flags = output ? VECOPS_TENSOR_WRITE : VECOPS_TENSOR_READ;
+  return p;
+}
+
+std::int32_t run_with(std::uint32_t kernel, const VecopsCall* call, VecopsError* error, bool only_workspace, std::uint64_t* bytes);
+
+template <std::uint32_t kKernel>
+std::int32_t run_variant(const VecopsCall* call, VecopsError* error) {
+  return run_with(kKernel, call, error, false, nullptr);
+}
+template <std::uint32_t kKernel>
+std::int32_t workspace_variant(const VecopsCall* call, std::uint64_t* bytes, VecopsError* error) {
+  return run_with(kKernel, call, error, true, bytes);
+}
+
+template <std::uint32_t kKernel>
+VariantDescriptor* build_variant(std::uint64_t a_mask, std::uint64_t b_mask, std::uint64_t c_mask, std::int64_t a_pitch_align,
+                                 std::int64_t b_pitch_align, std::int64_t k_align, bool contiguous_k, bool row_major_c) {
+  auto* v = new VariantDescriptor{};  // lives for the life of the process, like a DSO's static descriptor
+  v->a_sizes[0] = any_dim();
+  v->a_sizes[1] = k_align > 1 ? aligned_dim(k_align) : any_dim();
+  v->b_sizes[0] = any_dim();
+  v->b_sizes[1] = v->a_sizes[1];
+  v->c_sizes[0] = v->c_sizes[1] = any_dim();
+  v->a_strides[0] = a_pitch_align > 1 ? aligned_dim(a_pitch_align) : any_dim();
+  v->b_strides[0] = b_pitch_align > 1 ? aligned_dim(b_pitch_align) : any_dim();
+  v->a_strides[1] = v->b_strides[1] = contiguous_k ? const_dim(1) : any_dim();
+  v->c_strides[0] = any_dim();
+  v->c_strides[1] = row_major_c ? const_dim(1) : any_dim();
+  v->s_sizes[0] = any_dim();
+  v->s_strides[0] = const_dim(1);
+  v->parameters[0] = tensor_parameter("a", a_mask, 2, v->a_sizes, v->a_strides, false, false);
+  v->parameters[1] = tensor_parameter("b", b_mask, 2, v->b_sizes, v->b_strides, false, false);
+  v->parameters[2] = tensor_parameter("c", c_mask, 2, v->c_sizes, v->c_strides, false, true);
+  v->parameters[3] = tensor_parameter("column_scale", bit(VECOPS_DTYPE_F32), 1, v->s_sizes, v->s_strides, true, false);
+  auto& d = v->descriptor;
+  d.struct_size = sizeof(VecopsKernelDescriptorV1);
+  d.abi_version_major = VECOPS_KERNEL_ABI_VERSION_MAJOR;
+  d.abi_version_minor = VECOPS_KERNEL_ABI_VERSION_MINOR;
+  d.operator_name = kOperatorName;
+  d.specialization_key = "";
+  d.num_parameters = 4;
+  d.parameter_stride = sizeof(VecopsParameterDescriptor);
+  d.parameters = v->parameters;
+  d.workspace = &workspace_variant<kKernel>;
+  d.run = &run_variant<kKernel>;
+  d.flags = 0;
+  return v;
+}
+
+const VariantDescriptor* variant_descriptor(std::uint32_t kernel) {
+  constexpr auto f32 = bit(VECOPS_DTYPE_F32), bf16 = bit(VECOPS_DTYPE_BF16), i8 = bit(VECOPS_DTYPE_I8),
+                 u8 = bit(VECOPS_DTYPE_U8), i32 = bit(VECOPS_DTYPE_I32);
+  static const VariantDescriptor* const table[VECOPS_B200_KERNEL_COUNT_] = {
+      nullptr,
+      build_variant<VECOPS_B200_KERNEL_GENERIC>(f32 | bf16 | i8 | u8, f32 | bf16 | i8 | u8, f32 | bf16 | i32, 1, 1, 1, false, false),
+      build_variant<VECOPS_B200_KERNEL_F32_SIMT>(f32, f32, f32, 1, 1, 1, false, true),
+      // TMA wants 16-byte row pitches: 8 bf16 elements, 16 int8 elements
+      build_variant<VECOPS_B200_KERNEL_BF16_TCGEN05>(bf16, bf16, bf16 | f32, 8, 8, 1, true, true),
+      build_variant<VECOPS_B200_KERNEL_I8_TCGEN05>(i8 | u8, i8 | u8, i32, 16, 16, 1, true, true),
+      build_variant<VECOPS_B200_KERNEL_W8_SMALL_M>(bf16, i8, bf16 | f32, 8, 16, 32, true, true),
+      build_variant<VECOPS_B200_KERNEL_W8_TCGEN05>(bf16, i8, bf16 | f32, 8, 16, 32, true, true),
+  };
+  return kernel < VECOPS_B200_KERNEL_COUNT_ ? table[kernel] : nullptr;
+}
+
+// ---------------------------------------------------------------- ABI frame -> problem record
+
+std::int32_t fail(VecopsError* error, std::int32_t code, const char* message) {
+  if (error != nullptr && error->struct_size >= sizeof(VecopsError)) {
+    error->code = code;
+    error->message_required = std::strlen(message) + 1;
+    if (error->message != nullptr && error->message_capacity > 0) {
+      std::strncpy(error->message, message, error->message_capacity - 1);
+      error->message[error->message_capacity - 1] = '\0';
+    }
+  }
+  return code;
+}
+
+std::int32_t problem_from_frame(const VecopsCall* call, std::uint32_t kernel, VecopsB200Matmul* out, VecopsError* error) {
+  if (call == nullptr || call->struct_size < sizeof(VecopsCall)) return fail(error, VECOPS_STATUS_ABI_MISMATCH, "call frame is null or too small");
+  // a, b, c and the optional trailing column_scale (absent or VECOPS_VALUE_NONE = no scale)
+  if ((call->num_values != 3 && call->num_values != 4) || call->values == nullptr)
+    return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "matmul expects a, b, c and an optional column_scale");
+  const VecopsTensorView* t[4] = {nullptr, nullptr, nullptr, nullptr};
+  for (int i = 0; i < static_cast<int>(call->num_values); ++i) {
+    const VecopsValue& value = call->values[i];
+    if (value.kind == VECOPS_VALUE_TENSOR) t[i] = &value.value.tensor;
+    else if (!(i == 3 && value.kind == VECOPS_VALUE_NONE)) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "matmul values must be tensors");
+  }
+  if (t[0]->rank != 2 || t[1]->rank != 2 || t[2]->rank != 2 || (t[3] != nullptr && t[3]->rank != 1))
+    return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "matmul wants rank-2 a, b, c and a rank-1 column_scale");
+  VecopsB200Matmul p{};
+  p.struct_size = sizeof(VecopsB200Matmul);
+  p.kernel = kernel;
+  p.m = t[0]->sizes[0];
+  p.k = t[0]->sizes[1];
+  p.n = t[1]->sizes[0];
+  if (t[1]->sizes[1] != p.k || t[2]->sizes[0] != p.m || t[2]->sizes[1] != p.n || (t[3] != nullptr && t[3]->sizes[0] != p.n))
+    return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "matmul extents disagree: a[M,K] b[N,K] c[M,N] column_scale[N]");
+  auto base = [](const VecopsTensorView* v) { return static_cast<char*>(v->data) + v->byte_offset; };
+  p.a = base(t[0]);
+  p.a_stride_m = t[0]->strides[0];
+  p.a_stride_k = t[0]->strides[1];
+  p.b = base(t[1]);
+  p.b_stride_n = t[1]->strides[0];
+  p.b_stride_k = t[1]->strides[1];
+  p.c = base(t[2]);
+  p.c_stride_m = t[2]->strides[0];
+  p.c_stride_n = t[2]->strides[1];
+  if (t[3] != nullptr) {
+    if (t[3]->strides[0] != 1 && p.n > 1) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "column_scale must be contiguous");
+    p.column_scale = reinterpret_cast<const float*>(base(t[3]));
+  }
+  p.a_dtype = t[0]->dtype;
+  p.b_dtype = t[1]->dtype;
+  p.c_dtype = t[2]->dtype;
+  p.device_index = t[2]->device_index;
+  p.workspace = call->workspace;
+  p.workspace_size = call->workspace_size;
+  if (const VecopsExecutionContext* context = call->context) {
+    // append-only record: only read what the caller's struct_size covers
+    if (context->struct_size >= offsetof(VecopsExecutionContext, stream) + sizeof(context->stream)) p.stream = context->stream;
+    if (context->struct_size >= offsetof(VecopsExecutionContext, flags) + sizeof(context->flags) &&
+        (context->flags & VECOPS_B200_CONTEXT_FLAG_ASYNC) != 0)
+      p.flags |= VECOPS_B200_MATMUL_FLAG_ASYNC;
+  }
+  *out = p;
+  return VECOPS_STATUS_OK;
+}
+
+std::int32_t run_with(std::uint32_t kernel, const VecopsCall* call, VecopsError* error, bool only_workspace, std::uint64_t* bytes) {
+  VecopsB200Matmul problem;
+  if (const auto rc = problem_from_frame(call, kernel, &problem, error); rc != VECOPS_STATUS_OK) return rc;
+  if (only_workspace) return vecops_b200_matmul_workspace(&problem, bytes, error);
+  return vecops_b200_matmul_run(&problem, error);
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- definition
+
+KernelDef matmul_kernel_def() {
+  auto tensor = [](std::string name, std::vector<DimensionDef> shape, TensorDTypeDef dtype, TensorAccess access, bool optional) {
+    TensorDef t;
+    t.name = std::move(name);
+    t.strides.assign(shape.size(), DimensionDef::any());
+    t.shape = std::move(shape);
+    t.dtype = std::move(dtype);
+    t.access = access;
+    t.optional = optional;
+    t.device_type = VECOPS_DEVICE_CUDA;
+    t.device_index = -1;
+    return t;
+  };
+  auto M = [] { return DimensionDef::named_dynamic("M", 1, 0); };
+  auto N = [] { return DimensionDef::named_dynamic("N", 1, 0); };
+  auto K = [] { return DimensionDef::named_dynamic("K", 1, 0); };
+  return KernelDef(kOperatorName,
+                   {tensor("a", {M(), K()}, "TA", TensorAccess::Input, false),
+                    tensor("b", {N(), K()}, "TB", TensorAccess::Input, false),
+                    tensor("c", {M(), N()}, "TC", TensorAccess::Output, false),
+                    tensor("column_scale", {N()}, DType::Float32, TensorAccess::Input, true)},
+                   {{"TA", SpecializationType::DType}, {"TB", SpecializationType::DType}, {"TC", SpecializationType::DType}});
+}
+
+Result<VecopsB200Matmul> matmul_problem_from(std::span<const Value> values, std::uint32_t kernel) {
+  ArgumentMetadata arguments(std::vector<Value>(values.begin(), values.end()));
+  CallFrame frame(arguments);
+  VecopsB200Matmul problem;
+  ErrorText error;
+  if (const auto rc = problem_from_frame(&frame.abi(), kernel, &problem, &error.record); rc != VECOPS_STATUS_OK) return error.status(rc);
+  return problem;
+}
+
+// ---------------------------------------------------------------- recipe
+
+CudaMatmulRecipe::CudaMatmulRecipe(std::uint32_t kernel)
+    : kernel_(kernel), id_(std::string("cuda/sm_100a/") + (vecops_b200_kernel_name(kernel) ? vecops_b200_kernel_name(kernel) : "?")),
+      definition_(shared_definition()) {}
+
+Status CudaMatmulRecipe::match(const KernelCall& call) const {
+  auto problem = matmul_problem_from(call.arguments().values(), kernel_);
+  if (!problem) return Status(StatusCode::NotApplicable, problem.status().message());
+  ErrorText error;
+  std::uint32_t chosen = 0;
+  const auto rc = vecops_b200_matmul_select(&problem.value(), &chosen, &error.record);
+  if (rc == VECOPS_STATUS_OK) return Status::success();
+  // An unsupported dtype row is a property of the call, not of this recipe, but
+  // another operator recipe might still serve it: report "does not apply".
+  return Status(StatusCode::NotApplicable, error.text.data());
+}
+
+Result<BoundKernelRecipe> CudaMatmulRecipe::bind(const KernelCall& call) const {
+  auto binding = bind_kernel_call(*definition_, call);
+  if (!binding) return binding.status();
+  BoundKernelRecipe bound;
+  bound.recipe_id = id_;
+  bound.specialization_key = binding.value().specialization_key + ";kernel=" + vecops_b200_kernel_name(kernel_);
+  bound.artifact_key = id_;
+  return bound;
+}
+
+// ---------------------------------------------------------------- dispatch policy
+
+Result<std::vector<std::size_t>> MatmulRuntimeDispatch::candidates(
+    const KernelCall& call, std::span<const std::shared_ptr<const KernelRecipe>> recipes) const {
+  std::vector<std::size_t> order;
+  std::uint32_t chosen = VECOPS_B200_KERNEL_AUTO;
+  if (auto problem = matmul_problem_from(call.arguments().values(), VECOPS_B200_KERNEL_AUTO)) {
+    ErrorText error;
+    if (vecops_b200_matmul_select(&problem.value(), &chosen, &error.record) != VECOPS_STATUS_OK) chosen = VECOPS_B200_KERNEL_AUTO;
+  }
+  auto kernel_of = [&](std::size_t i) -> std::uint32_t {
+    const auto* recipe = dynamic_cast<const CudaMatmulRecipe*>(recipes[i].get());
+    return recipe != nullptr ? recipe->kernel() : static_cast<std::uint32_t>(VECOPS_B200_KERNEL_AUTO);
+  };
+  for (std::size_t i = 0; i < recipes.size(); ++i)
+    if (chosen != VECOPS_B200_KERNEL_AUTO && kernel_of(i) == chosen) order.push_back(i);
+  // then foreign recipes in declaration order, and the strided kernel as the safety net
+  for (std::size_t i = 0; i < recipes.size(); ++i)
+    if (kernel_of(i) == VECOPS_B200_KERNEL_AUTO) order.push_back(i);
+  for (std::size_t i = 0; i < recipes.size(); ++i)
+    if (kernel_of(i) == VECOPS_B200_KERNEL_GENERIC && chosen != VECOPS_B200_KERNEL_GENERIC) order.push_back(i);
+  return order;
+}
+
+// ---------------------------------------------------------------- provider
+
+namespace {
+struct OwnedDescriptor {
+  std::string key;
+  VecopsKernelDescriptorV1 descriptor;
+};
+}  // namespace
+
+Result<std::shared_ptr<Executable>> CudaExecutableProvider::resolve(const BoundKernelRecipe& recipe) {
+  {
+    std::lock_guard<std::mutex> lock(mutex_);
+    if (auto found = cache_.find(recipe.specialization_key); found != cache_.end()) return found->second;
+  }
+  constexpr std::string_view prefix = "cuda/sm_100a/";
+  if (!std::string_view(recipe.artifact_key).starts_with(prefix))
+    return Status(StatusCode::NotFound, "artifact '" + recipe.artifact_key + "' is not a prebuilt sm_100a kernel");
+  const std::string_view name = std::string_view(recipe.artifact_key).substr(prefix.size());
+  std::uint32_t kernel = VECOPS_B200_KERNEL_AUTO;
+  for (std::uint32_t k = 1; k < VECOPS_B200_KERNEL_COUNT_; ++k)
+    if (name == vecops_b200_kernel_name(k)) kernel = k;
+  const VariantDescriptor* variant = variant_descriptor(kernel);
+  if (kernel == VECOPS_B200_KERNEL_AUTO || variant == nullptr)
+    return Status(StatusCode::NotFound, "no prebuilt kernel image named '" + std::string(name) + "'");
+  if (kernel == VECOPS_B200_KERNEL_W8_TCGEN05)
+    return Status(StatusCode::NotFound, "kernel image 'w8_tcgen05' is not part of this build");
+  auto owned = std::make_shared<OwnedDescriptor>();
+  owned->key = recipe.specialization_key;
+  owned->descriptor = variant->descriptor;
+  owned->descriptor.specialization_key = owned->key.c_str();
+  auto module = LoadedModule::adopt(&owned->descriptor, owned);
+  if (!module) return module.status();
+  auto executable = std::make_shared<Executable>(std::move(module).value());
+  std::lock_guard<std::mutex> lock(mutex_);
+  // two threads may have raced to build the same key: the first one published wins
+  return cache_.emplace(recipe.specialization_key, std::move(executable)).first->second;
+}
+
+std::size_t CudaExecutableProvider::cached() const {
+  std::lock_guard<std::mutex> lock(mutex_);
+  return cache_.size();
+}
+
+std::shared_ptr<Operator> make_matmul_operator() {
+  std::vector<std::shared_ptr<const KernelRecipe>> recipes;
+  for (const auto kernel : kVariants) recipes.push_back(std::make_shared<CudaMatmulRecipe>(kernel));
+  return std::make_shared<Operator>(matmul_kernel_def(), std::move(recipes), std::make_shared<MatmulRuntimeDispatch>(),
+                                    std::make_shared<CudaExecutableProvider>());
+}
+
+const VecopsKernelDescriptorV1* matmul_descriptor_template(std::uint32_t kernel) {
+  const VariantDescriptor* variant = variant_descriptor(kernel);
+  return variant != nullptr ? &variant->descriptor : nullptr;
+}
+
+}  // namespace vecops::runtime
+
+// ------------------------------------------------------------------ C bridge
+
+using namespace vecops::runtime;
+
+namespace {
+
+constexpr std::uint64_t kMatmulHandle = 0x6d61746d756c0001ULL;
+
+const std::shared_ptr<Operator>& matmul_operator() {
+  static const std::shared_ptr<Operator> op = make_matmul_operator();
+  return op;
+}
+
+std::int32_t report(VecopsError* error, const Status& status) {
+  return fail(error, static_cast<std::int32_t>(status.code()), status.message().c_str());
+}
+
+// Copy the ABI frame into owned metadata (shape/stride arrays included).
+std::int32_t call_from_frame(const VecopsCall* call, std::uint32_t nspec, const VecopsSpecializationArgument* specs, KernelCall* out,
+                             VecopsError* error) {
+  if (call == nullptr || call->struct_size < sizeof(VecopsCall)) return fail(error, VECOPS_STATUS_ABI_MISMATCH, "call frame is null or too small");
+  if (call->num_values != 0 && call->values == nullptr) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "call frame has no values");
+  std::vector<Value> values;
+  for (std::uint32_t i = 0; i < call->num_values; ++i) {
+    const VecopsValue& v = call->values[i];
+    if (v.kind == VECOPS_VALUE_NONE) {
+      values.emplace_back(std::monostate{});
+    } else if (v.kind == VECOPS_VALUE_TENSOR) {
+      const VecopsTensorView& t = v.value.tensor;
+      if (t.rank != 0 && (t.sizes == nullptr || t.strides == nullptr)) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "tensor without sizes or strides");
+      TensorView view;
+      view.data = t.data;
+      view.byte_offset = t.byte_offset;
+      view.device_type = t.device_type;
+      view.device_index = t.device_index;
+      view.dtype = static_cast<DType>(t.dtype);
+      view.sizes.assign(t.sizes, t.sizes + t.rank);
+      view.strides.assign(t.strides, t.strides + t.rank);
+      view.flags = t.flags;
+      values.emplace_back(std::move(view));
+    } else if (v.kind == VECOPS_VALUE_SCALAR) {
+      Scalar s;
+      s.dtype = static_cast<DType>(v.value.scalar.dtype);
+      s.value = v.value.scalar.value;
+      values.emplace_back(s);
+    } else {
+      return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "unknown value kind");
+    }
+  }
+  SpecializationValues named;
+  for (std::uint32_t i = 0; i < nspec; ++i) {
+    if (specs == nullptr || specs[i].name == nullptr) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "specialization value without a name");
+    if (specs[i].kind == VECOPS_SPECIALIZATION_CONST_INT) named[specs[i].name] = specs[i].value.integer;
+    else if (specs[i].kind == VECOPS_SPECIALIZATION_DTYPE) named[specs[i].name] = static_cast<DType>(specs[i].value.dtype);
+    else return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "unknown specialization value kind");
+  }
+  *out = KernelCall(ArgumentMetadata(std::move(values)), std::move(named));
+  return VECOPS_STATUS_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+uint64_t vecops_b200_matmul_operator(void) {
+  (void)matmul_operator();
+  return kMatmulHandle;
+}
+
+int32_t vecops_operator_bridge_invoke_v1(uint64_t handle, const VecopsCall* call, uint32_t num_specialization_values,
+                                         const VecopsSpecializationArgument* specialization_values, VecopsError* error) {
+  if (handle != kMatmulHandle) return fail(error, VECOPS_STATUS_NOT_FOUND, "unknown operator handle");
+  KernelCall kernel_call;
+  if (const auto rc = call_from_frame(call, num_specialization_values, specialization_values, &kernel_call, error); rc != VECOPS_STATUS_OK) return rc;
+  const Status status = matmul_operator()->invoke(kernel_call, call->context, call->workspace, call->workspace_size);
+  return status.ok() ? VECOPS_STATUS_OK : report(error, status);
+}
+
+int32_t vecops_b200_operator_resolve(uint64_t handle, const VecopsCall* call, char* key, size_t capacity, VecopsError* error) {
+  if (handle != kMatmulHandle) return fail(error, VECOPS_STATUS_NOT_FOUND, "unknown operator handle");
+  KernelCall kernel_call;
+  if (const auto rc = call_from_frame(call, 0, nullptr, &kernel_call, error); rc != VECOPS_STATUS_OK) return rc;
+  auto executable = matmul_operator()->resolve(kernel_call, call->context);
+  if (!executable) return report(error, executable.status());
+  if (key != nullptr && capacity > 0) {
+    const auto text = executable.value()->specialization_key();
+    const size_t count = text.size() < capacity - 1 ? text.size() : capacity - 1;
+    std::memcpy(key, text.data(), count);
+    key[count] = '\0';
+  }
+  return VECOPS_STATUS_OK;
+}
+
+int32_t vecops_b200_operator_workspace(uint64_t handle, const VecopsCall* call, uint64_t* bytes, VecopsError* error) {
+  if (handle != kMatmulHandle) return fail(error, VECOPS_STATUS_NOT_FOUND, "unknown operator handle");
+  if (bytes == nullptr) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "bytes output pointer is null");
+  KernelCall kernel_call;
+  if (const auto rc = call_from_frame(call, 0, nullptr, &kernel_call, error); rc != VECOPS_STATUS_OK) return rc;
+  auto executable = matmul_operator()->resolve(kernel_call, call->context);
+  if (!executable) return report(error, executable.status());
+  auto bound = bind_kernel_call(matmul_kernel_def(), kernel_call);
+  if (!bound) return report(error, bound.status());
+  auto size = executable.value()->workspace_size(bound.value().arguments, call->context);
+  if (!size) return report(error, size.status());
+  *bytes = size.value();
+  return VECOPS_STATUS_OK;
+}
+
+const VecopsKernelDescriptorV1* vecops_b200_matmul_descriptor(uint32_t kernel) { return matmul_descriptor_template(kernel); }
+
+}  // extern "C"

@@ -1,0 +1,153 @@
+// Operator resolution and invocation.  Behaviour follows
+// src/runtime/Operator.cpp of vecops: logical schema :25-62, parallelism suffix
+// (source recipes only) :94-121, ordered policy :162-168, normalise :187-201,
+// candidate loop and key checks :215-263, invoke :265-285.
+#include "vecops_b200/runtime/operator.h"
+
+#include <algorithm>
+#include <numeric>
+
+namespace vecops::runtime {
+
+BoundKernelRecipe specialize_parallelism(BoundKernelRecipe recipe, std::int64_t parallelism) {
+  if (recipe.source == nullptr) return recipe;  // prebuilt artifacts carry no CPU lane count in their key
+  auto source = std::make_shared<BoundKernelRecipe::SourceInstantiation>(*recipe.source);
+  const std::string old_suffix = ";$Parallelism=i:" + std::to_string(source->parallelism);
+  auto strip = [&](std::string& text) {
+    if (text.ends_with(old_suffix)) text.resize(text.size() - old_suffix.size());
+  };
+  strip(source->binding.specialization_key);
+  strip(recipe.specialization_key);
+  strip(recipe.artifact_key);
+  source->parallelism = std::max<std::int64_t>(1, parallelism);
+  const std::string suffix = ";$Parallelism=i:" + std::to_string(source->parallelism);
+  source->binding.specialization_key += suffix;
+  recipe.specialization_key += suffix;
+  recipe.artifact_key += suffix;
+  recipe.source = std::move(source);
+  return recipe;
+}
+
+OperatorSchema logical_schema(const KernelDef& definition) {
+  auto constraint_of = [](const DimensionDef& d) {
+    if (d.kind() == DimensionDef::Kind::Fixed) return DimensionConstraint::constant(d.fixed_value());
+    if (d.kind() == DimensionDef::Kind::Dynamic && !d.alignment().is_symbol() && !d.lower_bound().is_symbol() &&
+        !d.upper_bound().is_symbol())
+      return DimensionConstraint::dynamic(d.lower_bound().fixed_value(), d.upper_bound().fixed_value(), d.alignment().fixed_value());
+    return DimensionConstraint::any();
+  };
+  std::vector<ParameterSchema> parameters;
+  for (const auto& parameter : definition.parameters()) {
+    if (const auto* scalar = std::get_if<ValueDef>(&parameter)) {
+      parameters.push_back(ParameterSchema{scalar->name, ScalarConstraint{dtype_bit(scalar->dtype)}});
+      continue;
+    }
+    const auto& tensor = std::get<TensorDef>(parameter);
+    TensorConstraint rule;
+    rule.rank = static_cast<std::uint32_t>(tensor.shape.size());
+    rule.device_type = tensor.device_type;
+    rule.device_index = tensor.device_index;
+    rule.optional = tensor.optional;
+    rule.required_flags = (tensor.readable() ? VECOPS_TENSOR_READ : 0) | (tensor.writable() ? VECOPS_TENSOR_WRITE : 0);
+    if (tensor.dtype.dtype()) rule.dtype_mask = dtype_bit(*tensor.dtype.dtype());
+    for (const auto& d : tensor.shape) rule.sizes.push_back(constraint_of(d));
+    for (const auto& d : tensor.strides) rule.strides.push_back(constraint_of(d));
+    parameters.push_back(ParameterSchema{tensor.name, std::move(rule)});
+  }
+  return OperatorSchema(definition.name(), std::move(parameters));
+}
+
+Result<std::vector<std::size_t>> OrderedDispatchPolicy::candidates(
+    const KernelCall&, std::span<const std::shared_ptr<const KernelRecipe>> recipes) const {
+  std::vector<std::size_t> order(recipes.size());
+  std::iota(order.begin(), order.end(), std::size_t{0});
+  return order;
+}
+
+Operator::Operator(OperatorSchema schema, std::vector<std::shared_ptr<const KernelRecipe>> recipes,
+                   std::shared_ptr<const DispatchPolicy> dispatch_policy, std::shared_ptr<ExecutableProvider> provider)
+    : schema_(std::move(schema)), recipes_(std::move(recipes)), dispatch_policy_(std::move(dispatch_policy)),
+      provider_(std::move(provider)) {}
+
+Operator::Operator(KernelDef definition, std::vector<std::shared_ptr<const KernelRecipe>> recipes,
+                   std::shared_ptr<const DispatchPolicy> dispatch_policy, std::shared_ptr<ExecutableProvider> provider)
+    : schema_(logical_schema(definition)), kernel_definition_(std::make_shared<KernelDef>(std::move(definition))),
+      recipes_(std::move(recipes)), dispatch_policy_(std::move(dispatch_policy)), provider_(std::move(provider)) {}
+
+Result<KernelCall> Operator::normalize(const KernelCall& call) const {
+  if (kernel_definition_ == nullptr) {
+    if (auto status = schema_.validate(call.arguments()); !status.ok()) return status;
+    return call;
+  }
+  auto binding = bind_kernel_call(*kernel_definition_, call);
+  if (!binding) return binding.status();
+  if (auto status = schema_.validate(binding.value().arguments); !status.ok()) return status;
+  return KernelCall(binding.value().arguments, binding.value().values);
+}
+
+Result<std::shared_ptr<Executable>> Operator::resolve(const ArgumentMetadata& arguments) const {
+  return resolve(KernelCall(arguments), nullptr);
+}
+
+Result<std::shared_ptr<Executable>> Operator::resolve(const KernelCall& call, const VecopsExecutionContext* context) const {
+  auto normalized = normalize(call);
+  if (!normalized) return normalized.status();
+  return resolve_normalized(normalized.value(), context);
+}
+
+Result<std::shared_ptr<Executable>> Operator::resolve_normalized(const KernelCall& call, const VecopsExecutionContext*) const {
+  if (dispatch_policy_ == nullptr || provider_ == nullptr)
+    return Status(StatusCode::InternalError, "operator has no dispatch policy or executable provider");
+  auto order = dispatch_policy_->candidates(call, recipes_);
+  if (!order) return order.status();
+  Status last(StatusCode::NotFound, "no kernel recipe accepted this invocation");
+  for (const auto index : order.value()) {
+    if (index >= recipes_.size() || recipes_[index] == nullptr)
+      return Status(StatusCode::InternalError, "dispatch policy returned an invalid recipe index");
+    const auto& recipe = recipes_[index];
+    if (auto status = recipe->match(call); !status.ok()) {
+      if (status.code() != StatusCode::NotApplicable) return status;
+      last = status;
+      continue;
+    }
+    auto bound = recipe->bind(call);
+    if (!bound) {
+      if (bound.status().code() != StatusCode::NotApplicable) return bound.status();
+      last = bound.status();
+      continue;
+    }
+    if (bound.value().recipe_id.empty()) bound.value().recipe_id = std::string(recipe->id());
+    // CPU lane counts only specialise source-compiled recipes; see specialize_parallelism.
+    bound.value() = specialize_parallelism(std::move(bound).value(), 1);
+    auto executable = provider_->resolve(bound.value());
+    if (!executable) {
+      const auto code = executable.status().code();
+      if (code != StatusCode::NotFound && code != StatusCode::NotApplicable) return executable.status();
+      last = executable.status();
+      continue;
+    }
+    if (executable.value() == nullptr) return Status(StatusCode::InternalError, "executable provider returned a null executable");
+    if (executable.value()->operator_name() != schema_.name())
+      return Status(StatusCode::AbiMismatch, "resolved executable belongs to a different operator");
+    if (executable.value()->specialization_key() != bound.value().specialization_key)
+      return Status(StatusCode::AbiMismatch, "resolved executable has a different specialization key");
+    return executable;
+  }
+  return last;
+}
+
+Status Operator::invoke(const ArgumentMetadata& arguments, void* workspace, std::uint64_t workspace_size,
+                        const VecopsExecutionContext* context) const {
+  return invoke(KernelCall(arguments), context, workspace, workspace_size);
+}
+
+Status Operator::invoke(const KernelCall& call, const VecopsExecutionContext* context, void* workspace,
+                        std::uint64_t workspace_size) const {
+  auto normalized = normalize(call);
+  if (!normalized) return normalized.status();
+  auto executable = resolve_normalized(normalized.value(), context);
+  if (!executable) return executable.status();
+  return executable.value()->invoke(normalized.value().arguments(), workspace, workspace_size, context);
+}
+
+}  // namespace vecops::runtime
