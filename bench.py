@@ -1,0 +1,538 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 matmul path.  Prints ONE JSON line on rank 0.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--no-extra]
+
+N = 1   headline workload: BF16 GEMM M=N=K=4096 (fp32 accumulate, bf16 out).  The other single-GPU
+        configurations are measured briefly and reported under "configs".
+N > 1   the large BF16 GEMM M=16384 N=53248 K=8192, B column-sharded over the ranks (one process per GPU,
+        launched by torch.distributed.run), A replicated, output slabs all-gathered over NCCL: strong scaling.
+
+A step is one pass of the operator over one batch of synthetic input.  `value` is measured with the operands
+resident in HBM (CUDA events on the launching stream, max over ranks); `e2e` runs the same step through the
+operator bridge with pinned HOST buffers, host->device copies of the inputs and a device->host read of the
+result inside the timed region.  `--impl reference` times the reference's own CPU matmul on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import sys
+import threading
+import time
+from ctypes import byref
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "GEMM TFLOP/s (BF16/INT8) & GB/s (decode) at 1/2/4/8 B200, % of roofline"
+NOMINAL = {"bf16_tflops": 2250.0, "i8_tops": 4500.0, "hbm_gbs": 8000.0, "fp32_tflops": 80.0}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
+# under profiles/ (None until a capture exists for that workload).
+NCU_TRAFFIC_BYTES = {"c2_bf16_4096": None, "c5_bf16_16384x53248x8192": None}
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return json.loads(path.read_text()), "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ---------------------------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a timed region runs (read-only)."""
+
+    REASONS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+               0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
+               0x100: "display_clock_setting"}
+
+    def __init__(self, index: int) -> None:
+        self.samples: list[int] = []
+        self.reason_bits = 0
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+        except Exception:  # NVML missing: report nothing rather than guess
+            self._nvml = None
+
+    def _loop(self) -> None:
+        nv = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
+                self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+            except Exception:
+                try:
+                    self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle))
+                except Exception:
+                    pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=1.0)
+
+    def summary(self) -> dict:
+        reasons = [name for bit, name in self.REASONS.items() if self.reason_bits & bit and name != "gpu_idle"]
+        return {"sm_mhz": int(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------------------------- our arm
+
+def device_sets(w, sets: int, dev, row0=0, row1=None):
+    """`sets` operand sets for workload `w` on `dev`: set 0 is the seeded workload, the rest same-distribution fills."""
+    import torch
+    from vecops_b200 import workloads
+    a0 = workloads.make_a(w)
+    b0 = workloads.make_b_nk(w, row0, row1)
+    s0 = workloads.make_scale(w, row0, row1)
+    bf16_a = w.kind in ("bf16", "w8")
+    bf16_b = w.kind == "bf16"
+
+    def up(x, as_bf16):
+        t = torch.from_numpy(x).to(dev)
+        return t.view(torch.bfloat16) if as_bf16 else t
+
+    out_dtype = {"f32": torch.float32, "i8": torch.int32}.get(w.kind, torch.bfloat16)
+    result = []
+    for i in range(sets):
+        if i == 0:
+            a, b = up(a0, bf16_a), up(b0, bf16_b)
+        else:
+            a, b = result[0]["a"].clone(), result[0]["b"][torch.randperm(b0.shape[0], device=dev)].contiguous()
+        if w.b_layout == "kn":
+            b = b.t().contiguous().t()  # stored as a row-major [K,N] matrix, addressed as its [N,K] view
+        result.append({"a": a, "b": b, "c": torch.empty((w.m, b0.shape[0]), dtype=out_dtype, device=dev),
+                       "scale": up(s0, False) if s0 is not None else None})
+    return result, (a0, b0, s0)
+
+
+def time_steps(step, steps: int, warmup: int, stream) -> float:
+    """Average milliseconds per step over exactly `steps` steps, CUDA events on `stream`."""
+    import torch
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for i in range(steps):
+        step(warmup + i)
+    stop.record(stream)
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / steps
+
+
+def take_status() -> int:
+    from vecops_b200 import capi
+    status = ctypes.c_uint32(0)
+    error = capi.ErrorBuffer()
+    capi.library().vecops_b200_take_device_status(0, byref(status), byref(error.record))
+    return status.value
+
+
+def parity_sample(w, host_inputs, c, port, rows: int = 16) -> dict:
+    """Checker on a few output rows of the seeded operand set."""
+    import torch
+    from oracle.checker import bf16_bits_to_f32, rel_frobenius
+    a0, b0, s0 = host_inputs
+    pick = np.unique(np.linspace(0, a0.shape[0] - 1, rows).astype(np.int64))
+    got = c[torch.from_numpy(pick).to(c.device)]
+    if w.kind == "i8":
+        want = port.matmul_i8(a0[pick], b0)
+        return {"rows": len(pick), "bit_exact": bool(np.array_equal(got.cpu().numpy(), want))}
+    if w.kind == "f32":
+        return {"rows": len(pick), "rel_fro": rel_frobenius(got.cpu().numpy(), port.matmul_f32(a0[pick], b0))}
+    got = bf16_bits_to_f32(got.contiguous().view(torch.int16).cpu().numpy().view(np.uint16))
+    want = port.matmul_bf16(a0[pick], b0) if w.kind == "bf16" else port.matmul_w8(a0[pick], b0, s0)
+    return {"rows": len(pick), "rel_fro": rel_frobenius(got, bf16_bits_to_f32(want))}
+
+
+def bound_of(w, peaks) -> tuple[str, float, float, str]:
+    """(bound, measured peak, nominal peak, unit) of the roofline that limits workload `w`."""
+    if w.kind == "bf16":
+        return "tensor", float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])), NOMINAL["bf16_tflops"], "TFLOP/s"
+    if w.kind == "i8":
+        # no measured int8 figure is provided: int8 dense is twice the bf16 rate on this part
+        return "tensor", 2.0 * float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])), NOMINAL["i8_tops"], "TOP/s"
+    if w.kind == "w8":
+        return "hbm", float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])), NOMINAL["hbm_gbs"], "GB/s"
+    return "fp32_fma", NOMINAL["fp32_tflops"], NOMINAL["fp32_tflops"], "TFLOP/s"
+
+
+def measure_single(name: str, steps: int, warmup: int, dev, port, peaks) -> dict:
+    """One single-GPU configuration with operands resident in HBM."""
+    import torch
+
+    import vecops_b200
+    from vecops_b200 import capi, harness, workloads
+    w = workloads.WORKLOADS[name]
+    l2 = 126e6
+    per_set = w.algorithmic_bytes
+    sets = 1 if per_set > 1.5 * l2 else int(np.ceil(1.6 * l2 / per_set)) + 1
+    operands, host_inputs = device_sets(w, sets, dev)
+    stream = torch.cuda.current_stream(dev)
+    kernel = vecops_b200.select_kernel(vecops_b200.matmul_problem(operands[0]["a"], operands[0]["b"], operands[0]["c"], operands[0]["scale"]))
+
+    def step(i):
+        o = operands[i % sets]
+        vecops_b200.matmul(o["a"], o["b"], o["c"], o["scale"], stream=stream, asynchronous=True)
+
+    step(0)
+    torch.cuda.synchronize()
+    parity = parity_sample(w, host_inputs, operands[0]["c"], port)
+    ms = time_steps(step, steps, warmup, stream)
+    status = take_status()
+    bound, peak, nominal, unit = bound_of(w, peaks)
+    achieved = (per_set / (ms * 1e-3) / 1e9) if bound == "hbm" else (w.flops / (ms * 1e-3) / 1e12)
+    return {"workload": name, "kernel": capi.library().vecops_b200_kernel_name(kernel).decode(), "ms_per_step": ms,
+            "value": achieved, "unit": unit, "bound": bound, "frac_of_measured_peak": achieved / peak,
+            "frac_of_nominal_peak": achieved / nominal, "tflops": w.flops / (ms * 1e-3) / 1e12,
+            "algorithmic_gb_per_s": per_set / (ms * 1e-3) / 1e9, "l2": f"rotating {sets} operand sets ({sets * per_set / 1e6:.0f} MB) vs L2 126 MB",
+            "parity": parity, "device_status": status}
+
+
+def bridge_invoker():
+    """Returns call(a, b, c, scale, stream): one asynchronous operator-bridge invocation (the reference-facing entry)."""
+    from vecops_b200 import capi
+    lib = capi.library()
+    lib.vecops_b200_matmul_operator.restype = ctypes.c_uint64
+    lib.vecops_operator_bridge_invoke_v1.argtypes = [ctypes.c_uint64, ctypes.POINTER(capi.VecopsCall), ctypes.c_uint32, ctypes.c_void_p,
+                                                     ctypes.POINTER(capi.VecopsError)]
+    handle = lib.vecops_b200_matmul_operator()
+
+    import vecops_b200
+
+    def value_of(t, writable, keep):
+        sizes = (ctypes.c_int64 * t.dim())(*t.shape)
+        strides = (ctypes.c_int64 * t.dim())(*t.stride())
+        keep += [sizes, strides]
+        v = capi.VecopsValue()
+        v.struct_size = ctypes.sizeof(capi.VecopsValue)
+        v.kind = capi.VALUE_TENSOR
+        tv = v.value.tensor
+        tv.struct_size = ctypes.sizeof(capi.VecopsTensorView)
+        tv.data, tv.byte_offset = t.data_ptr(), 0
+        tv.device_type, tv.device_index = capi.DEVICE_CUDA, t.device.index
+        tv.dtype, tv.rank, tv.sizes, tv.strides = vecops_b200.torch_dtype_code(t.dtype), t.dim(), sizes, strides
+        tv.flags = capi.TENSOR_READ | (capi.TENSOR_WRITE if writable else 0)
+        return v
+
+    def call(a, b, c, scale, stream):
+        keep: list = []
+        values = [value_of(a, False, keep), value_of(b, False, keep), value_of(c, True, keep)]
+        if scale is not None:
+            values.append(value_of(scale, False, keep))
+        array = (capi.VecopsValue * len(values))(*values)
+        context = capi.VecopsExecutionContext()
+        context.struct_size = ctypes.sizeof(context)
+        context.stream = stream.cuda_stream
+        context.flags = capi.CONTEXT_FLAG_ASYNC
+        frame = capi.VecopsCall(ctypes.sizeof(capi.VecopsCall), len(values), array, None, 0, ctypes.pointer(context))
+        error = capi.ErrorBuffer()
+        error.raise_for(lib.vecops_operator_bridge_invoke_v1(handle, byref(frame), 0, None, byref(error.record)))
+
+    return call
+
+
+def measure_e2e(w, operands, host_inputs, steps: int, warmup: int, dev) -> dict:
+    """Same step through the operator bridge with pinned host buffers; copies inside the timed region."""
+    import torch
+    o = operands[0]
+    a0, b0, s0 = host_inputs
+    invoke = bridge_invoker()
+    host_a = torch.from_numpy(a0).pin_memory()
+    host_b_src = b0 if w.b_layout == "nk" else np.ascontiguousarray(b0.T)
+    host_b = torch.from_numpy(host_b_src).pin_memory()
+    host_c = torch.empty(o["c"].shape, dtype=o["c"].dtype).pin_memory()
+    dev_a_raw = o["a"].view(torch.int16) if o["a"].dtype == torch.bfloat16 else o["a"]
+    b_storage = o["b"] if w.b_layout == "nk" else o["b"].t()
+    dev_b_raw = b_storage.view(torch.int16) if b_storage.dtype == torch.bfloat16 else b_storage
+    host_a_raw = host_a.view(torch.int16) if host_a.dtype == torch.uint16 else host_a
+    host_b_raw = host_b.view(torch.int16) if host_b.dtype == torch.uint16 else host_b
+    stream = torch.cuda.current_stream(dev)
+
+    def step(_):
+        dev_a_raw.copy_(host_a_raw, non_blocking=True)
+        dev_b_raw.copy_(host_b_raw, non_blocking=True)
+        invoke(o["a"], o["b"], o["c"], o["scale"], stream)
+        host_c.copy_(o["c"], non_blocking=True)
+
+    ms = time_steps(step, steps, warmup, stream)
+    h2d = host_a.numel() * host_a.element_size() + host_b.numel() * host_b.element_size()
+    d2h = host_c.numel() * host_c.element_size()
+    return {"ms_per_step": ms, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)}
+
+
+def cpu_baseline(w, steps: int = 3) -> dict:
+    """The reference's CPU matmul (or, where it cannot run, the C restatement) on a bounded sample of `w`."""
+    from oracle.checker import Port, Ref
+    from vecops_b200 import workloads
+    ref, why = Ref.load()
+    cores = Ref.default_threads()
+    unit = "GB/s" if w.kind == "w8" else ("TOP/s" if w.kind == "i8" else "TFLOP/s")
+    if ref is not None and w.kind in ("bf16", "i8", "w8"):
+        rows = min(w.m, 4096 if w.kind != "w8" else w.m)
+        cols = w.n if w.kind != "w8" else min(w.n, 1024 * cores)   # the reference's int8->bf16 conversion path is untuned
+        a, b = workloads.make_a(w, 0, rows), workloads.make_b_nk(w, 0, cols)
+        s = workloads.make_scale(w, 0, cols)
+        run = {"bf16": lambda: ref.matmul_bf16(a, b, True, cores), "i8": lambda: ref.matmul_i8(a, b, cores),
+               "w8": lambda: ref.matmul_w8(a, b, s, cores)}[w.kind]
+        kind, isa = "reference", "AMX (tdpbf16ps / tdpbssd) via the reference's ops::matmul"
+    else:
+        port = Port()
+        rows, cols = min(w.m, 64), w.n
+        a, b = workloads.make_a(w, 0, rows), workloads.make_b_nk(w, 0, cols)
+        s = workloads.make_scale(w, 0, cols)
+        run = {"bf16": lambda: port.matmul_bf16(a, b), "i8": lambda: port.matmul_i8(a, b), "w8": lambda: port.matmul_w8(a, b, s),
+               "f32": lambda: port.matmul_f32(a, b)}[w.kind]
+        kind, isa = "port", f"C restatement, OpenMP ({why or 'reference has no fp32 matmul on x86'})"
+        cores = port.threads
+    run()
+    best = min(_timed(run) for _ in range(steps))
+    flops = 2.0 * rows * cols * w.k
+    value = ((cols * w.k + 2 * rows * w.k + 2 * rows * cols) / best / 1e9) if w.kind == "w8" else flops / best / 1e12
+    return {"value": value, "unit": unit, "cores": cores, "kind": kind, "isa": isa,
+            "sample": f"{rows}x{cols}x{w.k} of {w.m}x{w.n}x{w.k}, best of {steps}", "seconds": best}
+
+
+def _timed(fn) -> float:
+    t0 = time.perf_counter()
+    fn()
+    return time.perf_counter() - t0
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    import vecops_b200
+    from oracle.checker import Port
+    from vecops_b200 import capi, sharding, workloads
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = capi.library()
+    peaks, peak_source = measured_peaks()
+    port = Port()
+
+    name = args.workload or ("c2_bf16_4096" if world == 1 else "c5_bf16_16384x53248x8192")
+    w = workloads.WORKLOADS[name]
+    sharded = world > 1 or name.startswith("c5")
+    steps = args.steps if args.steps is not None else (3 if sharded else 200)
+    warmup = args.warmup if args.warmup is not None else (3 if sharded else 10)
+    stream = torch.cuda.current_stream(dev)
+
+    if sharded:
+        n0, n1 = sharding.column_partition(w.n, world, rank)
+        operands, host_inputs = device_sets(w, 1, dev, n0, n1)
+        o = operands[0]
+        full = torch.empty((w.m, w.n), dtype=torch.bfloat16, device=dev)
+        staging = torch.empty((world, w.m, n1 - n0), dtype=torch.bfloat16, device=dev)
+        place = sharding.cuda_place(stream)
+
+        def step(_):
+            vecops_b200.matmul(o["a"], o["b"], o["c"], None, stream=stream, asynchronous=True)
+            sharding.gather_columns(o["c"], full, staging, world, place=place)
+
+        sets_note = f"operands {w.algorithmic_bytes / 1e9:.2f} GB > L2 126 MB"
+        launches_per_step = 1 + world
+    else:
+        per_set = w.algorithmic_bytes
+        sets = 1 if per_set > 1.5 * 126e6 else int(np.ceil(1.6 * 126e6 / per_set)) + 1
+        operands, host_inputs = device_sets(w, sets, dev)
+        o = operands[0]
+
+        def step(i):
+            x = operands[i % sets]
+            vecops_b200.matmul(x["a"], x["b"], x["c"], x["scale"], stream=stream, asynchronous=True)
+
+        sets_note = f"rotating {sets} operand sets ({sets * per_set / 1e6:.0f} MB) > L2 126 MB"
+        launches_per_step = 1
+
+    step(0)
+    torch.cuda.synchronize()
+    parity = parity_sample(w, host_inputs, o["c"], port, rows=8 if sharded else 16)
+
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches_before = lib.vecops_b200_launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        start.record(stream)
+        for i in range(steps):
+            step(warmup + i)
+        stop.record(stream)
+        torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches = lib.vecops_b200_launch_count() - launches_before
+    elapsed = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    ms = float(elapsed.item()) / steps
+    status = take_status()
+
+    # the GEMM kernel alone (what the roofline describes), timed live on the same stream
+    def gemm_only(i):
+        x = operands[i % len(operands)]
+        vecops_b200.matmul(x["a"], x["b"], x["c"], x["scale"], stream=stream, asynchronous=True)
+
+    kernel_ms = time_steps(gemm_only, steps, min(warmup, 3), stream) if sharded else ms
+    local_flops = 2.0 * w.m * (o["b"].shape[0]) * w.k
+    bound, peak, nominal, unit = bound_of(w, peaks)
+    if sharded:
+        peak = float(peaks.get("bf16_tflops_sustained", peak))  # seconds-long launches run under the power cap
+    achieved = local_flops / (kernel_ms * 1e-3) / 1e12
+    value = w.flops / (ms * 1e-3) / 1e12
+
+    # end to end through the operator bridge with host buffers
+    e2e_steps = max(1, min(steps, 20 if not sharded else 2))
+    e2e = measure_e2e(w, operands, host_inputs, e2e_steps, 1 if sharded else 3, dev)
+    e2e_ms = torch.tensor([e2e["ms_per_step"]], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_value = w.flops / (float(e2e_ms.item()) * 1e-3) / 1e12
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if sharded else "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (seeded; shapes, layouts and value distributions of the named configuration)",
+        "config": {"workload": name, "description": w.description, "m": w.m, "n": w.n, "k": w.k,
+                   "parallelism": f"N-sharded x{world}, NCCL all-gather of C slabs" if sharded else "single GPU",
+                   "l2": sets_note, "timing": "CUDA events on the launch stream, max over ranks"},
+        "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": f"{peak_source}: cuBLAS bf16 " + ("sustained" if sharded else "burst"),
+                     "frac_of_nominal": achieved / nominal, "kernel": "gemm_tcgen05_kernel<bf16>", "kernel_ms": kernel_ms,
+                     "algorithmic_flops_per_launch": local_flops, "algorithmic_bytes_per_launch": 2 * (w.m * w.k + o["b"].shape[0] * w.k + w.m * o["b"].shape[0])},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": e2e["d2h_bytes_per_step"], "ms_per_step": float(e2e_ms.item()), "steps": e2e_steps,
+                "path": "vecops_operator_bridge_invoke_v1 (Operator -> MatmulRuntimeDispatch -> CudaExecutableProvider -> descriptor.run), pinned host buffers"},
+        "gpu_launches": int(launches), "launches_per_step": launches_per_step, "clocks": clocks.summary(),
+        "parity": parity, "device_status": status,
+    }
+
+    if rank == 0 and world == 1:
+        try:
+            line["cpu_baseline"] = cpu_baseline(w)
+        except Exception as error:  # the baseline is reported, never the reason a GPU number is lost
+            line["cpu_baseline"] = {"error": repr(error)}
+        if not args.no_extra and not args.workload:
+            del operands, o
+            torch.cuda.empty_cache()
+            extras = {}
+            for extra, k_steps in [("c1_f32_1024", 100), ("c3_i8_4096x14336x4096", 50), ("c4_w8_m1", 200), ("c4_w8_m16", 200),
+                                   ("c4_w8_m128", 100)]:
+                try:
+                    extras[extra] = measure_single(extra, k_steps, 5, dev, port, peaks)
+                except Exception as error:
+                    extras[extra] = {"error": repr(error)}
+                torch.cuda.empty_cache()
+            line["configs"] = extras
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------- reference arm
+
+def run_reference(args) -> None:
+    """The reference's own CPU matmul on the host cores, same metric and configuration as our arm."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    from oracle.checker import Port, Ref
+    from vecops_b200 import workloads
+    name = args.workload or ("c2_bf16_4096" if world == 1 else "c5_bf16_16384x53248x8192")
+    w = workloads.WORKLOADS[name]
+    steps = args.steps if args.steps is not None else 5
+    warmup = args.warmup if args.warmup is not None else 1
+    ref, why = Ref.load()
+    cores = Ref.default_threads()
+    if ref is not None:
+        rows = w.m if w.flops <= 2e11 else 256          # a 256-row slab of the large GEMM, all N columns
+        a, b = workloads.make_a(w, 0, rows), workloads.make_b_nk(w)
+        run = lambda: ref.matmul_bf16(a, b, True, cores)
+        kind = "reference"
+        how = f"reference ops::matmul<AMX_BF16F32>, {cores} threads each owning an N slice"
+    else:
+        port = Port()
+        rows, cores = 64, port.threads
+        a, b = workloads.make_a(w, 0, rows), workloads.make_b_nk(w)
+        run = lambda: port.matmul_bf16(a, b)
+        kind = "port"
+        how = f"C restatement with OpenMP ({why})"
+    for _ in range(warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run()
+    seconds = (time.perf_counter() - t0) / steps
+    value = 2.0 * rows * w.n * w.k / seconds / 1e12
+    sample = f"{rows} of {w.m} rows x all {w.n} columns per step" + ("" if rows == w.m else " (throughput of the sample; the full job scales linearly in M)")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "strong" if world > 1 or name.startswith("c5") else "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (same seeded inputs as the GPU arm)",
+            "config": {"workload": name, "description": w.description, "m": w.m, "n": w.n, "k": w.k, "parallelism": f"{cores} host threads", "how": how},
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=None)
+    parser.add_argument("--warmup", type=int, default=None)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--workload", default=None, help="override the workload (a name from vecops_b200.workloads.WORKLOADS)")
+    parser.add_argument("--no-extra", action="store_true", help="skip the brief measurements of the other single-GPU configurations")
+    args = parser.parse_args()
+    if args.warmup is not None and args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3  # timing rule: at least three warm-up steps
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

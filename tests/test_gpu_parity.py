@@ -1,0 +1,287 @@
+"""Parity of the CUDA kernels with the CPU checker, through the C ABI.
+
+Every case calls `vecops_b200_matmul_run` (directly or through the operator
+bridge) on device tensors and compares with the checker on the same seeded
+inputs: bit-exact for int32 results, relative Frobenius error within the stated
+tolerance for floating-point results.
+"""
+import ctypes
+from ctypes import byref
+
+import numpy as np
+import pytest
+import torch
+
+import vecops_b200
+from oracle.checker import bf16_bits_to_f32, f32_to_bf16_bits, rel_frobenius
+from tests.helpers import TOL_BF16, TOL_F32, bf16_result_to_numpy, to_device
+from vecops_b200 import capi, harness
+
+pytestmark = pytest.mark.gpu
+
+K = capi  # kernel ids live there
+
+
+def run_case(kind, a, b, scale=None, out_bf16=True, kernel=capi.KERNEL_AUTO, b_kn=False, ldc_pad=0):
+    """Run on the GPU; returns a numpy result in the checker's representation."""
+    m, n = a.shape[0], b.shape[0]
+    da = to_device(a, bf16=kind in ("bf16", "w8"))
+    if b_kn:  # store B as a row-major [K,N] matrix and hand over its [N,K] view
+        db = to_device(np.ascontiguousarray(b.T), bf16=kind == "bf16").t()
+    else:
+        db = to_device(b, bf16=kind == "bf16")
+    ds = to_device(scale) if scale is not None else None
+    out_dtype = {"f32": torch.float32, "i8": torch.int32}.get(kind, torch.bfloat16 if out_bf16 else torch.float32)
+    storage = torch.full((m, n + ldc_pad), -3, dtype=out_dtype, device="cuda")
+    c = storage[:, :n]
+    vecops_b200.matmul(da, db, c, ds, kernel=kernel)
+    torch.cuda.synchronize()
+    if ldc_pad:
+        assert bool((storage[:, n:] == -3).all()), "kernel wrote outside its C columns"
+    return bf16_result_to_numpy(c) if out_dtype == torch.bfloat16 else c.contiguous().cpu().numpy()
+
+
+def check(kind, got, want, name=""):
+    if kind == "i8":
+        assert np.array_equal(got, want), f"{name}: int32 results differ"
+    elif kind == "f32":
+        assert rel_frobenius(got, want) <= TOL_F32, name
+    else:
+        g = bf16_bits_to_f32(got) if got.dtype == np.uint16 else got
+        w = bf16_bits_to_f32(want) if want.dtype == np.uint16 else want
+        assert rel_frobenius(g, w) <= TOL_BF16, name
+
+
+def inputs(kind, m, n, k, rng, a_dtype=np.int8, b_dtype=np.int8):
+    if kind == "f32":
+        return rng.uniform(-1, 1, (m, k)).astype(np.float32), rng.uniform(-1, 1, (n, k)).astype(np.float32), None
+    if kind == "bf16":
+        return (f32_to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32)),
+                f32_to_bf16_bits(rng.standard_normal((n, k), dtype=np.float32)), None)
+    if kind == "i8":
+        lo_a, hi_a = (-128, 128) if a_dtype == np.int8 else (0, 256)
+        lo_b, hi_b = (-128, 128) if b_dtype == np.int8 else (0, 256)
+        return rng.integers(lo_a, hi_a, (m, k)).astype(a_dtype), rng.integers(lo_b, hi_b, (n, k)).astype(b_dtype), None
+    if kind == "w8":
+        return (f32_to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32)), rng.integers(-127, 128, (n, k), dtype=np.int8),
+                rng.uniform(0.001, 0.02, n).astype(np.float32))
+    raise ValueError(kind)
+
+
+def oracle(kind, port, a, b, scale, out_bf16=True):
+    from tests.helpers import oracle_for
+    return oracle_for(kind, port, a, b, scale, out_bf16)
+
+
+# ------------------------------------------------------------------ golden fixtures (outputs of the reference itself)
+
+def test_golden_fixtures_through_automatic_dispatch(golden):
+    for name, case in golden.items():
+        kind = str(case["kind"])
+        a, b = case["a"], case["b"]
+        if kind == "i8":
+            check(kind, run_case(kind, a, b), case["c"], name)
+        elif kind == "f32":
+            check(kind, run_case(kind, a, b), case["c"], name)
+        elif kind == "bf16":
+            check(kind, run_case(kind, a, b, out_bf16=False), case["c_f32"], name)
+            check(kind, run_case(kind, a, b, out_bf16=True), case["c_bf16"], name)
+        else:
+            check(kind, run_case(kind, a, b, case["scale"]), case["c_bf16"], name)
+
+
+# ------------------------------------------------------------------ each kernel, forced, over shapes with tails
+
+TC_SHAPES = [(128, 256, 64), (128, 256, 512), (512, 1024, 512), (200, 328, 200), (1, 256, 128), (129, 257, 72), (640, 768, 1032)]
+
+
+@pytest.mark.parametrize("m,n,k", TC_SHAPES)
+@pytest.mark.parametrize("out_bf16", [True, False])
+def test_bf16_tcgen05(port, m, n, k, out_bf16):
+    rng = np.random.default_rng(m * 7 + n * 3 + k)
+    a, b, _ = inputs("bf16", m, n, k, rng)
+    check("bf16", run_case("bf16", a, b, out_bf16=out_bf16, kernel=K.KERNEL_BF16_TCGEN05), oracle("bf16", port, a, b, None, out_bf16))
+
+
+def test_bf16_tcgen05_scale_and_padded_c(port):
+    rng = np.random.default_rng(21)
+    a, b, _ = inputs("bf16", 300, 520, 264, rng)
+    scale = rng.uniform(0.5, 2.0, 520).astype(np.float32)
+    for out_bf16 in (True, False):
+        got = run_case("bf16", a, b, scale, out_bf16, K.KERNEL_BF16_TCGEN05, ldc_pad=24)
+        check("bf16", got, oracle("bf16", port, a, b, scale, out_bf16))
+
+
+def test_bf16_tcgen05_direct_epilogue_for_unaligned_c(port):
+    # a C row pitch that is not a multiple of 16 bytes cannot use TMA stores: the direct path must serve it
+    rng = np.random.default_rng(22)
+    a, b, _ = inputs("bf16", 150, 300, 128, rng)
+    got = run_case("bf16", a, b, None, True, K.KERNEL_BF16_TCGEN05, ldc_pad=3)
+    check("bf16", got, oracle("bf16", port, a, b, None, True))
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (384, 512, 1024), (150, 300, 272), (1, 512, 4096), (257, 129, 48)])
+@pytest.mark.parametrize("a_dtype,b_dtype", [(np.int8, np.int8), (np.uint8, np.int8), (np.int8, np.uint8), (np.uint8, np.uint8)])
+def test_i8_tcgen05_all_signedness_pairs(port, m, n, k, a_dtype, b_dtype):
+    rng = np.random.default_rng(m + n + k)
+    a, b, _ = inputs("i8", m, n, k, rng, a_dtype, b_dtype)
+    check("i8", run_case("i8", a, b, kernel=K.KERNEL_I8_TCGEN05), port.matmul_i8(a, b))
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 16, 17, 32, 40, 128])
+def test_w8_small_m(port, m):
+    rng = np.random.default_rng(100 + m)
+    a, w, s = inputs("w8", m, 208, 512, rng)
+    check("w8", run_case("w8", a, w, s, kernel=K.KERNEL_W8_SMALL_M), port.matmul_w8(a, w, s))
+
+
+def test_w8_small_m_ragged_n_no_scale_f32_out(port):
+    rng = np.random.default_rng(9)
+    a, w, s = inputs("w8", 5, 77, 96, rng)
+    check("w8", run_case("w8", a, w, None, False, K.KERNEL_W8_SMALL_M), port.matmul_w8(a, w, None, False))
+    check("w8", run_case("w8", a, w, s, True, K.KERNEL_W8_SMALL_M, ldc_pad=5), port.matmul_w8(a, w, s, True))
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 64, 64), (200, 300, 100), (130, 70, 45), (1, 1000, 333), (1024, 1024, 1024)])
+@pytest.mark.parametrize("b_kn", [True, False])
+def test_f32_simt(port, m, n, k, b_kn):
+    rng = np.random.default_rng(m + 2 * n + 3 * k)
+    a, b, _ = inputs("f32", m, n, k, rng)
+    check("f32", run_case("f32", a, b, kernel=K.KERNEL_F32_SIMT, b_kn=b_kn), port.matmul_f32(a, b))
+
+
+@pytest.mark.parametrize("kind", ["f32", "bf16", "i8", "w8"])
+def test_strided_kernel_on_reference_test_shapes(port, kind):
+    # ragged shapes and K tails the reference exercises (tests/ops/MatmulTest.cpp:434-452)
+    for m, n, k in [(16, 16, 35), (37, 51, 79), (1, 48, 79), (512, 1, 256), (96, 16, 67)]:
+        rng = np.random.default_rng(m * n + k)
+        a, b, s = inputs(kind, m, n, k, rng, np.uint8, np.int8)
+        got = run_case(kind, a, b, s, kernel=K.KERNEL_GENERIC, b_kn=(kind == "f32"), ldc_pad=1)
+        check(kind, got, oracle(kind, port, a, b, s))
+
+
+def test_int32_accumulators_wrap_like_the_reference(port):
+    # K = 262145 of 127*127 (and 255*255) overflows int32 and must wrap (tests/ops/MatmulTest.cpp:1025-1055)
+    k = 262145
+    for dtype, value in ((np.int8, 127), (np.uint8, 255)):
+        a = np.full((1, k), value, dtype=dtype)
+        got = run_case("i8", a, a)
+        assert got[0, 0] == np.uint32((value * value * k) % (1 << 32)).astype(np.int32)
+
+
+def test_empty_reduction_stores_zeros_and_empty_outputs_are_no_ops():
+    a = torch.empty((5, 0), dtype=torch.bfloat16, device="cuda")
+    b = torch.empty((7, 0), dtype=torch.bfloat16, device="cuda")
+    c = torch.full((5, 7), 9.0, dtype=torch.bfloat16, device="cuda")
+    vecops_b200.matmul(a, b, c)
+    assert bool((c == 0).all())  # K == 0 -> C = 0 (ops/Matmul.h:41-43)
+    vecops_b200.matmul(torch.empty((0, 8), dtype=torch.float32, device="cuda"), torch.empty((4, 8), dtype=torch.float32, device="cuda"),
+                       torch.empty((0, 4), dtype=torch.float32, device="cuda"))
+
+
+def test_full_range_int8_extremes(port):
+    # -128 * -128 * K: the largest magnitudes the int8 path can see
+    a = np.full((128, 4096), -128, dtype=np.int8)
+    b = np.full((256, 4096), -128, dtype=np.int8)
+    b[::2] = 127
+    check("i8", run_case("i8", a, b, kernel=K.KERNEL_I8_TCGEN05), port.matmul_i8(a, b))
+
+
+# ------------------------------------------------------------------ the operator path (bridge -> Operator -> provider -> descriptor.run)
+
+def _tensor_value(t, writable=False, keep=None):
+    sizes = (ctypes.c_int64 * t.dim())(*t.shape)
+    strides = (ctypes.c_int64 * t.dim())(*t.stride())
+    keep.extend([sizes, strides])
+    v = capi.VecopsValue()
+    v.struct_size = ctypes.sizeof(capi.VecopsValue)
+    v.kind = capi.VALUE_TENSOR
+    tv = v.value.tensor
+    tv.struct_size = ctypes.sizeof(capi.VecopsTensorView)
+    tv.data = t.data_ptr()
+    tv.byte_offset = 0
+    tv.device_type = capi.DEVICE_CUDA if t.is_cuda else capi.DEVICE_CPU
+    tv.device_index = t.device.index if t.is_cuda else 0
+    tv.dtype = vecops_b200.torch_dtype_code(t.dtype)
+    tv.rank = t.dim()
+    tv.sizes = sizes
+    tv.strides = strides
+    tv.flags = capi.TENSOR_READ | (capi.TENSOR_WRITE if writable else 0)
+    return v
+
+
+def bridge_call(a, b, c, scale=None, stream=None, asynchronous=False):
+    keep = []
+    values = [_tensor_value(a, keep=keep), _tensor_value(b, keep=keep), _tensor_value(c, True, keep=keep)]
+    if scale is not None:
+        values.append(_tensor_value(scale, keep=keep))
+    array = (capi.VecopsValue * len(values))(*values)
+    context = capi.VecopsExecutionContext()
+    context.struct_size = ctypes.sizeof(context)
+    context.stream = stream.cuda_stream if stream is not None else None
+    context.flags = capi.CONTEXT_FLAG_ASYNC if asynchronous else 0
+    call = capi.VecopsCall(ctypes.sizeof(capi.VecopsCall), len(values), array, None, 0, ctypes.pointer(context))
+    keep.extend([array, context])
+    return call, keep
+
+
+def bridge_lib():
+    lib = capi.library()
+    lib.vecops_b200_matmul_operator.restype = ctypes.c_uint64
+    lib.vecops_operator_bridge_invoke_v1.argtypes = [ctypes.c_uint64, ctypes.POINTER(capi.VecopsCall), ctypes.c_uint32, ctypes.c_void_p,
+                                                     ctypes.POINTER(capi.VecopsError)]
+    lib.vecops_b200_operator_resolve.argtypes = [ctypes.c_uint64, ctypes.POINTER(capi.VecopsCall), ctypes.c_char_p, ctypes.c_size_t,
+                                                 ctypes.POINTER(capi.VecopsError)]
+    return lib, lib.vecops_b200_matmul_operator()
+
+
+@pytest.mark.parametrize("kind,m,n,k", [("bf16", 256, 512, 256), ("i8", 256, 512, 256), ("w8", 16, 256, 512), ("f32", 96, 80, 64),
+                                        ("bf16", 16, 16, 35)])
+def test_operator_bridge_invokes_the_selected_kernel(port, kind, m, n, k):
+    lib, handle = bridge_lib()
+    rng = np.random.default_rng(k)
+    a, b, s = inputs(kind, m, n, k, rng)
+    da = to_device(a, bf16=kind in ("bf16", "w8"))
+    db = to_device(b, bf16=kind == "bf16")
+    ds = to_device(s) if s is not None else None
+    out_dtype = {"f32": torch.float32, "i8": torch.int32}.get(kind, torch.bfloat16)
+    c = torch.zeros((m, n), dtype=out_dtype, device="cuda")
+    call, keep = bridge_call(da, db, c, ds)
+    error = capi.ErrorBuffer()
+    key = ctypes.create_string_buffer(256)
+    error.raise_for(lib.vecops_b200_operator_resolve(handle, byref(call), key, 256, byref(error.record)))
+    assert key.value.decode().startswith("vecops::matmul;TA=")
+    before = lib.vecops_b200_launch_count()
+    error.raise_for(lib.vecops_operator_bridge_invoke_v1(handle, byref(call), 0, None, byref(error.record)))
+    assert lib.vecops_b200_launch_count() == before + 1
+    got = bf16_result_to_numpy(c) if out_dtype == torch.bfloat16 else c.cpu().numpy()
+    check(kind, got, oracle(kind, port, a, b, s))
+
+
+def test_operator_bridge_async_on_a_side_stream(port):
+    lib, handle = bridge_lib()
+    rng = np.random.default_rng(3)
+    a, b, _ = inputs("bf16", 512, 512, 512, rng)
+    da, db = to_device(a, True), to_device(b, True)
+    c = torch.zeros((512, 512), dtype=torch.bfloat16, device="cuda")
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    call, keep = bridge_call(da, db, c, stream=stream, asynchronous=True)
+    error = capi.ErrorBuffer()
+    error.raise_for(lib.vecops_operator_bridge_invoke_v1(handle, byref(call), 0, None, byref(error.record)))
+    stream.synchronize()
+    status = ctypes.c_uint32(1)
+    error.raise_for(lib.vecops_b200_take_device_status(0, byref(status), byref(error.record)))
+    assert status.value == 0
+    check("bf16", bf16_result_to_numpy(c), port.matmul_bf16(a, b))
+
+
+def test_operator_bridge_refuses_host_tensors_and_bad_handles():
+    lib, handle = bridge_lib()
+    a = torch.zeros((8, 8), dtype=torch.float32)
+    c = torch.zeros((8, 8), dtype=torch.float32)
+    call, keep = bridge_call(a, a, c)
+    error = capi.ErrorBuffer()
+    assert lib.vecops_operator_bridge_invoke_v1(handle, byref(call), 0, None, byref(error.record)) == capi.INVALID_ARGUMENT
+    assert b"wrong device" in error.text.value
+    assert lib.vecops_operator_bridge_invoke_v1(12345, byref(call), 0, None, byref(error.record)) == capi.NOT_FOUND
