@@ -21,6 +21,7 @@
 #include "gemm_tcgen05.cuh"
 #include "simt_kernels.cuh"
 #include "w8_small_m.cuh"
+#include "w8_stream.cuh"
 #include "shim_util.h"
 
 namespace vb200 {
@@ -396,8 +397,45 @@ void launch_w8_small_typed(const VecopsB200Matmul& p, cudaStream_t stream) {
   g_launches.fetch_add(1);
 }
 
-int32_t launch_w8_small(const VecopsB200Matmul& p, cudaStream_t stream, VecopsError* error) {
+template <int kMTiles, int kChunks, typename OutT>
+int32_t launch_w8_stream_typed(const VecopsB200Matmul& p, const DeviceState& dev, cudaStream_t stream, VecopsError* error) {
+  using G = W8Stream;
+  auto kernel = w8_stream_kernel<kMTiles, kChunks, OutT>;
+  const int smem = G::smem_bytes(static_cast<int>(p.k), kMTiles);
+  // the attribute is per kernel instantiation and per device; setting it is cheap and idempotent
+  int32_t rc = raise_smem_limit(kernel, smem, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  const long long items = (p.n + G::kRows - 1) / G::kRows;
+  const int grid = static_cast<int>(items < dev.prop.multiProcessorCount ? items : dev.prop.multiProcessorCount);
+  kernel<<<grid, G::kThreads, smem, stream>>>(static_cast<const __nv_bfloat16*>(p.a), p.a_stride_m, static_cast<const int8_t*>(p.b),
+                                              p.b_stride_n, p.column_scale, static_cast<OutT*>(p.c), p.c_stride_m,
+                                              static_cast<int>(p.m), static_cast<int>(p.n), static_cast<int>(p.k), g_status_host);
+  g_launches.fetch_add(1);
+  return VECOPS_STATUS_OK;
+}
+
+// The streaming form serves the decode shapes proper: few activation rows
+// (they stay in registers) and a K that fits the shared-memory ring.
+bool w8_stream_applicable(const VecopsB200Matmul& p, const DeviceState& dev) {
+  const char* path = getenv("VECOPS_B200_W8_PATH");
+  if (path != nullptr && strcmp(path, "small") == 0) return false;
+  return dev.prop.major >= 9 && p.m <= 16 && p.k % W8Stream::kChunkK == 0 && p.k <= W8Stream::kMaxK &&
+         static_cast<size_t>(W8Stream::smem_bytes(static_cast<int>(p.k), 2)) <= dev.prop.sharedMemPerBlockOptin;
+}
+
+int32_t launch_w8_small(const VecopsB200Matmul& p, const DeviceState& dev, cudaStream_t stream, VecopsError* error) {
   if (p.c_stride_n != 1) return set_error(error, VECOPS_STATUS_NOT_APPLICABLE, "w8_small_m needs a row-major C");
+  if (w8_stream_applicable(p, dev)) {
+    const bool bf16_out = p.c_dtype == VECOPS_DTYPE_BF16;
+    const bool one_tile = p.m <= 8, one_chunk = p.k <= 2048;
+    if (one_tile && one_chunk)
+      return bf16_out ? launch_w8_stream_typed<1, 1, __nv_bfloat16>(p, dev, stream, error) : launch_w8_stream_typed<1, 1, float>(p, dev, stream, error);
+    if (one_tile)
+      return bf16_out ? launch_w8_stream_typed<1, 2, __nv_bfloat16>(p, dev, stream, error) : launch_w8_stream_typed<1, 2, float>(p, dev, stream, error);
+    if (one_chunk)
+      return bf16_out ? launch_w8_stream_typed<2, 1, __nv_bfloat16>(p, dev, stream, error) : launch_w8_stream_typed<2, 1, float>(p, dev, stream, error);
+    return bf16_out ? launch_w8_stream_typed<2, 2, __nv_bfloat16>(p, dev, stream, error) : launch_w8_stream_typed<2, 2, float>(p, dev, stream, error);
+  }
   if ((p.m + 31) / 32 > 65535) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "M too large for w8_small_m");
   const bool c_bf16 = p.c_dtype == VECOPS_DTYPE_BF16;
   if (p.m <= 8) {
@@ -491,7 +529,7 @@ int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* err
                                               : launch_tcgen05<false, float>(p, *dev, stream, error);
           break;
         case VECOPS_B200_KERNEL_I8_TCGEN05: rc = launch_tcgen05<true, int32_t>(p, *dev, stream, error); break;
-        case VECOPS_B200_KERNEL_W8_SMALL_M: rc = launch_w8_small(p, stream, error); break;
+        case VECOPS_B200_KERNEL_W8_SMALL_M: rc = launch_w8_small(p, *dev, stream, error); break;
         default: rc = set_error(error, VECOPS_STATUS_INTERNAL_ERROR, "kernel id %u has no launcher", kernel);
       }
     }

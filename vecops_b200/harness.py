@@ -71,3 +71,42 @@ def matmul(a, b_nk, c, scale=None, kernel: int = capi.KERNEL_AUTO, stream=None, 
     if stream is None and a.is_cuda:
         stream = torch.cuda.current_stream(a.device)
     run(matmul_problem(a, b_nk, c, scale, kernel, stream, asynchronous))
+
+
+class PreparedMatmul:
+    """One problem record built once and launched many times (keeps per-launch host cost to a single C call)."""
+
+    def __init__(self, a, b_nk, c, scale=None, kernel: int = capi.KERNEL_AUTO, stream=None, asynchronous: bool = True) -> None:
+        import torch
+        if stream is None and a.is_cuda:
+            stream = torch.cuda.current_stream(a.device)
+        self.tensors = (a, b_nk, c, scale)  # keep the storage alive
+        self.problem = matmul_problem(a, b_nk, c, scale, kernel, stream, asynchronous)
+        self.error = capi.ErrorBuffer()
+        self._run = capi.library().vecops_b200_matmul_run
+        self._problem_ref = byref(self.problem)
+        self._error_ref = byref(self.error.record)
+
+    def launch(self) -> None:
+        rc = self._run(self._problem_ref, self._error_ref)
+        if rc != capi.OK:
+            self.error.raise_for(rc)
+
+
+def capture_graph(launches, stream=None):
+    """Capture a sequence of PreparedMatmul launches into one CUDA graph; returns the torch.cuda.CUDAGraph."""
+    import torch
+    side = stream or torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        prepared = [PreparedMatmul(*p.tensors, kernel=p.problem.kernel, stream=side) for p in launches]
+        for p in prepared:  # warm up outside capture: one-time attribute and tensor-map set-up
+            p.launch()
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for p in prepared:
+                p.launch()
+    torch.cuda.current_stream().wait_stream(side)
+    graph._vecops_keepalive = prepared
+    return graph
