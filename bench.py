@@ -241,7 +241,12 @@ def bridge_invoker():
     lib.vecops_b200_matmul_operator.restype = ctypes.c_uint64
     lib.vecops_operator_bridge_invoke_v1.argtypes = [ctypes.c_uint64, ctypes.POINTER(capi.VecopsCall), ctypes.c_uint32, ctypes.c_void_p,
                                                      ctypes.POINTER(capi.VecopsError)]
+    lib.vecops_b200_operator_workspace.argtypes = [ctypes.c_uint64, ctypes.POINTER(capi.VecopsCall), ctypes.POINTER(ctypes.c_uint64),
+                                                   ctypes.POINTER(capi.VecopsError)]
     handle = lib.vecops_b200_matmul_operator()
+    scratch: dict = {}  # device workspace per call signature, sized by the operator's own query
+
+    import torch
 
     import vecops_b200
 
@@ -272,6 +277,13 @@ def bridge_invoker():
         context.flags = capi.CONTEXT_FLAG_ASYNC
         frame = capi.VecopsCall(ctypes.sizeof(capi.VecopsCall), len(values), array, None, 0, ctypes.pointer(context))
         error = capi.ErrorBuffer()
+        key = (tuple(a.shape), tuple(b.shape), a.dtype, b.dtype, c.dtype, scale is not None)
+        if key not in scratch:
+            need = ctypes.c_uint64(0)
+            error.raise_for(lib.vecops_b200_operator_workspace(handle, byref(frame), byref(need), byref(error.record)))
+            scratch[key] = torch.empty(need.value, dtype=torch.uint8, device=c.device) if need.value else None
+        if scratch[key] is not None:
+            frame.workspace, frame.workspace_size = scratch[key].data_ptr(), scratch[key].numel()
         error.raise_for(lib.vecops_operator_bridge_invoke_v1(handle, byref(frame), 0, None, byref(error.record)))
 
     return call

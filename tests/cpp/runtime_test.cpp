@@ -242,6 +242,19 @@ void test_matmul_operator() {
               "vecops::matmul;TA=i8;TB=i8;TC=i32;$0=0;kernel=i8_tcgen05", "C3 resolves to the tcgen05 int8 kernel");
   require(resolve_key(matmul_call(DType::BFloat16, DType::Int8, DType::BFloat16, 16, 14336, 4096, true)) ==
               "vecops::matmul;TA=bf16;TB=i8;TC=bf16;$0=1;kernel=w8_small_m", "C4 resolves to the weight-only kernel");
+  require(resolve_key(matmul_call(DType::BFloat16, DType::Int8, DType::BFloat16, 128, 14336, 4096, true)) ==
+              "vecops::matmul;TA=bf16;TB=i8;TC=bf16;$0=1;kernel=w8_tcgen05", "C4 at M=128 resolves to the tensor-memory weight-only kernel");
+  {
+    // that kernel is the one that needs device scratch: the executable reports it, and refuses to run without it
+    auto call = matmul_call(DType::BFloat16, DType::Int8, DType::BFloat16, 128, 14336, 4096, true);
+    auto exe = op->resolve(call);
+    auto bound = bind_kernel_call(matmul_kernel_def(), call);
+    require(exe.ok() && bound.ok(), "w8_tcgen05 call binds");
+    auto bytes = exe.value()->workspace_size(bound.value().arguments);
+    require(bytes.ok() && bytes.value() > (10u << 20), "WorkspacePlanning sizes the device scratch");
+    auto refused = exe.value()->invoke(bound.value().arguments, nullptr, 0);
+    require(!refused.ok() && refused.code() == StatusCode::InvalidArgument, "invoke without the scratch is refused before run");
+  }
   require(resolve_key(matmul_call(DType::Float32, DType::Float32, DType::Float32, 1024, 1024, 1024)) ==
               "vecops::matmul;TA=f32;TB=f32;TC=f32;$0=0;kernel=f32_simt", "C1 resolves to the FP32 kernel");
   require(resolve_key(matmul_call(DType::BFloat16, DType::BFloat16, DType::Float32, 16, 16, 35)) ==

@@ -60,6 +60,7 @@ def test_dispatch_rules_pick_the_tensor_core_kernels_for_the_benchmark_shapes(li
     assert _name(vecops_b200.select_kernel(_problem(4096, 256, 512, torch.uint8, torch.int8, torch.int32))) == "i8_tcgen05"
     for m in (1, 16):
         assert _name(vecops_b200.select_kernel(_problem(m, 14336, 4096, torch.bfloat16, torch.int8, torch.bfloat16))) == "w8_small_m"
+    assert _name(vecops_b200.select_kernel(_problem(128, 14336, 4096, torch.bfloat16, torch.int8, torch.bfloat16))) == "w8_tcgen05"
     assert _name(vecops_b200.select_kernel(_problem(1024, 1024, 1024, torch.float32, torch.float32, torch.float32))) == "f32_simt"
 
 
@@ -109,6 +110,10 @@ def test_error_text_is_truncated_to_the_callers_buffer(library):
 def test_workspace_query_is_pure_host_logic(library):
     p = _problem(16, 14336, 4096, torch.bfloat16, torch.int8, torch.bfloat16)
     assert harness.workspace_bytes(p) == 0
+    # the stream-K weight-only kernel exchanges partial sums through device scratch:
+    # 160 CTA slots of [128 x 128] fp32 + flags + inverse row scales + an fp16 copy of the activations
+    p = _problem(128, 14336, 4096, torch.bfloat16, torch.int8, torch.bfloat16)
+    assert harness.workspace_bytes(p) == 160 * 128 * 128 * 4 + 160 * 4 * 8 + 128 * 4 + 2 * 128 * 4096
 
 
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU failure mode")

@@ -142,6 +142,32 @@ def test_w8_small_m_ragged_n_no_scale_f32_out(port):
     check("w8", run_case("w8", a, w, s, True, K.KERNEL_W8_SMALL_M, ldc_pad=5), port.matmul_w8(a, w, s, True))
 
 
+@pytest.mark.parametrize("m", [1, 16, 17, 32, 48, 100, 128])
+@pytest.mark.parametrize("n,k", [(128, 128), (256, 512), (300, 208), (1024, 1024), (2048, 384)])
+def test_w8_tcgen05(port, m, n, k):
+    # weights widened into tensor memory; stream-K partial sums through device scratch
+    rng = np.random.default_rng(1000 * m + n + k)
+    a, w, s = inputs("w8", m, n, k, rng)
+    check("w8", run_case("w8", a, w, s, kernel=K.KERNEL_W8_TCGEN05), port.matmul_w8(a, w, s), f"m={m} n={n} k={k}")
+
+
+def test_w8_tcgen05_f32_out_no_scale_padded_c(port):
+    rng = np.random.default_rng(77)
+    a, w, s = inputs("w8", 40, 640, 768, rng)
+    check("w8", run_case("w8", a, w, None, False, K.KERNEL_W8_TCGEN05, ldc_pad=7), port.matmul_w8(a, w, None, False))
+
+
+def test_w8_tcgen05_refuses_a_missing_workspace():
+    a = torch.zeros((32, 256), dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros((256, 256), dtype=torch.int8, device="cuda")
+    c = torch.zeros((32, 256), dtype=torch.bfloat16, device="cuda")
+    problem = vecops_b200.matmul_problem(a, w, c, kernel=K.KERNEL_W8_TCGEN05)
+    assert harness.workspace_bytes(problem) > 0
+    with pytest.raises(capi.VecopsB200Error) as info:
+        harness.run(problem)
+    assert info.value.code == capi.INVALID_ARGUMENT and "workspace" in info.value.message
+
+
 @pytest.mark.parametrize("m,n,k", [(64, 64, 64), (200, 300, 100), (130, 70, 45), (1, 1000, 333), (1024, 1024, 1024)])
 @pytest.mark.parametrize("b_kn", [True, False])
 def test_f32_simt(port, m, n, k, b_kn):
@@ -256,6 +282,32 @@ def test_operator_bridge_invokes_the_selected_kernel(port, kind, m, n, k):
     assert lib.vecops_b200_launch_count() == before + 1
     got = bf16_result_to_numpy(c) if out_dtype == torch.bfloat16 else c.cpu().numpy()
     check(kind, got, oracle(kind, port, a, b, s))
+
+
+def test_operator_bridge_sizes_and_uses_device_scratch(port):
+    # M = 40 weight-only: resolves to the stream-K kernel, whose descriptor reports the scratch it needs
+    lib, handle = bridge_lib()
+    lib.vecops_b200_operator_workspace.argtypes = [ctypes.c_uint64, ctypes.POINTER(capi.VecopsCall), ctypes.POINTER(ctypes.c_uint64),
+                                                   ctypes.POINTER(capi.VecopsError)]
+    rng = np.random.default_rng(40)
+    a, w, s = inputs("w8", 40, 512, 1024, rng)
+    da, dw, ds = to_device(a, True), to_device(w), to_device(s)
+    c = torch.zeros((40, 512), dtype=torch.bfloat16, device="cuda")
+    call, keep = bridge_call(da, dw, c, ds)
+    error = capi.ErrorBuffer()
+    key = ctypes.create_string_buffer(256)
+    error.raise_for(lib.vecops_b200_operator_resolve(handle, byref(call), key, 256, byref(error.record)))
+    assert key.value.decode().endswith("kernel=w8_tcgen05")
+    need = ctypes.c_uint64(0)
+    error.raise_for(lib.vecops_b200_operator_workspace(handle, byref(call), byref(need), byref(error.record)))
+    assert need.value > 0
+    assert lib.vecops_operator_bridge_invoke_v1(handle, byref(call), 0, None, byref(error.record)) == capi.INVALID_ARGUMENT
+    scratch = torch.empty(need.value, dtype=torch.uint8, device="cuda")
+    call.workspace, call.workspace_size = scratch.data_ptr(), need.value
+    for _ in range(2):  # the scratch is reusable as is: flags carry a per-launch nonce
+        c.zero_()
+        error.raise_for(lib.vecops_operator_bridge_invoke_v1(handle, byref(call), 0, None, byref(error.record)))
+        check("w8", bf16_result_to_numpy(c), port.matmul_w8(a, w, s))
 
 
 def test_operator_bridge_async_on_a_side_stream(port):

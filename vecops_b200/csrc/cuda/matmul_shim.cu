@@ -22,6 +22,7 @@
 #include "simt_kernels.cuh"
 #include "w8_small_m.cuh"
 #include "w8_stream.cuh"
+#include "w8_tcgen05.cuh"
 #include "shim_util.h"
 
 namespace vb200 {
@@ -56,6 +57,7 @@ struct DeviceState {
 std::mutex g_mutex;
 DeviceState g_devices[64];
 uint32_t* g_status_host = nullptr;  // pinned, mapped; kernels write here only when a wait ran out
+unsigned long long* g_trace = nullptr;  // optional device buffer for kernel timelines (tuning aid), see vecops_b200_debug_set_trace
 PFN_cuTensorMapEncodeTiled_v12000 g_encode_tiled = nullptr;
 
 int32_t cuda_fail(VecopsError* error, cudaError_t status, const char* what) {
@@ -167,7 +169,9 @@ bool applicable(const VecopsB200Matmul& p, Row row, uint32_t kernel) {
              aligned16(p.b) && p.a_stride_m % 8 == 0 && p.b_stride_n % 16 == 0 && p.n < (INT64_C(1) << 31) &&
              p.m < (INT64_C(1) << 31) && p.k < (INT64_C(1) << 31);
     case VECOPS_B200_KERNEL_W8_TCGEN05:
-      return false;  // reserved: selected nowhere until the kernel exists
+      return row == Row::W8 && p.m >= 1 && p.m <= W8Tc::kMaxM && p.a_stride_k == 1 && p.b_stride_k == 1 && p.c_stride_n == 1 &&
+             p.k > 0 && p.k % 8 == 0 && aligned16(p.a) && aligned16(p.b) && p.a_stride_m % 8 == 0 && p.b_stride_n % 16 == 0 &&
+             p.a_stride_m >= p.k && p.b_stride_n >= p.k && p.n < (INT64_C(1) << 31) && p.k < (INT64_C(1) << 31);
     default:
       return false;
   }
@@ -225,7 +229,9 @@ int32_t select_kernel(const VecopsB200Matmul& p, Row row, uint32_t* kernel, Veco
       if (!tiny && p.k <= 32767 && applicable(p, row, VECOPS_B200_KERNEL_I8_TCGEN05)) pick = VECOPS_B200_KERNEL_I8_TCGEN05;
       break;
     case Row::W8:
-      if (p.m > 0 && p.n >= 16 && applicable(p, row, VECOPS_B200_KERNEL_W8_SMALL_M)) pick = VECOPS_B200_KERNEL_W8_SMALL_M;
+      // few activation rows: the streaming CUDA-core form; up to 128 rows: weights widened into tensor memory
+      if (p.m > 16 && p.n >= 128 && applicable(p, row, VECOPS_B200_KERNEL_W8_TCGEN05)) pick = VECOPS_B200_KERNEL_W8_TCGEN05;
+      else if (p.m > 0 && p.n >= 16 && applicable(p, row, VECOPS_B200_KERNEL_W8_SMALL_M)) pick = VECOPS_B200_KERNEL_W8_SMALL_M;
       break;
     default:
       break;
@@ -448,6 +454,61 @@ int32_t launch_w8_small(const VecopsB200Matmul& p, const DeviceState& dev, cudaS
   return VECOPS_STATUS_OK;
 }
 
+uint64_t fresh_nonce(const void* salt) {
+  static std::atomic<uint64_t> counter{0x243F6A8885A308D3ull};
+  uint64_t z = counter.fetch_add(0x9E3779B97F4A7C15ull) ^ reinterpret_cast<uintptr_t>(salt);
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z ^= z >> 31;
+  return z == 0 ? 1 : z;
+}
+
+template <typename OutT>
+int32_t launch_w8_tcgen05_typed(const VecopsB200Matmul& p, const DeviceState& dev, cudaStream_t stream, VecopsError* error) {
+  using G = W8Tc;
+  if (dev.prop.major != 10)
+    return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "tcgen05 kernels need an sm_100 device, found sm_%d%d", dev.prop.major,
+                     dev.prop.minor);
+  const int mpad = G::m_padded(static_cast<int>(p.m));
+  const uint64_t need = G::scratch_bytes(static_cast<int>(p.m), p.k);
+  if (p.workspace == nullptr || p.workspace_size < need)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "w8_tcgen05 needs %llu bytes of device workspace, %llu were supplied",
+                     (unsigned long long)need, (unsigned long long)p.workspace_size);
+  if (!aligned16(p.workspace)) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "workspace must be 16-byte aligned");
+  CUtensorMap map_w, map_a;
+  int32_t rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.b, p.k, p.n, p.b_stride_n, G::kBlockK, G::kTileN, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  char* scratch = static_cast<char*>(p.workspace);
+  float* partials = reinterpret_cast<float*>(scratch);
+  auto* flags = reinterpret_cast<unsigned long long*>(scratch + G::flags_offset(mpad));
+  float* inv_scales = reinterpret_cast<float*>(scratch + G::scales_offset(mpad));
+  __half* act16 = reinterpret_cast<__half*>(scratch + G::act_offset(mpad));
+  const long long act_pitch = G::act_pitch(p.k);
+  rc = make_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act16, p.k, p.m, act_pitch * 2, 64, mpad, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  const char* skip = getenv("VECOPS_B200_W8TC_SKIP_PREPARE");  // timing experiments only: reuse the scratch's previous copy
+  if (skip == nullptr || skip[0] != '1') {
+    w8_prepare_activations_kernel<<<static_cast<int>(p.m), W8Prepare::kThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(p.a), p.a_stride_m, act16, act_pitch, inv_scales, static_cast<int>(p.k));
+    g_launches.fetch_add(1);
+  }
+  const char* flavour = getenv("VECOPS_B200_W8TC_PREFETCH");
+  auto kernel = (flavour != nullptr && flavour[0] == '0') ? w8_tcgen05_kernel<OutT, false> : w8_tcgen05_kernel<OutT, true>;
+  static_assert(G::smem_bytes(G::kMaxM) <= 227 * 1024 && G::smem_bytes(16) <= 227 * 1024, "w8_tcgen05 shared memory budget");
+  rc = raise_smem_limit(kernel, 227 * 1024, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  const long long units = ((p.n + G::kTileN - 1) / G::kTileN) * ((p.k + G::kBlockK - 1) / G::kBlockK);
+  long long grid = dev.prop.multiProcessorCount < G::kMaxGrid ? dev.prop.multiProcessorCount : G::kMaxGrid;
+  if (units < grid) grid = units;
+  // A = f16 (the widened weights, from tensor memory), B = f16 (the scaled activations), fp32 accumulate
+  const uint32_t idesc = umma_instr_desc(kUmmaAccF32, kUmmaF16, kUmmaF16, G::kTileN, mpad);
+  kernel<<<static_cast<int>(grid), G::kThreads, G::smem_bytes(mpad), stream>>>(
+      map_w, map_a, p.column_scale, static_cast<OutT*>(p.c), p.c_stride_m, static_cast<int>(p.m), static_cast<int>(p.n),
+      static_cast<int>(p.k), mpad, partials, flags, inv_scales, fresh_nonce(p.workspace), idesc, g_status_host, g_trace);
+  g_launches.fetch_add(1);
+  return VECOPS_STATUS_OK;
+}
+
 int32_t launch_f32(const VecopsB200Matmul& p, cudaStream_t stream, VecopsError* error) {
   if ((p.m + 63) / 64 > 65535) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "M too large for f32_simt");
   dim3 grid(static_cast<unsigned>((p.n + 63) / 64), static_cast<unsigned>((p.m + 63) / 64));
@@ -481,8 +542,9 @@ int32_t vecops_b200_matmul_workspace(const VecopsB200Matmul* problem, uint64_t* 
   uint32_t kernel;
   rc = select_kernel(*problem, row, &kernel, error);
   if (rc != VECOPS_STATUS_OK) return rc;
-  // Split-K of the kernels built so far meets in shared memory; none needs device scratch.
-  *bytes = 0;
+  // Only the stream-K weight-only kernel exchanges partial sums through device scratch; every other
+  // kernel's split-K meets in shared memory.
+  *bytes = kernel == VECOPS_B200_KERNEL_W8_TCGEN05 ? W8Tc::scratch_bytes(static_cast<int>(problem->m), problem->k) : 0;
   return VECOPS_STATUS_OK;
 }
 
@@ -530,6 +592,10 @@ int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* err
           break;
         case VECOPS_B200_KERNEL_I8_TCGEN05: rc = launch_tcgen05<true, int32_t>(p, *dev, stream, error); break;
         case VECOPS_B200_KERNEL_W8_SMALL_M: rc = launch_w8_small(p, *dev, stream, error); break;
+        case VECOPS_B200_KERNEL_W8_TCGEN05:
+          rc = p.c_dtype == VECOPS_DTYPE_BF16 ? launch_w8_tcgen05_typed<__nv_bfloat16>(p, *dev, stream, error)
+                                              : launch_w8_tcgen05_typed<float>(p, *dev, stream, error);
+          break;
         default: rc = set_error(error, VECOPS_STATUS_INTERNAL_ERROR, "kernel id %u has no launcher", kernel);
       }
     }
@@ -585,6 +651,12 @@ int32_t vecops_b200_device_info(int32_t device_index, VecopsB200DeviceInfo* info
 }
 
 uint64_t vecops_b200_launch_count(void) { return g_launches.load(); }
+
+// Tuning aid, deliberately not part of the public headers: kernels that support it write a timeline
+// (16 x 64-bit nanosecond stamps per CTA) into this device buffer; NULL switches it off.
+__attribute__((visibility("default"))) void vecops_b200_debug_set_trace(void* device_buffer) {
+  g_trace = static_cast<unsigned long long*>(device_buffer);
+}
 
 int32_t vecops_b200_take_device_status(int32_t device_index, uint32_t* status, VecopsError* error) {
   (void)device_index;

@@ -319,8 +319,6 @@ Result<std::shared_ptr<Executable>> CudaExecutableProvider::resolve(const BoundK
   const VariantDescriptor* variant = variant_descriptor(kernel);
   if (kernel == VECOPS_B200_KERNEL_AUTO || variant == nullptr)
     return Status(StatusCode::NotFound, "no prebuilt kernel image named '" + std::string(name) + "'");
-  if (kernel == VECOPS_B200_KERNEL_W8_TCGEN05)
-    return Status(StatusCode::NotFound, "kernel image 'w8_tcgen05' is not part of this build");
   auto owned = std::make_shared<OwnedDescriptor>();
   owned->key = recipe.specialization_key;
   owned->descriptor = variant->descriptor;

@@ -60,6 +60,19 @@ def workspace_bytes(problem: capi.VecopsB200Matmul) -> int:
     return out.value
 
 
+def attach_workspace(problem: capi.VecopsB200Matmul, device):
+    """Allocate the device scratch the chosen kernel asks for (torch owns the memory) and point the problem at it.
+
+    Returns the buffer (keep it alive until the launch has finished) or None when no scratch is needed."""
+    import torch
+    need = workspace_bytes(problem)
+    if need == 0:
+        return None
+    buffer = torch.empty(need, dtype=torch.uint8, device=device)
+    problem.workspace, problem.workspace_size = buffer.data_ptr(), need
+    return buffer
+
+
 def run(problem: capi.VecopsB200Matmul) -> None:
     error = capi.ErrorBuffer()
     error.raise_for(capi.library().vecops_b200_matmul_run(byref(problem), byref(error.record)))
@@ -70,7 +83,11 @@ def matmul(a, b_nk, c, scale=None, kernel: int = capi.KERNEL_AUTO, stream=None, 
     import torch
     if stream is None and a.is_cuda:
         stream = torch.cuda.current_stream(a.device)
-    run(matmul_problem(a, b_nk, c, scale, kernel, stream, asynchronous))
+    problem = matmul_problem(a, b_nk, c, scale, kernel, stream, asynchronous)
+    # freed after the call: torch's allocator re-issues the block only to later work on the same stream
+    scratch = attach_workspace(problem, a.device) if a.is_cuda else None
+    run(problem)
+    del scratch
 
 
 class PreparedMatmul:
@@ -82,6 +99,7 @@ class PreparedMatmul:
             stream = torch.cuda.current_stream(a.device)
         self.tensors = (a, b_nk, c, scale)  # keep the storage alive
         self.problem = matmul_problem(a, b_nk, c, scale, kernel, stream, asynchronous)
+        self.scratch = attach_workspace(self.problem, a.device) if a.is_cuda else None  # one buffer per prepared launch
         self.error = capi.ErrorBuffer()
         self._run = capi.library().vecops_b200_matmul_run
         self._problem_ref = byref(self.problem)
