@@ -64,6 +64,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
+// Non-blocking probe of phase `parity` (try_wait may suspend the thread for a while before giving up;
+// a loop that watches several barriers must not).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
 // Cycle budget of one wait (about a second at B200 clocks).  A healthy wait
 // lasts microseconds; the budget only matters when a pipeline is wedged.
 constexpr long long kWaitCycleBudget = 2000000000LL;

@@ -429,7 +429,7 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
       mark(1);
       while (raw_issued < my_units || act_issued < my_units) {
         bool progress = false;
-        if (raw_issued < my_units && mbar_try_wait(raw_empty + 8 * rs, rphase ^ 1u)) {
+        if (raw_issued < my_units && mbar_test_wait(raw_empty + 8 * rs, rphase ^ 1u)) {
           // a whole batch of consecutive k-blocks at once
           for (int b = 0; b < G::kRawBatch && raw_issued < my_units; ++b, ++raw_issued) {
             const long long u = begin + raw_issued;
@@ -441,7 +441,7 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
           if (rs == G::kRawStages) { rs = 0; rphase ^= 1u; }
           progress = true;
         }
-        if (act_issued < my_units && mbar_try_wait(act_empty + 8 * as, aphase ^ 1u)) {
+        if (act_issued < my_units && mbar_test_wait(act_empty + 8 * as, aphase ^ 1u)) {
           const int kb = static_cast<int>((begin + act_issued) % kblocks);
           mbar_arrive_expect_tx(act_full + 8 * as, static_cast<uint32_t>(act_stage));
           const uint32_t act_dst = act_base + as * act_stage;
