@@ -93,6 +93,29 @@ VECOPS_B200_EXPORT int32_t vecops_b200_matmul_workspace(const VecopsB200Matmul* 
  * legal: K == 0 stores zeros (ops/Matmul.h:41-43). */
 VECOPS_B200_EXPORT int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* error);
 
+/* The weight-only int8 tensor-core kernel (VECOPS_B200_KERNEL_W8_TCGEN05) with its scratch inside the
+ * library instead of in a caller workspace.  It has no counterpart in the reference: it exists for callers
+ * of this library that cannot allocate device memory at call time - a serving loop whose memory pool is
+ * sealed after start-up, an embedding whose allocator must not be re-entered from an operator, a latency
+ * budget that cannot take cudaMalloc's implicit synchronisation.  `workspace` is ignored.
+ *
+ *   - The scratch is a fixed array of VECOPS_B200_STATIC_SCRATCH_BYTES of device memory that every GPU
+ *     loading the library holds until the process exits.
+ *   - Serves bf16 A[M,K] x int8 W[N,K] -> bf16|f32 C, optional column_scale, 1 <= M <= 128, K % 8 == 0,
+ *     K-contiguous 16-byte aligned rows.  A problem whose scratch need (vecops_b200_matmul_workspace with
+ *     kernel = W8_TCGEN05) exceeds the array is refused with INVALID_ARGUMENT; e.g. M = 64, K = 8192 fits,
+ *     M = 128, K = 4096 does not.
+ *   - Every call on a device shares the array and inherits the previous call's contents (nothing needs
+ *     clearing).  Calls that overlap on the GPU - two streams, or asynchronous calls not ordered by one
+ *     stream - race on it: serialise them.
+ *   - The first call on a device also performs the one-time set-up (device address of the array, kernel
+ *     attributes); make that first call before any stream capture begins.
+ *   - Calls no cudaMalloc / cudaFree / cudaHostAlloc or any other allocating routine.
+ * Synchronous unless VECOPS_B200_MATMUL_FLAG_ASYNC is set; bounded-wait failures are reported by
+ * synchronous calls only. */
+#define VECOPS_B200_STATIC_SCRATCH_BYTES (8ull << 20)
+VECOPS_B200_EXPORT int32_t vecops_b200_matmul_w8_static_scratch(const VecopsB200Matmul* problem, VecopsError* error);
+
 /* Stable short name of a variant ("bf16_tcgen05", ...), NULL if out of range. */
 VECOPS_B200_EXPORT const char* vecops_b200_kernel_name(uint32_t kernel);
 

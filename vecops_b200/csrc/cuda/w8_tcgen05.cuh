@@ -136,7 +136,8 @@ struct W8Prepare {
   static constexpr int kMaxVectors = 4;  // 16-byte loads per thread: rows up to 512 * 4 * 8 = 16384 elements in one pass
 };
 
-__global__ void __launch_bounds__(W8Prepare::kThreads)
+// (static: this header is included by more than one translation unit)
+static __global__ void __launch_bounds__(W8Prepare::kThreads)
 w8_prepare_activations_kernel(const __nv_bfloat16* __restrict__ a, long long lda, __half* __restrict__ out, long long pitch,
                               float* __restrict__ inv_scale, int K) {
   using P = W8Prepare;
