@@ -372,6 +372,8 @@ def run_ours(args) -> None:
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: this program prints ONE line there
         dist.init_process_group("nccl", device_id=dev)
     lib = capi.library()
     peaks, peak_source = measured_peaks()
@@ -380,26 +382,55 @@ def run_ours(args) -> None:
     name = args.workload or ("c2_bf16_4096" if world == 1 else "c5_bf16_16384x53248x8192")
     w = workloads.WORKLOADS[name]
     sharded = world > 1 or name.startswith("c5")
-    steps = args.steps if args.steps is not None else (3 if sharded else 200)
+    steps = args.steps if args.steps is not None else (20 if sharded else 200)
     warmup = args.warmup if args.warmup is not None else (3 if sharded else 10)
     stream = torch.cuda.current_stream(dev)
 
+    gather_mode = "none"
     if sharded:
         n0, n1 = sharding.column_partition(w.n, world, rank)
         operands, host_inputs = device_sets(w, 1, dev, n0, n1)
         o = operands[0]
-        full = torch.empty((w.m, w.n), dtype=torch.bfloat16, device=dev)
-        staging = torch.empty((world, w.m, n1 - n0), dtype=torch.bfloat16, device=dev)
-        place = sharding.cuda_place(stream)
+        prepared = [harness.PreparedMatmul(o["a"], o["b"], o["c"], None, stream=stream)]  # the slab GEMM alone (roofline, e2e)
+        full = None
+        if world == 1:
+            step_launch = prepared[0].launch  # one GPU owns every column: the slab is the result
+            launches_per_step = 1
+        else:
+            fused = None
+            if args.gather == "fused":
+                try:  # epilogue TMA-stores each finished piece into every rank's result over NVLink (peer pointers)
+                    full, handle = sharding.symmetric_result(w.m, w.n, torch.bfloat16, dev)
+                    fused = sharding.FusedGatherGemm(o["a"], o["b"], [int(p) for p in handle.buffer_ptrs], w.n, w.n, n0, torch.bfloat16, stream)
+                    fused.launch()
+                    handle.barrier(channel=0)
+                    torch.cuda.synchronize()
+                    gather_mode = "fused: epilogue TMA stores to every rank's result over NVLink peer pointers + one device barrier"
+                except Exception as error:  # symmetric memory unavailable: fall back to the library collective
+                    print(f"[bench] fused gather unavailable on rank {rank}: {error!r}", file=sys.stderr)
+                    fused = None
+            ok = torch.tensor([1 if fused is not None else 0], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 1:
+                def step_launch():
+                    fused.launch()
+                    handle.barrier(channel=0)
+                launches_per_step = 1
+            else:
+                gather_mode = "nccl: all_gather_into_tensor of the slabs + placement kernel per slab"
+                full = torch.empty((w.m, w.n), dtype=torch.bfloat16, device=dev)
+                staging = torch.empty((world, w.m, n1 - n0), dtype=torch.bfloat16, device=dev)
+                place = sharding.cuda_place(stream)
 
-        prepared = [harness.PreparedMatmul(o["a"], o["b"], o["c"], None, stream=stream)]
+                def step_launch():
+                    prepared[0].launch()
+                    sharding.gather_columns(o["c"], full, staging, world, place=place)
+                launches_per_step = 1 + world
 
         def step(_):
-            prepared[0].launch()
-            sharding.gather_columns(o["c"], full, staging, world, place=place)
+            step_launch()
 
         sets_note = f"operands {w.algorithmic_bytes / 1e9:.2f} GB > L2 126 MB"
-        launches_per_step = 1 + world
     else:
         per_set = w.algorithmic_bytes
         sets = 1 if per_set > 1.5 * 126e6 else int(np.ceil(1.6 * 126e6 / per_set)) + 1
@@ -416,7 +447,8 @@ def run_ours(args) -> None:
 
     step(0)
     torch.cuda.synchronize()
-    parity = parity_sample(w, host_inputs, o["c"], port, rows=8 if sharded else 16)
+    result_view = full[:, n0:n1] if (sharded and full is not None) else o["c"]
+    parity = parity_sample(w, host_inputs, result_view, port, rows=8 if sharded else 16)
 
     for i in range(warmup):
         step(i)
@@ -467,7 +499,7 @@ def run_ours(args) -> None:
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if sharded else "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded; shapes, layouts and value distributions of the named configuration)",
         "config": {"workload": name, "description": w.description, "m": w.m, "n": w.n, "k": w.k,
-                   "parallelism": f"N-sharded x{world}, NCCL all-gather of C slabs" if sharded else "single GPU",
+                   "parallelism": f"N-sharded x{world}" if sharded else "single GPU", "gather": gather_mode,
                    "l2": sets_note, "timing": "CUDA events on the launch stream, max over ranks"},
         "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": f"{peak_source}: cuBLAS bf16 " + ("sustained" if sharded else "burst"),
@@ -556,6 +588,7 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=None)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--workload", default=None, help="override the workload (a name from vecops_b200.workloads.WORKLOADS)")
+    parser.add_argument("--gather", choices=["fused", "nccl"], default="fused", help="how the sharded GEMM's output is gathered")
     parser.add_argument("--no-extra", action="store_true", help="skip the brief measurements of the other single-GPU configurations")
     args = parser.parse_args()
     if args.warmup is not None and args.warmup < 3 and args.impl == "ours":

@@ -147,6 +147,27 @@ VECOPS_B200_EXPORT uint64_t vecops_b200_launch_count(void);
 VECOPS_B200_EXPORT int32_t vecops_b200_take_device_status(int32_t device_index, uint32_t* status,
                                                           VecopsError* error);
 
+/* Column-sharded GEMM with the all-gather of the output fused into the kernel.
+ *
+ * vecops has no multi-device layer; this is the device form of the N-partition its CPU callers use across
+ * threads (one matmul per lane on a sub-view, docs/WorkspacePlanning.md:96-110).  `problem` describes this
+ * rank's slab: A[M,K] (replicated), B[n,K] (this rank's rows of B), bf16 in, bf16 or f32 out; problem->c is
+ * ignored.  Each finished 32 x 128-byte piece of the slab is TMA-stored from shared memory straight into
+ * columns [col0, col0 + n) of EVERY destination in `c` - the full [M, n_total] result of each GPU, own
+ * included, reached through peer pointers (CUDA IPC / symmetric memory) - while the main loop continues.
+ * Only stores cross GPUs.  The caller orders ranks afterwards (a barrier on the stream) before anyone reads. */
+typedef struct VecopsB200Gather {
+  uint32_t struct_size;
+  int32_t world;       /* number of destinations, 1..8 */
+  void* const* c;      /* `world` device pointers: the full C of every rank */
+  int64_t n_total;     /* columns of the full C */
+  int64_t ldc;         /* row pitch of the full C, elements */
+  int64_t col0;        /* first column of this rank's slab */
+} VecopsB200Gather;
+
+VECOPS_B200_EXPORT int32_t vecops_b200_matmul_allgather_run(const VecopsB200Matmul* problem, const VecopsB200Gather* gather,
+                                                            VecopsError* error);
+
 /* Strided gather of column slabs: dst[M, ldd] columns [col0, col0+cols) <-
  * src[M, cols] (row pitch lds), `elem_size` bytes per element.  Used after the
  * all-gather of a column-sharded GEMM to place peers' slabs into the row-major

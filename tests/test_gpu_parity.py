@@ -186,6 +186,27 @@ def test_strided_kernel_on_reference_test_shapes(port, kind):
         check(kind, got, oracle(kind, port, a, b, s))
 
 
+def test_fused_allgather_epilogue_stores_the_slab_into_every_destination(port):
+    # Two destinations on ONE GPU stand in for two ranks' result matrices: the epilogue must place this
+    # rank's [M, n] slab at columns [col0, col0 + n) of both, and touch nothing else.
+    from vecops_b200 import sharding
+    rng = np.random.default_rng(88)
+    m, n, k, n_total, col0 = 384, 512, 256, 1536, 768
+    a, b, _ = inputs("bf16", m, n, k, rng)
+    da, db = to_device(a, True), to_device(b, True)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        full = [torch.full((m, n_total), -3.0, dtype=out_dtype, device="cuda") for _ in range(2)]
+        gemm = sharding.FusedGatherGemm(da, db, [t.data_ptr() for t in full], n_total, n_total, col0, out_dtype)
+        gemm.launch()
+        torch.cuda.synchronize()
+        want = port.matmul_bf16(a, b, None, out_dtype == torch.bfloat16)
+        for t in full:
+            slab = t[:, col0:col0 + n]
+            got = bf16_result_to_numpy(slab) if out_dtype == torch.bfloat16 else slab.contiguous().cpu().numpy()
+            check("bf16", got, want)
+            assert bool((t[:, :col0] == -3).all()) and bool((t[:, col0 + n:] == -3).all())
+
+
 def test_int32_accumulators_wrap_like_the_reference(port):
     # K = 262145 of 127*127 (and 255*255) overflows int32 and must wrap (tests/ops/MatmulTest.cpp:1025-1055)
     k = 262145

@@ -77,6 +77,11 @@ class VecopsB200Matmul(Structure):
                 ("flags", c_uint32), ("reserved", c_uint32)]
 
 
+class VecopsB200Gather(Structure):
+    _fields_ = [("struct_size", c_uint32), ("world", c_int32), ("c", POINTER(c_void_p)), ("n_total", c_int64), ("ldc", c_int64),
+                ("col0", c_int64)]
+
+
 class VecopsB200DeviceInfo(Structure):
     _fields_ = [("struct_size", c_uint32), ("sm_major", c_int32), ("sm_minor", c_int32), ("sm_count", c_int32),
                 ("l2_bytes", c_uint64), ("hbm_bytes", c_uint64), ("smem_per_block_optin", c_uint64), ("name", c_char * 64)]
@@ -116,6 +121,7 @@ def library() -> ctypes.CDLL:
         lib.vecops_b200_matmul_select.argtypes = [POINTER(VecopsB200Matmul), POINTER(c_uint32), e]
         lib.vecops_b200_matmul_workspace.argtypes = [POINTER(VecopsB200Matmul), POINTER(c_uint64), e]
         lib.vecops_b200_matmul_run.argtypes = [POINTER(VecopsB200Matmul), e]
+        lib.vecops_b200_matmul_allgather_run.argtypes = [POINTER(VecopsB200Matmul), POINTER(VecopsB200Gather), e]
         lib.vecops_b200_kernel_name.argtypes = [c_uint32]
         lib.vecops_b200_kernel_name.restype = c_char_p
         lib.vecops_b200_device_count.restype = c_int32

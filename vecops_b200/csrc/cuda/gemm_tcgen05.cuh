@@ -14,6 +14,12 @@
 // accumulate) share this file; the operand formats arrive in the instruction
 // descriptor.
 //
+// Fused all-gather: the TMA-store epilogue can send every finished slab to up to
+// eight destinations - the C matrices of all GPUs of a column-sharded GEMM, reached
+// through peer pointers over NVLink - at a column offset, so the gather of the
+// output overlaps the main loop tile by tile and needs no staging pass.  (Only
+// stores cross GPUs; every load, and anything with cluster multicast, stays local.)
+//
 // Algorithmic traffic per launch: (M*K + N*K) * sizeof(in) + M*N * sizeof(out).
 #pragma once
 
@@ -37,6 +43,12 @@ struct GemmTc {
   static constexpr int kThreads = 32 * (2 + kEpiWarps);
   static constexpr int kTmemColumns = 512;
   static constexpr int kGroupM = 16;  // raster: 16 row-tiles share each sweep over N
+};
+
+// Destinations of the TMA-store epilogue: map[0] is the local C, the rest are peers' C matrices.
+struct GemmStoreMaps {
+  static constexpr int kMax = 8;
+  CUtensorMap map[kMax];
 };
 
 // Device status codes ORed into the status word by a wait that ran out.
@@ -74,9 +86,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 template <bool kInt8, typename OutT>
 __global__ void __launch_bounds__(GemmTc::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                    const __grid_constant__ CUtensorMap tma_c, OutT* __restrict__ c, long long ldc, int M, int N,
-                    int K, const float* __restrict__ column_scale, uint32_t idesc, int use_tma_store,
-                    uint32_t* __restrict__ status) {
+                    const __grid_constant__ GemmStoreMaps tma_c, int num_dest, int c_col_offset, OutT* __restrict__ c,
+                    long long ldc, int M, int N, int K, const float* __restrict__ column_scale, uint32_t idesc,
+                    int use_tma_store, uint32_t* __restrict__ status) {
   using G = GemmTc;
   constexpr int kElemBytes = kInt8 ? 1 : 2;
   constexpr int kBlockK = G::kBlockKBytes / kElemBytes;  // elements per k-block
@@ -117,7 +129,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     mbar_fence_init();
     tma_prefetch_descriptor(&tma_a);
     tma_prefetch_descriptor(&tma_b);
-    if (use_tma_store) tma_prefetch_descriptor(&tma_c);
+    if (use_tma_store) tma_prefetch_descriptor(&tma_c.map[0]);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), G::kTmemColumns);
@@ -274,7 +286,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&tma_c, buf, col0, row0);
+            // one bulk group per slab, however many destinations read the staging buffer
+            for (int d = 0; d < num_dest; ++d) tma_store_2d(&tma_c.map[d], buf, c_col_offset + col0, row0);
             tma_store_commit();
           }
           buf_sel ^= 1;

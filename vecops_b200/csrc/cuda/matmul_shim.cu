@@ -305,29 +305,57 @@ int32_t raise_smem_limit(Kernel kernel, int bytes, VecopsError* error) {
   return VECOPS_STATUS_OK;
 }
 
+// Where the epilogue's TMA stores go when the output is gathered across GPUs.
+struct GatherTargets {
+  int count = 0;                 // 0 = plain GEMM into p.c
+  void* const* c = nullptr;      // `count` device pointers: each GPU's full C (own included)
+  int64_t n_total = 0;           // columns of the full C
+  int64_t ldc = 0;               // row pitch of the full C, elements
+  int64_t col0 = 0;              // first column of this rank's slab
+};
+
 template <bool kInt8, typename OutT>
-int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaStream_t stream, VecopsError* error) {
+int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaStream_t stream, VecopsError* error,
+                       const GatherTargets& gather = GatherTargets()) {
   using G = GemmTc;
   if (dev.prop.major != 10)
     return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "tcgen05 kernels need an sm_100 device, found sm_%d%d", dev.prop.major,
                      dev.prop.minor);
   constexpr size_t elem = kInt8 ? 1 : 2;
   const CUtensorMapDataType in_type = kInt8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const CUtensorMapDataType out_type = std::is_same<OutT, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                       : std::is_same<OutT, float>::value       ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                                                : CU_TENSOR_MAP_DATA_TYPE_INT32;
   const uint32_t box_k = G::kBlockKBytes / elem;
-  CUtensorMap map_a, map_b, map_c;
+  CUtensorMap map_a, map_b;
+  GemmStoreMaps maps;
   int32_t rc = make_map_2d(&map_a, in_type, elem, p.a, p.k, p.m, p.a_stride_m * elem, box_k, G::kBlockM, error);
   if (rc != VECOPS_STATUS_OK) return rc;
   rc = make_map_2d(&map_b, in_type, elem, p.b, p.k, p.n, p.b_stride_n * elem, box_k, G::kBlockN, error);
   if (rc != VECOPS_STATUS_OK) return rc;
-  const bool tma_store = !direct_epilogue_forced() && aligned16(p.c) && (p.c_stride_m * sizeof(OutT)) % 16 == 0;
-  if (tma_store) {
-    const CUtensorMapDataType out_type = std::is_same<OutT, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                         : std::is_same<OutT, float>::value       ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                                                                  : CU_TENSOR_MAP_DATA_TYPE_INT32;
-    rc = make_map_2d(&map_c, out_type, sizeof(OutT), p.c, p.n, p.m, p.c_stride_m * sizeof(OutT), 128 / sizeof(OutT), 32, error);
-    if (rc != VECOPS_STATUS_OK) return rc;
+  bool tma_store;
+  int num_dest = 1;
+  int col_offset = 0;
+  if (gather.count > 0) {
+    // every destination is a full [M, n_total] matrix; this rank's tiles land at column col0 + ...
+    tma_store = true;
+    num_dest = gather.count;
+    col_offset = static_cast<int>(gather.col0);
+    for (int d = 0; d < gather.count; ++d) {
+      rc = make_map_2d(&maps.map[d], out_type, sizeof(OutT), gather.c[d], gather.n_total, p.m, gather.ldc * sizeof(OutT),
+                       128 / sizeof(OutT), 32, error);
+      if (rc != VECOPS_STATUS_OK) return rc;
+    }
+    for (int d = gather.count; d < GemmStoreMaps::kMax; ++d) maps.map[d] = maps.map[0];
   } else {
-    map_c = map_a;  // never dereferenced
+    tma_store = !direct_epilogue_forced() && aligned16(p.c) && (p.c_stride_m * sizeof(OutT)) % 16 == 0;
+    if (tma_store) {
+      rc = make_map_2d(&maps.map[0], out_type, sizeof(OutT), p.c, p.n, p.m, p.c_stride_m * sizeof(OutT), 128 / sizeof(OutT), 32, error);
+      if (rc != VECOPS_STATUS_OK) return rc;
+    } else {
+      maps.map[0] = map_a;  // never dereferenced
+    }
+    for (int d = 1; d < GemmStoreMaps::kMax; ++d) maps.map[d] = maps.map[0];
   }
   uint32_t idesc;
   if (kInt8) {
@@ -347,7 +375,7 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
   }
   const long long tiles = ((p.m + G::kBlockM - 1) / G::kBlockM) * ((p.n + G::kBlockN - 1) / G::kBlockN);
   const int grid = static_cast<int>(tiles < dev.prop.multiProcessorCount ? tiles : dev.prop.multiProcessorCount);
-  kernel<<<grid, G::kThreads, G::kSmemBytes, stream>>>(map_a, map_b, map_c, static_cast<OutT*>(p.c), p.c_stride_m,
+  kernel<<<grid, G::kThreads, G::kSmemBytes, stream>>>(map_a, map_b, maps, num_dest, col_offset, static_cast<OutT*>(p.c), p.c_stride_m,
                                                        static_cast<int>(p.m), static_cast<int>(p.n), static_cast<int>(p.k),
                                                        kInt8 ? nullptr : p.column_scale, idesc, tma_store ? 1 : 0, g_status_host);
   g_launches.fetch_add(1);
@@ -667,6 +695,66 @@ int32_t vecops_b200_take_device_status(int32_t device_index, uint32_t* status, V
     *reinterpret_cast<volatile uint32_t*>(g_status_host) = 0;
   }
   return VECOPS_STATUS_OK;
+}
+
+int32_t vecops_b200_matmul_allgather_run(const VecopsB200Matmul* problem, const VecopsB200Gather* gather, VecopsError* error) {
+  Row row;
+  int32_t rc = check_problem(problem, &row, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  const VecopsB200Matmul& p = *problem;
+  if (gather == nullptr || gather->struct_size < sizeof(VecopsB200Gather) || gather->world < 1 || gather->world > GemmStoreMaps::kMax ||
+      gather->c == nullptr)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "gather record is null, too small, or names more than %d destinations",
+                     GemmStoreMaps::kMax);
+  if (row != Row::BF16 || !applicable(p, row, VECOPS_B200_KERNEL_BF16_TCGEN05))
+    return set_error(error, VECOPS_STATUS_NOT_APPLICABLE, "the fused all-gather serves the bf16 tcgen05 GEMM (K-contiguous, 16-byte aligned operands)");
+  const size_t out = dtype_size(p.c_dtype);
+  if (gather->col0 < 0 || gather->col0 + p.n > gather->n_total || gather->ldc < gather->n_total || (gather->ldc * out) % 16 != 0 ||
+      (gather->col0 * out) % 16 != 0)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "slab [col0, col0+n) must lie inside the full C and start on a 16-byte boundary");
+  for (int d = 0; d < gather->world; ++d)
+    if (gather->c[d] == nullptr || !aligned16(gather->c[d]))
+      return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "destination %d is null or not 16-byte aligned", d);
+  if (p.m == 0 || p.n == 0) return VECOPS_STATUS_OK;
+  if (p.k == 0) return set_error(error, VECOPS_STATUS_NOT_APPLICABLE, "K == 0 has nothing to gather; zero the result instead");
+
+  int device = 0;
+  rc = current_device(p, &device, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  int previous = -1;
+  cudaGetDevice(&previous);
+  if (previous != device) {
+    cudaError_t status = cudaSetDevice(device);
+    if (status != cudaSuccess) return cuda_fail(error, status, "cudaSetDevice");
+  }
+  const DeviceState* dev = nullptr;
+  rc = device_state(device, &dev, error);
+  cudaStream_t stream = static_cast<cudaStream_t>(p.stream);
+  if (rc == VECOPS_STATUS_OK) {
+    GatherTargets targets;
+    targets.count = gather->world;
+    targets.c = gather->c;
+    targets.n_total = gather->n_total;
+    targets.ldc = gather->ldc;
+    targets.col0 = gather->col0;
+    rc = p.c_dtype == VECOPS_DTYPE_BF16 ? launch_tcgen05<false, __nv_bfloat16>(p, *dev, stream, error, targets)
+                                        : launch_tcgen05<false, float>(p, *dev, stream, error, targets);
+  }
+  if (rc == VECOPS_STATUS_OK) {
+    cudaError_t status = cudaGetLastError();
+    if (status != cudaSuccess) rc = cuda_fail(error, status, "kernel launch");
+  }
+  if (rc == VECOPS_STATUS_OK && (p.flags & VECOPS_B200_MATMUL_FLAG_ASYNC) == 0) {
+    cudaError_t status = cudaStreamSynchronize(stream);
+    if (status != cudaSuccess) rc = cuda_fail(error, status, "cudaStreamSynchronize");
+    else if (g_status_host != nullptr && *reinterpret_cast<volatile uint32_t*>(g_status_host) != 0) {
+      const uint32_t word = *reinterpret_cast<volatile uint32_t*>(g_status_host);
+      *reinterpret_cast<volatile uint32_t*>(g_status_host) = 0;
+      rc = set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "fused all-gather GEMM: a bounded device wait ran out (status 0x%x)", word);
+    }
+  }
+  if (previous >= 0 && previous != device) cudaSetDevice(previous);
+  return rc;
 }
 
 int32_t vecops_b200_place_columns(void* dst, int64_t ldd, int64_t col0, const void* src, int64_t lds, int64_t rows,

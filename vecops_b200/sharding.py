@@ -65,3 +65,55 @@ def cuda_place(stream=None) -> Callable:
         error.raise_for(rc)
 
     return place
+
+
+class FusedGatherGemm:
+    """This rank's slab GEMM with the all-gather fused into its epilogue (vecops_b200_matmul_allgather_run).
+
+    `destinations` are the full [M, N] result tensors of every rank as seen from this process: the local tensor
+    and peer views of the others (torch symmetric memory, CUDA IPC).  Built once, launched many times.
+    """
+
+    def __init__(self, a, b_slab, destination_ptrs, n_total: int, ldc: int, col0: int, out_dtype, stream=None) -> None:
+        import ctypes
+
+        import torch
+
+        from . import capi, harness
+        self.keep = (a, b_slab)
+        m, n = a.shape[0], b_slab.shape[0]
+        # problem->c is ignored by the fused entry point; a 1-element placeholder keeps the record well formed
+        self.placeholder = torch.empty((m, n), dtype=out_dtype, device="meta")
+        problem = capi.VecopsB200Matmul()
+        problem.struct_size = ctypes.sizeof(capi.VecopsB200Matmul)
+        problem.kernel = capi.KERNEL_BF16_TCGEN05
+        problem.m, problem.n, problem.k = m, n, a.shape[1]
+        problem.a, problem.a_stride_m, problem.a_stride_k = a.data_ptr(), a.stride(0), a.stride(1)
+        problem.b, problem.b_stride_n, problem.b_stride_k = b_slab.data_ptr(), b_slab.stride(0), b_slab.stride(1)
+        problem.c, problem.c_stride_m, problem.c_stride_n = None, n, 1
+        stream = stream if stream is not None else torch.cuda.current_stream(a.device)
+        problem.stream = stream.cuda_stream
+        problem.a_dtype, problem.b_dtype = harness.torch_dtype_code(a.dtype), harness.torch_dtype_code(b_slab.dtype)
+        problem.c_dtype = harness.torch_dtype_code(out_dtype)
+        problem.device_index = a.device.index
+        problem.flags = capi.MATMUL_FLAG_ASYNC
+        self.problem = problem
+        self.pointers = (ctypes.c_void_p * len(destination_ptrs))(*destination_ptrs)
+        self.gather = capi.VecopsB200Gather(ctypes.sizeof(capi.VecopsB200Gather), len(destination_ptrs), self.pointers, n_total, ldc, col0)
+        self.error = capi.ErrorBuffer()
+        self._run = capi.library().vecops_b200_matmul_allgather_run
+        self._args = (ctypes.byref(self.problem), ctypes.byref(self.gather), ctypes.byref(self.error.record))
+
+    def launch(self) -> None:
+        rc = self._run(*self._args)
+        if rc != 0:
+            self.error.raise_for(rc)
+
+
+def symmetric_result(m: int, n: int, dtype, device, group=None):
+    """Allocate the full [M, N] result in symmetric memory; returns (tensor, handle) with handle.buffer_ptrs = every rank's copy."""
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm_mem
+    tensor = symm_mem.empty((m, n), dtype=dtype, device=device)
+    handle = symm_mem.rendezvous(tensor, group if group is not None else dist.group.WORLD)
+    return tensor, handle
