@@ -372,9 +372,20 @@ def run_ours(args) -> None:
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     if world > 1:
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: this program prints ONE line there
-        dist.init_process_group("nccl", device_id=dev)
+        # NCCL may print a version banner on stdout when its communicator comes up; this program owes stdout ONE line,
+        # so stdout is pointed at stderr until the first collective has run.
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev)
+            warm = torch.zeros(1, device=dev)
+            dist.all_reduce(warm)
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
     lib = capi.library()
     peaks, peak_source = measured_peaks()
     port = Port()
