@@ -358,3 +358,62 @@ def test_operator_bridge_refuses_host_tensors_and_bad_handles():
     assert lib.vecops_operator_bridge_invoke_v1(handle, byref(call), 0, None, byref(error.record)) == capi.INVALID_ARGUMENT
     assert b"wrong device" in error.text.value
     assert lib.vecops_operator_bridge_invoke_v1(12345, byref(call), 0, None, byref(error.record)) == capi.NOT_FOUND
+
+
+# ------------------------------------------------------------------ tail tiles cut along K (partials meet in device scratch)
+
+def _tail_split_case(kind, m, n, k, out_bf16, monkeypatch, port):
+    rng = np.random.default_rng(m + 3 * n + 7 * k)
+    a, b, _ = inputs(kind, m, n, k, rng)
+    kernel = K.KERNEL_I8_TCGEN05 if kind == "i8" else K.KERNEL_BF16_TCGEN05
+    # the harness attaches the scratch the workspace query asks for: a non-zero answer means the tail is split
+    da, db = to_device(a, bf16=kind == "bf16"), to_device(b, bf16=kind == "bf16")
+    out_dtype = torch.int32 if kind == "i8" else (torch.bfloat16 if out_bf16 else torch.float32)
+    probe = harness.matmul_problem(da, db, torch.empty((m, n), dtype=out_dtype, device="cuda"), kernel=kernel)
+    assert harness.workspace_bytes(probe) > 0, "shape does not leave a splittable tail on this GPU"
+    split = run_case(kind, a, b, out_bf16=out_bf16, kernel=kernel)
+    again = run_case(kind, a, b, out_bf16=out_bf16, kernel=kernel)
+    assert np.array_equal(split, again), "the split tail must be reproducible run to run"
+    monkeypatch.setenv("VECOPS_B200_TAIL_SPLIT", "0")
+    whole = run_case(kind, a, b, out_bf16=out_bf16, kernel=kernel)
+    monkeypatch.delenv("VECOPS_B200_TAIL_SPLIT")
+    rows = np.unique(np.concatenate([np.linspace(0, m - 1, 24).astype(np.int64), np.arange(m - 8, m)]))
+    want = oracle(kind, port, a[rows], b, None, out_bf16)
+    if kind == "i8":
+        assert np.array_equal(split, whole)
+        assert np.array_equal(split[rows], want)
+    else:
+        check(kind, split, whole)
+        check(kind, split[rows], want)
+
+
+@pytest.mark.parametrize("m,n,k,out_bf16", [
+    (1536, 3584, 1024, True),    # 168 tiles: 20 tail tiles, 4 slices each on 148 SMs
+    (1536, 3584, 1024, False),
+    (1024, 6912, 512, True),     # 216 tiles: 68 tail tiles, 2 slices each
+    (1000, 6900, 520, False),    # the same grid with ragged M, N and K
+])
+def test_bf16_tcgen05_tail_split(port, monkeypatch, m, n, k, out_bf16):
+    _tail_split_case("bf16", m, n, k, out_bf16, monkeypatch, port)
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (512, 10496, 4096),          # 164 tiles: 16 tail tiles, 8 slices each
+    (1536, 3584, 2048),          # 20 tail tiles, 4 slices each
+    (1000, 6900, 1040),          # 68 tail tiles, 2 slices, ragged
+])
+def test_i8_tcgen05_tail_split(port, monkeypatch, m, n, k):
+    _tail_split_case("i8", m, n, k, True, monkeypatch, port)
+
+
+def test_tcgen05_tail_runs_whole_without_scratch(port):
+    # no workspace supplied: same result, tail tiles computed whole
+    rng = np.random.default_rng(5)
+    a, b, _ = inputs("i8", 1536, 3584, 1024, rng)
+    da, db = to_device(a), to_device(b)
+    c = torch.empty((1536, 3584), dtype=torch.int32, device="cuda")
+    problem = harness.matmul_problem(da, db, c, kernel=K.KERNEL_I8_TCGEN05)
+    error = capi.ErrorBuffer()
+    error.raise_for(capi.library().vecops_b200_matmul_run(byref(problem), byref(error.record)))
+    rows = np.arange(1400, 1536)
+    assert np.array_equal(c.cpu().numpy()[rows], port.matmul_i8(a[rows], b))

@@ -20,6 +20,14 @@
 // output overlaps the main loop tile by tile and needs no staging pass.  (Only
 // stores cross GPUs; every load, and anything with cluster multicast, stays local.)
 //
+// Tail splitting: when the tile count leaves the last wave mostly empty (512 tiles
+// on 148 SMs = 3.46 waves), the tail tiles are cut along K into S slices (S a power
+// of two) so that the last wave keeps S times as many SMs busy for 1/S of the time.
+// The S CTAs of a tile exchange fp32 (int32) partial accumulators through DEVICE
+// SCRATCH: each publishes the columns it does not own and raises a nonce-carrying
+// flag, then adds the others' partials to the columns it owns and stores those.
+// Fixed summation order, so results are reproducible.  Without scratch S = 1.
+//
 // Algorithmic traffic per launch: (M*K + N*K) * sizeof(in) + M*N * sizeof(out).
 #pragma once
 
@@ -43,6 +51,16 @@ struct GemmTc {
   static constexpr int kThreads = 32 * (2 + kEpiWarps);
   static constexpr int kTmemColumns = 512;
   static constexpr int kGroupM = 16;  // raster: 16 row-tiles share each sweep over N
+  // Tail split: a slice owns whole 128-byte output slabs, so the split cannot exceed the slabs of a tile row.
+  static constexpr int kMinSliceKb = 4;  // k-blocks a slice must keep for the split to pay
+  __host__ __device__ static constexpr int max_split(size_t out_elem) { return out_elem == 2 ? 4 : 8; }
+  // scratch: `slices` partial accumulators of kBlockM x kBlockN 32-bit words, then 4 flags (one per row quarter) per slice
+  __host__ __device__ static constexpr unsigned long long split_flags_offset(long long slices) {
+    return static_cast<unsigned long long>(slices) * kBlockM * kBlockN * 4;
+  }
+  __host__ __device__ static constexpr unsigned long long split_scratch_bytes(long long slices) {
+    return split_flags_offset(slices) + static_cast<unsigned long long>(slices) * 4 * 8;
+  }
 };
 
 // Destinations of the TMA-store epilogue: map[0] is the local C, the rest are peers' C matrices.
@@ -77,6 +95,56 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = in_group / group_rows;
 }
 
+// What a CTA works on in its i-th round.
+struct GemmItem {
+  int tile;
+  int kb_begin, kb_end;
+  int slice;    // which K slice of a split tail tile (0 when the tile is whole)
+  int slices;   // 1 = whole tile
+  int tail_index;  // index of the tile among the split tail tiles
+};
+
+// Rounds 0 .. full_rounds-1 are whole tiles, round-robin over the grid; the last round holds the tail:
+// whole tiles when `split` == 1, else tile (first_tail + cta / split), slice (cta % split).
+__device__ __forceinline__ bool gemm_item(int round, int num_tiles, int num_kb, int split, GemmItem& item) {
+  const int grid = gridDim.x, cta = blockIdx.x;
+  const int full_rounds = num_tiles / grid;
+  item.slice = 0;
+  item.slices = 1;
+  item.tail_index = 0;
+  item.kb_begin = 0;
+  item.kb_end = num_kb;
+  if (round < full_rounds) {
+    item.tile = cta + round * grid;
+    return true;
+  }
+  if (round > full_rounds) return false;
+  const int first_tail = full_rounds * grid;
+  const int tail = num_tiles - first_tail;
+  if (split <= 1) {
+    item.tile = first_tail + cta;
+    return cta < tail;
+  }
+  if (cta >= tail * split) return false;
+  item.tail_index = cta / split;
+  item.tile = first_tail + item.tail_index;
+  item.slice = cta % split;
+  item.slices = split;
+  item.kb_begin = static_cast<int>(static_cast<long long>(num_kb) * item.slice / split);
+  item.kb_end = static_cast<int>(static_cast<long long>(num_kb) * (item.slice + 1) / split);
+  return true;
+}
+
+// Host and device agree on the split: the largest power of two S with tail * S <= grid, S <= max_split,
+// and at least kMinSliceKb k-blocks left per slice.
+__host__ __device__ inline int gemm_tail_split(long long num_tiles, int grid, int num_kb, int max_split) {
+  const long long tail = num_tiles % grid;
+  if (tail == 0 || num_tiles < grid) return 1;
+  int split = 1;
+  while (split * 2 <= max_split && tail * (split * 2) <= grid && split * 2 * GemmTc::kMinSliceKb <= num_kb) split *= 2;
+  return split;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -88,7 +156,8 @@ __global__ void __launch_bounds__(GemmTc::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const __grid_constant__ GemmStoreMaps tma_c, int num_dest, int c_col_offset, OutT* __restrict__ c,
                     long long ldc, int M, int N, int K, const float* __restrict__ column_scale, uint32_t idesc,
-                    int use_tma_store, uint32_t* __restrict__ status) {
+                    int use_tma_store, int split, uint32_t* __restrict__ partials, unsigned long long* __restrict__ flags,
+                    unsigned long long nonce, uint32_t* __restrict__ status, unsigned long long* __restrict__ trace) {
   using G = GemmTc;
   constexpr int kElemBytes = kInt8 ? 1 : 2;
   constexpr int kBlockK = G::kBlockKBytes / kElemBytes;  // elements per k-block
@@ -110,6 +179,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // optional timeline (nanoseconds) for tuning: 16 slots per CTA, written only when a trace buffer is given
+  auto mark = [&](int slot) {
+    if (trace != nullptr && slot < 16) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      trace[blockIdx.x * 16 + slot] = now;
+    }
+  };
+  if (threadIdx.x == 0) {
+    mark(0);
+    if (trace != nullptr) trace[blockIdx.x * 16 + 13] = static_cast<unsigned long long>(clock64());  // SM cycle counter at start
+  }
 
   const int tiles_m = (M + G::kBlockM - 1) / G::kBlockM;
   const int tiles_n = (N + G::kBlockN - 1) / G::kBlockN;
@@ -146,10 +227,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      GemmItem item;
+      for (int round = 0; ok && gemm_item(round, num_tiles, num_kb, split, item); ++round) {
         int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, tm, tn);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        tile_coords(item.tile, tiles_m, tiles_n, tm, tn);
+        for (int kb = item.kb_begin; kb < item.kb_end; ++kb) {
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag)) {
             report_status(status, kStatusProducerWait);
             *abort_flag = 1;
@@ -176,7 +258,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int tile_index = 0;
+      GemmItem item;
+      for (int round = 0; ok && gemm_item(round, num_tiles, num_kb, split, item); ++round, ++tile_index) {
+        mark(1 + 2 * tile_index);  // MMA issuer reaches tile i
         if (!mbar_wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag)) {
           report_status(status, kStatusMmaWaitTmem);
           *abort_flag = 1;
@@ -184,7 +269,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
         tcgen05_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * G::kBlockN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = item.kb_begin; kb < item.kb_end; ++kb) {
           if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag)) {
             report_status(status, kStatusMmaWaitFull);
             *abort_flag = 1;
@@ -198,7 +283,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 #pragma unroll
           for (int kk = 0; kk < G::kBlockKBytes / 32; ++kk) {
             // +32 bytes along K inside the swizzle atom = +2 in the address field
-            const uint32_t accumulate = (kb | kk) != 0 ? 1u : 0u;
+            const uint32_t accumulate = (kb != item.kb_begin || kk != 0) ? 1u : 0u;
             if (kInt8) umma_i8(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accumulate);
             else umma_f16(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accumulate);
           }
@@ -210,6 +295,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
         if (!ok) break;
         umma_commit(tmem_full_bar + 8 * acc);
+        mark(2 + 2 * tile_index);  // all MMAs of tile i issued
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -222,9 +308,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     int acc = 0;
     uint32_t acc_phase = 0;
     int buf_sel = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    GemmItem item;
+    bool epilogue_ok = true;
+    for (int round = 0; epilogue_ok && gemm_item(round, num_tiles, num_kb, split, item); ++round) {
       int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      tile_coords(item.tile, tiles_m, tiles_n, tm, tn);
       if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag)) {
         report_status(status, kStatusEpilogueWait);
         *abort_flag = 1;
@@ -234,14 +322,63 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       const int row0 = tm * G::kBlockM + quarter * 32;
       const int row = row0 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * G::kBlockN;
+      constexpr int kSlabs = G::kBlockN / kOutCols;
+      int slab_begin = 0, slab_end = kSlabs;
+      // partial accumulators of one split tile: [slice][column][row] 32-bit words, rows contiguous
+      const size_t tile_words = static_cast<size_t>(G::kBlockN) * G::kBlockM;
+      uint32_t* my_partial = nullptr;
+      if (item.slices > 1) {
+        // this slice stores the columns [slab_begin, slab_end); the rest of its accumulator goes to the owners
+        slab_begin = kSlabs * item.slice / item.slices;
+        slab_end = kSlabs * (item.slice + 1) / item.slices;
+        my_partial = partials + (static_cast<size_t>(item.tail_index) * item.slices + item.slice) * tile_words + quarter * 32 + lane;
+        for (int chunk = 0; chunk < G::kBlockN / 32; ++chunk) {
+          const int owner_slab = chunk * 32 / kOutCols;
+          if (owner_slab >= slab_begin && owner_slab < slab_end) continue;
+          uint32_t v[32];
+          tmem_load_32x32(taddr + chunk * 32, v);
+          tmem_load_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) __stcg(my_partial + static_cast<size_t>(chunk * 32 + j) * G::kBlockM, v[j]);
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release_gpu_u64(flags + (static_cast<size_t>(item.tail_index) * item.slices + item.slice) * 4 + quarter, nonce);
+        for (int other = 0; other < item.slices; ++other) {
+          if (other == item.slice) continue;
+          if (!wait_flag_u64(flags + (static_cast<size_t>(item.tail_index) * item.slices + other) * 4 + quarter, nonce, abort_flag)) {
+            report_status(status, kStatusEpilogueWait);
+            *abort_flag = 1;
+            epilogue_ok = false;
+          }
+        }
+        if (!epilogue_ok) break;
+      }
+      // adds the other slices' partial sums of 32 columns starting at `first_col` (column inside the tile)
+      auto add_partials = [&](uint32_t (&v)[32], int first_col) {
+        for (int other = 0; other < item.slices; ++other) {
+          if (other == item.slice) continue;
+          const uint32_t* src = partials + (static_cast<size_t>(item.tail_index) * item.slices + other) * tile_words +
+                                static_cast<size_t>(first_col) * G::kBlockM + quarter * 32 + lane;
+          uint32_t part[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) part[j] = __ldcg(src + static_cast<size_t>(j) * G::kBlockM);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if constexpr (kInt8) v[j] += part[j];
+            else v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(part[j]));
+          }
+        }
+      };
 #pragma unroll 1
-      for (int slab = 0; slab < G::kBlockN / kOutCols; ++slab) {
+      for (int slab = slab_begin; slab < slab_end; ++slab) {
         const int col0 = tn * G::kBlockN + slab * kOutCols;
         if (col0 >= N) break;  // uniform across the warp
         uint32_t words[32];    // 128 bytes of converted output for this thread's row
         if constexpr (sizeof(OutT) == 4) {
           tmem_load_32x32(taddr + slab * 32, words);
           tmem_load_wait();
+          if (item.slices > 1) add_partials(words, slab * 32);
           if constexpr (!kInt8) {
             if (column_scale != nullptr) {
 #pragma unroll
@@ -256,6 +393,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           tmem_load_32x32(taddr + slab * 64, v0);
           tmem_load_32x32(taddr + slab * 64 + 32, v1);
           tmem_load_wait();
+          if (item.slices > 1) {
+            add_partials(v0, slab * 64);
+            add_partials(v1, slab * 64 + 32);
+          }
           if (column_scale != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
@@ -322,6 +463,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       if (acc == 0) acc_phase ^= 1u;
     }
     if (use_tma_store && lane == 0) tma_store_wait_all<0>();
+    if (warp == 2 && lane == 0) {
+      mark(15);
+      if (trace != nullptr) trace[blockIdx.x * 16 + 14] = static_cast<unsigned long long>(clock64());  // ... and at the end
+    }
   }
 
   // ---------------------------------------------------------------- teardown

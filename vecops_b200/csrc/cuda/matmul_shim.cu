@@ -305,6 +305,14 @@ int32_t raise_smem_limit(Kernel kernel, int bytes, VecopsError* error) {
   return VECOPS_STATUS_OK;
 }
 
+uint64_t fresh_nonce(const void* salt);
+
+// Tuning aid: VECOPS_B200_TAIL_SPLIT=0 keeps tail tiles whole.
+bool tail_split_forced_off() {
+  const char* v = getenv("VECOPS_B200_TAIL_SPLIT");
+  return v != nullptr && v[0] == '0';
+}
+
 // Where the epilogue's TMA stores go when the output is gathered across GPUs.
 struct GatherTargets {
   int count = 0;                 // 0 = plain GEMM into p.c
@@ -375,9 +383,24 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
   }
   const long long tiles = ((p.m + G::kBlockM - 1) / G::kBlockM) * ((p.n + G::kBlockN - 1) / G::kBlockN);
   const int grid = static_cast<int>(tiles < dev.prop.multiProcessorCount ? tiles : dev.prop.multiProcessorCount);
+  // Tail tiles are cut along K when the caller supplied the scratch the slices meet in; without it the tail runs whole.
+  const int num_kb = static_cast<int>((p.k * elem + G::kBlockKBytes - 1) / G::kBlockKBytes);
+  int split = tail_split_forced_off() ? 1 : gemm_tail_split(tiles, grid, num_kb, G::max_split(sizeof(OutT)));
+  uint32_t* partials = nullptr;
+  unsigned long long* flags = nullptr;
+  if (split > 1) {
+    const long long slices = (tiles % grid) * split;
+    if (p.workspace == nullptr || !aligned16(p.workspace) || p.workspace_size < G::split_scratch_bytes(slices)) {
+      split = 1;
+    } else {
+      partials = static_cast<uint32_t*>(p.workspace);
+      flags = reinterpret_cast<unsigned long long*>(static_cast<char*>(p.workspace) + G::split_flags_offset(slices));
+    }
+  }
   kernel<<<grid, G::kThreads, G::kSmemBytes, stream>>>(map_a, map_b, maps, num_dest, col_offset, static_cast<OutT*>(p.c), p.c_stride_m,
                                                        static_cast<int>(p.m), static_cast<int>(p.n), static_cast<int>(p.k),
-                                                       kInt8 ? nullptr : p.column_scale, idesc, tma_store ? 1 : 0, g_status_host);
+                                                       kInt8 ? nullptr : p.column_scale, idesc, tma_store ? 1 : 0, split, partials, flags,
+                                                       split > 1 ? fresh_nonce(p.workspace) : 0ull, g_status_host, g_trace);
   g_launches.fetch_add(1);
   return VECOPS_STATUS_OK;
 }
@@ -482,6 +505,28 @@ int32_t launch_w8_small(const VecopsB200Matmul& p, const DeviceState& dev, cudaS
   return VECOPS_STATUS_OK;
 }
 
+// Scratch for the K slices of the tail tiles.  The grid is one CTA per SM; the SM count comes from the device the
+// problem names when one is usable, else from the part this library is built for (148).
+uint64_t tcgen05_tail_scratch(const VecopsB200Matmul& p, bool int8) {
+  using G = GemmTc;
+  if (p.m <= 0 || p.n <= 0 || p.k <= 0) return 0;
+  int sms = 148;
+  int device = p.device_index;
+  if (device < 0 && cudaGetDevice(&device) != cudaSuccess) device = -1;
+  if (device >= 0) {
+    int value = 0;
+    if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && value > 0) sms = value;
+  }
+  cudaGetLastError();  // a host without a GPU is a legal caller of the query
+  const long long tiles = ((p.m + G::kBlockM - 1) / G::kBlockM) * ((p.n + G::kBlockN - 1) / G::kBlockN);
+  const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  const size_t elem = int8 ? 1 : 2;
+  const size_t out = (int8 || p.c_dtype == VECOPS_DTYPE_F32) ? 4 : 2;
+  const int num_kb = static_cast<int>((p.k * elem + G::kBlockKBytes - 1) / G::kBlockKBytes);
+  const int split = gemm_tail_split(tiles, grid, num_kb, G::max_split(out));
+  return split > 1 ? G::split_scratch_bytes((tiles % grid) * split) : 0;
+}
+
 uint64_t fresh_nonce(const void* salt) {
   static std::atomic<uint64_t> counter{0x243F6A8885A308D3ull};
   uint64_t z = counter.fetch_add(0x9E3779B97F4A7C15ull) ^ reinterpret_cast<uintptr_t>(salt);
@@ -570,9 +615,14 @@ int32_t vecops_b200_matmul_workspace(const VecopsB200Matmul* problem, uint64_t* 
   uint32_t kernel;
   rc = select_kernel(*problem, row, &kernel, error);
   if (rc != VECOPS_STATUS_OK) return rc;
-  // Only the stream-K weight-only kernel exchanges partial sums through device scratch; every other
-  // kernel's split-K meets in shared memory.
-  *bytes = kernel == VECOPS_B200_KERNEL_W8_TCGEN05 ? W8Tc::scratch_bytes(static_cast<int>(problem->m), problem->k) : 0;
+  // Kernels whose CTAs exchange partial sums through device scratch: the stream-K weight-only kernel, and the
+  // tcgen05 GEMMs when their last wave is cut along K.  Every other split-K meets in shared memory.
+  *bytes = 0;
+  if (kernel == VECOPS_B200_KERNEL_W8_TCGEN05) {
+    *bytes = W8Tc::scratch_bytes(static_cast<int>(problem->m), problem->k);
+  } else if (kernel == VECOPS_B200_KERNEL_BF16_TCGEN05 || kernel == VECOPS_B200_KERNEL_I8_TCGEN05) {
+    *bytes = tcgen05_tail_scratch(*problem, kernel == VECOPS_B200_KERNEL_I8_TCGEN05);
+  }
   return VECOPS_STATUS_OK;
 }
 

@@ -99,6 +99,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return true;
 }
 
+// ---------------------------------------------------------------- flags between CTAs (global memory)
+
+__device__ __forceinline__ void st_release_gpu_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// Bounded wait until *flag == value (another CTA of the same grid publishes it).
+__device__ __forceinline__ bool wait_flag_u64(const unsigned long long* flag, unsigned long long value,
+                                              volatile uint32_t* abort_flag) {
+  const long long start = clock64();
+  for (;;) {
+    unsigned long long seen;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(flag) : "memory");
+    if (seen == value) return true;
+    __nanosleep(100);
+    if (*abort_flag != 0 || clock64() - start > kWaitCycleBudget) return false;
+  }
+}
+
 // ---------------------------------------------------------------- TMA
 
 __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) {

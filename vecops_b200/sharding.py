@@ -98,6 +98,7 @@ class FusedGatherGemm:
         problem.device_index = a.device.index
         problem.flags = capi.MATMUL_FLAG_ASYNC
         self.problem = problem
+        self.scratch = harness.attach_workspace(problem, a.device)  # partial sums of a split tail wave meet here
         self.pointers = (ctypes.c_void_p * len(destination_ptrs))(*destination_ptrs)
         self.gather = capi.VecopsB200Gather(ctypes.sizeof(capi.VecopsB200Gather), len(destination_ptrs), self.pointers, n_total, ldc, col0)
         self.error = capi.ErrorBuffer()
