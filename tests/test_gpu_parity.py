@@ -95,15 +95,22 @@ def test_golden_fixtures_through_automatic_dispatch(golden):
 TC_SHAPES = [(128, 256, 64), (128, 256, 512), (512, 1024, 512), (200, 328, 200), (1, 256, 128), (129, 257, 72), (640, 768, 1032)]
 
 
+@pytest.fixture(params=["single", "pair"])
+def cta_form(request, monkeypatch):
+    """Run the tcgen05 GEMM as single CTAs on 128x256 tiles, or as CTA pairs on 256x256 tiles (cta_group::2)."""
+    monkeypatch.setenv("VECOPS_B200_GEMM_PAIR", "1" if request.param == "pair" else "0")
+    return request.param
+
+
 @pytest.mark.parametrize("m,n,k", TC_SHAPES)
 @pytest.mark.parametrize("out_bf16", [True, False])
-def test_bf16_tcgen05(port, m, n, k, out_bf16):
+def test_bf16_tcgen05(port, cta_form, m, n, k, out_bf16):
     rng = np.random.default_rng(m * 7 + n * 3 + k)
     a, b, _ = inputs("bf16", m, n, k, rng)
     check("bf16", run_case("bf16", a, b, out_bf16=out_bf16, kernel=K.KERNEL_BF16_TCGEN05), oracle("bf16", port, a, b, None, out_bf16))
 
 
-def test_bf16_tcgen05_scale_and_padded_c(port):
+def test_bf16_tcgen05_scale_and_padded_c(port, cta_form):
     rng = np.random.default_rng(21)
     a, b, _ = inputs("bf16", 300, 520, 264, rng)
     scale = rng.uniform(0.5, 2.0, 520).astype(np.float32)
@@ -112,7 +119,7 @@ def test_bf16_tcgen05_scale_and_padded_c(port):
         check("bf16", got, oracle("bf16", port, a, b, scale, out_bf16))
 
 
-def test_bf16_tcgen05_direct_epilogue_for_unaligned_c(port):
+def test_bf16_tcgen05_direct_epilogue_for_unaligned_c(port, cta_form):
     # a C row pitch that is not a multiple of 16 bytes cannot use TMA stores: the direct path must serve it
     rng = np.random.default_rng(22)
     a, b, _ = inputs("bf16", 150, 300, 128, rng)
@@ -122,7 +129,7 @@ def test_bf16_tcgen05_direct_epilogue_for_unaligned_c(port):
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 128), (384, 512, 1024), (150, 300, 272), (1, 512, 4096), (257, 129, 48)])
 @pytest.mark.parametrize("a_dtype,b_dtype", [(np.int8, np.int8), (np.uint8, np.int8), (np.int8, np.uint8), (np.uint8, np.uint8)])
-def test_i8_tcgen05_all_signedness_pairs(port, m, n, k, a_dtype, b_dtype):
+def test_i8_tcgen05_all_signedness_pairs(port, cta_form, m, n, k, a_dtype, b_dtype):
     rng = np.random.default_rng(m + n + k)
     a, b, _ = inputs("i8", m, n, k, rng, a_dtype, b_dtype)
     check("i8", run_case("i8", a, b, kernel=K.KERNEL_I8_TCGEN05), port.matmul_i8(a, b))
@@ -186,7 +193,7 @@ def test_strided_kernel_on_reference_test_shapes(port, kind):
         check(kind, got, oracle(kind, port, a, b, s))
 
 
-def test_fused_allgather_epilogue_stores_the_slab_into_every_destination(port):
+def test_fused_allgather_epilogue_stores_the_slab_into_every_destination(port, cta_form):
     # Two destinations on ONE GPU stand in for two ranks' result matrices: the epilogue must place this
     # rank's [M, n] slab at columns [col0, col0 + n) of both, and touch nothing else.
     from vecops_b200 import sharding
@@ -388,12 +395,12 @@ def _tail_split_case(kind, m, n, k, out_bf16, monkeypatch, port):
 
 
 @pytest.mark.parametrize("m,n,k,out_bf16", [
-    (1536, 3584, 1024, True),    # 168 tiles: 20 tail tiles, 4 slices each on 148 SMs
+    (1536, 3584, 1024, True),    # 168 tiles: 20 tail tiles, 4 slices each on 148 SMs (pairs: 84 tiles, 10 in the tail)
     (1536, 3584, 1024, False),
     (1024, 6912, 512, True),     # 216 tiles: 68 tail tiles, 2 slices each
     (1000, 6900, 520, False),    # the same grid with ragged M, N and K
 ])
-def test_bf16_tcgen05_tail_split(port, monkeypatch, m, n, k, out_bf16):
+def test_bf16_tcgen05_tail_split(port, monkeypatch, cta_form, m, n, k, out_bf16):
     _tail_split_case("bf16", m, n, k, out_bf16, monkeypatch, port)
 
 
@@ -402,7 +409,7 @@ def test_bf16_tcgen05_tail_split(port, monkeypatch, m, n, k, out_bf16):
     (1536, 3584, 2048),          # 20 tail tiles, 4 slices each
     (1000, 6900, 1040),          # 68 tail tiles, 2 slices, ragged
 ])
-def test_i8_tcgen05_tail_split(port, monkeypatch, m, n, k):
+def test_i8_tcgen05_tail_split(port, monkeypatch, cta_form, m, n, k):
     _tail_split_case("i8", m, n, k, True, monkeypatch, port)
 
 

@@ -28,8 +28,17 @@
 // flag, then adds the others' partials to the columns it owns and stores those.
 // Fixed summation order, so results are reproducible.  Without scratch S = 1.
 //
+// CTA pairs (kPair): two CTAs of a cluster, on the two SMs of one TPC, share a 256x256 tile.  Each loads its 128 rows
+// of A and its 128 of the 256 rows of B (half the shared-memory fill and L2 traffic per SM of the single-CTA form) into
+// a 6-stage ring; the leader's MMA thread issues tcgen05.mma.cta_group::2 (M = 256), which reads both CTAs' shared
+// memory and writes each CTA's 128 rows of D into that CTA's TMEM; both CTAs run the epilogue on their own rows.
+// Barriers: both CTAs' loads count bytes on the leader's `full`; the leader's commits arrive on `empty` and
+// `tmem_full` of both CTAs; both epilogues arrive on the leader's `tmem_empty`.  Loads go to one CTA each.
+//
 // Algorithmic traffic per launch: (M*K + N*K) * sizeof(in) + M*N * sizeof(out).
 #pragma once
+
+#include <type_traits>
 
 #include "ptx.cuh"
 
@@ -50,7 +59,7 @@ struct GemmTc {
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarrierBytes + 1024;  // + alignment slack
   static constexpr int kThreads = 32 * (2 + kEpiWarps);
   static constexpr int kTmemColumns = 512;
-  static constexpr int kGroupM = 16;  // raster: 16 row-tiles share each sweep over N
+  static constexpr long long kGroupBytes = 32ll << 20;  // raster: row-tiles holding this much of A share each sweep over N
   // Tail split: a slice owns whole 128-byte output slabs, so the split cannot exceed the slabs of a tile row.
   static constexpr int kMinSliceKb = 4;  // k-blocks a slice must keep for the split to pay
   __host__ __device__ static constexpr int max_split(size_t out_elem) { return out_elem == 2 ? 4 : 8; }
@@ -62,6 +71,16 @@ struct GemmTc {
     return split_flags_offset(slices) + static_cast<unsigned long long>(slices) * 4 * 8;
   }
 };
+
+// The CTA-pair form: per-CTA constants (a CTA still owns 128 rows x 256 columns of accumulators).
+struct GemmPair : GemmTc {
+  static constexpr int kStages = 6;
+  static constexpr int kBRows = kBlockN / 2;  // rows of B this CTA feeds to the pair MMA
+  static constexpr int kBBytes = kBRows * kBlockKBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarrierBytes + 1024;
+};
+static_assert(GemmPair::kSmemBytes <= 227 * 1024 && GemmTc::kSmemBytes <= 227 * 1024, "shared memory budget");
 
 // Destinations of the TMA-store epilogue: map[0] is the local C, the rest are peers' C matrices.
 struct GemmStoreMaps {
@@ -85,11 +104,12 @@ __device__ __forceinline__ void report_status(uint32_t* status, uint32_t code) {
   __threadfence_system();
 }
 
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-  const int per_group = GemmTc::kGroupM * tiles_n;
+// Raster: `group_m` row-tiles share each sweep over N, so that one wave of tiles re-reads few rows of A and B.
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+  const int per_group = group_m * tiles_n;
   const int group = tile / per_group;
-  const int first_m = group * GemmTc::kGroupM;
-  const int group_rows = min(tiles_m - first_m, GemmTc::kGroupM);
+  const int first_m = group * group_m;
+  const int group_rows = min(tiles_m - first_m, group_m);
   const int in_group = tile - group * per_group;
   tm = first_m + in_group % group_rows;
   tn = in_group / group_rows;
@@ -104,35 +124,40 @@ struct GemmItem {
   int tail_index;  // index of the tile among the split tail tiles
 };
 
-// Rounds 0 .. full_rounds-1 are whole tiles, round-robin over the grid; the last round holds the tail:
-// whole tiles when `split` == 1, else tile (first_tail + cta / split), slice (cta % split).
-__device__ __forceinline__ bool gemm_item(int round, int num_tiles, int num_kb, int split, GemmItem& item) {
-  const int grid = gridDim.x, cta = blockIdx.x;
+// The whole tiles go round-robin over the workers (`cta` of `grid`: CTAs, or CTA pairs).  The tail tiles - those
+// left after the last full round - follow as whole tiles when `split` == 1.  When they are split, worker w takes slice
+// (w % split) of tail tile (w / split) and takes it FIRST: the exchange of partial sums and the wait for the other
+// slices then hide under the main loop of the worker's next tile instead of ending the kernel.
+__device__ __forceinline__ bool gemm_item(int round, int num_tiles, int num_kb, int split, int cta, int grid, GemmItem& item) {
   const int full_rounds = num_tiles / grid;
+  const int first_tail = full_rounds * grid;
+  const int tail = num_tiles - first_tail;
   item.slice = 0;
   item.slices = 1;
   item.tail_index = 0;
   item.kb_begin = 0;
   item.kb_end = num_kb;
+  if (split > 1 && cta < tail * split) {
+    if (round == 0) {
+      item.tail_index = cta / split;
+      item.tile = first_tail + item.tail_index;
+      item.slice = cta % split;
+      item.slices = split;
+      item.kb_begin = static_cast<int>(static_cast<long long>(num_kb) * item.slice / split);
+      item.kb_end = static_cast<int>(static_cast<long long>(num_kb) * (item.slice + 1) / split);
+      return true;
+    }
+    --round;
+  }
   if (round < full_rounds) {
     item.tile = cta + round * grid;
     return true;
   }
-  if (round > full_rounds) return false;
-  const int first_tail = full_rounds * grid;
-  const int tail = num_tiles - first_tail;
-  if (split <= 1) {
+  if (round == full_rounds && split <= 1 && cta < tail) {
     item.tile = first_tail + cta;
-    return cta < tail;
+    return true;
   }
-  if (cta >= tail * split) return false;
-  item.tail_index = cta / split;
-  item.tile = first_tail + item.tail_index;
-  item.slice = cta % split;
-  item.slices = split;
-  item.kb_begin = static_cast<int>(static_cast<long long>(num_kb) * item.slice / split);
-  item.kb_end = static_cast<int>(static_cast<long long>(num_kb) * (item.slice + 1) / split);
-  return true;
+  return false;
 }
 
 // Host and device agree on the split: the largest power of two S with tail * S <= grid, S <= max_split,
@@ -151,16 +176,20 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 // OutT: __nv_bfloat16 or float for kind::f16, int32_t for kind::i8.
-template <bool kInt8, typename OutT>
+template <bool kInt8, typename OutT, bool kPair>
 __global__ void __launch_bounds__(GemmTc::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const __grid_constant__ GemmStoreMaps tma_c, int num_dest, int c_col_offset, OutT* __restrict__ c,
                     long long ldc, int M, int N, int K, const float* __restrict__ column_scale, uint32_t idesc,
-                    int use_tma_store, int split, uint32_t* __restrict__ partials, unsigned long long* __restrict__ flags,
+                    int use_tma_store, int raster_group, int split, uint32_t* __restrict__ partials, unsigned long long* __restrict__ flags,
                     unsigned long long nonce, uint32_t* __restrict__ status, unsigned long long* __restrict__ trace) {
-  using G = GemmTc;
+  using G = typename std::conditional<kPair, GemmPair, GemmTc>::type;
   constexpr int kElemBytes = kInt8 ? 1 : 2;
   constexpr int kBlockK = G::kBlockKBytes / kElemBytes;  // elements per k-block
+  constexpr int kTileM = kPair ? 2 * G::kBlockM : G::kBlockM;  // rows of the tile a worker (CTA or pair) owns
+  const uint32_t pair_rank = kPair ? cluster_cta_rank() : 0u;
+  const int worker = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int workers = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   constexpr int kOutCols = 128 / static_cast<int>(sizeof(OutT));  // columns per 128-byte slab row
 
   extern __shared__ uint8_t smem_raw[];
@@ -169,7 +198,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const uint32_t epi_base = smem_base + G::kStages * G::kStageBytes;
   uint8_t* bar_gen = smem_gen + G::kStages * G::kStageBytes + G::kEpiBytes;
   const uint32_t bar_base = epi_base + G::kEpiBytes;
-  // barrier block: full[4] empty[4] tmem_full[2] tmem_empty[2] | tmem slot | abort flag
+  // barrier block: full[stages] empty[stages] tmem_full[2] tmem_empty[2] | tmem slot | abort flag
   const uint32_t full_bar = bar_base;
   const uint32_t empty_bar = bar_base + 8 * G::kStages;
   const uint32_t tmem_full_bar = bar_base + 16 * G::kStages;
@@ -192,7 +221,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     if (trace != nullptr) trace[blockIdx.x * 16 + 13] = static_cast<unsigned long long>(clock64());  // SM cycle counter at start
   }
 
-  const int tiles_m = (M + G::kBlockM - 1) / G::kBlockM;
+  const int tiles_m = (M + kTileM - 1) / kTileM;
   const int tiles_n = (N + G::kBlockN - 1) / G::kBlockN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + kBlockK - 1) / kBlockK;
@@ -204,7 +233,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar + 8 * a, 1);
-      mbar_init(tmem_empty_bar + 8 * a, G::kEpiWarps * 32);
+      mbar_init(tmem_empty_bar + 8 * a, G::kEpiWarps * 32 * (kPair ? 2 : 1));  // the leader's collects both epilogues
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -213,11 +242,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     if (use_tma_store) tma_prefetch_descriptor(&tma_c.map[0]);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), G::kTmemColumns);
-    tmem_relinquish();
+    if constexpr (kPair) {
+      tmem_alloc_pair(smem_u32(tmem_slot), G::kTmemColumns);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), G::kTmemColumns);
+      tmem_relinquish();
+    }
   }
   tcgen05_fence_before_sync();
   __syncthreads();
+  if constexpr (kPair) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -228,9 +263,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       uint32_t phase = 0;
       bool ok = true;
       GemmItem item;
-      for (int round = 0; ok && gemm_item(round, num_tiles, num_kb, split, item); ++round) {
+      for (int round = 0; ok && gemm_item(round, num_tiles, num_kb, split, worker, workers, item); ++round) {
         int tm, tn;
-        tile_coords(item.tile, tiles_m, tiles_n, tm, tn);
+        tile_coords(item.tile, tiles_m, tiles_n, raster_group, tm, tn);
         for (int kb = item.kb_begin; kb < item.kb_end; ++kb) {
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag)) {
             report_status(status, kStatusProducerWait);
@@ -240,9 +275,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           }
           const uint32_t a_dst = smem_base + stage * G::kStageBytes;
           const uint32_t b_dst = a_dst + G::kABytes;
-          mbar_arrive_expect_tx(full_bar + 8 * stage, G::kStageBytes);
-          tma_load_2d(a_dst, &tma_a, full_bar + 8 * stage, kb * kBlockK, tm * G::kBlockM);
-          tma_load_2d(b_dst, &tma_b, full_bar + 8 * stage, kb * kBlockK, tn * G::kBlockN);
+          if constexpr (kPair) {
+            // both CTAs' bytes are counted on the leader's barrier; the leader announces the sum
+            const uint32_t leader_full = map_to_cta(full_bar + 8 * stage, 0);
+            if (pair_rank == 0) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * G::kStageBytes);
+            tma_load_2d_pair(a_dst, &tma_a, leader_full, kb * kBlockK, tm * kTileM + static_cast<int>(pair_rank) * G::kBlockM);
+            tma_load_2d_pair(b_dst, &tma_b, leader_full, kb * kBlockK, tn * G::kBlockN + static_cast<int>(pair_rank) * GemmPair::kBRows);
+          } else {
+            mbar_arrive_expect_tx(full_bar + 8 * stage, G::kStageBytes);
+            tma_load_2d(a_dst, &tma_a, full_bar + 8 * stage, kb * kBlockK, tm * G::kBlockM);
+            tma_load_2d(b_dst, &tma_b, full_bar + 8 * stage, kb * kBlockK, tn * G::kBlockN);
+          }
           if (++stage == G::kStages) {
             stage = 0;
             phase ^= 1u;
@@ -252,7 +295,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && pair_rank == 0) {  // of a pair, only the leader issues
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -260,9 +303,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       bool ok = true;
       int tile_index = 0;
       GemmItem item;
-      for (int round = 0; ok && gemm_item(round, num_tiles, num_kb, split, item); ++round, ++tile_index) {
+      for (int round = 0; ok && gemm_item(round, num_tiles, num_kb, split, worker, workers, item); ++round, ++tile_index) {
         mark(1 + 2 * tile_index);  // MMA issuer reaches tile i
-        if (!mbar_wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag)) {
+        if (!(kPair ? mbar_wait_cluster(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag)
+                    : mbar_wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag))) {
           report_status(status, kStatusMmaWaitTmem);
           *abort_flag = 1;
           break;
@@ -284,17 +328,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           for (int kk = 0; kk < G::kBlockKBytes / 32; ++kk) {
             // +32 bytes along K inside the swizzle atom = +2 in the address field
             const uint32_t accumulate = (kb != item.kb_begin || kk != 0) ? 1u : 0u;
-            if (kInt8) umma_i8(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accumulate);
-            else umma_f16(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accumulate);
+            if constexpr (kPair) {
+              if (kInt8) umma_i8_pair(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accumulate);
+              else umma_f16_pair(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accumulate);
+            } else {
+              if (kInt8) umma_i8(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accumulate);
+              else umma_f16(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accumulate);
+            }
           }
-          umma_commit(empty_bar + 8 * stage);
+          if constexpr (kPair) umma_commit_pair(empty_bar + 8 * stage);
+          else umma_commit(empty_bar + 8 * stage);
           if (++stage == G::kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        umma_commit(tmem_full_bar + 8 * acc);
+        if constexpr (kPair) umma_commit_pair(tmem_full_bar + 8 * acc);
+        else umma_commit(tmem_full_bar + 8 * acc);
         mark(2 + 2 * tile_index);  // all MMAs of tile i issued
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
@@ -310,16 +361,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     int buf_sel = 0;
     GemmItem item;
     bool epilogue_ok = true;
-    for (int round = 0; epilogue_ok && gemm_item(round, num_tiles, num_kb, split, item); ++round) {
+    for (int round = 0; epilogue_ok && gemm_item(round, num_tiles, num_kb, split, worker, workers, item); ++round) {
       int tm, tn;
-      tile_coords(item.tile, tiles_m, tiles_n, tm, tn);
+      tile_coords(item.tile, tiles_m, tiles_n, raster_group, tm, tn);
       if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag)) {
         report_status(status, kStatusEpilogueWait);
         *abort_flag = 1;
         break;
       }
       tcgen05_fence_after_sync();
-      const int row0 = tm * G::kBlockM + quarter * 32;
+      const int row0 = tm * kTileM + static_cast<int>(pair_rank) * G::kBlockM + quarter * 32;
       const int row = row0 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * G::kBlockN;
       constexpr int kSlabs = G::kBlockN / kOutCols;
@@ -327,11 +378,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       // partial accumulators of one split tile: [slice][column][row] 32-bit words, rows contiguous
       const size_t tile_words = static_cast<size_t>(G::kBlockN) * G::kBlockM;
       uint32_t* my_partial = nullptr;
+      // scratch slot of slice `s` of this tile (of this CTA's half of it, for a pair)
+      auto slot_of = [&](int s) {
+        const size_t slot = static_cast<size_t>(item.tail_index) * item.slices + s;
+        return kPair ? slot * 2 + pair_rank : slot;
+      };
       if (item.slices > 1) {
         // this slice stores the columns [slab_begin, slab_end); the rest of its accumulator goes to the owners
         slab_begin = kSlabs * item.slice / item.slices;
         slab_end = kSlabs * (item.slice + 1) / item.slices;
-        my_partial = partials + (static_cast<size_t>(item.tail_index) * item.slices + item.slice) * tile_words + quarter * 32 + lane;
+        my_partial = partials + slot_of(item.slice) * tile_words + quarter * 32 + lane;
         for (int chunk = 0; chunk < G::kBlockN / 32; ++chunk) {
           const int owner_slab = chunk * 32 / kOutCols;
           if (owner_slab >= slab_begin && owner_slab < slab_end) continue;
@@ -343,10 +399,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
         __threadfence();
         __syncwarp();
-        if (lane == 0) st_release_gpu_u64(flags + (static_cast<size_t>(item.tail_index) * item.slices + item.slice) * 4 + quarter, nonce);
+        if (lane == 0) st_release_gpu_u64(flags + slot_of(item.slice) * 4 + quarter, nonce);
         for (int other = 0; other < item.slices; ++other) {
           if (other == item.slice) continue;
-          if (!wait_flag_u64(flags + (static_cast<size_t>(item.tail_index) * item.slices + other) * 4 + quarter, nonce, abort_flag)) {
+          if (!wait_flag_u64(flags + slot_of(other) * 4 + quarter, nonce, abort_flag)) {
             report_status(status, kStatusEpilogueWait);
             *abort_flag = 1;
             epilogue_ok = false;
@@ -358,7 +414,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       auto add_partials = [&](uint32_t (&v)[32], int first_col) {
         for (int other = 0; other < item.slices; ++other) {
           if (other == item.slice) continue;
-          const uint32_t* src = partials + (static_cast<size_t>(item.tail_index) * item.slices + other) * tile_words +
+          const uint32_t* src = partials + slot_of(other) * tile_words +
                                 static_cast<size_t>(first_col) * G::kBlockM + quarter * 32 + lane;
           uint32_t part[32];
 #pragma unroll
@@ -458,7 +514,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
       }
       tcgen05_fence_before_sync();
-      mbar_arrive(tmem_empty_bar + 8 * acc);
+      if constexpr (kPair) mbar_arrive_cluster(map_to_cta(tmem_empty_bar + 8 * acc, 0));
+      else mbar_arrive(tmem_empty_bar + 8 * acc);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
@@ -477,9 +534,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
     __syncthreads();
   }
+  if constexpr (kPair) cluster_sync_all();  // neither CTA leaves while the peer can still touch its barriers or TMEM
   if (warp == 1) {
     tcgen05_fence_after_sync();
-    tmem_dealloc(tmem_base, G::kTmemColumns);
+    if constexpr (kPair) tmem_dealloc_pair(tmem_base, G::kTmemColumns);
+    else tmem_dealloc(tmem_base, G::kTmemColumns);
   }
 }
 

@@ -313,6 +313,40 @@ bool tail_split_forced_off() {
   return v != nullptr && v[0] == '0';
 }
 
+// How a tcgen05 GEMM launch is laid out on `sms` SMs.  Shared by the launcher and the workspace query.
+struct Tcgen05Plan {
+  bool pair = false;       // CTA pairs on 256x256 tiles, else single CTAs on 128x256 tiles
+  long long tiles = 0;
+  int workers = 0;         // CTAs, or pairs
+  int num_kb = 0;
+  int split = 1;           // K slices per tail tile
+  long long scratch_slots = 0;  // per-CTA partial accumulators the split needs
+};
+
+Tcgen05Plan plan_tcgen05(const VecopsB200Matmul& p, bool int8, size_t out_elem, int sms, int max_pairs) {
+  using G = GemmTc;
+  Tcgen05Plan plan;
+  const size_t elem = int8 ? 1 : 2;
+  plan.num_kb = static_cast<int>((p.k * elem + G::kBlockKBytes - 1) / G::kBlockKBytes);
+  const long long tiles_n = (p.n + G::kBlockN - 1) / G::kBlockN;
+  const long long pair_tiles = ((p.m + 2 * G::kBlockM - 1) / (2 * G::kBlockM)) * tiles_n;
+  // Pairs halve the operand traffic per SM; they pay once the problem fills every pair with a whole 256-row tile.
+  plan.pair = max_pairs > 0 && p.m > G::kBlockM && pair_tiles >= max_pairs;
+  const char* force = getenv("VECOPS_B200_GEMM_PAIR");  // tuning aid: 0 = never, 1 = whenever the device can
+  if (force != nullptr && force[0] == '0') plan.pair = false;
+  if (force != nullptr && force[0] == '1') plan.pair = max_pairs > 0;
+  if (plan.pair) {
+    plan.tiles = pair_tiles;
+    plan.workers = static_cast<int>(pair_tiles < max_pairs ? pair_tiles : max_pairs);
+  } else {
+    plan.tiles = ((p.m + G::kBlockM - 1) / G::kBlockM) * tiles_n;
+    plan.workers = static_cast<int>(plan.tiles < sms ? plan.tiles : sms);
+  }
+  if (!tail_split_forced_off()) plan.split = gemm_tail_split(plan.tiles, plan.workers, plan.num_kb, G::max_split(out_elem));
+  if (plan.split > 1) plan.scratch_slots = (plan.tiles % plan.workers) * plan.split * (plan.pair ? 2 : 1);
+  return plan;
+}
+
 // Where the epilogue's TMA stores go when the output is gathered across GPUs.
 struct GatherTargets {
   int count = 0;                 // 0 = plain GEMM into p.c
@@ -321,6 +355,49 @@ struct GatherTargets {
   int64_t ldc = 0;               // row pitch of the full C, elements
   int64_t col0 = 0;              // first column of this rank's slab
 };
+
+// One-time per device: raise the dynamic shared memory limits of both forms of the kernel.
+template <bool kInt8, typename OutT>
+int32_t prepare_gemm_kernels(int device, VecopsError* error) {
+  static std::atomic<bool> raised[64];
+  if (device < 0 || device >= 64) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "device ordinal out of range");
+  if (raised[device].load()) return VECOPS_STATUS_OK;
+  int32_t rc = raise_smem_limit(gemm_tcgen05_kernel<kInt8, OutT, false>, GemmTc::kSmemBytes, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  rc = raise_smem_limit(gemm_tcgen05_kernel<kInt8, OutT, true>, GemmPair::kSmemBytes, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  raised[device].store(true);
+  return VECOPS_STATUS_OK;
+}
+
+// CTA pairs the device can keep resident at once (0 when it cannot run the pair form).  Asked once per device.
+template <bool kInt8, typename OutT>
+int pair_capacity(int device) {
+  static std::atomic<int> cached[64];
+  if (device < 0 || device >= 64) return 0;
+  int value = cached[device].load();
+  if (value != 0) return value > 0 ? value : 0;
+  VecopsError ignored = {};
+  ignored.struct_size = sizeof ignored;
+  int clusters = 0;
+  if (prepare_gemm_kernels<kInt8, OutT>(device, &ignored) == VECOPS_STATUS_OK) {
+    cudaLaunchConfig_t config = {};
+    cudaLaunchAttribute cluster = {};
+    cluster.id = cudaLaunchAttributeClusterDimension;
+    cluster.val.clusterDim.x = 2;
+    cluster.val.clusterDim.y = 1;
+    cluster.val.clusterDim.z = 1;
+    config.gridDim = dim3(2);
+    config.blockDim = dim3(GemmTc::kThreads);
+    config.dynamicSmemBytes = GemmPair::kSmemBytes;
+    config.attrs = &cluster;
+    config.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_kernel<kInt8, OutT, true>, &config) != cudaSuccess) clusters = 0;
+    cudaGetLastError();
+  }
+  cached[device].store(clusters > 0 ? clusters : -1);
+  return clusters > 0 ? clusters : 0;
+}
 
 template <bool kInt8, typename OutT>
 int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaStream_t stream, VecopsError* error,
@@ -335,11 +412,14 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
                                        : std::is_same<OutT, float>::value       ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                                                                 : CU_TENSOR_MAP_DATA_TYPE_INT32;
   const uint32_t box_k = G::kBlockKBytes / elem;
+  int device = 0;
+  cudaGetDevice(&device);
+  const Tcgen05Plan plan = plan_tcgen05(p, kInt8, sizeof(OutT), dev.prop.multiProcessorCount, pair_capacity<kInt8, OutT>(device));
   CUtensorMap map_a, map_b;
   GemmStoreMaps maps;
   int32_t rc = make_map_2d(&map_a, in_type, elem, p.a, p.k, p.m, p.a_stride_m * elem, box_k, G::kBlockM, error);
   if (rc != VECOPS_STATUS_OK) return rc;
-  rc = make_map_2d(&map_b, in_type, elem, p.b, p.k, p.n, p.b_stride_n * elem, box_k, G::kBlockN, error);
+  rc = make_map_2d(&map_b, in_type, elem, p.b, p.k, p.n, p.b_stride_n * elem, box_k, plan.pair ? GemmPair::kBRows : G::kBlockN, error);
   if (rc != VECOPS_STATUS_OK) return rc;
   bool tma_store;
   int num_dest = 1;
@@ -365,42 +445,66 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
     }
     for (int d = 1; d < GemmStoreMaps::kMax; ++d) maps.map[d] = maps.map[0];
   }
+  const uint32_t mma_m = plan.pair ? 2 * G::kBlockM : G::kBlockM;
   uint32_t idesc;
   if (kInt8) {
     idesc = umma_instr_desc(kUmmaAccS32, p.a_dtype == VECOPS_DTYPE_I8 ? kUmmaS8 : kUmmaU8,
-                            p.b_dtype == VECOPS_DTYPE_I8 ? kUmmaS8 : kUmmaU8, G::kBlockM, G::kBlockN);
+                            p.b_dtype == VECOPS_DTYPE_I8 ? kUmmaS8 : kUmmaU8, mma_m, G::kBlockN);
   } else {
-    idesc = umma_instr_desc(kUmmaAccF32, kUmmaBF16, kUmmaBF16, G::kBlockM, G::kBlockN);
+    idesc = umma_instr_desc(kUmmaAccF32, kUmmaBF16, kUmmaBF16, mma_m, G::kBlockN);
   }
-  auto kernel = gemm_tcgen05_kernel<kInt8, OutT>;
-  static std::atomic<bool> raised[64];
-  int device = 0;
-  cudaGetDevice(&device);
-  if (!raised[device].load()) {
-    rc = raise_smem_limit(kernel, G::kSmemBytes, error);
-    if (rc != VECOPS_STATUS_OK) return rc;
-    raised[device].store(true);
-  }
-  const long long tiles = ((p.m + G::kBlockM - 1) / G::kBlockM) * ((p.n + G::kBlockN - 1) / G::kBlockN);
-  const int grid = static_cast<int>(tiles < dev.prop.multiProcessorCount ? tiles : dev.prop.multiProcessorCount);
+  rc = prepare_gemm_kernels<kInt8, OutT>(device, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
   // Tail tiles are cut along K when the caller supplied the scratch the slices meet in; without it the tail runs whole.
-  const int num_kb = static_cast<int>((p.k * elem + G::kBlockKBytes - 1) / G::kBlockKBytes);
-  int split = tail_split_forced_off() ? 1 : gemm_tail_split(tiles, grid, num_kb, G::max_split(sizeof(OutT)));
+  int split = plan.split;
   uint32_t* partials = nullptr;
   unsigned long long* flags = nullptr;
   if (split > 1) {
-    const long long slices = (tiles % grid) * split;
-    if (p.workspace == nullptr || !aligned16(p.workspace) || p.workspace_size < G::split_scratch_bytes(slices)) {
+    if (p.workspace == nullptr || !aligned16(p.workspace) || p.workspace_size < G::split_scratch_bytes(plan.scratch_slots)) {
       split = 1;
     } else {
       partials = static_cast<uint32_t*>(p.workspace);
-      flags = reinterpret_cast<unsigned long long*>(static_cast<char*>(p.workspace) + G::split_flags_offset(slices));
+      flags = reinterpret_cast<unsigned long long*>(static_cast<char*>(p.workspace) + G::split_flags_offset(plan.scratch_slots));
     }
   }
-  kernel<<<grid, G::kThreads, G::kSmemBytes, stream>>>(map_a, map_b, maps, num_dest, col_offset, static_cast<OutT*>(p.c), p.c_stride_m,
-                                                       static_cast<int>(p.m), static_cast<int>(p.n), static_cast<int>(p.k),
-                                                       kInt8 ? nullptr : p.column_scale, idesc, tma_store ? 1 : 0, split, partials, flags,
-                                                       split > 1 ? fresh_nonce(p.workspace) : 0ull, g_status_host, g_trace);
+  cudaLaunchConfig_t config = {};
+  cudaLaunchAttribute cluster = {};
+  config.blockDim = dim3(G::kThreads);
+  config.stream = stream;
+  if (plan.pair) {
+    config.gridDim = dim3(2 * plan.workers);
+    config.dynamicSmemBytes = GemmPair::kSmemBytes;
+    cluster.id = cudaLaunchAttributeClusterDimension;
+    cluster.val.clusterDim.x = 2;
+    cluster.val.clusterDim.y = 1;
+    cluster.val.clusterDim.z = 1;
+    config.attrs = &cluster;
+    config.numAttrs = 1;
+  } else {
+    config.gridDim = dim3(plan.workers);
+    config.dynamicSmemBytes = G::kSmemBytes;
+  }
+  OutT* c = static_cast<OutT*>(p.c);
+  long long ldc = p.c_stride_m;
+  int m = static_cast<int>(p.m), n = static_cast<int>(p.n), k = static_cast<int>(p.k);
+  const float* scale = kInt8 ? nullptr : p.column_scale;
+  int store_flag = tma_store ? 1 : 0;
+  // Row-tiles that share a sweep over N: as many as keep their rows of A (about 32 MB) in L2 while B streams past.
+  long long group_tiles = G::kGroupBytes / (static_cast<long long>(mma_m) * p.k * static_cast<long long>(elem));
+  int raster_group = static_cast<int>(group_tiles < 4 ? 4 : group_tiles > 32 ? 32 : group_tiles);
+  if (const char* v = getenv("VECOPS_B200_GEMM_GROUP")) {  // tuning aid
+    const int forced = atoi(v);
+    if (forced > 0) raster_group = forced;
+  }
+  unsigned long long nonce = split > 1 ? fresh_nonce(p.workspace) : 0ull;
+  uint32_t* status_word = g_status_host;
+  unsigned long long* trace = g_trace;
+  void* args[] = {&map_a, &map_b, &maps, &num_dest, &col_offset, &c, &ldc, &m, &n, &k, &scale, &idesc, &store_flag,
+                  &raster_group, &split, &partials, &flags, &nonce, &status_word, &trace};
+  const void* entry = plan.pair ? reinterpret_cast<const void*>(gemm_tcgen05_kernel<kInt8, OutT, true>)
+                                : reinterpret_cast<const void*>(gemm_tcgen05_kernel<kInt8, OutT, false>);
+  cudaError_t launched = cudaLaunchKernelExC(&config, entry, args);
+  if (launched != cudaSuccess) return cuda_fail(error, launched, "launch of the tcgen05 GEMM");
   g_launches.fetch_add(1);
   return VECOPS_STATUS_OK;
 }
@@ -518,13 +622,13 @@ uint64_t tcgen05_tail_scratch(const VecopsB200Matmul& p, bool int8) {
     if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && value > 0) sms = value;
   }
   cudaGetLastError();  // a host without a GPU is a legal caller of the query
-  const long long tiles = ((p.m + G::kBlockM - 1) / G::kBlockM) * ((p.n + G::kBlockN - 1) / G::kBlockN);
-  const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  const size_t elem = int8 ? 1 : 2;
   const size_t out = (int8 || p.c_dtype == VECOPS_DTYPE_F32) ? 4 : 2;
-  const int num_kb = static_cast<int>((p.k * elem + G::kBlockKBytes - 1) / G::kBlockKBytes);
-  const int split = gemm_tail_split(tiles, grid, num_kb, G::max_split(out));
-  return split > 1 ? G::split_scratch_bytes((tiles % grid) * split) : 0;
+  // The launcher may find fewer resident pairs than sms / 2 and then lays the work out differently; the answer covers
+  // both layouts (a launch whose scratch is too small for its layout runs its tail whole).
+  const Tcgen05Plan paired = plan_tcgen05(p, int8, out, sms, sms / 2);
+  const Tcgen05Plan single = plan_tcgen05(p, int8, out, sms, 0);
+  const long long slots = paired.scratch_slots > single.scratch_slots ? paired.scratch_slots : single.scratch_slots;
+  return slots > 0 ? G::split_scratch_bytes(slots) : 0;
 }
 
 uint64_t fresh_nonce(const void* salt) {
