@@ -35,7 +35,7 @@ NOMINAL = {"bf16_tflops": 2250.0, "i8_tops": 4500.0, "hbm_gbs": 8000.0, "fp32_tf
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
 # under profiles/ (None until a capture exists for that workload).
-NCU_TRAFFIC_BYTES = {"c2_bf16_4096": None, "c5_bf16_16384x53248x8192": None}
+NCU_TRAFFIC_BYTES = {"c2_bf16_4096": 99.3e6, "c5_bf16_16384x53248x8192": None}
 
 
 def measured_peaks() -> tuple[dict, str]:
@@ -290,32 +290,93 @@ def bridge_invoker():
 
 
 def measure_e2e(w, operands, host_inputs, steps: int, warmup: int, dev) -> dict:
-    """Same step through the operator bridge with pinned host buffers; copies inside the timed region."""
+    """The same step through the operator bridge with pinned host buffers; every step's copies are inside the timed region.
+
+    Two measurements.  `serial`: copy in, run, copy out on one stream, one step after the other (the latency of a step).
+    `pipelined` (the reported value): two operand sets in flight on three streams, so that the host-to-device copy of
+    step i+1 and the device-to-host read of step i-1 overlap step i; still one copy-in and one read-back per step.
+    """
     import torch
-    o = operands[0]
     a0, b0, s0 = host_inputs
     invoke = bridge_invoker()
     host_a = torch.from_numpy(a0).pin_memory()
     host_b_src = b0 if w.b_layout == "nk" else np.ascontiguousarray(b0.T)
     host_b = torch.from_numpy(host_b_src).pin_memory()
-    host_c = torch.empty(o["c"].shape, dtype=o["c"].dtype).pin_memory()
-    dev_a_raw = o["a"].view(torch.int16) if o["a"].dtype == torch.bfloat16 else o["a"]
-    b_storage = o["b"] if w.b_layout == "nk" else o["b"].t()
-    dev_b_raw = b_storage.view(torch.int16) if b_storage.dtype == torch.bfloat16 else b_storage
     host_a_raw = host_a.view(torch.int16) if host_a.dtype == torch.uint16 else host_a
     host_b_raw = host_b.view(torch.int16) if host_b.dtype == torch.uint16 else host_b
-    stream = torch.cuda.current_stream(dev)
 
-    def step(_):
-        dev_a_raw.copy_(host_a_raw, non_blocking=True)
-        dev_b_raw.copy_(host_b_raw, non_blocking=True)
-        invoke(o["a"], o["b"], o["c"], o["scale"], stream)
-        host_c.copy_(o["c"], non_blocking=True)
+    def raw_views(o):
+        a_raw = o["a"].view(torch.int16) if o["a"].dtype == torch.bfloat16 else o["a"]
+        b_storage = o["b"] if w.b_layout == "nk" else o["b"].t()
+        return a_raw, (b_storage.view(torch.int16) if b_storage.dtype == torch.bfloat16 else b_storage)
 
-    ms = time_steps(step, steps, warmup, stream)
+    lanes = []
+    for i in range(2):
+        if i < len(operands):
+            o = operands[i]
+        else:  # the sharded configuration keeps one operand set: give the second lane its own buffers
+            first = operands[0]
+            o = {"a": torch.empty_like(first["a"]), "b": torch.empty_like(first["b"]), "c": torch.empty_like(first["c"]), "scale": first["scale"]}
+        a_raw, b_raw = raw_views(o)
+        lanes.append({"o": o, "a_raw": a_raw, "b_raw": b_raw, "host_c": torch.empty(o["c"].shape, dtype=o["c"].dtype).pin_memory(),
+                      "loaded": torch.cuda.Event(), "computed": torch.cuda.Event(), "read": torch.cuda.Event(), "used": False})
+    main = torch.cuda.current_stream(dev)
+
+    def serial_step(_):
+        lane = lanes[0]
+        lane["a_raw"].copy_(host_a_raw, non_blocking=True)
+        lane["b_raw"].copy_(host_b_raw, non_blocking=True)
+        invoke(lane["o"]["a"], lane["o"]["b"], lane["o"]["c"], lane["o"]["scale"], main)
+        lane["host_c"].copy_(lane["o"]["c"], non_blocking=True)
+
+    serial_ms = time_steps(serial_step, steps, warmup, main)
+
+    copy_in, compute, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def pipelined_step(i):
+        lane = lanes[i % 2]
+        with torch.cuda.stream(copy_in):
+            if lane["used"]:
+                copy_in.wait_event(lane["computed"])  # the lane's previous run has read its A and B
+            lane["a_raw"].copy_(host_a_raw, non_blocking=True)
+            lane["b_raw"].copy_(host_b_raw, non_blocking=True)
+            lane["loaded"].record(copy_in)
+        compute.wait_event(lane["loaded"])
+        if lane["used"]:
+            compute.wait_event(lane["read"])  # the lane's previous C has reached the host
+        invoke(lane["o"]["a"], lane["o"]["b"], lane["o"]["c"], lane["o"]["scale"], compute)
+        lane["computed"].record(compute)
+        with torch.cuda.stream(copy_out):
+            copy_out.wait_event(lane["computed"])
+            lane["host_c"].copy_(lane["o"]["c"], non_blocking=True)
+            lane["read"].record(copy_out)
+        lane["used"] = True
+
+    def drain():
+        for side in (copy_in, compute, copy_out):
+            main.wait_stream(side)
+
+    for i in range(warmup):
+        pipelined_step(i)
+    drain()
+    torch.cuda.synchronize(dev)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(main)
+    for side in (copy_in, compute, copy_out):
+        side.wait_event(start)
+    for i in range(steps):
+        pipelined_step(warmup + i)
+    drain()
+    stop.record(main)
+    torch.cuda.synchronize(dev)
+    pipelined_ms = start.elapsed_time(stop) / steps
+    # the read-back is the product's result: compare what reached the host with the device copy
+    last = lanes[(warmup + steps - 1) % 2]
+    if not torch.equal(last["host_c"], last["o"]["c"].cpu()):
+        raise RuntimeError("end-to-end read-back differs from the device result")
     h2d = host_a.numel() * host_a.element_size() + host_b.numel() * host_b.element_size()
-    d2h = host_c.numel() * host_c.element_size()
-    return {"ms_per_step": ms, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)}
+    d2h = lanes[0]["host_c"].numel() * lanes[0]["host_c"].element_size()
+    return {"ms_per_step": pipelined_ms, "serial_ms_per_step": serial_ms, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)}
 
 
 def cpu_baseline(w, steps: int = 3) -> dict:
@@ -518,6 +579,8 @@ def run_ours(args) -> None:
                      "algorithmic_flops_per_launch": local_flops, "algorithmic_bytes_per_launch": 2 * (w.m * w.k + o["b"].shape[0] * w.k + w.m * o["b"].shape[0])},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
                 "d2h_bytes_per_step": e2e["d2h_bytes_per_step"], "ms_per_step": float(e2e_ms.item()), "steps": e2e_steps,
+                "serial_ms_per_step": e2e["serial_ms_per_step"], "serial_value": w.flops / (e2e["serial_ms_per_step"] * 1e-3) / 1e12,
+                "pipelining": "two operand sets in flight on copy-in / compute / read-back streams; serial_* is one step at a time on one stream",
                 "path": "vecops_operator_bridge_invoke_v1 (Operator -> MatmulRuntimeDispatch -> CudaExecutableProvider -> descriptor.run), pinned host buffers"},
         "gpu_launches": int(launches), "launches_per_step": launches_per_step, "clocks": clocks.summary(),
         "parity": parity, "device_status": status,
