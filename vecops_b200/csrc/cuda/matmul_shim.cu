@@ -23,6 +23,7 @@
 #include "w8_small_m.cuh"
 #include "w8_stream.cuh"
 #include "w8_tcgen05.cuh"
+#include "w8_mixed_tcgen05.cuh"
 #include "shim_util.h"
 
 namespace vb200 {
@@ -172,13 +173,17 @@ bool applicable(const VecopsB200Matmul& p, Row row, uint32_t kernel) {
       return row == Row::W8 && p.m >= 1 && p.m <= W8Tc::kMaxM && p.a_stride_k == 1 && p.b_stride_k == 1 && p.c_stride_n == 1 &&
              p.k > 0 && p.k % 8 == 0 && aligned16(p.a) && aligned16(p.b) && p.a_stride_m % 8 == 0 && p.b_stride_n % 16 == 0 &&
              p.a_stride_m >= p.k && p.b_stride_n >= p.k && p.n < (INT64_C(1) << 31) && p.k < (INT64_C(1) << 31);
+    case VECOPS_B200_KERNEL_W8_MIXED_TCGEN05:
+      return row == Row::W8 && p.m >= 1 && p.m <= W8Mix::kMaxM && p.a_stride_k == 1 && p.b_stride_k == 1 && p.c_stride_n == 1 &&
+             p.k > 0 && p.k % 16 == 0 && aligned16(p.a) && aligned16(p.b) && p.a_stride_m % 8 == 0 && p.b_stride_n % 16 == 0 &&
+             p.a_stride_m >= p.k && p.b_stride_n >= p.k && p.n < (INT64_C(1) << 31) && p.k < (INT64_C(1) << 31);
     default:
       return false;
   }
 }
 
 const char* const kKernelNames[VECOPS_B200_KERNEL_COUNT_] = {
-    "auto", "generic", "f32_simt", "bf16_tcgen05", "i8_tcgen05", "w8_small_m", "w8_tcgen05"};
+    "auto", "generic", "f32_simt", "bf16_tcgen05", "i8_tcgen05", "w8_small_m", "w8_tcgen05", "w8_mixed_tcgen05"};
 
 uint32_t forced_by_environment() {
   const char* text = getenv("VECOPS_B200_FORCE_KERNEL");
@@ -306,6 +311,25 @@ int32_t raise_smem_limit(Kernel kernel, int bytes, VecopsError* error) {
 }
 
 uint64_t fresh_nonce(const void* salt);
+
+// Clusters of two CTAs of `kernel` the current device keeps resident at once; 0 when it cannot run them.
+int cluster_capacity(const void* kernel, int threads, size_t smem_bytes) {
+  cudaLaunchConfig_t config = {};
+  cudaLaunchAttribute cluster = {};
+  cluster.id = cudaLaunchAttributeClusterDimension;
+  cluster.val.clusterDim.x = 2;
+  cluster.val.clusterDim.y = 1;
+  cluster.val.clusterDim.z = 1;
+  config.gridDim = dim3(2);
+  config.blockDim = dim3(threads);
+  config.dynamicSmemBytes = smem_bytes;
+  config.attrs = &cluster;
+  config.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) clusters = 0;
+  cudaGetLastError();
+  return clusters;
+}
 
 // Tuning aid: VECOPS_B200_TAIL_SPLIT=0 keeps tail tiles whole.
 bool tail_split_forced_off() {
@@ -661,7 +685,33 @@ int32_t launch_w8_tcgen05_typed(const VecopsB200Matmul& p, const DeviceState& de
   float* inv_scales = reinterpret_cast<float*>(scratch + G::scales_offset(mpad));
   __half* act16 = reinterpret_cast<__half*>(scratch + G::act_offset(mpad));
   const long long act_pitch = G::act_pitch(p.k);
-  rc = make_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act16, p.k, p.m, act_pitch * 2, 64, mpad, error);
+  // CTA pairs: 256-row weight tiles, one MMA for both CTAs.
+  auto pair_kernel = w8_tcgen05_kernel<OutT, true>;
+  auto single_kernel = w8_tcgen05_kernel<OutT, false>;
+  static_assert(G::smem_bytes(G::kMaxM) <= 227 * 1024 && G::smem_bytes(16) <= 227 * 1024, "w8_tcgen05 shared memory budget");
+  int device = 0;
+  cudaGetDevice(&device);
+  static std::atomic<bool> raised[64];
+  if (device < 0 || device >= 64 || !raised[device].load()) {
+    rc = raise_smem_limit(single_kernel, 227 * 1024, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+    rc = raise_smem_limit(pair_kernel, 227 * 1024, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+    if (device >= 0 && device < 64) raised[device].store(true);
+  }
+  static std::atomic<int> pair_cache[64];
+  int pairs = device >= 0 && device < 64 ? pair_cache[device].load() : -1;
+  if (pairs == 0) {
+    pairs = cluster_capacity(reinterpret_cast<const void*>(pair_kernel), G::kThreads, G::smem_bytes(G::kMaxM));
+    if (device >= 0 && device < 64) pair_cache[device].store(pairs > 0 ? pairs : -1);
+  }
+  if (pairs < 0) pairs = 0;
+  if (pairs > G::kMaxGrid / 2) pairs = G::kMaxGrid / 2;
+  // Measured slower than single CTAs (36 vs 41 us at M = 128): each issuing thread still runs the same number of
+  // MMAs, and every hand-off crosses SMs.  Kept as an option for tuning (VECOPS_B200_W8TC_PAIR=1).
+  bool pair = false;
+  if (const char* v = getenv("VECOPS_B200_W8TC_PAIR")) pair = v[0] == '1' && pairs > 0;
+  rc = make_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act16, p.k, p.m, act_pitch * 2, 64, pair ? mpad / 2 : mpad, error);
   if (rc != VECOPS_STATUS_OK) return rc;
   const char* skip = getenv("VECOPS_B200_W8TC_SKIP_PREPARE");  // timing experiments only: reuse the scratch's previous copy
   if (skip == nullptr || skip[0] != '1') {
@@ -669,19 +719,78 @@ int32_t launch_w8_tcgen05_typed(const VecopsB200Matmul& p, const DeviceState& de
         static_cast<const __nv_bfloat16*>(p.a), p.a_stride_m, act16, act_pitch, inv_scales, static_cast<int>(p.k));
     g_launches.fetch_add(1);
   }
-  const char* flavour = getenv("VECOPS_B200_W8TC_PREFETCH");
-  auto kernel = (flavour != nullptr && flavour[0] == '0') ? w8_tcgen05_kernel<OutT, false> : w8_tcgen05_kernel<OutT, true>;
-  static_assert(G::smem_bytes(G::kMaxM) <= 227 * 1024 && G::smem_bytes(16) <= 227 * 1024, "w8_tcgen05 shared memory budget");
-  rc = raise_smem_limit(kernel, 227 * 1024, error);
+  const int tile_rows = pair ? 2 * G::kTileN : G::kTileN;
+  const long long units = ((p.n + tile_rows - 1) / tile_rows) * ((p.k + G::kBlockK - 1) / G::kBlockK);
+  long long workers = pair ? pairs : (dev.prop.multiProcessorCount < G::kMaxGrid ? dev.prop.multiProcessorCount : G::kMaxGrid);
+  if (units < workers) workers = units;
+  // A = f16 (the widened weights, from tensor memory), B = f16 (the scaled activations), fp32 accumulate
+  uint32_t idesc = umma_instr_desc(kUmmaAccF32, kUmmaF16, kUmmaF16, tile_rows, mpad);
+  cudaLaunchConfig_t config = {};
+  cudaLaunchAttribute cluster = {};
+  config.blockDim = dim3(G::kThreads);
+  config.dynamicSmemBytes = G::smem_bytes(mpad);
+  config.stream = stream;
+  config.gridDim = dim3(static_cast<unsigned>(pair ? 2 * workers : workers));
+  if (pair) {
+    cluster.id = cudaLaunchAttributeClusterDimension;
+    cluster.val.clusterDim.x = 2;
+    cluster.val.clusterDim.y = 1;
+    cluster.val.clusterDim.z = 1;
+    config.attrs = &cluster;
+    config.numAttrs = 1;
+  }
+  const float* scale = p.column_scale;
+  OutT* c = static_cast<OutT*>(p.c);
+  long long ldc = p.c_stride_m;
+  int m = static_cast<int>(p.m), n = static_cast<int>(p.n), k = static_cast<int>(p.k), mpad_arg = mpad;
+  const float* inv = inv_scales;
+  unsigned long long nonce = fresh_nonce(p.workspace);
+  uint32_t* status_word = g_status_host;
+  unsigned long long* trace = g_trace;
+  void* args[] = {&map_w, &map_a, &scale, &c, &ldc, &m, &n, &k, &mpad_arg, &partials, &flags, &inv, &nonce, &idesc, &status_word, &trace};
+  cudaError_t launched = cudaLaunchKernelExC(&config, pair ? reinterpret_cast<const void*>(pair_kernel) : reinterpret_cast<const void*>(single_kernel), args);
+  if (launched != cudaSuccess) return cuda_fail(error, launched, "launch of w8_tcgen05");
+  g_launches.fetch_add(1);
+  return VECOPS_STATUS_OK;
+}
+
+template <typename OutT>
+int32_t launch_w8_mixed_typed(const VecopsB200Matmul& p, const DeviceState& dev, cudaStream_t stream, VecopsError* error) {
+  using G = W8Mix;
+  if (dev.prop.major != 10)
+    return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "tcgen05 kernels need an sm_100 device, found sm_%d%d", dev.prop.major,
+                     dev.prop.minor);
+  const int m = static_cast<int>(p.m);
+  const uint64_t need = G::scratch_bytes(m);
+  if (p.workspace == nullptr || p.workspace_size < need)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "w8_mixed_tcgen05 needs %llu bytes of device workspace, %llu were supplied",
+                     (unsigned long long)need, (unsigned long long)p.workspace_size);
+  if (!aligned16(p.workspace)) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "workspace must be 16-byte aligned");
+  CUtensorMap map_w, map_a;
+  int32_t rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.b, p.k, p.n, p.b_stride_n, G::kUnitK, G::kTileN, error);
   if (rc != VECOPS_STATUS_OK) return rc;
-  const long long units = ((p.n + G::kTileN - 1) / G::kTileN) * ((p.k + G::kBlockK - 1) / G::kBlockK);
+  rc = make_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.a, p.k, p.m, p.a_stride_m * 2, G::kStepK, G::act_rows(m), error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  auto kernel = w8_mixed_tcgen05_kernel<OutT>;
+  int device = 0;
+  cudaGetDevice(&device);
+  static std::atomic<bool> raised[64];
+  if (device < 0 || device >= 64 || !raised[device].load()) {
+    rc = raise_smem_limit(kernel, 227 * 1024, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+    if (device >= 0 && device < 64) raised[device].store(true);
+  }
+  char* scratch = static_cast<char*>(p.workspace);
+  float* partials = reinterpret_cast<float*>(scratch);
+  auto* flags = reinterpret_cast<unsigned long long*>(scratch + G::flags_offset(m));
+  const long long units = ((p.n + G::kTileN - 1) / G::kTileN) * ((p.k + G::kUnitK - 1) / G::kUnitK);
   long long grid = dev.prop.multiProcessorCount < G::kMaxGrid ? dev.prop.multiProcessorCount : G::kMaxGrid;
   if (units < grid) grid = units;
-  // A = f16 (the widened weights, from tensor memory), B = f16 (the scaled activations), fp32 accumulate
-  const uint32_t idesc = umma_instr_desc(kUmmaAccF32, kUmmaF16, kUmmaF16, G::kTileN, mpad);
-  kernel<<<static_cast<int>(grid), G::kThreads, G::smem_bytes(mpad), stream>>>(
-      map_w, map_a, p.column_scale, static_cast<OutT*>(p.c), p.c_stride_m, static_cast<int>(p.m), static_cast<int>(p.n),
-      static_cast<int>(p.k), mpad, partials, flags, inv_scales, fresh_nonce(p.workspace), idesc, g_status_host, g_trace);
+  // A = bf16 activations, B = the widened bf16 weights, both K-major in shared memory; fp32 accumulate
+  const uint32_t idesc = umma_instr_desc(kUmmaAccF32, kUmmaBF16, kUmmaBF16, 128, G::kTileN);
+  kernel<<<static_cast<int>(grid), G::kThreads, G::smem_bytes(m), stream>>>(
+      map_w, map_a, p.column_scale, static_cast<OutT*>(p.c), p.c_stride_m, m, static_cast<int>(p.n), static_cast<int>(p.k), partials,
+      flags, fresh_nonce(p.workspace), idesc, g_status_host, g_trace);
   g_launches.fetch_add(1);
   return VECOPS_STATUS_OK;
 }
@@ -724,6 +833,8 @@ int32_t vecops_b200_matmul_workspace(const VecopsB200Matmul* problem, uint64_t* 
   *bytes = 0;
   if (kernel == VECOPS_B200_KERNEL_W8_TCGEN05) {
     *bytes = W8Tc::scratch_bytes(static_cast<int>(problem->m), problem->k);
+  } else if (kernel == VECOPS_B200_KERNEL_W8_MIXED_TCGEN05) {
+    *bytes = W8Mix::scratch_bytes(static_cast<int>(problem->m));
   } else if (kernel == VECOPS_B200_KERNEL_BF16_TCGEN05 || kernel == VECOPS_B200_KERNEL_I8_TCGEN05) {
     *bytes = tcgen05_tail_scratch(*problem, kernel == VECOPS_B200_KERNEL_I8_TCGEN05);
   }
@@ -777,6 +888,10 @@ int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* err
         case VECOPS_B200_KERNEL_W8_TCGEN05:
           rc = p.c_dtype == VECOPS_DTYPE_BF16 ? launch_w8_tcgen05_typed<__nv_bfloat16>(p, *dev, stream, error)
                                               : launch_w8_tcgen05_typed<float>(p, *dev, stream, error);
+          break;
+        case VECOPS_B200_KERNEL_W8_MIXED_TCGEN05:
+          rc = p.c_dtype == VECOPS_DTYPE_BF16 ? launch_w8_mixed_typed<__nv_bfloat16>(p, *dev, stream, error)
+                                              : launch_w8_mixed_typed<float>(p, *dev, stream, error);
           break;
         default: rc = set_error(error, VECOPS_STATUS_INTERNAL_ERROR, "kernel id %u has no launcher", kernel);
       }

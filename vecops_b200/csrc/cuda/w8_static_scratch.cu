@@ -76,8 +76,8 @@ int32_t set_up(int device, const PerDevice** out, VecopsError* error) {
     if (status != cudaSuccess) return cuda_error(error, status, "cudaDeviceGetAttribute(SM count)");
     status = cudaDeviceGetAttribute(&state.sm_major, cudaDevAttrComputeCapabilityMajor, device);
     if (status != cudaSuccess) return cuda_error(error, status, "cudaDeviceGetAttribute(compute capability)");
-    for (auto kernel : {reinterpret_cast<const void*>(w8_tcgen05_kernel<__nv_bfloat16, true>),
-                        reinterpret_cast<const void*>(w8_tcgen05_kernel<float, true>)}) {
+    for (auto kernel : {reinterpret_cast<const void*>(w8_tcgen05_kernel<__nv_bfloat16, false>),
+                        reinterpret_cast<const void*>(w8_tcgen05_kernel<float, false>)}) {
       status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
       if (status != cudaSuccess) return cuda_error(error, status, "cudaFuncSetAttribute(max dynamic shared memory)");
     }
@@ -129,7 +129,7 @@ void launch(const VecopsB200Matmul& p, const PerDevice& dev, int mpad, const CUt
   long long grid = dev.sm_count < G::kMaxGrid ? dev.sm_count : G::kMaxGrid;
   if (units < grid) grid = units;
   const uint32_t idesc = umma_instr_desc(kUmmaAccF32, kUmmaF16, kUmmaF16, G::kTileN, mpad);
-  w8_tcgen05_kernel<OutT, true><<<static_cast<int>(grid), G::kThreads, G::smem_bytes(mpad), stream>>>(
+  w8_tcgen05_kernel<OutT, false><<<static_cast<int>(grid), G::kThreads, G::smem_bytes(mpad), stream>>>(
       map_w, map_a, p.column_scale, static_cast<OutT*>(p.c), p.c_stride_m, static_cast<int>(p.m), static_cast<int>(p.n),
       static_cast<int>(p.k), mpad, partials, flags, inv_scales, next_nonce(), idesc, dev.status, nullptr);
 }

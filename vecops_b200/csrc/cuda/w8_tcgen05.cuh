@@ -32,6 +32,15 @@
 //
 // Warps: 0 TMA producer | 1 MMA issuer + TMEM owner | 4-7 epilogue | 8-23 widening (two groups, alternate units).
 //
+// CTA pairs (kPair): the thread that issues tcgen05 work, not HBM, sets the pace of the single-CTA form (about 70
+// cycles per MMA, eight MMAs per 16 KB of weights).  Two CTAs of a cluster therefore share 256-row weight tiles: each
+// streams and widens its own 128 rows into its own TMEM and holds half of the activation rows in shared memory, and
+// the leader issues ONE tcgen05.mma.cta_group::2 (M = 256) where the single form needs two - half the issue work per
+// byte of weights.  Barriers follow the dense GEMM's pair form: both CTAs' activation loads count on the leader's
+// `act_full`, both CTAs' widening warps arrive on the leader's `a_full`, the leader's commits arrive on `a_empty`,
+// `act_empty` and `d_full` of both CTAs, both epilogues arrive on the leader's `d_empty`.  Stream-K ranges are per
+// pair; each CTA exchanges partial sums with the CTA of the same rank in the neighbouring pairs.
+//
 // Algorithmic traffic per launch: N*K + 4*N + 2*M*K + sizeof(C)*M*N bytes.
 #pragma once
 
@@ -49,9 +58,17 @@ struct W8Tc {
   static constexpr int kRawStages = 8;      // int8 weight tiles in flight (two batches)
   static constexpr int kRawBytes = kTileN * kBlockK;
   static constexpr int kMaxActStages = 6;
-  static constexpr int kAStages = 4;        // widened weight tiles in TMEM
+  static constexpr int kMaxAStages = 6;     // widened weight tiles in TMEM (as many as the accumulators leave room for)
   static constexpr int kAColumns = kBlockK / 2;  // two fp16 per 32-bit TMEM column
-  static constexpr int kDColumns = 128;
+  // TMEM: two accumulators of d_columns each, then the ring of widened weight tiles
+  __host__ __device__ static constexpr int d_columns(int mpad) { return mpad <= 32 ? 32 : mpad <= 64 ? 64 : 128; }
+  __host__ __device__ static constexpr int a_stages(int mpad) {
+    const int fit = (512 - 2 * d_columns(mpad)) / (kBlockK / 2);
+    return fit < kMaxAStages ? fit : kMaxAStages;
+  }
+  // k-blocks per activation stage: few activation rows make small k-blocks, and one barrier round trip per
+  // k-block costs the MMA thread more than the MMAs themselves
+  __host__ __device__ static constexpr int act_kblocks(int mpad) { return mpad <= 16 ? 4 : mpad <= 32 ? 2 : 1; }
   static constexpr int kTmemColumns = 512;  // D0 | D1 | A ring
   static constexpr int kDequantWarps = 8;    // per group: 4 lane quarters x 2 k-halves of one unit
   static constexpr int kDequantGroups = 2;   // groups take alternate units: widening one unit has a long latency
@@ -59,7 +76,7 @@ struct W8Tc {
   static constexpr int kTailParts = 1 + 2 * kDequantGroups;  // warps per lane quarter that share a final combine
   static constexpr int kMaxGrid = 160;      // scratch is sized for this many CTAs
   __host__ __device__ static constexpr int m_padded(int m) { return (m + 15) & ~15; }
-  __host__ __device__ static constexpr int act_stage_bytes(int mpad) { return 2 * mpad * 128; }
+  __host__ __device__ static constexpr int act_stage_bytes(int mpad) { return act_kblocks(mpad) * 2 * mpad * 128; }
   // as many activation stages as fit beside the weight ring (32 KB each at M = 128, 4 KB at M <= 16)
   __host__ __device__ static constexpr int act_stages(int mpad) {
     const int fit = (200 * 1024 - kRawStages * kRawBytes) / act_stage_bytes(mpad);
@@ -102,6 +119,19 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
       ".reg .pred p;\n"
       "setp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// The same for a CTA pair: each CTA's 128 rows of A come from its own TMEM, each holds half of B's rows.
+__device__ __forceinline__ void umma_f16_ts_pair(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n"
       "}\n" ::"r"(tmem_d),
       "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
@@ -258,7 +288,7 @@ __device__ __forceinline__ bool w8tc_segment(long long total_units, int grid, in
   }
 }
 
-template <typename OutT, bool kPrefetch>
+template <typename OutT, bool kPair>
 __global__ void __launch_bounds__(W8Tc::kThreads, 1)
 w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_a,
                   const float* __restrict__ scale, OutT* __restrict__ c, long long ldc, int M, int N, int K, int mpad,
@@ -269,8 +299,15 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const int act_stage = G::act_stage_bytes(mpad);
+  constexpr int kTileRows = kPair ? 2 * G::kTileN : G::kTileN;  // weight rows a worker (CTA or pair) covers per tile
+  const uint32_t pair_rank = kPair ? cluster_cta_rank() : 0u;
+  const int act_rows = kPair ? mpad / 2 : mpad;                  // activation rows this CTA keeps in shared memory
+  const int act_kb_bytes = 2 * act_rows * 128;                   // one k-block: two 64-wide swizzle atoms
+  const int act_kblocks = G::act_kblocks(mpad);                  // k-blocks per activation stage
+  const int act_stage = act_kblocks * act_kb_bytes;
   const int act_stages = G::act_stages(mpad);
+  const int a_stages = G::a_stages(mpad);
+  const int d_columns = G::d_columns(mpad);
   const uint32_t raw_base = smem_base;
   const uint32_t act_base = smem_base + G::kRawStages * G::kRawBytes;
   const int bar_offset = G::kRawStages * G::kRawBytes + act_stages * act_stage;
@@ -280,7 +317,7 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
   auto take = [&](int count) { const uint32_t at = next_bar; next_bar += 8 * count; return at; };
   const uint32_t raw_full = take(G::kRawStages), raw_empty = take(G::kRawStages);
   const uint32_t act_full = take(G::kMaxActStages), act_empty = take(G::kMaxActStages);
-  const uint32_t a_full = take(G::kAStages), a_empty = take(G::kAStages);
+  const uint32_t a_full = take(G::kMaxAStages), a_empty = take(G::kMaxAStages);
   const uint32_t d_full = take(2), d_empty = take(2);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_gen + (next_bar - bar_base));
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bar_gen + (next_bar - bar_base) + 4);
@@ -289,10 +326,12 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int kblocks = (K + G::kBlockK - 1) / G::kBlockK;
-  const int tiles = (N + G::kTileN - 1) / G::kTileN;
+  const int tiles = (N + kTileRows - 1) / kTileRows;
   const long long total_units = static_cast<long long>(tiles) * kblocks;
-  const int grid = gridDim.x;
-  const int cta = blockIdx.x;
+  // `cta` of `grid` counts workers (CTAs, or pairs); scratch slots are per CTA
+  const int grid = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int cta = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  auto slot_of = [&](int worker) { return kPair ? 2 * worker + static_cast<int>(pair_rank) : worker; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < G::kRawStages; ++s) {
@@ -304,13 +343,13 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
       mbar_init(act_full + 8 * s, 1);
       mbar_init(act_empty + 8 * s, 1);
     }
-    for (int s = 0; s < G::kAStages; ++s) {
-      mbar_init(a_full + 8 * s, G::kDequantWarps);
+    for (int s = 0; s < G::kMaxAStages; ++s) {
+      mbar_init(a_full + 8 * s, G::kDequantWarps * (kPair ? 2 : 1));  // the leader's collects both CTAs' widening warps
       mbar_init(a_empty + 8 * s, 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(d_full + 8 * s, 1);
-      mbar_init(d_empty + 8 * s, 4);
+      mbar_init(d_empty + 8 * s, 4 * (kPair ? 2 : 1));
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -318,17 +357,23 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
     tma_prefetch_descriptor(&tma_a);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), G::kTmemColumns);
-    tmem_relinquish();
+    if constexpr (kPair) {
+      tmem_alloc_pair(smem_u32(tmem_slot), G::kTmemColumns);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), G::kTmemColumns);
+      tmem_relinquish();
+    }
   }
   if (warp == 2) {
     for (int m = lane; m < G::kMaxM; m += 32) inv_scale_smem[m] = m < M ? __ldg(inv_row_scale + m) : 0.f;
   }
   tcgen05_fence_before_sync();
   __syncthreads();
+  if constexpr (kPair) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_a_base = tmem_base + 2 * G::kDColumns;
+  const uint32_t tmem_a_base = tmem_base + 2 * d_columns;
 
   // optional timeline (nanoseconds) for tuning: 16 slots per CTA, written only when a trace buffer is given
   auto mark = [&](int slot) {
@@ -351,9 +396,9 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
   auto finish = [&](const W8TcSegment& seg, int buf, int part, int parts) -> bool {
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;  // weight row inside the tile = TMEM lane
-    const int n = seg.tile * G::kTileN + row;
+    const int n = seg.tile * kTileRows + static_cast<int>(pair_rank) * G::kTileN + row;
     const float s = (scale != nullptr && n < N) ? __ldg(scale + n) : 1.f;
-    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * G::kDColumns;
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * d_columns;
     // contributors: the CTAs after this one whose ranges begin inside this tile (they published early)
     int last_contributor = cta;
     if (seg.has_contributors) {
@@ -361,7 +406,7 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
       while (last_contributor + 1 < grid && w8tc_range_begin(total_units, grid, last_contributor + 1) < tile_end_unit) ++last_contributor;
       // a warp only needs its own 32 rows of each partner, published by the partner's warp of the same quarter
       for (int other = cta + 1; other <= last_contributor; ++other)
-        if (!wait_flag(flags + 4 * other + quarter, nonce, abort_flag)) return false;
+        if (!wait_flag(flags + 4 * slot_of(other) + quarter, nonce, abort_flag)) return false;
     }
     for (int col0 = 16 * part; col0 < mpad && col0 < M; col0 += 16 * parts) {
       uint32_t v[16];
@@ -378,7 +423,7 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
         for (int other = cta + 1; other <= last_contributor || first_pass; ++other) {
           float part_sum[16];
           const bool has = other <= last_contributor;
-          const float* src = partials + static_cast<long long>(other) * mpad * G::kTileN + col0 * G::kTileN + row;
+          const float* src = partials + static_cast<long long>(slot_of(other)) * mpad * G::kTileN + col0 * G::kTileN + row;
 #pragma unroll
           for (int j = 0; j < 16; ++j) part_sum[j] = (has && col0 + j < M) ? __ldcg(src + j * G::kTileN) : 0.f;
           if (first_pass) {
@@ -403,7 +448,7 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
         }
       } else {
         tmem_load_wait();
-        float* dst = partials + static_cast<long long>(cta) * mpad * G::kTileN + col0 * G::kTileN + row;
+        float* dst = partials + static_cast<long long>(slot_of(cta)) * mpad * G::kTileN + col0 * G::kTileN + row;
 #pragma unroll
         for (int j = 0; j < 16; ++j)
           if (col0 + j < M) __stcg(dst + j * G::kTileN, __uint_as_float(v[j]));
@@ -412,7 +457,7 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
     if (!seg.owner) {
       __threadfence();
       __syncwarp();
-      if (lane == 0) st_release_u64(flags + 4 * cta + quarter, nonce);
+      if (lane == 0) st_release_u64(flags + 4 * slot_of(cta) + quarter, nonce);
     }
     return true;
   };
@@ -436,20 +481,42 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
             const long long u = begin + raw_issued;
             const int tile = static_cast<int>(u / kblocks), kb = static_cast<int>(u % kblocks);
             mbar_arrive_expect_tx(raw_full + 8 * (rs + b), G::kRawBytes);
-            tma_load_2d(raw_base + (rs + b) * G::kRawBytes, &tma_w, raw_full + 8 * (rs + b), kb * G::kBlockK, tile * G::kTileN);
+            tma_load_2d(raw_base + (rs + b) * G::kRawBytes, &tma_w, raw_full + 8 * (rs + b), kb * G::kBlockK,
+                        tile * kTileRows + static_cast<int>(pair_rank) * G::kTileN);
           }
           rs += G::kRawBatch;
           if (rs == G::kRawStages) { rs = 0; rphase ^= 1u; }
           progress = true;
         }
         if (act_issued < my_units && mbar_test_wait(act_empty + 8 * as, aphase ^ 1u)) {
+          // one stage = the aligned group of act_kblocks k-blocks that holds this unit's; the units of the group
+          // that follow in this CTA's range share it
           const int kb = static_cast<int>((begin + act_issued) % kblocks);
-          mbar_arrive_expect_tx(act_full + 8 * as, static_cast<uint32_t>(act_stage));
+          const int first_kb = kb - kb % act_kblocks;
           const uint32_t act_dst = act_base + as * act_stage;
-          tma_load_2d(act_dst, &tma_a, act_full + 8 * as, kb * G::kBlockK, 0);
-          tma_load_2d(act_dst + mpad * 128, &tma_a, act_full + 8 * as, kb * G::kBlockK + 64, 0);
+          const int first_row = kPair ? static_cast<int>(pair_rank) * act_rows : 0;
+          uint32_t bar = act_full + 8 * as;
+          if constexpr (kPair) {
+            // each CTA brings its half of the activation rows; the bytes of both are counted on the leader's barrier
+            if (pair_rank == 0) mbar_arrive_expect_tx(act_full + 8 * as, 2u * static_cast<uint32_t>(act_stage));
+            bar = map_to_cta(bar, 0);
+          } else {
+            mbar_arrive_expect_tx(act_full + 8 * as, static_cast<uint32_t>(act_stage));
+          }
+          for (int j = 0; j < act_kblocks; ++j) {
+            const uint32_t dst = act_dst + j * act_kb_bytes;
+            const int k0 = (first_kb + j) * G::kBlockK;  // past K: zero-filled by TMA
+            if constexpr (kPair) {
+              tma_load_2d_pair(dst, &tma_a, bar, k0, first_row);
+              tma_load_2d_pair(dst + act_rows * 128, &tma_a, bar, k0 + 64, first_row);
+            } else {
+              tma_load_2d(dst, &tma_a, bar, k0, first_row);
+              tma_load_2d(dst + act_rows * 128, &tma_a, bar, k0 + 64, first_row);
+            }
+          }
           if (++as == act_stages) { as = 0; aphase ^= 1u; }
-          ++act_issued;
+          // the rest of the group, which ends with the tile at the latest (may run past my_units: the loop ends)
+          act_issued += min(act_kblocks - kb % act_kblocks, kblocks - kb);
           progress = true;
         }
         if (!progress && (*abort_flag != 0 || clock64() - started > 4 * kWaitCycleBudget)) {
@@ -460,47 +527,86 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
       mark(2);
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer (one thread)
-    if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer (one thread; of a pair, the leader's)
+    if (lane == 0 && pair_rank == 0) {
       int as = 0, ai = 0;
       uint32_t aphase = 0, iphase = 0;
       uint32_t dphase[2] = {0, 0};
       W8TcSegment seg;
       bool ok = true;
+      bool first_unit = true;
+      const bool tracing = trace != nullptr;
+      long long spent[5] = {0, 0, 0, 0, 0};  // tuning aid: cycles waiting for widened weights | for activations | issuing MMAs | committing; units
+      const long long loop_start = tracing ? clock64() : 0;
       for (int si = 0; ok && w8tc_segment(total_units, grid, cta, kblocks, si, seg); ++si) {
         const int buf = si & 1;
-        if (!mbar_wait(d_empty + 8 * buf, dphase[buf] ^ 1u, abort_flag)) {
+        if (!(kPair ? mbar_wait_cluster(d_empty + 8 * buf, dphase[buf] ^ 1u, abort_flag)
+                    : mbar_wait(d_empty + 8 * buf, dphase[buf] ^ 1u, abort_flag))) {
           give_up(kStatusMmaWaitTmem);
           break;
         }
         tcgen05_fence_after_sync();
-        const uint32_t tmem_d = tmem_base + buf * G::kDColumns;
+        const uint32_t tmem_d = tmem_base + buf * d_columns;
         for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb) {
-          if (!mbar_wait(a_full + 8 * ai, iphase, abort_flag) || !mbar_wait(act_full + 8 * as, aphase, abort_flag)) {
+          const long long t0 = tracing ? clock64() : 0;
+          if (!(kPair ? mbar_wait_cluster(a_full + 8 * ai, iphase, abort_flag) : mbar_wait(a_full + 8 * ai, iphase, abort_flag))) {
             give_up(kStatusMmaWaitFull);
             ok = false;
             break;
           }
+          const long long t1 = tracing ? clock64() : 0;
+          // a new activation stage at the start of the range and at every aligned group of k-blocks
+          if (first_unit || kb % act_kblocks == 0) {
+            if (!first_unit) {
+              if constexpr (kPair) umma_commit_pair(act_empty + 8 * as);
+              else umma_commit(act_empty + 8 * as);
+              if (++as == act_stages) { as = 0; aphase ^= 1u; }
+            }
+            first_unit = false;
+            if (!mbar_wait(act_full + 8 * as, aphase, abort_flag)) {
+              give_up(kStatusMmaWaitFull);
+              ok = false;
+              break;
+            }
+          }
           tcgen05_fence_after_sync();
+          const long long t2 = tracing ? clock64() : 0;
           if (si == 0 && kb == seg.kb_begin) mark(3);
-          const uint32_t act_src = act_base + as * act_stage;
+          const uint32_t act_src = act_base + as * act_stage + (kb % act_kblocks) * act_kb_bytes;
           const uint64_t b_lo = umma_smem_desc_sw128(act_src);
-          const uint64_t b_hi = umma_smem_desc_sw128(act_src + mpad * 128);
+          const uint64_t b_hi = umma_smem_desc_sw128(act_src + act_rows * 128);
           const uint32_t a_src = tmem_a_base + ai * G::kAColumns;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const uint64_t b_desc = (i < 4 ? b_lo : b_hi) + 2 * (i & 3);  // +32 bytes along K per MMA
-            umma_f16_ts(tmem_d, a_src + 8 * i, b_desc, idesc, (kb != seg.kb_begin || i != 0) ? 1u : 0u);
+            if constexpr (kPair) umma_f16_ts_pair(tmem_d, a_src + 8 * i, b_desc, idesc, (kb != seg.kb_begin || i != 0) ? 1u : 0u);
+            else umma_f16_ts(tmem_d, a_src + 8 * i, b_desc, idesc, (kb != seg.kb_begin || i != 0) ? 1u : 0u);
           }
-          umma_commit(a_empty + 8 * ai);
-          umma_commit(act_empty + 8 * as);
-          if (++ai == G::kAStages) { ai = 0; iphase ^= 1u; }
-          if (++as == act_stages) { as = 0; aphase ^= 1u; }
+          const long long t3 = tracing ? clock64() : 0;
+          if constexpr (kPair) umma_commit_pair(a_empty + 8 * ai);
+          else umma_commit(a_empty + 8 * ai);
+          if (tracing) {
+            const long long t4 = clock64();
+            spent[0] += t1 - t0;
+            spent[1] += t2 - t1;
+            spent[2] += t3 - t2;
+            spent[3] += t4 - t3;
+            ++spent[4];
+          }
+          if (++ai == a_stages) { ai = 0; iphase ^= 1u; }
         }
         if (!ok) break;
-        umma_commit(d_full + 8 * buf);
+        if constexpr (kPair) umma_commit_pair(d_full + 8 * buf);
+        else umma_commit(d_full + 8 * buf);
         dphase[buf] ^= 1u;
-        mark(4 + (si == 0 ? 0 : 1));
+      }
+      if (tracing) {
+        trace[blockIdx.x * 16 + 4] = static_cast<unsigned long long>(spent[0]);
+        trace[blockIdx.x * 16 + 5] = static_cast<unsigned long long>(spent[1]);
+        trace[blockIdx.x * 16 + 11] = static_cast<unsigned long long>(spent[2]);
+        trace[blockIdx.x * 16 + 14] = static_cast<unsigned long long>(spent[3]);
+        trace[blockIdx.x * 16 + 15] = static_cast<unsigned long long>(spent[4]);
+        trace[blockIdx.x * 16 + 9] = static_cast<unsigned long long>(clock64() - loop_start);
       }
     }
   } else if (warp >= 8) {
@@ -514,9 +620,9 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
     const int my_units = static_cast<int>(w8tc_range_begin(total_units, grid, cta + 1) - w8tc_range_begin(total_units, grid, cta));
     bool ok = true;
     for (int u = group; ok && u < my_units; u += G::kDequantGroups) {
-      const int rs = u % G::kRawStages, ai = u % G::kAStages;
+      const int rs = u % G::kRawStages, ai = u % a_stages;
       const uint32_t rphase = static_cast<uint32_t>(u / G::kRawStages) & 1u;
-      const uint32_t iphase = static_cast<uint32_t>(u / G::kAStages) & 1u;
+      const uint32_t iphase = static_cast<uint32_t>(u / a_stages) & 1u;
       if (!mbar_wait(raw_full + 8 * rs, rphase, abort_flag)) {
         if (lane == 0) give_up(kStatusW8Wait);
         ok = false;
@@ -545,7 +651,10 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
       tmem_store_wait();
       tcgen05_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(a_full + 8 * ai);
+      if (lane == 0) {
+        if constexpr (kPair) mbar_arrive_cluster(map_to_cta(a_full + 8 * ai, 0));
+        else mbar_arrive(a_full + 8 * ai);
+      }
     }
     if (warp == 8 && lane == 0) mark(12);
     // A final tile that collects partial sums is latency-bound (L2 round trips per column group): these warps are
@@ -588,8 +697,11 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
       }
       tcgen05_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(d_empty + 8 * buf);
-      if (warp == 4 && lane == 0) mark(8 + (si == 0 ? 0 : 1));
+      if (lane == 0) {
+        if constexpr (kPair) mbar_arrive_cluster(map_to_cta(d_empty + 8 * buf, 0));
+        else mbar_arrive(d_empty + 8 * buf);
+      }
+      if (warp == 4 && lane == 0 && si == 0) mark(8);
     }
     if (warp == 4 && lane == 0) mark(10);
   }
@@ -602,9 +714,11 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
     __syncthreads();
   }
+  if constexpr (kPair) cluster_sync_all();  // neither CTA leaves while the peer can still touch its barriers or TMEM
   if (warp == 1) {
     tcgen05_fence_after_sync();
-    tmem_dealloc(tmem_base, G::kTmemColumns);
+    if constexpr (kPair) tmem_dealloc_pair(tmem_base, G::kTmemColumns);
+    else tmem_dealloc(tmem_base, G::kTmemColumns);
   }
 }
 
