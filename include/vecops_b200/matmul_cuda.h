@@ -50,8 +50,7 @@ typedef enum VecopsB200MatmulKernel {
   VECOPS_B200_KERNEL_I8_TCGEN05 = 4,   /* tcgen05 kind::i8, TMEM i32 accumulators, TMA pipeline */
   VECOPS_B200_KERNEL_W8_SMALL_M = 5,   /* weight-only int8, M <= 32: 128-bit loads, in-register dequant, split-K */
   VECOPS_B200_KERNEL_W8_TCGEN05 = 6,   /* weight-only int8, M <= 128: weights widened into tensor memory, tcgen05 with W as the M operand */
-  VECOPS_B200_KERNEL_W8_MIXED_TCGEN05 = 7, /* weight-only int8, M <= 128: weights widened to bf16 in swizzled smem, W as the N operand of 128x256x16 MMAs */
-  VECOPS_B200_KERNEL_COUNT_ = 8
+  VECOPS_B200_KERNEL_COUNT_ = 7
 } VecopsB200MatmulKernel;
 
 #define VECOPS_B200_MATMUL_FLAG_ASYNC (1u << 0) /* enqueue only; caller synchronises the stream */

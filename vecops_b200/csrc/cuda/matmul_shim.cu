@@ -23,7 +23,6 @@
 #include "w8_small_m.cuh"
 #include "w8_stream.cuh"
 #include "w8_tcgen05.cuh"
-#include "w8_mixed_tcgen05.cuh"
 #include "shim_util.h"
 
 namespace vb200 {
@@ -173,17 +172,13 @@ bool applicable(const VecopsB200Matmul& p, Row row, uint32_t kernel) {
       return row == Row::W8 && p.m >= 1 && p.m <= W8Tc::kMaxM && p.a_stride_k == 1 && p.b_stride_k == 1 && p.c_stride_n == 1 &&
              p.k > 0 && p.k % 8 == 0 && aligned16(p.a) && aligned16(p.b) && p.a_stride_m % 8 == 0 && p.b_stride_n % 16 == 0 &&
              p.a_stride_m >= p.k && p.b_stride_n >= p.k && p.n < (INT64_C(1) << 31) && p.k < (INT64_C(1) << 31);
-    case VECOPS_B200_KERNEL_W8_MIXED_TCGEN05:
-      return row == Row::W8 && p.m >= 1 && p.m <= W8Mix::kMaxM && p.a_stride_k == 1 && p.b_stride_k == 1 && p.c_stride_n == 1 &&
-             p.k > 0 && p.k % 16 == 0 && aligned16(p.a) && aligned16(p.b) && p.a_stride_m % 8 == 0 && p.b_stride_n % 16 == 0 &&
-             p.a_stride_m >= p.k && p.b_stride_n >= p.k && p.n < (INT64_C(1) << 31) && p.k < (INT64_C(1) << 31);
     default:
       return false;
   }
 }
 
 const char* const kKernelNames[VECOPS_B200_KERNEL_COUNT_] = {
-    "auto", "generic", "f32_simt", "bf16_tcgen05", "i8_tcgen05", "w8_small_m", "w8_tcgen05", "w8_mixed_tcgen05"};
+    "auto", "generic", "f32_simt", "bf16_tcgen05", "i8_tcgen05", "w8_small_m", "w8_tcgen05"};
 
 uint32_t forced_by_environment() {
   const char* text = getenv("VECOPS_B200_FORCE_KERNEL");
@@ -754,47 +749,6 @@ int32_t launch_w8_tcgen05_typed(const VecopsB200Matmul& p, const DeviceState& de
   return VECOPS_STATUS_OK;
 }
 
-template <typename OutT>
-int32_t launch_w8_mixed_typed(const VecopsB200Matmul& p, const DeviceState& dev, cudaStream_t stream, VecopsError* error) {
-  using G = W8Mix;
-  if (dev.prop.major != 10)
-    return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "tcgen05 kernels need an sm_100 device, found sm_%d%d", dev.prop.major,
-                     dev.prop.minor);
-  const int m = static_cast<int>(p.m);
-  const uint64_t need = G::scratch_bytes(m);
-  if (p.workspace == nullptr || p.workspace_size < need)
-    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "w8_mixed_tcgen05 needs %llu bytes of device workspace, %llu were supplied",
-                     (unsigned long long)need, (unsigned long long)p.workspace_size);
-  if (!aligned16(p.workspace)) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "workspace must be 16-byte aligned");
-  CUtensorMap map_w, map_a;
-  int32_t rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.b, p.k, p.n, p.b_stride_n, G::kUnitK, G::kTileN, error);
-  if (rc != VECOPS_STATUS_OK) return rc;
-  rc = make_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.a, p.k, p.m, p.a_stride_m * 2, G::kStepK, G::act_rows(m), error);
-  if (rc != VECOPS_STATUS_OK) return rc;
-  auto kernel = w8_mixed_tcgen05_kernel<OutT>;
-  int device = 0;
-  cudaGetDevice(&device);
-  static std::atomic<bool> raised[64];
-  if (device < 0 || device >= 64 || !raised[device].load()) {
-    rc = raise_smem_limit(kernel, 227 * 1024, error);
-    if (rc != VECOPS_STATUS_OK) return rc;
-    if (device >= 0 && device < 64) raised[device].store(true);
-  }
-  char* scratch = static_cast<char*>(p.workspace);
-  float* partials = reinterpret_cast<float*>(scratch);
-  auto* flags = reinterpret_cast<unsigned long long*>(scratch + G::flags_offset(m));
-  const long long units = ((p.n + G::kTileN - 1) / G::kTileN) * ((p.k + G::kUnitK - 1) / G::kUnitK);
-  long long grid = dev.prop.multiProcessorCount < G::kMaxGrid ? dev.prop.multiProcessorCount : G::kMaxGrid;
-  if (units < grid) grid = units;
-  // A = bf16 activations, B = the widened bf16 weights, both K-major in shared memory; fp32 accumulate
-  const uint32_t idesc = umma_instr_desc(kUmmaAccF32, kUmmaBF16, kUmmaBF16, 128, G::kTileN);
-  kernel<<<static_cast<int>(grid), G::kThreads, G::smem_bytes(m), stream>>>(
-      map_w, map_a, p.column_scale, static_cast<OutT*>(p.c), p.c_stride_m, m, static_cast<int>(p.n), static_cast<int>(p.k), partials,
-      flags, fresh_nonce(p.workspace), idesc, g_status_host, g_trace);
-  g_launches.fetch_add(1);
-  return VECOPS_STATUS_OK;
-}
-
 int32_t launch_f32(const VecopsB200Matmul& p, cudaStream_t stream, VecopsError* error) {
   if ((p.m + 63) / 64 > 65535) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "M too large for f32_simt");
   dim3 grid(static_cast<unsigned>((p.n + 63) / 64), static_cast<unsigned>((p.m + 63) / 64));
@@ -833,8 +787,6 @@ int32_t vecops_b200_matmul_workspace(const VecopsB200Matmul* problem, uint64_t* 
   *bytes = 0;
   if (kernel == VECOPS_B200_KERNEL_W8_TCGEN05) {
     *bytes = W8Tc::scratch_bytes(static_cast<int>(problem->m), problem->k);
-  } else if (kernel == VECOPS_B200_KERNEL_W8_MIXED_TCGEN05) {
-    *bytes = W8Mix::scratch_bytes(static_cast<int>(problem->m));
   } else if (kernel == VECOPS_B200_KERNEL_BF16_TCGEN05 || kernel == VECOPS_B200_KERNEL_I8_TCGEN05) {
     *bytes = tcgen05_tail_scratch(*problem, kernel == VECOPS_B200_KERNEL_I8_TCGEN05);
   }
@@ -888,10 +840,6 @@ int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* err
         case VECOPS_B200_KERNEL_W8_TCGEN05:
           rc = p.c_dtype == VECOPS_DTYPE_BF16 ? launch_w8_tcgen05_typed<__nv_bfloat16>(p, *dev, stream, error)
                                               : launch_w8_tcgen05_typed<float>(p, *dev, stream, error);
-          break;
-        case VECOPS_B200_KERNEL_W8_MIXED_TCGEN05:
-          rc = p.c_dtype == VECOPS_DTYPE_BF16 ? launch_w8_mixed_typed<__nv_bfloat16>(p, *dev, stream, error)
-                                              : launch_w8_mixed_typed<float>(p, *dev, stream, error);
           break;
         default: rc = set_error(error, VECOPS_STATUS_INTERNAL_ERROR, "kernel id %u has no launcher", kernel);
       }

@@ -14,7 +14,6 @@ namespace {
 constexpr const char* kOperatorName = "vecops::matmul";
 constexpr std::uint32_t kVariants[] = {VECOPS_B200_KERNEL_BF16_TCGEN05, VECOPS_B200_KERNEL_I8_TCGEN05,
                                        VECOPS_B200_KERNEL_W8_SMALL_M,   VECOPS_B200_KERNEL_W8_TCGEN05,
-                                       VECOPS_B200_KERNEL_W8_MIXED_TCGEN05,
                                        VECOPS_B200_KERNEL_F32_SIMT,     VECOPS_B200_KERNEL_GENERIC};
 
 struct ErrorText {
@@ -130,7 +129,6 @@ const VariantDescriptor* variant_descriptor(std::uint32_t kernel) {
       build_variant<VECOPS_B200_KERNEL_I8_TCGEN05>(i8 | u8, i8 | u8, i32, 16, 16, 1, true, true),
       build_variant<VECOPS_B200_KERNEL_W8_SMALL_M>(bf16, i8, bf16 | f32, 8, 16, 32, true, true),
       build_variant<VECOPS_B200_KERNEL_W8_TCGEN05>(bf16, i8, bf16 | f32, 8, 16, 32, true, true),
-      build_variant<VECOPS_B200_KERNEL_W8_MIXED_TCGEN05>(bf16, i8, bf16 | f32, 8, 16, 16, true, true),
   };
   return kernel < VECOPS_B200_KERNEL_COUNT_ ? table[kernel] : nullptr;
 }
