@@ -470,14 +470,24 @@ def run_ours(args) -> None:
             launches_per_step = 1
         else:
             fused = None
-            if args.gather == "fused":
-                try:  # epilogue TMA-stores each finished piece into every rank's result over NVLink (peer pointers)
+            if args.gather in ("fused", "fused-peer"):
+                try:  # epilogue TMA-stores each finished piece into every rank's result over NVLink
                     full, handle = sharding.symmetric_result(w.m, w.n, torch.bfloat16, dev)
-                    fused = sharding.FusedGatherGemm(o["a"], o["b"], [int(p) for p in handle.buffer_ptrs], w.n, w.n, n0, torch.bfloat16, stream)
+                    multicast = int(getattr(handle, "multicast_ptr", 0) or 0) if args.gather == "fused" else 0
+                    # every rank must take the same route
+                    route = torch.tensor([1 if multicast else 0], device=dev)
+                    dist.all_reduce(route, op=dist.ReduceOp.MIN)
+                    if int(route.item()) == 1:
+                        # one store to the multicast address: the switch writes it into every rank's copy, own included
+                        targets = [multicast]
+                        gather_mode = "fused: epilogue multimem.st to the NVSwitch multicast address of the result (one store, every rank's copy) + one device barrier"
+                    else:
+                        targets = [int(p) for p in handle.buffer_ptrs]
+                        gather_mode = "fused: epilogue TMA stores to every rank's result over NVLink peer pointers + one device barrier"
+                    fused = sharding.FusedGatherGemm(o["a"], o["b"], targets, w.n, w.n, n0, torch.bfloat16, stream, multicast=len(targets) == 1)
                     fused.launch()
                     handle.barrier(channel=0)
                     torch.cuda.synchronize()
-                    gather_mode = "fused: epilogue TMA stores to every rank's result over NVLink peer pointers + one device barrier"
                 except Exception as error:  # symmetric memory unavailable: fall back to the library collective
                     print(f"[bench] fused gather unavailable on rank {rank}: {error!r}", file=sys.stderr)
                     fused = None
@@ -521,6 +531,15 @@ def run_ours(args) -> None:
     torch.cuda.synchronize()
     result_view = full[:, n0:n1] if (sharded and full is not None) else o["c"]
     parity = parity_sample(w, host_inputs, result_view, port, rows=8 if sharded else 16)
+    if sharded and full is not None and world > 1:
+        # what a PEER computed must have arrived here too: the next rank's first 256 columns, four rows
+        from oracle.checker import bf16_bits_to_f32, rel_frobenius
+        from vecops_b200 import workloads
+        p0, _ = sharding.column_partition(w.n, world, (rank + 1) % world)
+        rows = np.array([0, w.m // 3, w.m // 2 + 1, w.m - 1])
+        peer_b = workloads.make_b_nk(w, p0, p0 + 256)
+        got = full[torch.from_numpy(rows).to(dev)][:, p0:p0 + 256].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+        parity["gathered_from_peer_rel_fro"] = rel_frobenius(bf16_bits_to_f32(got), bf16_bits_to_f32(port.matmul_bf16(host_inputs[0][rows], peer_b)))
 
     for i in range(warmup):
         step(i)
@@ -662,7 +681,9 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=None)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--workload", default=None, help="override the workload (a name from vecops_b200.workloads.WORKLOADS)")
-    parser.add_argument("--gather", choices=["fused", "nccl"], default="fused", help="how the sharded GEMM's output is gathered")
+    parser.add_argument("--gather", choices=["fused", "fused-peer", "nccl"], default="fused",
+                        help="how the sharded GEMM's output is gathered: fused = epilogue stores through the NVSwitch multicast address when "
+                             "there is one, else to every rank's peer pointer; fused-peer = peer pointers only; nccl = library collective")
     parser.add_argument("--no-extra", action="store_true", help="skip the brief measurements of the other single-GPU configurations")
     args = parser.parse_args()
     if args.warmup is not None and args.warmup < 3 and args.impl == "ours":

@@ -163,7 +163,14 @@ typedef struct VecopsB200Gather {
   int64_t n_total;     /* columns of the full C */
   int64_t ldc;         /* row pitch of the full C, elements */
   int64_t col0;        /* first column of this rank's slab */
+  uint32_t flags;      /* VECOPS_B200_GATHER_*; a record that ends before this field means 0 */
+  uint32_t reserved;
 } VecopsB200Gather;
+
+/* c[0] is the NVSwitch MULTICAST address of the result (world must be 1): every finished piece is written once with
+ * multimem.st and the switch delivers it into the copy of every GPU bound to the multicast object, the sender's own
+ * included - one store leaves the GPU instead of one per peer.  Needs n % 8 == 0 (whole 16-byte stores). */
+#define VECOPS_B200_GATHER_MULTICAST (1u << 0)
 
 VECOPS_B200_EXPORT int32_t vecops_b200_matmul_allgather_run(const VecopsB200Matmul* problem, const VecopsB200Gather* gather,
                                                             VecopsError* error);

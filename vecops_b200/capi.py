@@ -79,7 +79,10 @@ class VecopsB200Matmul(Structure):
 
 class VecopsB200Gather(Structure):
     _fields_ = [("struct_size", c_uint32), ("world", c_int32), ("c", POINTER(c_void_p)), ("n_total", c_int64), ("ldc", c_int64),
-                ("col0", c_int64)]
+                ("col0", c_int64), ("flags", c_uint32), ("reserved", c_uint32)]
+
+
+GATHER_MULTICAST = 1
 
 
 class VecopsB200DeviceInfo(Structure):

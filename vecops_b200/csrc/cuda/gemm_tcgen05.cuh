@@ -17,8 +17,10 @@
 // Fused all-gather: the TMA-store epilogue can send every finished slab to up to
 // eight destinations - the C matrices of all GPUs of a column-sharded GEMM, reached
 // through peer pointers over NVLink - at a column offset, so the gather of the
-// output overlaps the main loop tile by tile and needs no staging pass.  (Only
-// stores cross GPUs; every load, and anything with cluster multicast, stays local.)
+// output overlaps the main loop tile by tile and needs no staging pass.  Where the
+// result is bound to an NVSwitch multicast object the epilogue instead writes each
+// slab ONCE, with multimem.st, and the switch delivers it to every GPU.  (Only
+// stores cross GPUs; every load stays local.)
 //
 // Tail splitting: when the tile count leaves the last wave mostly empty (512 tiles
 // on 148 SMs = 3.46 waves), the tail tiles are cut along K into S slices (S a power
@@ -239,7 +241,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     mbar_fence_init();
     tma_prefetch_descriptor(&tma_a);
     tma_prefetch_descriptor(&tma_b);
-    if (use_tma_store) tma_prefetch_descriptor(&tma_c.map[0]);
+    if (use_tma_store == 1) tma_prefetch_descriptor(&tma_c.map[0]);
   }
   if (warp == 1) {
     if constexpr (kPair) {
@@ -468,7 +470,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             words[16 + j] = pack_bf16x2(__uint_as_float(v1[2 * j]), __uint_as_float(v1[2 * j + 1]));
           }
         }
-        if (use_tma_store) {
+        if (use_tma_store == 2) {
+          // Multicast gather: stage the 32-row x 128-byte slab as for a TMA store, then read it back four rows at a
+          // time - eight lanes per row, 16 bytes per lane, 128 contiguous bytes per row on the wire - and store to the
+          // multicast address of the full result.  (`c` is that address, `ldc` the full result's pitch.)
+          const uint32_t buf = my_buf + buf_sel * G::kEpiBufBytes;
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t dst = buf + lane * 128 + ((j ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(words[4 * j]),
+                         "r"(words[4 * j + 1]), "r"(words[4 * j + 2]), "r"(words[4 * j + 3])
+                         : "memory");
+          }
+          __syncwarp();
+          const int chunk = lane & 7;
+          const int chunk_col = col0 + chunk * (16 / static_cast<int>(sizeof(OutT)));
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + (lane >> 3);
+            uint4 piece;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(piece.x), "=r"(piece.y), "=r"(piece.z), "=r"(piece.w)
+                         : "r"(buf + r * 128 + ((chunk ^ (r & 7)) << 4)));
+            if (row0 + r < M && chunk_col < N)
+              multimem_st_v4(c + static_cast<long long>(row0 + r) * ldc + c_col_offset + chunk_col, piece);
+          }
+          buf_sel ^= 1;
+        } else if (use_tma_store) {
           const uint32_t buf = my_buf + buf_sel * G::kEpiBufBytes;
           // the store issued two slabs ago from this buffer must have read it
           if (lane == 0) tma_store_wait_read<1>();
@@ -519,7 +548,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
-    if (use_tma_store && lane == 0) tma_store_wait_all<0>();
+    if (use_tma_store == 1 && lane == 0) tma_store_wait_all<0>();
     if (warp == 2 && lane == 0) {
       mark(15);
       if (trace != nullptr) trace[blockIdx.x * 16 + 14] = static_cast<unsigned long long>(clock64());  // ... and at the end

@@ -12,6 +12,7 @@
 #include <type_traits>
 #include <unordered_map>
 
+#include <cstddef>
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <cuda_runtime.h>
@@ -373,6 +374,7 @@ struct GatherTargets {
   int64_t n_total = 0;           // columns of the full C
   int64_t ldc = 0;               // row pitch of the full C, elements
   int64_t col0 = 0;              // first column of this rank's slab
+  bool multicast = false;        // c[0] is the NVSwitch multicast address of the full C: multimem stores, no tensor map
 };
 
 // One-time per device: raise the dynamic shared memory limits of both forms of the kernel.
@@ -443,7 +445,11 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
   bool tma_store;
   int num_dest = 1;
   int col_offset = 0;
-  if (gather.count > 0) {
+  if (gather.count > 0 && gather.multicast) {
+    tma_store = false;
+    col_offset = static_cast<int>(gather.col0);
+    for (int d = 0; d < GemmStoreMaps::kMax; ++d) maps.map[d] = map_a;  // never dereferenced
+  } else if (gather.count > 0) {
     // every destination is a full [M, n_total] matrix; this rank's tiles land at column col0 + ...
     tma_store = true;
     num_dest = gather.count;
@@ -508,6 +514,11 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
   int m = static_cast<int>(p.m), n = static_cast<int>(p.n), k = static_cast<int>(p.k);
   const float* scale = kInt8 ? nullptr : p.column_scale;
   int store_flag = tma_store ? 1 : 0;
+  if (gather.count > 0 && gather.multicast) {
+    c = static_cast<OutT*>(gather.c[0]);
+    ldc = gather.ldc;
+    store_flag = 2;
+  }
   // Row-tiles that share a sweep over N: as many as keep their rows of A (about 32 MB) in L2 while B streams past.
   long long group_tiles = G::kGroupBytes / (static_cast<long long>(mma_m) * p.k * static_cast<long long>(elem));
   int raster_group = static_cast<int>(group_tiles < 4 ? 4 : group_tiles > 32 ? 32 : group_tiles);
@@ -919,7 +930,7 @@ int32_t vecops_b200_matmul_allgather_run(const VecopsB200Matmul* problem, const 
   int32_t rc = check_problem(problem, &row, error);
   if (rc != VECOPS_STATUS_OK) return rc;
   const VecopsB200Matmul& p = *problem;
-  if (gather == nullptr || gather->struct_size < sizeof(VecopsB200Gather) || gather->world < 1 || gather->world > GemmStoreMaps::kMax ||
+  if (gather == nullptr || gather->struct_size < offsetof(VecopsB200Gather, flags) || gather->world < 1 || gather->world > GemmStoreMaps::kMax ||
       gather->c == nullptr)
     return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "gather record is null, too small, or names more than %d destinations",
                      GemmStoreMaps::kMax);
@@ -932,6 +943,10 @@ int32_t vecops_b200_matmul_allgather_run(const VecopsB200Matmul* problem, const 
   for (int d = 0; d < gather->world; ++d)
     if (gather->c[d] == nullptr || !aligned16(gather->c[d]))
       return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "destination %d is null or not 16-byte aligned", d);
+  const bool has_flags = gather->struct_size >= offsetof(VecopsB200Gather, flags) + sizeof(uint32_t);
+  const bool multicast = has_flags && (gather->flags & VECOPS_B200_GATHER_MULTICAST) != 0;
+  if (multicast && (gather->world != 1 || (p.n * out) % 16 != 0))
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "a multicast gather takes one destination and a slab of whole 16-byte pieces");
   if (p.m == 0 || p.n == 0) return VECOPS_STATUS_OK;
   if (p.k == 0) return set_error(error, VECOPS_STATUS_NOT_APPLICABLE, "K == 0 has nothing to gather; zero the result instead");
 
@@ -954,6 +969,7 @@ int32_t vecops_b200_matmul_allgather_run(const VecopsB200Matmul* problem, const 
     targets.n_total = gather->n_total;
     targets.ldc = gather->ldc;
     targets.col0 = gather->col0;
+    targets.multicast = multicast;
     rc = p.c_dtype == VECOPS_DTYPE_BF16 ? launch_tcgen05<false, __nv_bfloat16>(p, *dev, stream, error, targets)
                                         : launch_tcgen05<false, float>(p, *dev, stream, error, targets);
   }

@@ -173,6 +173,16 @@ __device__ __forceinline__ bool wait_flag_u64(const unsigned long long* flag, un
   }
 }
 
+// ---------------------------------------------------------------- NVSwitch multicast
+
+// 16-byte store to a multicast address: the switch writes it into the memory of every GPU bound to the multicast
+// object.  (Multicast addresses take multimem.* instructions only.)
+__device__ __forceinline__ void multimem_st_v4(void* multicast_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(multicast_addr), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
 // ---------------------------------------------------------------- TMA
 
 __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) {

@@ -71,10 +71,11 @@ class FusedGatherGemm:
     """This rank's slab GEMM with the all-gather fused into its epilogue (vecops_b200_matmul_allgather_run).
 
     `destinations` are the full [M, N] result tensors of every rank as seen from this process: the local tensor
-    and peer views of the others (torch symmetric memory, CUDA IPC).  Built once, launched many times.
+    and peer views of the others (torch symmetric memory, CUDA IPC) - or, with `multicast`, the single NVSwitch
+    multicast address of the result.  Built once, launched many times.
     """
 
-    def __init__(self, a, b_slab, destination_ptrs, n_total: int, ldc: int, col0: int, out_dtype, stream=None) -> None:
+    def __init__(self, a, b_slab, destination_ptrs, n_total: int, ldc: int, col0: int, out_dtype, stream=None, multicast: bool = False) -> None:
         import ctypes
 
         import torch
@@ -100,7 +101,8 @@ class FusedGatherGemm:
         self.problem = problem
         self.scratch = harness.attach_workspace(problem, a.device)  # partial sums of a split tail wave meet here
         self.pointers = (ctypes.c_void_p * len(destination_ptrs))(*destination_ptrs)
-        self.gather = capi.VecopsB200Gather(ctypes.sizeof(capi.VecopsB200Gather), len(destination_ptrs), self.pointers, n_total, ldc, col0)
+        self.gather = capi.VecopsB200Gather(ctypes.sizeof(capi.VecopsB200Gather), len(destination_ptrs), self.pointers, n_total, ldc, col0,
+                                            capi.GATHER_MULTICAST if multicast else 0, 0)
         self.error = capi.ErrorBuffer()
         self._run = capi.library().vecops_b200_matmul_allgather_run
         self._args = (ctypes.byref(self.problem), ctypes.byref(self.gather), ctypes.byref(self.error.record))
