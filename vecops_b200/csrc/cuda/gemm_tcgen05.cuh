@@ -257,6 +257,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   if constexpr (kPair) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Back-to-back launches: everything above touched only this CTA's own shared and tensor memory, so it may run while
+  // the previous kernel of the stream drains; everything below reads or writes global memory and waits for it.  The
+  // next kernel's set-up may likewise overlap this kernel's last tiles.
+  grid_launch_dependents();
+  grid_dependency_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer

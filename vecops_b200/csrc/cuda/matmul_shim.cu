@@ -493,18 +493,26 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
     }
   }
   cudaLaunchConfig_t config = {};
-  cudaLaunchAttribute cluster = {};
+  cudaLaunchAttribute attributes[2] = {};
   config.blockDim = dim3(G::kThreads);
   config.stream = stream;
+  config.attrs = attributes;
+  // programmatic dependent launch: the kernel's set-up may overlap the tail of the previous kernel in the stream; it
+  // waits (griddepcontrol.wait) before its first global access.  VECOPS_B200_GEMM_PDL=0 launches the ordinary way.
+  const char* pdl = getenv("VECOPS_B200_GEMM_PDL");
+  if (pdl == nullptr || pdl[0] != '0') {
+    attributes[config.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[config.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+    ++config.numAttrs;
+  }
   if (plan.pair) {
     config.gridDim = dim3(2 * plan.workers);
     config.dynamicSmemBytes = GemmPair::kSmemBytes;
-    cluster.id = cudaLaunchAttributeClusterDimension;
-    cluster.val.clusterDim.x = 2;
-    cluster.val.clusterDim.y = 1;
-    cluster.val.clusterDim.z = 1;
-    config.attrs = &cluster;
-    config.numAttrs = 1;
+    attributes[config.numAttrs].id = cudaLaunchAttributeClusterDimension;
+    attributes[config.numAttrs].val.clusterDim.x = 2;
+    attributes[config.numAttrs].val.clusterDim.y = 1;
+    attributes[config.numAttrs].val.clusterDim.z = 1;
+    ++config.numAttrs;
   } else {
     config.gridDim = dim3(plan.workers);
     config.dynamicSmemBytes = G::kSmemBytes;

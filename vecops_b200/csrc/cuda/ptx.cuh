@@ -173,6 +173,16 @@ __device__ __forceinline__ bool wait_flag_u64(const unsigned long long* flag, un
   }
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+
+// Tell the launch machinery that the next kernel in the stream - if it was launched as a programmatic dependent -
+// may start being placed on SMs as they free up.  No effect otherwise.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Wait until every kernel this one programmatically depends on has finished and its writes are visible.  Returns at
+// once when the kernel was launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---------------------------------------------------------------- NVSwitch multicast
 
 // 16-byte store to a multicast address: the switch writes it into the memory of every GPU bound to the multicast
