@@ -534,7 +534,7 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
       uint32_t dphase[2] = {0, 0};
       W8TcSegment seg;
       bool ok = true;
-      bool first_unit = true;
+      bool have_act = false;
       const bool tracing = trace != nullptr;
       long long spent[5] = {0, 0, 0, 0, 0};  // tuning aid: cycles waiting for widened weights | for activations | issuing MMAs | committing; units
       const long long loop_start = tracing ? clock64() : 0;
@@ -555,19 +555,14 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
             break;
           }
           const long long t1 = tracing ? clock64() : 0;
-          // a new activation stage at the start of the range and at every aligned group of k-blocks
-          if (first_unit || kb % act_kblocks == 0) {
-            if (!first_unit) {
-              if constexpr (kPair) umma_commit_pair(act_empty + 8 * as);
-              else umma_commit(act_empty + 8 * as);
-              if (++as == act_stages) { as = 0; aphase ^= 1u; }
-            }
-            first_unit = false;
+          // one activation stage serves an aligned group of k-blocks (or what of it lies in this CTA's range)
+          if (!have_act) {
             if (!mbar_wait(act_full + 8 * as, aphase, abort_flag)) {
               give_up(kStatusMmaWaitFull);
               ok = false;
               break;
             }
+            have_act = true;
           }
           tcgen05_fence_after_sync();
           const long long t2 = tracing ? clock64() : 0;
@@ -585,6 +580,13 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
           const long long t3 = tracing ? clock64() : 0;
           if constexpr (kPair) umma_commit_pair(a_empty + 8 * ai);
           else umma_commit(a_empty + 8 * ai);
+          if ((kb + 1) % act_kblocks == 0 || kb + 1 == kblocks) {
+            // the group ends here: its stage goes back to the producer as soon as these MMAs have read it
+            if constexpr (kPair) umma_commit_pair(act_empty + 8 * as);
+            else umma_commit(act_empty + 8 * as);
+            if (++as == act_stages) { as = 0; aphase ^= 1u; }
+            have_act = false;
+          }
           if (tracing) {
             const long long t4 = clock64();
             spent[0] += t1 - t0;
