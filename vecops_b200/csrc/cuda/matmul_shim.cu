@@ -725,10 +725,18 @@ int32_t launch_w8_tcgen05_typed(const VecopsB200Matmul& p, const DeviceState& de
   // MMAs, and every hand-off crosses SMs.  Kept as an option for tuning (VECOPS_B200_W8TC_PAIR=1).
   bool pair = false;
   if (const char* v = getenv("VECOPS_B200_W8TC_PAIR")) pair = v[0] == '1' && pairs > 0;
-  rc = make_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act16, p.k, p.m, act_pitch * 2, 64, pair ? mpad / 2 : mpad, error);
-  if (rc != VECOPS_STATUS_OK) return rc;
-  const char* skip = getenv("VECOPS_B200_W8TC_SKIP_PREPARE");  // timing experiments only: reuse the scratch's previous copy
-  if (skip == nullptr || skip[0] != '1') {
+  // Operands: bf16 x bf16 - the activations as the caller stores them, the weights widened to bf16, both exact - unless
+  // VECOPS_B200_W8TC_FP16=1 asks for the older form (a row-scaled fp16 copy of the activations made by a pre-pass kernel,
+  // weights widened to fp16: one instruction less per weight, one launch more).
+  const char* fp16_form = getenv("VECOPS_B200_W8TC_FP16");
+  const bool bf16_operands = !(fp16_form != nullptr && fp16_form[0] == '1');
+  if (bf16_operands) {
+    rc = make_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.a, p.k, p.m, p.a_stride_m * 2, 64, pair ? mpad / 2 : mpad, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+    inv_scales = nullptr;
+  } else {
+    rc = make_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act16, p.k, p.m, act_pitch * 2, 64, pair ? mpad / 2 : mpad, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
     w8_prepare_activations_kernel<<<static_cast<int>(p.m), W8Prepare::kThreads, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(p.a), p.a_stride_m, act16, act_pitch, inv_scales, static_cast<int>(p.k));
     g_launches.fetch_add(1);
@@ -737,8 +745,9 @@ int32_t launch_w8_tcgen05_typed(const VecopsB200Matmul& p, const DeviceState& de
   const long long units = ((p.n + tile_rows - 1) / tile_rows) * ((p.k + G::kBlockK - 1) / G::kBlockK);
   long long workers = pair ? pairs : (dev.prop.multiProcessorCount < G::kMaxGrid ? dev.prop.multiProcessorCount : G::kMaxGrid);
   if (units < workers) workers = units;
-  // A = f16 (the widened weights, from tensor memory), B = f16 (the scaled activations), fp32 accumulate
-  uint32_t idesc = umma_instr_desc(kUmmaAccF32, kUmmaF16, kUmmaF16, tile_rows, mpad);
+  // A = the widened weights (from tensor memory), B = the activations, same 16-bit format, fp32 accumulate
+  const uint32_t format = bf16_operands ? kUmmaBF16 : kUmmaF16;
+  uint32_t idesc = umma_instr_desc(kUmmaAccF32, format, format, tile_rows, mpad);
   cudaLaunchConfig_t config = {};
   cudaLaunchAttribute cluster = {};
   config.blockDim = dim3(G::kThreads);

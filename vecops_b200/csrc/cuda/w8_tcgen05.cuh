@@ -5,18 +5,19 @@
 // The product is computed transposed, D[n,m] = W[n,:] . A[m,:], so that the
 // 128 rows of a weight tile fill the tensor core's M dimension and the few
 // activation rows are its N dimension (vecops' SwapAB idea, ops/Matmul.h:76-83):
-//   * A-operand: the weight tile, widened int8 -> fp16 (exact) by eight CUDA-core
-//     warps and written with tcgen05.st straight into TENSOR MEMORY - the
-//     widened weights never touch shared memory;
-//   * B-operand: the activation tile, fp16, TMA-loaded with the 128-byte swizzle
-//     (rows past M are zero-filled by TMA).  The fp16 copy of the activations is
-//     made once per launch by w8_prepare_activations_kernel into the scratch:
-//     each bf16 row is multiplied by the power of two that brings its largest
-//     magnitude to 2^14 and converted, which is exact for every element within
-//     2^31 of the row maximum (bf16 has 8 significant bits, fp16 has 11 and its
-//     subnormals reach 2^-24); the power of two is divided out of the accumulator;
-//   * tcgen05.mma kind::f16 with A = f16 from TMEM and B = f16 from shared
-//     memory, fp32 accumulators in TMEM.  Every product is exact in fp32.
+//   * A-operand: the weight tile, widened int8 -> bf16 (exact: |w| <= 128 needs 8 significant bits) by sixteen
+//     CUDA-core warps and written with tcgen05.st straight into TENSOR MEMORY - the widened weights never touch
+//     shared memory;
+//   * B-operand: the activation tile, bf16 exactly as the caller stores it, TMA-loaded with the 128-byte swizzle
+//     (rows past M are zero-filled by TMA);
+//   * tcgen05.mma kind::f16 with A = bf16 from TMEM and B = bf16 from shared memory, fp32 accumulators in TMEM.
+//     Every product is exact in fp32, as with the reference's AMX tdpbf16ps on a bf16-converted weight.
+//   An older operand form remains selectable (and is what the static-scratch entry point uses): weights widened to
+//   fp16 (one instruction less per weight) against an fp16 copy of the activations that w8_prepare_activations_kernel
+//   makes once per launch - each bf16 row multiplied by the power of two that brings its largest magnitude to 2^14,
+//   exact for every element within 2^31 of the row maximum, the power of two divided out of the accumulator.  It
+//   costs a second launch, which is why it is no longer the default.  (Mixed formats, A = f16 with B = bf16, are
+//   not an option: that instruction descriptor raises an illegal-instruction error on this part.)
 //
 // Work is cut stream-K style: the (128-row tile) x (128-wide k-block) units are
 // laid out tile-major and each of the <= 148 persistent CTAs takes an equal
@@ -158,6 +159,18 @@ __device__ __forceinline__ bool wait_flag(const unsigned long long* flag, unsign
   return true;
 }
 
+// Four int8 in one word -> two bf16x2 words {w0,w1}, {w2,w3}, exactly (|w| <= 128 needs 8 significant bits).  0x43xx
+// with bit 7 clear is 128 + (x & 127); the same word reduced to 0x4300 | (x & 128) is 128 or 256: their difference is
+// the two's-complement value.
+__device__ __forceinline__ void dequant4_bf16(uint32_t packed, uint32_t& lo, uint32_t& hi) {
+  const uint32_t p0 = __byte_perm(packed, 0x43434343u, 0x4140);
+  const uint32_t p1 = __byte_perm(packed, 0x43434343u, 0x4342);
+  const uint32_t x0 = p0 & 0xff7fff7fu, c0 = p0 & 0xff80ff80u;
+  const uint32_t x1 = p1 & 0xff7fff7fu, c1 = p1 & 0xff80ff80u;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(x0), "r"(c0));
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(x1), "r"(c1));
+}
+
 // One CTA per activation row: largest |a|, power-of-two scale, fp16 copy, inverse scale.  The row is read once,
 // 16 bytes per thread per step with every load issued before the first use, and converted from registers.
 // Needs 16-byte aligned rows (lda % 8 == 0, checked by the dispatch rules).
@@ -296,6 +309,10 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
                   const float* __restrict__ inv_row_scale, unsigned long long nonce, uint32_t idesc,
                   uint32_t* __restrict__ status, unsigned long long* __restrict__ trace) {
   using G = W8Tc;
+  // Two operand formats, chosen by the launcher through `inv_row_scale`: null = the activations are the caller's bf16
+  // rows and the weights are widened to bf16 (exact both ways, no pre-pass); non-null = the activations are the
+  // row-scaled fp16 copy w8_prepare_activations_kernel made and the weights are widened to fp16.
+  const bool bf16_operands = inv_row_scale == nullptr;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -366,7 +383,7 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
     }
   }
   if (warp == 2) {
-    for (int m = lane; m < G::kMaxM; m += 32) inv_scale_smem[m] = m < M ? __ldg(inv_row_scale + m) : 0.f;
+    for (int m = lane; m < G::kMaxM; m += 32) inv_scale_smem[m] = m >= M ? 0.f : bf16_operands ? 1.f : __ldg(inv_row_scale + m);
   }
   tcgen05_fence_before_sync();
   __syncthreads();
@@ -641,7 +658,10 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
       for (int q = 0; q < 4; ++q) {
         const uint32_t words[4] = {raw[q].x, raw[q].y, raw[q].z, raw[q].w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) dequant4_f16(words[j], wide[8 * q + 2 * j], wide[8 * q + 2 * j + 1]);
+        for (int j = 0; j < 4; ++j) {
+          if (bf16_operands) dequant4_bf16(words[j], wide[8 * q + 2 * j], wide[8 * q + 2 * j + 1]);
+          else dequant4_f16(words[j], wide[8 * q + 2 * j], wide[8 * q + 2 * j + 1]);
+        }
       }
       if (!mbar_wait(a_empty + 8 * ai, iphase ^ 1u, abort_flag)) {
         if (lane == 0) give_up(kStatusW8Wait);
