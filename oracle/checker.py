@@ -54,6 +54,17 @@ def _strides(array: np.ndarray) -> tuple[int, int]:
     return array.strides[0] // item, array.strides[1] // item
 
 
+ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SILU, ACT_CLAMP = range(5)
+
+
+def _cin_view(cin, m: int, n: int):
+    """(array viewed as [m, n] with possibly zero strides, kind) - kind 1 for bf16 bits, else 0."""
+    if cin is None:
+        return None, 0
+    kind = 1 if cin.dtype == np.uint16 else 0
+    return np.broadcast_to(cin, (m, n)), kind
+
+
 class Port:
     """The C restatement.  Every method returns a fresh C-contiguous result."""
 
@@ -67,6 +78,13 @@ class Port:
         self.lib.oracle_matmul_bf16.argtypes = [_I64] * 3 + [_P, _I64, _I64, _P, _I64, _I64, _P, _P, _I64, _I64, c_int]
         self.lib.oracle_matmul_i8.argtypes = [_I64] * 3 + [_P, _I64, _I64, c_int, _P, _I64, _I64, c_int, _P, _I64, _I64]
         self.lib.oracle_matmul_w8.argtypes = [_I64] * 3 + [_P, _I64, _I64, _P, _I64, _I64, _P, _P, _I64, _I64, c_int]
+        _F = ctypes.c_float
+        self.lib.oracle_matmul_bf16_fused.argtypes = [_I64] * 3 + [_P, _I64, _I64, _P, _I64, _I64, _P, c_int, _I64, _I64, _F, _P, c_int, _F, _F,
+                                                                  _P, _I64, _I64, c_int]
+        self.lib.oracle_matmul_f32_fused.argtypes = [_I64] * 3 + [_P, _I64, _I64, _P, _I64, _I64, _P, _I64, _I64, _F, _P, c_int, _F, _F, _P,
+                                                                 _I64, _I64]
+        self.lib.oracle_matmul_i8_accumulate.argtypes = [_I64] * 3 + [_P, _I64, _I64, c_int, _P, _I64, _I64, c_int, _P, _I64, _I64, _P, _I64,
+                                                                     _I64]
 
     @property
     def threads(self) -> int:
@@ -105,6 +123,40 @@ class Port:
         return c
 
 
+    # ---- fused forms: COut = activation((CIn + A.B^T) * alpha * column_scale)
+
+    def matmul_bf16_fused(self, a, b_nk, cin=None, alpha=1.0, scale=None, act=ACT_NONE, lo=0.0, hi=0.0, out_bf16=True):
+        """`cin`: None, or an [M,N]-broadcastable float32 / uint16 (bf16 bits) array; its strides may be zero."""
+        m, k = a.shape
+        n = b_nk.shape[0]
+        c = np.empty((m, n), dtype=np.uint16 if out_bf16 else np.float32)
+        cin_view, kind = _cin_view(cin, m, n)
+        self.lib.oracle_matmul_bf16_fused(m, n, k, _ptr(a), *_strides(a), _ptr(b_nk), *_strides(b_nk), _ptr(cin_view), kind,
+                                          *(_strides(cin_view) if cin_view is not None else (0, 0)), float(alpha), _ptr(scale), int(act),
+                                          float(lo), float(hi), _ptr(c), n, 1, int(out_bf16))
+        return c
+
+    def matmul_f32_fused(self, a, b_nk, cin=None, alpha=1.0, scale=None, act=ACT_NONE, lo=0.0, hi=0.0):
+        m, k = a.shape
+        n = b_nk.shape[0]
+        c = np.empty((m, n), dtype=np.float32)
+        cin_view, _ = _cin_view(cin, m, n)
+        self.lib.oracle_matmul_f32_fused(m, n, k, _ptr(a), *_strides(a), _ptr(b_nk), *_strides(b_nk), _ptr(cin_view),
+                                         *(_strides(cin_view) if cin_view is not None else (0, 0)), float(alpha), _ptr(scale), int(act),
+                                         float(lo), float(hi), _ptr(c), n, 1)
+        return c
+
+    def matmul_i8_accumulate(self, a, b_nk, cin):
+        m, k = a.shape
+        n = b_nk.shape[0]
+        c = np.empty((m, n), dtype=np.int32)
+        cin_view, _ = _cin_view(cin, m, n)
+        self.lib.oracle_matmul_i8_accumulate(m, n, k, _ptr(a), *_strides(a), int(a.dtype == np.int8), _ptr(b_nk), *_strides(b_nk),
+                                             int(b_nk.dtype == np.int8), _ptr(cin_view),
+                                             *(_strides(cin_view) if cin_view is not None else (0, 0)), _ptr(c), n, 1)
+        return c
+
+
 class Ref:
     """The reference's own ops::matmul.  ``Ref.load()`` returns None when unavailable here."""
 
@@ -115,6 +167,35 @@ class Ref:
         lib.ref_matmul_i8.argtypes = [_I64] * 3 + [_P, _I64, c_int, _P, _I64, c_int, _P, _I64, c_int]
         lib.ref_matmul_w8.argtypes = [_I64] * 3 + [_P, _I64, _P, _I64, _P, _P, _I64, c_int]
         lib.ref_matmul_f32_leaf.argtypes = [_I64] * 3 + [_P, _I64, _P, _I64, _P, _I64, c_int]
+        _F = ctypes.c_float
+        if hasattr(lib, "ref_matmul_bf16_fused"):
+            lib.ref_matmul_bf16_fused.argtypes = [_I64] * 3 + [_P, _I64, _P, _I64, _P, _I64, _I64, _F, _P, c_int, _F, _F, _P, _I64, c_int]
+            lib.ref_matmul_i8_accumulate.argtypes = [_I64] * 3 + [_P, _I64, _P, _I64, _P, _I64, _I64, _P, _I64]
+
+    def matmul_bf16_fused(self, a, b_nk, cin=None, alpha=1.0, scale=None, act=ACT_NONE, lo=0.0, hi=0.0, out_bf16=True):
+        """The reference's explicit accumulate form with one composed output transform; `cin` float32 or None.
+        `scale` needs 64 readable floats past n (the transform loads whole vectors)."""
+        m, k = a.shape
+        n = b_nk.shape[0]
+        c = np.empty((m, n), dtype=np.uint16 if out_bf16 else np.float32)
+        cin_view, kind = _cin_view(cin, m, n)
+        assert kind == 0, "the reference driver takes an f32 accumulator input"
+        padded = None if scale is None else np.concatenate([scale.astype(np.float32), np.zeros(64, np.float32)])
+        rc = self.lib.ref_matmul_bf16_fused(m, n, k, _ptr(a), self._rows(a), _ptr(b_nk), self._rows(b_nk), _ptr(cin_view),
+                                            *(_strides(cin_view) if cin_view is not None else (0, 0)), float(alpha), _ptr(padded), int(act),
+                                            float(lo), float(hi), _ptr(c), n, int(out_bf16))
+        assert rc == 0
+        return c
+
+    def matmul_i8_accumulate(self, a, b_nk, cin):
+        m, k = a.shape
+        n = b_nk.shape[0]
+        c = np.empty((m, n), dtype=np.int32)
+        cin_view, _ = _cin_view(cin, m, n)
+        rc = self.lib.ref_matmul_i8_accumulate(m, n, k, _ptr(a), self._rows(a), _ptr(b_nk), self._rows(b_nk), _ptr(cin_view),
+                                               *_strides(cin_view), _ptr(c), n)
+        assert rc == 0
+        return c
 
     @staticmethod
     def load() -> tuple["Ref | None", str]:

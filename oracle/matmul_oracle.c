@@ -127,6 +127,75 @@ void oracle_matmul_w8(int64_t m, int64_t n, int64_t k, const uint16_t* a, int64_
   }
 }
 
+/* Fused forms: the reference's explicit accumulate form COut = transform(CIn + A.B^T) (ops/Matmul.h:519-570) with the
+ * transforms its fusion tests compose (tests/ops/MatmulConversionTestCommon.h:623-704 runtime and per-column scale,
+ * :705-770 bias as a stride-0 CIn + clamp, :1028-1160 relu / sigmoid / silu): the accumulator input joins the sum, then
+ * value * alpha * column_scale[col], then the activation, then the store conversion.
+ * act: 0 none, 1 relu, 2 sigmoid, 3 silu, 4 clamp(lo, hi).  cin: f32 (cin_kind 0) or bf16 bits (1); strides may be 0. */
+static float oracle_activation(float x, int act, float lo, float hi) {
+  switch (act) {
+    case 1: return x > 0.f ? x : 0.f;
+    case 2: return (float)(1.0 / (1.0 + exp(-(double)x)));
+    case 3: return (float)((double)x / (1.0 + exp(-(double)x)));
+    case 4: return x < lo ? lo : (x > hi ? hi : x);
+    default: return x;
+  }
+}
+
+void oracle_matmul_bf16_fused(int64_t m, int64_t n, int64_t k, const uint16_t* a, int64_t sam, int64_t sak,
+                              const uint16_t* b, int64_t sbn, int64_t sbk, const void* cin, int cin_kind, int64_t cin_sm,
+                              int64_t cin_sn, float alpha, const float* column_scale, int act, float lo, float hi, void* c,
+                              int64_t scm, int64_t scn, int c_is_bf16) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t i = 0; i < m; ++i) {
+    for (int64_t j = 0; j < n; ++j) {
+      double sum = 0.0;
+      if (cin) sum = cin_kind == 1 ? (double)bf16_to_f32(((const uint16_t*)cin)[i * cin_sm + j * cin_sn])
+                                   : (double)((const float*)cin)[i * cin_sm + j * cin_sn];
+      for (int64_t kk = 0; kk < k; ++kk)
+        sum += (double)bf16_to_f32(a[i * sam + kk * sak]) * (double)bf16_to_f32(b[j * sbn + kk * sbk]);
+      float acc = (float)sum * alpha;
+      if (column_scale) acc *= column_scale[j];
+      acc = oracle_activation(acc, act, lo, hi);
+      if (c_is_bf16) ((uint16_t*)c)[i * scm + j * scn] = f32_to_bf16(acc);
+      else ((float*)c)[i * scm + j * scn] = acc;
+    }
+  }
+}
+
+void oracle_matmul_f32_fused(int64_t m, int64_t n, int64_t k, const float* a, int64_t sam, int64_t sak, const float* b,
+                             int64_t sbn, int64_t sbk, const float* cin, int64_t cin_sm, int64_t cin_sn, float alpha,
+                             const float* column_scale, int act, float lo, float hi, float* c, int64_t scm, int64_t scn) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t i = 0; i < m; ++i) {
+    for (int64_t j = 0; j < n; ++j) {
+      double sum = cin ? (double)cin[i * cin_sm + j * cin_sn] : 0.0;
+      for (int64_t kk = 0; kk < k; ++kk) sum += (double)a[i * sam + kk * sak] * (double)b[j * sbn + kk * sbk];
+      float acc = (float)sum * alpha;
+      if (column_scale) acc *= column_scale[j];
+      c[i * scm + j * scn] = oracle_activation(acc, act, lo, hi);
+    }
+  }
+}
+
+/* Native integer accumulate: C = CIn + A.B^T in int32, wrapping (check_native_integer_accumulate). */
+void oracle_matmul_i8_accumulate(int64_t m, int64_t n, int64_t k, const void* a, int64_t sam, int64_t sak, int a_signed,
+                                 const void* b, int64_t sbn, int64_t sbk, int b_signed, const int32_t* cin, int64_t cin_sm,
+                                 int64_t cin_sn, int32_t* c, int64_t scm, int64_t scn) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t i = 0; i < m; ++i) {
+    for (int64_t j = 0; j < n; ++j) {
+      uint32_t sum = cin ? (uint32_t)cin[i * cin_sm + j * cin_sn] : 0u;
+      for (int64_t kk = 0; kk < k; ++kk) {
+        const int32_t x = a_signed ? ((const int8_t*)a)[i * sam + kk * sak] : ((const uint8_t*)a)[i * sam + kk * sak];
+        const int32_t y = b_signed ? ((const int8_t*)b)[j * sbn + kk * sbk] : ((const uint8_t*)b)[j * sbn + kk * sbk];
+        sum += (uint32_t)(x * y);
+      }
+      c[i * scm + j * scn] = (int32_t)sum;
+    }
+  }
+}
+
 /* How many threads the loops above use (1 when built without OpenMP). */
 #ifdef _OPENMP
 #include <omp.h>

@@ -136,6 +136,76 @@ int ref_matmul_w8(int64_t m, int64_t n, int64_t k, const uint16_t* a, int64_t ld
   return 0;
 }
 
+// Fused forms (the reference's explicit accumulate form COut = transform(CIn + A.B^T), ops/Matmul.h:519-570, with the
+// transforms its fusion tests compose: MatmulConversionTestCommon.h:623-704 scale, :705-770 bias + clamp, :1028-1160
+// relu / sigmoid / silu).  One transform covers them: value * alpha * column_scale[col], then the activation.
+// act: 0 none, 1 relu, 2 sigmoid, 3 silu, 4 clamp(lo, hi).  cin may be null (zero accumulator input).
+int ref_matmul_bf16_fused(int64_t m, int64_t n, int64_t k, const uint16_t* a, int64_t lda, const uint16_t* b, int64_t ldb,
+                          const float* cin, int64_t cin_sm, int64_t cin_sn, float alpha, const float* scale, int act, float lo,
+                          float hi, void* c, int64_t ldc, int c_is_bf16) {
+  if (!request_amx()) return 1;
+  auto transform = make_lane_local_vec_transform<float32_t, float32_t>(
+      [=](auto tag, auto value, const auto& context) VECOPS_KERNEL_LAMBDA {
+        const auto coordinate = context.lane_coord(0);
+        const nint_t column = coordinate[coordinate.size() - 1];
+        auto x = vec::mul(tag, value, vec::fill(tag, alpha));
+        if (scale != nullptr) x = vec::mul(tag, x, vec::load(tag, scale + column));
+        const auto one = vec::fill(tag, 1.0f);
+        if (act == 1) x = vec::max(tag, x, vec::fill(tag, 0.0f));
+        if (act == 2) x = vec::div(tag, one, vec::add(tag, one, vec::exp(tag, vec::neg(tag, x))));
+        if (act == 3) x = vec::mul(tag, x, vec::div(tag, one, vec::add(tag, one, vec::exp(tag, vec::neg(tag, x)))));
+        if (act == 4) x = vec::min(tag, vec::max(tag, x, vec::fill(tag, lo)), vec::fill(tag, hi));
+        return x;
+      });
+  const auto* ap = reinterpret_cast<const bfloat16_t*>(a);
+  const auto* bp = reinterpret_cast<const bfloat16_t*>(b);
+  auto at = make_tensor(ap, make_layout(make_shape(Any{m}, Any{k}), make_strides(Any{lda}, cint<1>)));
+  auto bt = make_tensor(bp, make_layout(make_shape(Any{n}, Any{k}), make_strides(Any{ldb}, cint<1>)));
+  auto ai = input<bfloat16_t>(at);
+  auto bi = input<bfloat16_t>(bt);
+  auto op = ops::matmul(ops::MatmulConfig<matmul::AMX_BF16F32>{});
+  auto run = [&](auto co) {
+    if (cin != nullptr) {
+      auto cint_tensor = make_tensor(cin, make_layout(make_shape(Any{m}, Any{n}), make_strides(Any{cin_sm}, Any{cin_sn})));
+      auto ci = input<float32_t>(cint_tensor);
+      kernel::Workspace storage(op.required_workspace(Any{m}, Any{n}, Any{k}, ai, bi, ci, co));
+      auto view = storage.view();
+      op(view, Any{m}, Any{n}, Any{k}, ai, bi, ci, co);
+    } else {
+      kernel::Workspace storage(op.required_workspace(Any{m}, Any{n}, Any{k}, ai, bi, co));
+      auto view = storage.view();
+      op(view, Any{m}, Any{n}, Any{k}, ai, bi, co);
+    }
+  };
+  if (c_is_bf16) {
+    auto ct = make_tensor(reinterpret_cast<bfloat16_t*>(c), make_layout(make_shape(Any{m}, Any{n}), make_strides(Any{ldc}, cint<1>)));
+    run(output<float32_t>(ct, transform));
+  } else {
+    auto ct = make_tensor(reinterpret_cast<float*>(c), make_layout(make_shape(Any{m}, Any{n}), make_strides(Any{ldc}, cint<1>)));
+    run(output<float32_t>(ct, transform));
+  }
+  return 0;
+}
+
+// Native integer accumulate (MatmulConversionTestCommon.h check_native_integer_accumulate): C = Cin + A.B^T in int32.
+int ref_matmul_i8_accumulate(int64_t m, int64_t n, int64_t k, const int8_t* a, int64_t lda, const int8_t* b, int64_t ldb,
+                             const int32_t* cin, int64_t cin_sm, int64_t cin_sn, int32_t* c, int64_t ldc) {
+  if (!request_amx()) return 1;
+  auto at = make_tensor(a, make_layout(make_shape(Any{m}, Any{k}), make_strides(Any{lda}, cint<1>)));
+  auto bt = make_tensor(b, make_layout(make_shape(Any{n}, Any{k}), make_strides(Any{ldb}, cint<1>)));
+  auto ct = make_tensor(c, make_layout(make_shape(Any{m}, Any{n}), make_strides(Any{ldc}, cint<1>)));
+  auto cin_tensor = make_tensor(cin, make_layout(make_shape(Any{m}, Any{n}), make_strides(Any{cin_sm}, Any{cin_sn})));
+  auto ai = input<int8_t>(at);
+  auto bi = input<int8_t>(bt);
+  auto ci = input<int32_t>(cin_tensor);
+  auto co = output<int32_t>(ct);
+  auto op = ops::matmul(ops::MatmulConfig<matmul::AMX_I8I32<int8_t, int8_t>>{});
+  kernel::Workspace storage(op.required_workspace(Any{m}, Any{n}, Any{k}, ai, bi, ci, co));
+  auto view = storage.view();
+  op(view, Any{m}, Any{n}, Any{k}, ai, bi, ci, co);
+  return 0;
+}
+
 // fp32: the reference has no fp32 matmul atom on x86; its only fp32 x fp32
 // product code is the AVX-512 vector leaf (amx/Backend.h:767-901) instantiated
 // with equal types.  B is [N,K] here.

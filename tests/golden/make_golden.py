@@ -21,7 +21,7 @@ import numpy as np
 ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
 
-from oracle.checker import Ref, f32_to_bf16_bits  # noqa: E402
+from oracle.checker import ACT_CLAMP, ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SILU, Ref, f32_to_bf16_bits  # noqa: E402
 
 HERE = Path(__file__).resolve().parent
 
@@ -85,6 +85,47 @@ def main() -> None:
         a = conversion_pattern(m * k, 3, np.float32).reshape(m, k)
         b = conversion_pattern(n * k, 5, np.float32).reshape(n, k)
         cases[f"f32_{m}x{n}x{k}"] = dict(kind="f32", a=a, b=b, c=ref.matmul_f32_leaf(a, b))
+
+    # fused forms: COut = activation((CIn + A.B^T) * alpha * column_scale), on the reference fusion tests' shapes and
+    # input patterns (MatmulFusionTest.cpp:29-70; MatmulConversionTestCommon.h:705-770 bias + clamp, :1028-1160
+    # relu / sigmoid / silu, :623-704 runtime and per-column scale)
+    def fused_inputs(m, n, k):
+        a = f32_to_bf16_bits(conversion_pattern(m * k, 3, np.float32)).reshape(m, k)
+        b = f32_to_bf16_bits(conversion_pattern(n * k, 11, np.float32)).reshape(n, k)
+        bias = (((np.arange(n) * 3) % 11 - 5) / 8.0).astype(np.float32)
+        return a, b, bias
+
+    def fused_case(name, m, n, k, cin=None, alpha=1.0, scale=None, act=ACT_NONE, lo=0.0, hi=0.0):
+        a, b, bias = fused_inputs(m, n, k)
+        if isinstance(cin, str):
+            cin = {"bias": bias, "full": (((np.arange(m * n) * 5) % 13 - 6) / 4.0).astype(np.float32).reshape(m, n),
+                   "column": (((np.arange(m) * 7) % 9 - 4) / 2.0).astype(np.float32).reshape(m, 1)}[cin]
+        arrays = dict(kind="fused_bf16", a=a, b=b, alpha=np.float32(alpha), act=np.int32(act), lo=np.float32(lo), hi=np.float32(hi),
+                      c_f32=ref.matmul_bf16_fused(a, b, cin, alpha, scale, act, lo, hi, out_bf16=False),
+                      c_bf16=ref.matmul_bf16_fused(a, b, cin, alpha, scale, act, lo, hi, out_bf16=True))
+        if cin is not None:
+            arrays["cin"] = cin
+        if scale is not None:
+            arrays["scale"] = scale
+        cases[f"fused_{name}_{m}x{n}x{k}"] = arrays
+
+    fused_case("bias_clamp", 19, 23, 65, cin="bias", act=ACT_CLAMP, lo=-0.25, hi=0.25)
+    for m, n, k in [(19, 23, 65), (1, 8, 129), (8, 1, 129)]:
+        fused_case("relu", m, n, k, act=ACT_RELU)
+        fused_case("sigmoid", m, n, k, act=ACT_SIGMOID)
+    fused_case("silu", 1, 8, 129, act=ACT_SILU)
+    fused_case("bias_silu", 1, 8, 129, cin="bias", act=ACT_SILU)
+    fused_case("alpha", 19, 23, 65, alpha=0.75)
+    fused_case("alpha_scale_relu_cin", 19, 23, 65, cin="full", alpha=0.75,
+               scale=(0.5 + (np.arange(23) % 5) / 4.0).astype(np.float32), act=ACT_RELU)
+    fused_case("column_cin", 19, 23, 65, cin="column")
+
+    # native integer accumulate (check_native_integer_accumulate): C = CIn + A.B^T in int32
+    for m, n, k in [(19, 23, 65), (1, 8, 129)]:
+        a = conversion_pattern(m * k, 3, np.int8).reshape(m, k)
+        b = conversion_pattern(n * k, 11, np.int8).reshape(n, k)
+        cin = ((np.arange(m * n, dtype=np.int64) * 37) % 1001 - 500).astype(np.int32).reshape(m, n)
+        cases[f"i8acc_{m}x{n}x{k}"] = dict(kind="i8acc", a=a, b=b, cin=cin, c=ref.matmul_i8_accumulate(a, b, cin))
 
     for name, arrays in cases.items():
         kind = arrays.pop("kind")

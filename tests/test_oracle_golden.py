@@ -38,10 +38,18 @@ def test_port_matches_golden_fixtures(port, golden):
         elif kind == "w8":
             got = bf16_bits_to_f32(port.matmul_w8(a, b, case["scale"], True))
             assert rel_frobenius(got, bf16_bits_to_f32(case["c_bf16"])) <= TOL_BF16, name
+        elif kind == "fused_bf16":
+            args = dict(cin=case.get("cin"), alpha=float(case["alpha"]), scale=case.get("scale"), act=int(case["act"]),
+                        lo=float(case["lo"]), hi=float(case["hi"]))
+            assert rel_frobenius(port.matmul_bf16_fused(a, b, out_bf16=False, **args), case["c_f32"]) <= 1e-6, name
+            got = bf16_bits_to_f32(port.matmul_bf16_fused(a, b, out_bf16=True, **args))
+            assert rel_frobenius(got, bf16_bits_to_f32(case["c_bf16"])) <= TOL_BF16, name
+        elif kind == "i8acc":
+            assert np.array_equal(port.matmul_i8_accumulate(a, b, case["cin"]), case["c"]), name
         else:
             raise AssertionError(f"unknown fixture kind {kind}")
         checked += 1
-    assert checked >= 15
+    assert checked >= 30
 
 
 def test_int32_accumulator_wraps(port):
