@@ -93,6 +93,42 @@ VECOPS_B200_EXPORT int32_t vecops_b200_matmul_workspace(const VecopsB200Matmul* 
  * legal: K == 0 stores zeros (ops/Matmul.h:41-43). */
 VECOPS_B200_EXPORT int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* error);
 
+/* Fused form: COut = convert( activation( (CIn + A . B^T) * alpha * column_scale[n] ) ).
+ *
+ * vecops writes this as the explicit accumulate form `COutput = CInput + A*B^T` (include/vecops/ops/Matmul.h:519-570)
+ * with an output transform composed from vec primitives; the compositions its fusion tests use
+ * (tests/ops/MatmulFusionTest.cpp:29-120; tests/ops/MatmulConversionTestCommon.h:623-704 runtime and per-column scale,
+ * :705-770 bias as a stride-0 CIn + clamp, :1028-1160 relu / sigmoid / silu) are the enumeration below.
+ *   - `cin` is optional; its strides count elements and may be 0 (stride_m = 0: a bias row; stride_n = 0: a column).
+ *     Float rows take an f32 or bf16 CIn, added in fp32 before anything else.  The int8 row takes an int32 CIn, added
+ *     with wraparound ("native integer accumulate"), and nothing else: alpha must be 1 and activation NONE.
+ *   - problem->column_scale keeps its meaning and is applied together with alpha.
+ *   - Served by the tcgen05 GEMMs, the fp32 kernel and the strided kernel; a weight-only problem with a fused form goes
+ *     to the strided kernel (correct, not fast).  Forcing a kernel that cannot serve the form is NOT_APPLICABLE.
+ * Workspace and selection are those of the plain problem. */
+typedef enum VecopsB200Activation {
+  VECOPS_B200_ACTIVATION_NONE = 0,
+  VECOPS_B200_ACTIVATION_RELU = 1,
+  VECOPS_B200_ACTIVATION_SIGMOID = 2,  /* 1 / (1 + exp(-x)) */
+  VECOPS_B200_ACTIVATION_SILU = 3,     /* x / (1 + exp(-x)) */
+  VECOPS_B200_ACTIVATION_CLAMP = 4,    /* min(max(x, clamp_lo), clamp_hi) */
+  VECOPS_B200_ACTIVATION_COUNT_ = 5
+} VecopsB200Activation;
+
+typedef struct VecopsB200Epilogue {
+  uint32_t struct_size;
+  uint32_t activation;  /* VecopsB200Activation */
+  const void* cin;      /* [M,N] accumulator input, NULL = none */
+  int64_t cin_stride_m, cin_stride_n;
+  uint32_t cin_dtype;   /* VecopsDType: F32 | BF16 (float rows), I32 (int8 row) */
+  float alpha;          /* factor on the accumulator, 1 = none */
+  float clamp_lo, clamp_hi;
+  uint32_t reserved;
+} VecopsB200Epilogue;
+
+VECOPS_B200_EXPORT int32_t vecops_b200_matmul_run_fused(const VecopsB200Matmul* problem, const VecopsB200Epilogue* epilogue,
+                                                        VecopsError* error);
+
 /* The weight-only int8 tensor-core kernel (VECOPS_B200_KERNEL_W8_TCGEN05) with its scratch inside the
  * library instead of in a caller workspace.  It has no counterpart in the reference: it exists for callers
  * of this library that cannot allocate device memory at call time - a serving loop whose memory pool is
@@ -115,6 +151,11 @@ VECOPS_B200_EXPORT int32_t vecops_b200_matmul_run(const VecopsB200Matmul* proble
  * synchronous calls only. */
 #define VECOPS_B200_STATIC_SCRATCH_BYTES (8ull << 20)
 VECOPS_B200_EXPORT int32_t vecops_b200_matmul_w8_static_scratch(const VecopsB200Matmul* problem, VecopsError* error);
+
+/* Tuning aid: when `device_buffer` (160 x 16 uint64 on the device the kernels run on) is non-NULL the tensor-core
+ * kernels write a per-CTA timeline into it (globaltimer stamps and cycle counts of their roles); NULL turns it off.
+ * Process-wide; not for concurrent launches. */
+VECOPS_B200_EXPORT void vecops_b200_debug_set_trace(void* device_buffer);
 
 /* Stable short name of a variant ("bf16_tcgen05", ...), NULL if out of range. */
 VECOPS_B200_EXPORT const char* vecops_b200_kernel_name(uint32_t kernel);

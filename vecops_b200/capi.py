@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import (POINTER, Structure, Union, byref, c_char, c_char_p, c_int32, c_int64, c_size_t, c_uint16, c_uint32,
-                    c_uint64, c_void_p)
+                    c_uint64, c_void_p, c_float)
 from pathlib import Path
 
 LIBRARY_PATH = Path(__file__).resolve().parent / "lib" / "libvecops_b200.so"
@@ -77,6 +77,15 @@ class VecopsB200Matmul(Structure):
                 ("flags", c_uint32), ("reserved", c_uint32)]
 
 
+class VecopsB200Epilogue(Structure):
+    _fields_ = [("struct_size", c_uint32), ("activation", c_uint32), ("cin", c_void_p), ("cin_stride_m", c_int64),
+                ("cin_stride_n", c_int64), ("cin_dtype", c_uint32), ("alpha", c_float), ("clamp_lo", c_float),
+                ("clamp_hi", c_float), ("reserved", c_uint32)]
+
+
+ACTIVATION_NONE, ACTIVATION_RELU, ACTIVATION_SIGMOID, ACTIVATION_SILU, ACTIVATION_CLAMP = range(5)
+
+
 class VecopsB200Gather(Structure):
     _fields_ = [("struct_size", c_uint32), ("world", c_int32), ("c", POINTER(c_void_p)), ("n_total", c_int64), ("ldc", c_int64),
                 ("col0", c_int64), ("flags", c_uint32), ("reserved", c_uint32)]
@@ -124,6 +133,7 @@ def library() -> ctypes.CDLL:
         lib.vecops_b200_matmul_select.argtypes = [POINTER(VecopsB200Matmul), POINTER(c_uint32), e]
         lib.vecops_b200_matmul_workspace.argtypes = [POINTER(VecopsB200Matmul), POINTER(c_uint64), e]
         lib.vecops_b200_matmul_run.argtypes = [POINTER(VecopsB200Matmul), e]
+        lib.vecops_b200_matmul_run_fused.argtypes = [POINTER(VecopsB200Matmul), POINTER(VecopsB200Epilogue), e]
         lib.vecops_b200_matmul_allgather_run.argtypes = [POINTER(VecopsB200Matmul), POINTER(VecopsB200Gather), e]
         lib.vecops_b200_kernel_name.argtypes = [c_uint32]
         lib.vecops_b200_kernel_name.restype = c_char_p

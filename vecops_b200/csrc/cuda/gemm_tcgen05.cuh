@@ -42,6 +42,7 @@
 
 #include <type_traits>
 
+#include "epilogue.cuh"
 #include "ptx.cuh"
 
 namespace vb200 {
@@ -184,7 +185,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                     const __grid_constant__ GemmStoreMaps tma_c, int num_dest, int c_col_offset, OutT* __restrict__ c,
                     long long ldc, int M, int N, int K, const float* __restrict__ column_scale, uint32_t idesc,
                     int use_tma_store, int raster_group, int split, uint32_t* __restrict__ partials, unsigned long long* __restrict__ flags,
-                    unsigned long long nonce, uint32_t* __restrict__ status, unsigned long long* __restrict__ trace) {
+                    unsigned long long nonce, EpilogueArgs ep, uint32_t* __restrict__ status,
+                    unsigned long long* __restrict__ trace) {
   using G = typename std::conditional<kPair, GemmPair, GemmTc>::type;
   constexpr int kElemBytes = kInt8 ? 1 : 2;
   constexpr int kBlockK = G::kBlockKBytes / kElemBytes;  // elements per k-block
@@ -443,12 +445,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           tmem_load_wait();
           if (item.slices > 1) add_partials(words, slab * 32);
           if constexpr (!kInt8) {
-            if (column_scale != nullptr) {
+            if (ep.active) {
+              // the fused transform needs each element's own row and column (accumulator input, per-column factor)
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (row < M && col0 + j < N) {
+                  const float s = column_scale != nullptr ? __ldg(column_scale + col0 + j) : 1.f;
+                  words[j] = __float_as_uint(epilogue_float(__uint_as_float(words[j]), ep, row, col0 + j, s));
+                }
+              }
+            } else if (column_scale != nullptr) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
                 const float s = (col0 + j < N) ? __ldg(column_scale + col0 + j) : 0.f;
                 words[j] = __float_as_uint(__uint_as_float(words[j]) * s);
               }
+            }
+          } else {
+            if (ep.active) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (row < M && col0 + j < N) words[j] = epilogue_int(words[j], ep, row, col0 + j);
             }
           }
         } else {
@@ -460,7 +477,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             add_partials(v0, slab * 64);
             add_partials(v1, slab * 64 + 32);
           }
-          if (column_scale != nullptr) {
+          if (ep.active) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (row < M && col0 + j < N) {
+                const float s0 = column_scale != nullptr ? __ldg(column_scale + col0 + j) : 1.f;
+                v0[j] = __float_as_uint(epilogue_float(__uint_as_float(v0[j]), ep, row, col0 + j, s0));
+              }
+              if (row < M && col0 + 32 + j < N) {
+                const float s1 = column_scale != nullptr ? __ldg(column_scale + col0 + 32 + j) : 1.f;
+                v1[j] = __float_as_uint(epilogue_float(__uint_as_float(v1[j]), ep, row, col0 + 32 + j, s1));
+              }
+            }
+          } else if (column_scale != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float s0 = (col0 + j < N) ? __ldg(column_scale + col0 + j) : 0.f;

@@ -308,6 +308,10 @@ int32_t raise_smem_limit(Kernel kernel, int bytes, VecopsError* error) {
 
 uint64_t fresh_nonce(const void* salt);
 
+// The fused output transform of the call in flight on this thread (vecops_b200_matmul_run_fused sets it around the
+// ordinary run); the launchers hand it to the kernels that implement it.
+thread_local EpilogueArgs tl_epilogue;
+
 // Clusters of two CTAs of `kernel` the current device keeps resident at once; 0 when it cannot run them.
 int cluster_capacity(const void* kernel, int threads, size_t smem_bytes) {
   cudaLaunchConfig_t config = {};
@@ -537,8 +541,9 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
   unsigned long long nonce = split > 1 ? fresh_nonce(p.workspace) : 0ull;
   uint32_t* status_word = g_status_host;
   unsigned long long* trace = g_trace;
+  EpilogueArgs epilogue = tl_epilogue;
   void* args[] = {&map_a, &map_b, &maps, &num_dest, &col_offset, &c, &ldc, &m, &n, &k, &scale, &idesc, &store_flag,
-                  &raster_group, &split, &partials, &flags, &nonce, &status_word, &trace};
+                  &raster_group, &split, &partials, &flags, &nonce, &epilogue, &status_word, &trace};
   const void* entry = plan.pair ? reinterpret_cast<const void*>(gemm_tcgen05_kernel<kInt8, OutT, true>)
                                 : reinterpret_cast<const void*>(gemm_tcgen05_kernel<kInt8, OutT, false>);
   cudaError_t launched = cudaLaunchKernelExC(&config, entry, args);
@@ -553,7 +558,7 @@ void launch_generic_typed(const VecopsB200Matmul& p, cudaStream_t stream) {
   gemm_generic_kernel<TA, TB, TC, Acc><<<grid, 256, 0, stream>>>(
       static_cast<const TA*>(p.a), p.a_stride_m, p.a_stride_k, static_cast<const TB*>(p.b), p.b_stride_n, p.b_stride_k,
       static_cast<TC*>(p.c), p.c_stride_m, p.c_stride_n, static_cast<int>(p.m), static_cast<int>(p.n), static_cast<int>(p.k),
-      p.column_scale);
+      p.column_scale, tl_epilogue);
   g_launches.fetch_add(1);
 }
 
@@ -782,7 +787,7 @@ int32_t launch_f32(const VecopsB200Matmul& p, cudaStream_t stream, VecopsError* 
   dim3 grid(static_cast<unsigned>((p.n + 63) / 64), static_cast<unsigned>((p.m + 63) / 64));
   gemm_f32_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(p.a), p.a_stride_m, static_cast<const float*>(p.b), p.b_stride_n,
                                             p.b_stride_k, static_cast<float*>(p.c), p.c_stride_m, static_cast<int>(p.m),
-                                            static_cast<int>(p.n), static_cast<int>(p.k));
+                                            static_cast<int>(p.n), static_cast<int>(p.k), tl_epilogue);
   g_launches.fetch_add(1);
   return VECOPS_STATUS_OK;
 }
@@ -847,7 +852,7 @@ int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* err
   cudaStream_t stream = static_cast<cudaStream_t>(p.stream);
 
   if (rc == VECOPS_STATUS_OK) {
-    if (p.k == 0) {
+    if (p.k == 0 && !tl_epilogue.active) {
       // empty reduction: C = 0 (include/vecops/ops/Matmul.h:41-43)
       const size_t esz = dtype_size(p.c_dtype);
       const long long total = p.m * p.n;
@@ -889,6 +894,66 @@ int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* err
     }
   }
   if (previous >= 0 && previous != device) cudaSetDevice(previous);
+  return rc;
+}
+
+int32_t vecops_b200_matmul_run_fused(const VecopsB200Matmul* problem, const VecopsB200Epilogue* epilogue, VecopsError* error) {
+  Row row;
+  int32_t rc = check_problem(problem, &row, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  if (epilogue == nullptr) return vecops_b200_matmul_run(problem, error);
+  if (epilogue->struct_size < sizeof(VecopsB200Epilogue))
+    return set_error(error, VECOPS_STATUS_ABI_MISMATCH, "epilogue record is %u bytes, this library needs %zu", epilogue->struct_size,
+                     sizeof(VecopsB200Epilogue));
+  if (epilogue->activation >= VECOPS_B200_ACTIVATION_COUNT_)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "unknown activation %u", epilogue->activation);
+  EpilogueArgs args;
+  args.activation = static_cast<int>(epilogue->activation);
+  args.alpha = epilogue->alpha;
+  args.clamp_lo = epilogue->clamp_lo;
+  args.clamp_hi = epilogue->clamp_hi;
+  if (epilogue->cin != nullptr) {
+    args.cin = epilogue->cin;
+    args.cin_stride_m = epilogue->cin_stride_m;
+    args.cin_stride_n = epilogue->cin_stride_n;
+    if (epilogue->cin_stride_m < 0 || epilogue->cin_stride_n < 0)
+      return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "accumulator input strides must not be negative");
+    if (row == Row::I8) {
+      if (epilogue->cin_dtype != VECOPS_DTYPE_I32)
+        return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "int32 accumulators take an int32 accumulator input");
+      args.cin_kind = kCinI32;
+    } else if (epilogue->cin_dtype == VECOPS_DTYPE_F32) {
+      args.cin_kind = kCinF32;
+    } else if (epilogue->cin_dtype == VECOPS_DTYPE_BF16) {
+      args.cin_kind = kCinBF16;
+    } else {
+      return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "fp32 accumulators take an f32 or bf16 accumulator input");
+    }
+  }
+  if (row == Row::I8 && (epilogue->alpha != 1.f || epilogue->activation != VECOPS_B200_ACTIVATION_NONE))
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "int32 accumulators take an accumulator input only: no factor, no activation");
+  if (epilogue->activation == VECOPS_B200_ACTIVATION_CLAMP && !(epilogue->clamp_lo <= epilogue->clamp_hi))
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "clamp needs clamp_lo <= clamp_hi");
+  args.active = (args.cin_kind != kCinNone || args.alpha != 1.f || args.activation != kActNone) ? 1 : 0;
+  if (!args.active) return vecops_b200_matmul_run(problem, error);
+
+  // which kernel: the plain problem's choice, unless that kernel does not implement the transform
+  VecopsB200Matmul fused = *problem;
+  uint32_t kernel;
+  rc = select_kernel(fused, row, &kernel, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  const bool implements = kernel == VECOPS_B200_KERNEL_GENERIC || kernel == VECOPS_B200_KERNEL_F32_SIMT ||
+                          kernel == VECOPS_B200_KERNEL_BF16_TCGEN05 || kernel == VECOPS_B200_KERNEL_I8_TCGEN05;
+  if (!implements) {
+    if (problem->kernel != VECOPS_B200_KERNEL_AUTO || forced_by_environment() != VECOPS_B200_KERNEL_AUTO)
+      return set_error(error, VECOPS_STATUS_NOT_APPLICABLE, "kernel '%s' has no fused output transform", kKernelNames[kernel]);
+    fused.kernel = VECOPS_B200_KERNEL_GENERIC;
+  }
+  if (fused.k == 0)  // an empty reduction leaves transform(CIn): the strided kernel computes it with zero trips
+    fused.kernel = VECOPS_B200_KERNEL_GENERIC;
+  tl_epilogue = args;
+  rc = vecops_b200_matmul_run(&fused, error);
+  tl_epilogue = EpilogueArgs();
   return rc;
 }
 

@@ -2,6 +2,8 @@
 // unaligned problems, and the tiled FP32 FMA GEMM.
 #pragma once
 
+#include "epilogue.cuh"
+
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -51,7 +53,7 @@ template <typename TA, typename TB, typename TC, typename Acc>
 __global__ void __launch_bounds__(256)
 gemm_generic_kernel(const TA* __restrict__ a, long long sam, long long sak, const TB* __restrict__ b, long long sbn,
                     long long sbk, TC* __restrict__ c, long long scm, long long scn, int M, int N, int K,
-                    const float* __restrict__ column_scale) {
+                    const float* __restrict__ column_scale, EpilogueArgs ep) {
   constexpr int T = 32;
   __shared__ Acc as[T][T + 1];
   __shared__ Acc bs[T][T + 1];
@@ -86,8 +88,12 @@ gemm_generic_kernel(const TA* __restrict__ a, long long sam, long long sak, cons
     const int m = m0 + ty + 8 * j;
     if (m >= M) continue;
     Acc v = acc[j];
-    if constexpr (sizeof(Acc) == 4 && !std::is_same<Acc, uint32_t>::value) {
-      if (column_scale != nullptr) v *= column_scale[n];
+    if constexpr (std::is_same<Acc, float>::value) {
+      const float factor = column_scale != nullptr ? column_scale[n] : 1.f;
+      if (ep.active) v = epilogue_float(v, ep, m, n, factor);
+      else v *= factor;
+    } else if constexpr (std::is_same<Acc, uint32_t>::value) {
+      if (ep.active) v = epilogue_int(v, ep, m, n);
     }
     store_from<TC, Acc>(c + m * scm + n * scn, v);
   }
@@ -108,7 +114,7 @@ struct GemmF32 {
 
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ a, long long lda, const float* __restrict__ b, long long sbn,
-                long long sbk, float* __restrict__ c, long long ldc, int M, int N, int K) {
+                long long sbk, float* __restrict__ c, long long ldc, int M, int N, int K, EpilogueArgs ep) {
   using G = GemmF32;
   __shared__ __align__(16) float as[2][G::kDepth][G::kTile + G::kPad];
   __shared__ __align__(16) float bs[2][G::kDepth][G::kTile + G::kPad];
@@ -187,6 +193,11 @@ gemm_f32_kernel(const float* __restrict__ a, long long lda, const float* __restr
     if (m >= M) continue;
     float* dst = c + static_cast<long long>(m) * ldc + n0 + tx * 4;
     const int n = n0 + tx * 4;
+    if (ep.active) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (n + j < N) acc[i][j] = epilogue_float(acc[i][j], ep, m, n + j, 1.f);
+    }
     if (n + 3 < N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
       *reinterpret_cast<float4*>(dst) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
     } else {

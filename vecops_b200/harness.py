@@ -73,20 +73,41 @@ def attach_workspace(problem: capi.VecopsB200Matmul, device):
     return buffer
 
 
-def run(problem: capi.VecopsB200Matmul) -> None:
+def epilogue_record(cin=None, alpha: float = 1.0, activation: int = capi.ACTIVATION_NONE, clamp_lo: float = 0.0,
+                    clamp_hi: float = 0.0, rows: int | None = None, cols: int | None = None) -> capi.VecopsB200Epilogue:
+    """The fused output transform: COut = activation((CIn + A.B^T) * alpha * column_scale).
+
+    `cin` is a torch tensor broadcastable to [rows, cols] (a bias row [cols], a column [rows, 1], or the full matrix)."""
+    e = capi.VecopsB200Epilogue()
+    e.struct_size = ctypes.sizeof(capi.VecopsB200Epilogue)
+    e.activation, e.alpha, e.clamp_lo, e.clamp_hi = activation, alpha, clamp_lo, clamp_hi
+    if cin is not None:
+        view = cin.expand(rows, cols) if tuple(cin.shape) != (rows, cols) else cin
+        e.cin, e.cin_stride_m, e.cin_stride_n = view.data_ptr(), view.stride(0), view.stride(1)
+        e.cin_dtype = torch_dtype_code(view.dtype)
+    return e
+
+
+def run(problem: capi.VecopsB200Matmul, epilogue: capi.VecopsB200Epilogue | None = None) -> None:
     error = capi.ErrorBuffer()
-    error.raise_for(capi.library().vecops_b200_matmul_run(byref(problem), byref(error.record)))
+    if epilogue is None:
+        error.raise_for(capi.library().vecops_b200_matmul_run(byref(problem), byref(error.record)))
+    else:
+        error.raise_for(capi.library().vecops_b200_matmul_run_fused(byref(problem), byref(epilogue), byref(error.record)))
 
 
-def matmul(a, b_nk, c, scale=None, kernel: int = capi.KERNEL_AUTO, stream=None, asynchronous: bool = False) -> None:
-    """Run C = A . B^T on the GPU through the C ABI; raises VecopsB200Error on any failure."""
+def matmul(a, b_nk, c, scale=None, kernel: int = capi.KERNEL_AUTO, stream=None, asynchronous: bool = False, cin=None,
+           alpha: float = 1.0, activation: int = capi.ACTIVATION_NONE, clamp_lo: float = 0.0, clamp_hi: float = 0.0) -> None:
+    """Run C = A . B^T (or its fused form, see epilogue_record) on the GPU through the C ABI; raises VecopsB200Error."""
     import torch
     if stream is None and a.is_cuda:
         stream = torch.cuda.current_stream(a.device)
     problem = matmul_problem(a, b_nk, c, scale, kernel, stream, asynchronous)
+    fused = cin is not None or alpha != 1.0 or activation != capi.ACTIVATION_NONE
+    epilogue = epilogue_record(cin, alpha, activation, clamp_lo, clamp_hi, c.shape[0], c.shape[1]) if fused else None
     # freed after the call: torch's allocator re-issues the block only to later work on the same stream
     scratch = attach_workspace(problem, a.device) if a.is_cuda else None
-    run(problem)
+    run(problem, epilogue)
     del scratch
 
 
