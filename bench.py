@@ -205,8 +205,9 @@ def bound_of(w, peaks) -> tuple[str, float, float, str]:
     return "fp32_fma", NOMINAL["fp32_tflops"], NOMINAL["fp32_tflops"], "TFLOP/s"
 
 
-def measure_single(name: str, steps: int, warmup: int, dev, port, peaks) -> dict:
-    """One single-GPU configuration with operands resident in HBM."""
+def measure_single(name: str, steps: int, warmup: int, dev, port, peaks, fused: bool = False) -> dict:
+    """One single-GPU configuration with operands resident in HBM.  `fused`: the same launches with a bias row as the
+    accumulator input and SiLU as the output transform (what the fused epilogue costs on top of the plain GEMM)."""
     import torch
 
     import vecops_b200
@@ -219,15 +220,30 @@ def measure_single(name: str, steps: int, warmup: int, dev, port, peaks) -> dict
     stream = torch.cuda.current_stream(dev)
     kernel = vecops_b200.select_kernel(vecops_b200.matmul_problem(operands[0]["a"], operands[0]["b"], operands[0]["c"], operands[0]["scale"]))
 
-    prepared = [harness.PreparedMatmul(o["a"], o["b"], o["c"], o["scale"], stream=stream) for o in operands]
-    prepared[0].launch()
-    torch.cuda.synchronize()
-    parity = parity_sample(w, host_inputs, operands[0]["c"], port)
+    if fused:
+        from oracle.checker import ACT_SILU, bf16_bits_to_f32, rel_frobenius
+        bias_host = np.random.default_rng(5).uniform(-1, 1, w.n).astype(np.float32)
+        bias = torch.from_numpy(bias_host).to(dev)
+        record = harness.epilogue_record(bias, 1.0, capi.ACTIVATION_SILU, 0.0, 0.0, w.m, w.n)
+        prepared = [harness.PreparedMatmul(o["a"], o["b"], o["c"], o["scale"], stream=stream, epilogue=record, keep=(bias,)) for o in operands]
+        prepared[0].launch()
+        torch.cuda.synchronize()
+        a0, b0, _ = host_inputs
+        pick = np.unique(np.linspace(0, w.m - 1, 8).astype(np.int64))
+        got = operands[0]["c"][torch.from_numpy(pick).to(dev)].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+        want = port.matmul_bf16_fused(a0[pick], b0, bias_host, 1.0, None, ACT_SILU)
+        parity = {"rows": len(pick), "rel_fro": rel_frobenius(bf16_bits_to_f32(got), bf16_bits_to_f32(want))}
+    else:
+        prepared = [harness.PreparedMatmul(o["a"], o["b"], o["c"], o["scale"], stream=stream) for o in operands]
+        prepared[0].launch()
+        torch.cuda.synchronize()
+        parity = parity_sample(w, host_inputs, operands[0]["c"], port)
     ms = time_graph(prepared, steps, warmup, dev)
     status = take_status()
     bound, peak, nominal, unit = bound_of(w, peaks)
     achieved = (per_set / (ms * 1e-3) / 1e9) if bound == "hbm" else (w.flops / (ms * 1e-3) / 1e12)
-    return {"workload": name, "kernel": capi.library().vecops_b200_kernel_name(kernel).decode(), "ms_per_step": ms,
+    return {"workload": name + (" + bias row + SiLU, fused" if fused else ""), "kernel": capi.library().vecops_b200_kernel_name(kernel).decode(),
+            "ms_per_step": ms,
             "value": achieved, "unit": unit, "bound": bound, "frac_of_measured_peak": achieved / peak,
             "frac_of_nominal_peak": achieved / nominal, "tflops": w.flops / (ms * 1e-3) / 1e12,
             "algorithmic_gb_per_s": per_set / (ms * 1e-3) / 1e9, "l2": f"rotating {sets} operand sets ({sets * per_set / 1e6:.0f} MB) vs L2 126 MB",
@@ -621,6 +637,11 @@ def run_ours(args) -> None:
                 except Exception as error:
                     extras[extra] = {"error": repr(error)}
                 torch.cuda.empty_cache()
+            try:  # next-row feature: what the fused output transform costs on the headline shape
+                extras["c2_bf16_4096_fused_bias_silu"] = measure_single("c2_bf16_4096", 50, 5, dev, port, peaks, fused=True)
+            except Exception as error:
+                extras["c2_bf16_4096_fused_bias_silu"] = {"error": repr(error)}
+            torch.cuda.empty_cache()
             line["configs"] = extras
     if rank == 0:
         print(json.dumps(line), flush=True)

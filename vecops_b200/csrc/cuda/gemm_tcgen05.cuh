@@ -446,14 +446,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           if (item.slices > 1) add_partials(words, slab * 32);
           if constexpr (!kInt8) {
             if (ep.active) {
-              // the fused transform needs each element's own row and column (accumulator input, per-column factor)
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (row < M && col0 + j < N) {
-                  const float s = column_scale != nullptr ? __ldg(column_scale + col0 + j) : 1.f;
-                  words[j] = __float_as_uint(epilogue_float(__uint_as_float(words[j]), ep, row, col0 + j, s));
-                }
-              }
+              epilogue_float_row32(words, ep, column_scale, row, col0, M, N);
             } else if (column_scale != nullptr) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
@@ -462,11 +455,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
               }
             }
           } else {
-            if (ep.active) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (row < M && col0 + j < N) words[j] = epilogue_int(words[j], ep, row, col0 + j);
-            }
+            if (ep.active) epilogue_int_row32(words, ep, row, col0, M, N);
           }
         } else {
           uint32_t v0[32], v1[32];
@@ -478,17 +467,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             add_partials(v1, slab * 64 + 32);
           }
           if (ep.active) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (row < M && col0 + j < N) {
-                const float s0 = column_scale != nullptr ? __ldg(column_scale + col0 + j) : 1.f;
-                v0[j] = __float_as_uint(epilogue_float(__uint_as_float(v0[j]), ep, row, col0 + j, s0));
-              }
-              if (row < M && col0 + 32 + j < N) {
-                const float s1 = column_scale != nullptr ? __ldg(column_scale + col0 + 32 + j) : 1.f;
-                v1[j] = __float_as_uint(epilogue_float(__uint_as_float(v1[j]), ep, row, col0 + 32 + j, s1));
-              }
-            }
+            epilogue_float_row32(v0, ep, column_scale, row, col0, M, N);
+            epilogue_float_row32(v1, ep, column_scale, row, col0 + 32, M, N);
           } else if (column_scale != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {

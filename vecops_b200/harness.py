@@ -114,11 +114,14 @@ def matmul(a, b_nk, c, scale=None, kernel: int = capi.KERNEL_AUTO, stream=None, 
 class PreparedMatmul:
     """One problem record built once and launched many times (keeps per-launch host cost to a single C call)."""
 
-    def __init__(self, a, b_nk, c, scale=None, kernel: int = capi.KERNEL_AUTO, stream=None, asynchronous: bool = True) -> None:
+    def __init__(self, a, b_nk, c, scale=None, kernel: int = capi.KERNEL_AUTO, stream=None, asynchronous: bool = True,
+                 epilogue: capi.VecopsB200Epilogue | None = None, keep=()) -> None:
         import torch
         if stream is None and a.is_cuda:
             stream = torch.cuda.current_stream(a.device)
         self.tensors = (a, b_nk, c, scale)  # keep the storage alive
+        self.keep = keep                    # ... and whatever else the launch reads (the epilogue's accumulator input)
+        self.epilogue = epilogue
         self.problem = matmul_problem(a, b_nk, c, scale, kernel, stream, asynchronous)
         self.scratch = attach_workspace(self.problem, a.device) if a.is_cuda else None  # one buffer per prepared launch
         self.error = capi.ErrorBuffer()
@@ -127,7 +130,10 @@ class PreparedMatmul:
         self._error_ref = byref(self.error.record)
 
     def launch(self) -> None:
-        rc = self._run(self._problem_ref, self._error_ref)
+        if self.epilogue is None:
+            rc = self._run(self._problem_ref, self._error_ref)
+        else:
+            rc = capi.library().vecops_b200_matmul_run_fused(self._problem_ref, byref(self.epilogue), self._error_ref)
         if rc != capi.OK:
             self.error.raise_for(rc)
 
@@ -138,7 +144,7 @@ def capture_graph(launches, stream=None):
     side = stream or torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
-        prepared = [PreparedMatmul(*p.tensors, kernel=p.problem.kernel, stream=side) for p in launches]
+        prepared = [PreparedMatmul(*p.tensors, kernel=p.problem.kernel, stream=side, epilogue=p.epilogue, keep=p.keep) for p in launches]
         for p in prepared:  # warm up outside capture: one-time attribute and tensor-map set-up
             p.launch()
         side.synchronize()
