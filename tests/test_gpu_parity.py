@@ -542,3 +542,47 @@ def test_fused_form_refuses_what_int32_accumulators_cannot_do():
     with pytest.raises(capi.VecopsB200Error) as info:
         vecops_b200.matmul(a, a, c, cin=torch.zeros((16, 16), dtype=torch.float32, device="cuda"))
     assert info.value.code == capi.INVALID_ARGUMENT
+
+
+def _scalar_value(dtype_code, value):
+    v = capi.VecopsValue()
+    v.struct_size = ctypes.sizeof(capi.VecopsValue)
+    v.kind = capi.VALUE_SCALAR
+    v.value.scalar.struct_size = ctypes.sizeof(capi.VecopsScalar)
+    v.value.scalar.dtype = dtype_code
+    if dtype_code == capi.DTYPE_F32:
+        v.value.scalar.value.f64 = float(value)   # scalars travel widened, the dtype tag says what they were
+    else:
+        v.value.scalar.value.i64 = int(value)
+    return v
+
+
+def test_operator_bridge_carries_the_fused_form(port):
+    # a, b, c, column_scale = none, cin = a bias row (stride 0), alpha, activation, clamp_lo, clamp_hi
+    from oracle.checker import ACT_CLAMP
+    lib, handle = bridge_lib()
+    rng = np.random.default_rng(31)
+    m, n, k = 300, 520, 264
+    a, b, _ = inputs("bf16", m, n, k, rng)
+    a = f32_to_bf16_bits(bf16_bits_to_f32(a) * 0.1)
+    bias = rng.uniform(-1, 1, n).astype(np.float32)
+    da, db, dbias = to_device(a, True), to_device(b, True), to_device(bias)
+    c = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    keep = []
+    none = capi.VecopsValue()
+    none.struct_size = ctypes.sizeof(capi.VecopsValue)
+    none.kind = capi.VALUE_NONE
+    values = [_tensor_value(da, keep=keep), _tensor_value(db, keep=keep), _tensor_value(c, True, keep=keep), none,
+              _tensor_value(dbias.expand(m, n), keep=keep), _scalar_value(capi.DTYPE_F32, 0.5), _scalar_value(capi.DTYPE_I32, ACT_CLAMP),
+              _scalar_value(capi.DTYPE_F32, -0.75), _scalar_value(capi.DTYPE_F32, 1.25)]
+    array = (capi.VecopsValue * len(values))(*values)
+    context = capi.VecopsExecutionContext()
+    context.struct_size = ctypes.sizeof(context)
+    call = capi.VecopsCall(ctypes.sizeof(capi.VecopsCall), len(values), array, None, 0, ctypes.pointer(context))
+    error = capi.ErrorBuffer()
+    key = ctypes.create_string_buffer(256)
+    error.raise_for(lib.vecops_b200_operator_resolve(handle, byref(call), key, 256, byref(error.record)))
+    assert key.value.decode() == "vecops::matmul;TA=bf16;TB=bf16;TC=bf16;$0=0;$1=1;$2=f32;kernel=bf16_tcgen05"
+    error.raise_for(lib.vecops_operator_bridge_invoke_v1(handle, byref(call), 0, None, byref(error.record)))
+    want = port.matmul_bf16_fused(a, b, bias, 0.5, None, ACT_CLAMP, -0.75, 1.25)
+    check("bf16", bf16_result_to_numpy(c), want)

@@ -44,11 +44,25 @@ constexpr VecopsDimensionConstraint aligned_dim(std::int64_t alignment) {
   return {sizeof(VecopsDimensionConstraint), VECOPS_DIM_DYNAMIC, 0, 0, INT64_MAX, alignment};
 }
 
+// Parameters of every matmul specialization: a, b, c, column_scale?, cin?, alpha, activation, clamp_lo, clamp_hi.
+constexpr std::uint32_t kMatmulParameters = 9;
+
 struct VariantDescriptor {
-  VecopsDimensionConstraint a_sizes[2], a_strides[2], b_sizes[2], b_strides[2], c_sizes[2], c_strides[2], s_sizes[1], s_strides[1];
-  VecopsParameterDescriptor parameters[4];
+  VecopsDimensionConstraint a_sizes[2], a_strides[2], b_sizes[2], b_strides[2], c_sizes[2], c_strides[2], s_sizes[1], s_strides[1],
+      cin_sizes[2], cin_strides[2];
+  VecopsParameterDescriptor parameters[kMatmulParameters];
   VecopsKernelDescriptorV1 descriptor;
 };
+
+VecopsParameterDescriptor scalar_parameter(const char* name, std::uint64_t dtype_mask) {
+  VecopsParameterDescriptor p{};
+  p.struct_size = sizeof(VecopsParameterDescriptor);
+  p.kind = VECOPS_VALUE_SCALAR;
+  p.name = name;
+  p.constraint.scalar.struct_size = sizeof(VecopsScalarParameter);
+  p.constraint.scalar.dtype_mask = dtype_mask;
+  return p;
+}
 
 VecopsParameterDescriptor tensor_parameter(const char* name, std::uint64_t dtype_mask, std::int32_t rank,
                                            const VecopsDimensionConstraint* sizes, const VecopsDimensionConstraint* strides,
@@ -102,13 +116,22 @@ VariantDescriptor* build_variant(std::uint64_t a_mask, std::uint64_t b_mask, std
   v->parameters[1] = tensor_parameter("b", b_mask, 2, v->b_sizes, v->b_strides, false, false);
   v->parameters[2] = tensor_parameter("c", c_mask, 2, v->c_sizes, v->c_strides, false, true);
   v->parameters[3] = tensor_parameter("column_scale", bit(VECOPS_DTYPE_F32), 1, v->s_sizes, v->s_strides, true, false);
+  // the fused form's accumulator input (any strides, 0 included: a bias row or a column) and output transform
+  v->cin_sizes[0] = v->cin_sizes[1] = any_dim();
+  v->cin_strides[0] = v->cin_strides[1] = any_dim();
+  v->parameters[4] = tensor_parameter("cin", bit(VECOPS_DTYPE_F32) | bit(VECOPS_DTYPE_BF16) | bit(VECOPS_DTYPE_I32), 2, v->cin_sizes,
+                                      v->cin_strides, true, false);
+  v->parameters[5] = scalar_parameter("alpha", bit(VECOPS_DTYPE_F32));
+  v->parameters[6] = scalar_parameter("activation", bit(VECOPS_DTYPE_I32));
+  v->parameters[7] = scalar_parameter("clamp_lo", bit(VECOPS_DTYPE_F32));
+  v->parameters[8] = scalar_parameter("clamp_hi", bit(VECOPS_DTYPE_F32));
   auto& d = v->descriptor;
   d.struct_size = sizeof(VecopsKernelDescriptorV1);
   d.abi_version_major = VECOPS_KERNEL_ABI_VERSION_MAJOR;
   d.abi_version_minor = VECOPS_KERNEL_ABI_VERSION_MINOR;
   d.operator_name = kOperatorName;
   d.specialization_key = "";
-  d.num_parameters = 4;
+  d.num_parameters = kMatmulParameters;
   d.parameter_stride = sizeof(VecopsParameterDescriptor);
   d.parameters = v->parameters;
   d.workspace = &workspace_variant<kKernel>;
@@ -147,27 +170,48 @@ std::int32_t fail(VecopsError* error, std::int32_t code, const char* message) {
   return code;
 }
 
-std::int32_t problem_from_frame(const VecopsCall* call, std::uint32_t kernel, VecopsB200Matmul* out, VecopsError* error) {
+std::int32_t problem_from_frame(const VecopsCall* call, std::uint32_t kernel, VecopsB200Matmul* out, VecopsB200Epilogue* fused,
+                                VecopsError* error) {
   if (call == nullptr || call->struct_size < sizeof(VecopsCall)) return fail(error, VECOPS_STATUS_ABI_MISMATCH, "call frame is null or too small");
-  // a, b, c and the optional trailing column_scale (absent or VECOPS_VALUE_NONE = no scale)
-  if ((call->num_values != 3 && call->num_values != 4) || call->values == nullptr)
-    return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "matmul expects a, b, c and an optional column_scale");
-  const VecopsTensorView* t[4] = {nullptr, nullptr, nullptr, nullptr};
+  // a, b, c, then - each optional from the right - column_scale, cin (absent or VECOPS_VALUE_NONE = none), and the
+  // scalars alpha, activation, clamp_lo, clamp_hi (absent = 1, none, 0, 0)
+  if (call->num_values < 3 || call->num_values > kMatmulParameters || call->values == nullptr)
+    return fail(error, VECOPS_STATUS_INVALID_ARGUMENT,
+                "matmul expects a, b, c and optionally column_scale, cin, alpha, activation, clamp_lo, clamp_hi");
+  const VecopsTensorView* t[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+  VecopsB200Epilogue e{};
+  e.struct_size = sizeof(VecopsB200Epilogue);
+  e.alpha = 1.f;
   for (int i = 0; i < static_cast<int>(call->num_values); ++i) {
     const VecopsValue& value = call->values[i];
-    if (value.kind == VECOPS_VALUE_TENSOR) t[i] = &value.value.tensor;
-    else if (!(i == 3 && value.kind == VECOPS_VALUE_NONE)) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "matmul values must be tensors");
+    if (i < 5) {
+      if (value.kind == VECOPS_VALUE_TENSOR) t[i] = &value.value.tensor;
+      else if (!(i >= 3 && value.kind == VECOPS_VALUE_NONE)) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "matmul operands must be tensors");
+      continue;
+    }
+    if (value.kind != VECOPS_VALUE_SCALAR) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "alpha, activation, clamp_lo and clamp_hi are scalars");
+    const VecopsScalar& scalar = value.value.scalar;
+    const bool is_f32 = scalar.dtype == VECOPS_DTYPE_F32;
+    if (i == 6) {
+      // (scalars travel widened: integers in i64, floating point in f64, with the dtype tag saying what they were)
+      if (scalar.dtype != VECOPS_DTYPE_I32 || scalar.value.i64 < 0) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "activation is a non-negative i32");
+      e.activation = static_cast<std::uint32_t>(scalar.value.i64);
+    } else {
+      if (!is_f32) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "alpha, clamp_lo and clamp_hi are f32");
+      (i == 5 ? e.alpha : i == 7 ? e.clamp_lo : e.clamp_hi) = static_cast<float>(scalar.value.f64);
+    }
   }
-  if (t[0]->rank != 2 || t[1]->rank != 2 || t[2]->rank != 2 || (t[3] != nullptr && t[3]->rank != 1))
-    return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "matmul wants rank-2 a, b, c and a rank-1 column_scale");
+  if (t[0]->rank != 2 || t[1]->rank != 2 || t[2]->rank != 2 || (t[3] != nullptr && t[3]->rank != 1) || (t[4] != nullptr && t[4]->rank != 2))
+    return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "matmul wants rank-2 a, b, c, cin and a rank-1 column_scale");
   VecopsB200Matmul p{};
   p.struct_size = sizeof(VecopsB200Matmul);
   p.kernel = kernel;
   p.m = t[0]->sizes[0];
   p.k = t[0]->sizes[1];
   p.n = t[1]->sizes[0];
-  if (t[1]->sizes[1] != p.k || t[2]->sizes[0] != p.m || t[2]->sizes[1] != p.n || (t[3] != nullptr && t[3]->sizes[0] != p.n))
-    return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "matmul extents disagree: a[M,K] b[N,K] c[M,N] column_scale[N]");
+  if (t[1]->sizes[1] != p.k || t[2]->sizes[0] != p.m || t[2]->sizes[1] != p.n || (t[3] != nullptr && t[3]->sizes[0] != p.n) ||
+      (t[4] != nullptr && (t[4]->sizes[0] != p.m || t[4]->sizes[1] != p.n)))
+    return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "matmul extents disagree: a[M,K] b[N,K] c[M,N] column_scale[N] cin[M,N]");
   auto base = [](const VecopsTensorView* v) { return static_cast<char*>(v->data) + v->byte_offset; };
   p.a = base(t[0]);
   p.a_stride_m = t[0]->strides[0];
@@ -181,6 +225,12 @@ std::int32_t problem_from_frame(const VecopsCall* call, std::uint32_t kernel, Ve
   if (t[3] != nullptr) {
     if (t[3]->strides[0] != 1 && p.n > 1) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "column_scale must be contiguous");
     p.column_scale = reinterpret_cast<const float*>(base(t[3]));
+  }
+  if (t[4] != nullptr) {
+    e.cin = base(t[4]);
+    e.cin_stride_m = t[4]->strides[0];
+    e.cin_stride_n = t[4]->strides[1];
+    e.cin_dtype = t[4]->dtype;
   }
   p.a_dtype = t[0]->dtype;
   p.b_dtype = t[1]->dtype;
@@ -196,14 +246,18 @@ std::int32_t problem_from_frame(const VecopsCall* call, std::uint32_t kernel, Ve
       p.flags |= VECOPS_B200_MATMUL_FLAG_ASYNC;
   }
   *out = p;
+  if (fused != nullptr) *fused = e;
   return VECOPS_STATUS_OK;
 }
 
+bool transform_present(const VecopsB200Epilogue& e) { return e.cin != nullptr || e.alpha != 1.f || e.activation != VECOPS_B200_ACTIVATION_NONE; }
+
 std::int32_t run_with(std::uint32_t kernel, const VecopsCall* call, VecopsError* error, bool only_workspace, std::uint64_t* bytes) {
   VecopsB200Matmul problem;
-  if (const auto rc = problem_from_frame(call, kernel, &problem, error); rc != VECOPS_STATUS_OK) return rc;
+  VecopsB200Epilogue fused;
+  if (const auto rc = problem_from_frame(call, kernel, &problem, &fused, error); rc != VECOPS_STATUS_OK) return rc;
   if (only_workspace) return vecops_b200_matmul_workspace(&problem, bytes, error);
-  return vecops_b200_matmul_run(&problem, error);
+  return transform_present(fused) ? vecops_b200_matmul_run_fused(&problem, &fused, error) : vecops_b200_matmul_run(&problem, error);
 }
 
 }  // namespace
@@ -230,7 +284,14 @@ KernelDef matmul_kernel_def() {
                    {tensor("a", {M(), K()}, "TA", TensorAccess::Input, false),
                     tensor("b", {N(), K()}, "TB", TensorAccess::Input, false),
                     tensor("c", {M(), N()}, "TC", TensorAccess::Output, false),
-                    tensor("column_scale", {N()}, DType::Float32, TensorAccess::Input, true)},
+                    tensor("column_scale", {N()}, DType::Float32, TensorAccess::Input, true),
+                    // the fused form COut = activation((CIn + A.B^T) * alpha * column_scale): vecops' explicit accumulate form
+                    // (ops/Matmul.h:519-570) with the output transforms its fusion tests compose, as parameters
+                    tensor("cin", {M(), N()}, TensorDTypeDef(), TensorAccess::Input, true),
+                    ValueDef{"alpha", DType::Float32, Scalar::floating(1.0, DType::Float32)},
+                    ValueDef{"activation", DType::Int32, Scalar::signed_integer(0, DType::Int32)},
+                    ValueDef{"clamp_lo", DType::Float32, Scalar::floating(0.0, DType::Float32)},
+                    ValueDef{"clamp_hi", DType::Float32, Scalar::floating(0.0, DType::Float32)}},
                    {{"TA", SpecializationType::DType}, {"TB", SpecializationType::DType}, {"TC", SpecializationType::DType}});
 }
 
@@ -239,7 +300,7 @@ Result<VecopsB200Matmul> matmul_problem_from(std::span<const Value> values, std:
   CallFrame frame(arguments);
   VecopsB200Matmul problem;
   ErrorText error;
-  if (const auto rc = problem_from_frame(&frame.abi(), kernel, &problem, &error.record); rc != VECOPS_STATUS_OK) return error.status(rc);
+  if (const auto rc = problem_from_frame(&frame.abi(), kernel, &problem, nullptr, &error.record); rc != VECOPS_STATUS_OK) return error.status(rc);
   return problem;
 }
 
