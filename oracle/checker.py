@@ -55,6 +55,7 @@ def _strides(array: np.ndarray) -> tuple[int, int]:
 
 
 ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SILU, ACT_CLAMP = range(5)
+_F = ctypes.c_float
 
 
 def _cin_view(cin, m: int, n: int):
@@ -85,6 +86,10 @@ class Port:
                                                                  _I64, _I64]
         self.lib.oracle_matmul_i8_accumulate.argtypes = [_I64] * 3 + [_P, _I64, _I64, c_int, _P, _I64, _I64, c_int, _P, _I64, _I64, _P, _I64,
                                                                      _I64]
+
+        self.lib.oracle_quantize_rows.argtypes = [_I64, _I64, _P, _I64, _I64, _F, _F, _P, _I64, _I64, c_int]
+        self.lib.oracle_matmul_i8_dequant.argtypes = [_I64] * 3 + [_P, _I64, _I64, c_int, _P, _I64, _I64, c_int, _P, _I64, _I64, _F, _P, c_int,
+                                                                  _F, _F, _P, _I64, _I64, c_int]
 
     @property
     def threads(self) -> int:
@@ -157,6 +162,26 @@ class Port:
         return c
 
 
+    # ---- the quantised form: 8-bit operands, int32 accumulate + int32 accumulator input, float output transform
+
+    def quantize_rows(self, a_f32, scale, zero_point, signed=False):
+        m, k = a_f32.shape
+        out = np.empty((m, k), dtype=np.int8 if signed else np.uint8)
+        self.lib.oracle_quantize_rows(m, k, _ptr(a_f32), *_strides(a_f32), float(scale), float(zero_point), _ptr(out), k, 1, int(signed))
+        return out
+
+    def matmul_i8_dequant(self, a, b_nk, cin=None, alpha=1.0, scale=None, act=ACT_NONE, lo=0.0, hi=0.0, out_bf16=False):
+        m, k = a.shape
+        n = b_nk.shape[0]
+        c = np.empty((m, n), dtype=np.uint16 if out_bf16 else np.float32)
+        cin_view, _ = _cin_view(cin, m, n)
+        self.lib.oracle_matmul_i8_dequant(m, n, k, _ptr(a), *_strides(a), int(a.dtype == np.int8), _ptr(b_nk), *_strides(b_nk),
+                                          int(b_nk.dtype == np.int8), _ptr(cin_view),
+                                          *(_strides(cin_view) if cin_view is not None else (0, 0)), float(alpha), _ptr(scale), int(act),
+                                          float(lo), float(hi), _ptr(c), n, 1, int(out_bf16))
+        return c
+
+
 class Ref:
     """The reference's own ops::matmul.  ``Ref.load()`` returns None when unavailable here."""
 
@@ -171,6 +196,18 @@ class Ref:
         if hasattr(lib, "ref_matmul_bf16_fused"):
             lib.ref_matmul_bf16_fused.argtypes = [_I64] * 3 + [_P, _I64, _P, _I64, _P, _I64, _I64, _F, _P, c_int, _F, _F, _P, _I64, c_int]
             lib.ref_matmul_i8_accumulate.argtypes = [_I64] * 3 + [_P, _I64, _P, _I64, _P, _I64, _I64, _P, _I64]
+        if hasattr(lib, "ref_matmul_quantized_u8s8"):
+            lib.ref_matmul_quantized_u8s8.argtypes = [_I64] * 3 + [_P, _I64, _F, _F, _P, _I64, _P, _F, _P, _I64]
+
+    def matmul_quantized_u8s8(self, a_f32, a_scale, a_zero_point, b_nk, correction, dequant):
+        """fp32 A quantised on load to u8, s8 B, int32 correction row, dequantising output transform, fp32 C."""
+        m, k = a_f32.shape
+        n = b_nk.shape[0]
+        c = np.empty((m, n), dtype=np.float32)
+        rc = self.lib.ref_matmul_quantized_u8s8(m, n, k, _ptr(a_f32), self._rows(a_f32), float(a_scale), float(a_zero_point), _ptr(b_nk),
+                                                self._rows(b_nk), _ptr(correction), float(dequant), _ptr(c), n)
+        assert rc == 0
+        return c
 
     def matmul_bf16_fused(self, a, b_nk, cin=None, alpha=1.0, scale=None, act=ACT_NONE, lo=0.0, hi=0.0, out_bf16=True):
         """The reference's explicit accumulate form with one composed output transform; `cin` float32 or None.

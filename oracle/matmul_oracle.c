@@ -196,6 +196,52 @@ void oracle_matmul_i8_accumulate(int64_t m, int64_t n, int64_t k, const void* a,
   }
 }
 
+/* The quantised form as the reference ships it (tests/ops/MatmulConversionTestCommon.h:501-618 check_asymmetric_quantized):
+ * A quantised on load, value * scale + zero_point converted to the 8-bit compute type by truncation toward zero with
+ * saturation (observed by running the reference: 3.51 -> 3, 255.6 -> 255, -0.6 -> 0, 1e9 -> 255); 8-bit B; an int32
+ * accumulator input (the correction row -zero_point * sum_k B[n,k]); int32 accumulate, wrapping; then the float output
+ * transform on the converted accumulator: activation(float(acc) * alpha * column_scale[n]). */
+void oracle_quantize_rows(int64_t m, int64_t k, const float* src, int64_t ssm, int64_t ssk, float scale, float zero_point,
+                          void* dst, int64_t dsm, int64_t dsk, int dst_signed) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < m; ++i) {
+    for (int64_t j = 0; j < k; ++j) {
+      float q = truncf(src[i * ssm + j * ssk] * scale + zero_point);
+      if (dst_signed) {
+        q = q < -128.f ? -128.f : (q > 127.f ? 127.f : q);
+        if (q != q) q = 0.f;
+        ((int8_t*)dst)[i * dsm + j * dsk] = (int8_t)q;
+      } else {
+        q = q < 0.f ? 0.f : (q > 255.f ? 255.f : q);
+        if (q != q) q = 0.f;
+        ((uint8_t*)dst)[i * dsm + j * dsk] = (uint8_t)q;
+      }
+    }
+  }
+}
+
+void oracle_matmul_i8_dequant(int64_t m, int64_t n, int64_t k, const void* a, int64_t sam, int64_t sak, int a_signed,
+                              const void* b, int64_t sbn, int64_t sbk, int b_signed, const int32_t* cin, int64_t cin_sm,
+                              int64_t cin_sn, float alpha, const float* column_scale, int act, float lo, float hi, void* c,
+                              int64_t scm, int64_t scn, int c_is_bf16) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t i = 0; i < m; ++i) {
+    for (int64_t j = 0; j < n; ++j) {
+      uint32_t sum = cin ? (uint32_t)cin[i * cin_sm + j * cin_sn] : 0u;
+      for (int64_t kk = 0; kk < k; ++kk) {
+        const int32_t x = a_signed ? ((const int8_t*)a)[i * sam + kk * sak] : ((const uint8_t*)a)[i * sam + kk * sak];
+        const int32_t y = b_signed ? ((const int8_t*)b)[j * sbn + kk * sbk] : ((const uint8_t*)b)[j * sbn + kk * sbk];
+        sum += (uint32_t)(x * y);
+      }
+      float acc = (float)(int32_t)sum * alpha;
+      if (column_scale) acc *= column_scale[j];
+      acc = oracle_activation(acc, act, lo, hi);
+      if (c_is_bf16) ((uint16_t*)c)[i * scm + j * scn] = f32_to_bf16(acc);
+      else ((float*)c)[i * scm + j * scn] = acc;
+    }
+  }
+}
+
 /* How many threads the loops above use (1 when built without OpenMP). */
 #ifdef _OPENMP
 #include <omp.h>

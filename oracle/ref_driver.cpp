@@ -206,6 +206,34 @@ int ref_matmul_i8_accumulate(int64_t m, int64_t n, int64_t k, const int8_t* a, i
   return 0;
 }
 
+// The asymmetric quantised form as the reference ships it (tests/ops/MatmulConversionTestCommon.h:501-618
+// check_asymmetric_quantized): fp32 A quantised on load to u8 (value * a_scale + a_zero_point, converted like the
+// reference converts), s8 B read directly, an int32 correction row (-zero_point * column sums of B) as the accumulator
+// input, and a dequantising output transform (accumulator * dequant) to an fp32 C.  AMX_I8I32<uint8_t, int8_t>.
+int ref_matmul_quantized_u8s8(int64_t m, int64_t n, int64_t k, const float* a, int64_t lda, float a_scale, float a_zero_point,
+                              const int8_t* b, int64_t ldb, const int32_t* correction, float dequant, float* c, int64_t ldc) {
+  if (!request_amx()) return 1;
+  auto at = make_tensor(a, make_layout(make_shape(Any{m}, Any{k}), make_strides(Any{lda}, cint<1>)));
+  auto bt = make_tensor(b, make_layout(make_shape(Any{n}, Any{k}), make_strides(Any{ldb}, cint<1>)));
+  auto ct = make_tensor(c, make_layout(make_shape(Any{m}, Any{n}), make_strides(Any{ldc}, cint<1>)));
+  auto correction_tensor = make_tensor(correction, make_layout(make_shape(Any{m}, Any{n}), make_strides(cint<0>, cint<1>)));
+  auto quantize_a = make_elementwise_vec_transform<float32_t, float32_t>([=](auto tag, auto value) VECOPS_KERNEL_LAMBDA {
+    return vec::add(tag, vec::mul(tag, value, vec::fill(tag, a_scale)), vec::fill(tag, a_zero_point));
+  });
+  auto dequantize = make_elementwise_vec_transform<float32_t, float32_t>([=](auto tag, auto value) VECOPS_KERNEL_LAMBDA {
+    return vec::mul(tag, value, vec::fill(tag, dequant));
+  });
+  auto ai = input<uint8_t>(at, quantize_a);
+  auto bi = input<int8_t>(bt);
+  auto ci = input<int32_t>(correction_tensor);
+  auto co = output<int32_t>(ct, dequantize);
+  auto op = ops::matmul(ops::MatmulConfig<matmul::AMX_I8I32<uint8_t, int8_t>>{});
+  kernel::Workspace storage(op.required_workspace(Any{m}, Any{n}, Any{k}, ai, bi, ci, co));
+  auto view = storage.view();
+  op(view, Any{m}, Any{n}, Any{k}, ai, bi, ci, co);
+  return 0;
+}
+
 // fp32: the reference has no fp32 matmul atom on x86; its only fp32 x fp32
 // product code is the AVX-512 vector leaf (amx/Backend.h:767-901) instantiated
 // with equal types.  B is [N,K] here.

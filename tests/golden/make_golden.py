@@ -127,6 +127,23 @@ def main() -> None:
         cin = ((np.arange(m * n, dtype=np.int64) * 37) % 1001 - 500).astype(np.int32).reshape(m, n)
         cases[f"i8acc_{m}x{n}x{k}"] = dict(kind="i8acc", a=a, b=b, cin=cin, c=ref.matmul_i8_accumulate(a, b, cin))
 
+    # the quantised form as shipped (check_asymmetric_quantized, MatmulConversionTestCommon.h:501-618): fp32 A quantised on
+    # load to u8 (value * 4 + 3), s8 B, correction row -3 * column sums of B, dequantising transform * 0.0625, fp32 C
+    for m, n, k in [(19, 23, 65), (32, 64, 128), (1, 8, 129)]:
+        a = conversion_pattern(m * k, 3, np.float32).reshape(m, k)
+        b = conversion_pattern(n * k, 11, np.int8).reshape(n, k)
+        correction = (-3 * b.astype(np.int64).sum(axis=1)).astype(np.int32)
+        cases[f"quant_u8s8_{m}x{n}x{k}"] = dict(kind="quant_u8s8", a=a, a_scale=np.float32(4.0), a_zero_point=np.float32(3.0), b=b,
+                                                correction=correction, dequant=np.float32(0.0625),
+                                                c=ref.matmul_quantized_u8s8(a, 4.0, 3.0, b, correction, 0.0625))
+    rng = np.random.default_rng(4)  # out-of-range activations: the conversion saturates
+    a = rng.uniform(-40, 80, (33, 96)).astype(np.float32)
+    b = rng.integers(-128, 128, (47, 96), dtype=np.int8)
+    correction = (-7 * b.astype(np.int64).sum(axis=1)).astype(np.int32)
+    cases["quant_u8s8_saturating_33x47x96"] = dict(kind="quant_u8s8", a=a, a_scale=np.float32(2.5), a_zero_point=np.float32(7.0), b=b,
+                                                   correction=correction, dequant=np.float32(0.01),
+                                                   c=ref.matmul_quantized_u8s8(a, 2.5, 7.0, b, correction, 0.01))
+
     for name, arrays in cases.items():
         kind = arrays.pop("kind")
         np.savez_compressed(HERE / f"{name}.npz", kind=np.array(kind), **arrays)

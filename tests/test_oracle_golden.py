@@ -46,10 +46,14 @@ def test_port_matches_golden_fixtures(port, golden):
             assert rel_frobenius(got, bf16_bits_to_f32(case["c_bf16"])) <= TOL_BF16, name
         elif kind == "i8acc":
             assert np.array_equal(port.matmul_i8_accumulate(a, b, case["cin"]), case["c"]), name
+        elif kind == "quant_u8s8":
+            quantized = port.quantize_rows(a, float(case["a_scale"]), float(case["a_zero_point"]))
+            got = port.matmul_i8_dequant(quantized, b, case["correction"], float(case["dequant"]))
+            assert np.array_equal(got, case["c"]), name
         else:
             raise AssertionError(f"unknown fixture kind {kind}")
         checked += 1
-    assert checked >= 30
+    assert checked >= 34
 
 
 def test_int32_accumulator_wraps(port):
