@@ -21,6 +21,10 @@
  *     bf16   bf16   f32    opt.    f32          AMX_BF16F32
  *     i8/u8  i8/u8  i32    -       i32 (wraps)  AMX_I8I32<A,B>
  *     bf16   i8     bf16   opt.    f32          AMX_BF16F32 with input<bfloat16_t>(int8 W)
+ *     i8/u8  i8/u8  f32|bf16 opt.  i32 (wraps)  AMX_I8I32<A,B> with a dequantising output<int32_t>(float C) transform
+ *                                               (tests/ops/MatmulConversionTestCommon.h:501-618): the int32 sum - plus, in
+ *                                               the fused form, an int32 accumulator input such as the zero-point
+ *                                               correction row - is converted and then scaled / activated
  *
  * All pointers are DEVICE pointers on `device_index`; strides count elements.
  * Nothing here allocates device memory: scratch is passed in by the caller
@@ -215,6 +219,19 @@ typedef struct VecopsB200Gather {
 
 VECOPS_B200_EXPORT int32_t vecops_b200_matmul_allgather_run(const VecopsB200Matmul* problem, const VecopsB200Gather* gather,
                                                             VecopsError* error);
+
+/* Quantise-on-load, done ahead of the product: dst[m,k] = convert(src[m,k] * scale + zero_point) with vecops' conversion of
+ * an fp32 memory element to an 8-bit compute element - truncation toward zero, saturating (quantize_a in
+ * tests/ops/MatmulConversionTestCommon.h:549-556).  src f32 or bf16 with element strides; dst u8 or i8, K-contiguous rows. */
+VECOPS_B200_EXPORT int32_t vecops_b200_quantize_rows(const void* src, uint32_t src_dtype, int64_t src_stride_m, int64_t src_stride_k,
+                                                     void* dst, uint32_t dst_dtype, int64_t dst_stride_m, int64_t rows, int64_t cols,
+                                                     float scale, float zero_point, void* stream, VecopsError* error);
+
+/* out[n] = -zero_point * sum_k B[n,k] for an 8-bit K-contiguous B[N,K]: the int32 accumulator-input row (stride_m = 0) that
+ * removes the activations' zero point from an asymmetric product (MatmulConversionTestCommon.h:529-541; the compensation
+ * ops::matmul_pack_b_compensated computes, ops/MatmulPack.h:28-35). */
+VECOPS_B200_EXPORT int32_t vecops_b200_column_correction(const void* b, uint32_t b_dtype, int64_t b_stride_n, int64_t n, int64_t k,
+                                                         int32_t zero_point, int32_t* out, void* stream, VecopsError* error);
 
 /* Strided gather of column slabs: dst[M, ldd] columns [col0, col0+cols) <-
  * src[M, cols] (row pitch lds), `elem_size` bytes per element.  Used after the

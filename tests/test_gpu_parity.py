@@ -79,7 +79,7 @@ def test_golden_fixtures_through_automatic_dispatch(golden):
     for name, case in golden.items():
         kind = str(case["kind"])
         a, b = case["a"], case["b"]
-        if kind in ("fused_bf16", "i8acc"):
+        if kind in ("fused_bf16", "i8acc", "quant_u8s8"):
             continue  # the fused forms have their own test below
         if kind == "i8":
             check(kind, run_case(kind, a, b), case["c"], name)
@@ -586,3 +586,61 @@ def test_operator_bridge_carries_the_fused_form(port):
     error.raise_for(lib.vecops_operator_bridge_invoke_v1(handle, byref(call), 0, None, byref(error.record)))
     want = port.matmul_bf16_fused(a, b, bias, 0.5, None, ACT_CLAMP, -0.75, 1.25)
     check("bf16", bf16_result_to_numpy(c), want)
+
+
+# ------------------------------------------------------------------ the quantised form as the reference ships it
+
+def _quantized_gpu(a_f32, a_scale, a_zp, b, dequant, kernel, out_dtype=torch.float32, scale=None, act=0):
+    """quantise-on-load pre-pass, correction row, u8 x s8 product with int32 accumulate, dequantising transform."""
+    m, k = a_f32.shape
+    n = b.shape[0]
+    da = to_device(a_f32)
+    qa = torch.empty((m, k), dtype=torch.uint8, device="cuda")
+    harness.quantize_rows(da, qa, a_scale, a_zp)
+    db = to_device(b)
+    correction = torch.empty(n, dtype=torch.int32, device="cuda")
+    harness.column_correction(db, int(a_zp), correction)
+    c = torch.full((m, n), -3, dtype=out_dtype, device="cuda")
+    ds = to_device(scale) if scale is not None else None
+    vecops_b200.matmul(qa, db, c, ds, kernel=kernel, cin=correction, alpha=dequant, activation=act)
+    torch.cuda.synchronize()
+    return qa.cpu().numpy(), correction.cpu().numpy(), (bf16_result_to_numpy(c) if out_dtype == torch.bfloat16 else c.cpu().numpy())
+
+
+def test_quantized_golden_fixtures(golden, port):
+    seen = 0
+    for name, case in golden.items():
+        if str(case["kind"]) != "quant_u8s8":
+            continue
+        for kernel in (K.KERNEL_AUTO, K.KERNEL_GENERIC):
+            qa, correction, got = _quantized_gpu(case["a"], float(case["a_scale"]), float(case["a_zero_point"]), case["b"],
+                                                 float(case["dequant"]), kernel)
+            assert np.array_equal(qa, port.quantize_rows(case["a"], float(case["a_scale"]), float(case["a_zero_point"]))), name
+            assert np.array_equal(correction, case["correction"]), name
+            assert np.array_equal(got, case["c"]), name   # integers converted and multiplied by a power of two: exact
+        seen += 1
+    assert seen >= 4
+
+
+@pytest.mark.parametrize("m,n,k", [(384, 512, 1024), (1536, 3584, 1024)])  # the second: split tail tiles
+def test_quantized_form_on_the_tensor_cores(port, cta_form, m, n, k):
+    from oracle.checker import ACT_RELU
+    rng = np.random.default_rng(m + k)
+    a = rng.uniform(-30, 60, (m, k)).astype(np.float32)
+    b = rng.integers(-128, 128, (n, k), dtype=np.int8)
+    scale = rng.uniform(0.5, 2.0, n).astype(np.float32)
+    rows = np.unique(np.concatenate([np.linspace(0, m - 1, 12).astype(np.int64), np.arange(m - 4, m)]))
+    for out_dtype in (torch.float32, torch.bfloat16):
+        qa, correction, got = _quantized_gpu(a, 2.0, 5.0, b, 0.01, K.KERNEL_I8_TCGEN05, out_dtype, scale, ACT_RELU)
+        assert np.array_equal(qa, port.quantize_rows(a, 2.0, 5.0))
+        assert np.array_equal(correction, (-5 * b.astype(np.int64).sum(axis=1)).astype(np.int32))
+        want = port.matmul_i8_dequant(qa[rows], b, correction, 0.01, scale, ACT_RELU, out_bf16=out_dtype == torch.bfloat16)
+        if out_dtype == torch.float32:
+            assert rel_frobenius(got[rows], want) <= 1e-6
+        else:
+            check("bf16", got[rows], want)
+    # the plain call of this dtype row: C = float(A . B^T)
+    da, db = to_device(qa), to_device(b)
+    c = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    vecops_b200.matmul(da, db, c, kernel=K.KERNEL_I8_TCGEN05)
+    assert np.array_equal(c.cpu().numpy()[rows], port.matmul_i8(qa[rows], b).astype(np.float32))

@@ -134,6 +134,9 @@ def library() -> ctypes.CDLL:
         lib.vecops_b200_matmul_workspace.argtypes = [POINTER(VecopsB200Matmul), POINTER(c_uint64), e]
         lib.vecops_b200_matmul_run.argtypes = [POINTER(VecopsB200Matmul), e]
         lib.vecops_b200_matmul_run_fused.argtypes = [POINTER(VecopsB200Matmul), POINTER(VecopsB200Epilogue), e]
+        lib.vecops_b200_quantize_rows.argtypes = [c_void_p, c_uint32, c_int64, c_int64, c_void_p, c_uint32, c_int64, c_int64, c_int64, c_float,
+                                                  c_float, c_void_p, e]
+        lib.vecops_b200_column_correction.argtypes = [c_void_p, c_uint32, c_int64, c_int64, c_int64, c_int32, c_void_p, c_void_p, e]
         lib.vecops_b200_matmul_allgather_run.argtypes = [POINTER(VecopsB200Matmul), POINTER(VecopsB200Gather), e]
         lib.vecops_b200_kernel_name.argtypes = [c_uint32]
         lib.vecops_b200_kernel_name.restype = c_char_p

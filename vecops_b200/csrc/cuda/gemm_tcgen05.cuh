@@ -435,6 +435,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           }
         }
       };
+      // accumulators of 32 consecutive columns of this thread's row -> what gets stored (still as 32-bit patterns):
+      // int32 accumulators take their int32 accumulator input; when the output is floating point they are then converted
+      // and run through the float transform (the dequantising form); fp32 accumulators take the float transform or, for
+      // the plain GEMM, just the column scale
+      auto transform32 = [&](uint32_t (&v)[32], int first_col) {
+        if constexpr (kInt8) {
+          if (ep.active) epilogue_int_row32(v, ep, row, first_col, M, N);
+          if constexpr (!std::is_same<OutT, int32_t>::value) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(static_cast<float>(static_cast<int32_t>(v[j])));
+            if (ep.active || column_scale != nullptr) epilogue_float_row32(v, ep, column_scale, row, first_col, M, N);
+          }
+        } else {
+          if (ep.active) {
+            epilogue_float_row32(v, ep, column_scale, row, first_col, M, N);
+          } else if (column_scale != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float s = (first_col + j < N) ? __ldg(column_scale + first_col + j) : 0.f;
+              v[j] = __float_as_uint(__uint_as_float(v[j]) * s);
+            }
+          }
+        }
+      };
 #pragma unroll 1
       for (int slab = slab_begin; slab < slab_end; ++slab) {
         const int col0 = tn * G::kBlockN + slab * kOutCols;
@@ -444,19 +468,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           tmem_load_32x32(taddr + slab * 32, words);
           tmem_load_wait();
           if (item.slices > 1) add_partials(words, slab * 32);
-          if constexpr (!kInt8) {
-            if (ep.active) {
-              epilogue_float_row32(words, ep, column_scale, row, col0, M, N);
-            } else if (column_scale != nullptr) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const float s = (col0 + j < N) ? __ldg(column_scale + col0 + j) : 0.f;
-                words[j] = __float_as_uint(__uint_as_float(words[j]) * s);
-              }
-            }
-          } else {
-            if (ep.active) epilogue_int_row32(words, ep, row, col0, M, N);
-          }
+          transform32(words, col0);
         } else {
           uint32_t v0[32], v1[32];
           tmem_load_32x32(taddr + slab * 64, v0);
@@ -466,18 +478,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             add_partials(v0, slab * 64);
             add_partials(v1, slab * 64 + 32);
           }
-          if (ep.active) {
-            epilogue_float_row32(v0, ep, column_scale, row, col0, M, N);
-            epilogue_float_row32(v1, ep, column_scale, row, col0 + 32, M, N);
-          } else if (column_scale != nullptr) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float s0 = (col0 + j < N) ? __ldg(column_scale + col0 + j) : 0.f;
-              const float s1 = (col0 + 32 + j < N) ? __ldg(column_scale + col0 + 32 + j) : 0.f;
-              v0[j] = __float_as_uint(__uint_as_float(v0[j]) * s0);
-              v1[j] = __float_as_uint(__uint_as_float(v1[j]) * s1);
-            }
-          }
+          transform32(v0, col0);
+          transform32(v1, col0 + 32);
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             words[j] = pack_bf16x2(__uint_as_float(v0[2 * j]), __uint_as_float(v0[2 * j + 1]));

@@ -115,7 +115,7 @@ int32_t current_device(const VecopsB200Matmul& p, int* device, VecopsError* erro
 
 // ------------------------------------------------------------------ problem classification
 
-enum class Row { Invalid, F32, BF16, I8, W8 };
+enum class Row { Invalid, F32, BF16, I8, W8, QI8 };  // QI8: 8-bit operands, int32 accumulate, floating-point output (dequantising form)
 
 size_t dtype_size(uint32_t dtype) {
   switch (dtype) {
@@ -133,6 +133,7 @@ Row classify(const VecopsB200Matmul& p) {
   if (a == VECOPS_DTYPE_F32 && b == VECOPS_DTYPE_F32 && c == VECOPS_DTYPE_F32) return Row::F32;
   if (a == VECOPS_DTYPE_BF16 && b == VECOPS_DTYPE_BF16 && (c == VECOPS_DTYPE_BF16 || c == VECOPS_DTYPE_F32)) return Row::BF16;
   if (a8 && b8 && c == VECOPS_DTYPE_I32) return Row::I8;
+  if (a8 && b8 && (c == VECOPS_DTYPE_F32 || c == VECOPS_DTYPE_BF16)) return Row::QI8;
   if (a == VECOPS_DTYPE_BF16 && b == VECOPS_DTYPE_I8 && (c == VECOPS_DTYPE_BF16 || c == VECOPS_DTYPE_F32)) return Row::W8;
   return Row::Invalid;
 }
@@ -164,7 +165,7 @@ bool applicable(const VecopsB200Matmul& p, Row row, uint32_t kernel) {
     case VECOPS_B200_KERNEL_BF16_TCGEN05:
       return row == Row::BF16 && tma_operands_ok(p, 2);
     case VECOPS_B200_KERNEL_I8_TCGEN05:
-      return row == Row::I8 && tma_operands_ok(p, 1) && p.column_scale == nullptr;
+      return (row == Row::I8 && tma_operands_ok(p, 1) && p.column_scale == nullptr) || (row == Row::QI8 && tma_operands_ok(p, 1));
     case VECOPS_B200_KERNEL_W8_SMALL_M:
       return row == Row::W8 && p.a_stride_k == 1 && p.b_stride_k == 1 && p.k > 0 && p.k % 32 == 0 && aligned16(p.a) &&
              aligned16(p.b) && p.a_stride_m % 8 == 0 && p.b_stride_n % 16 == 0 && p.n < (INT64_C(1) << 31) &&
@@ -224,6 +225,7 @@ int32_t select_kernel(const VecopsB200Matmul& p, Row row, uint32_t* kernel, Veco
     case Row::BF16:
       if (!tiny && applicable(p, row, VECOPS_B200_KERNEL_BF16_TCGEN05)) pick = VECOPS_B200_KERNEL_BF16_TCGEN05;
       break;
+    case Row::QI8:
     case Row::I8:
       // int32 accumulators must wrap modulo 2^32 (vecops semantic); the tensor
       // pipe is used where |sum| < 2^31 is guaranteed: K * 2^16 < 2^31.
@@ -524,7 +526,7 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
   OutT* c = static_cast<OutT*>(p.c);
   long long ldc = p.c_stride_m;
   int m = static_cast<int>(p.m), n = static_cast<int>(p.n), k = static_cast<int>(p.k);
-  const float* scale = kInt8 ? nullptr : p.column_scale;
+  const float* scale = std::is_same<OutT, int32_t>::value ? nullptr : p.column_scale;
   int store_flag = tma_store ? 1 : 0;
   if (gather.count > 0 && gather.multicast) {
     c = static_cast<OutT*>(gather.c[0]);
@@ -583,6 +585,21 @@ int32_t launch_generic(const VecopsB200Matmul& p, Row row, cudaStream_t stream, 
       else if (as) launch_generic_typed<int8_t, uint8_t, int32_t, uint32_t>(p, stream);
       else if (bs) launch_generic_typed<uint8_t, int8_t, int32_t, uint32_t>(p, stream);
       else launch_generic_typed<uint8_t, uint8_t, int32_t, uint32_t>(p, stream);
+      break;
+    }
+    case Row::QI8: {
+      const bool as = p.a_dtype == VECOPS_DTYPE_I8, bs = p.b_dtype == VECOPS_DTYPE_I8;
+      if (c_bf16) {
+        if (as && bs) launch_generic_typed<int8_t, int8_t, bf16, uint32_t>(p, stream);
+        else if (as) launch_generic_typed<int8_t, uint8_t, bf16, uint32_t>(p, stream);
+        else if (bs) launch_generic_typed<uint8_t, int8_t, bf16, uint32_t>(p, stream);
+        else launch_generic_typed<uint8_t, uint8_t, bf16, uint32_t>(p, stream);
+      } else {
+        if (as && bs) launch_generic_typed<int8_t, int8_t, float, uint32_t>(p, stream);
+        else if (as) launch_generic_typed<int8_t, uint8_t, float, uint32_t>(p, stream);
+        else if (bs) launch_generic_typed<uint8_t, int8_t, float, uint32_t>(p, stream);
+        else launch_generic_typed<uint8_t, uint8_t, float, uint32_t>(p, stream);
+      }
       break;
     }
     default: return set_error(error, VECOPS_STATUS_INTERNAL_ERROR, "unclassified problem reached the strided kernel");
@@ -868,7 +885,11 @@ int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* err
           rc = p.c_dtype == VECOPS_DTYPE_BF16 ? launch_tcgen05<false, __nv_bfloat16>(p, *dev, stream, error)
                                               : launch_tcgen05<false, float>(p, *dev, stream, error);
           break;
-        case VECOPS_B200_KERNEL_I8_TCGEN05: rc = launch_tcgen05<true, int32_t>(p, *dev, stream, error); break;
+        case VECOPS_B200_KERNEL_I8_TCGEN05:
+          rc = p.c_dtype == VECOPS_DTYPE_I32    ? launch_tcgen05<true, int32_t>(p, *dev, stream, error)
+               : p.c_dtype == VECOPS_DTYPE_BF16 ? launch_tcgen05<true, __nv_bfloat16>(p, *dev, stream, error)
+                                                : launch_tcgen05<true, float>(p, *dev, stream, error);
+          break;
         case VECOPS_B200_KERNEL_W8_SMALL_M: rc = launch_w8_small(p, *dev, stream, error); break;
         case VECOPS_B200_KERNEL_W8_TCGEN05:
           rc = p.c_dtype == VECOPS_DTYPE_BF16 ? launch_w8_tcgen05_typed<__nv_bfloat16>(p, *dev, stream, error)
@@ -918,7 +939,7 @@ int32_t vecops_b200_matmul_run_fused(const VecopsB200Matmul* problem, const Veco
     args.cin_stride_n = epilogue->cin_stride_n;
     if (epilogue->cin_stride_m < 0 || epilogue->cin_stride_n < 0)
       return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "accumulator input strides must not be negative");
-    if (row == Row::I8) {
+    if (row == Row::I8 || row == Row::QI8) {
       if (epilogue->cin_dtype != VECOPS_DTYPE_I32)
         return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "int32 accumulators take an int32 accumulator input");
       args.cin_kind = kCinI32;
@@ -1070,6 +1091,57 @@ int32_t vecops_b200_matmul_allgather_run(const VecopsB200Matmul* problem, const 
   }
   if (previous >= 0 && previous != device) cudaSetDevice(previous);
   return rc;
+}
+
+int32_t vecops_b200_quantize_rows(const void* src, uint32_t src_dtype, int64_t src_stride_m, int64_t src_stride_k, void* dst,
+                                  uint32_t dst_dtype, int64_t dst_stride_m, int64_t rows, int64_t cols, float scale, float zero_point,
+                                  void* stream, VecopsError* error) {
+  if (rows == 0 || cols == 0) return VECOPS_STATUS_OK;
+  if (src == nullptr || dst == nullptr || rows < 0 || cols < 0 || dst_stride_m < cols)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "quantize_rows: null pointer, negative extent or overlapping destination rows");
+  if ((src_dtype != VECOPS_DTYPE_F32 && src_dtype != VECOPS_DTYPE_BF16) || (dst_dtype != VECOPS_DTYPE_U8 && dst_dtype != VECOPS_DTYPE_I8))
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "quantize_rows converts f32 or bf16 to u8 or i8");
+  if (vecops_b200_device_count() == 0)
+    return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "no usable CUDA device; there is no CPU fallback");
+  const long long total = rows * cols;
+  const int blocks = static_cast<int>(total / 256 + 1 < 148 * 8 ? total / 256 + 1 : 148 * 8);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint8_t* out = static_cast<uint8_t*>(dst);
+  const bool is_signed = dst_dtype == VECOPS_DTYPE_I8;
+  if (src_dtype == VECOPS_DTYPE_F32) {
+    const float* in = static_cast<const float*>(src);
+    if (is_signed) quantize_rows_kernel<float, true><<<blocks, 256, 0, s>>>(in, src_stride_m, src_stride_k, out, dst_stride_m, rows, cols, scale, zero_point);
+    else quantize_rows_kernel<float, false><<<blocks, 256, 0, s>>>(in, src_stride_m, src_stride_k, out, dst_stride_m, rows, cols, scale, zero_point);
+  } else {
+    const __nv_bfloat16* in = static_cast<const __nv_bfloat16*>(src);
+    if (is_signed) quantize_rows_kernel<__nv_bfloat16, true><<<blocks, 256, 0, s>>>(in, src_stride_m, src_stride_k, out, dst_stride_m, rows, cols, scale, zero_point);
+    else quantize_rows_kernel<__nv_bfloat16, false><<<blocks, 256, 0, s>>>(in, src_stride_m, src_stride_k, out, dst_stride_m, rows, cols, scale, zero_point);
+  }
+  g_launches.fetch_add(1);
+  cudaError_t status = cudaGetLastError();
+  if (status != cudaSuccess) return cuda_fail(error, status, "quantize_rows launch");
+  return VECOPS_STATUS_OK;
+}
+
+int32_t vecops_b200_column_correction(const void* b, uint32_t b_dtype, int64_t b_stride_n, int64_t n, int64_t k, int32_t zero_point,
+                                      int32_t* out, void* stream, VecopsError* error) {
+  if (n == 0) return VECOPS_STATUS_OK;
+  if (b == nullptr || out == nullptr || n < 0 || k < 0 || n >= (INT64_C(1) << 31) || k >= (INT64_C(1) << 31))
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "column_correction: null pointer or extent out of range");
+  if (b_dtype != VECOPS_DTYPE_I8 && b_dtype != VECOPS_DTYPE_U8)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "column_correction sums the rows of an 8-bit B[N,K]");
+  if (vecops_b200_device_count() == 0)
+    return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "no usable CUDA device; there is no CPU fallback");
+  const int blocks = static_cast<int>((n * 32 + 255) / 256);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (b_dtype == VECOPS_DTYPE_I8)
+    column_correction_kernel<int8_t><<<blocks, 256, 0, s>>>(static_cast<const int8_t*>(b), b_stride_n, static_cast<int>(n), static_cast<int>(k), zero_point, out);
+  else
+    column_correction_kernel<uint8_t><<<blocks, 256, 0, s>>>(static_cast<const uint8_t*>(b), b_stride_n, static_cast<int>(n), static_cast<int>(k), zero_point, out);
+  g_launches.fetch_add(1);
+  cudaError_t status = cudaGetLastError();
+  if (status != cudaSuccess) return cuda_fail(error, status, "column_correction launch");
+  return VECOPS_STATUS_OK;
 }
 
 int32_t vecops_b200_place_columns(void* dst, int64_t ldd, int64_t col0, const void* src, int64_t lds, int64_t rows,

@@ -94,6 +94,12 @@ gemm_generic_kernel(const TA* __restrict__ a, long long sam, long long sak, cons
       else v *= factor;
     } else if constexpr (std::is_same<Acc, uint32_t>::value) {
       if (ep.active) v = epilogue_int(v, ep, m, n);
+      if constexpr (!std::is_same<TC, int32_t>::value) {
+        // the dequantising form: the int32 accumulator, converted, takes the float transform
+        const float factor = column_scale != nullptr ? column_scale[n] : 1.f;
+        store_from<TC, float>(c + m * scm + n * scn, epilogue_float(static_cast<float>(static_cast<int32_t>(v)), ep, m, n, factor));
+        continue;
+      }
     }
     store_from<TC, Acc>(c + m * scm + n * scn, v);
   }
@@ -206,6 +212,40 @@ gemm_f32_kernel(const float* __restrict__ a, long long lda, const float* __restr
         if (n + j < N) dst[j] = acc[i][j];
     }
   }
+}
+
+// ------------------------------------------------------------------ quantise-on-load helpers
+
+// dst[m,k] = convert(src[m,k] * scale + zero_point): truncation toward zero, saturating to the 8-bit range, as vecops
+// converts an fp32 memory element to an 8-bit compute element (tests/ops/MatmulConversionTestCommon.h:549-556 quantize_a;
+// the conversion rule was observed by running the reference: 3.51 -> 3, 255.6 -> 255, -0.6 -> 0).
+template <typename TS, bool kSigned>
+__global__ void quantize_rows_kernel(const TS* __restrict__ src, long long ssm, long long ssk, uint8_t* __restrict__ dst,
+                                     long long dsm, long long rows, long long cols, float scale, float zero_point) {
+  const long long total = rows * cols;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long m = i / cols, k = i % cols;
+    float q = truncf(load_as<float, TS>(src + m * ssm + k * ssk) * scale + zero_point);
+    if (!(q == q)) q = 0.f;
+    if (kSigned) dst[m * dsm + k] = static_cast<uint8_t>(static_cast<int8_t>(fminf(fmaxf(q, -128.f), 127.f)));
+    else dst[m * dsm + k] = static_cast<uint8_t>(fminf(fmaxf(q, 0.f), 255.f));
+  }
+}
+
+// out[n] = -zero_point * sum_k B[n,k]: the accumulator-input row that removes the activations' zero point from an
+// asymmetric 8-bit product (MatmulConversionTestCommon.h:529-541; ops/MatmulPack.h:28-35 matmul_pack_b_compensated).
+// One warp per row of B.
+template <typename TB>
+__global__ void column_correction_kernel(const TB* __restrict__ b, long long sbn, int N, int K, int zero_point, int32_t* __restrict__ out) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= N) return;
+  const TB* row = b + static_cast<long long>(warp) * sbn;
+  int sum = 0;
+  for (int k = lane; k < K; k += 32) sum += static_cast<int>(row[k]);
+  for (int offset = 16; offset > 0; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+  if (lane == 0) out[warp] = -zero_point * sum;
 }
 
 // ------------------------------------------------------------------ fills and slab placement

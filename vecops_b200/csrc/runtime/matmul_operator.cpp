@@ -149,7 +149,7 @@ const VariantDescriptor* variant_descriptor(std::uint32_t kernel) {
       build_variant<VECOPS_B200_KERNEL_F32_SIMT>(f32, f32, f32, 1, 1, 1, false, true),
       // TMA wants 16-byte row pitches: 8 bf16 elements, 16 int8 elements
       build_variant<VECOPS_B200_KERNEL_BF16_TCGEN05>(bf16, bf16, bf16 | f32, 8, 8, 1, true, true),
-      build_variant<VECOPS_B200_KERNEL_I8_TCGEN05>(i8 | u8, i8 | u8, i32, 16, 16, 1, true, true),
+      build_variant<VECOPS_B200_KERNEL_I8_TCGEN05>(i8 | u8, i8 | u8, i32 | f32 | bf16, 16, 16, 1, true, true),
       build_variant<VECOPS_B200_KERNEL_W8_SMALL_M>(bf16, i8, bf16 | f32, 8, 16, 32, true, true),
       build_variant<VECOPS_B200_KERNEL_W8_TCGEN05>(bf16, i8, bf16 | f32, 8, 16, 32, true, true),
   };

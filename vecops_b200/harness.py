@@ -111,6 +111,28 @@ def matmul(a, b_nk, c, scale=None, kernel: int = capi.KERNEL_AUTO, stream=None, 
     del scratch
 
 
+def quantize_rows(src, dst, scale: float, zero_point: float, stream=None) -> None:
+    """dst[m,k] = convert(src[m,k] * scale + zero_point): src f32 or bf16 [M,K], dst u8 or i8 with K-contiguous rows."""
+    import torch
+    if stream is None:
+        stream = torch.cuda.current_stream(src.device)
+    error = capi.ErrorBuffer()
+    error.raise_for(capi.library().vecops_b200_quantize_rows(src.data_ptr(), torch_dtype_code(src.dtype), src.stride(0), src.stride(1),
+                                                            dst.data_ptr(), torch_dtype_code(dst.dtype), dst.stride(0), src.shape[0],
+                                                            src.shape[1], scale, zero_point, stream.cuda_stream, byref(error.record)))
+
+
+def column_correction(b_nk, zero_point: int, out, stream=None) -> None:
+    """out[n] = -zero_point * sum_k B[n,k] (int32), the accumulator-input row of an asymmetric 8-bit product."""
+    import torch
+    if stream is None:
+        stream = torch.cuda.current_stream(b_nk.device)
+    error = capi.ErrorBuffer()
+    error.raise_for(capi.library().vecops_b200_column_correction(b_nk.data_ptr(), torch_dtype_code(b_nk.dtype), b_nk.stride(0), b_nk.shape[0],
+                                                                b_nk.shape[1], zero_point, out.data_ptr(), stream.cuda_stream,
+                                                                byref(error.record)))
+
+
 class PreparedMatmul:
     """One problem record built once and launched many times (keeps per-launch host cost to a single C call)."""
 
