@@ -140,9 +140,22 @@ __device__ __forceinline__ void epilogue_int_row32(uint32_t (&v)[32], const Epil
   if (row >= M || ep.cin_kind != kCinI32) return;
   const int valid = min(32, N - col0);
   const int32_t* src = static_cast<const int32_t*>(ep.cin) + row * ep.cin_stride_m + static_cast<long long>(col0) * ep.cin_stride_n;
+  if (ep.cin_stride_n == 1 && valid == 32 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+    // contiguous columns: eight 16-byte loads (one address for the whole warp when CIn is a correction row); thirty-two
+    // scalar loads here cost an int8 tile's epilogue more than its MMAs
 #pragma unroll
-  for (int j = 0; j < 32; ++j)
-    if (j < valid) v[j] += static_cast<uint32_t>(__ldg(src + j * ep.cin_stride_n));
+    for (int q = 0; q < 8; ++q) {
+      const int4 part = __ldg(reinterpret_cast<const int4*>(src) + q);
+      v[4 * q] += static_cast<uint32_t>(part.x);
+      v[4 * q + 1] += static_cast<uint32_t>(part.y);
+      v[4 * q + 2] += static_cast<uint32_t>(part.z);
+      v[4 * q + 3] += static_cast<uint32_t>(part.w);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) v[j] += static_cast<uint32_t>(__ldg(src + j * ep.cin_stride_n));
+  }
 }
 
 // int32 accumulators take an int32 accumulator input and nothing else (wrapping add, like the accumulation itself).

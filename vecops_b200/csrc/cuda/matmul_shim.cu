@@ -1108,7 +1108,15 @@ int32_t vecops_b200_quantize_rows(const void* src, uint32_t src_dtype, int64_t s
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   uint8_t* out = static_cast<uint8_t*>(dst);
   const bool is_signed = dst_dtype == VECOPS_DTYPE_I8;
-  if (src_dtype == VECOPS_DTYPE_F32) {
+  const bool by_four = src_dtype == VECOPS_DTYPE_F32 && src_stride_k == 1 && cols % 4 == 0 && aligned16(src) && src_stride_m % 4 == 0 &&
+                       (reinterpret_cast<uintptr_t>(dst) & 3u) == 0 && dst_stride_m % 4 == 0;
+  if (by_four) {
+    const long long groups = rows * (cols / 4);
+    const int grid4 = static_cast<int>(groups / 256 + 1 < 148 * 16 ? groups / 256 + 1 : 148 * 16);
+    const float* in = static_cast<const float*>(src);
+    if (is_signed) quantize_rows_f32x4_kernel<true><<<grid4, 256, 0, s>>>(in, src_stride_m, out, dst_stride_m, rows, cols / 4, scale, zero_point);
+    else quantize_rows_f32x4_kernel<false><<<grid4, 256, 0, s>>>(in, src_stride_m, out, dst_stride_m, rows, cols / 4, scale, zero_point);
+  } else if (src_dtype == VECOPS_DTYPE_F32) {
     const float* in = static_cast<const float*>(src);
     if (is_signed) quantize_rows_kernel<float, true><<<blocks, 256, 0, s>>>(in, src_stride_m, src_stride_k, out, dst_stride_m, rows, cols, scale, zero_point);
     else quantize_rows_kernel<float, false><<<blocks, 256, 0, s>>>(in, src_stride_m, src_stride_k, out, dst_stride_m, rows, cols, scale, zero_point);

@@ -233,6 +233,29 @@ __global__ void quantize_rows_kernel(const TS* __restrict__ src, long long ssm, 
   }
 }
 
+// The common case of the above - fp32 rows, K-contiguous, whole 16-byte groups - four elements per thread.
+template <bool kSigned>
+__global__ void quantize_rows_f32x4_kernel(const float* __restrict__ src, long long ssm, uint8_t* __restrict__ dst, long long dsm,
+                                           long long rows, long long groups_per_row, float scale, float zero_point) {
+  const long long total = rows * groups_per_row;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long m = i / groups_per_row, g = i % groups_per_row;
+    const float4 x = __ldg(reinterpret_cast<const float4*>(src + m * ssm) + g);
+    const float in[4] = {x.x, x.y, x.z, x.w};
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float q = truncf(in[j] * scale + zero_point);
+      if (!(q == q)) q = 0.f;
+      const uint32_t byte = kSigned ? static_cast<uint32_t>(static_cast<uint8_t>(static_cast<int8_t>(fminf(fmaxf(q, -128.f), 127.f))))
+                                    : static_cast<uint32_t>(static_cast<uint8_t>(fminf(fmaxf(q, 0.f), 255.f)));
+      packed |= byte << (8 * j);
+    }
+    reinterpret_cast<uint32_t*>(dst + m * dsm)[g] = packed;
+  }
+}
+
 // out[n] = -zero_point * sum_k B[n,k]: the accumulator-input row that removes the activations' zero point from an
 // asymmetric 8-bit product (MatmulConversionTestCommon.h:529-541; ops/MatmulPack.h:28-35 matmul_pack_b_compensated).
 // One warp per row of B.
