@@ -250,6 +250,61 @@ def measure_single(name: str, steps: int, warmup: int, dev, port, peaks, fused: 
             "launch": "one CUDA graph of all timed launches", "parity": parity, "device_status": status}
 
 
+def measure_quantized(steps: int, warmup: int, dev, port, peaks) -> dict:
+    """The quantised form at C3's size: fp32 activations quantised to u8 (pre-pass), s8 weights, int32 correction row, dequantising
+    transform with a per-column scale, bf16 out.  The timed launches are the product kernel alone; the pre-passes are timed beside it."""
+    import torch
+    from oracle.checker import bf16_bits_to_f32, rel_frobenius
+    from vecops_b200 import capi, harness
+    m, n, k = 4096, 14336, 4096
+    rng = np.random.default_rng(6)
+    a_host = rng.uniform(-20, 40, (m, k)).astype(np.float32)
+    b_host = [rng.integers(-128, 128, (n, k), dtype=np.int8) for _ in range(2)]
+    scale_host = rng.uniform(0.5, 2.0, n).astype(np.float32)
+    a32 = torch.from_numpy(a_host).to(dev)
+    qa = torch.empty((m, k), dtype=torch.uint8, device=dev)
+    bs = [torch.from_numpy(x).to(dev) for x in b_host]
+    scale = torch.from_numpy(scale_host).to(dev)
+    corrections = [torch.empty(n, dtype=torch.int32, device=dev) for _ in bs]
+    stream = torch.cuda.current_stream(dev)
+
+    def timed(fn, count=20):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(count):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / count
+
+    quantize_ms = timed(lambda: harness.quantize_rows(a32, qa, 2.0, 5.0))
+    correction_ms = timed(lambda: harness.column_correction(bs[0], 5, corrections[0]))
+    harness.column_correction(bs[1], 5, corrections[1])
+    outs = [torch.empty((m, n), dtype=torch.bfloat16, device=dev) for _ in bs]
+    prepared = [harness.PreparedMatmul(qa, bs[j], outs[j], scale, stream=stream,
+                                       epilogue=harness.epilogue_record(corrections[j], 0.01, capi.ACTIVATION_NONE, 0.0, 0.0, m, n),
+                                       keep=(corrections[j],)) for j in range(2)]
+    prepared[0].launch()
+    torch.cuda.synchronize()
+    pick = np.unique(np.linspace(0, m - 1, 8).astype(np.int64))
+    quantized_rows = port.quantize_rows(a_host[pick], 2.0, 5.0)
+    correction_host = (-5 * b_host[0].astype(np.int64).sum(axis=1)).astype(np.int32)
+    want = port.matmul_i8_dequant(quantized_rows, b_host[0], correction_host, 0.01, scale_host, out_bf16=True)
+    got = outs[0][torch.from_numpy(pick).to(dev)].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    parity = {"rows": len(pick), "rel_fro": rel_frobenius(bf16_bits_to_f32(got), bf16_bits_to_f32(want)),
+              "quantized_rows_equal": bool(np.array_equal(qa[torch.from_numpy(pick).to(dev)].cpu().numpy(), quantized_rows)),
+              "correction_equal": bool(np.array_equal(corrections[0].cpu().numpy(), correction_host))}
+    ms = time_graph(prepared, steps, warmup, dev)
+    tops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+    peak = 2.0 * float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    return {"workload": "c3 shape, quantised form: u8 (quantised fp32) x s8 + int32 correction row, dequantised and column-scaled to bf16",
+            "kernel": "i8_tcgen05", "ms_per_step": ms, "value": tops, "unit": "TOP/s", "bound": "tensor", "frac_of_measured_peak": tops / peak,
+            "quantize_rows_ms": quantize_ms, "column_correction_ms": correction_ms, "parity": parity, "device_status": take_status(),
+            "launch": "one CUDA graph of all timed launches; two weight sets (235 MB) > L2"}
+
+
 def bridge_invoker():
     """Returns call(a, b, c, scale, stream): one asynchronous operator-bridge invocation (the reference-facing entry)."""
     from vecops_b200 import capi
@@ -641,6 +696,11 @@ def run_ours(args) -> None:
                 extras["c2_bf16_4096_fused_bias_silu"] = measure_single("c2_bf16_4096", 50, 5, dev, port, peaks, fused=True)
             except Exception as error:
                 extras["c2_bf16_4096_fused_bias_silu"] = {"error": repr(error)}
+            torch.cuda.empty_cache()
+            try:  # next-row feature: the quantised form as the reference ships it, at C3's size
+                extras["c3_quantized_u8s8"] = measure_quantized(50, 5, dev, port, peaks)
+            except Exception as error:
+                extras["c3_quantized_u8s8"] = {"error": repr(error)}
             torch.cuda.empty_cache()
             line["configs"] = extras
     if rank == 0:
