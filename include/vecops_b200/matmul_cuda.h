@@ -107,8 +107,7 @@ VECOPS_B200_EXPORT int32_t vecops_b200_matmul_run(const VecopsB200Matmul* proble
  *     Float rows take an f32 or bf16 CIn, added in fp32 before anything else.  The int8 row takes an int32 CIn, added
  *     with wraparound ("native integer accumulate"), and nothing else: alpha must be 1 and activation NONE.
  *   - problem->column_scale keeps its meaning and is applied together with alpha.
- *   - Served by the tcgen05 GEMMs, the fp32 kernel and the strided kernel; a weight-only problem with a fused form goes
- *     to the strided kernel (correct, not fast).  Forcing a kernel that cannot serve the form is NOT_APPLICABLE.
+ *   - Every kernel applies it where it stores C.
  * Workspace and selection are those of the plain problem. */
 typedef enum VecopsB200Activation {
   VECOPS_B200_ACTIVATION_NONE = 0,

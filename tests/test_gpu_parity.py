@@ -503,17 +503,15 @@ def test_fused_f32_and_weight_only_and_empty_reduction(port):
     bias = rng.uniform(-1, 1, 200).astype(np.float32)
     got = _fused_gpu("f32", a, b, torch.float32, K.KERNEL_F32_SIMT, cin=bias, act=ACT_SILU, alpha=0.25)
     assert rel_frobenius(got, port.matmul_f32_fused(a, b, bias, 0.25, None, ACT_SILU)) <= 1e-5
-    # a weight-only problem with a fused form is served by the strided kernel
-    aw, w, s = inputs("w8", 16, 256, 128, rng)
-    da, dw, ds = to_device(aw, True), to_device(w), to_device(s)
-    c = torch.zeros((16, 256), dtype=torch.bfloat16, device="cuda")
-    bias_w = rng.uniform(-1, 1, 256).astype(np.float32)
-    vecops_b200.matmul(da, dw, c, ds, cin=to_device(bias_w), activation=ACT_RELU)
-    want = port.matmul_bf16_fused(aw, f32_to_bf16_bits(w.astype(np.float32)), bias_w, 1.0, s, ACT_RELU)
-    check("w8", bf16_result_to_numpy(c), want)
-    with pytest.raises(capi.VecopsB200Error) as info:
-        vecops_b200.matmul(da, dw, c, ds, kernel=K.KERNEL_W8_SMALL_M, activation=ACT_RELU)
-    assert info.value.code == capi.NOT_APPLICABLE
+    # weight-only problems take the fused form in their own kernels: streaming (M <= 16), general, and tensor-core
+    bias_w = rng.uniform(-1, 1, 2048).astype(np.float32)
+    for m, kernel in ((16, K.KERNEL_W8_SMALL_M), (40, K.KERNEL_W8_SMALL_M), (40, K.KERNEL_W8_TCGEN05), (128, K.KERNEL_AUTO)):
+        aw, w, s = inputs("w8", m, 2048, 1024, rng)
+        da, dw, ds = to_device(aw, True), to_device(w), to_device(s)
+        c = torch.zeros((m, 2048), dtype=torch.bfloat16, device="cuda")
+        vecops_b200.matmul(da, dw, c, ds, kernel=kernel, cin=to_device(bias_w), alpha=0.5, activation=ACT_SILU)
+        want = port.matmul_bf16_fused(aw, f32_to_bf16_bits(w.astype(np.float32)), bias_w, 0.5, s, ACT_SILU)
+        check("w8", bf16_result_to_numpy(c), want, f"m={m} kernel={kernel}")
     # K == 0: the result is transform(CIn)
     e = torch.zeros((4, 8), dtype=torch.float32, device="cuda")
     vecops_b200.matmul(torch.zeros((4, 0), device="cuda"), torch.zeros((8, 0), device="cuda"), e, cin=to_device(bias[:8].copy()), alpha=2.0)

@@ -614,7 +614,7 @@ void launch_w8_small_typed(const VecopsB200Matmul& p, cudaStream_t stream) {
             static_cast<unsigned>((p.m + 8 * kMTiles - 1) / (8 * kMTiles)));
   w8_small_m_kernel<kMTiles, OutT><<<grid, G::kThreads, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(p.a), p.a_stride_m, static_cast<const int8_t*>(p.b), p.b_stride_n, p.column_scale,
-      static_cast<OutT*>(p.c), p.c_stride_m, static_cast<int>(p.m), static_cast<int>(p.n), static_cast<int>(p.k));
+      static_cast<OutT*>(p.c), p.c_stride_m, static_cast<int>(p.m), static_cast<int>(p.n), static_cast<int>(p.k), tl_epilogue);
   g_launches.fetch_add(1);
 }
 
@@ -630,7 +630,7 @@ int32_t launch_w8_stream_typed(const VecopsB200Matmul& p, const DeviceState& dev
   const int grid = static_cast<int>(items < dev.prop.multiProcessorCount ? items : dev.prop.multiProcessorCount);
   kernel<<<grid, G::kThreads, smem, stream>>>(static_cast<const __nv_bfloat16*>(p.a), p.a_stride_m, static_cast<const int8_t*>(p.b),
                                               p.b_stride_n, p.column_scale, static_cast<OutT*>(p.c), p.c_stride_m,
-                                              static_cast<int>(p.m), static_cast<int>(p.n), static_cast<int>(p.k), g_status_host);
+                                              static_cast<int>(p.m), static_cast<int>(p.n), static_cast<int>(p.k), tl_epilogue, g_status_host);
   g_launches.fetch_add(1);
   return VECOPS_STATUS_OK;
 }
@@ -792,7 +792,8 @@ int32_t launch_w8_tcgen05_typed(const VecopsB200Matmul& p, const DeviceState& de
   unsigned long long nonce = fresh_nonce(p.workspace);
   uint32_t* status_word = g_status_host;
   unsigned long long* trace = g_trace;
-  void* args[] = {&map_w, &map_a, &scale, &c, &ldc, &m, &n, &k, &mpad_arg, &partials, &flags, &inv, &nonce, &idesc, &status_word, &trace};
+  EpilogueArgs epilogue = tl_epilogue;
+  void* args[] = {&map_w, &map_a, &scale, &c, &ldc, &m, &n, &k, &mpad_arg, &partials, &flags, &inv, &nonce, &idesc, &epilogue, &status_word, &trace};
   cudaError_t launched = cudaLaunchKernelExC(&config, pair ? reinterpret_cast<const void*>(pair_kernel) : reinterpret_cast<const void*>(single_kernel), args);
   if (launched != cudaSuccess) return cuda_fail(error, launched, "launch of w8_tcgen05");
   g_launches.fetch_add(1);
@@ -963,13 +964,8 @@ int32_t vecops_b200_matmul_run_fused(const VecopsB200Matmul* problem, const Veco
   uint32_t kernel;
   rc = select_kernel(fused, row, &kernel, error);
   if (rc != VECOPS_STATUS_OK) return rc;
-  const bool implements = kernel == VECOPS_B200_KERNEL_GENERIC || kernel == VECOPS_B200_KERNEL_F32_SIMT ||
-                          kernel == VECOPS_B200_KERNEL_BF16_TCGEN05 || kernel == VECOPS_B200_KERNEL_I8_TCGEN05;
-  if (!implements) {
-    if (problem->kernel != VECOPS_B200_KERNEL_AUTO || forced_by_environment() != VECOPS_B200_KERNEL_AUTO)
-      return set_error(error, VECOPS_STATUS_NOT_APPLICABLE, "kernel '%s' has no fused output transform", kKernelNames[kernel]);
-    fused.kernel = VECOPS_B200_KERNEL_GENERIC;
-  }
+  // (every kernel implements the transform; `kernel` is only needed for the empty reduction below)
+  (void)kernel;
   if (fused.k == 0)  // an empty reduction leaves transform(CIn): the strided kernel computes it with zero trips
     fused.kernel = VECOPS_B200_KERNEL_GENERIC;
   tl_epilogue = args;

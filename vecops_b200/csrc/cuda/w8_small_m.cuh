@@ -18,6 +18,8 @@
 // Algorithmic traffic per launch: N*K + 4*N + 2*M*K + sizeof(C)*M*N bytes.
 #pragma once
 
+#include "epilogue.cuh"
+
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -70,7 +72,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 template <int kMTiles, typename OutT>
 __global__ void __launch_bounds__(W8SmallM::kThreads)
 w8_small_m_kernel(const __nv_bfloat16* __restrict__ a, long long lda, const int8_t* __restrict__ w, long long ldw,
-                  const float* __restrict__ scale, OutT* __restrict__ c, long long ldc, int M, int N, int K) {
+                  const float* __restrict__ scale, OutT* __restrict__ c, long long ldc, int M, int N, int K, EpilogueArgs ep) {
   using G = W8SmallM;
   __shared__ float red[2][G::kKSplit][kMTiles][32][4];
 
@@ -191,7 +193,8 @@ w8_small_m_kernel(const __nv_bfloat16* __restrict__ a, long long lda, const int8
       const int m = m_base + 8 * j + 2 * t + (e & 1);
       const int n = (e < 2) ? n_out_lo : n_out_hi;
       if (m < M && n < N) {
-        const float v = sum[e] * ((e < 2) ? s_lo : s_hi);
+        const float factor = (e < 2) ? s_lo : s_hi;
+        const float v = ep.active ? epilogue_float(sum[e], ep, m, n, factor) : sum[e] * factor;
         if constexpr (sizeof(OutT) == 2) c[static_cast<long long>(m) * ldc + n] = __float2bfloat16_rn(v);
         else c[static_cast<long long>(m) * ldc + n] = v;
       }

@@ -131,7 +131,7 @@ void launch(const VecopsB200Matmul& p, const PerDevice& dev, int mpad, const CUt
   const uint32_t idesc = umma_instr_desc(kUmmaAccF32, kUmmaF16, kUmmaF16, G::kTileN, mpad);
   w8_tcgen05_kernel<OutT, false><<<static_cast<int>(grid), G::kThreads, G::smem_bytes(mpad), stream>>>(
       map_w, map_a, p.column_scale, static_cast<OutT*>(p.c), p.c_stride_m, static_cast<int>(p.m), static_cast<int>(p.n),
-      static_cast<int>(p.k), mpad, partials, flags, inv_scales, next_nonce(), idesc, dev.status, nullptr);
+      static_cast<int>(p.k), mpad, partials, flags, inv_scales, next_nonce(), idesc, EpilogueArgs(), dev.status, nullptr);
 }
 
 }  // namespace

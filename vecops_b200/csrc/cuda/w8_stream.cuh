@@ -39,6 +39,7 @@
 
 #include <cuda_fp16.h>
 
+#include "epilogue.cuh"
 #include "gemm_tcgen05.cuh"  // status codes, report_status
 #include "ptx.cuh"
 
@@ -95,7 +96,7 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
 template <int kMTiles, int kChunks, typename OutT>
 __global__ void __launch_bounds__(W8Stream::kThreads, 1)
 w8_stream_kernel(const __nv_bfloat16* __restrict__ a, long long lda, const int8_t* __restrict__ w, long long ldw,
-                 const float* __restrict__ scale, OutT* __restrict__ c, long long ldc, int M, int N, int K,
+                 const float* __restrict__ scale, OutT* __restrict__ c, long long ldc, int M, int N, int K, EpilogueArgs ep,
                  uint32_t* __restrict__ status) {
   using G = W8Stream;
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -311,7 +312,9 @@ w8_stream_kernel(const __nv_bfloat16* __restrict__ a, long long lda, const int8_
         const int m = 8 * j + 2 * ft + (e & 1);
         const int n = item * G::kRows + fg + ((e & 2) ? 8 : 0);
         if (m < M && n < N) {
-          const float v = sum * inv_row_scale[m] * (scale != nullptr ? __ldg(scale + n) : 1.f);
+          const float factor = scale != nullptr ? __ldg(scale + n) : 1.f;
+          // (the fused form's accumulator input joins the sum once the power of two of the row is divided out)
+          const float v = ep.active ? epilogue_float(sum * inv_row_scale[m], ep, m, n, factor) : sum * inv_row_scale[m] * factor;
           if constexpr (sizeof(OutT) == 2) c[static_cast<long long>(m) * ldc + n] = __float2bfloat16_rn(v);
           else c[static_cast<long long>(m) * ldc + n] = v;
         }

@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(W8Tc::kThreads, 1)
 w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_a,
                   const float* __restrict__ scale, OutT* __restrict__ c, long long ldc, int M, int N, int K, int mpad,
                   float* __restrict__ partials, unsigned long long* __restrict__ flags,
-                  const float* __restrict__ inv_row_scale, unsigned long long nonce, uint32_t idesc,
+                  const float* __restrict__ inv_row_scale, unsigned long long nonce, uint32_t idesc, EpilogueArgs ep,
                   uint32_t* __restrict__ status, unsigned long long* __restrict__ trace) {
   using G = W8Tc;
   // Two operand formats, chosen by the launcher through `inv_row_scale`: null = the activations are the caller's bf16
@@ -457,7 +457,7 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
           for (int j = 0; j < 16; ++j) {
             const int m = col0 + j;
             if (m < M) {
-              const float out = acc[j] * inv_scale_smem[m] * s;
+              const float out = ep.active ? epilogue_float(acc[j] * inv_scale_smem[m], ep, m, n, s) : acc[j] * inv_scale_smem[m] * s;
               if constexpr (sizeof(OutT) == 2) c[static_cast<long long>(m) * ldc + n] = __float2bfloat16_rn(out);
               else c[static_cast<long long>(m) * ldc + n] = out;
             }
