@@ -196,8 +196,22 @@ class Ref:
         if hasattr(lib, "ref_matmul_bf16_fused"):
             lib.ref_matmul_bf16_fused.argtypes = [_I64] * 3 + [_P, _I64, _P, _I64, _P, _I64, _I64, _F, _P, c_int, _F, _F, _P, _I64, c_int]
             lib.ref_matmul_i8_accumulate.argtypes = [_I64] * 3 + [_P, _I64, _P, _I64, _P, _I64, _I64, _P, _I64]
+        if hasattr(lib, "ref_matmul_bf16_batched"):
+            lib.ref_matmul_bf16_batched.argtypes = [_I64] * 4 + [_P, _I64, _I64, _P, _I64, _I64, _P, _P, _I64, _I64]
         if hasattr(lib, "ref_matmul_quantized_u8s8"):
             lib.ref_matmul_quantized_u8s8.argtypes = [_I64] * 3 + [_P, _I64, _F, _F, _P, _I64, _P, _F, _P, _I64]
+
+    def matmul_bf16_batched(self, a3, b3, bias=None):
+        """Rank-3 bf16 operands [B,M,K] x [B,N,K] -> f32 [B,M,N]; a leading stride may be 0 (np.broadcast_to views)."""
+        batch, m, k = a3.shape
+        n = b3.shape[1]
+        c = np.empty((batch, m, n), dtype=np.float32)
+        item = a3.itemsize
+        assert a3.strides[2] == item and b3.strides[2] == item
+        rc = self.lib.ref_matmul_bf16_batched(batch, m, n, k, _ptr(a3), a3.strides[0] // item, a3.strides[1] // item, _ptr(b3),
+                                              b3.strides[0] // item, b3.strides[1] // item, _ptr(bias), _ptr(c), m * n, n)
+        assert rc == 0
+        return c
 
     def matmul_quantized_u8s8(self, a_f32, a_scale, a_zero_point, b_nk, correction, dequant):
         """fp32 A quantised on load to u8, s8 B, int32 correction row, dequantising output transform, fp32 C."""

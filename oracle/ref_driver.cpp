@@ -234,6 +234,34 @@ int ref_matmul_quantized_u8s8(int64_t m, int64_t n, int64_t k, const float* a, i
   return 0;
 }
 
+// Rank-3 operands: a leading batch axis on A, B and C, any of whose strides may be 0 (a shared A, or shared weights), as
+// in tests/ops/MatmulBatchTest.cpp:96-131; `bias` (optional, [N]) enters as the accumulator input with strides (0, 0, 1).
+int ref_matmul_bf16_batched(int64_t batch, int64_t m, int64_t n, int64_t k, const uint16_t* a, int64_t a_sb, int64_t lda,
+                            const uint16_t* b, int64_t b_sb, int64_t ldb, const float* bias, float* c, int64_t c_sb, int64_t ldc) {
+  if (!request_amx()) return 1;
+  auto at = make_tensor(reinterpret_cast<const bfloat16_t*>(a),
+                        make_layout(make_shape(Any{batch}, Any{m}, Any{k}), make_strides(Any{a_sb}, Any{lda}, cint<1>)));
+  auto bt = make_tensor(reinterpret_cast<const bfloat16_t*>(b),
+                        make_layout(make_shape(Any{batch}, Any{n}, Any{k}), make_strides(Any{b_sb}, Any{ldb}, cint<1>)));
+  auto ct = make_tensor(c, make_layout(make_shape(Any{batch}, Any{m}, Any{n}), make_strides(Any{c_sb}, Any{ldc}, cint<1>)));
+  auto ai = input<bfloat16_t>(at);
+  auto bi = input<bfloat16_t>(bt);
+  auto co = output<float32_t>(ct);
+  auto op = ops::matmul(ops::MatmulConfig<matmul::AMX_BF16F32>{});
+  if (bias != nullptr) {
+    auto bias_tensor = make_tensor(bias, make_layout(make_shape(Any{batch}, Any{m}, Any{n}), make_strides(cint<0>, cint<0>, cint<1>)));
+    auto ci = input<float32_t>(bias_tensor);
+    kernel::Workspace storage(op.required_workspace(Any{m}, Any{n}, Any{k}, ai, bi, ci, co));
+    auto view = storage.view();
+    op(view, Any{m}, Any{n}, Any{k}, ai, bi, ci, co);
+  } else {
+    kernel::Workspace storage(op.required_workspace(Any{m}, Any{n}, Any{k}, ai, bi, co));
+    auto view = storage.view();
+    op(view, Any{m}, Any{n}, Any{k}, ai, bi, co);
+  }
+  return 0;
+}
+
 // fp32: the reference has no fp32 matmul atom on x86; its only fp32 x fp32
 // product code is the AVX-512 vector leaf (amx/Backend.h:767-901) instantiated
 // with equal types.  B is [N,K] here.

@@ -144,6 +144,26 @@ def main() -> None:
                                                    correction=correction, dequant=np.float32(0.01),
                                                    c=ref.matmul_quantized_u8s8(a, 2.5, 7.0, b, correction, 0.01))
 
+    # rank-3 operands with a leading batch axis (tests/ops/MatmulBatchTest.cpp:96-131): a shared A (batch stride 0) against
+    # batched B with a bias row; batched A against shared weights; everything batched
+    def bf16_pattern(count, seed, shape):
+        return f32_to_bf16_bits(conversion_pattern(count, seed, np.float32)).reshape(shape)
+
+    batch, m, n, k = 3, 5, 23, 65
+    a = bf16_pattern(m * k, 3, (m, k))
+    b = bf16_pattern(batch * n * k, 11, (batch, n, k))
+    bias = conversion_pattern(n, 5, np.float32)
+    cases["batched_shared_a_bias_3x5x23x65"] = dict(kind="batched_bf16", a=a, b=b, bias=bias, shared=np.array("a"),
+                                                    c=ref.matmul_bf16_batched(np.broadcast_to(a, (batch, m, k)), b, bias))
+    a = bf16_pattern(batch * m * k, 3, (batch, m, k))
+    b = bf16_pattern(n * k, 11, (n, k))
+    cases["batched_shared_b_3x5x23x65"] = dict(kind="batched_bf16", a=a, b=b, shared=np.array("b"),
+                                               c=ref.matmul_bf16_batched(a, np.broadcast_to(b, (batch, n, k))))
+    batch, m, n, k = 4, 19, 21, 72
+    a = bf16_pattern(batch * m * k, 3, (batch, m, k))
+    b = bf16_pattern(batch * n * k, 11, (batch, n, k))
+    cases["batched_4x19x21x72"] = dict(kind="batched_bf16", a=a, b=b, shared=np.array(""), c=ref.matmul_bf16_batched(a, b))
+
     for name, arrays in cases.items():
         kind = arrays.pop("kind")
         np.savez_compressed(HERE / f"{name}.npz", kind=np.array(kind), **arrays)

@@ -46,6 +46,14 @@ def test_port_matches_golden_fixtures(port, golden):
             assert rel_frobenius(got, bf16_bits_to_f32(case["c_bf16"])) <= TOL_BF16, name
         elif kind == "i8acc":
             assert np.array_equal(port.matmul_i8_accumulate(a, b, case["cin"]), case["c"]), name
+        elif kind == "batched_bf16":
+            # the reference's rank-3 form is one product per batch index, a leading stride of 0 sharing an operand
+            batch = case["c"].shape[0]
+            for i in range(batch):
+                ai = a if a.ndim == 2 else a[i]
+                bi = b if b.ndim == 2 else b[i]
+                got = port.matmul_bf16_fused(ai, bi, case.get("bias"), out_bf16=False)
+                assert rel_frobenius(got, case["c"][i]) <= 1e-6, name
         elif kind == "quant_u8s8":
             quantized = port.quantize_rows(a, float(case["a_scale"]), float(case["a_zero_point"]))
             got = port.matmul_i8_dequant(quantized, b, case["correction"], float(case["dequant"]))
@@ -53,7 +61,7 @@ def test_port_matches_golden_fixtures(port, golden):
         else:
             raise AssertionError(f"unknown fixture kind {kind}")
         checked += 1
-    assert checked >= 34
+    assert checked >= 37
 
 
 def test_int32_accumulator_wraps(port):
