@@ -132,6 +132,27 @@ typedef struct VecopsB200Epilogue {
 VECOPS_B200_EXPORT int32_t vecops_b200_matmul_run_fused(const VecopsB200Matmul* problem, const VecopsB200Epilogue* epilogue,
                                                         VecopsError* error);
 
+/* Rank-3 operands: a leading batch axis on A [B,M,K], B [B,N,K] and C [B,M,N], as vecops' operands may carry
+ * (tests/ops/MatmulBatchTest.cpp:96-131).  `problem` describes one batch entry; the strides below step from one entry to
+ * the next, in elements, and may be 0 for an operand every entry shares (a shared A, or shared weights).
+ *   - Shared weights with A and C stacked densely along the batch axis (a_stride_b = M * a_stride_m, likewise C and a
+ *     full-matrix CIn) is ONE product with M * count rows: it is run as such.
+ *   - Otherwise one launch per entry on problem->stream, asynchronously, and - unless the problem asks for asynchronous
+ *     execution - one synchronisation at the end.  Launches share problem->workspace: they are ordered by the stream.
+ *   - `epilogue` may be NULL.  cin_stride_b steps its accumulator input (0 = the same bias / matrix for every entry);
+ *     column_scale is shared by all entries.
+ * Workspace: what vecops_b200_matmul_workspace reports for the problem with m replaced by m * count covers both ways. */
+typedef struct VecopsB200Batch {
+  uint32_t struct_size;
+  uint32_t reserved;
+  int64_t count;
+  int64_t a_stride_b, b_stride_b, c_stride_b;
+  int64_t cin_stride_b;
+} VecopsB200Batch;
+
+VECOPS_B200_EXPORT int32_t vecops_b200_matmul_run_batched(const VecopsB200Matmul* problem, const VecopsB200Batch* batch,
+                                                          const VecopsB200Epilogue* epilogue, VecopsError* error);
+
 /* The weight-only int8 tensor-core kernel (VECOPS_B200_KERNEL_W8_TCGEN05) with its scratch inside the
  * library instead of in a caller workspace.  It has no counterpart in the reference: it exists for callers
  * of this library that cannot allocate device memory at call time - a serving loop whose memory pool is

@@ -79,7 +79,7 @@ def test_golden_fixtures_through_automatic_dispatch(golden):
     for name, case in golden.items():
         kind = str(case["kind"])
         a, b = case["a"], case["b"]
-        if kind in ("fused_bf16", "i8acc", "quant_u8s8"):
+        if kind in ("fused_bf16", "i8acc", "quant_u8s8", "batched_bf16"):
             continue  # the fused forms have their own test below
         if kind == "i8":
             check(kind, run_case(kind, a, b), case["c"], name)
@@ -642,3 +642,54 @@ def test_quantized_form_on_the_tensor_cores(port, cta_form, m, n, k):
     c = torch.empty((m, n), dtype=torch.float32, device="cuda")
     vecops_b200.matmul(da, db, c, kernel=K.KERNEL_I8_TCGEN05)
     assert np.array_equal(c.cpu().numpy()[rows], port.matmul_i8(qa[rows], b).astype(np.float32))
+
+
+# ------------------------------------------------------------------ rank-3 operands (a leading batch axis)
+
+def test_batched_golden_fixtures(golden):
+    seen = 0
+    for name, case in golden.items():
+        if str(case["kind"]) != "batched_bf16":
+            continue
+        batch, m, n = case["c"].shape
+        a, b = to_device(case["a"], True), to_device(case["b"], True)
+        a3 = a.expand(batch, *a.shape) if a.dim() == 2 else a
+        b3 = b.expand(batch, *b.shape) if b.dim() == 2 else b
+        c = torch.full((batch, m, n), -3.0, dtype=torch.float32, device="cuda")
+        bias = to_device(case["bias"]) if "bias" in case else None
+        harness.matmul_batched(a3, b3, c, cin=bias)
+        torch.cuda.synchronize()
+        check("bf16", c.cpu().numpy().reshape(batch * m, n), case["c"].reshape(batch * m, n), name)
+        seen += 1
+    assert seen >= 3
+
+
+def test_batched_on_the_tensor_cores(port):
+    rng = np.random.default_rng(17)
+    batch, m, n, k = 3, 256, 512, 264
+    a = f32_to_bf16_bits(rng.standard_normal((batch, m, k), dtype=np.float32))
+    b = f32_to_bf16_bits(rng.standard_normal((batch, n, k), dtype=np.float32))
+    bias = rng.uniform(-1, 1, n).astype(np.float32)
+    da, db, dbias = to_device(a, True), to_device(b, True), to_device(bias)
+    # everything batched, a bias row and ReLU: one launch per entry
+    c = torch.zeros((batch, m, n), dtype=torch.bfloat16, device="cuda")
+    before = capi.library().vecops_b200_launch_count()
+    harness.matmul_batched(da, db, c, cin=dbias, activation=capi.ACTIVATION_RELU)
+    assert capi.library().vecops_b200_launch_count() - before == batch
+    for i in range(batch):
+        check("bf16", bf16_result_to_numpy(c[i]), port.matmul_bf16_fused(a[i], b[i], bias, 1.0, None, 1), f"entry {i}")
+    # shared weights, A and C stacked densely: ONE launch with M * batch rows
+    c2 = torch.zeros((batch, m, n), dtype=torch.bfloat16, device="cuda")
+    before = capi.library().vecops_b200_launch_count()
+    harness.matmul_batched(da, db[0].expand(batch, n, k), c2, cin=dbias)
+    assert capi.library().vecops_b200_launch_count() - before == 1
+    for i in range(batch):
+        check("bf16", bf16_result_to_numpy(c2[i]), port.matmul_bf16_fused(a[i], b[0], bias), f"stacked entry {i}")
+    # a shared A against batched int8 weights (weight-only row), per-entry launches
+    w = rng.integers(-127, 128, (batch, 256, 512), dtype=np.int8)
+    aw = f32_to_bf16_bits(rng.standard_normal((16, 512), dtype=np.float32))
+    s = rng.uniform(0.001, 0.02, 256).astype(np.float32)
+    cw = torch.zeros((batch, 16, 256), dtype=torch.bfloat16, device="cuda")
+    harness.matmul_batched(to_device(aw, True).expand(batch, 16, 512), to_device(w), cw, to_device(s))
+    for i in range(batch):
+        check("w8", bf16_result_to_numpy(cw[i]), port.matmul_w8(aw, w[i], s), f"w8 entry {i}")

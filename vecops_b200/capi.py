@@ -86,6 +86,11 @@ class VecopsB200Epilogue(Structure):
 ACTIVATION_NONE, ACTIVATION_RELU, ACTIVATION_SIGMOID, ACTIVATION_SILU, ACTIVATION_CLAMP = range(5)
 
 
+class VecopsB200Batch(Structure):
+    _fields_ = [("struct_size", c_uint32), ("reserved", c_uint32), ("count", c_int64), ("a_stride_b", c_int64), ("b_stride_b", c_int64),
+                ("c_stride_b", c_int64), ("cin_stride_b", c_int64)]
+
+
 class VecopsB200Gather(Structure):
     _fields_ = [("struct_size", c_uint32), ("world", c_int32), ("c", POINTER(c_void_p)), ("n_total", c_int64), ("ldc", c_int64),
                 ("col0", c_int64), ("flags", c_uint32), ("reserved", c_uint32)]
@@ -134,6 +139,7 @@ def library() -> ctypes.CDLL:
         lib.vecops_b200_matmul_workspace.argtypes = [POINTER(VecopsB200Matmul), POINTER(c_uint64), e]
         lib.vecops_b200_matmul_run.argtypes = [POINTER(VecopsB200Matmul), e]
         lib.vecops_b200_matmul_run_fused.argtypes = [POINTER(VecopsB200Matmul), POINTER(VecopsB200Epilogue), e]
+        lib.vecops_b200_matmul_run_batched.argtypes = [POINTER(VecopsB200Matmul), POINTER(VecopsB200Batch), POINTER(VecopsB200Epilogue), e]
         lib.vecops_b200_quantize_rows.argtypes = [c_void_p, c_uint32, c_int64, c_int64, c_void_p, c_uint32, c_int64, c_int64, c_int64, c_float,
                                                   c_float, c_void_p, e]
         lib.vecops_b200_column_correction.argtypes = [c_void_p, c_uint32, c_int64, c_int64, c_int64, c_int32, c_void_p, c_void_p, e]

@@ -974,6 +974,69 @@ int32_t vecops_b200_matmul_run_fused(const VecopsB200Matmul* problem, const Veco
   return rc;
 }
 
+int32_t vecops_b200_matmul_run_batched(const VecopsB200Matmul* problem, const VecopsB200Batch* batch, const VecopsB200Epilogue* epilogue,
+                                       VecopsError* error) {
+  Row row;
+  int32_t rc = check_problem(problem, &row, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  if (batch == nullptr || batch->struct_size < sizeof(VecopsB200Batch) || batch->count < 0 || batch->a_stride_b < 0 ||
+      batch->b_stride_b < 0 || batch->c_stride_b < 0 || batch->cin_stride_b < 0)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "batch record is null, too small, or has a negative count or stride");
+  if (epilogue != nullptr && epilogue->struct_size < sizeof(VecopsB200Epilogue))
+    return set_error(error, VECOPS_STATUS_ABI_MISMATCH, "epilogue record is %u bytes, this library needs %zu", epilogue->struct_size,
+                     sizeof(VecopsB200Epilogue));
+  if (batch->count == 0 || problem->m == 0 || problem->n == 0) return VECOPS_STATUS_OK;
+  if (batch->count > 1 && batch->c_stride_b == 0)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "the batch entries of C must not share storage");
+  const VecopsB200Matmul& p = *problem;
+  const bool has_cin = epilogue != nullptr && epilogue->cin != nullptr;
+  // shared weights, A / C / CIn stacked densely along the batch axis: one product with M * count rows
+  const bool cin_stacks = !has_cin || (epilogue->cin_stride_m == 0 && batch->cin_stride_b == 0) ||
+                          (epilogue->cin_stride_m != 0 && batch->cin_stride_b == p.m * epilogue->cin_stride_m);
+  if (batch->count == 1 || (batch->b_stride_b == 0 && batch->a_stride_b == p.m * p.a_stride_m && batch->c_stride_b == p.m * p.c_stride_m &&
+                            cin_stacks && p.m * batch->count < (INT64_C(1) << 31))) {
+    VecopsB200Matmul flat = p;
+    flat.m = p.m * batch->count;
+    return epilogue != nullptr ? vecops_b200_matmul_run_fused(&flat, epilogue, error) : vecops_b200_matmul_run(&flat, error);
+  }
+  const size_t a_elem = dtype_size(p.a_dtype), b_elem = dtype_size(p.b_dtype), c_elem = dtype_size(p.c_dtype);
+  const size_t cin_elem = has_cin ? dtype_size(epilogue->cin_dtype) : 0;
+  if (has_cin && cin_elem == 0) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "unknown accumulator input dtype");
+  for (int64_t i = 0; i < batch->count; ++i) {
+    VecopsB200Matmul entry = p;
+    entry.flags |= VECOPS_B200_MATMUL_FLAG_ASYNC;
+    entry.a = p.a == nullptr ? nullptr : static_cast<const char*>(p.a) + i * batch->a_stride_b * static_cast<int64_t>(a_elem);
+    entry.b = p.b == nullptr ? nullptr : static_cast<const char*>(p.b) + i * batch->b_stride_b * static_cast<int64_t>(b_elem);
+    entry.c = p.c == nullptr ? nullptr : static_cast<char*>(p.c) + i * batch->c_stride_b * static_cast<int64_t>(c_elem);
+    if (epilogue != nullptr) {
+      VecopsB200Epilogue step = *epilogue;
+      if (has_cin) step.cin = static_cast<const char*>(epilogue->cin) + i * batch->cin_stride_b * static_cast<int64_t>(cin_elem);
+      rc = vecops_b200_matmul_run_fused(&entry, &step, error);
+    } else {
+      rc = vecops_b200_matmul_run(&entry, error);
+    }
+    if (rc != VECOPS_STATUS_OK) return rc;
+  }
+  if ((p.flags & VECOPS_B200_MATMUL_FLAG_ASYNC) == 0) {
+    int device = 0;
+    rc = current_device(p, &device, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+    int previous = -1;
+    cudaGetDevice(&previous);
+    if (previous != device) cudaSetDevice(device);
+    cudaError_t status = cudaStreamSynchronize(static_cast<cudaStream_t>(p.stream));
+    if (status != cudaSuccess) {
+      rc = cuda_fail(error, status, "cudaStreamSynchronize");
+    } else if (g_status_host != nullptr && *reinterpret_cast<volatile uint32_t*>(g_status_host) != 0) {
+      const uint32_t word = *reinterpret_cast<volatile uint32_t*>(g_status_host);
+      *reinterpret_cast<volatile uint32_t*>(g_status_host) = 0;
+      rc = set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "a bounded device wait ran out in a batched launch (status 0x%x)", word);
+    }
+    if (previous >= 0 && previous != device) cudaSetDevice(previous);
+  }
+  return rc;
+}
+
 const char* vecops_b200_kernel_name(uint32_t kernel) {
   return kernel < VECOPS_B200_KERNEL_COUNT_ ? kKernelNames[kernel] : nullptr;
 }

@@ -111,6 +111,39 @@ def matmul(a, b_nk, c, scale=None, kernel: int = capi.KERNEL_AUTO, stream=None, 
     del scratch
 
 
+def matmul_batched(a3, b3, c3, scale=None, kernel: int = capi.KERNEL_AUTO, stream=None, cin=None, alpha: float = 1.0,
+                   activation: int = capi.ACTIVATION_NONE, clamp_lo: float = 0.0, clamp_hi: float = 0.0) -> None:
+    """Rank-3 operands a3 [B,M,K], b3 [B,N,K], c3 [B,M,N] (expanded views share an operand across the batch: stride 0).
+
+    `cin`: a bias row [N], or a tensor broadcastable to [B,M,N]."""
+    import torch
+    if stream is None:
+        stream = torch.cuda.current_stream(c3.device)
+    count, m, n = c3.shape
+    problem = matmul_problem(a3[0], b3[0], c3[0], scale, kernel, stream, False)
+    batch = capi.VecopsB200Batch(ctypes.sizeof(capi.VecopsB200Batch), 0, count, a3.stride(0), b3.stride(0), c3.stride(0), 0)
+    fused = cin is not None or alpha != 1.0 or activation != capi.ACTIVATION_NONE
+    epilogue = None
+    if fused:
+        view = None
+        if cin is not None:
+            view = cin.expand(count, m, n)
+            batch.cin_stride_b = view.stride(0)
+            view = view[0]
+        epilogue = epilogue_record(view, alpha, activation, clamp_lo, clamp_hi, m, n)
+    # scratch for either way the library may run it: stacked into one product, or entry by entry
+    stacked = matmul_problem(a3[0], b3[0], c3[0], scale, kernel, stream, False)
+    stacked.m = m * count
+    need = max(workspace_bytes(problem), workspace_bytes(stacked))
+    scratch = torch.empty(need, dtype=torch.uint8, device=c3.device) if need else None
+    if scratch is not None:
+        problem.workspace, problem.workspace_size = scratch.data_ptr(), need
+    error = capi.ErrorBuffer()
+    error.raise_for(capi.library().vecops_b200_matmul_run_batched(byref(problem), byref(batch), byref(epilogue) if epilogue is not None else None,
+                                                                 byref(error.record)))
+    del scratch
+
+
 def quantize_rows(src, dst, scale: float, zero_point: float, stream=None) -> None:
     """dst[m,k] = convert(src[m,k] * scale + zero_point): src f32 or bf16 [M,K], dst u8 or i8 with K-contiguous rows."""
     import torch
