@@ -250,6 +250,35 @@ def measure_single(name: str, steps: int, warmup: int, dev, port, peaks, fused: 
             "launch": "one CUDA graph of all timed launches", "parity": parity, "device_status": status}
 
 
+def measure_f16(steps: int, warmup: int, dev, port, peaks) -> dict:
+    """The fp16 row at C2's shape (fp16 x fp16, fp32 accumulate, fp16 out) on the 16-bit tensor-core kernel."""
+    import torch
+    from oracle.checker import rel_frobenius
+    from vecops_b200 import capi, harness
+    m = n = k = 4096
+    rng = np.random.default_rng(7)
+    a_host = rng.standard_normal((m, k), dtype=np.float32).astype(np.float16)
+    b_host = rng.standard_normal((n, k), dtype=np.float32).astype(np.float16)
+    stream = torch.cuda.current_stream(dev)
+    sets = []
+    for i in range(4):  # 4 x 100 MB of operands and results: more than L2
+        a = torch.from_numpy(a_host).to(dev)
+        b = torch.from_numpy(b_host).to(dev) if i == 0 else sets[0][1][torch.randperm(n, device=dev)].contiguous()
+        sets.append((a, b, torch.empty((m, n), dtype=torch.float16, device=dev)))
+    prepared = [harness.PreparedMatmul(a, b, c, None, stream=stream) for a, b, c in sets]
+    prepared[0].launch()
+    torch.cuda.synchronize()
+    pick = np.unique(np.linspace(0, m - 1, 8).astype(np.int64))
+    want = port.matmul_f16(a_host[pick].view(np.uint16), b_host.view(np.uint16), out_f16=True).view(np.float16).astype(np.float32)
+    got = sets[0][2][torch.from_numpy(pick).to(dev)].float().cpu().numpy()
+    ms = time_graph(prepared, steps, warmup, dev)
+    tflops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+    return {"workload": "fp16 x fp16 -> fp16, M=N=K=4096, fp32 accumulate", "kernel": "bf16_tcgen05 (fp16 operand formats)", "ms_per_step": ms,
+            "value": tflops, "unit": "TFLOP/s", "bound": "tensor", "frac_of_measured_peak": tflops / float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])),
+            "l2": "rotating 4 operand sets (403 MB) vs L2 126 MB", "parity": {"rows": len(pick), "rel_fro": rel_frobenius(got, want)},
+            "device_status": take_status()}
+
+
 def measure_quantized(steps: int, warmup: int, dev, port, peaks) -> dict:
     """The quantised form at C3's size: fp32 activations quantised to u8 (pre-pass), s8 weights, int32 correction row, dequantising
     transform with a per-column scale, bf16 out.  The timed launches are the product kernel alone; the pre-passes are timed beside it."""
@@ -701,6 +730,10 @@ def run_ours(args) -> None:
                 extras["c3_quantized_u8s8"] = measure_quantized(50, 5, dev, port, peaks)
             except Exception as error:
                 extras["c3_quantized_u8s8"] = {"error": repr(error)}
+            try:
+                extras["c2_shape_f16"] = measure_f16(50, 5, dev, port, peaks)
+            except Exception as error:  # noqa: BLE001
+                extras["c2_shape_f16"] = {"error": repr(error)}
             torch.cuda.empty_cache()
             line["configs"] = extras
     if rank == 0:

@@ -19,6 +19,9 @@
  *     f32    f32    f32    -       f32          (AVX-512 fmadd leaf, amx/Backend.h:767-901)
  *     bf16   bf16   bf16   opt.    f32          AMX_BF16F32 with output<float>(bf16 C)
  *     bf16   bf16   f32    opt.    f32          AMX_BF16F32
+ *     f16    f16    f16|f32 opt.   f32          AMX_F16F32 (Atoms.h:74-77), fp16 C through output<float>(fp16 C); same
+ *                                               kernels as the bf16 rows (VECOPS_B200_KERNEL_BF16_TCGEN05 or the strided
+ *                                               one), the operand format being a field of the instruction descriptor
  *     i8/u8  i8/u8  i32    -       i32 (wraps)  AMX_I8I32<A,B>
  *     bf16   i8     bf16   opt.    f32          AMX_BF16F32 with input<bfloat16_t>(int8 W)
  *     i8/u8  i8/u8  f32|bf16 opt.  i32 (wraps)  AMX_I8I32<A,B> with a dequantising output<int32_t>(float C) transform
@@ -50,7 +53,7 @@ typedef enum VecopsB200MatmulKernel {
   VECOPS_B200_KERNEL_AUTO = 0,
   VECOPS_B200_KERNEL_GENERIC = 1,      /* strided SIMT; every dtype row above, any shape */
   VECOPS_B200_KERNEL_F32_SIMT = 2,     /* tiled FP32 FMA GEMM */
-  VECOPS_B200_KERNEL_BF16_TCGEN05 = 3, /* tcgen05 kind::f16, TMEM f32 accumulators, TMA pipeline */
+  VECOPS_B200_KERNEL_BF16_TCGEN05 = 3, /* tcgen05 kind::f16 (bf16 or fp16 operand pairs), TMEM f32 accumulators, TMA pipeline */
   VECOPS_B200_KERNEL_I8_TCGEN05 = 4,   /* tcgen05 kind::i8, TMEM i32 accumulators, TMA pipeline */
   VECOPS_B200_KERNEL_W8_SMALL_M = 5,   /* weight-only int8, M <= 32: 128-bit loads, in-register dequant, split-K */
   VECOPS_B200_KERNEL_W8_TCGEN05 = 6,   /* weight-only int8, M <= 128: weights widened into tensor memory, tcgen05 with W as the M operand */

@@ -58,6 +58,21 @@ ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SILU, ACT_CLAMP = range(5)
 _F = ctypes.c_float
 
 
+def f16_conversion_inputs() -> tuple[np.ndarray, np.ndarray]:
+    """(every fp16 bit pattern, float32 inputs for the narrowing) - the sweep the fp16 conversions are pinned on:
+    each fp16 value exactly, the tie above it and the floats either side of the tie, 2^20 random bit patterns, and
+    the edges of the range (2^-25, 65520, infinities, NaNs)."""
+    patterns = np.arange(65536, dtype=np.uint16)
+    base = patterns.view(np.float16).astype(np.float32).view(np.uint32)
+    rng = np.random.default_rng(5)
+    bits = np.concatenate([
+        base, base + np.uint32(0x1000), base + np.uint32(0x0fff), base + np.uint32(0x1001),
+        rng.integers(0, 2**32, 1 << 20, dtype=np.uint64).astype(np.uint32),
+        np.array([0x33000000, 0x33000001, 0x32ffffff, 0x477fe000, 0x477fefff, 0x477ff000, 0x477ff001, 0x7f800000, 0xff800000,
+                  0x7fc00000, 0x7f800001], dtype=np.uint32)])
+    return patterns, bits.view(np.float32)
+
+
 def _cin_view(cin, m: int, n: int):
     """(array viewed as [m, n] with possibly zero strides, kind) - kind 1 for bf16 bits, else 0."""
     if cin is None:
@@ -87,6 +102,14 @@ class Port:
         self.lib.oracle_matmul_i8_accumulate.argtypes = [_I64] * 3 + [_P, _I64, _I64, c_int, _P, _I64, _I64, c_int, _P, _I64, _I64, _P, _I64,
                                                                      _I64]
 
+        self.lib.oracle_f32_to_f16.restype = ctypes.c_uint16
+        self.lib.oracle_f32_to_f16.argtypes = [ctypes.c_float]
+        self.lib.oracle_f16_to_f32.restype = ctypes.c_float
+        self.lib.oracle_f16_to_f32.argtypes = [ctypes.c_uint16]
+        self.lib.oracle_f16_widen.argtypes = [_P, _P, _I64]
+        self.lib.oracle_f16_narrow.argtypes = [_P, _P, _I64]
+        self.lib.oracle_matmul_f16_fused.argtypes = [_I64] * 3 + [_P, _I64, _I64, _P, _I64, _I64, _P, _I64, _I64, _F, _P, c_int, _F, _F, _P,
+                                                                 _I64, _I64, c_int]
         self.lib.oracle_quantize_rows.argtypes = [_I64, _I64, _P, _I64, _I64, _F, _F, _P, _I64, _I64, c_int]
         self.lib.oracle_matmul_i8_dequant.argtypes = [_I64] * 3 + [_P, _I64, _I64, c_int, _P, _I64, _I64, c_int, _P, _I64, _I64, _F, _P, c_int,
                                                                   _F, _F, _P, _I64, _I64, c_int]
@@ -139,6 +162,30 @@ class Port:
         self.lib.oracle_matmul_bf16_fused(m, n, k, _ptr(a), *_strides(a), _ptr(b_nk), *_strides(b_nk), _ptr(cin_view), kind,
                                           *(_strides(cin_view) if cin_view is not None else (0, 0)), float(alpha), _ptr(scale), int(act),
                                           float(lo), float(hi), _ptr(c), n, 1, int(out_bf16))
+        return c
+
+    def f16_widen(self, bits: np.ndarray) -> np.ndarray:
+        bits = np.ascontiguousarray(bits, dtype=np.uint16)
+        out = np.empty(bits.shape, dtype=np.float32)
+        self.lib.oracle_f16_widen(_ptr(bits), _ptr(out), bits.size)
+        return out
+
+    def f16_narrow(self, values: np.ndarray) -> np.ndarray:
+        values = np.ascontiguousarray(values, dtype=np.float32)
+        out = np.empty(values.shape, dtype=np.uint16)
+        self.lib.oracle_f16_narrow(_ptr(values), _ptr(out), values.size)
+        return out
+
+    def matmul_f16(self, a, b_nk, cin=None, alpha=1.0, scale=None, act=ACT_NONE, lo=0.0, hi=0.0, out_f16=True):
+        """fp16 bit patterns (uint16) in; fp16 bits or float32 out.  `cin`: None or an [M,N]-broadcastable float32 array."""
+        m, k = a.shape
+        n = b_nk.shape[0]
+        c = np.empty((m, n), dtype=np.uint16 if out_f16 else np.float32)
+        cin_view, kind = _cin_view(cin, m, n)
+        assert kind == 0, "the fp16 form takes an f32 accumulator input"
+        self.lib.oracle_matmul_f16_fused(m, n, k, _ptr(a), *_strides(a), _ptr(b_nk), *_strides(b_nk), _ptr(cin_view),
+                                         *(_strides(cin_view) if cin_view is not None else (0, 0)), float(alpha), _ptr(scale), int(act),
+                                         float(lo), float(hi), _ptr(c), n, 1, int(out_f16))
         return c
 
     def matmul_f32_fused(self, a, b_nk, cin=None, alpha=1.0, scale=None, act=ACT_NONE, lo=0.0, hi=0.0):
@@ -198,8 +245,23 @@ class Ref:
             lib.ref_matmul_i8_accumulate.argtypes = [_I64] * 3 + [_P, _I64, _P, _I64, _P, _I64, _I64, _P, _I64]
         if hasattr(lib, "ref_matmul_bf16_batched"):
             lib.ref_matmul_bf16_batched.argtypes = [_I64] * 4 + [_P, _I64, _I64, _P, _I64, _I64, _P, _P, _I64, _I64]
+        if hasattr(lib, "ref_f16_widen"):
+            lib.ref_f16_widen.argtypes = [_P, _P, _I64]
+            lib.ref_f16_narrow.argtypes = [_P, _P, _I64]
         if hasattr(lib, "ref_matmul_quantized_u8s8"):
             lib.ref_matmul_quantized_u8s8.argtypes = [_I64] * 3 + [_P, _I64, _F, _F, _P, _I64, _P, _F, _P, _I64]
+
+    def f16_widen(self, bits: np.ndarray) -> np.ndarray:
+        bits = np.ascontiguousarray(bits, dtype=np.uint16)
+        out = np.empty(bits.shape, dtype=np.float32)
+        self.lib.ref_f16_widen(_ptr(bits), _ptr(out), bits.size)
+        return out
+
+    def f16_narrow(self, values: np.ndarray) -> np.ndarray:
+        values = np.ascontiguousarray(values, dtype=np.float32)
+        out = np.empty(values.shape, dtype=np.uint16)
+        self.lib.ref_f16_narrow(_ptr(values), _ptr(out), values.size)
+        return out
 
     def matmul_bf16_batched(self, a3, b3, bias=None):
         """Rank-3 bf16 operands [B,M,K] x [B,N,K] -> f32 [B,M,N]; a leading stride may be 0 (np.broadcast_to views)."""

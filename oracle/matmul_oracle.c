@@ -31,6 +31,9 @@
  *
  * Pinned against the reference itself: oracle/_ref (the reference's own
  * ops::matmul built from its headers) on the fixtures under tests/golden/.
+ * One row is the exception - fp16 operands: PARITY UNPINNED for the product
+ * (the reference's fp16 tile kernel needs AMX-FP16, absent on the hosts this
+ * was built on); its two conversions are pinned, see oracle_matmul_f16_fused.
  */
 #include <math.h>
 #include <stdint.h>
@@ -158,6 +161,88 @@ void oracle_matmul_bf16_fused(int64_t m, int64_t n, int64_t k, const uint16_t* a
       if (column_scale) acc *= column_scale[j];
       acc = oracle_activation(acc, act, lo, hi);
       if (c_is_bf16) ((uint16_t*)c)[i * scm + j * scn] = f32_to_bf16(acc);
+      else ((float*)c)[i * scm + j * scn] = acc;
+    }
+  }
+}
+
+/* fp16 x fp16 -> fp32 accumulate -> transform -> fp16 or fp32: the AMX_F16F32 row of the reference
+ * (include/vecops/matmul/details/kernel/amx/Atoms.h:74-77; the accumulate form is the bf16 one above).
+ * float16_t is a 16-bit storage wrapper whose widening is exact and whose narrowing is IEEE round to nearest even
+ * (include/vecops/util/Float16.h:272-277).  Both conversions below are pinned bit for bit against the reference's
+ * own (all 65536 patterns; a sweep of floats through the narrowing).  The product itself is NOT pinned: the
+ * reference's fp16 tile kernel needs AMX-FP16, which the hosts this was developed on do not have ("parity unpinned"
+ * for this one row; the tests hold the CUDA path to this restatement). */
+static inline float f16_to_f32(uint16_t bits) {
+  const uint32_t sign = (uint32_t)(bits & 0x8000u) << 16;
+  uint32_t exponent = (bits >> 10) & 0x1fu;
+  uint32_t mantissa = bits & 0x3ffu;
+  uint32_t wide;
+  if (exponent == 0x1fu) {
+    wide = sign | 0x7f800000u | (mantissa << 13) | (mantissa ? 0x00400000u : 0u); /* a NaN comes out quiet, payload kept */
+  } else if (exponent != 0) {
+    wide = sign | ((exponent + 112u) << 23) | (mantissa << 13);
+  } else if (mantissa == 0) {
+    wide = sign;
+  } else { /* subnormal: renormalise */
+    int shift = 0;
+    while ((mantissa & 0x400u) == 0) {
+      mantissa <<= 1;
+      ++shift;
+    }
+    mantissa &= 0x3ffu;
+    wide = sign | ((uint32_t)(113 - shift) << 23) | (mantissa << 13);
+  }
+  float out;
+  memcpy(&out, &wide, sizeof(out));
+  return out;
+}
+
+static inline uint16_t f32_to_f16(float value) {
+  uint32_t wide;
+  memcpy(&wide, &value, sizeof(wide));
+  const uint16_t sign = (uint16_t)((wide >> 16) & 0x8000u);
+  const uint32_t magnitude = wide & 0x7fffffffu;
+  if (magnitude > 0x7f800000u) return (uint16_t)(sign | 0x7e00u | ((magnitude >> 13) & 0x1ffu)); /* quiet NaN, top payload bits kept */
+  if (magnitude >= 0x47800000u) return (uint16_t)(sign | 0x7c00u); /* >= 65536 (or inf): infinity; 65520..65536 rounds there below */
+  if (magnitude < 0x33000000u) return sign;                        /* < 2^-25: rounds to zero (2^-25 itself ties to even = 0) */
+  const int32_t exponent = (int32_t)(magnitude >> 23) - 127;
+  uint32_t mantissa = (magnitude & 0x7fffffu) | 0x800000u;          /* 24 significant bits */
+  int drop = exponent >= -14 ? 13 : 13 + (-14 - exponent);           /* bits that do not fit */
+  uint32_t kept = mantissa >> drop;
+  const uint32_t rest = mantissa & ((1u << drop) - 1u);
+  const uint32_t half = 1u << (drop - 1);
+  if (rest > half || (rest == half && (kept & 1u))) ++kept;
+  uint32_t out;
+  if (exponent >= -14) out = ((uint32_t)(exponent + 15) << 10) + (kept - 0x400u); /* a carry out of the mantissa bumps the exponent */
+  else out = kept;                                                                  /* subnormal; a carry lands on the smallest normal */
+  return (uint16_t)(sign | out);
+}
+
+uint16_t oracle_f32_to_f16(float value) { return f32_to_f16(value); }
+float oracle_f16_to_f32(uint16_t bits) { return f16_to_f32(bits); }
+void oracle_f16_widen(const uint16_t* src, float* dst, int64_t count) {
+  for (int64_t i = 0; i < count; ++i) dst[i] = f16_to_f32(src[i]);
+}
+void oracle_f16_narrow(const float* src, uint16_t* dst, int64_t count) {
+  for (int64_t i = 0; i < count; ++i) dst[i] = f32_to_f16(src[i]);
+}
+
+/* cin: f32 only (or NULL).  act, alpha, column_scale as in the bf16 form. */
+void oracle_matmul_f16_fused(int64_t m, int64_t n, int64_t k, const uint16_t* a, int64_t sam, int64_t sak, const uint16_t* b,
+                             int64_t sbn, int64_t sbk, const float* cin, int64_t cin_sm, int64_t cin_sn, float alpha,
+                             const float* column_scale, int act, float lo, float hi, void* c, int64_t scm, int64_t scn,
+                             int c_is_f16) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t i = 0; i < m; ++i) {
+    for (int64_t j = 0; j < n; ++j) {
+      double sum = cin ? (double)cin[i * cin_sm + j * cin_sn] : 0.0;
+      for (int64_t kk = 0; kk < k; ++kk)
+        sum += (double)f16_to_f32(a[i * sam + kk * sak]) * (double)f16_to_f32(b[j * sbn + kk * sbk]);
+      float acc = (float)sum * alpha;
+      if (column_scale) acc *= column_scale[j];
+      acc = oracle_activation(acc, act, lo, hi);
+      if (c_is_f16) ((uint16_t*)c)[i * scm + j * scn] = f32_to_f16(acc);
       else ((float*)c)[i * scm + j * scn] = acc;
     }
   }

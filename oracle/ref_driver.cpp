@@ -274,4 +274,13 @@ int ref_matmul_f32_leaf(int64_t m, int64_t n, int64_t k, const float* a, int64_t
   return 0;
 }
 
+// float16_t's own conversions (util/Float16.h:272-277), element by element: the part of the fp16 row that runs on
+// a host without AMX-FP16.
+void ref_f16_widen(const uint16_t* src, float* dst, int64_t count) {
+  for (int64_t i = 0; i < count; ++i) dst[i] = static_cast<float>(float16_t::from_bits(src[i]));
+}
+void ref_f16_narrow(const float* src, uint16_t* dst, int64_t count) {
+  for (int64_t i = 0; i < count; ++i) dst[i] = float16_t(src[i]).to_bits();
+}
+
 }  // extern "C"

@@ -13,6 +13,7 @@ pairs, GEMV orientations: MatmulTest.cpp:434-452, :1005-1023).
 """
 from __future__ import annotations
 
+import hashlib
 import sys
 from pathlib import Path
 
@@ -21,7 +22,8 @@ import numpy as np
 ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
 
-from oracle.checker import ACT_CLAMP, ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SILU, Ref, f32_to_bf16_bits  # noqa: E402
+from oracle.checker import (ACT_CLAMP, ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SILU, Ref, f16_conversion_inputs,  # noqa: E402
+                            f32_to_bf16_bits)
 
 HERE = Path(__file__).resolve().parent
 
@@ -163,6 +165,13 @@ def main() -> None:
     a = bf16_pattern(batch * m * k, 3, (batch, m, k))
     b = bf16_pattern(batch * n * k, 11, (batch, n, k))
     cases["batched_4x19x21x72"] = dict(kind="batched_bf16", a=a, b=b, shared=np.array(""), c=ref.matmul_bf16_batched(a, b))
+
+    # float16_t's widening and narrowing (util/Float16.h:272-277) over the whole sweep, as digests: the part of the
+    # AMX_F16F32 row a host without AMX-FP16 can run
+    patterns, floats = f16_conversion_inputs()
+    cases["f16_conversions"] = dict(kind="f16_convert",
+                                    widen_sha256=np.array(hashlib.sha256(ref.f16_widen(patterns).tobytes()).hexdigest()),
+                                    narrow_sha256=np.array(hashlib.sha256(ref.f16_narrow(floats).tobytes()).hexdigest()))
 
     for name, arrays in cases.items():
         kind = arrays.pop("kind")

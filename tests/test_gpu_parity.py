@@ -78,9 +78,9 @@ def oracle(kind, port, a, b, scale, out_bf16=True):
 def test_golden_fixtures_through_automatic_dispatch(golden):
     for name, case in golden.items():
         kind = str(case["kind"])
+        if kind in ("fused_bf16", "i8acc", "quant_u8s8", "batched_bf16", "f16_convert"):
+            continue  # the fused forms have their own tests below; the conversion digests are the checker's own
         a, b = case["a"], case["b"]
-        if kind in ("fused_bf16", "i8acc", "quant_u8s8", "batched_bf16"):
-            continue  # the fused forms have their own test below
         if kind == "i8":
             check(kind, run_case(kind, a, b), case["c"], name)
         elif kind == "f32":
@@ -693,3 +693,88 @@ def test_batched_on_the_tensor_cores(port):
     harness.matmul_batched(to_device(aw, True).expand(batch, 16, 512), to_device(w), cw, to_device(s))
     for i in range(batch):
         check("w8", bf16_result_to_numpy(cw[i]), port.matmul_w8(aw, w[i], s), f"w8 entry {i}")
+
+
+# ------------------------------------------------------------------ fp16 operands (the reference's AMX_F16F32 row)
+
+def _f16_gpu(a_bits, b_bits, out_f16, kernel, ldc_pad=0, **fused):
+    m, n = a_bits.shape[0], b_bits.shape[0]
+    da = to_device(a_bits).view(torch.float16)
+    db = to_device(b_bits).view(torch.float16)
+    cin = fused.pop("cin", None)
+    scale = fused.pop("scale", None)
+    storage = torch.full((m, n + ldc_pad), -3, dtype=torch.float16 if out_f16 else torch.float32, device="cuda")
+    c = storage[:, :n]
+    vecops_b200.matmul(da, db, c, to_device(scale) if scale is not None else None, kernel=kernel,
+                       cin=to_device(cin) if cin is not None else None, **fused)
+    torch.cuda.synchronize()
+    if ldc_pad:
+        assert bool((storage[:, n:] == -3).all()), "kernel wrote outside its C columns"
+    return c.contiguous().float().cpu().numpy()
+
+
+def _f16_inputs(m, n, k, rng):
+    a = rng.standard_normal((m, k), dtype=np.float32).astype(np.float16).view(np.uint16)
+    b = rng.standard_normal((n, k), dtype=np.float32).astype(np.float16).view(np.uint16)
+    return a, b
+
+
+def _f16_want(port, a, b, out_f16, **kw):
+    want = port.matmul_f16(a, b, out_f16=out_f16, **kw)
+    return want.view(np.float16).astype(np.float32) if out_f16 else want
+
+
+@pytest.mark.parametrize("m,n,k", TC_SHAPES)
+@pytest.mark.parametrize("out_f16", [True, False])
+def test_f16_tcgen05(port, cta_form, m, n, k, out_f16):
+    # the 16-bit tensor-core kernel with fp16 formats in the instruction descriptor and fp16 tensor maps
+    rng = np.random.default_rng(m * 5 + n * 3 + k)
+    a, b = _f16_inputs(m, n, k, rng)
+    got = _f16_gpu(a, b, out_f16, K.KERNEL_BF16_TCGEN05)
+    assert rel_frobenius(got, _f16_want(port, a, b, out_f16)) <= TOL_BF16
+
+
+def test_f16_precision_is_fp16_not_bf16(port):
+    # values with ten mantissa bits: a kernel that read them as bf16, or narrowed them to bf16, would miss by ~4e-3
+    rng = np.random.default_rng(3)
+    a = (1.0 + rng.integers(0, 1024, (128, 256)) / 1024.0).astype(np.float16).view(np.uint16)
+    b = (1.0 + rng.integers(0, 1024, (256, 256)) / 1024.0).astype(np.float16).view(np.uint16)
+    for kernel in (K.KERNEL_BF16_TCGEN05, K.KERNEL_GENERIC):
+        got = _f16_gpu(a, b, False, kernel)
+        assert rel_frobenius(got, _f16_want(port, a, b, False)) <= 1e-5  # fp32 summation order only
+        got = _f16_gpu(a, b, True, kernel)
+        assert rel_frobenius(got, _f16_want(port, a, b, True)) <= 3e-4  # one fp16 rounding of the result on both sides
+
+
+def test_f16_ragged_strided_and_fused(port):
+    from oracle.checker import ACT_RELU, ACT_SILU
+    rng = np.random.default_rng(8)
+    # shapes TMA cannot address run on the strided kernel through automatic dispatch
+    for m, n, k in [(19, 23, 65), (1, 8, 129), (8, 1, 129), (37, 51, 79)]:
+        a, b = _f16_inputs(m, n, k, rng)
+        for out_f16 in (True, False):
+            got = _f16_gpu(a, b, out_f16, K.KERNEL_AUTO, ldc_pad=3)
+            assert rel_frobenius(got, _f16_want(port, a, b, out_f16)) <= TOL_BF16
+    # fused output transform on both kernels
+    m, n, k = 300, 520, 264
+    a, b = _f16_inputs(m, n, k, rng)
+    a = (a.view(np.float16).astype(np.float32) * 0.1).astype(np.float16).view(np.uint16)
+    bias = rng.uniform(-1, 1, n).astype(np.float32)
+    scale = rng.uniform(0.5, 2.0, n).astype(np.float32)
+    for kernel in (K.KERNEL_BF16_TCGEN05, K.KERNEL_GENERIC):
+        for out_f16 in (True, False):
+            got = _f16_gpu(a, b, out_f16, kernel, cin=bias, scale=scale, alpha=0.5, activation=capi.ACTIVATION_SILU)
+            want = _f16_want(port, a, b, out_f16, cin=bias, scale=scale, alpha=0.5, act=ACT_SILU)
+            assert rel_frobenius(got, want) <= TOL_BF16
+            got = _f16_gpu(a, b, out_f16, kernel, activation=capi.ACTIVATION_RELU)
+            assert rel_frobenius(got, _f16_want(port, a, b, out_f16, act=ACT_RELU)) <= TOL_BF16
+
+
+def test_f16_mixed_with_bf16_is_refused():
+    a = torch.zeros((128, 64), dtype=torch.float16, device="cuda")
+    b = torch.zeros((256, 64), dtype=torch.bfloat16, device="cuda")
+    c = torch.zeros((128, 256), dtype=torch.float32, device="cuda")
+    with pytest.raises(capi.VecopsB200Error):
+        vecops_b200.matmul(a, b, c)
+    with pytest.raises(capi.VecopsB200Error):  # fp16 operands narrow to fp16 or stay fp32, never bf16
+        vecops_b200.matmul(a, a[:64].contiguous(), torch.zeros((128, 64), dtype=torch.bfloat16, device="cuda"))

@@ -1,10 +1,12 @@
 """The CPU checker against the reference: committed fixtures (outputs of the
 reference's own ops::matmul) and, where this host can run it, the reference
 library itself."""
+import hashlib
+
 import numpy as np
 import pytest
 
-from oracle.checker import Ref, bf16_bits_to_f32, f32_to_bf16_bits, rel_frobenius
+from oracle.checker import Ref, bf16_bits_to_f32, f16_conversion_inputs, f32_to_bf16_bits, rel_frobenius
 from tests.helpers import TOL_BF16, TOL_F32
 
 
@@ -26,6 +28,13 @@ def test_port_matches_golden_fixtures(port, golden):
     checked = 0
     for name, case in golden.items():
         kind = str(case["kind"])
+        if kind == "f16_convert":
+            # float16_t's own conversions, recorded as digests over the whole sweep (every pattern, every tie)
+            patterns, floats = f16_conversion_inputs()
+            assert hashlib.sha256(port.f16_widen(patterns).tobytes()).hexdigest() == str(case["widen_sha256"]), name
+            assert hashlib.sha256(port.f16_narrow(floats).tobytes()).hexdigest() == str(case["narrow_sha256"]), name
+            checked += 1
+            continue
         a, b = case["a"], case["b"]
         if kind == "i8":
             assert np.array_equal(port.matmul_i8(a, b), case["c"]), name
@@ -61,7 +70,7 @@ def test_port_matches_golden_fixtures(port, golden):
         else:
             raise AssertionError(f"unknown fixture kind {kind}")
         checked += 1
-    assert checked >= 37
+    assert checked >= 38
 
 
 def test_int32_accumulator_wraps(port):
@@ -103,3 +112,15 @@ def test_port_against_reference_library_live(port):
     s = rng.uniform(0.001, 0.02, 64).astype(np.float32)
     got = bf16_bits_to_f32(port.matmul_w8(a[:16], w, s))
     assert rel_frobenius(got, bf16_bits_to_f32(ref.matmul_w8(a[:16], w, s))) <= TOL_BF16
+
+
+def test_fp16_product_against_numpy(port):
+    # the fp16 row's restatement (conversions pinned by the fixture above) against a float64 numpy product
+    rng = np.random.default_rng(11)
+    a = rng.standard_normal((19, 65)).astype(np.float16)
+    b = rng.standard_normal((23, 65)).astype(np.float16)
+    want = a.astype(np.float64) @ b.astype(np.float64).T
+    got = port.matmul_f16(a.view(np.uint16), b.view(np.uint16), out_f16=False)
+    assert np.array_equal(got, want.astype(np.float32))
+    got16 = port.matmul_f16(a.view(np.uint16), b.view(np.uint16), out_f16=True)
+    assert np.array_equal(got16, want.astype(np.float32).astype(np.float16).view(np.uint16))

@@ -40,6 +40,7 @@
 // Algorithmic traffic per launch: (M*K + N*K) * sizeof(in) + M*N * sizeof(out).
 #pragma once
 
+#include <cuda_fp16.h>
 #include <type_traits>
 
 #include "epilogue.cuh"
@@ -173,12 +174,26 @@ __host__ __device__ inline int gemm_tail_split(long long num_tiles, int grid, in
   return split;
 }
 
+// Two fp32 values -> one word of two 16-bit outputs of type OutT (bf16 or fp16), round to nearest even.
+template <typename OutT>
+__device__ __forceinline__ uint32_t pack_out16x2(float lo, float hi);
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// OutT: __nv_bfloat16 or float for kind::f16, int32_t for kind::i8.
+template <>
+__device__ __forceinline__ uint32_t pack_out16x2<__nv_bfloat16>(float lo, float hi) {
+  return pack_bf16x2(lo, hi);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_out16x2<__half>(float lo, float hi) {
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// OutT: __nv_bfloat16, __half or float for kind::f16 (bf16 or fp16 operands, chosen by the instruction descriptor), int32_t for kind::i8.
 template <bool kInt8, typename OutT, bool kPair>
 __global__ void __launch_bounds__(GemmTc::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -482,8 +497,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           transform32(v1, col0 + 32);
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            words[j] = pack_bf16x2(__uint_as_float(v0[2 * j]), __uint_as_float(v0[2 * j + 1]));
-            words[16 + j] = pack_bf16x2(__uint_as_float(v1[2 * j]), __uint_as_float(v1[2 * j + 1]));
+            words[j] = pack_out16x2<OutT>(__uint_as_float(v0[2 * j]), __uint_as_float(v0[2 * j + 1]));
+            words[16 + j] = pack_out16x2<OutT>(__uint_as_float(v1[2 * j]), __uint_as_float(v1[2 * j + 1]));
           }
         }
         if (use_tma_store == 2) {

@@ -115,7 +115,7 @@ int32_t current_device(const VecopsB200Matmul& p, int* device, VecopsError* erro
 
 // ------------------------------------------------------------------ problem classification
 
-enum class Row { Invalid, F32, BF16, I8, W8, QI8 };  // QI8: 8-bit operands, int32 accumulate, floating-point output (dequantising form)
+enum class Row { Invalid, F32, BF16, I8, W8, QI8, F16 };  // QI8: 8-bit operands, int32 accumulate, floating-point output (dequantising form)
 
 size_t dtype_size(uint32_t dtype) {
   switch (dtype) {
@@ -132,6 +132,7 @@ Row classify(const VecopsB200Matmul& p) {
   const bool b8 = b == VECOPS_DTYPE_I8 || b == VECOPS_DTYPE_U8;
   if (a == VECOPS_DTYPE_F32 && b == VECOPS_DTYPE_F32 && c == VECOPS_DTYPE_F32) return Row::F32;
   if (a == VECOPS_DTYPE_BF16 && b == VECOPS_DTYPE_BF16 && (c == VECOPS_DTYPE_BF16 || c == VECOPS_DTYPE_F32)) return Row::BF16;
+  if (a == VECOPS_DTYPE_F16 && b == VECOPS_DTYPE_F16 && (c == VECOPS_DTYPE_F16 || c == VECOPS_DTYPE_F32)) return Row::F16;
   if (a8 && b8 && c == VECOPS_DTYPE_I32) return Row::I8;
   if (a8 && b8 && (c == VECOPS_DTYPE_F32 || c == VECOPS_DTYPE_BF16)) return Row::QI8;
   if (a == VECOPS_DTYPE_BF16 && b == VECOPS_DTYPE_I8 && (c == VECOPS_DTYPE_BF16 || c == VECOPS_DTYPE_F32)) return Row::W8;
@@ -163,7 +164,7 @@ bool applicable(const VecopsB200Matmul& p, Row row, uint32_t kernel) {
       return row == Row::F32 && p.a_stride_k == 1 && p.c_stride_n == 1 && (p.b_stride_k == 1 || p.b_stride_n == 1) &&
              p.column_scale == nullptr;
     case VECOPS_B200_KERNEL_BF16_TCGEN05:
-      return row == Row::BF16 && tma_operands_ok(p, 2);
+      return (row == Row::BF16 || row == Row::F16) && tma_operands_ok(p, 2);  // fp16 rides the same kernel: the formats are in the instruction descriptor
     case VECOPS_B200_KERNEL_I8_TCGEN05:
       return (row == Row::I8 && tma_operands_ok(p, 1) && p.column_scale == nullptr) || (row == Row::QI8 && tma_operands_ok(p, 1));
     case VECOPS_B200_KERNEL_W8_SMALL_M:
@@ -222,6 +223,7 @@ int32_t select_kernel(const VecopsB200Matmul& p, Row row, uint32_t* kernel, Veco
     case Row::F32:
       if (!tiny && applicable(p, row, VECOPS_B200_KERNEL_F32_SIMT)) pick = VECOPS_B200_KERNEL_F32_SIMT;
       break;
+    case Row::F16:
     case Row::BF16:
       if (!tiny && applicable(p, row, VECOPS_B200_KERNEL_BF16_TCGEN05)) pick = VECOPS_B200_KERNEL_BF16_TCGEN05;
       break;
@@ -434,8 +436,12 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
     return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "tcgen05 kernels need an sm_100 device, found sm_%d%d", dev.prop.major,
                      dev.prop.minor);
   constexpr size_t elem = kInt8 ? 1 : 2;
-  const CUtensorMapDataType in_type = kInt8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const bool fp16_in = !kInt8 && p.a_dtype == VECOPS_DTYPE_F16;
+  const CUtensorMapDataType in_type = kInt8     ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                      : fp16_in ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const CUtensorMapDataType out_type = std::is_same<OutT, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                       : std::is_same<OutT, __half>::value      ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                        : std::is_same<OutT, float>::value       ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                                                                 : CU_TENSOR_MAP_DATA_TYPE_INT32;
   const uint32_t box_k = G::kBlockKBytes / elem;
@@ -482,7 +488,8 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
     idesc = umma_instr_desc(kUmmaAccS32, p.a_dtype == VECOPS_DTYPE_I8 ? kUmmaS8 : kUmmaU8,
                             p.b_dtype == VECOPS_DTYPE_I8 ? kUmmaS8 : kUmmaU8, mma_m, G::kBlockN);
   } else {
-    idesc = umma_instr_desc(kUmmaAccF32, kUmmaBF16, kUmmaBF16, mma_m, G::kBlockN);
+    const uint32_t format = fp16_in ? kUmmaF16 : kUmmaBF16;
+    idesc = umma_instr_desc(kUmmaAccF32, format, format, mma_m, G::kBlockN);
   }
   rc = prepare_gemm_kernels<kInt8, OutT>(device, error);
   if (rc != VECOPS_STATUS_OK) return rc;
@@ -574,6 +581,10 @@ int32_t launch_generic(const VecopsB200Matmul& p, Row row, cudaStream_t stream, 
     case Row::BF16:
       if (c_bf16) launch_generic_typed<bf16, bf16, bf16, float>(p, stream);
       else launch_generic_typed<bf16, bf16, float, float>(p, stream);
+      break;
+    case Row::F16:
+      if (p.c_dtype == VECOPS_DTYPE_F16) launch_generic_typed<__half, __half, __half, float>(p, stream);
+      else launch_generic_typed<__half, __half, float, float>(p, stream);
       break;
     case Row::W8:
       if (c_bf16) launch_generic_typed<bf16, int8_t, bf16, float>(p, stream);
@@ -883,8 +894,9 @@ int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* err
         case VECOPS_B200_KERNEL_GENERIC: rc = launch_generic(p, row, stream, error); break;
         case VECOPS_B200_KERNEL_F32_SIMT: rc = launch_f32(p, stream, error); break;
         case VECOPS_B200_KERNEL_BF16_TCGEN05:
-          rc = p.c_dtype == VECOPS_DTYPE_BF16 ? launch_tcgen05<false, __nv_bfloat16>(p, *dev, stream, error)
-                                              : launch_tcgen05<false, float>(p, *dev, stream, error);
+          rc = p.c_dtype == VECOPS_DTYPE_BF16  ? launch_tcgen05<false, __nv_bfloat16>(p, *dev, stream, error)
+               : p.c_dtype == VECOPS_DTYPE_F16 ? launch_tcgen05<false, __half>(p, *dev, stream, error)
+                                               : launch_tcgen05<false, float>(p, *dev, stream, error);
           break;
         case VECOPS_B200_KERNEL_I8_TCGEN05:
           rc = p.c_dtype == VECOPS_DTYPE_I32    ? launch_tcgen05<true, int32_t>(p, *dev, stream, error)

@@ -5,6 +5,7 @@
 #include "epilogue.cuh"
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -23,6 +24,10 @@ __device__ __forceinline__ float load_as<float, __nv_bfloat16>(const __nv_bfloat
 // 8-bit operands widen to 32-bit and accumulate modulo 2^32 (the vecops
 // int32 accumulator wraps: include/vecops/vec/WideningDot.h:100-103).
 template <>
+__device__ __forceinline__ float load_as<float, __half>(const __half* p) {
+  return __half2float(*p);
+}
+template <>
 __device__ __forceinline__ uint32_t load_as<uint32_t, int8_t>(const int8_t* p) {
   return static_cast<uint32_t>(static_cast<int32_t>(*p));
 }
@@ -38,6 +43,10 @@ __device__ __forceinline__ void store_from(Out* p, Acc v) {
 template <>
 __device__ __forceinline__ void store_from<__nv_bfloat16, float>(__nv_bfloat16* p, float v) {
   *p = __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ void store_from<__half, float>(__half* p, float v) {
+  *p = __float2half_rn(v);
 }
 template <>
 __device__ __forceinline__ void store_from<int32_t, uint32_t>(int32_t* p, uint32_t v) {

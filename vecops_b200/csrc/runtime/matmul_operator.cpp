@@ -142,13 +142,15 @@ VariantDescriptor* build_variant(std::uint64_t a_mask, std::uint64_t b_mask, std
 
 const VariantDescriptor* variant_descriptor(std::uint32_t kernel) {
   constexpr auto f32 = bit(VECOPS_DTYPE_F32), bf16 = bit(VECOPS_DTYPE_BF16), i8 = bit(VECOPS_DTYPE_I8),
-                 u8 = bit(VECOPS_DTYPE_U8), i32 = bit(VECOPS_DTYPE_I32);
+                 u8 = bit(VECOPS_DTYPE_U8), i32 = bit(VECOPS_DTYPE_I32), f16 = bit(VECOPS_DTYPE_F16);
   static const VariantDescriptor* const table[VECOPS_B200_KERNEL_COUNT_] = {
       nullptr,
-      build_variant<VECOPS_B200_KERNEL_GENERIC>(f32 | bf16 | i8 | u8, f32 | bf16 | i8 | u8, f32 | bf16 | i32, 1, 1, 1, false, false),
+      build_variant<VECOPS_B200_KERNEL_GENERIC>(f32 | bf16 | f16 | i8 | u8, f32 | bf16 | f16 | i8 | u8, f32 | bf16 | f16 | i32, 1, 1, 1, false,
+                                                false),
       build_variant<VECOPS_B200_KERNEL_F32_SIMT>(f32, f32, f32, 1, 1, 1, false, true),
-      // TMA wants 16-byte row pitches: 8 bf16 elements, 16 int8 elements
-      build_variant<VECOPS_B200_KERNEL_BF16_TCGEN05>(bf16, bf16, bf16 | f32, 8, 8, 1, true, true),
+      // TMA wants 16-byte row pitches: 8 bf16 elements, 16 int8 elements.  The 16-bit kernel serves bf16 and fp16 pairs
+      // (never mixed: the problem record's own check refuses those).
+      build_variant<VECOPS_B200_KERNEL_BF16_TCGEN05>(bf16 | f16, bf16 | f16, bf16 | f16 | f32, 8, 8, 1, true, true),
       build_variant<VECOPS_B200_KERNEL_I8_TCGEN05>(i8 | u8, i8 | u8, i32 | f32 | bf16, 16, 16, 1, true, true),
       build_variant<VECOPS_B200_KERNEL_W8_SMALL_M>(bf16, i8, bf16 | f32, 8, 16, 32, true, true),
       build_variant<VECOPS_B200_KERNEL_W8_TCGEN05>(bf16, i8, bf16 | f32, 8, 16, 32, true, true),
