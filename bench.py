@@ -279,6 +279,59 @@ def measure_f16(steps: int, warmup: int, dev, port, peaks) -> dict:
             "device_status": take_status()}
 
 
+def measure_pack(dev, peaks) -> dict:
+    """Operand preparation at C4's weight shape: a [K, N]-stored matrix (N = 14336, K = 4096) transposed into the packed
+    [N, K] form, and the row copy of an already K-contiguous one.  HBM-bound: every element read once, written once."""
+    import torch
+    from vecops_b200 import capi, harness
+    n, k = 14336, 4096
+    hbm = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+    side = torch.cuda.Stream(dev)
+    out = {}
+    for name, dtype, narrow in [("bf16", torch.bfloat16, None), ("i8", torch.int8, None), ("f32_to_bf16", torch.float32, torch.bfloat16)]:
+        sources = []
+        for i in range(3):  # three sources and destinations in rotation: more than L2 between reuses
+            if dtype == torch.int8:
+                sources.append(torch.randint(-128, 128, (k, n), dtype=torch.int8, device=dev))
+            else:
+                sources.append(torch.randn((k, n), dtype=torch.float32, device=dev).to(dtype))
+        pitch, size = harness.packed_layout(narrow or dtype, n, k)
+        packed = [torch.empty((n, pitch), dtype=narrow or dtype, device=dev) for _ in sources]
+        for form in ("transpose", "row_copy"):
+            views = [x.t() if form == "transpose" else x.t().contiguous() for x in sources]
+            records = [capi.VecopsB200Pack(ctypes.sizeof(capi.VecopsB200Pack), 1, n, k, v.data_ptr(), v.stride(0), v.stride(1),
+                                           harness.torch_dtype_code(v.dtype), harness.torch_dtype_code(d.dtype), d.data_ptr(), size, dev.index or 0, 0,
+                                           side.cuda_stream) for v, d in zip(views, packed)]
+            error = capi.ErrorBuffer()
+            count = 12
+            torch.cuda.synchronize()
+            with torch.cuda.stream(side):
+                error.raise_for(capi.library().vecops_b200_matmul_pack(byref(records[0]), byref(error.record)))  # warm-up, outside the graph
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(count):
+                        error.raise_for(capi.library().vecops_b200_matmul_pack(byref(records[i % 3]), byref(error.record)))
+                graph.replay()
+                side.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(side)
+                graph.replay()
+                e1.record(side)
+                side.synchronize()
+            ms = e0.elapsed_time(e1) / count
+            moved = n * k * (views[0].element_size() + packed[0].element_size())
+            got = packed[2][:64, :64].float().cpu()
+            want = views[2][:64, :64].to(narrow or dtype).float().cpu()
+            out[f"{name}_{form}"] = {"ms": ms, "algorithmic_gb_per_s": moved / (ms * 1e-3) / 1e9, "frac_of_measured_hbm_peak": moved / (ms * 1e-3) / 1e9 / hbm,
+                                     "equal_sample": bool(torch.equal(got, want))}
+            del views, graph
+        del sources, packed
+        torch.cuda.empty_cache()
+    return {"workload": "pack of a [14336, 4096] operand from a [K, N]-stored (transpose) or [N, K]-stored (row copy) source", "bound": "hbm",
+            "timing": "12 launches in one CUDA graph, three source/destination sets in rotation", "cases": out}
+
+
 def measure_quantized(steps: int, warmup: int, dev, port, peaks) -> dict:
     """The quantised form at C3's size: fp32 activations quantised to u8 (pre-pass), s8 weights, int32 correction row, dequantising
     transform with a per-column scale, bf16 out.  The timed launches are the product kernel alone; the pre-passes are timed beside it."""
@@ -730,6 +783,10 @@ def run_ours(args) -> None:
                 extras["c3_quantized_u8s8"] = measure_quantized(50, 5, dev, port, peaks)
             except Exception as error:
                 extras["c3_quantized_u8s8"] = {"error": repr(error)}
+            try:
+                extras["pack_14336x4096"] = measure_pack(dev, peaks)
+            except Exception as error:  # noqa: BLE001
+                extras["pack_14336x4096"] = {"error": repr(error)}
             try:
                 extras["c2_shape_f16"] = measure_f16(50, 5, dev, port, peaks)
             except Exception as error:  # noqa: BLE001

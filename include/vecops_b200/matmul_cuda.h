@@ -256,6 +256,52 @@ VECOPS_B200_EXPORT int32_t vecops_b200_quantize_rows(const void* src, uint32_t s
 VECOPS_B200_EXPORT int32_t vecops_b200_column_correction(const void* b, uint32_t b_dtype, int64_t b_stride_n, int64_t n, int64_t k,
                                                          int32_t zero_point, int32_t* out, void* stream, VecopsError* error);
 
+/* ---------------------------------------------------------------------------------------------------------------
+ * Operand preparation: the device counterpart of ops::matmul_pack (include/vecops/ops/MatmulPack.h:93-131) and of
+ * matmul::packed_layout<Atom, Side> (include/vecops/matmul/Packing.h:72-136).
+ *
+ * vecops packs an operand once into the blocked layout its tile instructions read, and a matmul handed such a tensor
+ * skips its own packing stage.  The layout the tensor-core kernels of this library read through TMA is simpler: rows
+ * that are K-contiguous, start on 16-byte boundaries and sit on a pitch that is a multiple of 16 bytes.  The packed
+ * form is therefore [rows, pitch] with pitch = K rounded up to 128 bytes, elements past K zero - and preparing an
+ * operand means bringing any strided view into it: a weight matrix stored [K, N] (C1's layout) is transposed once, an
+ * odd K (rows TMA cannot address) gets an aligned pitch, fp32 storage is narrowed to the bf16 / fp16 compute type
+ * (the reference's packing converts memory type to compute type too, tests/ops/MatmulPackTest.cpp:339-352).  A matmul
+ * "recognises" the packed operand by its strides alone: pass dst as a / b with stride pitch and k-stride 1 and the
+ * dispatch picks the tcgen05 kernels where the raw view would have gone to the strided kernel.
+ *
+ * The same form serves either side (A is [M,K], B is [N,K]); `operand` is recorded for the caller's bookkeeping only.
+ */
+typedef struct VecopsB200Pack {
+  uint32_t struct_size;
+  uint32_t operand;          /* 0: A, 1: B */
+  int64_t rows, k;           /* logical [rows, K] */
+  const void* src;           /* device pointer */
+  int64_t src_stride_row, src_stride_k; /* in elements, >= 0 */
+  uint32_t src_dtype;        /* VecopsDType */
+  uint32_t dst_dtype;        /* same as src_dtype, or bf16 / f16 from an f32 source (round to nearest even) */
+  void* dst;                 /* device pointer, 16-byte aligned, not overlapping the source view */
+  uint64_t dst_size;         /* bytes available at dst; at least what vecops_b200_matmul_packed_layout reports */
+  int32_t device_index;      /* -1: current device */
+  uint32_t flags;            /* 0 */
+  void* stream;              /* cudaStream_t; the call returns once the kernel is queued */
+} VecopsB200Pack;
+
+/* pitch (in elements) and size (bytes) of the packed form of a [rows, K] operand of `dtype`; either output may be NULL. */
+VECOPS_B200_EXPORT int32_t vecops_b200_matmul_packed_layout(uint32_t dtype, int64_t rows, int64_t k, int64_t* pitch_elements,
+                                                            uint64_t* bytes, VecopsError* error);
+
+/* Fill dst with the packed form of the source view.  rows == 0 or K == 0 touches no memory
+ * (tests/ops/MatmulPackTest.cpp:436-459).  INVALID_ARGUMENT for an undersized or unaligned destination, overlap, a
+ * dtype pair that is not served. */
+VECOPS_B200_EXPORT int32_t vecops_b200_matmul_pack(const VecopsB200Pack* pack, VecopsError* error);
+
+/* ops::matmul_pack_b_compensated (ops/MatmulPack.h:28-35, :104-118): pack a signed 8-bit B and also emit the int32[N]
+ * row compensation[n] = -a_zero_point * sum_k B[n,k] - the accumulator input (row stride 0) that removes the zero point
+ * of an asymmetrically quantised u8 A from the product.  K == 0 yields an all-zero row. */
+VECOPS_B200_EXPORT int32_t vecops_b200_matmul_pack_b_compensated(const VecopsB200Pack* pack, int32_t a_zero_point,
+                                                                 int32_t* compensation, VecopsError* error);
+
 /* Strided gather of column slabs: dst[M, ldd] columns [col0, col0+cols) <-
  * src[M, cols] (row pitch lds), `elem_size` bytes per element.  Used after the
  * all-gather of a column-sharded GEMM to place peers' slabs into the row-major

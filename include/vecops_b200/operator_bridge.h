@@ -37,6 +37,11 @@ typedef struct VecopsSpecializationArgument {
 /* Handle of the process-wide CUDA matmul operator (created on first use). */
 VECOPS_B200_EXPORT uint64_t vecops_b200_matmul_operator(void);
 
+/* Handle of a process-wide operand-preparation operator: vecops::matmul_pack, values = {src, dst} (compensated == 0),
+ * or vecops::matmul_pack_b_compensated, values = {src, dst, compensation, a_zero_point}; dst a tensor over
+ * vecops_b200_matmul_packed_layout's layout (ops/MatmulPack.h:93-131, :28-35). */
+VECOPS_B200_EXPORT uint64_t vecops_b200_matmul_pack_operator(int32_t compensated);
+
 /* Validate, resolve and run one call: values = {a, b, c[, column_scale]}.
  * Replaces vecops_operator_bridge_invoke_v1 (OperatorBridgeAbi.h:156-158). */
 VECOPS_B200_EXPORT int32_t vecops_operator_bridge_invoke_v1(uint64_t handle, const VecopsCall* call,

@@ -76,6 +76,13 @@ private:
 // The assembled operator: every variant's recipe, MatmulRuntimeDispatch, one provider.
 [[nodiscard]] std::shared_ptr<Operator> make_matmul_operator();
 
+// ops::matmul_pack, values = {src[R,K], dst[R,P]}, and ops::matmul_pack_b_compensated, values = {src, dst,
+// compensation[R], a_zero_point}, as operators; dst a tensor over the packed layout of src
+// (include/vecops/ops/MatmulPack.h:93-131, :28-35).
+[[nodiscard]] KernelDef matmul_pack_kernel_def();
+[[nodiscard]] KernelDef matmul_pack_b_compensated_kernel_def();
+[[nodiscard]] std::shared_ptr<Operator> make_matmul_pack_operator(bool compensated = false);
+
 // Static descriptor template of one variant (specialization_key left empty).
 [[nodiscard]] const VecopsKernelDescriptorV1* matmul_descriptor_template(std::uint32_t kernel);
 

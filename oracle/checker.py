@@ -73,6 +73,34 @@ def f16_conversion_inputs() -> tuple[np.ndarray, np.ndarray]:
     return patterns, bits.view(np.float32)
 
 
+def packed_pitch(itemsize: int, k: int) -> int:
+    """Elements per row of the packed form: K rounded up to whole 128-byte lines."""
+    per_line = 128 // itemsize
+    return (k + per_line - 1) // per_line * per_line
+
+
+def pack_rows(view: np.ndarray, narrow: str | None = None) -> np.ndarray:
+    """Restatement of operand packing as the reference's tests state it (tests/ops/MatmulPackTest.cpp:186-207): every
+    packed position holds the logical element (row, k) - converted to the compute type - or zero past the extents.
+    Here the packed form is [rows, pitch], K-contiguous.  `narrow`: None (same type), "bf16" or "f16" for a float32
+    view (returned as uint16 bit patterns)."""
+    rows, k = view.shape
+    if narrow == "bf16":
+        values = f32_to_bf16_bits(np.ascontiguousarray(view, dtype=np.float32))
+    elif narrow == "f16":
+        values = np.ascontiguousarray(view, dtype=np.float32).astype(np.float16).view(np.uint16)
+    else:
+        values = np.ascontiguousarray(view)
+    out = np.zeros((rows, packed_pitch(values.itemsize, k)), dtype=values.dtype)
+    out[:, :k] = values
+    return out
+
+
+def pack_compensation(b_nk: np.ndarray, a_zero_point: int) -> np.ndarray:
+    """-a_zero_point * sum_k B[n,k] as int32 (tests/ops/MatmulPackTest.cpp:209-216)."""
+    return (-int(a_zero_point) * b_nk.astype(np.int64).sum(axis=1)).astype(np.int32)
+
+
 def _cin_view(cin, m: int, n: int):
     """(array viewed as [m, n] with possibly zero strides, kind) - kind 1 for bf16 bits, else 0."""
     if cin is None:

@@ -343,6 +343,40 @@ void test_invoke_without_gpu_reports_execution_error() {
 
 }  // namespace
 
+// ------------------------------------------------------------------ the operand-preparation operator (resolution only)
+
+void test_matmul_pack_operator() {
+  auto op = make_matmul_pack_operator();
+  require(op->schema().name() == "vecops::matmul_pack" && op->schema().parameters().size() == 2, "matmul_pack schema has src and dst");
+  auto compensated_op = make_matmul_pack_operator(true);
+  require(compensated_op->schema().name() == "vecops::matmul_pack_b_compensated" && compensated_op->schema().parameters().size() == 4,
+          "matmul_pack_b_compensated is its own operator: src, dst, compensation, a_zero_point");
+  void* src = reinterpret_cast<void*>(0x10000);
+  void* dst = reinterpret_cast<void*>(0x900000);
+  auto resolve_key = [&](std::vector<Value> values) {
+    auto executable = op->resolve(KernelCall(ArgumentMetadata(std::move(values))));
+    return executable.ok() ? std::string(executable.value()->specialization_key()) : "ERROR: " + executable.status().message();
+  };
+  // a [K, N]-stored int8 weight (row stride 1, k stride N) into its packed form: K = 129 -> pitch 256
+  std::vector<Value> plain{device_tensor(src, DType::Int8, {33, 129}, {1, 33}, 0, false), device_tensor(dst, DType::Int8, {33, 256}, {256, 1}, 0, true)};
+  require(resolve_key(plain) == "vecops::matmul_pack;TD=i8;TS=i8;kernel=pack", "a pack call resolves to the one pack recipe");
+  std::vector<Value> compensated = plain;
+  compensated.emplace_back(device_tensor(reinterpret_cast<void*>(0xa00000), DType::Int32, {33}, {1}, 0, true));
+  compensated.emplace_back(Scalar::signed_integer(3, DType::Int32));
+  {
+    auto executable = compensated_op->resolve(KernelCall(ArgumentMetadata(compensated)));
+    require(executable.ok() && executable.value()->specialization_key() == "vecops::matmul_pack_b_compensated;kernel=pack",
+            "the compensated call resolves on its own operator");
+    require(!op->resolve(KernelCall(ArgumentMetadata(compensated))).ok(), "the plain operator takes src and dst only");
+  }
+  std::vector<Value> narrowing{device_tensor(src, DType::Float32, {5, 9}, {21, 2}, 0, false), device_tensor(dst, DType::BFloat16, {5, 64}, {64, 1}, 0, true)};
+  require(resolve_key(narrowing) == "vecops::matmul_pack;TD=bf16;TS=f32;kernel=pack", "fp32 storage narrows to the bf16 compute type");
+  std::vector<Value> wrong_layout{device_tensor(src, DType::Int8, {33, 129}, {129, 1}, 0, false), device_tensor(dst, DType::Int8, {33, 129}, {129, 1}, 0, true)};
+  require(!op->resolve(KernelCall(ArgumentMetadata(wrong_layout))).ok(), "a destination that is not over the packed layout does not resolve");
+  std::vector<Value> wrong_types{device_tensor(src, DType::Int8, {33, 129}, {129, 1}, 0, false), device_tensor(dst, DType::BFloat16, {33, 192}, {192, 1}, 0, true)};
+  require(!op->resolve(KernelCall(ArgumentMetadata(wrong_types))).ok(), "int8 -> bf16 is not a packing conversion");
+}
+
 int main(int argc, char** argv) {
   if (argc < 2) {
     std::fprintf(stderr, "usage: runtime_test <fixture_artifact.so>\n");
@@ -352,6 +386,7 @@ int main(int argc, char** argv) {
   test_schema();
   test_fixture_artifact(argv[1]);
   test_matmul_operator();
+  test_matmul_pack_operator();
   test_invoke_without_gpu_reports_execution_error();
   std::printf("runtime_test PASS (%d checks)\n", g_checks);
   return 0;

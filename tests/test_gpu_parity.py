@@ -778,3 +778,209 @@ def test_f16_mixed_with_bf16_is_refused():
         vecops_b200.matmul(a, b, c)
     with pytest.raises(capi.VecopsB200Error):  # fp16 operands narrow to fp16 or stay fp32, never bf16
         vecops_b200.matmul(a, a[:64].contiguous(), torch.zeros((128, 64), dtype=torch.bfloat16, device="cuda"))
+
+
+# ------------------------------------------------------------------ prepared operands (the reference's ops::matmul_pack)
+
+def _torch_of(array, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(array)).cuda()
+    return t.view(dtype) if dtype is not None else t
+
+
+def _strided_source(logical, layout, canary):
+    """A device tensor view equal to `logical` [rows, K] under one of the source layouts the pack must serve."""
+    rows, k = logical.shape
+    if layout == "k_contiguous":
+        return _torch_of(logical)
+    if layout == "k_contiguous_odd_pitch":        # row pitch K + 3, view starts one element in: nothing is 16-byte aligned
+        storage = np.full(rows * (k + 3) + 1, canary, dtype=logical.dtype)
+        host = np.lib.stride_tricks.as_strided(storage[1:], (rows, k), ((k + 3) * logical.itemsize, logical.itemsize))
+        host[...] = logical
+        return torch.as_strided(_torch_of(storage), (rows, k), (k + 3, 1), 1)
+    if layout == "row_contiguous":                # stored [K, rows] row-major, handed over as its transposed view
+        return _torch_of(np.ascontiguousarray(logical.T)).t()
+    if layout == "row_contiguous_odd_pitch":
+        storage = np.full(k * (rows + 5) + 3, canary, dtype=logical.dtype)
+        host = np.lib.stride_tricks.as_strided(storage[3:], (rows, k), (logical.itemsize, (rows + 5) * logical.itemsize))
+        host[...] = logical
+        return torch.as_strided(_torch_of(storage), (rows, k), (1, rows + 5), 3)
+    if layout == "both_strided":                  # StrideK = 2, row pitch 2K + 3 (tests/ops/MatmulPackTest.cpp:221-237)
+        storage = np.full(rows * (2 * k + 3), canary, dtype=logical.dtype)
+        host = np.lib.stride_tricks.as_strided(storage, (rows, k), ((2 * k + 3) * logical.itemsize, 2 * logical.itemsize))
+        host[...] = logical
+        return torch.as_strided(_torch_of(storage), (rows, k), (2 * k + 3, 2), 0)
+    raise ValueError(layout)
+
+
+PACK_LAYOUTS = ["k_contiguous", "k_contiguous_odd_pitch", "row_contiguous", "row_contiguous_odd_pitch", "both_strided"]
+PACK_SHAPES = [(16, 32), (17, 33), (19, 35), (1, 1), (16, 64), (31, 79), (129, 65), (300, 1000), (1024, 512), (5, 9)]
+
+
+@pytest.mark.parametrize("layout", PACK_LAYOUTS)
+@pytest.mark.parametrize("dtype,narrow", [(np.int8, None), (np.uint8, None), (np.uint16, None), (np.float32, None), (np.float32, "bf16"),
+                                          (np.float32, "f16")])
+def test_pack_brings_every_layout_into_the_packed_form(layout, dtype, narrow):
+    from oracle.checker import pack_rows
+    rng = np.random.default_rng(17)
+    torch_out = {None: None, "bf16": torch.bfloat16, "f16": torch.float16}[narrow]
+    for rows, k in PACK_SHAPES:
+        if dtype == np.float32:
+            logical = (rng.standard_normal((rows, k)) * 3).astype(np.float32)
+        else:
+            info = np.iinfo(dtype)
+            logical = rng.integers(info.min, int(info.max) + 1, (rows, k)).astype(dtype)
+        source = _strided_source(logical, layout, canary=dtype(77))
+        if dtype == np.uint16:
+            source = source.view(torch.bfloat16)  # any 2-byte type: a bit copy
+        packed = harness.pack_operand(source, torch_out)
+        torch.cuda.synchronize()
+        want = pack_rows(logical, narrow)
+        assert packed.stride(0) == want.shape[1] and packed.stride(1) == 1, (rows, k)
+        whole = torch.as_strided(packed, (rows, want.shape[1]), (want.shape[1], 1))
+        got = whole.contiguous().view(torch.int16 if want.itemsize == 2 else whole.dtype).cpu().numpy().view(want.dtype)
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), f"{layout} {dtype} {narrow} rows={rows} k={k}"
+
+
+def test_packed_layout_sizes_and_refusals():
+    assert harness.packed_layout(torch.int8, 33, 129) == (256, 33 * 256)
+    assert harness.packed_layout(torch.bfloat16, 19, 35) == (64, 19 * 128)
+    assert harness.packed_layout(torch.float32, 5, 32) == (32, 5 * 128)
+    assert harness.packed_layout(torch.bfloat16, 7, 0) == (0, 0)          # a zero-K packed layout is empty
+    assert harness.packed_layout(torch.int8, 0, 64) == (128, 0)
+    harness.pack_operand(torch.empty((0, 64), dtype=torch.int8, device="cuda"))  # zero extents touch no memory
+    harness.pack_operand(torch.empty((9, 0), dtype=torch.bfloat16, device="cuda"))
+    lib = capi.library()
+    src = torch.zeros((64, 64), dtype=torch.int8, device="cuda")
+    dst = torch.zeros((64, 128), dtype=torch.int8, device="cuda")
+
+    def record(source, destination, size, dst_dtype=capi.DTYPE_I8):
+        return capi.VecopsB200Pack(ctypes.sizeof(capi.VecopsB200Pack), 1, 64, 64, source.data_ptr(), 64, 1, capi.DTYPE_I8, dst_dtype,
+                                   destination.data_ptr(), size, -1, 0, None)
+
+    for bad in (record(src, dst, 64 * 128 - 1),                      # undersized destination
+                record(src, src, 64 * 128),                          # aliasing
+                record(src, dst, 64 * 128, capi.DTYPE_BF16)):        # int8 -> bf16 is not a packing conversion
+        error = capi.ErrorBuffer()
+        assert lib.vecops_b200_matmul_pack(byref(bad), byref(error.record)) == capi.INVALID_ARGUMENT
+    error = capi.ErrorBuffer()
+    misaligned = capi.VecopsB200Pack(ctypes.sizeof(capi.VecopsB200Pack), 1, 32, 64, src.data_ptr(), 64, 1, capi.DTYPE_I8, capi.DTYPE_I8,
+                                     dst.data_ptr() + 4, 32 * 128, -1, 0, None)
+    assert lib.vecops_b200_matmul_pack(byref(misaligned), byref(error.record)) == capi.INVALID_ARGUMENT
+
+
+def test_packed_operands_reach_the_tensor_core_kernels(port):
+    # a [K, N]-stored weight and an odd K both send the raw views to the strided kernel; their packed forms run on tcgen05
+    rng = np.random.default_rng(23)
+    m, n, k = 256, 512, 325
+    a, b, _ = inputs("bf16", m, n, k, rng)
+    da = to_device(a, bf16=True)
+    db_kn = to_device(np.ascontiguousarray(b.T), bf16=True).t()           # [N, K] view of a [K, N] matrix
+    c = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    assert vecops_b200.select_kernel(vecops_b200.matmul_problem(da, db_kn, c)) == K.KERNEL_GENERIC
+    pa, pb = harness.pack_operand(da, operand=0), harness.pack_operand(db_kn)
+    assert vecops_b200.select_kernel(vecops_b200.matmul_problem(pa, pb, c)) == K.KERNEL_BF16_TCGEN05
+    vecops_b200.matmul(pa, pb, c)
+    torch.cuda.synchronize()
+    check("bf16", c.cpu().numpy(), port.matmul_bf16(a, b, None, False))
+    # fp32 storage narrowed to the bf16 compute type while packing (memory type != compute type)
+    a32, b32 = bf16_bits_to_f32(a) * 1.001, bf16_bits_to_f32(b) * 0.999
+    pa = harness.pack_operand(torch.from_numpy(a32).cuda(), torch.bfloat16, operand=0)
+    pb = harness.pack_operand(torch.from_numpy(np.ascontiguousarray(b32.T)).cuda().t(), torch.bfloat16)
+    vecops_b200.matmul(pa, pb, c)
+    torch.cuda.synchronize()
+    check("bf16", c.cpu().numpy(), port.matmul_bf16(f32_to_bf16_bits(a32), f32_to_bf16_bits(b32), None, False))
+    # int8: bit-exact, and equal to what the raw strided views give
+    ai = rng.integers(-128, 128, (m, k)).astype(np.int8)
+    bi = rng.integers(-128, 128, (n, k)).astype(np.int8)
+    dai, dbi = to_device(ai), to_device(np.ascontiguousarray(bi.T)).t()
+    ci_raw = torch.empty((m, n), dtype=torch.int32, device="cuda")
+    ci_packed = torch.empty((m, n), dtype=torch.int32, device="cuda")
+    vecops_b200.matmul(dai, dbi, ci_raw)
+    pai, pbi = harness.pack_operand(dai, operand=0), harness.pack_operand(dbi)
+    assert vecops_b200.select_kernel(vecops_b200.matmul_problem(pai, pbi, ci_packed)) == K.KERNEL_I8_TCGEN05
+    vecops_b200.matmul(pai, pbi, ci_packed)
+    torch.cuda.synchronize()
+    want = port.matmul_i8(ai, bi)
+    assert np.array_equal(ci_packed.cpu().numpy(), want) and np.array_equal(ci_raw.cpu().numpy(), want)
+
+
+def test_pack_b_compensated_emits_the_zero_point_row(port):
+    from oracle.checker import pack_compensation, pack_rows
+    # the reference test's own case: N=33, K=129, row pitch K+3, a_zero_point 3, values (n*17 + k*3) % 61 - 30
+    # (tests/ops/MatmulPackTest.cpp:354-376); the row after the compensation keeps its canary (:217)
+    n, k, zp = 33, 129, 3
+    logical = ((np.arange(n)[:, None] * 17 + np.arange(k)[None, :] * 3) % 61 - 30).astype(np.int8)
+    source = _strided_source(logical, "k_contiguous_odd_pitch", np.int8(-99))
+    pitch, size = harness.packed_layout(torch.int8, n, k)
+    storage = torch.zeros(n * pitch, dtype=torch.int8, device="cuda")
+    compensation = torch.full((n + 1,), 0x13579bdf, dtype=torch.int32, device="cuda")
+    record = capi.VecopsB200Pack(ctypes.sizeof(capi.VecopsB200Pack), 1, n, k, source.data_ptr(), source.stride(0), source.stride(1), capi.DTYPE_I8,
+                                 capi.DTYPE_I8, storage.data_ptr(), size, -1, 0, None)
+    error = capi.ErrorBuffer()
+    error.raise_for(capi.library().vecops_b200_matmul_pack_b_compensated(byref(record), zp, compensation.data_ptr(), byref(error.record)))
+    torch.cuda.synchronize()
+    assert np.array_equal(storage.view(n, pitch).cpu().numpy(), pack_rows(logical))
+    assert np.array_equal(compensation[:n].cpu().numpy(), pack_compensation(logical, zp))
+    assert int(compensation[n]) == 0x13579bdf
+    # and used: u8 A (zero point 3) x packed s8 B with the row as the accumulator input equals the product of the centred values
+    rng = np.random.default_rng(4)
+    a_u8 = rng.integers(0, 256, (21, k)).astype(np.uint8)
+    packed, row = harness.pack_operand(source, zero_point=zp)
+    c = torch.empty((21, n), dtype=torch.int32, device="cuda")
+    vecops_b200.matmul(harness.pack_operand(to_device(a_u8), operand=0), packed, c, cin=row)
+    torch.cuda.synchronize()
+    centred = (a_u8.astype(np.int64) - zp) @ logical.astype(np.int64).T
+    assert np.array_equal(c.cpu().numpy(), centred.astype(np.int32))
+    # zero extents (tests/ops/MatmulPackTest.cpp:401-434): K == 0 gives an all-zero row
+    empty = torch.empty((7, 0), dtype=torch.int8, device="cuda")
+    _, row0 = harness.pack_operand(empty, zero_point=5)
+    torch.cuda.synchronize()
+    assert bool((row0 == 0).all()) and row0.numel() == 7
+
+
+def test_pack_operator_through_the_bridge():
+    # vecops::matmul_pack behind the same Operator machinery: {src, dst} and {src, dst, compensation, a_zero_point}
+    from oracle.checker import pack_compensation, pack_rows
+    lib, _ = bridge_lib()
+    lib.vecops_b200_matmul_pack_operator.restype = ctypes.c_uint64
+    lib.vecops_b200_matmul_pack_operator.argtypes = [ctypes.c_int32]
+    handle = lib.vecops_b200_matmul_pack_operator(0)
+    compensated_handle = lib.vecops_b200_matmul_pack_operator(1)
+    rng = np.random.default_rng(31)
+    n, k = 200, 333
+    logical = rng.integers(-128, 128, (n, k)).astype(np.int8)
+    source = to_device(np.ascontiguousarray(logical.T)).t()            # a [K, N]-stored weight
+    pitch, _ = harness.packed_layout(torch.int8, n, k)
+    dst = torch.full((n, pitch), 55, dtype=torch.int8, device="cuda")
+    row = torch.zeros(n, dtype=torch.int32, device="cuda")
+
+    def frame(values, keep):
+        array = (capi.VecopsValue * len(values))(*values)
+        context = capi.VecopsExecutionContext()
+        context.struct_size = ctypes.sizeof(context)
+        context.stream = None
+        keep.extend([array, context])
+        return capi.VecopsCall(ctypes.sizeof(capi.VecopsCall), len(values), array, None, 0, ctypes.pointer(context))
+
+    keep = []
+    call = frame([_tensor_value(source, keep=keep), _tensor_value(dst, True, keep=keep)], keep)
+    error = capi.ErrorBuffer()
+    key = ctypes.create_string_buffer(256)
+    error.raise_for(lib.vecops_b200_operator_resolve(handle, byref(call), key, 256, byref(error.record)))
+    assert key.value.decode() == "vecops::matmul_pack;TD=i8;TS=i8;kernel=pack", key.value
+    error.raise_for(lib.vecops_operator_bridge_invoke_v1(handle, byref(call), 0, None, byref(error.record)))
+    torch.cuda.synchronize()
+    assert np.array_equal(dst.cpu().numpy(), pack_rows(logical))
+    dst.fill_(55)
+    call = frame([_tensor_value(source, keep=keep), _tensor_value(dst, True, keep=keep), _tensor_value(row, True, keep=keep),
+                  _scalar_value(capi.DTYPE_I32, 7)], keep)
+    assert lib.vecops_operator_bridge_invoke_v1(handle, byref(call), 0, None, byref(capi.ErrorBuffer().record)) != capi.OK  # its own operator
+    error.raise_for(lib.vecops_operator_bridge_invoke_v1(compensated_handle, byref(call), 0, None, byref(error.record)))
+    torch.cuda.synchronize()
+    assert np.array_equal(dst.cpu().numpy(), pack_rows(logical))
+    assert np.array_equal(row.cpu().numpy(), pack_compensation(logical, 7))
+    # a destination that is not a tensor over the packed layout is refused
+    wrong = torch.zeros((n, k), dtype=torch.int8, device="cuda")
+    call = frame([_tensor_value(source, keep=keep), _tensor_value(wrong, True, keep=keep)], keep)
+    error = capi.ErrorBuffer()
+    assert lib.vecops_operator_bridge_invoke_v1(handle, byref(call), 0, None, byref(error.record)) != capi.OK

@@ -124,3 +124,19 @@ def test_fp16_product_against_numpy(port):
     assert np.array_equal(got, want.astype(np.float32))
     got16 = port.matmul_f16(a.view(np.uint16), b.view(np.uint16), out_f16=True)
     assert np.array_equal(got16, want.astype(np.float32).astype(np.float16).view(np.uint16))
+
+
+def test_pack_restatement_follows_the_reference_tests_expectations():
+    # the strided conversion case of tests/ops/MatmulPackTest.cpp:221-262: 5 x 9 fp32 values s*17 + k + 0.25 with StrideK 2,
+    # packed as bf16: every position holds the converted logical element, zero past the extents
+    from oracle.checker import pack_compensation, pack_rows, packed_pitch
+    spatial, k = 5, 9
+    storage = np.full(spatial * (2 * k + 3), -999.0, dtype=np.float32)
+    view = np.lib.stride_tricks.as_strided(storage, (spatial, k), ((2 * k + 3) * 4, 8))
+    view[...] = np.arange(spatial)[:, None] * 17 + np.arange(k)[None, :] + 0.25
+    packed = pack_rows(view, "bf16")
+    assert packed.shape == (spatial, 64) and packed_pitch(2, k) == 64
+    assert np.array_equal(packed[:, :k], f32_to_bf16_bits(np.ascontiguousarray(view)))
+    assert not packed[:, k:].any()
+    logical = ((np.arange(33)[:, None] * 17 + np.arange(129)[None, :] * 3) % 61 - 30).astype(np.int8)
+    assert np.array_equal(pack_compensation(logical, 3), -3 * logical.astype(np.int32).sum(axis=1))

@@ -91,6 +91,12 @@ class VecopsB200Batch(Structure):
                 ("c_stride_b", c_int64), ("cin_stride_b", c_int64)]
 
 
+class VecopsB200Pack(Structure):
+    _fields_ = [("struct_size", c_uint32), ("operand", c_uint32), ("rows", c_int64), ("k", c_int64), ("src", c_void_p),
+                ("src_stride_row", c_int64), ("src_stride_k", c_int64), ("src_dtype", c_uint32), ("dst_dtype", c_uint32), ("dst", c_void_p),
+                ("dst_size", c_uint64), ("device_index", c_int32), ("flags", c_uint32), ("stream", c_void_p)]
+
+
 class VecopsB200Gather(Structure):
     _fields_ = [("struct_size", c_uint32), ("world", c_int32), ("c", POINTER(c_void_p)), ("n_total", c_int64), ("ldc", c_int64),
                 ("col0", c_int64), ("flags", c_uint32), ("reserved", c_uint32)]
@@ -143,6 +149,9 @@ def library() -> ctypes.CDLL:
         lib.vecops_b200_quantize_rows.argtypes = [c_void_p, c_uint32, c_int64, c_int64, c_void_p, c_uint32, c_int64, c_int64, c_int64, c_float,
                                                   c_float, c_void_p, e]
         lib.vecops_b200_column_correction.argtypes = [c_void_p, c_uint32, c_int64, c_int64, c_int64, c_int32, c_void_p, c_void_p, e]
+        lib.vecops_b200_matmul_packed_layout.argtypes = [c_uint32, c_int64, c_int64, POINTER(c_int64), POINTER(c_uint64), e]
+        lib.vecops_b200_matmul_pack.argtypes = [POINTER(VecopsB200Pack), e]
+        lib.vecops_b200_matmul_pack_b_compensated.argtypes = [POINTER(VecopsB200Pack), c_int32, c_void_p, e]
         lib.vecops_b200_matmul_allgather_run.argtypes = [POINTER(VecopsB200Matmul), POINTER(VecopsB200Gather), e]
         lib.vecops_b200_kernel_name.argtypes = [c_uint32]
         lib.vecops_b200_kernel_name.restype = c_char_p

@@ -411,6 +411,226 @@ const VecopsKernelDescriptorV1* matmul_descriptor_template(std::uint32_t kernel)
   return variant != nullptr ? &variant->descriptor : nullptr;
 }
 
+// ================================================================== vecops::matmul_pack
+//
+// Two more operators behind the same Operator machinery: ops::matmul_pack, values = {src[R,K], dst[R,P]}, and
+// ops::matmul_pack_b_compensated, values = {src, dst, compensation[R], a_zero_point} (include/vecops/ops/MatmulPack.h;
+// separate operators there too, :28-35 - and a writable tensor cannot be optional in a schema).  dst must be a tensor
+// over the packed layout of src - P = vecops_b200_matmul_packed_layout's pitch, strides (P, 1) - as the reference
+// demands of its output (tests/ops/MatmulPackTest.cpp:461-487).  One recipe each: the layout decides the kernel inside.
+
+namespace {
+
+constexpr const char* kPackOperatorName = "vecops::matmul_pack";
+constexpr const char* kPackCompensatedOperatorName = "vecops::matmul_pack_b_compensated";
+constexpr std::uint32_t kPackParameters = 4;  // of the compensated operator; the plain one has the first two
+
+std::int32_t pack_from_frame(const VecopsCall* call, VecopsB200Pack* out, std::int32_t* zero_point, std::int32_t** compensation,
+                             VecopsError* error) {
+  if (call == nullptr || call->struct_size < sizeof(VecopsCall)) return fail(error, VECOPS_STATUS_ABI_MISMATCH, "call frame is null or too small");
+  if (call->num_values < 2 || call->num_values > kPackParameters || call->values == nullptr)
+    return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "matmul_pack expects src, dst and optionally compensation, a_zero_point");
+  if (call->values[0].kind != VECOPS_VALUE_TENSOR || call->values[1].kind != VECOPS_VALUE_TENSOR)
+    return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "matmul_pack operands must be tensors");
+  const VecopsTensorView& src = call->values[0].value.tensor;
+  const VecopsTensorView& dst = call->values[1].value.tensor;
+  if (src.rank != 2 || dst.rank != 2) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "matmul_pack wants rank-2 src and dst");
+  *compensation = nullptr;
+  *zero_point = 0;
+  if (call->num_values > 2 && call->values[2].kind == VECOPS_VALUE_TENSOR) {
+    const VecopsTensorView& row = call->values[2].value.tensor;
+    if (row.rank != 1 || row.sizes[0] != src.sizes[0] || row.dtype != VECOPS_DTYPE_I32 || (row.strides[0] != 1 && row.sizes[0] > 1))
+      return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "compensation must be a contiguous int32 tensor of one element per packed row");
+    *compensation = reinterpret_cast<std::int32_t*>(static_cast<char*>(row.data) + row.byte_offset);
+  } else if (call->num_values > 2 && call->values[2].kind != VECOPS_VALUE_NONE) {
+    return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "compensation is a tensor or absent");
+  }
+  if (call->num_values > 3) {
+    const VecopsValue& value = call->values[3];
+    if (value.kind != VECOPS_VALUE_SCALAR || value.value.scalar.dtype != VECOPS_DTYPE_I32)
+      return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "a_zero_point is an i32 scalar");
+    *zero_point = static_cast<std::int32_t>(value.value.scalar.value.i64);
+  }
+  std::int64_t pitch = 0;
+  std::uint64_t bytes = 0;
+  if (const auto rc = vecops_b200_matmul_packed_layout(dst.dtype, src.sizes[0], src.sizes[1], &pitch, &bytes, error); rc != VECOPS_STATUS_OK) return rc;
+  if (dst.sizes[0] != src.sizes[0] || dst.sizes[1] != pitch || (dst.strides[0] != pitch && dst.sizes[0] > 1) || (dst.strides[1] != 1 && pitch > 1))
+    return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "dst is not a tensor over the packed layout of src ([rows, pitch], strides (pitch, 1))");
+  VecopsB200Pack p{};
+  p.struct_size = sizeof(VecopsB200Pack);
+  p.operand = 1;
+  p.rows = src.sizes[0];
+  p.k = src.sizes[1];
+  p.src = static_cast<const char*>(src.data) + src.byte_offset;
+  p.src_stride_row = src.strides[0];
+  p.src_stride_k = src.strides[1];
+  p.src_dtype = src.dtype;
+  p.dst_dtype = dst.dtype;
+  p.dst = static_cast<char*>(dst.data) + dst.byte_offset;
+  p.dst_size = bytes;
+  p.device_index = dst.device_index;
+  if (const VecopsExecutionContext* context = call->context)
+    if (context->struct_size >= offsetof(VecopsExecutionContext, stream) + sizeof(context->stream)) p.stream = context->stream;
+  *out = p;
+  return VECOPS_STATUS_OK;
+}
+
+template <bool kCompensated>
+std::int32_t run_pack(const VecopsCall* call, VecopsError* error) {
+  VecopsB200Pack pack;
+  std::int32_t zero_point = 0;
+  std::int32_t* compensation = nullptr;
+  if (const auto rc = pack_from_frame(call, &pack, &zero_point, &compensation, error); rc != VECOPS_STATUS_OK) return rc;
+  if (kCompensated != (compensation != nullptr))
+    return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, kCompensated ? "matmul_pack_b_compensated needs its compensation row" : "matmul_pack takes src and dst only");
+  if (kCompensated) return vecops_b200_matmul_pack_b_compensated(&pack, zero_point, compensation, error);
+  return vecops_b200_matmul_pack(&pack, error);
+}
+
+std::int32_t pack_workspace(const VecopsCall*, std::uint64_t* bytes, VecopsError*) {
+  if (bytes != nullptr) *bytes = 0;  // as matmul_pack_workspace_bytes of the reference's direct plans (MatmulPackTest.cpp:178-182)
+  return VECOPS_STATUS_OK;
+}
+
+struct PackDescriptor {
+  VecopsDimensionConstraint sizes2[2], src_strides[2], dst_strides[2], sizes1[1], strides1[1];
+  VecopsParameterDescriptor parameters[kPackParameters];
+  VecopsKernelDescriptorV1 descriptor;
+};
+
+PackDescriptor* build_pack_descriptor(bool compensated) {
+  auto* v = new PackDescriptor{};
+  constexpr auto all = bit(VECOPS_DTYPE_F32) | bit(VECOPS_DTYPE_BF16) | bit(VECOPS_DTYPE_F16) | bit(VECOPS_DTYPE_I8) | bit(VECOPS_DTYPE_U8);
+  v->sizes2[0] = v->sizes2[1] = any_dim();
+  v->src_strides[0] = v->src_strides[1] = any_dim();
+  v->dst_strides[0] = any_dim();
+  v->dst_strides[1] = const_dim(1);
+  v->sizes1[0] = any_dim();
+  v->strides1[0] = const_dim(1);
+  v->parameters[0] = tensor_parameter("src", compensated ? bit(VECOPS_DTYPE_I8) : all, 2, v->sizes2, v->src_strides, false, false);
+  v->parameters[1] = tensor_parameter("dst", compensated ? bit(VECOPS_DTYPE_I8) : all, 2, v->sizes2, v->dst_strides, false, true);
+  v->parameters[2] = tensor_parameter("compensation", bit(VECOPS_DTYPE_I32), 1, v->sizes1, v->strides1, false, true);
+  v->parameters[3] = scalar_parameter("a_zero_point", bit(VECOPS_DTYPE_I32));
+  auto& d = v->descriptor;
+  d.struct_size = sizeof(VecopsKernelDescriptorV1);
+  d.abi_version_major = VECOPS_KERNEL_ABI_VERSION_MAJOR;
+  d.abi_version_minor = VECOPS_KERNEL_ABI_VERSION_MINOR;
+  d.operator_name = compensated ? kPackCompensatedOperatorName : kPackOperatorName;
+  d.specialization_key = "";
+  d.num_parameters = compensated ? kPackParameters : 2;
+  d.parameter_stride = sizeof(VecopsParameterDescriptor);
+  d.parameters = v->parameters;
+  d.workspace = &pack_workspace;
+  d.run = compensated ? &run_pack<true> : &run_pack<false>;
+  d.flags = 0;
+  return v;
+}
+
+const PackDescriptor* pack_descriptor(bool compensated) {
+  static const PackDescriptor* const built[2] = {build_pack_descriptor(false), build_pack_descriptor(true)};
+  return built[compensated ? 1 : 0];
+}
+
+class CudaPackRecipe final : public KernelRecipe {
+public:
+  explicit CudaPackRecipe(bool compensated)
+      : compensated_(compensated),
+        definition_(std::make_shared<const KernelDef>(compensated ? matmul_pack_b_compensated_kernel_def() : matmul_pack_kernel_def())) {}
+  [[nodiscard]] std::string_view id() const override { return compensated_ ? "cuda/sm_100a/matmul_pack_b_compensated" : "cuda/sm_100a/matmul_pack"; }
+  [[nodiscard]] Status match(const KernelCall& call) const override {
+    ArgumentMetadata arguments(std::vector<Value>(call.arguments().values().begin(), call.arguments().values().end()));
+    CallFrame frame(arguments);
+    VecopsB200Pack pack;
+    std::int32_t zero_point = 0;
+    std::int32_t* compensation = nullptr;
+    ErrorText error;
+    if (const auto rc = pack_from_frame(&frame.abi(), &pack, &zero_point, &compensation, &error.record); rc != VECOPS_STATUS_OK)
+      return Status(StatusCode::NotApplicable, error.text.data());
+    const bool same = pack.src_dtype == pack.dst_dtype;
+    const bool narrowing = pack.src_dtype == VECOPS_DTYPE_F32 && (pack.dst_dtype == VECOPS_DTYPE_BF16 || pack.dst_dtype == VECOPS_DTYPE_F16);
+    if (!same && !narrowing) return Status(StatusCode::NotApplicable, "matmul_pack keeps the element type or narrows f32 to bf16 / f16");
+    if (compensated_ != (compensation != nullptr)) return Status(StatusCode::NotApplicable, "compensation row missing or unexpected");
+    if (compensated_ && (pack.src_dtype != VECOPS_DTYPE_I8 || pack.dst_dtype != VECOPS_DTYPE_I8))
+      return Status(StatusCode::NotApplicable, "the compensated form packs a signed 8-bit B");
+    return Status::success();
+  }
+  [[nodiscard]] Result<BoundKernelRecipe> bind(const KernelCall& call) const override {
+    auto binding = bind_kernel_call(*definition_, call);
+    if (!binding) return binding.status();
+    BoundKernelRecipe bound;
+    bound.recipe_id = std::string(id());
+    bound.specialization_key = binding.value().specialization_key + ";kernel=pack";
+    bound.artifact_key = std::string(id());
+    return bound;
+  }
+
+private:
+  bool compensated_;
+  std::shared_ptr<const KernelDef> definition_;
+};
+
+class CudaPackProvider final : public ExecutableProvider {
+public:
+  [[nodiscard]] Result<std::shared_ptr<Executable>> resolve(const BoundKernelRecipe& recipe) override {
+    std::lock_guard<std::mutex> lock(mutex_);
+    if (auto found = cache_.find(recipe.specialization_key); found != cache_.end()) return found->second;
+    const bool compensated = recipe.artifact_key == "cuda/sm_100a/matmul_pack_b_compensated";
+    if (!compensated && recipe.artifact_key != "cuda/sm_100a/matmul_pack")
+      return Status(StatusCode::NotFound, "artifact '" + recipe.artifact_key + "' is not a prebuilt pack kernel");
+    auto owned = std::make_shared<OwnedDescriptor>();
+    owned->key = recipe.specialization_key;
+    owned->descriptor = pack_descriptor(compensated)->descriptor;
+    owned->descriptor.specialization_key = owned->key.c_str();
+    auto module = LoadedModule::adopt(&owned->descriptor, owned);
+    if (!module) return module.status();
+    return cache_.emplace(recipe.specialization_key, std::make_shared<Executable>(std::move(module).value())).first->second;
+  }
+
+private:
+  std::mutex mutex_;
+  std::map<std::string, std::shared_ptr<Executable>, std::less<>> cache_;
+};
+
+}  // namespace
+
+namespace {
+TensorDef pack_tensor(std::string name, std::vector<DimensionDef> shape, TensorDTypeDef dtype, TensorAccess access) {
+  TensorDef t;
+  t.name = std::move(name);
+  t.strides.assign(shape.size(), DimensionDef::any());
+  t.shape = std::move(shape);
+  t.dtype = std::move(dtype);
+  t.access = access;
+  t.optional = false;
+  t.device_type = VECOPS_DEVICE_CUDA;
+  t.device_index = -1;
+  return t;
+}
+DimensionDef pack_dim(const char* name) { return DimensionDef::named_dynamic(name, 1, 0); }
+}  // namespace
+
+KernelDef matmul_pack_kernel_def() {
+  return KernelDef(kPackOperatorName,
+                   {pack_tensor("src", {pack_dim("R"), pack_dim("K")}, "TS", TensorAccess::Input),
+                    pack_tensor("dst", {pack_dim("R"), pack_dim("P")}, "TD", TensorAccess::Output)},
+                   {{"TS", SpecializationType::DType}, {"TD", SpecializationType::DType}});
+}
+
+KernelDef matmul_pack_b_compensated_kernel_def() {
+  return KernelDef(kPackCompensatedOperatorName,
+                   {pack_tensor("src", {pack_dim("R"), pack_dim("K")}, DType::Int8, TensorAccess::Input),
+                    pack_tensor("dst", {pack_dim("R"), pack_dim("P")}, DType::Int8, TensorAccess::Output),
+                    pack_tensor("compensation", {pack_dim("R")}, DType::Int32, TensorAccess::Output),
+                    ValueDef{"a_zero_point", DType::Int32, Scalar::signed_integer(0, DType::Int32)}},
+                   {});
+}
+
+std::shared_ptr<Operator> make_matmul_pack_operator(bool compensated) {
+  std::vector<std::shared_ptr<const KernelRecipe>> recipes{std::make_shared<CudaPackRecipe>(compensated)};
+  return std::make_shared<Operator>(compensated ? matmul_pack_b_compensated_kernel_def() : matmul_pack_kernel_def(), std::move(recipes),
+                                    std::make_shared<OrderedDispatchPolicy>(), std::make_shared<CudaPackProvider>());
+}
+
 }  // namespace vecops::runtime
 
 // ------------------------------------------------------------------ C bridge
@@ -420,10 +640,24 @@ using namespace vecops::runtime;
 namespace {
 
 constexpr std::uint64_t kMatmulHandle = 0x6d61746d756c0001ULL;
+constexpr std::uint64_t kPackHandle = 0x6d61746d756c0002ULL;
+constexpr std::uint64_t kPackCompensatedHandle = 0x6d61746d756c0003ULL;
 
 const std::shared_ptr<Operator>& matmul_operator() {
   static const std::shared_ptr<Operator> op = make_matmul_operator();
   return op;
+}
+
+const std::shared_ptr<Operator>& pack_operator(bool compensated) {
+  static const std::shared_ptr<Operator> ops[2] = {make_matmul_pack_operator(false), make_matmul_pack_operator(true)};
+  return ops[compensated ? 1 : 0];
+}
+
+const Operator* operator_of(std::uint64_t handle) {
+  if (handle == kMatmulHandle) return matmul_operator().get();
+  if (handle == kPackHandle) return pack_operator(false).get();
+  if (handle == kPackCompensatedHandle) return pack_operator(true).get();
+  return nullptr;
 }
 
 std::int32_t report(VecopsError* error, const Status& status) {
@@ -482,20 +716,27 @@ uint64_t vecops_b200_matmul_operator(void) {
   return kMatmulHandle;
 }
 
+uint64_t vecops_b200_matmul_pack_operator(int32_t compensated) {
+  (void)pack_operator(compensated != 0);
+  return compensated != 0 ? kPackCompensatedHandle : kPackHandle;
+}
+
 int32_t vecops_operator_bridge_invoke_v1(uint64_t handle, const VecopsCall* call, uint32_t num_specialization_values,
                                          const VecopsSpecializationArgument* specialization_values, VecopsError* error) {
-  if (handle != kMatmulHandle) return fail(error, VECOPS_STATUS_NOT_FOUND, "unknown operator handle");
+  const Operator* op = operator_of(handle);
+  if (op == nullptr) return fail(error, VECOPS_STATUS_NOT_FOUND, "unknown operator handle");
   KernelCall kernel_call;
   if (const auto rc = call_from_frame(call, num_specialization_values, specialization_values, &kernel_call, error); rc != VECOPS_STATUS_OK) return rc;
-  const Status status = matmul_operator()->invoke(kernel_call, call->context, call->workspace, call->workspace_size);
+  const Status status = op->invoke(kernel_call, call->context, call->workspace, call->workspace_size);
   return status.ok() ? VECOPS_STATUS_OK : report(error, status);
 }
 
 int32_t vecops_b200_operator_resolve(uint64_t handle, const VecopsCall* call, char* key, size_t capacity, VecopsError* error) {
-  if (handle != kMatmulHandle) return fail(error, VECOPS_STATUS_NOT_FOUND, "unknown operator handle");
+  const Operator* op = operator_of(handle);
+  if (op == nullptr) return fail(error, VECOPS_STATUS_NOT_FOUND, "unknown operator handle");
   KernelCall kernel_call;
   if (const auto rc = call_from_frame(call, 0, nullptr, &kernel_call, error); rc != VECOPS_STATUS_OK) return rc;
-  auto executable = matmul_operator()->resolve(kernel_call, call->context);
+  auto executable = op->resolve(kernel_call, call->context);
   if (!executable) return report(error, executable.status());
   if (key != nullptr && capacity > 0) {
     const auto text = executable.value()->specialization_key();

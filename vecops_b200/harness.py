@@ -6,7 +6,7 @@ library's own kernels.
 from __future__ import annotations
 
 import ctypes
-from ctypes import byref, c_uint32, c_uint64
+from ctypes import byref, c_int64, c_uint32, c_uint64
 
 from . import capi
 
@@ -153,6 +153,42 @@ def quantize_rows(src, dst, scale: float, zero_point: float, stream=None) -> Non
     error.raise_for(capi.library().vecops_b200_quantize_rows(src.data_ptr(), torch_dtype_code(src.dtype), src.stride(0), src.stride(1),
                                                             dst.data_ptr(), torch_dtype_code(dst.dtype), dst.stride(0), src.shape[0],
                                                             src.shape[1], scale, zero_point, stream.cuda_stream, byref(error.record)))
+
+
+def packed_layout(dtype, rows: int, k: int) -> tuple[int, int]:
+    """(pitch in elements, bytes) of the packed form of a [rows, K] operand of torch dtype `dtype`."""
+    pitch, size = c_int64(0), c_uint64(0)
+    error = capi.ErrorBuffer()
+    error.raise_for(capi.library().vecops_b200_matmul_packed_layout(torch_dtype_code(dtype), rows, k, byref(pitch), byref(size),
+                                                                    byref(error.record)))
+    return pitch.value, size.value
+
+
+def pack_operand(view, dtype=None, operand: int = 1, zero_point: int | None = None, stream=None):
+    """Prepare one matmul operand: any strided [rows, K] view (a `.t()` of a [K, N]-stored weight included) -> its packed form,
+    K-contiguous rows on a 128-byte pitch, optionally narrowed from fp32 to `dtype` (bf16 / fp16).
+
+    Returns the packed operand as a [rows, K] tensor view (row stride = pitch) to hand to `matmul` in place of `view`;
+    with `zero_point` (signed 8-bit B only) returns (packed, compensation) where compensation[n] = -zero_point * sum_k B[n,k]."""
+    import torch
+    if view.dim() != 2:
+        raise ValueError("operand must be 2-D")
+    dtype = dtype or view.dtype
+    rows, k = view.shape
+    pitch, size = packed_layout(dtype, rows, k)
+    storage = torch.empty((rows, pitch), dtype=dtype, device=view.device)
+    if stream is None:
+        stream = torch.cuda.current_stream(view.device)
+    record = capi.VecopsB200Pack(ctypes.sizeof(capi.VecopsB200Pack), operand, rows, k, view.data_ptr(), view.stride(0), view.stride(1),
+                                 torch_dtype_code(view.dtype), torch_dtype_code(dtype), storage.data_ptr(), size,
+                                 view.device.index if view.device.index is not None else -1, 0, stream.cuda_stream)
+    error = capi.ErrorBuffer()
+    if zero_point is None:
+        error.raise_for(capi.library().vecops_b200_matmul_pack(byref(record), byref(error.record)))
+        return storage[:, :k]
+    compensation = torch.empty(rows, dtype=torch.int32, device=view.device)
+    error.raise_for(capi.library().vecops_b200_matmul_pack_b_compensated(byref(record), zero_point, compensation.data_ptr(), byref(error.record)))
+    return storage[:, :k], compensation
 
 
 def column_correction(b_nk, zero_point: int, out, stream=None) -> None:
