@@ -302,6 +302,48 @@ VECOPS_B200_EXPORT int32_t vecops_b200_matmul_pack(const VecopsB200Pack* pack, V
 VECOPS_B200_EXPORT int32_t vecops_b200_matmul_pack_b_compensated(const VecopsB200Pack* pack, int32_t a_zero_point,
                                                                  int32_t* compensation, VecopsError* error);
 
+/* ---------------------------------------------------------------------------------------------------------------
+ * The caller one step above matmul: scaled dot-product attention for one head, composed as vecops composes it
+ * (ops::scaled_dot_product_attention, include/vecops/ops/details/attention/SDPA.h:72-84 and :305-383, materialized
+ * strategy): S = Q.K^T through the matmul path; s = S*scale + bias, -inf wherever the query mask, the key mask, the
+ * keep mask or the causal cut drops the pair (Common.h:200-289); p = softmax row, rounded to the matmul operand type
+ * (bf16) - an all-dropped row is all zero (Common.h:293-345); O = P.V through the matmul path again.
+ * Q [Lq,Dqk], K [Lkv,Dqk], V [Lkv,Dv] bf16 with element strides, out [Lq,Dv] f32 or bf16.  Masks are bytes (non-zero
+ * keeps; the reference takes bool tensors), bias is f32; each may be NULL.  Device scratch (scores, probabilities, the
+ * packed V^T and the products' own scratch) is the caller's: ask vecops_b200_sdpa_workspace, pass 256-byte aligned memory.
+ * Not a fused attention kernel: the score matrix makes one round trip through device memory. */
+typedef struct VecopsB200Attention {
+  uint32_t struct_size;
+  uint32_t causal;            /* 0 none, 1 top left (key <= query), 2 bottom right (key <= query + Lkv - Lq) */
+  int64_t lq, lkv, dqk, dv;
+  const void* q;
+  int64_t q_stride_row, q_stride_col;
+  const void* k;
+  int64_t k_stride_row, k_stride_col;
+  const void* v;
+  int64_t v_stride_row, v_stride_col;
+  void* out;
+  int64_t out_stride_row, out_stride_col;
+  uint32_t qkv_dtype;         /* VECOPS_DTYPE_BF16 */
+  uint32_t out_dtype;         /* F32 | BF16 */
+  const uint8_t* query_mask;  /* [Lq] or NULL */
+  const uint8_t* key_mask;    /* [Lkv] or NULL */
+  const uint8_t* keep_mask;   /* [Lq,Lkv] or NULL */
+  int64_t keep_stride_row, keep_stride_col;
+  const float* bias;          /* [Lq,Lkv] or NULL, added after the scaling */
+  int64_t bias_stride_row, bias_stride_col;
+  float scale;
+  uint32_t flags;             /* VECOPS_B200_MATMUL_FLAG_ASYNC: enqueue only */
+  void* workspace;
+  uint64_t workspace_size;
+  void* stream;
+  int32_t device_index;
+  uint32_t reserved;
+} VecopsB200Attention;
+
+VECOPS_B200_EXPORT int32_t vecops_b200_sdpa_workspace(const VecopsB200Attention* attention, uint64_t* bytes, VecopsError* error);
+VECOPS_B200_EXPORT int32_t vecops_b200_sdpa_run(const VecopsB200Attention* attention, VecopsError* error);
+
 /* Strided gather of column slabs: dst[M, ldd] columns [col0, col0+cols) <-
  * src[M, cols] (row pitch lds), `elem_size` bytes per element.  Used after the
  * all-gather of a column-sharded GEMM to place peers' slabs into the row-major

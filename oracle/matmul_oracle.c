@@ -37,6 +37,7 @@
  */
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 static inline float bf16_to_f32(uint16_t bits) {
@@ -328,6 +329,60 @@ void oracle_matmul_i8_dequant(int64_t m, int64_t n, int64_t k, const void* a, in
 }
 
 /* How many threads the loops above use (1 when built without OpenMP). */
+/* Scaled dot-product attention for one head, the caller one step above matmul
+ * (include/vecops/ops/details/attention/SDPA.h:72-84, :305-383; Common.h:200-345):
+ *   S = Q.K^T in the accumulator type (bf16 operands, fp32 sums);
+ *   s = S * scale + bias;  kept where the query is active, the key is active, the keep mask is non-zero and - causal -
+ *       key <= query (top_left) or key <= query + (Lkv - Lq) (bottom_right); everything else is -inf;
+ *   p = exp(s - rowmax) / sum, converted to the PROBABILITY type = the matmul atom's operand type (bf16, round to
+ *       nearest even); a row with nothing kept is all zero;
+ *   O = P.V in fp32, stored as fp32 or bf16.
+ * The reference evaluates exp with its fast estimate (relative error <= 1e-3, tests/ops/AttentionTest.cpp:100-130) and
+ * its own tests accept 2.5e-2 .. 5e-2 absolute (AttentionTest.cpp:243-247, :284-286); this restatement uses the exact
+ * exponential, and the pin against the reference's outputs carries that tolerance.
+ * causal: 0 none, 1 top_left, 2 bottom_right.  Masks are bytes, non-zero = keep; any of them and bias may be NULL. */
+void oracle_sdpa_bf16(int64_t lq, int64_t lkv, int64_t dqk, int64_t dv, const uint16_t* q, int64_t sq, const uint16_t* k, int64_t sk,
+                      const uint16_t* v, int64_t sv, const uint8_t* query_mask, const uint8_t* key_mask, const uint8_t* keep_mask,
+                      int64_t keep_sr, const float* bias, int64_t bias_sr, int causal, float scale, void* out, int64_t so, int out_is_bf16) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < lq; ++i) {
+    float* s = (float*)malloc((size_t)(lkv > 0 ? lkv : 1) * sizeof(float));
+    uint16_t* p = (uint16_t*)malloc((size_t)(lkv > 0 ? lkv : 1) * sizeof(uint16_t));
+    const int64_t last_key = causal == 1 ? i : (causal == 2 ? i + (lkv - lq) : lkv - 1);
+    const int query_active = query_mask == NULL || query_mask[i] != 0;
+    float maximum = -INFINITY;
+    int any = 0;
+    for (int64_t j = 0; j < lkv; ++j) {
+      double sum = 0.0;
+      for (int64_t d = 0; d < dqk; ++d) sum += (double)bf16_to_f32(q[i * sq + d]) * (double)bf16_to_f32(k[j * sk + d]);
+      float value = (float)sum * scale;
+      if (bias) value += bias[i * bias_sr + j];
+      const int keep = query_active && j <= last_key && (key_mask == NULL || key_mask[j] != 0) &&
+                       (keep_mask == NULL || keep_mask[i * keep_sr + j] != 0);
+      s[j] = keep ? value : -INFINITY;
+      if (keep) any = 1;
+      if (s[j] > maximum) maximum = s[j];
+    }
+    double total = 0.0;
+    if (any && maximum != -INFINITY)
+      for (int64_t j = 0; j < lkv; ++j) {
+        s[j] = s[j] == -INFINITY ? 0.f : (float)exp((double)s[j] - (double)maximum);
+        total += s[j];
+      }
+    const int valid = any && maximum != -INFINITY && total > 0.0;
+    const float reciprocal = valid ? 1.0f / (float)total : 0.f;
+    for (int64_t j = 0; j < lkv; ++j) p[j] = valid ? f32_to_bf16(s[j] * reciprocal) : 0;
+    for (int64_t d = 0; d < dv; ++d) {
+      double sum = 0.0;
+      for (int64_t j = 0; j < lkv; ++j) sum += (double)bf16_to_f32(p[j]) * (double)bf16_to_f32(v[j * sv + d]);
+      if (out_is_bf16) ((uint16_t*)out)[i * so + d] = f32_to_bf16((float)sum);
+      else ((float*)out)[i * so + d] = (float)sum;
+    }
+    free(s);
+    free(p);
+  }
+}
+
 #ifdef _OPENMP
 #include <omp.h>
 int oracle_threads(void) { return omp_get_max_threads(); }

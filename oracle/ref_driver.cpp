@@ -20,6 +20,7 @@
 #include <thread>
 #include <vector>
 
+#include "vecops/ops/Attention.h"
 #include "vecops/ops/Matmul.h"
 
 using namespace vecops;
@@ -281,6 +282,51 @@ void ref_f16_widen(const uint16_t* src, float* dst, int64_t count) {
 }
 void ref_f16_narrow(const float* src, uint16_t* dst, int64_t count) {
   for (int64_t i = 0; i < count; ++i) dst[i] = float16_t(src[i]).to_bits();
+}
+
+}  // extern "C"
+
+// The reference's scaled dot-product attention for one head (ops/details/attention/SDPA.h:72-84), materialized strategy:
+// Q[Lq,Dqk], K[Lkv,Dqk], V[Lkv,Dv] bf16, out[Lq,Dv] f32.  Call forms as in tests/ops/AttentionTest.cpp:238-241 (plain) and
+// :603-607 (query mask, key mask, keep mask, bias - all four or none).  causal: 0 none, 1 top_left, 2 bottom_right.
+template <ops::AttentionCausalMode Causal>
+static int ref_sdpa_typed(int64_t lq, int64_t lkv, int64_t dqk, int64_t dv, const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                          const uint8_t* query_mask, const uint8_t* key_mask, const uint8_t* keep_mask, const float* bias, float scale,
+                          float* out) {
+  using Config = ops::AttentionConfig<ops::MatmulConfig<matmul::AMX_BF16F32>, 32, 32, Causal, ops::SDPAStrategy::materialized>;
+  auto qt = make_tensor(reinterpret_cast<const bfloat16_t*>(q), make_shape(Any{lq}, Any{dqk}));
+  auto kt = make_tensor(reinterpret_cast<const bfloat16_t*>(k), make_shape(Any{lkv}, Any{dqk}));
+  auto vt = make_tensor(reinterpret_cast<const bfloat16_t*>(v), make_shape(Any{lkv}, Any{dv}));
+  auto ot = make_tensor(out, make_shape(Any{lq}, Any{dv}));
+  auto op = ops::scaled_dot_product_attention(Config{});
+  if (query_mask == nullptr) {
+    kernel::Workspace storage(op.required_workspace(qt, kt, vt, ot));
+    auto workspace = storage.view();
+    op(workspace, qt, kt, vt, ot, scale);
+    return 0;
+  }
+  auto qmt = make_tensor(reinterpret_cast<const bool*>(query_mask), make_shape(Any{lq}));
+  auto kmt = make_tensor(reinterpret_cast<const bool*>(key_mask), make_shape(Any{lkv}));
+  auto amt = make_tensor(reinterpret_cast<const bool*>(keep_mask), make_shape(Any{lq}, Any{lkv}));
+  auto bt = make_tensor(bias, make_shape(Any{lq}, Any{lkv}));
+  kernel::Workspace storage(op.required_workspace(qt, kt, vt, qmt, kmt, amt, bt, ot));
+  auto workspace = storage.view();
+  op(workspace, qt, kt, vt, qmt, kmt, amt, bt, ot, scale);
+  return 0;
+}
+
+extern "C" {
+
+int ref_sdpa_bf16(int64_t lq, int64_t lkv, int64_t dqk, int64_t dv, const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                  const uint8_t* query_mask, const uint8_t* key_mask, const uint8_t* keep_mask, const float* bias, int causal, float scale,
+                  float* out) {
+  if (!request_amx()) return 1;
+  if ((query_mask == nullptr) != (key_mask == nullptr) || (query_mask == nullptr) != (keep_mask == nullptr) ||
+      (query_mask == nullptr) != (bias == nullptr))
+    return 2;  // this door passes all four optional operands or none
+  if (causal == 1) return ref_sdpa_typed<ops::AttentionCausalMode::top_left>(lq, lkv, dqk, dv, q, k, v, query_mask, key_mask, keep_mask, bias, scale, out);
+  if (causal == 2) return ref_sdpa_typed<ops::AttentionCausalMode::bottom_right>(lq, lkv, dqk, dv, q, k, v, query_mask, key_mask, keep_mask, bias, scale, out);
+  return ref_sdpa_typed<ops::AttentionCausalMode::none>(lq, lkv, dqk, dv, q, k, v, query_mask, key_mask, keep_mask, bias, scale, out);
 }
 
 }  // extern "C"

@@ -166,6 +166,40 @@ def main() -> None:
     b = bf16_pattern(batch * n * k, 11, (batch, n, k))
     cases["batched_4x19x21x72"] = dict(kind="batched_bf16", a=a, b=b, shared=np.array(""), c=ref.matmul_bf16_batched(a, b))
 
+    # scaled dot-product attention, one head (ops/details/attention/SDPA.h): the reference tests' own operand patterns
+    # (tests/ops/AttentionTest.cpp:256-286 tail shapes; :568-612 masks, bias and a fully masked query row) and seeded cases
+    # with causal modes
+    def attention_case(name, q, k, v, scale, causal=0, **optional):
+        out = ref.sdpa_bf16(q, k, v, scale, causal=causal, **optional)
+        cases[name] = dict(kind="sdpa_bf16", q=q, k=k, v=v, scale=np.float32(scale), causal=np.int32(causal), out=out, **optional)
+
+    lq, lkv, dqk, dv = 5, 7, 8, 6
+    q = f32_to_bf16_bits((((np.arange(lq * dqk) * 3) % 11 - 5) / 8).astype(np.float32)).reshape(lq, dqk)
+    k = f32_to_bf16_bits((((np.arange(lkv * dqk) * 5) % 13 - 6) / 8).astype(np.float32)).reshape(lkv, dqk)
+    v = f32_to_bf16_bits((((np.arange(lkv * dv) * 7) % 17 - 8) / 16).astype(np.float32)).reshape(lkv, dv)
+    attention_case("sdpa_tail_5x7x8x6", q, k, v, 0.375)
+    lq, lkv, d = 3, 5, 8
+    q = f32_to_bf16_bits(np.full((lq, d), 0.25, np.float32))
+    k = f32_to_bf16_bits(np.full((lkv, d), 0.5, np.float32))
+    v = f32_to_bf16_bits(((np.arange(lkv * d) % 9 - 4) / 8).astype(np.float32)).reshape(lkv, d)
+    keep = np.ones((lq, lkv), np.uint8)
+    keep[2, 3] = 0
+    attention_case("sdpa_masks_bias_3x5x8x8", q, k, v, 0.5, query_mask=np.array([1, 0, 1], np.uint8), key_mask=np.array([1, 1, 0, 1, 1], np.uint8),
+                   keep_mask=keep, bias=((np.arange(lq * lkv) % lkv) * 0.125).astype(np.float32).reshape(lq, lkv))
+    rng = np.random.default_rng(41)
+    for name, (lq, lkv, dqk, dv), causal, optional in [("sdpa_bottom_right_33x70x16x24", (33, 70, 16, 24), 2, False),
+                                                         ("sdpa_top_left_40x40x64x64", (40, 40, 64, 64), 1, False),
+                                                         ("sdpa_masks_bottom_right_37x53x32x40", (37, 53, 32, 40), 2, True),
+                                                         ("sdpa_masks_130x257x64x64", (130, 257, 64, 64), 0, True)]:
+        q = f32_to_bf16_bits(rng.standard_normal((lq, dqk)).astype(np.float32))
+        k = f32_to_bf16_bits(rng.standard_normal((lkv, dqk)).astype(np.float32))
+        v = f32_to_bf16_bits(rng.standard_normal((lkv, dv)).astype(np.float32))
+        extra = {}
+        if optional:
+            extra = dict(query_mask=(rng.random(lq) > 0.2).astype(np.uint8), key_mask=(rng.random(lkv) > 0.2).astype(np.uint8),
+                         keep_mask=(rng.random((lq, lkv)) > 0.1).astype(np.uint8), bias=rng.uniform(-1, 1, (lq, lkv)).astype(np.float32))
+        attention_case(name, q, k, v, 1.0 / np.sqrt(dqk), causal, **extra)
+
     # float16_t's widening and narrowing (util/Float16.h:272-277) over the whole sweep, as digests: the part of the
     # AMX_F16F32 row a host without AMX-FP16 can run
     patterns, floats = f16_conversion_inputs()

@@ -78,7 +78,7 @@ def oracle(kind, port, a, b, scale, out_bf16=True):
 def test_golden_fixtures_through_automatic_dispatch(golden):
     for name, case in golden.items():
         kind = str(case["kind"])
-        if kind in ("fused_bf16", "i8acc", "quant_u8s8", "batched_bf16", "f16_convert"):
+        if kind in ("fused_bf16", "i8acc", "quant_u8s8", "batched_bf16", "f16_convert", "sdpa_bf16"):
             continue  # the fused forms have their own tests below; the conversion digests are the checker's own
         a, b = case["a"], case["b"]
         if kind == "i8":
@@ -984,3 +984,68 @@ def test_pack_operator_through_the_bridge():
     call = frame([_tensor_value(source, keep=keep), _tensor_value(wrong, True, keep=keep)], keep)
     error = capi.ErrorBuffer()
     assert lib.vecops_operator_bridge_invoke_v1(handle, byref(call), 0, None, byref(error.record)) != capi.OK
+
+
+# ------------------------------------------------------------------ the caller one step up: scaled dot-product attention
+
+def _sdpa_gpu(case_or_kwargs, out_dtype=torch.float32):
+    c = case_or_kwargs
+    q, k, v = (to_device(c[name], bf16=True) for name in ("q", "k", "v"))
+    out = torch.full((q.shape[0], v.shape[1]), -99, dtype=out_dtype, device="cuda")
+    optional = {name: to_device(np.ascontiguousarray(c[name])) for name in ("query_mask", "key_mask", "keep_mask", "bias") if c.get(name) is not None}
+    harness.sdpa(q, k, v, out, float(c["scale"]), causal=int(c.get("causal", 0)), **optional)
+    torch.cuda.synchronize()
+    return bf16_bits_to_f32(bf16_result_to_numpy(out)) if out_dtype == torch.bfloat16 else out.cpu().numpy()
+
+
+def test_sdpa_golden_fixtures(golden):
+    # outputs of the reference's own scaled_dot_product_attention on its tests' operand patterns and on seeded cases
+    seen = 0
+    for name, case in golden.items():
+        if str(case["kind"]) != "sdpa_bf16":
+            continue
+        got = _sdpa_gpu(case)
+        assert rel_frobenius(got, case["out"]) <= TOL_BF16, name
+        assert np.array_equal((got == 0).all(axis=1), (case["out"] == 0).all(axis=1)), name  # fully masked rows are exactly zero
+        seen += 1
+    assert seen >= 6
+
+
+@pytest.mark.parametrize("lq,lkv,dqk,dv,causal", [(512, 768, 64, 64, 0), (1024, 1024, 128, 128, 2), (300, 520, 72, 40, 1), (1, 2048, 128, 128, 0),
+                                                    (257, 129, 64, 96, 2)])
+def test_sdpa_against_the_checker(port, lq, lkv, dqk, dv, causal):
+    # sizes at which both products run on the tensor-core kernels (and ragged ones that do not)
+    rng = np.random.default_rng(lq + lkv)
+    case = dict(q=f32_to_bf16_bits(rng.standard_normal((lq, dqk)).astype(np.float32)),
+                k=f32_to_bf16_bits(rng.standard_normal((lkv, dqk)).astype(np.float32)),
+                v=f32_to_bf16_bits(rng.standard_normal((lkv, dv)).astype(np.float32)), scale=1.0 / np.sqrt(dqk), causal=causal)
+    rows = np.unique(np.concatenate([np.linspace(0, lq - 1, 24).astype(np.int64), np.arange(max(0, lq - 3), lq)]))
+    got = _sdpa_gpu(case)
+    # rows of attention are independent: the checker runs on a sample of query rows (causal cuts are per row, so the
+    # sample keeps its row indices through a keep mask instead)
+    last = np.arange(lq)[:, None] + (0 if causal == 1 else lkv - lq)
+    keep = np.ones((lq, lkv), np.uint8) if causal == 0 else (np.arange(lkv)[None, :] <= last).astype(np.uint8)
+    want = port.sdpa_bf16(case["q"][rows], case["k"], case["v"], case["scale"], keep_mask=keep[rows])
+    assert rel_frobenius(got[rows], want) <= TOL_BF16
+    # with every optional operand, bf16 out
+    case.update(query_mask=(rng.random(lq) > 0.1).astype(np.uint8), key_mask=(rng.random(lkv) > 0.1).astype(np.uint8),
+                keep_mask=(rng.random((lq, lkv)) > 0.05).astype(np.uint8), bias=rng.uniform(-1, 1, (lq, lkv)).astype(np.float32))
+    got = _sdpa_gpu(case, torch.bfloat16)
+    combined = (keep & case["keep_mask"])[rows]
+    want = port.sdpa_bf16(case["q"][rows], case["k"], case["v"], case["scale"], query_mask=case["query_mask"][rows], key_mask=case["key_mask"],
+                          keep_mask=combined, bias=case["bias"][rows], out_bf16=True)
+    assert rel_frobenius(got[rows], bf16_bits_to_f32(want)) <= 3e-3  # one more bf16 rounding of the output on both sides
+
+
+def test_sdpa_degenerate_extents_and_refusals():
+    q = torch.zeros((4, 8), dtype=torch.bfloat16, device="cuda")
+    out = torch.full((4, 8), 7.0, dtype=torch.float32, device="cuda")
+    harness.sdpa(q, torch.zeros((0, 8), dtype=torch.bfloat16, device="cuda"), torch.zeros((0, 8), dtype=torch.bfloat16, device="cuda"), out, 1.0)
+    torch.cuda.synchronize()
+    assert bool((out == 0).all())  # no key: every row is an all-dropped row
+    harness.sdpa(q[:0], q, q, out[:0], 1.0)  # no query: nothing to write
+    with pytest.raises(capi.VecopsB200Error):
+        harness.sdpa(q.float(), q.float(), q.float(), out, 1.0)  # fp32 q, k, v are not served
+    record = harness.sdpa_record(q, q, q, out, 1.0)
+    error = capi.ErrorBuffer()
+    assert capi.library().vecops_b200_sdpa_run(byref(record), byref(error.record)) == capi.INVALID_ARGUMENT  # no scratch given

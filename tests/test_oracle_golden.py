@@ -35,6 +35,14 @@ def test_port_matches_golden_fixtures(port, golden):
             assert hashlib.sha256(port.f16_narrow(floats).tobytes()).hexdigest() == str(case["narrow_sha256"]), name
             checked += 1
             continue
+        if kind == "sdpa_bf16":
+            # the caller one step up: outputs of the reference's own attention (materialized strategy)
+            got = port.sdpa_bf16(case["q"], case["k"], case["v"], float(case["scale"]), case.get("query_mask"), case.get("key_mask"),
+                                 case.get("keep_mask"), case.get("bias"), int(case["causal"]))
+            assert rel_frobenius(got, case["out"]) <= 1e-5, name  # the reference's fast exp is the only difference
+            assert np.array_equal((got == 0).all(axis=1), (case["out"] == 0).all(axis=1)), name  # fully masked rows are exactly zero
+            checked += 1
+            continue
         a, b = case["a"], case["b"]
         if kind == "i8":
             assert np.array_equal(port.matmul_i8(a, b), case["c"]), name
@@ -70,7 +78,7 @@ def test_port_matches_golden_fixtures(port, golden):
         else:
             raise AssertionError(f"unknown fixture kind {kind}")
         checked += 1
-    assert checked >= 38
+    assert checked >= 44
 
 
 def test_int32_accumulator_wraps(port):

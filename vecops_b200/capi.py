@@ -97,6 +97,20 @@ class VecopsB200Pack(Structure):
                 ("dst_size", c_uint64), ("device_index", c_int32), ("flags", c_uint32), ("stream", c_void_p)]
 
 
+class VecopsB200Attention(Structure):
+    _fields_ = [("struct_size", c_uint32), ("causal", c_uint32), ("lq", c_int64), ("lkv", c_int64), ("dqk", c_int64), ("dv", c_int64),
+                ("q", c_void_p), ("q_stride_row", c_int64), ("q_stride_col", c_int64), ("k", c_void_p), ("k_stride_row", c_int64),
+                ("k_stride_col", c_int64), ("v", c_void_p), ("v_stride_row", c_int64), ("v_stride_col", c_int64), ("out", c_void_p),
+                ("out_stride_row", c_int64), ("out_stride_col", c_int64), ("qkv_dtype", c_uint32), ("out_dtype", c_uint32),
+                ("query_mask", c_void_p), ("key_mask", c_void_p), ("keep_mask", c_void_p), ("keep_stride_row", c_int64),
+                ("keep_stride_col", c_int64), ("bias", c_void_p), ("bias_stride_row", c_int64), ("bias_stride_col", c_int64),
+                ("scale", c_float), ("flags", c_uint32), ("workspace", c_void_p), ("workspace_size", c_uint64), ("stream", c_void_p),
+                ("device_index", c_int32), ("reserved", c_uint32)]
+
+
+CAUSAL_NONE, CAUSAL_TOP_LEFT, CAUSAL_BOTTOM_RIGHT = 0, 1, 2
+
+
 class VecopsB200Gather(Structure):
     _fields_ = [("struct_size", c_uint32), ("world", c_int32), ("c", POINTER(c_void_p)), ("n_total", c_int64), ("ldc", c_int64),
                 ("col0", c_int64), ("flags", c_uint32), ("reserved", c_uint32)]
@@ -152,6 +166,8 @@ def library() -> ctypes.CDLL:
         lib.vecops_b200_matmul_packed_layout.argtypes = [c_uint32, c_int64, c_int64, POINTER(c_int64), POINTER(c_uint64), e]
         lib.vecops_b200_matmul_pack.argtypes = [POINTER(VecopsB200Pack), e]
         lib.vecops_b200_matmul_pack_b_compensated.argtypes = [POINTER(VecopsB200Pack), c_int32, c_void_p, e]
+        lib.vecops_b200_sdpa_workspace.argtypes = [POINTER(VecopsB200Attention), POINTER(c_uint64), e]
+        lib.vecops_b200_sdpa_run.argtypes = [POINTER(VecopsB200Attention), e]
         lib.vecops_b200_matmul_allgather_run.argtypes = [POINTER(VecopsB200Matmul), POINTER(VecopsB200Gather), e]
         lib.vecops_b200_kernel_name.argtypes = [c_uint32]
         lib.vecops_b200_kernel_name.restype = c_char_p

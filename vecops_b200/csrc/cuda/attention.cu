@@ -1,0 +1,203 @@
+// Scaled dot-product attention for one head, built the way vecops builds it: two products through the matmul
+// entry points with a row softmax between them (include/vecops/ops/details/attention/SDPA.h:305-383, the
+// "materialized" strategy).  The caller one step above the matmul path - not a fused attention kernel: the score
+// matrix makes one round trip through device memory.
+//
+//   S = Q.K^T            vecops_b200_matmul_run, bf16 x bf16 -> f32            (tcgen05 when the operands allow)
+//   P = softmax rows     sdpa_softmax_kernel: scale, bias, masks, causal cut, exp, normalise, round to bf16
+//   Vt = pack(V^T)       vecops_b200_matmul_pack: V is [Lkv, Dv]; the product wants B = V^T as K-contiguous rows
+//   O = P.Vt^T           vecops_b200_matmul_run, bf16 x bf16 -> f32 | bf16
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "vecops_b200/matmul_cuda.h"
+
+#include "shim_util.h"
+
+using namespace vb200;
+
+namespace {
+
+__device__ __forceinline__ float block_reduce(float value, bool take_max, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, value, offset);
+    value = take_max ? fmaxf(value, other) : value + other;
+  }
+  __syncthreads();  // the previous use of `scratch` is over
+  if (lane == 0) scratch[warp] = value;
+  __syncthreads();
+  float total = scratch[0];
+  for (int w = 1; w < static_cast<int>(blockDim.x >> 5); ++w) total = take_max ? fmaxf(total, scratch[w]) : total + scratch[w];
+  return total;
+}
+
+// One CTA per score row.  In place on S like the reference (Common.h:236-345): decorate (s * scale + bias, -inf where
+// not kept) and take the maximum; exponentiate and sum; normalise into the probability type.  Each thread revisits only
+// the elements it wrote itself, so the passes need no barrier beyond the two reductions.
+__global__ void __launch_bounds__(256) sdpa_softmax_kernel(float* __restrict__ scores, long long ld_scores, __nv_bfloat16* __restrict__ probabilities,
+                                                           long long ld_probabilities, int lq, int lkv, float scale,
+                                                           const uint8_t* __restrict__ query_mask, const uint8_t* __restrict__ key_mask,
+                                                           const uint8_t* __restrict__ keep_mask, long long keep_sr, long long keep_sc,
+                                                           const float* __restrict__ bias, long long bias_sr, long long bias_sc, int causal) {
+  __shared__ float scratch[8];
+  const float negative_infinity = -INFINITY;
+  for (int row = blockIdx.x; row < lq; row += gridDim.x) {
+    float* s = scores + row * ld_scores;
+    __nv_bfloat16* p = probabilities + row * ld_probabilities;
+    const bool query_active = query_mask == nullptr || query_mask[row] != 0;
+    const long long last_key = causal == 1 ? row : (causal == 2 ? static_cast<long long>(row) + (lkv - lq) : lkv - 1);
+    float maximum = negative_infinity;
+    for (int j = threadIdx.x; j < lkv; j += blockDim.x) {
+      float value = __fmul_rn(s[j], scale);
+      if (bias != nullptr) value = __fadd_rn(value, bias[row * bias_sr + j * bias_sc]);
+      const bool keep = query_active && j <= last_key && (key_mask == nullptr || key_mask[j] != 0) &&
+                        (keep_mask == nullptr || keep_mask[row * keep_sr + j * keep_sc] != 0);
+      value = keep ? value : negative_infinity;
+      s[j] = value;
+      maximum = fmaxf(maximum, value);
+    }
+    maximum = block_reduce(maximum, true, scratch);
+    float sum = 0.f;
+    if (maximum != negative_infinity) {
+      for (int j = threadIdx.x; j < lkv; j += blockDim.x) {
+        const float e = s[j] == negative_infinity ? 0.f : __expf(s[j] - maximum);
+        s[j] = e;
+        sum += e;
+      }
+    }
+    sum = block_reduce(sum, false, scratch);
+    const bool valid = maximum != negative_infinity && sum > 0.f;  // a row with nothing kept is all zero
+    const float reciprocal = valid ? 1.f / sum : 0.f;
+    for (int j = threadIdx.x; j < lkv; j += blockDim.x) p[j] = __float2bfloat16_rn(valid ? s[j] * reciprocal : 0.f);
+  }
+}
+
+uint64_t round_up(uint64_t value, uint64_t to) { return (value + to - 1) / to * to; }
+
+struct Plan {
+  int64_t ld_scores, pitch;           // elements
+  uint64_t scores_at, probabilities_at, values_at, scratch_at, scratch_bytes, total;
+  VecopsB200Matmul qk, pv;
+};
+
+int32_t plan_of(const VecopsB200Attention& a, char* base, Plan* out, VecopsError* error) {
+  if (a.lq < 0 || a.lkv < 0 || a.dqk < 0 || a.dv < 0 || a.lq >= (INT64_C(1) << 31) || a.lkv >= (INT64_C(1) << 31) - 128)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "sdpa: extent out of range");
+  if (a.qkv_dtype != VECOPS_DTYPE_BF16 || (a.out_dtype != VECOPS_DTYPE_F32 && a.out_dtype != VECOPS_DTYPE_BF16))
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "sdpa serves bf16 q, k, v with an f32 or bf16 output");
+  if (a.causal > 2) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "sdpa: causal is 0 (none), 1 (top left) or 2 (bottom right)");
+  Plan p{};
+  p.ld_scores = static_cast<int64_t>(round_up(static_cast<uint64_t>(a.lkv), 4));
+  uint64_t packed_bytes = 0;
+  int32_t rc = vecops_b200_matmul_packed_layout(VECOPS_DTYPE_BF16, a.dv, a.lkv, &p.pitch, &packed_bytes, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  p.scores_at = 0;
+  p.probabilities_at = round_up(static_cast<uint64_t>(a.lq) * p.ld_scores * 4, 256);
+  p.values_at = round_up(p.probabilities_at + static_cast<uint64_t>(a.lq) * p.pitch * 2, 256);
+  p.scratch_at = round_up(p.values_at + packed_bytes, 256);
+
+  VecopsB200Matmul& qk = p.qk;
+  qk.struct_size = sizeof(VecopsB200Matmul);
+  qk.kernel = VECOPS_B200_KERNEL_AUTO;
+  qk.m = a.lq, qk.n = a.lkv, qk.k = a.dqk;
+  qk.a = a.q, qk.a_stride_m = a.q_stride_row, qk.a_stride_k = a.q_stride_col;
+  qk.b = a.k, qk.b_stride_n = a.k_stride_row, qk.b_stride_k = a.k_stride_col;
+  qk.c = base + p.scores_at, qk.c_stride_m = p.ld_scores, qk.c_stride_n = 1;
+  qk.a_dtype = qk.b_dtype = VECOPS_DTYPE_BF16;
+  qk.c_dtype = VECOPS_DTYPE_F32;
+  qk.device_index = a.device_index;
+  qk.stream = a.stream;
+  qk.flags = VECOPS_B200_MATMUL_FLAG_ASYNC;
+
+  VecopsB200Matmul& pv = p.pv;
+  pv = qk;
+  pv.m = a.lq, pv.n = a.dv, pv.k = a.lkv;
+  pv.a = base + p.probabilities_at, pv.a_stride_m = p.pitch, pv.a_stride_k = 1;
+  pv.b = base + p.values_at, pv.b_stride_n = p.pitch, pv.b_stride_k = 1;
+  pv.c = a.out, pv.c_stride_m = a.out_stride_row, pv.c_stride_n = a.out_stride_col;
+  pv.c_dtype = a.out_dtype;
+  pv.flags = a.flags & VECOPS_B200_MATMUL_FLAG_ASYNC;
+
+  uint64_t need_qk = 0, need_pv = 0;
+  if (a.lq > 0 && a.lkv > 0) {
+    rc = vecops_b200_matmul_workspace(&qk, &need_qk, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+  }
+  if (a.lq > 0 && a.dv > 0) {
+    rc = vecops_b200_matmul_workspace(&pv, &need_pv, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+  }
+  p.scratch_bytes = need_qk > need_pv ? need_qk : need_pv;
+  p.total = p.scratch_at + p.scratch_bytes;
+  qk.workspace = pv.workspace = p.scratch_bytes != 0 ? base + p.scratch_at : nullptr;
+  qk.workspace_size = pv.workspace_size = p.scratch_bytes;
+  *out = p;
+  return VECOPS_STATUS_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t vecops_b200_sdpa_workspace(const VecopsB200Attention* attention, uint64_t* bytes, VecopsError* error) {
+  if (attention == nullptr || attention->struct_size < sizeof(VecopsB200Attention) || bytes == nullptr)
+    return set_error(error, VECOPS_STATUS_ABI_MISMATCH, "attention record is null or too small, or no output pointer");
+  Plan plan;
+  const int32_t rc = plan_of(*attention, nullptr, &plan, error);
+  if (rc == VECOPS_STATUS_OK) *bytes = plan.total;
+  return rc;
+}
+
+int32_t vecops_b200_sdpa_run(const VecopsB200Attention* attention, VecopsError* error) {
+  if (attention == nullptr || attention->struct_size < sizeof(VecopsB200Attention))
+    return set_error(error, VECOPS_STATUS_ABI_MISMATCH, "attention record is null or too small");
+  const VecopsB200Attention& a = *attention;
+  Plan plan;
+  int32_t rc = plan_of(a, static_cast<char*>(a.workspace), &plan, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  if (a.lq == 0 || a.dv == 0) return VECOPS_STATUS_OK;  // no output element exists
+  if (a.out == nullptr || (a.lkv > 0 && a.v == nullptr))  // (q and k are checked by the first product, which knows whether Dqk is 0)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "sdpa: null operand");
+  if (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & 255u) != 0 || a.workspace_size < plan.total)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "sdpa needs %llu bytes of 256-byte aligned device scratch (vecops_b200_sdpa_workspace)",
+                     (unsigned long long)plan.total);
+  if (vecops_b200_device_count() == 0)
+    return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "no usable CUDA device; there is no CPU fallback");
+  if (a.device_index >= 0) {
+    const cudaError_t status = cudaSetDevice(a.device_index);
+    if (status != cudaSuccess) return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "cudaSetDevice(%d): %s", a.device_index, cudaGetErrorString(status));
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
+  char* base = static_cast<char*>(a.workspace);
+  if (a.lkv > 0) {
+    rc = vecops_b200_matmul_run(&plan.qk, error);  // S = Q.K^T (zeros when Dqk == 0)
+    if (rc != VECOPS_STATUS_OK) return rc;
+    const int rows = static_cast<int>(a.lq < 148 * 16 ? a.lq : 148 * 16);
+    sdpa_softmax_kernel<<<rows, 256, 0, stream>>>(reinterpret_cast<float*>(base + plan.scores_at), plan.ld_scores,
+                                                  reinterpret_cast<__nv_bfloat16*>(base + plan.probabilities_at), plan.pitch, static_cast<int>(a.lq),
+                                                  static_cast<int>(a.lkv), a.scale, a.query_mask, a.key_mask, a.keep_mask, a.keep_stride_row,
+                                                  a.keep_stride_col, a.bias, a.bias_stride_row, a.bias_stride_col, static_cast<int>(a.causal));
+    g_launches.fetch_add(1);
+    const cudaError_t status = cudaGetLastError();
+    if (status != cudaSuccess) return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "sdpa softmax launch: %s", cudaGetErrorString(status));
+    VecopsB200Pack pack{};
+    pack.struct_size = sizeof(VecopsB200Pack);
+    pack.operand = 1;
+    pack.rows = a.dv, pack.k = a.lkv;   // B of the second product is V^T: rows run along V's columns
+    pack.src = a.v, pack.src_stride_row = a.v_stride_col, pack.src_stride_k = a.v_stride_row;
+    pack.src_dtype = pack.dst_dtype = VECOPS_DTYPE_BF16;
+    pack.dst = base + plan.values_at;
+    pack.dst_size = plan.scratch_at - plan.values_at;
+    pack.device_index = a.device_index;
+    pack.stream = a.stream;
+    rc = vecops_b200_matmul_pack(&pack, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+  }
+  return vecops_b200_matmul_run(&plan.pv, error);  // O = P.V (zeros when Lkv == 0); synchronises unless the caller asked not to
+}
+
+}  // extern "C"

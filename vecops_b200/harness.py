@@ -191,6 +191,52 @@ def pack_operand(view, dtype=None, operand: int = 1, zero_point: int | None = No
     return storage[:, :k], compensation
 
 
+def sdpa_record(q, k, v, out, scale: float, query_mask=None, key_mask=None, keep_mask=None, bias=None, causal: int = 0, stream=None,
+                asynchronous: bool = False) -> capi.VecopsB200Attention:
+    """Describe one head of scaled dot-product attention: q [Lq,Dqk], k [Lkv,Dqk], v [Lkv,Dv] bf16, out [Lq,Dv] f32 or bf16;
+    masks uint8 / bool tensors (non-zero keeps), bias float32 [Lq,Lkv]."""
+    a = capi.VecopsB200Attention()
+    a.struct_size = ctypes.sizeof(capi.VecopsB200Attention)
+    a.causal = causal
+    a.lq, a.dqk = q.shape
+    a.lkv, a.dv = v.shape
+    if tuple(k.shape) != (a.lkv, a.dqk) or tuple(out.shape) != (a.lq, a.dv):
+        raise ValueError(f"shape mismatch: q{tuple(q.shape)} k{tuple(k.shape)} v{tuple(v.shape)} out{tuple(out.shape)}")
+    a.q, a.q_stride_row, a.q_stride_col = q.data_ptr(), q.stride(0), q.stride(1)
+    a.k, a.k_stride_row, a.k_stride_col = k.data_ptr(), k.stride(0), k.stride(1)
+    a.v, a.v_stride_row, a.v_stride_col = v.data_ptr(), v.stride(0), v.stride(1)
+    a.out, a.out_stride_row, a.out_stride_col = out.data_ptr(), out.stride(0), out.stride(1)
+    a.qkv_dtype, a.out_dtype = torch_dtype_code(q.dtype), torch_dtype_code(out.dtype)
+    if query_mask is not None:
+        a.query_mask = query_mask.data_ptr()
+    if key_mask is not None:
+        a.key_mask = key_mask.data_ptr()
+    if keep_mask is not None:
+        a.keep_mask, a.keep_stride_row, a.keep_stride_col = keep_mask.data_ptr(), keep_mask.stride(0), keep_mask.stride(1)
+    if bias is not None:
+        a.bias, a.bias_stride_row, a.bias_stride_col = bias.data_ptr(), bias.stride(0), bias.stride(1)
+    a.scale = scale
+    a.flags = capi.MATMUL_FLAG_ASYNC if asynchronous else 0
+    a.stream = stream.cuda_stream if stream is not None else None
+    a.device_index = out.device.index if out.is_cuda and out.device.index is not None else -1
+    return a
+
+
+def sdpa(q, k, v, out, scale: float, **kwargs) -> None:
+    """Run one head of attention on the GPU through the C ABI (two products through the matmul path around a row softmax)."""
+    import torch
+    kwargs.setdefault("stream", torch.cuda.current_stream(out.device) if out.is_cuda else None)
+    record = sdpa_record(q, k, v, out, scale, **kwargs)
+    need = c_uint64(0)
+    error = capi.ErrorBuffer()
+    error.raise_for(capi.library().vecops_b200_sdpa_workspace(byref(record), byref(need), byref(error.record)))
+    scratch = torch.empty(max(need.value, 256) + 256, dtype=torch.uint8, device=out.device)
+    offset = (-scratch.data_ptr()) % 256
+    record.workspace, record.workspace_size = scratch.data_ptr() + offset, need.value
+    error.raise_for(capi.library().vecops_b200_sdpa_run(byref(record), byref(error.record)))
+    del scratch
+
+
 def column_correction(b_nk, zero_point: int, out, stream=None) -> None:
     """out[n] = -zero_point * sum_k B[n,k] (int32), the accumulator-input row of an asymmetric 8-bit product."""
     import torch
