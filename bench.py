@@ -312,14 +312,16 @@ def measure_pack(dev, peaks) -> dict:
                 with torch.cuda.graph(graph, stream=side):
                     for i in range(count):
                         error.raise_for(capi.library().vecops_b200_matmul_pack(byref(records[i % 3]), byref(error.record)))
-                graph.replay()
+                for _ in range(20):  # warm-up: clocks up, caches in their steady state
+                    graph.replay()
                 side.synchronize()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(side)
-                graph.replay()
+                for _ in range(5):
+                    graph.replay()
                 e1.record(side)
                 side.synchronize()
-            ms = e0.elapsed_time(e1) / count
+            ms = e0.elapsed_time(e1) / (5 * count)
             moved = n * k * (views[0].element_size() + packed[0].element_size())
             got = packed[2][:64, :64].float().cpu()
             want = views[2][:64, :64].to(narrow or dtype).float().cpu()
@@ -329,7 +331,7 @@ def measure_pack(dev, peaks) -> dict:
         del sources, packed
         torch.cuda.empty_cache()
     return {"workload": "pack of a [14336, 4096] operand from a [K, N]-stored (transpose) or [N, K]-stored (row copy) source", "bound": "hbm",
-            "timing": "12 launches in one CUDA graph, three source/destination sets in rotation", "cases": out}
+            "timing": "a CUDA graph of 12 launches (three source/destination sets in rotation), 20 warm-up replays, 5 timed", "cases": out}
 
 
 def measure_sdpa(dev, port) -> dict:
@@ -359,7 +361,10 @@ def measure_sdpa(dev, port) -> dict:
     keep = (np.arange(length)[None, :] <= pick[:, None]).astype(np.uint8)
     want = port.sdpa_bf16(host[0][pick], host[1], host[2], 1.0 / np.sqrt(d), keep_mask=keep, out_bf16=True)
     got = out[torch.from_numpy(pick).to(dev)].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
-    count = 20
+    count = 50
+    for _ in range(20):  # warm-up
+        run()
+    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(count):
@@ -896,6 +901,19 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_extra(which: str) -> None:
+    """One of the extra measurements alone, on cuda:0."""
+    import torch
+    from oracle.checker import Port
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks, _ = measured_peaks()
+    port = Port()
+    record = {"attention": lambda: measure_sdpa(dev, port), "pack": lambda: measure_pack(dev, peaks),
+              "f16": lambda: measure_f16(50, 5, dev, port, peaks), "quantized": lambda: measure_quantized(50, 5, dev, port, peaks)}[which]()
+    print(json.dumps({"extra": which, **record}), flush=True)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
@@ -906,12 +924,16 @@ def main() -> None:
     parser.add_argument("--gather", choices=["fused", "fused-peer", "nccl"], default="fused",
                         help="how the sharded GEMM's output is gathered: fused = epilogue stores through the NVSwitch multicast address when "
                              "there is one, else to every rank's peer pointer; fused-peer = peer pointers only; nccl = library collective")
+    parser.add_argument("--extra", choices=["attention", "pack", "f16", "quantized"], default=None,
+                        help="run ONLY this one of the extra single-GPU measurements and print its record (for profiling that kernel)")
     parser.add_argument("--no-extra", action="store_true", help="skip the brief measurements of the other single-GPU configurations")
     args = parser.parse_args()
     if args.warmup is not None and args.warmup < 3 and args.impl == "ours":
         args.warmup = 3  # timing rule: at least three warm-up steps
     if args.impl == "reference":
         run_reference(args)
+    elif args.extra:
+        run_extra(args.extra)
     else:
         run_ours(args)
 

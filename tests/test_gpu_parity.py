@@ -1012,7 +1012,7 @@ def test_sdpa_golden_fixtures(golden):
 
 
 @pytest.mark.parametrize("lq,lkv,dqk,dv,causal", [(512, 768, 64, 64, 0), (1024, 1024, 128, 128, 2), (300, 520, 72, 40, 1), (1, 2048, 128, 128, 0),
-                                                    (257, 129, 64, 96, 2)])
+                                                    (257, 129, 64, 96, 2), (40, 9000, 64, 64, 0)])  # the last: rows too long for registers
 def test_sdpa_against_the_checker(port, lq, lkv, dqk, dv, causal):
     # sizes at which both products run on the tensor-core kernels (and ragged ones that do not)
     rng = np.random.default_rng(lq + lkv)

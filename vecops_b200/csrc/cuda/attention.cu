@@ -35,44 +35,79 @@ __device__ __forceinline__ float block_reduce(float value, bool take_max, float*
   return total;
 }
 
-// One CTA per score row.  In place on S like the reference (Common.h:236-345): decorate (s * scale + bias, -inf where
-// not kept) and take the maximum; exponentiate and sum; normalise into the probability type.  Each thread revisits only
-// the elements it wrote itself, so the passes need no barrier beyond the two reductions.
-__global__ void __launch_bounds__(256) sdpa_softmax_kernel(float* __restrict__ scores, long long ld_scores, __nv_bfloat16* __restrict__ probabilities,
-                                                           long long ld_probabilities, int lq, int lkv, float scale,
-                                                           const uint8_t* __restrict__ query_mask, const uint8_t* __restrict__ key_mask,
-                                                           const uint8_t* __restrict__ keep_mask, long long keep_sr, long long keep_sc,
-                                                           const float* __restrict__ bias, long long bias_sr, long long bias_sc, int causal) {
-  __shared__ float scratch[8];
+// One CTA per score row: decorate (s * scale + bias, -inf where not kept) and take the maximum; exponentiate and sum;
+// normalise into the probability type (Common.h:236-345).  kInRegisters: rows of up to 256 x kPerThread scores stay in
+// registers between the passes - one read of S, one write of P; longer rows go through S in place, as the reference
+// does, each thread revisiting only the elements it wrote itself (no barrier beyond the two reductions).
+constexpr int kSoftmaxThreads = 256;
+constexpr int kSoftmaxPerThread = 32;
+
+template <bool kInRegisters>
+__global__ void __launch_bounds__(kSoftmaxThreads) sdpa_softmax_kernel(float* __restrict__ scores, long long ld_scores,
+                                                                       __nv_bfloat16* __restrict__ probabilities, long long ld_probabilities, int lq,
+                                                                       int lkv, float scale, const uint8_t* __restrict__ query_mask,
+                                                                       const uint8_t* __restrict__ key_mask, const uint8_t* __restrict__ keep_mask,
+                                                                       long long keep_sr, long long keep_sc, const float* __restrict__ bias,
+                                                                       long long bias_sr, long long bias_sc, int causal) {
+  __shared__ float scratch[kSoftmaxThreads / 32];
   const float negative_infinity = -INFINITY;
   for (int row = blockIdx.x; row < lq; row += gridDim.x) {
     float* s = scores + row * ld_scores;
     __nv_bfloat16* p = probabilities + row * ld_probabilities;
     const bool query_active = query_mask == nullptr || query_mask[row] != 0;
     const long long last_key = causal == 1 ? row : (causal == 2 ? static_cast<long long>(row) + (lkv - lq) : lkv - 1);
-    float maximum = negative_infinity;
-    for (int j = threadIdx.x; j < lkv; j += blockDim.x) {
+    auto decorated = [&](int j) {
       float value = __fmul_rn(s[j], scale);
       if (bias != nullptr) value = __fadd_rn(value, bias[row * bias_sr + j * bias_sc]);
       const bool keep = query_active && j <= last_key && (key_mask == nullptr || key_mask[j] != 0) &&
                         (keep_mask == nullptr || keep_mask[row * keep_sr + j * keep_sc] != 0);
-      value = keep ? value : negative_infinity;
-      s[j] = value;
-      maximum = fmaxf(maximum, value);
+      return keep ? value : negative_infinity;
+    };
+    float held[kInRegisters ? kSoftmaxPerThread : 1];
+    float maximum = negative_infinity;
+    if constexpr (kInRegisters) {
+#pragma unroll
+      for (int i = 0; i < kSoftmaxPerThread; ++i) {
+        const int j = threadIdx.x + i * kSoftmaxThreads;
+        held[i] = j < lkv ? decorated(j) : negative_infinity;
+        maximum = fmaxf(maximum, held[i]);
+      }
+    } else {
+      for (int j = threadIdx.x; j < lkv; j += kSoftmaxThreads) {
+        const float value = decorated(j);
+        s[j] = value;
+        maximum = fmaxf(maximum, value);
+      }
     }
     maximum = block_reduce(maximum, true, scratch);
     float sum = 0.f;
     if (maximum != negative_infinity) {
-      for (int j = threadIdx.x; j < lkv; j += blockDim.x) {
-        const float e = s[j] == negative_infinity ? 0.f : __expf(s[j] - maximum);
-        s[j] = e;
-        sum += e;
+      if constexpr (kInRegisters) {
+#pragma unroll
+        for (int i = 0; i < kSoftmaxPerThread; ++i) {
+          held[i] = held[i] == negative_infinity ? 0.f : __expf(held[i] - maximum);
+          sum += held[i];
+        }
+      } else {
+        for (int j = threadIdx.x; j < lkv; j += kSoftmaxThreads) {
+          const float e = s[j] == negative_infinity ? 0.f : __expf(s[j] - maximum);
+          s[j] = e;
+          sum += e;
+        }
       }
     }
     sum = block_reduce(sum, false, scratch);
     const bool valid = maximum != negative_infinity && sum > 0.f;  // a row with nothing kept is all zero
     const float reciprocal = valid ? 1.f / sum : 0.f;
-    for (int j = threadIdx.x; j < lkv; j += blockDim.x) p[j] = __float2bfloat16_rn(valid ? s[j] * reciprocal : 0.f);
+    if constexpr (kInRegisters) {
+#pragma unroll
+      for (int i = 0; i < kSoftmaxPerThread; ++i) {
+        const int j = threadIdx.x + i * kSoftmaxThreads;
+        if (j < lkv) p[j] = __float2bfloat16_rn(valid ? held[i] * reciprocal : 0.f);
+      }
+    } else {
+      for (int j = threadIdx.x; j < lkv; j += kSoftmaxThreads) p[j] = __float2bfloat16_rn(valid ? s[j] * reciprocal : 0.f);
+    }
   }
 }
 
@@ -176,8 +211,9 @@ int32_t vecops_b200_sdpa_run(const VecopsB200Attention* attention, VecopsError* 
   if (a.lkv > 0) {
     rc = vecops_b200_matmul_run(&plan.qk, error);  // S = Q.K^T (zeros when Dqk == 0)
     if (rc != VECOPS_STATUS_OK) return rc;
-    const int rows = static_cast<int>(a.lq < 148 * 16 ? a.lq : 148 * 16);
-    sdpa_softmax_kernel<<<rows, 256, 0, stream>>>(reinterpret_cast<float*>(base + plan.scores_at), plan.ld_scores,
+    const int rows = static_cast<int>(a.lq < 148 * 64 ? a.lq : 148 * 64);
+    auto* softmax = a.lkv <= kSoftmaxThreads * kSoftmaxPerThread ? &sdpa_softmax_kernel<true> : &sdpa_softmax_kernel<false>;
+    softmax<<<rows, kSoftmaxThreads, 0, stream>>>(reinterpret_cast<float*>(base + plan.scores_at), plan.ld_scores,
                                                   reinterpret_cast<__nv_bfloat16*>(base + plan.probabilities_at), plan.pitch, static_cast<int>(a.lq),
                                                   static_cast<int>(a.lkv), a.scale, a.query_mask, a.key_mask, a.keep_mask, a.keep_stride_row,
                                                   a.keep_stride_col, a.bias, a.bias_stride_row, a.bias_stride_col, static_cast<int>(a.causal));
