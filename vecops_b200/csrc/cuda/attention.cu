@@ -36,13 +36,16 @@ __device__ __forceinline__ float block_reduce(float value, bool take_max, float*
 }
 
 // One CTA per score row: decorate (s * scale + bias, -inf where not kept) and take the maximum; exponentiate and sum;
-// normalise into the probability type (Common.h:236-345).  kInRegisters: rows of up to 256 x kPerThread scores stay in
-// registers between the passes - one read of S, one write of P; longer rows go through S in place, as the reference
-// does, each thread revisiting only the elements it wrote itself (no barrier beyond the two reductions).
+// normalise into the probability type (Common.h:236-345).
+//
+// kPerThread > 0: rows of up to 256 x kPerThread scores stay in registers between the passes - one 16-byte read of S
+// per four scores, one 8-byte write of P.  The kernel is bound by instruction issue, not by memory, so the count is a
+// template parameter (no dead slots) and kPlain drops the mask and bias handling when none of them was given.
+// kPerThread == 0: rows of any length go through S in place, as the reference does, each thread revisiting only the
+// elements it wrote itself (no barrier beyond the two reductions).
 constexpr int kSoftmaxThreads = 256;
-constexpr int kSoftmaxPerThread = 32;
 
-template <bool kInRegisters>
+template <int kPerThread, bool kPlain>
 __global__ void __launch_bounds__(kSoftmaxThreads) sdpa_softmax_kernel(float* __restrict__ scores, long long ld_scores,
                                                                        __nv_bfloat16* __restrict__ probabilities, long long ld_probabilities, int lq,
                                                                        int lkv, float scale, const uint8_t* __restrict__ query_mask,
@@ -56,59 +59,88 @@ __global__ void __launch_bounds__(kSoftmaxThreads) sdpa_softmax_kernel(float* __
     __nv_bfloat16* p = probabilities + row * ld_probabilities;
     const bool query_active = query_mask == nullptr || query_mask[row] != 0;
     const long long last_key = causal == 1 ? row : (causal == 2 ? static_cast<long long>(row) + (lkv - lq) : lkv - 1);
-    auto decorated = [&](int j) {
-      float value = __fmul_rn(s[j], scale);
+    // keys [0, limit) survive the query mask, the causal cut and the row's end
+    const int limit = !query_active ? 0 : static_cast<int>(last_key + 1 < 0 ? 0 : (last_key + 1 < lkv ? last_key + 1 : lkv));
+    auto decorated = [&](int j, float score) {
+      float value = __fmul_rn(score, scale);
+      if (kPlain || j >= limit) return j < limit ? value : negative_infinity;  // (nothing past `limit` is read: it may lie past the row)
       if (bias != nullptr) value = __fadd_rn(value, bias[row * bias_sr + j * bias_sc]);
-      const bool keep = query_active && j <= last_key && (key_mask == nullptr || key_mask[j] != 0) &&
-                        (keep_mask == nullptr || keep_mask[row * keep_sr + j * keep_sc] != 0);
+      const bool keep = (key_mask == nullptr || key_mask[j] != 0) && (keep_mask == nullptr || keep_mask[row * keep_sr + j * keep_sc] != 0);
       return keep ? value : negative_infinity;
     };
-    float held[kInRegisters ? kSoftmaxPerThread : 1];
+    float held[kPerThread > 0 ? kPerThread : 1];
     float maximum = negative_infinity;
-    if constexpr (kInRegisters) {
+    if constexpr (kPerThread > 0) {
+      // 16-byte loads: the row pitch is a multiple of four floats, so a vector that starts inside the row ends inside the pitch
 #pragma unroll
-      for (int i = 0; i < kSoftmaxPerThread; ++i) {
-        const int j = threadIdx.x + i * kSoftmaxThreads;
-        held[i] = j < lkv ? decorated(j) : negative_infinity;
-        maximum = fmaxf(maximum, held[i]);
+      for (int i = 0; i < kPerThread / 4; ++i) {
+        const int j = 4 * (threadIdx.x + i * kSoftmaxThreads);
+        float4 raw = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (j < lkv) raw = *reinterpret_cast<const float4*>(s + j);
+        const float in[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          held[4 * i + e] = decorated(j + e, in[e]);  // (limit <= Lkv: slots past the row's end are -inf too)
+          maximum = fmaxf(maximum, held[4 * i + e]);
+        }
       }
     } else {
       for (int j = threadIdx.x; j < lkv; j += kSoftmaxThreads) {
-        const float value = decorated(j);
+        const float value = decorated(j, s[j]);
         s[j] = value;
         maximum = fmaxf(maximum, value);
       }
     }
     maximum = block_reduce(maximum, true, scratch);
+    if (maximum == negative_infinity) {  // nothing kept in this row (uniform across the CTA): all zero
+      for (int j = threadIdx.x; j < lkv; j += kSoftmaxThreads) p[j] = __float2bfloat16_rn(0.f);
+      continue;
+    }
     float sum = 0.f;
-    if (maximum != negative_infinity) {
-      if constexpr (kInRegisters) {
+    if constexpr (kPerThread > 0) {
 #pragma unroll
-        for (int i = 0; i < kSoftmaxPerThread; ++i) {
-          held[i] = held[i] == negative_infinity ? 0.f : __expf(held[i] - maximum);
-          sum += held[i];
-        }
-      } else {
-        for (int j = threadIdx.x; j < lkv; j += kSoftmaxThreads) {
-          const float e = s[j] == negative_infinity ? 0.f : __expf(s[j] - maximum);
-          s[j] = e;
-          sum += e;
-        }
+      for (int i = 0; i < kPerThread; ++i) {
+        held[i] = __expf(held[i] - maximum);  // exp(-inf) = 0 for the dropped ones
+        sum += held[i];
+      }
+    } else {
+      for (int j = threadIdx.x; j < lkv; j += kSoftmaxThreads) {
+        const float e = __expf(s[j] - maximum);
+        s[j] = e;
+        sum += e;
       }
     }
     sum = block_reduce(sum, false, scratch);
-    const bool valid = maximum != negative_infinity && sum > 0.f;  // a row with nothing kept is all zero
-    const float reciprocal = valid ? 1.f / sum : 0.f;
-    if constexpr (kInRegisters) {
+    const float reciprocal = sum > 0.f ? 1.f / sum : 0.f;
+    if constexpr (kPerThread > 0) {
+      // 8-byte stores; the probability pitch is a multiple of 64 elements, positions past Lkv inside it get zeros
 #pragma unroll
-      for (int i = 0; i < kSoftmaxPerThread; ++i) {
-        const int j = threadIdx.x + i * kSoftmaxThreads;
-        if (j < lkv) p[j] = __float2bfloat16_rn(valid ? held[i] * reciprocal : 0.f);
+      for (int i = 0; i < kPerThread / 4; ++i) {
+        const int j = 4 * (threadIdx.x + i * kSoftmaxThreads);
+        if (j >= lkv) continue;
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(held[4 * i] * reciprocal, held[4 * i + 1] * reciprocal);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(held[4 * i + 2] * reciprocal, held[4 * i + 3] * reciprocal);
+        uint2 packed;
+        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p + j) = packed;
       }
     } else {
-      for (int j = threadIdx.x; j < lkv; j += kSoftmaxThreads) p[j] = __float2bfloat16_rn(valid ? s[j] * reciprocal : 0.f);
+      for (int j = threadIdx.x; j < lkv; j += kSoftmaxThreads) p[j] = __float2bfloat16_rn(s[j] * reciprocal);
     }
   }
+}
+
+using SoftmaxKernel = void (*)(float*, long long, __nv_bfloat16*, long long, int, int, float, const uint8_t*, const uint8_t*, const uint8_t*, long long,
+                               long long, const float*, long long, long long, int);
+
+template <bool kPlain>
+SoftmaxKernel softmax_for(int64_t lkv) {
+  if (lkv <= kSoftmaxThreads * 4) return &sdpa_softmax_kernel<4, kPlain>;
+  if (lkv <= kSoftmaxThreads * 8) return &sdpa_softmax_kernel<8, kPlain>;
+  if (lkv <= kSoftmaxThreads * 16) return &sdpa_softmax_kernel<16, kPlain>;
+  if (lkv <= kSoftmaxThreads * 32) return &sdpa_softmax_kernel<32, kPlain>;
+  return &sdpa_softmax_kernel<0, kPlain>;
 }
 
 uint64_t round_up(uint64_t value, uint64_t to) { return (value + to - 1) / to * to; }
@@ -212,7 +244,8 @@ int32_t vecops_b200_sdpa_run(const VecopsB200Attention* attention, VecopsError* 
     rc = vecops_b200_matmul_run(&plan.qk, error);  // S = Q.K^T (zeros when Dqk == 0)
     if (rc != VECOPS_STATUS_OK) return rc;
     const int rows = static_cast<int>(a.lq < 148 * 64 ? a.lq : 148 * 64);
-    auto* softmax = a.lkv <= kSoftmaxThreads * kSoftmaxPerThread ? &sdpa_softmax_kernel<true> : &sdpa_softmax_kernel<false>;
+    const bool plain = a.key_mask == nullptr && a.keep_mask == nullptr && a.bias == nullptr;
+    const SoftmaxKernel softmax = plain ? softmax_for<true>(a.lkv) : softmax_for<false>(a.lkv);
     softmax<<<rows, kSoftmaxThreads, 0, stream>>>(reinterpret_cast<float*>(base + plan.scores_at), plan.ld_scores,
                                                   reinterpret_cast<__nv_bfloat16*>(base + plan.probabilities_at), plan.pitch, static_cast<int>(a.lq),
                                                   static_cast<int>(a.lkv), a.scale, a.query_mask, a.key_mask, a.keep_mask, a.keep_stride_row,
