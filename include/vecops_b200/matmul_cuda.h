@@ -339,6 +339,12 @@ typedef struct VecopsB200Attention {
   void* stream;
   int32_t device_index;
   uint32_t reserved;
+  /* Several heads in one call: head h reads q + h*q_stride_head (elements) and so on; a stride of 0 shares the operand
+   * between heads (grouped-query K and V, one mask for all).  heads <= 1 means one head and the strides are ignored.
+   * The heads run one after the other on the stream and share the scratch, which is sized for one head. */
+  int64_t heads;
+  int64_t q_stride_head, k_stride_head, v_stride_head, out_stride_head;
+  int64_t query_mask_stride_head, key_mask_stride_head, keep_stride_head, bias_stride_head;
 } VecopsB200Attention;
 
 VECOPS_B200_EXPORT int32_t vecops_b200_sdpa_workspace(const VecopsB200Attention* attention, uint64_t* bytes, VecopsError* error);

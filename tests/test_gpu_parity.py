@@ -1049,3 +1049,29 @@ def test_sdpa_degenerate_extents_and_refusals():
     record = harness.sdpa_record(q, q, q, out, 1.0)
     error = capi.ErrorBuffer()
     assert capi.library().vecops_b200_sdpa_run(byref(record), byref(error.record)) == capi.INVALID_ARGUMENT  # no scratch given
+
+
+def test_sdpa_heads_in_one_call(port):
+    # [heads, L, D] operands; K and V shared by pairs of heads (grouped-query: head stride via expanded views), one mask for all
+    rng = np.random.default_rng(77)
+    heads, lq, lkv, d = 4, 96, 160, 64
+    qh = f32_to_bf16_bits(rng.standard_normal((heads, lq, d)).astype(np.float32))
+    kh = f32_to_bf16_bits(rng.standard_normal((heads // 2, lkv, d)).astype(np.float32))
+    vh = f32_to_bf16_bits(rng.standard_normal((heads // 2, lkv, d)).astype(np.float32))
+    key_mask = (rng.random(lkv) > 0.2).astype(np.uint8)
+    bias = rng.uniform(-1, 1, (heads, lq, lkv)).astype(np.float32)
+    q = to_device(qh, bf16=True)
+    k = to_device(kh, bf16=True).repeat_interleave(2, dim=0)       # heads 0,1 -> group 0; heads 2,3 -> group 1
+    v = to_device(vh, bf16=True).repeat_interleave(2, dim=0)
+    out = torch.full((heads, lq, d), -99, dtype=torch.float32, device="cuda")
+    harness.sdpa(q, k, v, out, 0.125, key_mask=to_device(key_mask), bias=to_device(bias), causal=capi.CAUSAL_BOTTOM_RIGHT)
+    torch.cuda.synchronize()
+    for h in range(heads):
+        want = port.sdpa_bf16(qh[h], kh[h // 2], vh[h // 2], 0.125, key_mask=key_mask, bias=bias[h], causal=2)
+        assert rel_frobenius(out[h].cpu().numpy(), want) <= TOL_BF16, h
+    # a head stride of 0 shares K and V between all heads
+    shared_k, shared_v = to_device(kh[:1], bf16=True).expand(heads, lkv, d), to_device(vh[:1], bf16=True).expand(heads, lkv, d)
+    harness.sdpa(q, shared_k, shared_v, out, 0.125)
+    torch.cuda.synchronize()
+    for h in (0, heads - 1):
+        assert rel_frobenius(out[h].cpu().numpy(), port.sdpa_bf16(qh[h], kh[0], vh[0], 0.125)) <= TOL_BF16, h

@@ -219,10 +219,37 @@ int32_t vecops_b200_sdpa_workspace(const VecopsB200Attention* attention, uint64_
   return rc;
 }
 
+static int32_t sdpa_run_one(const VecopsB200Attention& a, VecopsError* error);
+
 int32_t vecops_b200_sdpa_run(const VecopsB200Attention* attention, VecopsError* error) {
   if (attention == nullptr || attention->struct_size < sizeof(VecopsB200Attention))
     return set_error(error, VECOPS_STATUS_ABI_MISMATCH, "attention record is null or too small");
-  const VecopsB200Attention& a = *attention;
+  if (attention->heads <= 1) return sdpa_run_one(*attention, error);
+  // one head after the other on the stream, sharing the scratch; only the last one synchronises (when the caller wants that)
+  for (int64_t h = 0; h < attention->heads; ++h) {
+    VecopsB200Attention head = *attention;
+    head.heads = 1;
+    auto at = [h](const void* base, int64_t stride, size_t elem) -> const void* {
+      return base == nullptr ? nullptr : static_cast<const char*>(base) + h * stride * static_cast<int64_t>(elem);
+    };
+    head.q = at(attention->q, attention->q_stride_head, 2);
+    head.k = at(attention->k, attention->k_stride_head, 2);
+    head.v = at(attention->v, attention->v_stride_head, 2);
+    head.out = const_cast<void*>(at(attention->out, attention->out_stride_head, attention->out_dtype == VECOPS_DTYPE_F32 ? 4 : 2));
+    head.query_mask = static_cast<const uint8_t*>(at(attention->query_mask, attention->query_mask_stride_head, 1));
+    head.key_mask = static_cast<const uint8_t*>(at(attention->key_mask, attention->key_mask_stride_head, 1));
+    head.keep_mask = static_cast<const uint8_t*>(at(attention->keep_mask, attention->keep_stride_head, 1));
+    head.bias = static_cast<const float*>(at(attention->bias, attention->bias_stride_head, 4));
+    if (h + 1 < attention->heads) head.flags |= VECOPS_B200_MATMUL_FLAG_ASYNC;
+    const int32_t rc = sdpa_run_one(head, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+  }
+  return VECOPS_STATUS_OK;
+}
+
+}  // extern "C"
+
+static int32_t sdpa_run_one(const VecopsB200Attention& a, VecopsError* error) {
   Plan plan;
   int32_t rc = plan_of(a, static_cast<char*>(a.workspace), &plan, error);
   if (rc != VECOPS_STATUS_OK) return rc;
@@ -268,5 +295,3 @@ int32_t vecops_b200_sdpa_run(const VecopsB200Attention* attention, VecopsError* 
   }
   return vecops_b200_matmul_run(&plan.pv, error);  // O = P.V (zeros when Lkv == 0); synchronises unless the caller asked not to
 }
-
-}  // extern "C"

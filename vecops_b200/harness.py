@@ -193,11 +193,23 @@ def pack_operand(view, dtype=None, operand: int = 1, zero_point: int | None = No
 
 def sdpa_record(q, k, v, out, scale: float, query_mask=None, key_mask=None, keep_mask=None, bias=None, causal: int = 0, stream=None,
                 asynchronous: bool = False) -> capi.VecopsB200Attention:
-    """Describe one head of scaled dot-product attention: q [Lq,Dqk], k [Lkv,Dqk], v [Lkv,Dv] bf16, out [Lq,Dv] f32 or bf16;
-    masks uint8 / bool tensors (non-zero keeps), bias float32 [Lq,Lkv]."""
+    """Describe scaled dot-product attention: q [Lq,Dqk], k [Lkv,Dqk], v [Lkv,Dv] bf16, out [Lq,Dv] f32 or bf16; masks
+    uint8 / bool tensors (non-zero keeps), bias float32 [Lq,Lkv].  With a leading head axis on q, k, v and out (and
+    optionally on the masks and the bias) the heads run one after the other; `.expand`ed views share an operand."""
     a = capi.VecopsB200Attention()
     a.struct_size = ctypes.sizeof(capi.VecopsB200Attention)
     a.causal = causal
+    if q.dim() == 3:  # [heads, L, D]; expanded views (head stride 0) share an operand between heads
+        a.heads = out.shape[0]
+        a.q_stride_head, a.k_stride_head, a.v_stride_head, a.out_stride_head = q.stride(0), k.stride(0), v.stride(0), out.stride(0)
+        for name, tensor in (("query_mask", query_mask), ("key_mask", key_mask), ("keep", keep_mask), ("bias", bias)):
+            if tensor is not None and tensor.dim() == (3 if name in ("keep", "bias") else 2):
+                setattr(a, f"{name}_stride_head", tensor.stride(0))
+        q, k, v, out = q[0], k[0], v[0], out[0]
+        query_mask = query_mask[0] if query_mask is not None and query_mask.dim() == 2 else query_mask
+        key_mask = key_mask[0] if key_mask is not None and key_mask.dim() == 2 else key_mask
+        keep_mask = keep_mask[0] if keep_mask is not None and keep_mask.dim() == 3 else keep_mask
+        bias = bias[0] if bias is not None and bias.dim() == 3 else bias
     a.lq, a.dqk = q.shape
     a.lkv, a.dv = v.shape
     if tuple(k.shape) != (a.lkv, a.dqk) or tuple(out.shape) != (a.lq, a.dv):
