@@ -17,7 +17,8 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-REFERENCE_ROOT = Path(os.environ.get("VECOPS_REFERENCE_ROOT", "/root/reference"))
+# the reference checkout: $VECOPS_REFERENCE_ROOT, else a directory named "reference" beside this repository
+REFERENCE_ROOT = Path(os.environ.get("VECOPS_REFERENCE_ROOT", str(HERE.parent.parent / "reference")))
 PORT_LIB = HERE / "liboracle.so"
 REF_DIR = HERE / "_ref"
 REF_LIB = REF_DIR / "libvecops_ref.so"
