@@ -184,7 +184,7 @@ def test_w8_tcgen05_refuses_a_missing_workspace():
     assert info.value.code == capi.INVALID_ARGUMENT and "workspace" in info.value.message
 
 
-@pytest.mark.parametrize("m,n,k", [(64, 64, 64), (200, 300, 100), (130, 70, 45), (1, 1000, 333), (1024, 1024, 1024)])
+@pytest.mark.parametrize("m,n,k", [(64, 64, 64), (200, 300, 100), (130, 70, 45), (1, 1000, 333), (1024, 1024, 1024), (128, 192, 48), (64, 64, 16)])
 @pytest.mark.parametrize("b_kn", [True, False])
 def test_f32_simt(port, m, n, k, b_kn):
     rng = np.random.default_rng(m + 2 * n + 3 * k)
@@ -1075,3 +1075,22 @@ def test_sdpa_heads_in_one_call(port):
     torch.cuda.synchronize()
     for h in (0, heads - 1):
         assert rel_frobenius(out[h].cpu().numpy(), port.sdpa_bf16(qh[h], kh[0], vh[0], 0.125)) <= TOL_BF16, h
+
+
+
+@pytest.mark.parametrize("b_kn", [True, False])
+def test_f32_whole_tile_form_agrees_with_the_general_kernel(port, b_kn, monkeypatch):
+    # shapes made of whole 64 x 64 x 16 tiles run on the 8 x 8-per-thread kernel; the switch keeps the general one
+    from oracle.checker import ACT_SILU
+    rng = np.random.default_rng(12)
+    a, b, _ = inputs("f32", 192, 256, 80, rng)
+    want = port.matmul_f32(a, b)
+    fast = run_case("f32", a, b, kernel=K.KERNEL_F32_SIMT, b_kn=b_kn)
+    monkeypatch.setenv("VECOPS_B200_F32_TILE8", "0")
+    general = run_case("f32", a, b, kernel=K.KERNEL_F32_SIMT, b_kn=b_kn)
+    monkeypatch.delenv("VECOPS_B200_F32_TILE8")
+    assert rel_frobenius(fast, want) <= TOL_F32 and rel_frobenius(general, want) <= TOL_F32
+    assert rel_frobenius(fast, general) <= 1e-6  # the same fp32 FMAs in the same k order
+    bias = rng.uniform(-1, 1, 256).astype(np.float32)
+    got = _fused_gpu("f32", a, b, torch.float32, K.KERNEL_F32_SIMT, cin=bias, act=ACT_SILU, alpha=0.25)
+    assert rel_frobenius(got, port.matmul_f32_fused(a, b, bias, 0.25, None, ACT_SILU)) <= 1e-5

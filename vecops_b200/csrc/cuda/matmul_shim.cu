@@ -814,6 +814,28 @@ int32_t launch_w8_tcgen05_typed(const VecopsB200Matmul& p, const DeviceState& de
 int32_t launch_f32(const VecopsB200Matmul& p, cudaStream_t stream, VecopsError* error) {
   if ((p.m + 63) / 64 > 65535) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "M too large for f32_simt");
   dim3 grid(static_cast<unsigned>((p.n + 63) / 64), static_cast<unsigned>((p.m + 63) / 64));
+  // whole tiles and 16-byte aligned rows: the 8 x 8-per-thread form (VECOPS_B200_F32_TILE8=0 keeps the general kernel)
+  const char* tile8_switch = getenv("VECOPS_B200_F32_TILE8");
+  const bool b_k_contig = p.b_stride_k == 1, b_n_contig = p.b_stride_n == 1;
+  const int64_t ldb = b_k_contig ? p.b_stride_n : p.b_stride_k;
+  const bool tile8 = !(tile8_switch != nullptr && tile8_switch[0] == '0') && p.m % 64 == 0 && p.n % 64 == 0 && p.k % 16 == 0 && p.k > 0 &&
+                     p.a_stride_k == 1 && p.c_stride_n == 1 && (b_k_contig || b_n_contig) && p.a_stride_m % 4 == 0 && ldb % 4 == 0 &&
+                     p.c_stride_m % 4 == 0 && aligned16(p.a) && aligned16(p.b) && aligned16(p.c);
+  if (tile8) {
+    // 8 x 8 outputs per thread (64 threads); VECOPS_B200_F32_TILE8=4 selects 4 x 8 per thread (128 threads), measured 10 % slower
+    // at 1024^3 (88 vs 80 us; the general kernel 92 us)
+    const bool eight = !(tile8_switch != nullptr && tile8_switch[0] == '4');
+    const float* pa = static_cast<const float*>(p.a);
+    const float* pb = static_cast<const float*>(p.b);
+    float* pc = static_cast<float*>(p.c);
+    const int k = static_cast<int>(p.k);
+    if (eight && b_k_contig) gemm_f32_tile8_kernel<true, 8><<<grid, 64, 0, stream>>>(pa, p.a_stride_m, pb, ldb, pc, p.c_stride_m, k, tl_epilogue);
+    else if (eight) gemm_f32_tile8_kernel<false, 8><<<grid, 64, 0, stream>>>(pa, p.a_stride_m, pb, ldb, pc, p.c_stride_m, k, tl_epilogue);
+    else if (b_k_contig) gemm_f32_tile8_kernel<true, 4><<<grid, 128, 0, stream>>>(pa, p.a_stride_m, pb, ldb, pc, p.c_stride_m, k, tl_epilogue);
+    else gemm_f32_tile8_kernel<false, 4><<<grid, 128, 0, stream>>>(pa, p.a_stride_m, pb, ldb, pc, p.c_stride_m, k, tl_epilogue);
+    g_launches.fetch_add(1);
+    return VECOPS_STATUS_OK;
+  }
   gemm_f32_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(p.a), p.a_stride_m, static_cast<const float*>(p.b), p.b_stride_n,
                                             p.b_stride_k, static_cast<float*>(p.c), p.c_stride_m, static_cast<int>(p.m),
                                             static_cast<int>(p.n), static_cast<int>(p.k), tl_epilogue);

@@ -223,6 +223,102 @@ gemm_f32_kernel(const float* __restrict__ a, long long lda, const float* __restr
   }
 }
 
+// The same product for shapes made of whole tiles with 16-byte aligned rows (C1 is one): a 64 x 64 x 16 tile per CTA of
+// 64 threads, 8 x 8 outputs per thread held as four 4 x 4 quadrants 32 rows / columns apart (so that a warp's 16-byte
+// shared-memory reads fall on consecutive words), 16-byte global loads prefetched into registers one k-tile ahead, two
+// shared buffers, one barrier per k-tile.  64 independent accumulators per thread keep the FMA pipe busy from a single
+// warp per scheduler, which is all a 1024^3 problem gives 148 SMs.  Every product and sum is still an fp32 FMA.
+// kBKContig: B rows are K-contiguous ([N,K] storage); otherwise N-contiguous ([K,N] storage, C1's layout).
+template <bool kBKContig, int kRowsPerThread>
+__global__ void __launch_bounds__(512 / kRowsPerThread)
+gemm_f32_tile8_kernel(const float* __restrict__ a, long long lda, const float* __restrict__ b, long long ldb, float* __restrict__ c,
+                      long long ldc, int K, EpilogueArgs ep) {
+  // kRowsPerThread 8: 64 threads, 8 x 8 outputs each (rows 4ty.. and 32+4ty..); 4: 128 threads, 4 x 8 outputs each (rows 4ty..)
+  constexpr int kTile = 64, kDepth = 16, kPitch = kTile + 4, kThreads = 512 / kRowsPerThread;
+  constexpr int kLoads = 256 / kThreads;  // 16-byte pieces of each operand tile per thread
+  __shared__ __align__(16) float as[2][kDepth][kPitch];
+  __shared__ __align__(16) float bs[2][kDepth][kPitch];
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * kTile, n0 = blockIdx.x * kTile;
+  const int tx = tid & 7, ty = tid >> 3;
+
+  float acc[kRowsPerThread][8];
+#pragma unroll
+  for (int i = 0; i < kRowsPerThread; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+  float4 ra[kLoads], rb[kLoads];
+  // A (and a K-contiguous B): a thread owns row (t mod 64) of the tile and kLoads of its four 16-byte pieces along k
+  const int row = tid & 63, first_piece = (tid >> 6) * kLoads;
+  const float* a_row = a + static_cast<long long>(m0 + row) * lda + 4 * first_piece;
+  const float* b_row = kBKContig ? b + static_cast<long long>(n0 + row) * ldb + 4 * first_piece : b + n0 + 4 * (tid & 15);
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int q = 0; q < kLoads; ++q) {
+      ra[q] = __ldg(reinterpret_cast<const float4*>(a_row + k0 + 4 * q));
+      if (kBKContig) rb[q] = __ldg(reinterpret_cast<const float4*>(b_row + k0 + 4 * q));
+      else rb[q] = __ldg(reinterpret_cast<const float4*>(b_row + static_cast<long long>(k0 + (tid >> 4) + (kThreads / 16) * q) * ldb));
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int q = 0; q < kLoads; ++q) {
+      const int k4 = 4 * (first_piece + q);
+      as[buf][k4 + 0][row] = ra[q].x, as[buf][k4 + 1][row] = ra[q].y, as[buf][k4 + 2][row] = ra[q].z, as[buf][k4 + 3][row] = ra[q].w;
+      if (kBKContig) {
+        bs[buf][k4 + 0][row] = rb[q].x, bs[buf][k4 + 1][row] = rb[q].y, bs[buf][k4 + 2][row] = rb[q].z, bs[buf][k4 + 3][row] = rb[q].w;
+      } else {
+        *reinterpret_cast<float4*>(&bs[buf][(tid >> 4) + (kThreads / 16) * q][4 * (tid & 15)]) = rb[q];
+      }
+    }
+  };
+
+  const int num_kb = K / kDepth;
+  if (num_kb > 0) {
+    fetch(0);
+    stash(0);
+  }
+  __syncthreads();
+  for (int kb = 0; kb < num_kb; ++kb) {
+    const int buf = kb & 1;
+    if (kb + 1 < num_kb) fetch((kb + 1) * kDepth);
+#pragma unroll
+    for (int kk = 0; kk < kDepth; ++kk) {
+      float av[kRowsPerThread];
+      const float4 a_lo = *reinterpret_cast<const float4*>(&as[buf][kk][4 * ty]);
+      av[0] = a_lo.x, av[1] = a_lo.y, av[2] = a_lo.z, av[3] = a_lo.w;
+      if constexpr (kRowsPerThread == 8) {
+        const float4 a_hi = *reinterpret_cast<const float4*>(&as[buf][kk][32 + 4 * ty]);
+        av[4] = a_hi.x, av[5] = a_hi.y, av[6] = a_hi.z, av[7] = a_hi.w;
+      }
+      const float4 b_lo = *reinterpret_cast<const float4*>(&bs[buf][kk][4 * tx]);
+      const float4 b_hi = *reinterpret_cast<const float4*>(&bs[buf][kk][32 + 4 * tx]);
+      const float bv[8] = {b_lo.x, b_lo.y, b_lo.z, b_lo.w, b_hi.x, b_hi.y, b_hi.z, b_hi.w};
+#pragma unroll
+      for (int i = 0; i < kRowsPerThread; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    if (kb + 1 < num_kb) stash(buf ^ 1);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < kRowsPerThread; ++i) {
+    const int m = m0 + (i < 4 ? 4 * ty + i : 32 + 4 * ty + i - 4);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int n = n0 + 32 * half + 4 * tx;
+      float out[4] = {acc[i][4 * half], acc[i][4 * half + 1], acc[i][4 * half + 2], acc[i][4 * half + 3]};
+      if (ep.active) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) out[j] = epilogue_float(out[j], ep, m, n + j, 1.f);
+      }
+      *reinterpret_cast<float4*>(c + static_cast<long long>(m) * ldc + n) = make_float4(out[0], out[1], out[2], out[3]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ quantise-on-load helpers
 
 // dst[m,k] = convert(src[m,k] * scale + zero_point): truncation toward zero, saturating to the 8-bit range, as vecops
