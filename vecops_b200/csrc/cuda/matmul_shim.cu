@@ -828,11 +828,48 @@ int32_t launch_f32(const VecopsB200Matmul& p, cudaStream_t stream, VecopsError* 
     const float* pa = static_cast<const float*>(p.a);
     const float* pb = static_cast<const float*>(p.b);
     float* pc = static_cast<float*>(p.c);
-    const int k = static_cast<int>(p.k);
-    if (eight && b_k_contig) gemm_f32_tile8_kernel<true, 8><<<grid, 64, 0, stream>>>(pa, p.a_stride_m, pb, ldb, pc, p.c_stride_m, k, tl_epilogue);
-    else if (eight) gemm_f32_tile8_kernel<false, 8><<<grid, 64, 0, stream>>>(pa, p.a_stride_m, pb, ldb, pc, p.c_stride_m, k, tl_epilogue);
-    else if (b_k_contig) gemm_f32_tile8_kernel<true, 4><<<grid, 128, 0, stream>>>(pa, p.a_stride_m, pb, ldb, pc, p.c_stride_m, k, tl_epilogue);
-    else gemm_f32_tile8_kernel<false, 4><<<grid, 128, 0, stream>>>(pa, p.a_stride_m, pb, ldb, pc, p.c_stride_m, k, tl_epilogue);
+    const long long lda = p.a_stride_m, ldb_arg = ldb, ldc = p.c_stride_m;
+    int k = static_cast<int>(p.k);
+    EpilogueArgs epilogue = tl_epilogue;
+    // Too few tiles for the SMs: clusters of 2 or 4 CTAs share a tile along K (VECOPS_B200_F32_SPLIT=1|2|4 forces the count)
+    int device = 0, sms = 148;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const long long tiles = static_cast<long long>(grid.x) * grid.y;
+    int split = 1;
+    if (eight) {
+      // measured at 1024^3 on one box: whole 94 us, pairs 72 us, clusters of four 107 us (three serial remote reads per sum
+      // and four CTAs to co-schedule cost more than the extra warps give) - so pairs, and four only when forced
+      if (tiles * 2 <= 8LL * sms && p.k % 32 == 0 && p.k >= 128) split = 2;
+      if (const char* forced = getenv("VECOPS_B200_F32_SPLIT")) {
+        const int want = atoi(forced);
+        if ((want == 1 || want == 2 || want == 4) && p.k % (16 * want) == 0) split = want;
+      }
+    }
+    if (!eight) {
+      if (b_k_contig) gemm_f32_tile8_kernel<true, 4, 1><<<grid, 128, 0, stream>>>(pa, lda, pb, ldb_arg, pc, ldc, k, epilogue);
+      else gemm_f32_tile8_kernel<false, 4, 1><<<grid, 128, 0, stream>>>(pa, lda, pb, ldb_arg, pc, ldc, k, epilogue);
+    } else {
+      const void* kernel = nullptr;
+      if (split == 4) kernel = b_k_contig ? reinterpret_cast<const void*>(gemm_f32_tile8_kernel<true, 8, 4>) : reinterpret_cast<const void*>(gemm_f32_tile8_kernel<false, 8, 4>);
+      else if (split == 2) kernel = b_k_contig ? reinterpret_cast<const void*>(gemm_f32_tile8_kernel<true, 8, 2>) : reinterpret_cast<const void*>(gemm_f32_tile8_kernel<false, 8, 2>);
+      else kernel = b_k_contig ? reinterpret_cast<const void*>(gemm_f32_tile8_kernel<true, 8, 1>) : reinterpret_cast<const void*>(gemm_f32_tile8_kernel<false, 8, 1>);
+      cudaLaunchConfig_t config{};
+      config.gridDim = dim3(grid.x, grid.y, static_cast<unsigned>(split));
+      config.blockDim = dim3(64, 1, 1);
+      config.dynamicSmemBytes = 0;
+      config.stream = stream;
+      cudaLaunchAttribute attribute{};
+      attribute.id = cudaLaunchAttributeClusterDimension;
+      attribute.val.clusterDim.x = 1;
+      attribute.val.clusterDim.y = 1;
+      attribute.val.clusterDim.z = static_cast<unsigned>(split);
+      config.attrs = &attribute;
+      config.numAttrs = split > 1 ? 1 : 0;
+      void* args[] = {&pa, const_cast<long long*>(&lda), &pb, const_cast<long long*>(&ldb_arg), &pc, const_cast<long long*>(&ldc), &k, &epilogue};
+      const cudaError_t launched = cudaLaunchKernelExC(&config, kernel, args);
+      if (launched != cudaSuccess) return cuda_fail(error, launched, "launch of f32_simt (whole-tile form)");
+    }
     g_launches.fetch_add(1);
     return VECOPS_STATUS_OK;
   }

@@ -149,6 +149,13 @@ __device__ __forceinline__ void cluster_sync_all() {
                "barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// Read one float from another CTA's shared memory (`cluster_addr` from map_to_cta).
+__device__ __forceinline__ float ld_shared_cluster_f32(uint32_t cluster_addr) {
+  float value;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(cluster_addr) : "memory");
+  return value;
+}
+
 // Arrive on a barrier that may live in the peer CTA (`cluster_addr` from map_to_cta).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");

@@ -3,6 +3,7 @@
 #pragma once
 
 #include "epilogue.cuh"
+#include "ptx.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -229,18 +230,25 @@ gemm_f32_kernel(const float* __restrict__ a, long long lda, const float* __restr
 // shared buffers, one barrier per k-tile.  64 independent accumulators per thread keep the FMA pipe busy from a single
 // warp per scheduler, which is all a 1024^3 problem gives 148 SMs.  Every product and sum is still an fp32 FMA.
 // kBKContig: B rows are K-contiguous ([N,K] storage); otherwise N-contiguous ([K,N] storage, C1's layout).
-template <bool kBKContig, int kRowsPerThread>
+// kSplit > 1: the kernel is launched as thread-block clusters of kSplit CTAs along z, CTA r of a cluster sums the r-th
+// part of K; the others park their sums in their own shared memory and CTA 0 reads them through distributed shared
+// memory, adds them in rank order (the same order every run) and stores.  That multiplies the resident warps of a
+// problem too small to fill the SMs with 64 x 64 tiles.
+template <bool kBKContig, int kRowsPerThread, int kSplit>
 __global__ void __launch_bounds__(512 / kRowsPerThread)
 gemm_f32_tile8_kernel(const float* __restrict__ a, long long lda, const float* __restrict__ b, long long ldb, float* __restrict__ c,
                       long long ldc, int K, EpilogueArgs ep) {
   // kRowsPerThread 8: 64 threads, 8 x 8 outputs each (rows 4ty.. and 32+4ty..); 4: 128 threads, 4 x 8 outputs each (rows 4ty..)
   constexpr int kTile = 64, kDepth = 16, kPitch = kTile + 4, kThreads = 512 / kRowsPerThread;
   constexpr int kLoads = 256 / kThreads;  // 16-byte pieces of each operand tile per thread
-  __shared__ __align__(16) float as[2][kDepth][kPitch];
-  __shared__ __align__(16) float bs[2][kDepth][kPitch];
+  __shared__ __align__(16) float staging[2 * 2 * kDepth * kPitch];  // as[2][16][68] then bs[2][16][68]; 4096 sums fit for the exchange
+  float (*as)[kDepth][kPitch] = reinterpret_cast<float (*)[kDepth][kPitch]>(staging);
+  float (*bs)[kDepth][kPitch] = reinterpret_cast<float (*)[kDepth][kPitch]>(staging + 2 * kDepth * kPitch);
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * kTile, n0 = blockIdx.x * kTile;
   const int tx = tid & 7, ty = tid >> 3;
+  const int rank = kSplit > 1 ? static_cast<int>(cluster_cta_rank()) : 0;
+  const int k_begin = rank * (K / kSplit);  // K is a multiple of 16 * kSplit
 
   float acc[kRowsPerThread][8];
 #pragma unroll
@@ -274,15 +282,15 @@ gemm_f32_tile8_kernel(const float* __restrict__ a, long long lda, const float* _
     }
   };
 
-  const int num_kb = K / kDepth;
+  const int num_kb = K / kSplit / kDepth;
   if (num_kb > 0) {
-    fetch(0);
+    fetch(k_begin);
     stash(0);
   }
   __syncthreads();
   for (int kb = 0; kb < num_kb; ++kb) {
     const int buf = kb & 1;
-    if (kb + 1 < num_kb) fetch((kb + 1) * kDepth);
+    if (kb + 1 < num_kb) fetch(k_begin + (kb + 1) * kDepth);
 #pragma unroll
     for (int kk = 0; kk < kDepth; ++kk) {
       float av[kRowsPerThread];
@@ -302,6 +310,28 @@ gemm_f32_tile8_kernel(const float* __restrict__ a, long long lda, const float* _
     }
     if (kb + 1 < num_kb) stash(buf ^ 1);
     __syncthreads();
+  }
+  if constexpr (kSplit > 1) {
+    // (the loop's last barrier is behind every thread: the operand tiles are dead, the buffer is free)
+    if (rank != 0) {
+#pragma unroll
+      for (int i = 0; i < kRowsPerThread; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) staging[(i * 8 + j) * kThreads + tid] = acc[i][j];
+    }
+    cluster_sync_all();  // the parked sums are visible cluster-wide
+    if (rank == 0) {
+      const uint32_t mine = static_cast<uint32_t>(__cvta_generic_to_shared(staging));
+      for (int r = 1; r < kSplit; ++r) {
+        const uint32_t theirs = map_to_cta(mine, static_cast<uint32_t>(r));
+#pragma unroll
+        for (int i = 0; i < kRowsPerThread; ++i)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[i][j] += ld_shared_cluster_f32(theirs + 4u * static_cast<uint32_t>((i * 8 + j) * kThreads + tid));
+      }
+    }
+    cluster_sync_all();  // nobody leaves while CTA 0 may still read its shared memory
+    if (rank != 0) return;
   }
 #pragma unroll
   for (int i = 0; i < kRowsPerThread; ++i) {
