@@ -100,7 +100,7 @@ VECOPS_B200_EXPORT int32_t vecops_b200_matmul_workspace(const VecopsB200Matmul* 
  * legal: K == 0 stores zeros (ops/Matmul.h:41-43). */
 VECOPS_B200_EXPORT int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* error);
 
-/* Fused form: COut = convert( activation( (CIn + A . B^T) * alpha * column_scale[n] ) ).
+/* Fused form: COut = convert( activation( (CIn + A . B^T) * alpha * row_scale[m] * column_scale[n] ) ).
  *
  * vecops writes this as the explicit accumulate form `COutput = CInput + A*B^T` (include/vecops/ops/Matmul.h:519-570)
  * with an output transform composed from vec primitives; the compositions its fusion tests use
@@ -130,6 +130,11 @@ typedef struct VecopsB200Epilogue {
   float alpha;          /* factor on the accumulator, 1 = none */
   float clamp_lo, clamp_hi;
   uint32_t reserved;
+  /* Appended (read only when struct_size covers it): an optional f32 factor per OUTPUT ROW, row_scale[m] - with
+   * column_scale the row-by-column dequantisation of vecops' per-token quantised matmul, value * row_scales[row] *
+   * column_scales[col] (include/vecops/matmul/Quantization.h:195-246; tests/ops/MatmulConversionTestCommon.h:1384-1436).
+   * Not for the plain int32 row.  In a batched call over stacked rows the index is the stacked row. */
+  const float* row_scale;
 } VecopsB200Epilogue;
 
 VECOPS_B200_EXPORT int32_t vecops_b200_matmul_run_fused(const VecopsB200Matmul* problem, const VecopsB200Epilogue* epilogue,
@@ -249,6 +254,14 @@ VECOPS_B200_EXPORT int32_t vecops_b200_matmul_allgather_run(const VecopsB200Matm
 VECOPS_B200_EXPORT int32_t vecops_b200_quantize_rows(const void* src, uint32_t src_dtype, int64_t src_stride_m, int64_t src_stride_k,
                                                      void* dst, uint32_t dst_dtype, int64_t dst_stride_m, int64_t rows, int64_t cols,
                                                      float scale, float zero_point, void* stream, VecopsError* error);
+
+/* The same with one multiplier per row in place of `scale`: dst[m,k] = convert(src[m,k] * multipliers[m] + zero_point) - vecops'
+ * per-row asymmetric quantisation of the activations (include/vecops/matmul/Quantization.h:76-140,
+ * make_runtime_per_row_asymmetric_quantize_transform), whose counterpart on the output side is VecopsB200Epilogue::row_scale. */
+VECOPS_B200_EXPORT int32_t vecops_b200_quantize_rows_per_row(const void* src, uint32_t src_dtype, int64_t src_stride_m,
+                                                             int64_t src_stride_k, void* dst, uint32_t dst_dtype, int64_t dst_stride_m,
+                                                             int64_t rows, int64_t cols, const float* multipliers, float zero_point,
+                                                             void* stream, VecopsError* error);
 
 /* out[n] = -zero_point * sum_k B[n,k] for an 8-bit K-contiguous B[N,K]: the int32 accumulator-input row (stride_m = 0) that
  * removes the activations' zero point from an asymmetric product (MatmulConversionTestCommon.h:529-541; the compensation

@@ -139,6 +139,9 @@ class Port:
         self.lib.oracle_matmul_f16_fused.argtypes = [_I64] * 3 + [_P, _I64, _I64, _P, _I64, _I64, _P, _I64, _I64, _F, _P, c_int, _F, _F, _P,
                                                                  _I64, _I64, c_int]
         self.lib.oracle_sdpa_bf16.argtypes = [_I64] * 4 + [_P, _I64, _P, _I64, _P, _I64, _P, _P, _P, _I64, _P, _I64, c_int, _F, _P, _I64, c_int]
+        self.lib.oracle_quantize_rows_per_row.argtypes = [_I64, _I64, _P, _I64, _I64, _P, _F, _P, _I64, _I64, c_int]
+        self.lib.oracle_matmul_i8_dequant_rows.argtypes = [_I64] * 3 + [_P, _I64, _I64, c_int, _P, _I64, _I64, c_int, _P, _I64, _I64, _P, _P, _P,
+                                                                       _I64, _I64, c_int]
         self.lib.oracle_quantize_rows.argtypes = [_I64, _I64, _P, _I64, _I64, _F, _F, _P, _I64, _I64, c_int]
         self.lib.oracle_matmul_i8_dequant.argtypes = [_I64] * 3 + [_P, _I64, _I64, c_int, _P, _I64, _I64, c_int, _P, _I64, _I64, _F, _P, c_int,
                                                                   _F, _F, _P, _I64, _I64, c_int]
@@ -260,6 +263,26 @@ class Port:
         self.lib.oracle_quantize_rows(m, k, _ptr(a_f32), *_strides(a_f32), float(scale), float(zero_point), _ptr(out), k, 1, int(signed))
         return out
 
+    def quantize_rows_per_row(self, a_f32, multipliers, zero_point, signed=False):
+        m, k = a_f32.shape
+        out = np.empty((m, k), dtype=np.int8 if signed else np.uint8)
+        multipliers = np.ascontiguousarray(multipliers, dtype=np.float32)
+        self.lib.oracle_quantize_rows_per_row(m, k, _ptr(a_f32), *_strides(a_f32), _ptr(multipliers), float(zero_point), _ptr(out), k, 1,
+                                              int(signed))
+        return out
+
+    def matmul_i8_dequant_rows(self, a, b_nk, cin, row_scale, column_scale, out_bf16=False):
+        """int32 product plus the int32 accumulator input, then value * row_scale[row] * column_scale[col]."""
+        m, k = a.shape
+        n = b_nk.shape[0]
+        c = np.empty((m, n), dtype=np.uint16 if out_bf16 else np.float32)
+        cin_view, _ = _cin_view(cin, m, n)
+        self.lib.oracle_matmul_i8_dequant_rows(m, n, k, _ptr(a), *_strides(a), int(a.dtype == np.int8), _ptr(b_nk), *_strides(b_nk),
+                                               int(b_nk.dtype == np.int8), _ptr(cin_view),
+                                               *(_strides(cin_view) if cin_view is not None else (0, 0)), _ptr(row_scale), _ptr(column_scale),
+                                               _ptr(c), n, 1, int(out_bf16))
+        return c
+
     def matmul_i8_dequant(self, a, b_nk, cin=None, alpha=1.0, scale=None, act=ACT_NONE, lo=0.0, hi=0.0, out_bf16=False):
         m, k = a.shape
         n = b_nk.shape[0]
@@ -288,6 +311,8 @@ class Ref:
             lib.ref_matmul_i8_accumulate.argtypes = [_I64] * 3 + [_P, _I64, _P, _I64, _P, _I64, _I64, _P, _I64]
         if hasattr(lib, "ref_matmul_bf16_batched"):
             lib.ref_matmul_bf16_batched.argtypes = [_I64] * 4 + [_P, _I64, _I64, _P, _I64, _I64, _P, _P, _I64, _I64]
+        if hasattr(lib, "ref_matmul_quantized_per_row"):
+            lib.ref_matmul_quantized_per_row.argtypes = [_I64] * 3 + [_P, _I64, _P, ctypes.c_int32, _P, _I64, _P, _P, _P, _P, _I64]
         if hasattr(lib, "ref_sdpa_bf16"):
             lib.ref_sdpa_bf16.argtypes = [_I64] * 4 + [_P] * 7 + [c_int, ctypes.c_float, _P]
         if hasattr(lib, "ref_f16_widen"):
@@ -330,6 +355,19 @@ class Ref:
         assert a3.strides[2] == item and b3.strides[2] == item
         rc = self.lib.ref_matmul_bf16_batched(batch, m, n, k, _ptr(a3), a3.strides[0] // item, a3.strides[1] // item, _ptr(b3),
                                               b3.strides[0] // item, b3.strides[1] // item, _ptr(bias), _ptr(c), m * n, n)
+        assert rc == 0
+        return c
+
+    def matmul_quantized_per_row(self, a_f32, multipliers, zero_point, b_nk, correction, row_scales, column_scales):
+        """Per-token quantisation with the reference's named transforms; fp32 C."""
+        m, k = a_f32.shape
+        n = b_nk.shape[0]
+        c = np.empty((m, n), dtype=np.float32)
+        padded = np.concatenate([np.asarray(column_scales, np.float32), np.zeros(64, np.float32)])
+        multipliers = np.ascontiguousarray(multipliers, dtype=np.float32)
+        row_scales = np.ascontiguousarray(row_scales, dtype=np.float32)
+        rc = self.lib.ref_matmul_quantized_per_row(m, n, k, _ptr(a_f32), self._rows(a_f32), _ptr(multipliers), int(zero_point), _ptr(b_nk),
+                                                   self._rows(b_nk), _ptr(correction), _ptr(row_scales), _ptr(padded), _ptr(c), n)
         assert rc == 0
         return c
 

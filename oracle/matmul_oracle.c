@@ -328,6 +328,37 @@ void oracle_matmul_i8_dequant(int64_t m, int64_t n, int64_t k, const void* a, in
   }
 }
 
+/* Per-token quantisation (include/vecops/matmul/Quantization.h:76-246; the expected value of
+ * tests/ops/MatmulConversionTestCommon.h:1403-1436): q = convert(x * multipliers[row] + zero_point) on load, int32
+ * product plus the correction row, then value * row_scales[row] * column_scales[col] in that order. */
+void oracle_quantize_rows_per_row(int64_t m, int64_t k, const float* src, int64_t ssm, int64_t ssk, const float* multipliers,
+                                  float zero_point, void* dst, int64_t dsm, int64_t dsk, int dst_signed) {
+  for (int64_t i = 0; i < m; ++i)
+    oracle_quantize_rows(1, k, src + i * ssm, ssm, ssk, multipliers[i], zero_point, (char*)dst + i * dsm, dsm, dsk, dst_signed);
+}
+
+void oracle_matmul_i8_dequant_rows(int64_t m, int64_t n, int64_t k, const void* a, int64_t sam, int64_t sak, int a_signed,
+                                   const void* b, int64_t sbn, int64_t sbk, int b_signed, const int32_t* cin, int64_t cin_sm,
+                                   int64_t cin_sn, const float* row_scale, const float* column_scale, void* c, int64_t scm,
+                                   int64_t scn, int c_is_bf16) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t i = 0; i < m; ++i) {
+    for (int64_t j = 0; j < n; ++j) {
+      uint32_t sum = cin ? (uint32_t)cin[i * cin_sm + j * cin_sn] : 0u;
+      for (int64_t kk = 0; kk < k; ++kk) {
+        const int32_t x = a_signed ? ((const int8_t*)a)[i * sam + kk * sak] : ((const uint8_t*)a)[i * sam + kk * sak];
+        const int32_t y = b_signed ? ((const int8_t*)b)[j * sbn + kk * sbk] : ((const uint8_t*)b)[j * sbn + kk * sbk];
+        sum += (uint32_t)(x * y);
+      }
+      float acc = (float)(int32_t)sum;
+      if (row_scale) acc *= row_scale[i];
+      if (column_scale) acc *= column_scale[j];
+      if (c_is_bf16) ((uint16_t*)c)[i * scm + j * scn] = f32_to_bf16(acc);
+      else ((float*)c)[i * scm + j * scn] = acc;
+    }
+  }
+}
+
 /* How many threads the loops above use (1 when built without OpenMP). */
 /* Scaled dot-product attention for one head, the caller one step above matmul
  * (include/vecops/ops/details/attention/SDPA.h:72-84, :305-383; Common.h:200-345):

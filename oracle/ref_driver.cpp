@@ -21,6 +21,7 @@
 #include <vector>
 
 #include "vecops/ops/Attention.h"
+#include "vecops/matmul/Quantization.h"
 #include "vecops/ops/Matmul.h"
 
 using namespace vecops;
@@ -224,6 +225,31 @@ int ref_matmul_quantized_u8s8(int64_t m, int64_t n, int64_t k, const float* a, i
   auto dequantize = make_elementwise_vec_transform<float32_t, float32_t>([=](auto tag, auto value) VECOPS_KERNEL_LAMBDA {
     return vec::mul(tag, value, vec::fill(tag, dequant));
   });
+  auto ai = input<uint8_t>(at, quantize_a);
+  auto bi = input<int8_t>(bt);
+  auto ci = input<int32_t>(correction_tensor);
+  auto co = output<int32_t>(ct, dequantize);
+  auto op = ops::matmul(ops::MatmulConfig<matmul::AMX_I8I32<uint8_t, int8_t>>{});
+  kernel::Workspace storage(op.required_workspace(Any{m}, Any{n}, Any{k}, ai, bi, ci, co));
+  auto view = storage.view();
+  op(view, Any{m}, Any{n}, Any{k}, ai, bi, ci, co);
+  return 0;
+}
+
+// Per-token quantisation with the reference's own named transforms (include/vecops/matmul/Quantization.h:76-246; call
+// form of tests/ops/MatmulConversionTestCommon.h:1384-1401): fp32 A quantised on load to u8 with one multiplier per
+// row and a shared int32 zero point, s8 B, the int32 correction row as the accumulator input, and the row-by-column
+// dequantising output transform.  `column_scales` needs 64 readable floats past n (the transform loads whole vectors).
+int ref_matmul_quantized_per_row(int64_t m, int64_t n, int64_t k, const float* a, int64_t lda, const float* multipliers, int32_t zero_point,
+                                 const int8_t* b, int64_t ldb, const int32_t* correction, const float* row_scales,
+                                 const float* column_scales, float* c, int64_t ldc) {
+  if (!request_amx()) return 1;
+  auto at = make_tensor(a, make_layout(make_shape(Any{m}, Any{k}), make_strides(Any{lda}, cint<1>)));
+  auto bt = make_tensor(b, make_layout(make_shape(Any{n}, Any{k}), make_strides(Any{ldb}, cint<1>)));
+  auto ct = make_tensor(c, make_layout(make_shape(Any{m}, Any{n}), make_strides(Any{ldc}, cint<1>)));
+  auto correction_tensor = make_tensor(correction, make_layout(make_shape(Any{m}, Any{n}), make_strides(cint<0>, cint<1>)));
+  auto quantize_a = ::vecops::matmul::make_runtime_per_row_asymmetric_quantize_transform({multipliers, &zero_point, nint_t{0}});
+  auto dequantize = ::vecops::matmul::make_runtime_per_row_column_dequantize_transform({row_scales, column_scales, nint_t{0}});
   auto ai = input<uint8_t>(at, quantize_a);
   auto bi = input<int8_t>(bt);
   auto ci = input<int32_t>(correction_tensor);

@@ -200,6 +200,27 @@ def main() -> None:
                          keep_mask=(rng.random((lq, lkv)) > 0.1).astype(np.uint8), bias=rng.uniform(-1, 1, (lq, lkv)).astype(np.float32))
         attention_case(name, q, k, v, 1.0 / np.sqrt(dqk), causal, **extra)
 
+    # per-token quantisation with the reference's named transforms (matmul/Quantization.h:76-246): the reference test's own
+    # operand pattern (tests/ops/MatmulConversionTestCommon.h:1455-1480: multipliers 4 << (row % 2), logical values
+    # ((row*k + kk) % 7 - 3) / multiplier, zero point 7, column scales 0.03125 + (col % 5) / 128) and a seeded case
+    def per_row_case(name, a, multipliers, zero_point, b, row_scales, column_scales):
+        correction = (-zero_point * b.astype(np.int64).sum(axis=1)).astype(np.int32)
+        cases[name] = dict(kind="quant_per_row", a=a, multipliers=multipliers, zero_point=np.int32(zero_point), b=b, correction=correction,
+                           row_scales=row_scales, column_scales=column_scales,
+                           c=ref.matmul_quantized_per_row(a, multipliers, zero_point, b, correction, row_scales, column_scales))
+
+    for m, n, k in [(19, 23, 65), (1, 8, 129), (33, 47, 96)]:
+        multipliers = np.array([4 << (r % 2) for r in range(m)], np.float32)
+        a = (((np.arange(m * k) % 7) - 3).reshape(m, k) / multipliers[:, None]).astype(np.float32)
+        b = conversion_pattern(n * k, 11, np.int8).reshape(n, k)
+        per_row_case(f"quant_per_row_{m}x{n}x{k}", a, multipliers, 7, b, (1.0 / multipliers).astype(np.float32),
+                     (0.03125 + (np.arange(n) % 5) * 0.0078125).astype(np.float32))
+    rng = np.random.default_rng(43)
+    m, n, k = 37, 51, 128
+    multipliers = rng.uniform(10, 40, m).astype(np.float32)
+    per_row_case("quant_per_row_seeded_37x51x128", rng.uniform(-3, 3, (m, k)).astype(np.float32), multipliers, 100,
+                 rng.integers(-128, 128, (n, k), dtype=np.int8), (1.0 / multipliers).astype(np.float32), rng.uniform(0.01, 0.05, n).astype(np.float32))
+
     # float16_t's widening and narrowing (util/Float16.h:272-277) over the whole sweep, as digests: the part of the
     # AMX_F16F32 row a host without AMX-FP16 can run
     patterns, floats = f16_conversion_inputs()

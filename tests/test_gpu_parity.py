@@ -78,7 +78,7 @@ def oracle(kind, port, a, b, scale, out_bf16=True):
 def test_golden_fixtures_through_automatic_dispatch(golden):
     for name, case in golden.items():
         kind = str(case["kind"])
-        if kind in ("fused_bf16", "i8acc", "quant_u8s8", "batched_bf16", "f16_convert", "sdpa_bf16"):
+        if kind in ("fused_bf16", "i8acc", "quant_u8s8", "batched_bf16", "f16_convert", "sdpa_bf16", "quant_per_row"):
             continue  # the fused forms have their own tests below; the conversion digests are the checker's own
         a, b = case["a"], case["b"]
         if kind == "i8":
@@ -1094,3 +1094,68 @@ def test_f32_whole_tile_form_agrees_with_the_general_kernel(port, b_kn, monkeypa
     bias = rng.uniform(-1, 1, 256).astype(np.float32)
     got = _fused_gpu("f32", a, b, torch.float32, K.KERNEL_F32_SIMT, cin=bias, act=ACT_SILU, alpha=0.25)
     assert rel_frobenius(got, port.matmul_f32_fused(a, b, bias, 0.25, None, ACT_SILU)) <= 1e-5
+
+
+# ------------------------------------------------------------------ per-token quantisation: row multipliers in, row-by-column scales out
+
+def _per_row_gpu(a, multipliers, zero_point, b, correction, row_scales, column_scales, kernel, out_dtype=torch.float32):
+    m, k = a.shape
+    n = b.shape[0]
+    qa = torch.empty((m, k), dtype=torch.uint8, device="cuda")
+    harness.quantize_rows(to_device(a), qa, to_device(np.ascontiguousarray(multipliers, dtype=np.float32)), float(zero_point))
+    c = torch.full((m, n), -3, dtype=out_dtype, device="cuda")
+    vecops_b200.matmul(qa, to_device(b), c, to_device(column_scales), kernel=kernel, cin=to_device(correction),
+                       row_scale=to_device(np.ascontiguousarray(row_scales, dtype=np.float32)))
+    torch.cuda.synchronize()
+    return qa.cpu().numpy(), (bf16_result_to_numpy(c) if out_dtype == torch.bfloat16 else c.cpu().numpy())
+
+
+def test_per_row_quantised_golden_fixtures(port, golden):
+    # outputs of the reference's own per-row quantise / row-by-column dequantise transforms: bit-exact
+    seen = 0
+    for name, case in golden.items():
+        if str(case["kind"]) != "quant_per_row":
+            continue
+        for kernel in (K.KERNEL_AUTO, K.KERNEL_GENERIC):
+            quantized, got = _per_row_gpu(case["a"], case["multipliers"], int(case["zero_point"]), case["b"], case["correction"], case["row_scales"],
+                                          case["column_scales"], kernel)
+            assert np.array_equal(quantized, port.quantize_rows_per_row(case["a"], case["multipliers"], float(case["zero_point"]))), name
+            assert np.array_equal(got, case["c"]), name
+        seen += 1
+    assert seen >= 4
+
+
+def test_per_row_scales_on_the_tensor_core_kernels(port, cta_form):
+    from oracle.checker import pack_compensation
+    rng = np.random.default_rng(61)
+    m, n, k = 300, 520, 256
+    a = rng.uniform(-3, 3, (m, k)).astype(np.float32)
+    multipliers = rng.uniform(10, 40, m).astype(np.float32)
+    b = rng.integers(-128, 128, (n, k), dtype=np.int8)
+    correction = pack_compensation(b, 100)
+    rows, cols = (1.0 / multipliers).astype(np.float32), rng.uniform(0.01, 0.05, n).astype(np.float32)
+    quantized = port.quantize_rows_per_row(a, multipliers, 100.0)
+    for out_dtype in (torch.float32, torch.bfloat16):
+        got_q, got = _per_row_gpu(a, multipliers, 100, b, correction, rows, cols, K.KERNEL_I8_TCGEN05, out_dtype)
+        assert np.array_equal(got_q, quantized)
+        want = port.matmul_i8_dequant_rows(quantized, b, correction, rows, cols, out_bf16=out_dtype == torch.bfloat16)
+        assert np.array_equal(got, want), out_dtype
+    # float rows take the row factor too: bf16 product, and the weight-only kernels (which compute the product transposed)
+    ab, bb, _ = inputs("bf16", m, n, k, rng)
+    row = rng.uniform(0.5, 2.0, m).astype(np.float32)
+    c = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    vecops_b200.matmul(to_device(ab, bf16=True), to_device(bb, bf16=True), c, to_device(cols), kernel=K.KERNEL_BF16_TCGEN05, row_scale=to_device(row))
+    torch.cuda.synchronize()
+    want = port.matmul_bf16(ab, bb, None, False) * row[:, None] * cols[None, :]
+    assert rel_frobenius(c.cpu().numpy(), want) <= TOL_BF16
+    for mw, kernel in ((16, K.KERNEL_AUTO), (8, K.KERNEL_W8_SMALL_M), (96, K.KERNEL_W8_TCGEN05)):
+        aw, w, s = inputs("w8", mw, 512, 1024, rng)
+        roww = rng.uniform(0.5, 2.0, mw).astype(np.float32)
+        cw = torch.empty((mw, 512), dtype=torch.float32, device="cuda")
+        vecops_b200.matmul(to_device(aw, bf16=True), to_device(w), cw, to_device(s), kernel=kernel, row_scale=to_device(roww))
+        torch.cuda.synchronize()
+        wantw = port.matmul_w8(aw, w, s, False) * roww[:, None]
+        assert rel_frobenius(cw.cpu().numpy(), wantw) <= TOL_BF16, mw
+    # the plain int32 row refuses a row factor
+    with pytest.raises(capi.VecopsB200Error):
+        vecops_b200.matmul(to_device(quantized), to_device(b), torch.empty((m, n), dtype=torch.int32, device="cuda"), row_scale=to_device(rows))

@@ -43,6 +43,12 @@ def test_port_matches_golden_fixtures(port, golden):
             assert np.array_equal((got == 0).all(axis=1), (case["out"] == 0).all(axis=1)), name  # fully masked rows are exactly zero
             checked += 1
             continue
+        if kind == "quant_per_row":
+            quantized = port.quantize_rows_per_row(case["a"], case["multipliers"], float(case["zero_point"]))
+            got = port.matmul_i8_dequant_rows(quantized, case["b"], case["correction"], case["row_scales"], case["column_scales"])
+            assert np.array_equal(got, case["c"]), name
+            checked += 1
+            continue
         a, b = case["a"], case["b"]
         if kind == "i8":
             assert np.array_equal(port.matmul_i8(a, b), case["c"]), name
@@ -78,7 +84,7 @@ def test_port_matches_golden_fixtures(port, golden):
         else:
             raise AssertionError(f"unknown fixture kind {kind}")
         checked += 1
-    assert checked >= 44
+    assert checked >= 48
 
 
 def test_int32_accumulator_wraps(port):

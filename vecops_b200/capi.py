@@ -80,7 +80,7 @@ class VecopsB200Matmul(Structure):
 class VecopsB200Epilogue(Structure):
     _fields_ = [("struct_size", c_uint32), ("activation", c_uint32), ("cin", c_void_p), ("cin_stride_m", c_int64),
                 ("cin_stride_n", c_int64), ("cin_dtype", c_uint32), ("alpha", c_float), ("clamp_lo", c_float),
-                ("clamp_hi", c_float), ("reserved", c_uint32)]
+                ("clamp_hi", c_float), ("reserved", c_uint32), ("row_scale", c_void_p)]
 
 
 ACTIVATION_NONE, ACTIVATION_RELU, ACTIVATION_SIGMOID, ACTIVATION_SILU, ACTIVATION_CLAMP = range(5)
@@ -164,6 +164,8 @@ def library() -> ctypes.CDLL:
         lib.vecops_b200_matmul_run_batched.argtypes = [POINTER(VecopsB200Matmul), POINTER(VecopsB200Batch), POINTER(VecopsB200Epilogue), e]
         lib.vecops_b200_quantize_rows.argtypes = [c_void_p, c_uint32, c_int64, c_int64, c_void_p, c_uint32, c_int64, c_int64, c_int64, c_float,
                                                   c_float, c_void_p, e]
+        lib.vecops_b200_quantize_rows_per_row.argtypes = [c_void_p, c_uint32, c_int64, c_int64, c_void_p, c_uint32, c_int64, c_int64, c_int64,
+                                                          c_void_p, c_float, c_void_p, e]
         lib.vecops_b200_column_correction.argtypes = [c_void_p, c_uint32, c_int64, c_int64, c_int64, c_int32, c_void_p, c_void_p, e]
         lib.vecops_b200_matmul_packed_layout.argtypes = [c_uint32, c_int64, c_int64, POINTER(c_int64), POINTER(c_uint64), e]
         lib.vecops_b200_matmul_pack.argtypes = [POINTER(VecopsB200Pack), e]

@@ -1,9 +1,10 @@
 // The fused output transform shared by the GEMM kernels:
-//     COut[m,n] = convert( activation( (CIn[m,n] + sum_k A[m,k] B[n,k]) * alpha * column_scale[n] ) )
+//     COut[m,n] = convert( activation( (CIn[m,n] + sum_k A[m,k] B[n,k]) * alpha * row_scale[m] * column_scale[n] ) )
 // vecops expresses this as the explicit accumulate form COut = transform(CIn + A.B^T) with an output transform composed
 // from vec primitives (include/vecops/ops/Matmul.h:519-570; tests/ops/MatmulConversionTestCommon.h:623-704 runtime and
 // per-column scale, :705-770 bias as a stride-0 CIn + clamp, :1028-1160 relu / sigmoid / silu).  On the device the
-// transforms those tests compose are an enumeration carried in this record.
+// transforms those tests compose are an enumeration carried in this record.  The per-row factor is the row half of vecops'
+// row-by-column dequantisation (include/vecops/matmul/Quantization.h:195-246: value * row_scales[row] * column_scales[col]).
 #pragma once
 
 #include <cuda_bf16.h>
@@ -25,7 +26,13 @@ struct EpilogueArgs {
   float clamp_lo = 0.f;
   float clamp_hi = 0.f;
   int active = 0;
+  const float* row_scale = nullptr;  // optional [M] factor, one per output row
 };
+
+// alpha with the row's own factor folded in (alpha is 1 in vecops' row-by-column form, so the product order is value * row * column)
+__device__ __forceinline__ float epilogue_row_alpha(const EpilogueArgs& ep, long long row) {
+  return ep.row_scale != nullptr ? ep.alpha * __ldg(ep.row_scale + row) : ep.alpha;
+}
 
 __device__ __forceinline__ float epilogue_activation(float x, const EpilogueArgs& ep) {
   switch (ep.activation) {
@@ -45,7 +52,7 @@ __device__ __forceinline__ float epilogue_float(float acc, const EpilogueArgs& e
   } else if (ep.cin_kind == kCinBF16) {
     acc += __bfloat162float(static_cast<const __nv_bfloat16*>(ep.cin)[row * ep.cin_stride_m + col * ep.cin_stride_n]);
   }
-  return epilogue_activation(acc * ep.alpha * column_factor, ep);
+  return epilogue_activation(acc * epilogue_row_alpha(ep, row) * column_factor, ep);
 }
 
 // The same transform over 32 consecutive columns of one row held in registers (`v` = fp32 bit patterns), written as a
@@ -56,6 +63,7 @@ __device__ __forceinline__ void epilogue_float_row32(uint32_t (&v)[32], const Ep
                                                      long long row, int col0, int M, int N) {
   if (row >= M) return;
   const int valid = min(32, N - col0);
+  const float alpha = epilogue_row_alpha(ep, row);
   if (ep.cin_kind == kCinF32) {
     const float* src = static_cast<const float*>(ep.cin) + row * ep.cin_stride_m + static_cast<long long>(col0) * ep.cin_stride_n;
     if (ep.cin_stride_n == 1 && valid == 32 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
@@ -97,19 +105,19 @@ __device__ __forceinline__ void epilogue_float_row32(uint32_t (&v)[32], const Ep
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         const float4 f = __ldg(reinterpret_cast<const float4*>(column_scale + col0) + q);
-        v[4 * q] = __float_as_uint(__uint_as_float(v[4 * q]) * ep.alpha * f.x);
-        v[4 * q + 1] = __float_as_uint(__uint_as_float(v[4 * q + 1]) * ep.alpha * f.y);
-        v[4 * q + 2] = __float_as_uint(__uint_as_float(v[4 * q + 2]) * ep.alpha * f.z);
-        v[4 * q + 3] = __float_as_uint(__uint_as_float(v[4 * q + 3]) * ep.alpha * f.w);
+        v[4 * q] = __float_as_uint(__uint_as_float(v[4 * q]) * alpha * f.x);
+        v[4 * q + 1] = __float_as_uint(__uint_as_float(v[4 * q + 1]) * alpha * f.y);
+        v[4 * q + 2] = __float_as_uint(__uint_as_float(v[4 * q + 2]) * alpha * f.z);
+        v[4 * q + 3] = __float_as_uint(__uint_as_float(v[4 * q + 3]) * alpha * f.w);
       }
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (j < valid) v[j] = __float_as_uint(__uint_as_float(v[j]) * ep.alpha * __ldg(column_scale + col0 + j));
+        if (j < valid) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha * __ldg(column_scale + col0 + j));
     }
-  } else if (ep.alpha != 1.f) {
+  } else if (alpha != 1.f) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * ep.alpha);
+    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
   }
   switch (ep.activation) {
     case kActRelu:

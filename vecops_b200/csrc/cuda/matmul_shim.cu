@@ -995,9 +995,10 @@ int32_t vecops_b200_matmul_run_fused(const VecopsB200Matmul* problem, const Veco
   int32_t rc = check_problem(problem, &row, error);
   if (rc != VECOPS_STATUS_OK) return rc;
   if (epilogue == nullptr) return vecops_b200_matmul_run(problem, error);
-  if (epilogue->struct_size < sizeof(VecopsB200Epilogue))
-    return set_error(error, VECOPS_STATUS_ABI_MISMATCH, "epilogue record is %u bytes, this library needs %zu", epilogue->struct_size,
-                     sizeof(VecopsB200Epilogue));
+  if (epilogue->struct_size < offsetof(VecopsB200Epilogue, row_scale))
+    return set_error(error, VECOPS_STATUS_ABI_MISMATCH, "epilogue record is %u bytes, this library needs at least %zu", epilogue->struct_size,
+                     offsetof(VecopsB200Epilogue, row_scale));
+  const float* row_scale = epilogue->struct_size >= sizeof(VecopsB200Epilogue) ? epilogue->row_scale : nullptr;
   if (epilogue->activation >= VECOPS_B200_ACTIVATION_COUNT_)
     return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "unknown activation %u", epilogue->activation);
   EpilogueArgs args;
@@ -1023,11 +1024,12 @@ int32_t vecops_b200_matmul_run_fused(const VecopsB200Matmul* problem, const Veco
       return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "fp32 accumulators take an f32 or bf16 accumulator input");
     }
   }
-  if (row == Row::I8 && (epilogue->alpha != 1.f || epilogue->activation != VECOPS_B200_ACTIVATION_NONE))
+  if (row == Row::I8 && (epilogue->alpha != 1.f || epilogue->activation != VECOPS_B200_ACTIVATION_NONE || row_scale != nullptr))
     return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "int32 accumulators take an accumulator input only: no factor, no activation");
+  args.row_scale = row_scale;
   if (epilogue->activation == VECOPS_B200_ACTIVATION_CLAMP && !(epilogue->clamp_lo <= epilogue->clamp_hi))
     return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "clamp needs clamp_lo <= clamp_hi");
-  args.active = (args.cin_kind != kCinNone || args.alpha != 1.f || args.activation != kActNone) ? 1 : 0;
+  args.active = (args.cin_kind != kCinNone || args.alpha != 1.f || args.activation != kActNone || args.row_scale != nullptr) ? 1 : 0;
   if (!args.active) return vecops_b200_matmul_run(problem, error);
 
   // which kernel: the plain problem's choice, unless that kernel does not implement the transform
@@ -1054,7 +1056,7 @@ int32_t vecops_b200_matmul_run_batched(const VecopsB200Matmul* problem, const Ve
       batch->b_stride_b < 0 || batch->c_stride_b < 0 || batch->cin_stride_b < 0)
     return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "batch record is null, too small, or has a negative count or stride");
   if (epilogue != nullptr && epilogue->struct_size < sizeof(VecopsB200Epilogue))
-    return set_error(error, VECOPS_STATUS_ABI_MISMATCH, "epilogue record is %u bytes, this library needs %zu", epilogue->struct_size,
+    return set_error(error, VECOPS_STATUS_ABI_MISMATCH, "epilogue record is %u bytes, the batched form needs %zu", epilogue->struct_size,
                      sizeof(VecopsB200Epilogue));
   if (batch->count == 0 || problem->m == 0 || problem->n == 0) return VECOPS_STATUS_OK;
   if (batch->count > 1 && batch->c_stride_b == 0)
@@ -1082,6 +1084,9 @@ int32_t vecops_b200_matmul_run_batched(const VecopsB200Matmul* problem, const Ve
     if (epilogue != nullptr) {
       VecopsB200Epilogue step = *epilogue;
       if (has_cin) step.cin = static_cast<const char*>(epilogue->cin) + i * batch->cin_stride_b * static_cast<int64_t>(cin_elem);
+      // row factors belong to A's rows: entries that share A share them, otherwise entry i owns rows [i*M, (i+1)*M)
+      // (vecops' scale index is batch * batch_stride + row with batch_stride = M, 0 for a broadcast A)
+      if (step.row_scale != nullptr && batch->a_stride_b != 0) step.row_scale = epilogue->row_scale + i * p.m;
       rc = vecops_b200_matmul_run_fused(&entry, &step, error);
     } else {
       rc = vecops_b200_matmul_run(&entry, error);
@@ -1223,9 +1228,9 @@ int32_t vecops_b200_matmul_allgather_run(const VecopsB200Matmul* problem, const 
   return rc;
 }
 
-int32_t vecops_b200_quantize_rows(const void* src, uint32_t src_dtype, int64_t src_stride_m, int64_t src_stride_k, void* dst,
+static int32_t quantize_rows_impl(const void* src, uint32_t src_dtype, int64_t src_stride_m, int64_t src_stride_k, void* dst,
                                   uint32_t dst_dtype, int64_t dst_stride_m, int64_t rows, int64_t cols, float scale, float zero_point,
-                                  void* stream, VecopsError* error) {
+                                  const float* multipliers, void* stream, VecopsError* error) {
   if (rows == 0 || cols == 0) return VECOPS_STATUS_OK;
   if (src == nullptr || dst == nullptr || rows < 0 || cols < 0 || dst_stride_m < cols)
     return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "quantize_rows: null pointer, negative extent or overlapping destination rows");
@@ -1244,21 +1249,37 @@ int32_t vecops_b200_quantize_rows(const void* src, uint32_t src_dtype, int64_t s
     const long long groups = rows * (cols / 4);
     const int grid4 = static_cast<int>(groups / 256 + 1 < 148 * 16 ? groups / 256 + 1 : 148 * 16);
     const float* in = static_cast<const float*>(src);
-    if (is_signed) quantize_rows_f32x4_kernel<true><<<grid4, 256, 0, s>>>(in, src_stride_m, out, dst_stride_m, rows, cols / 4, scale, zero_point);
-    else quantize_rows_f32x4_kernel<false><<<grid4, 256, 0, s>>>(in, src_stride_m, out, dst_stride_m, rows, cols / 4, scale, zero_point);
+    if (is_signed) quantize_rows_f32x4_kernel<true><<<grid4, 256, 0, s>>>(in, src_stride_m, out, dst_stride_m, rows, cols / 4, scale, zero_point, multipliers);
+    else quantize_rows_f32x4_kernel<false><<<grid4, 256, 0, s>>>(in, src_stride_m, out, dst_stride_m, rows, cols / 4, scale, zero_point, multipliers);
   } else if (src_dtype == VECOPS_DTYPE_F32) {
     const float* in = static_cast<const float*>(src);
-    if (is_signed) quantize_rows_kernel<float, true><<<blocks, 256, 0, s>>>(in, src_stride_m, src_stride_k, out, dst_stride_m, rows, cols, scale, zero_point);
-    else quantize_rows_kernel<float, false><<<blocks, 256, 0, s>>>(in, src_stride_m, src_stride_k, out, dst_stride_m, rows, cols, scale, zero_point);
+    if (is_signed) quantize_rows_kernel<float, true><<<blocks, 256, 0, s>>>(in, src_stride_m, src_stride_k, out, dst_stride_m, rows, cols, scale, zero_point, multipliers);
+    else quantize_rows_kernel<float, false><<<blocks, 256, 0, s>>>(in, src_stride_m, src_stride_k, out, dst_stride_m, rows, cols, scale, zero_point, multipliers);
   } else {
     const __nv_bfloat16* in = static_cast<const __nv_bfloat16*>(src);
-    if (is_signed) quantize_rows_kernel<__nv_bfloat16, true><<<blocks, 256, 0, s>>>(in, src_stride_m, src_stride_k, out, dst_stride_m, rows, cols, scale, zero_point);
-    else quantize_rows_kernel<__nv_bfloat16, false><<<blocks, 256, 0, s>>>(in, src_stride_m, src_stride_k, out, dst_stride_m, rows, cols, scale, zero_point);
+    if (is_signed) quantize_rows_kernel<__nv_bfloat16, true><<<blocks, 256, 0, s>>>(in, src_stride_m, src_stride_k, out, dst_stride_m, rows, cols, scale, zero_point, multipliers);
+    else quantize_rows_kernel<__nv_bfloat16, false><<<blocks, 256, 0, s>>>(in, src_stride_m, src_stride_k, out, dst_stride_m, rows, cols, scale, zero_point, multipliers);
   }
   g_launches.fetch_add(1);
   cudaError_t status = cudaGetLastError();
   if (status != cudaSuccess) return cuda_fail(error, status, "quantize_rows launch");
   return VECOPS_STATUS_OK;
+}
+
+int32_t vecops_b200_quantize_rows(const void* src, uint32_t src_dtype, int64_t src_stride_m, int64_t src_stride_k, void* dst,
+                                  uint32_t dst_dtype, int64_t dst_stride_m, int64_t rows, int64_t cols, float scale, float zero_point,
+                                  void* stream, VecopsError* error) {
+  return quantize_rows_impl(src, src_dtype, src_stride_m, src_stride_k, dst, dst_dtype, dst_stride_m, rows, cols, scale, zero_point, nullptr,
+                            stream, error);
+}
+
+int32_t vecops_b200_quantize_rows_per_row(const void* src, uint32_t src_dtype, int64_t src_stride_m, int64_t src_stride_k, void* dst,
+                                          uint32_t dst_dtype, int64_t dst_stride_m, int64_t rows, int64_t cols, const float* multipliers,
+                                          float zero_point, void* stream, VecopsError* error) {
+  if (multipliers == nullptr && rows > 0 && cols > 0)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "quantize_rows_per_row: null multipliers");
+  return quantize_rows_impl(src, src_dtype, src_stride_m, src_stride_k, dst, dst_dtype, dst_stride_m, rows, cols, 1.f, zero_point, multipliers,
+                            stream, error);
 }
 
 int32_t vecops_b200_column_correction(const void* b, uint32_t b_dtype, int64_t b_stride_n, int64_t n, int64_t k, int32_t zero_point,

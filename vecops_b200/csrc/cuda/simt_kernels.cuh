@@ -356,12 +356,16 @@ gemm_f32_tile8_kernel(const float* __restrict__ a, long long lda, const float* _
 // the conversion rule was observed by running the reference: 3.51 -> 3, 255.6 -> 255, -0.6 -> 0).
 template <typename TS, bool kSigned>
 __global__ void quantize_rows_kernel(const TS* __restrict__ src, long long ssm, long long ssk, uint8_t* __restrict__ dst,
-                                     long long dsm, long long rows, long long cols, float scale, float zero_point) {
+                                     long long dsm, long long rows, long long cols, float scale, float zero_point,
+                                     const float* __restrict__ multipliers) {
+  // `multipliers` (may be null): one factor per row in place of `scale` - vecops' per-row asymmetric quantisation,
+  // q = x * multipliers[row] + zero_point (include/vecops/matmul/Quantization.h:76-140)
   const long long total = rows * cols;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long m = i / cols, k = i % cols;
-    float q = truncf(load_as<float, TS>(src + m * ssm + k * ssk) * scale + zero_point);
+    const float factor = multipliers != nullptr ? __ldg(multipliers + m) : scale;
+    float q = truncf(load_as<float, TS>(src + m * ssm + k * ssk) * factor + zero_point);
     if (!(q == q)) q = 0.f;
     if (kSigned) dst[m * dsm + k] = static_cast<uint8_t>(static_cast<int8_t>(fminf(fmaxf(q, -128.f), 127.f)));
     else dst[m * dsm + k] = static_cast<uint8_t>(fminf(fmaxf(q, 0.f), 255.f));
@@ -371,11 +375,13 @@ __global__ void quantize_rows_kernel(const TS* __restrict__ src, long long ssm, 
 // The common case of the above - fp32 rows, K-contiguous, whole 16-byte groups - four elements per thread.
 template <bool kSigned>
 __global__ void quantize_rows_f32x4_kernel(const float* __restrict__ src, long long ssm, uint8_t* __restrict__ dst, long long dsm,
-                                           long long rows, long long groups_per_row, float scale, float zero_point) {
+                                           long long rows, long long groups_per_row, float scale, float zero_point,
+                                           const float* __restrict__ multipliers) {
   const long long total = rows * groups_per_row;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long m = i / groups_per_row, g = i % groups_per_row;
+    if (multipliers != nullptr) scale = __ldg(multipliers + m);
     const float4 x = __ldg(reinterpret_cast<const float4*>(src + m * ssm) + g);
     const float in[4] = {x.x, x.y, x.z, x.w};
     uint32_t packed = 0;

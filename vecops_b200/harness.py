@@ -74,10 +74,11 @@ def attach_workspace(problem: capi.VecopsB200Matmul, device):
 
 
 def epilogue_record(cin=None, alpha: float = 1.0, activation: int = capi.ACTIVATION_NONE, clamp_lo: float = 0.0,
-                    clamp_hi: float = 0.0, rows: int | None = None, cols: int | None = None) -> capi.VecopsB200Epilogue:
-    """The fused output transform: COut = activation((CIn + A.B^T) * alpha * column_scale).
+                    clamp_hi: float = 0.0, rows: int | None = None, cols: int | None = None, row_scale=None) -> capi.VecopsB200Epilogue:
+    """The fused output transform: COut = activation((CIn + A.B^T) * alpha * row_scale[m] * column_scale[n]).
 
-    `cin` is a torch tensor broadcastable to [rows, cols] (a bias row [cols], a column [rows, 1], or the full matrix)."""
+    `cin` is a torch tensor broadcastable to [rows, cols] (a bias row [cols], a column [rows, 1], or the full matrix);
+    `row_scale` a contiguous float32 tensor with one factor per output row."""
     e = capi.VecopsB200Epilogue()
     e.struct_size = ctypes.sizeof(capi.VecopsB200Epilogue)
     e.activation, e.alpha, e.clamp_lo, e.clamp_hi = activation, alpha, clamp_lo, clamp_hi
@@ -85,6 +86,8 @@ def epilogue_record(cin=None, alpha: float = 1.0, activation: int = capi.ACTIVAT
         view = cin.expand(rows, cols) if tuple(cin.shape) != (rows, cols) else cin
         e.cin, e.cin_stride_m, e.cin_stride_n = view.data_ptr(), view.stride(0), view.stride(1)
         e.cin_dtype = torch_dtype_code(view.dtype)
+    if row_scale is not None:
+        e.row_scale = row_scale.data_ptr()
     return e
 
 
@@ -97,14 +100,14 @@ def run(problem: capi.VecopsB200Matmul, epilogue: capi.VecopsB200Epilogue | None
 
 
 def matmul(a, b_nk, c, scale=None, kernel: int = capi.KERNEL_AUTO, stream=None, asynchronous: bool = False, cin=None,
-           alpha: float = 1.0, activation: int = capi.ACTIVATION_NONE, clamp_lo: float = 0.0, clamp_hi: float = 0.0) -> None:
+           alpha: float = 1.0, activation: int = capi.ACTIVATION_NONE, clamp_lo: float = 0.0, clamp_hi: float = 0.0, row_scale=None) -> None:
     """Run C = A . B^T (or its fused form, see epilogue_record) on the GPU through the C ABI; raises VecopsB200Error."""
     import torch
     if stream is None and a.is_cuda:
         stream = torch.cuda.current_stream(a.device)
     problem = matmul_problem(a, b_nk, c, scale, kernel, stream, asynchronous)
-    fused = cin is not None or alpha != 1.0 or activation != capi.ACTIVATION_NONE
-    epilogue = epilogue_record(cin, alpha, activation, clamp_lo, clamp_hi, c.shape[0], c.shape[1]) if fused else None
+    fused = cin is not None or alpha != 1.0 or activation != capi.ACTIVATION_NONE or row_scale is not None
+    epilogue = epilogue_record(cin, alpha, activation, clamp_lo, clamp_hi, c.shape[0], c.shape[1], row_scale) if fused else None
     # freed after the call: torch's allocator re-issues the block only to later work on the same stream
     scratch = attach_workspace(problem, a.device) if a.is_cuda else None
     run(problem, epilogue)
@@ -144,12 +147,19 @@ def matmul_batched(a3, b3, c3, scale=None, kernel: int = capi.KERNEL_AUTO, strea
     del scratch
 
 
-def quantize_rows(src, dst, scale: float, zero_point: float, stream=None) -> None:
-    """dst[m,k] = convert(src[m,k] * scale + zero_point): src f32 or bf16 [M,K], dst u8 or i8 with K-contiguous rows."""
+def quantize_rows(src, dst, scale, zero_point: float, stream=None) -> None:
+    """dst[m,k] = convert(src[m,k] * scale + zero_point): src f32 or bf16 [M,K], dst u8 or i8 with K-contiguous rows.
+    `scale`: a number, or a contiguous float32 tensor of one multiplier per row (per-token quantisation)."""
     import torch
     if stream is None:
         stream = torch.cuda.current_stream(src.device)
     error = capi.ErrorBuffer()
+    if isinstance(scale, torch.Tensor):
+        error.raise_for(capi.library().vecops_b200_quantize_rows_per_row(src.data_ptr(), torch_dtype_code(src.dtype), src.stride(0), src.stride(1),
+                                                                        dst.data_ptr(), torch_dtype_code(dst.dtype), dst.stride(0), src.shape[0],
+                                                                        src.shape[1], scale.data_ptr(), zero_point, stream.cuda_stream,
+                                                                        byref(error.record)))
+        return
     error.raise_for(capi.library().vecops_b200_quantize_rows(src.data_ptr(), torch_dtype_code(src.dtype), src.stride(0), src.stride(1),
                                                             dst.data_ptr(), torch_dtype_code(dst.dtype), dst.stride(0), src.shape[0],
                                                             src.shape[1], scale, zero_point, stream.cuda_stream, byref(error.record)))
