@@ -124,3 +124,19 @@ def test_run_without_a_gpu_fails_loudly_instead_of_falling_back(library):
         harness.run(p)
     assert info.value.code == capi.EXECUTION_ERROR
     assert "no CPU fallback" in info.value.message
+
+
+def test_torch_operator_library_registers_its_schemas():
+    # host-only: the library loads without a GPU, the three operators exist, and a CPU tensor is refused (no CPU path)
+    import pytest
+    import torch
+
+    from vecops_b200 import _build, torch_ops
+    _build.build_torch_bridge()
+    torch_ops.load()
+    schema = str(torch.ops.vecops_b200.matmul.default._schema)
+    assert "Tensor? column_scale=None" in schema and "Tensor? cin=None" in schema
+    assert "Tensor(a!) c" in str(torch.ops.vecops_b200.matmul_out.default._schema)
+    assert "int causal=0" in str(torch.ops.vecops_b200.sdpa.default._schema)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        torch.ops.vecops_b200.matmul(torch.zeros(4, 4), torch.zeros(4, 4))

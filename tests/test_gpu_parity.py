@@ -1159,3 +1159,59 @@ def test_per_row_scales_on_the_tensor_core_kernels(port, cta_form):
     # the plain int32 row refuses a row factor
     with pytest.raises(capi.VecopsB200Error):
         vecops_b200.matmul(to_device(quantized), to_device(b), torch.empty((m, n), dtype=torch.int32, device="cuda"), row_scale=to_device(rows))
+
+
+# ------------------------------------------------------------------ the Torch operators (dispatcher -> C++ -> operator bridge)
+
+def test_torch_ops_reach_the_kernels(port):
+    from oracle.checker import ACT_SILU
+    from vecops_b200 import torch_ops
+    torch_ops.load()
+    ops = torch.ops.vecops_b200
+    lib = capi.library()
+    rng = np.random.default_rng(88)
+    m, n, k = 256, 512, 256
+    a, b, _ = inputs("bf16", m, n, k, rng)
+    da, db = to_device(a, bf16=True), to_device(b, bf16=True)
+    before = lib.vecops_b200_launch_count()
+    c = ops.matmul(da, db)
+    torch.cuda.synchronize()
+    assert lib.vecops_b200_launch_count() == before + 1 and c.dtype == torch.bfloat16
+    check("bf16", bf16_result_to_numpy(c), port.matmul_bf16(a, b))
+    # fused form with a bias row, f32 out, under a side stream
+    bias = rng.uniform(-1, 1, n).astype(np.float32)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        c32 = ops.matmul(da, db, None, to_device(bias), 0.5, capi.ACTIVATION_SILU, 0.0, 0.0, torch.float32)
+    side.synchronize()
+    check("bf16", c32.cpu().numpy(), port.matmul_bf16_fused(a, b, bias, 0.5, None, ACT_SILU, out_bf16=False))
+    # int8 -> int32, into a caller's tensor; weight-only int8 with its scratch from torch's allocator
+    ai, bi, _ = inputs("i8", m, n, k, rng)
+    ci = torch.empty((m, n), dtype=torch.int32, device="cuda")
+    ops.matmul_out(to_device(ai), to_device(bi), ci)
+    aw, w, s = inputs("w8", 64, 512, 1024, rng)
+    cw = ops.matmul(to_device(aw, bf16=True), to_device(w), to_device(s))
+    torch.cuda.synchronize()
+    assert np.array_equal(ci.cpu().numpy(), port.matmul_i8(ai, bi))
+    check("w8", bf16_result_to_numpy(cw), port.matmul_w8(aw, w, s))
+    # attention over heads
+    heads, length, d = 2, 192, 64
+    q, kk, v = (f32_to_bf16_bits(rng.standard_normal((heads, length, d)).astype(np.float32)) for _ in range(3))
+    out = ops.sdpa(to_device(q, bf16=True), to_device(kk, bf16=True), to_device(v, bf16=True), 0.125, capi.CAUSAL_BOTTOM_RIGHT, None, None, torch.float32)
+    torch.cuda.synchronize()
+    for h in range(heads):
+        assert rel_frobenius(out[h].cpu().numpy(), port.sdpa_bf16(q[h], kk[h], v[h], 0.125, causal=2)) <= TOL_BF16
+    # a captured CUDA graph replays the operator
+    static_c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    ops.matmul_out(da, db, static_c)  # warm-up outside the capture (first-use set-up)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ops.matmul_out(da, db, static_c)
+    static_c.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    check("bf16", bf16_result_to_numpy(static_c), port.matmul_bf16(a, b))
+    with pytest.raises(RuntimeError):
+        ops.matmul(torch.zeros(4, 4), torch.zeros(4, 4))  # no CPU implementation

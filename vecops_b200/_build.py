@@ -69,6 +69,31 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIBRARY
 
 
+TORCH_BRIDGE = LIB_DIR / "libvecops_b200_torch.so"
+
+
+def build_torch_bridge(force: bool = False, verbose: bool = False) -> Path:
+    """The Torch operator library (torch.ops.vecops_b200.*): csrc/torch/torch_bridge.cpp against the installed torch's
+    headers, linked to libvecops_b200.so beside it.  Host code only - no device code lives in it."""
+    import torch
+    from torch.utils import cpp_extension
+    library = build(force=False, verbose=verbose)
+    source = CSRC / "torch" / "torch_bridge.cpp"
+    if not force and not _stale(TORCH_BRIDGE, [source, library, *sorted(INCLUDE.rglob("*.h")), Path(__file__)]):
+        return TORCH_BRIDGE
+    includes = [f"-I{path}" for path in cpp_extension.include_paths()] + [f"-I{INCLUDE}", "-I/usr/local/cuda/include"]
+    library_dirs = cpp_extension.library_paths()
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    command = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", f"-D_GLIBCXX_USE_CXX11_ABI={abi}", *includes, str(source),
+               "-o", str(TORCH_BRIDGE), f"-L{LIB_DIR}", "-lvecops_b200", "-Wl,-rpath,$ORIGIN",
+               *[f"-L{d}" for d in library_dirs], *[f"-Wl,-rpath,{d}" for d in library_dirs], "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_cuda",
+               "-lc10_cuda"]
+    subprocess.run(command, check=True, stdout=None if verbose else subprocess.DEVNULL)
+    return TORCH_BRIDGE
+
+
 if __name__ == "__main__":
     import sys
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--torch" in sys.argv:
+        print(build_torch_bridge(force="--force" in sys.argv, verbose="-v" in sys.argv))
