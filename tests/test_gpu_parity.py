@@ -1215,3 +1215,17 @@ def test_torch_ops_reach_the_kernels(port):
     check("bf16", bf16_result_to_numpy(static_c), port.matmul_bf16(a, b))
     with pytest.raises(RuntimeError):
         ops.matmul(torch.zeros(4, 4), torch.zeros(4, 4))  # no CPU implementation
+
+
+def test_numpy_face(port):
+    from vecops_b200 import numpy_ops
+    rng = np.random.default_rng(5)
+    a, b, _ = inputs("bf16", 200, 328, 200, rng)
+    check("bf16", numpy_ops.matmul(a, b, bf16=True), port.matmul_bf16(a, b))
+    check("bf16", numpy_ops.matmul(a, b, bf16=True, out_dtype=np.float32), port.matmul_bf16(a, b, None, False))
+    af, bf, _ = inputs("f32", 96, 80, 64, rng)
+    check("f32", numpy_ops.matmul(af, bf), port.matmul_f32(af, bf))
+    ai, bi, _ = inputs("i8", 64, 48, 100, rng, np.uint8, np.int8)
+    assert np.array_equal(numpy_ops.matmul(ai, bi), port.matmul_i8(ai, bi))
+    aw, w, s = inputs("w8", 4, 256, 512, rng)
+    check("w8", numpy_ops.matmul(aw, w, s, bf16=True), port.matmul_w8(aw, w, s))
