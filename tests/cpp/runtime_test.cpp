@@ -230,21 +230,21 @@ void test_fixture_artifact(const char* fixture_path) {
 
 void test_matmul_operator() {
   auto op = make_matmul_operator();
-  require(op->schema().name() == "vecops::matmul" && op->schema().parameters().size() == 9,
-          "matmul schema has a, b, c, column_scale, cin and the four scalars of the output transform");
+  require(op->schema().name() == "vecops::matmul" && op->schema().parameters().size() == 10,
+          "matmul schema has a, b, c, column_scale, cin, the four scalars of the output transform and row_scale");
 
   auto resolve_key = [&](const KernelCall& call) {
     auto executable = op->resolve(call);
     return executable.ok() ? std::string(executable.value()->specialization_key()) : "ERROR: " + executable.status().message();
   };
   require(resolve_key(matmul_call(DType::BFloat16, DType::BFloat16, DType::BFloat16, 4096, 4096, 4096)) ==
-              "vecops::matmul;TA=bf16;TB=bf16;TC=bf16;$0=0;$1=0;kernel=bf16_tcgen05", "C2 resolves to the tcgen05 bf16 kernel");
+              "vecops::matmul;TA=bf16;TB=bf16;TC=bf16;$0=0;$1=0;$2=0;kernel=bf16_tcgen05", "C2 resolves to the tcgen05 bf16 kernel");
   require(resolve_key(matmul_call(DType::Int8, DType::Int8, DType::Int32, 4096, 14336, 4096)) ==
-              "vecops::matmul;TA=i8;TB=i8;TC=i32;$0=0;$1=0;kernel=i8_tcgen05", "C3 resolves to the tcgen05 int8 kernel");
+              "vecops::matmul;TA=i8;TB=i8;TC=i32;$0=0;$1=0;$2=0;kernel=i8_tcgen05", "C3 resolves to the tcgen05 int8 kernel");
   require(resolve_key(matmul_call(DType::BFloat16, DType::Int8, DType::BFloat16, 16, 14336, 4096, true)) ==
-              "vecops::matmul;TA=bf16;TB=i8;TC=bf16;$0=1;$1=0;kernel=w8_small_m", "C4 resolves to the weight-only kernel");
+              "vecops::matmul;TA=bf16;TB=i8;TC=bf16;$0=1;$1=0;$2=0;kernel=w8_small_m", "C4 resolves to the weight-only kernel");
   require(resolve_key(matmul_call(DType::BFloat16, DType::Int8, DType::BFloat16, 128, 14336, 4096, true)) ==
-              "vecops::matmul;TA=bf16;TB=i8;TC=bf16;$0=1;$1=0;kernel=w8_tcgen05", "C4 at M=128 resolves to the tensor-memory weight-only kernel");
+              "vecops::matmul;TA=bf16;TB=i8;TC=bf16;$0=1;$1=0;$2=0;kernel=w8_tcgen05", "C4 at M=128 resolves to the tensor-memory weight-only kernel");
   {
     // that kernel is the one that needs device scratch: the executable reports it, and refuses to run without it
     auto call = matmul_call(DType::BFloat16, DType::Int8, DType::BFloat16, 128, 14336, 4096, true);
@@ -257,9 +257,9 @@ void test_matmul_operator() {
     require(!refused.ok() && refused.code() == StatusCode::InvalidArgument, "invoke without the scratch is refused before run");
   }
   require(resolve_key(matmul_call(DType::Float32, DType::Float32, DType::Float32, 1024, 1024, 1024)) ==
-              "vecops::matmul;TA=f32;TB=f32;TC=f32;$0=0;$1=0;kernel=f32_simt", "C1 resolves to the FP32 kernel");
+              "vecops::matmul;TA=f32;TB=f32;TC=f32;$0=0;$1=0;$2=0;kernel=f32_simt", "C1 resolves to the FP32 kernel");
   require(resolve_key(matmul_call(DType::BFloat16, DType::BFloat16, DType::Float32, 16, 16, 35)) ==
-              "vecops::matmul;TA=bf16;TB=bf16;TC=f32;$0=0;$1=0;kernel=generic", "an unaligned K falls to the strided kernel");
+              "vecops::matmul;TA=bf16;TB=bf16;TC=f32;$0=0;$1=0;$2=0;kernel=generic", "an unaligned K falls to the strided kernel");
 
   {
     // the fused form COut = activation((CIn + A.B^T) * alpha): a bias row as a stride-0 accumulator input and SiLU
@@ -270,7 +270,7 @@ void test_matmul_operator() {
     fused.emplace_back(Scalar::floating(1.0, DType::Float32));
     fused.emplace_back(Scalar::signed_integer(VECOPS_B200_ACTIVATION_SILU, DType::Int32));
     auto key = resolve_key(KernelCall(ArgumentMetadata(fused)));
-    require(key == "vecops::matmul;TA=bf16;TB=bf16;TC=bf16;$0=0;$1=1;$2=f32;kernel=bf16_tcgen05",
+    require(key == "vecops::matmul;TA=bf16;TB=bf16;TC=bf16;$0=0;$1=1;$2=f32;$3=0;kernel=bf16_tcgen05",
             "a fused call resolves to the same kernel; the accumulator input's presence and dtype enter the key, the scalars do not");
     std::vector<Value> bad_scalar = fused;
     bad_scalar[6] = Scalar::floating(3.0, DType::Float32);
@@ -321,7 +321,7 @@ void test_matmul_operator() {
 
   // descriptor templates state each variant's constraints
   const auto* d = vecops_b200_matmul_descriptor(VECOPS_B200_KERNEL_I8_TCGEN05);
-  require(d != nullptr && d->num_parameters == 9 && d->parameters[4].constraint.tensor.optional != 0 && d->parameters[6].kind == VECOPS_VALUE_SCALAR && d->parameters[0].constraint.tensor.device_type == VECOPS_DEVICE_CUDA &&
+  require(d != nullptr && d->num_parameters == 10 && d->parameters[9].constraint.tensor.optional != 0 && d->parameters[4].constraint.tensor.optional != 0 && d->parameters[6].kind == VECOPS_VALUE_SCALAR && d->parameters[0].constraint.tensor.device_type == VECOPS_DEVICE_CUDA &&
               d->parameters[0].constraint.tensor.strides[0].alignment == 16 && d->run != nullptr && d->workspace != nullptr,
           "int8 descriptor wants CUDA tensors with 16-element row pitches");
   require(vecops_b200_matmul_descriptor(VECOPS_B200_KERNEL_AUTO) == nullptr, "AUTO has no descriptor");

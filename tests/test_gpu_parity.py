@@ -580,7 +580,7 @@ def test_operator_bridge_carries_the_fused_form(port):
     error = capi.ErrorBuffer()
     key = ctypes.create_string_buffer(256)
     error.raise_for(lib.vecops_b200_operator_resolve(handle, byref(call), key, 256, byref(error.record)))
-    assert key.value.decode() == "vecops::matmul;TA=bf16;TB=bf16;TC=bf16;$0=0;$1=1;$2=f32;kernel=bf16_tcgen05"
+    assert key.value.decode() == "vecops::matmul;TA=bf16;TB=bf16;TC=bf16;$0=0;$1=1;$2=f32;$3=0;kernel=bf16_tcgen05"
     error.raise_for(lib.vecops_operator_bridge_invoke_v1(handle, byref(call), 0, None, byref(error.record)))
     want = port.matmul_bf16_fused(a, b, bias, 0.5, None, ACT_CLAMP, -0.75, 1.25)
     check("bf16", bf16_result_to_numpy(c), want)
@@ -1195,6 +1195,16 @@ def test_torch_ops_reach_the_kernels(port):
     torch.cuda.synchronize()
     assert np.array_equal(ci.cpu().numpy(), port.matmul_i8(ai, bi))
     check("w8", bf16_result_to_numpy(cw), port.matmul_w8(aw, w, s))
+    # per-token quantised product through the operator layer: u8 x s8, correction row, row and column factors -> f32, bit-exact
+    from oracle.checker import pack_compensation
+    aq = rng.integers(0, 256, (m, k)).astype(np.uint8)
+    bq = rng.integers(-128, 128, (n, k), dtype=np.int8)
+    correction = pack_compensation(bq, 9)
+    row_factors, column_factors = rng.uniform(0.01, 0.1, m).astype(np.float32), rng.uniform(0.01, 0.05, n).astype(np.float32)
+    cq = ops.matmul(to_device(aq), to_device(bq), to_device(column_factors), to_device(correction), 1.0, 0, 0.0, 0.0, torch.float32,
+                    to_device(row_factors))
+    torch.cuda.synchronize()
+    assert np.array_equal(cq.cpu().numpy(), port.matmul_i8_dequant_rows(aq, bq, correction, row_factors, column_factors))
     # attention over heads
     heads, length, d = 2, 192, 64
     q, kk, v = (f32_to_bf16_bits(rng.standard_normal((heads, length, d)).astype(np.float32)) for _ in range(3))

@@ -44,12 +44,12 @@ constexpr VecopsDimensionConstraint aligned_dim(std::int64_t alignment) {
   return {sizeof(VecopsDimensionConstraint), VECOPS_DIM_DYNAMIC, 0, 0, INT64_MAX, alignment};
 }
 
-// Parameters of every matmul specialization: a, b, c, column_scale?, cin?, alpha, activation, clamp_lo, clamp_hi.
-constexpr std::uint32_t kMatmulParameters = 9;
+// Parameters of every matmul specialization: a, b, c, column_scale?, cin?, alpha, activation, clamp_lo, clamp_hi, row_scale?.
+constexpr std::uint32_t kMatmulParameters = 10;
 
 struct VariantDescriptor {
   VecopsDimensionConstraint a_sizes[2], a_strides[2], b_sizes[2], b_strides[2], c_sizes[2], c_strides[2], s_sizes[1], s_strides[1],
-      cin_sizes[2], cin_strides[2];
+      cin_sizes[2], cin_strides[2], r_sizes[1], r_strides[1];
   VecopsParameterDescriptor parameters[kMatmulParameters];
   VecopsKernelDescriptorV1 descriptor;
 };
@@ -125,6 +125,10 @@ VariantDescriptor* build_variant(std::uint64_t a_mask, std::uint64_t b_mask, std
   v->parameters[6] = scalar_parameter("activation", bit(VECOPS_DTYPE_I32));
   v->parameters[7] = scalar_parameter("clamp_lo", bit(VECOPS_DTYPE_F32));
   v->parameters[8] = scalar_parameter("clamp_hi", bit(VECOPS_DTYPE_F32));
+  // one factor per output row: the row half of vecops' row-by-column dequantisation (matmul/Quantization.h:195-246)
+  v->r_sizes[0] = any_dim();
+  v->r_strides[0] = const_dim(1);
+  v->parameters[9] = tensor_parameter("row_scale", bit(VECOPS_DTYPE_F32), 1, v->r_sizes, v->r_strides, true, false);
   auto& d = v->descriptor;
   d.struct_size = sizeof(VecopsKernelDescriptorV1);
   d.abi_version_major = VECOPS_KERNEL_ABI_VERSION_MAJOR;
@@ -175,12 +179,13 @@ std::int32_t fail(VecopsError* error, std::int32_t code, const char* message) {
 std::int32_t problem_from_frame(const VecopsCall* call, std::uint32_t kernel, VecopsB200Matmul* out, VecopsB200Epilogue* fused,
                                 VecopsError* error) {
   if (call == nullptr || call->struct_size < sizeof(VecopsCall)) return fail(error, VECOPS_STATUS_ABI_MISMATCH, "call frame is null or too small");
-  // a, b, c, then - each optional from the right - column_scale, cin (absent or VECOPS_VALUE_NONE = none), and the
-  // scalars alpha, activation, clamp_lo, clamp_hi (absent = 1, none, 0, 0)
+  // a, b, c, then - each optional from the right - column_scale, cin (absent or VECOPS_VALUE_NONE = none), the
+  // scalars alpha, activation, clamp_lo, clamp_hi (absent = 1, none, 0, 0) and row_scale (absent or NONE = none)
   if (call->num_values < 3 || call->num_values > kMatmulParameters || call->values == nullptr)
     return fail(error, VECOPS_STATUS_INVALID_ARGUMENT,
-                "matmul expects a, b, c and optionally column_scale, cin, alpha, activation, clamp_lo, clamp_hi");
+                "matmul expects a, b, c and optionally column_scale, cin, alpha, activation, clamp_lo, clamp_hi, row_scale");
   const VecopsTensorView* t[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+  const VecopsTensorView* row_scale = nullptr;
   VecopsB200Epilogue e{};
   e.struct_size = sizeof(VecopsB200Epilogue);
   e.alpha = 1.f;
@@ -189,6 +194,13 @@ std::int32_t problem_from_frame(const VecopsCall* call, std::uint32_t kernel, Ve
     if (i < 5) {
       if (value.kind == VECOPS_VALUE_TENSOR) t[i] = &value.value.tensor;
       else if (!(i >= 3 && value.kind == VECOPS_VALUE_NONE)) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "matmul operands must be tensors");
+      continue;
+    }
+    if (i == 9) {
+      if (value.kind == VECOPS_VALUE_NONE) continue;
+      if (value.kind != VECOPS_VALUE_TENSOR || value.value.tensor.rank != 1 || value.value.tensor.dtype != VECOPS_DTYPE_F32)
+        return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "row_scale is a rank-1 f32 tensor");
+      row_scale = &value.value.tensor;
       continue;
     }
     if (value.kind != VECOPS_VALUE_SCALAR) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "alpha, activation, clamp_lo and clamp_hi are scalars");
@@ -234,6 +246,11 @@ std::int32_t problem_from_frame(const VecopsCall* call, std::uint32_t kernel, Ve
     e.cin_stride_n = t[4]->strides[1];
     e.cin_dtype = t[4]->dtype;
   }
+  if (row_scale != nullptr) {
+    if (row_scale->sizes[0] != p.m || (row_scale->strides[0] != 1 && p.m > 1))
+      return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "row_scale must be a contiguous tensor of M factors");
+    e.row_scale = reinterpret_cast<const float*>(base(row_scale));
+  }
   p.a_dtype = t[0]->dtype;
   p.b_dtype = t[1]->dtype;
   p.c_dtype = t[2]->dtype;
@@ -252,7 +269,9 @@ std::int32_t problem_from_frame(const VecopsCall* call, std::uint32_t kernel, Ve
   return VECOPS_STATUS_OK;
 }
 
-bool transform_present(const VecopsB200Epilogue& e) { return e.cin != nullptr || e.alpha != 1.f || e.activation != VECOPS_B200_ACTIVATION_NONE; }
+bool transform_present(const VecopsB200Epilogue& e) {
+  return e.cin != nullptr || e.alpha != 1.f || e.activation != VECOPS_B200_ACTIVATION_NONE || e.row_scale != nullptr;
+}
 
 std::int32_t run_with(std::uint32_t kernel, const VecopsCall* call, VecopsError* error, bool only_workspace, std::uint64_t* bytes) {
   VecopsB200Matmul problem;
@@ -293,7 +312,8 @@ KernelDef matmul_kernel_def() {
                     ValueDef{"alpha", DType::Float32, Scalar::floating(1.0, DType::Float32)},
                     ValueDef{"activation", DType::Int32, Scalar::signed_integer(0, DType::Int32)},
                     ValueDef{"clamp_lo", DType::Float32, Scalar::floating(0.0, DType::Float32)},
-                    ValueDef{"clamp_hi", DType::Float32, Scalar::floating(0.0, DType::Float32)}},
+                    ValueDef{"clamp_hi", DType::Float32, Scalar::floating(0.0, DType::Float32)},
+                    tensor("row_scale", {M()}, DType::Float32, TensorAccess::Input, true)},
                    {{"TA", SpecializationType::DType}, {"TB", SpecializationType::DType}, {"TC", SpecializationType::DType}});
 }
 

@@ -80,7 +80,8 @@ VecopsValue scalar_value(uint32_t dtype, double real, int64_t integer) {
 
 // c = activation((cin + a . b_nk^T) * alpha * column_scale), written into `c`
 void matmul_out(const at::Tensor& a, const at::Tensor& b_nk, at::Tensor& c, const c10::optional<at::Tensor>& column_scale,
-                const c10::optional<at::Tensor>& cin, double alpha, int64_t activation, double clamp_lo, double clamp_hi) {
+                const c10::optional<at::Tensor>& cin, double alpha, int64_t activation, double clamp_lo, double clamp_hi,
+                const c10::optional<at::Tensor>& row_scale) {
   TORCH_CHECK(a.is_cuda() && b_nk.is_cuda() && c.is_cuda(), "vecops_b200.matmul: CUDA tensors only (there is no CPU path)");
   TORCH_CHECK(a.dim() == 2 && b_nk.dim() == 2 && c.dim() == 2, "vecops_b200.matmul: a [M,K], b_nk [N,K], c [M,N]");
   const c10::cuda::CUDAGuard guard(c.device());
@@ -89,7 +90,8 @@ void matmul_out(const at::Tensor& a, const at::Tensor& b_nk, at::Tensor& c, cons
   at::Tensor cin_view;
   if (has_cin) cin_view = cin->expand({c.size(0), c.size(1)});  // a bias row or a column becomes a stride-0 view
   std::vector<VecopsValue> values{tensor_value(a, false), tensor_value(b_nk, false), tensor_value(c, true)};
-  const bool fused = has_cin || alpha != 1.0 || activation != 0;
+  const bool has_row = row_scale.has_value() && row_scale->defined();
+  const bool fused = has_cin || alpha != 1.0 || activation != 0 || has_row;
   if (has_scale || fused) values.push_back(has_scale ? tensor_value(*column_scale, false) : none_value());
   if (fused) {
     values.push_back(has_cin ? tensor_value(cin_view, false) : none_value());
@@ -97,6 +99,7 @@ void matmul_out(const at::Tensor& a, const at::Tensor& b_nk, at::Tensor& c, cons
     values.push_back(scalar_value(VECOPS_DTYPE_I32, 0.0, activation));
     values.push_back(scalar_value(VECOPS_DTYPE_F32, clamp_lo, 0));
     values.push_back(scalar_value(VECOPS_DTYPE_F32, clamp_hi, 0));
+    if (has_row) values.push_back(tensor_value(*row_scale, false));
   }
   VecopsExecutionContext context{};
   context.struct_size = sizeof(VecopsExecutionContext);
@@ -122,13 +125,13 @@ void matmul_out(const at::Tensor& a, const at::Tensor& b_nk, at::Tensor& c, cons
 
 at::Tensor matmul(const at::Tensor& a, const at::Tensor& b_nk, const c10::optional<at::Tensor>& column_scale,
                   const c10::optional<at::Tensor>& cin, double alpha, int64_t activation, double clamp_lo, double clamp_hi,
-                  c10::optional<at::ScalarType> out_dtype) {
+                  c10::optional<at::ScalarType> out_dtype, const c10::optional<at::Tensor>& row_scale) {
   TORCH_CHECK(a.dim() == 2 && b_nk.dim() == 2, "vecops_b200.matmul: a [M,K], b_nk [N,K]");
   at::ScalarType type = a.scalar_type();
   if (out_dtype.has_value()) type = *out_dtype;
   else if (a.scalar_type() == at::kChar || a.scalar_type() == at::kByte) type = at::kInt;  // 8-bit operands accumulate in int32
   at::Tensor c = at::empty({a.size(0), b_nk.size(0)}, a.options().dtype(type));
-  matmul_out(a, b_nk, c, column_scale, cin, alpha, activation, clamp_lo, clamp_hi);
+  matmul_out(a, b_nk, c, column_scale, cin, alpha, activation, clamp_lo, clamp_hi, row_scale);
   return c;
 }
 
@@ -192,9 +195,9 @@ at::Tensor sdpa(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, d
 
 TORCH_LIBRARY(vecops_b200, m) {
   m.def("matmul(Tensor a, Tensor b_nk, Tensor? column_scale=None, Tensor? cin=None, float alpha=1.0, int activation=0, float clamp_lo=0.0, "
-        "float clamp_hi=0.0, ScalarType? out_dtype=None) -> Tensor");
+        "float clamp_hi=0.0, ScalarType? out_dtype=None, Tensor? row_scale=None) -> Tensor");
   m.def("matmul_out(Tensor a, Tensor b_nk, Tensor(a!) c, Tensor? column_scale=None, Tensor? cin=None, float alpha=1.0, int activation=0, "
-        "float clamp_lo=0.0, float clamp_hi=0.0) -> ()");
+        "float clamp_lo=0.0, float clamp_hi=0.0, Tensor? row_scale=None) -> ()");
   m.def("sdpa(Tensor q, Tensor k, Tensor v, float scale, int causal=0, Tensor? key_mask=None, Tensor? bias=None, ScalarType? out_dtype=None) -> Tensor");
 }
 

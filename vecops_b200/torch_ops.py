@@ -2,8 +2,8 @@
 
 ``load()`` registers three operators implemented in C++ (csrc/torch/torch_bridge.cpp) for CUDA tensors:
 
-    torch.ops.vecops_b200.matmul(a, b_nk, column_scale=None, cin=None, alpha=1.0, activation=0, clamp_lo=0.0, clamp_hi=0.0, out_dtype=None)
-    torch.ops.vecops_b200.matmul_out(a, b_nk, c, column_scale=None, cin=None, alpha=1.0, activation=0, clamp_lo=0.0, clamp_hi=0.0)
+    torch.ops.vecops_b200.matmul(a, b_nk, column_scale=None, cin=None, alpha=1.0, activation=0, clamp_lo=0.0, clamp_hi=0.0, out_dtype=None, row_scale=None)
+    torch.ops.vecops_b200.matmul_out(a, b_nk, c, column_scale=None, cin=None, alpha=1.0, activation=0, clamp_lo=0.0, clamp_hi=0.0, row_scale=None)
     torch.ops.vecops_b200.sdpa(q, k, v, scale, causal=0, key_mask=None, bias=None, out_dtype=None)
 
 A call goes dispatcher -> C++ -> operator bridge -> kernel on the current CUDA stream; Python is not on that path.
