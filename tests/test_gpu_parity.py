@@ -357,6 +357,15 @@ def test_operator_bridge_async_on_a_side_stream(port):
     stream.wait_stream(torch.cuda.current_stream())
     call, keep = bridge_call(da, db, c, stream=stream, asynchronous=True)
     error = capi.ErrorBuffer()
+    # eight tiles on 148 SMs are cut along K: the executable asks for the scratch the slices meet in, as the contract has it
+    lib.vecops_b200_operator_workspace.argtypes = [ctypes.c_uint64, ctypes.POINTER(capi.VecopsCall), ctypes.POINTER(ctypes.c_uint64),
+                                                   ctypes.POINTER(capi.VecopsError)]
+    need = ctypes.c_uint64(0)
+    error.raise_for(lib.vecops_b200_operator_workspace(handle, byref(call), byref(need), byref(error.record)))
+    assert need.value > 0
+    assert lib.vecops_operator_bridge_invoke_v1(handle, byref(call), 0, None, byref(capi.ErrorBuffer().record)) == capi.INVALID_ARGUMENT  # none given
+    scratch = torch.empty(need.value, dtype=torch.uint8, device="cuda")
+    call.workspace, call.workspace_size = scratch.data_ptr(), need.value
     error.raise_for(lib.vecops_operator_bridge_invoke_v1(handle, byref(call), 0, None, byref(error.record)))
     stream.synchronize()
     status = ctypes.c_uint32(1)

@@ -372,6 +372,17 @@ Tcgen05Plan plan_tcgen05(const VecopsB200Matmul& p, bool int8, size_t out_elem, 
   }
   if (!tail_split_forced_off()) plan.split = gemm_tail_split(plan.tiles, plan.workers, plan.num_kb, G::max_split(out_elem));
   if (plan.split > 1) plan.scratch_slots = (plan.tiles % plan.workers) * plan.split * (plan.pair ? 2 : 1);
+  // Fewer tiles than SMs (a skinny product with a long K, such as probabilities x values in attention): every tile is
+  // a "tail" tile, cut along K over as many CTAs as the SMs hold - the same exchange, just with no whole round before it.
+  if (!plan.pair && plan.split == 1 && plan.tiles < sms && !tail_split_forced_off()) {
+    int split = 1;
+    while (split * 2 <= G::max_split(out_elem) && plan.tiles * (split * 2) <= sms && split * 2 * G::kMinSliceKb <= plan.num_kb) split *= 2;
+    if (split > 1) {
+      plan.split = split;
+      plan.workers = static_cast<int>(plan.tiles * split);
+      plan.scratch_slots = plan.tiles * split;
+    }
+  }
   return plan;
 }
 
