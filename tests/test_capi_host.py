@@ -140,3 +140,23 @@ def test_torch_operator_library_registers_its_schemas():
     assert "int causal=0" in str(torch.ops.vecops_b200.sdpa.default._schema)
     with pytest.raises((RuntimeError, NotImplementedError)):
         torch.ops.vecops_b200.matmul(torch.zeros(4, 4), torch.zeros(4, 4))
+
+
+def test_ctypes_records_match_the_header(tmp_path):
+    # the header compiled by gcc is the authority: sizes and the offsets of late fields of every record the Python binding mirrors
+    import subprocess
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    records = {"VecopsB200Matmul": "reserved", "VecopsB200Epilogue": "row_scale", "VecopsB200Batch": "cin_stride_b", "VecopsB200Pack": "stream",
+               "VecopsB200Attention": "bias_stride_head", "VecopsB200Gather": "flags"}
+    lines = "".join(f'  printf("{name} %zu %zu\\n", sizeof({name}), offsetof({name}, {field}));\n' for name, field in records.items())
+    source = tmp_path / "sizes.c"
+    source.write_text('#include <stddef.h>\n#include <stdio.h>\n#include "vecops_b200/matmul_cuda.h"\nint main(void) {\n' + lines + "  return 0;\n}\n")
+    binary = tmp_path / "sizes"
+    subprocess.run(["gcc", "-std=c11", f"-I{root / 'include'}", str(source), "-o", str(binary)], check=True)
+    out = subprocess.run([str(binary)], check=True, capture_output=True, text=True).stdout.split("\n")
+    for line in filter(None, out):
+        name, size, offset = line.split()
+        record = getattr(capi, name)
+        assert ctypes.sizeof(record) == int(size), name
+        assert getattr(record, records[name]).offset == int(offset), name
