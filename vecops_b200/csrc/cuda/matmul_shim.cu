@@ -1256,7 +1256,14 @@ static int32_t quantize_rows_impl(const void* src, uint32_t src_dtype, int64_t s
   const bool is_signed = dst_dtype == VECOPS_DTYPE_I8;
   const bool by_four = src_dtype == VECOPS_DTYPE_F32 && src_stride_k == 1 && cols % 4 == 0 && aligned16(src) && src_stride_m % 4 == 0 &&
                        (reinterpret_cast<uintptr_t>(dst) & 3u) == 0 && dst_stride_m % 4 == 0;
-  if (by_four) {
+  const bool by_sixteen = by_four && cols % 16 == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 && dst_stride_m % 16 == 0;
+  if (by_sixteen) {
+    const long long groups = rows * (cols / 16);
+    const int grid16 = static_cast<int>(groups / 256 + 1 < 148 * 32 ? groups / 256 + 1 : 148 * 32);
+    const float* in = static_cast<const float*>(src);
+    if (is_signed) quantize_rows_f32x16_kernel<true><<<grid16, 256, 0, s>>>(in, src_stride_m, out, dst_stride_m, rows, cols / 16, scale, zero_point, multipliers);
+    else quantize_rows_f32x16_kernel<false><<<grid16, 256, 0, s>>>(in, src_stride_m, out, dst_stride_m, rows, cols / 16, scale, zero_point, multipliers);
+  } else if (by_four) {
     const long long groups = rows * (cols / 4);
     const int grid4 = static_cast<int>(groups / 256 + 1 < 148 * 16 ? groups / 256 + 1 : 148 * 16);
     const float* in = static_cast<const float*>(src);
