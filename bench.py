@@ -3,10 +3,12 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--no-extra]
 
-N = 1   headline workload: BF16 GEMM M=N=K=4096 (fp32 accumulate, bf16 out).  The other single-GPU
-        configurations are measured briefly and reported under "configs".
-N > 1   the large BF16 GEMM M=16384 N=53248 K=8192, B column-sharded over the ranks (one process per GPU,
-        launched by torch.distributed.run), A replicated, output slabs all-gathered over NCCL: strong scaling.
+Headline workload at EVERY N (1, 2, 4, 8): the large BF16 GEMM M=16384 N=53248 K=8192, B column-sharded over the ranks
+(one process per GPU, launched by torch.distributed.run), A replicated, the output gathered on every rank by the GEMM's
+own epilogue - strong scaling, so the per-N values form one curve.  It fits one GPU (2.9 GB), where the slab is the
+whole result.  At N = 1 the other single-GPU configurations (BF16 4096^3, FP32 1024^3, INT8 4096x14336x4096, the three
+weight-only decode shapes) are measured too and reported under "configs", each with its own `roofline`,
+`cpu_baseline` and `e2e` record.
 
 A step is one pass of the operator over one batch of synthetic input.  `value` is measured with the operands
 resident in HBM (CUDA events on the launching stream, max over ranks); `e2e` runs the same step through the
@@ -31,11 +33,22 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 METRIC = "GEMM TFLOP/s (BF16/INT8) & GB/s (decode) at 1/2/4/8 B200, % of roofline"
-NOMINAL = {"bf16_tflops": 2250.0, "i8_tops": 4500.0, "hbm_gbs": 8000.0, "fp32_tflops": 80.0}
+NOMINAL = {"bf16_tflops": 2250.0, "i8_tops": 4500.0, "hbm_gbs": 8000.0, "fp32_tflops": 74.4}  # fp32: 148 SMs x 128 FMA lanes x 2 x 1.965 GHz
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
-# under profiles/ (None until a capture exists for that workload).
-NCU_TRAFFIC_BYTES = {"c2_bf16_4096": 99.3e6, "c5_bf16_16384x53248x8192": None}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, read from one ncu capture of that
+# workload, with the committed summary the figure was taken from.  A workload without a capture reports null.
+NCU_TRAFFIC = {
+    "c1_f32_1024": (8.45e6, "profiles/gemm_f32__c1_f32_1024.md"),
+    "c2_bf16_4096": (99.3e6, "profiles/gemm_tcgen05_bf16__c2_bf16_4096.md"),
+    "c3_i8_4096x14336x4096": (282.6e6, "profiles/gemm_tcgen05_i8__c3_i8_4096x14336x4096.md"),
+    "c4_w8_m16": (59.3e6, "profiles/w8_stream__c4_w8_m16.md"),
+    "c4_w8_m128": (63.1e6, "profiles/w8_tcgen05__c4_w8_m128.md"),
+}
+# What a GPU can receive when all eight send to all eight at once: a store-only all-to-all probe on this pool
+# (148 CTAs per GPU issuing the epilogue's own 32-row x 128-byte TMA stores to the seven peers) measured 668 GB/s per
+# direction per GPU.  Not measured in this run; it bounds "result gathered on every rank" from below.
+NVLINK_RECEIVE_GBS = 668.0
+BURST_BELOW_MS = 5.0  # kernels shorter than this are held to the burst cuBLAS figure, longer ones to the sustained one
 
 
 def measured_peaks() -> tuple[dict, str]:
@@ -168,11 +181,11 @@ def time_graph(prepared, steps: int, warmup: int, dev) -> float:
     return start.elapsed_time(stop) / steps
 
 
-def take_status() -> int:
+def take_status(device: int = 0) -> int:
     from vecops_b200 import capi
     status = ctypes.c_uint32(0)
     error = capi.ErrorBuffer()
-    capi.library().vecops_b200_take_device_status(0, byref(status), byref(error.record))
+    capi.library().vecops_b200_take_device_status(device, byref(status), byref(error.record))
     return status.value
 
 
@@ -193,32 +206,55 @@ def parity_sample(w, host_inputs, c, port, rows: int = 16) -> dict:
     return {"rows": len(pick), "rel_fro": rel_frobenius(got, bf16_bits_to_f32(want))}
 
 
-def bound_of(w, peaks) -> tuple[str, float, float, str]:
-    """(bound, measured peak, nominal peak, unit) of the roofline that limits workload `w`."""
+def bound_of(w, peaks, peak_source: str, kernel_ms: float) -> tuple[str, float, float, str, str]:
+    """(bound, peak, nominal peak, unit, where the peak comes from) of the roofline that limits workload `w`."""
+    burst = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    sustained = float(peaks.get("bf16_tflops_sustained", burst))
+    tensor, which = (burst, "burst") if kernel_ms < BURST_BELOW_MS else (sustained, "sustained")
     if w.kind == "bf16":
-        return "tensor", float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])), NOMINAL["bf16_tflops"], "TFLOP/s"
+        return "tensor", tensor, NOMINAL["bf16_tflops"], "TFLOP/s", f"{peak_source}: cuBLAS bf16 {which} ({'<' if which == 'burst' else '>='} {BURST_BELOW_MS:g} ms per launch)"
     if w.kind == "i8":
-        # no measured int8 figure is provided: int8 dense is twice the bf16 rate on this part
-        return "tensor", 2.0 * float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])), NOMINAL["i8_tops"], "TOP/s"
+        return "tensor", 2.0 * tensor, NOMINAL["i8_tops"], "TOP/s", f"ASSUMED 2 x the {peak_source} cuBLAS bf16 {which} figure: no int8 peak is measured on this pool"
     if w.kind == "w8":
-        return "hbm", float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])), NOMINAL["hbm_gbs"], "GB/s"
-    return "fp32_fma", NOMINAL["fp32_tflops"], NOMINAL["fp32_tflops"], "TFLOP/s"
+        return "hbm", float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])), NOMINAL["hbm_gbs"], "GB/s", f"{peak_source}: device-to-device copy"
+    return "fp32_fma", NOMINAL["fp32_tflops"], NOMINAL["fp32_tflops"], "TFLOP/s", "nominal FP32 FMA rate (128 lanes x 148 SMs x 2 x 1.965 GHz); no measured figure exists"
 
 
-def measure_single(name: str, steps: int, warmup: int, dev, port, peaks, fused: bool = False) -> dict:
-    """One single-GPU configuration with operands resident in HBM.  `fused`: the same launches with a bias row as the
-    accumulator input and SiLU as the output transform (what the fused epilogue costs on top of the plain GEMM)."""
+def roofline_record(w, name: str, kernel: str, kernel_ms: float, flops: float, algorithmic_bytes: float, peaks, peak_source: str) -> dict:
+    """The roofline object of one kernel launch: achieved = algorithmic work per launch / measured launch time."""
+    bound, peak, nominal, unit, source = bound_of(w, peaks, peak_source, kernel_ms)
+    seconds = kernel_ms * 1e-3
+    achieved = algorithmic_bytes / seconds / 1e9 if bound == "hbm" else flops / seconds / 1e12
+    traffic, traffic_from = NCU_TRAFFIC.get(name, (None, None))
+    return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak, "traffic": traffic,
+            "traffic_source": traffic_from, "peak_source": source, "frac_of_nominal": achieved / nominal, "nominal_peak": nominal,
+            "kernel": kernel, "kernel_ms": kernel_ms, "algorithmic_flops_per_launch": flops,
+            "algorithmic_bytes_per_launch": algorithmic_bytes}
+
+
+def operand_sets_for(w) -> int:
+    """Operand sets to rotate so that no launch finds its operands in the 126 MB L2."""
+    l2 = 126e6
+    return 1 if w.algorithmic_bytes > 1.5 * l2 else int(np.ceil(1.6 * l2 / w.algorithmic_bytes)) + 1
+
+
+def measure_single(name: str, steps: int, warmup: int, dev, port, peaks, peak_source: str = "measured", fused: bool = False,
+                   full_record: bool = True) -> dict:
+    """One single-GPU configuration: the kernel with operands resident in HBM (value, roofline), the same step end to end
+    through the operator bridge with host buffers (e2e), and the reference's CPU matmul on the host cores (cpu_baseline).
+    `fused`: the same launches with a bias row as the accumulator input and SiLU as the output transform (what the fused
+    epilogue costs on top of the plain GEMM); kernel figures only."""
     import torch
 
     import vecops_b200
     from vecops_b200 import capi, harness, workloads
     w = workloads.WORKLOADS[name]
-    l2 = 126e6
     per_set = w.algorithmic_bytes
-    sets = 1 if per_set > 1.5 * l2 else int(np.ceil(1.6 * l2 / per_set)) + 1
+    sets = operand_sets_for(w)
     operands, host_inputs = device_sets(w, sets, dev)
     stream = torch.cuda.current_stream(dev)
     kernel = vecops_b200.select_kernel(vecops_b200.matmul_problem(operands[0]["a"], operands[0]["b"], operands[0]["c"], operands[0]["scale"]))
+    kernel_name = capi.library().vecops_b200_kernel_name(kernel).decode()
 
     if fused:
         from oracle.checker import ACT_SILU, bf16_bits_to_f32, rel_frobenius
@@ -238,16 +274,37 @@ def measure_single(name: str, steps: int, warmup: int, dev, port, peaks, fused: 
         prepared[0].launch()
         torch.cuda.synchronize()
         parity = parity_sample(w, host_inputs, operands[0]["c"], port)
+    before = capi.library().vecops_b200_launch_count()
     ms = time_graph(prepared, steps, warmup, dev)
-    status = take_status()
-    bound, peak, nominal, unit = bound_of(w, peaks)
-    achieved = (per_set / (ms * 1e-3) / 1e9) if bound == "hbm" else (w.flops / (ms * 1e-3) / 1e12)
-    return {"workload": name + (" + bias row + SiLU, fused" if fused else ""), "kernel": capi.library().vecops_b200_kernel_name(kernel).decode(),
-            "ms_per_step": ms,
-            "value": achieved, "unit": unit, "bound": bound, "frac_of_measured_peak": achieved / peak,
-            "frac_of_nominal_peak": achieved / nominal, "tflops": w.flops / (ms * 1e-3) / 1e12,
-            "algorithmic_gb_per_s": per_set / (ms * 1e-3) / 1e9, "l2": f"rotating {sets} operand sets ({sets * per_set / 1e6:.0f} MB) vs L2 126 MB",
-            "launch": "one CUDA graph of all timed launches", "parity": parity, "device_status": status}
+    launches = capi.library().vecops_b200_launch_count() - before  # counted while the graphs were captured: steps + warm-up + set-up
+    status = take_status(dev.index or 0)
+    roofline = roofline_record(w, name, kernel_name, ms, w.flops, per_set, peaks, peak_source)
+    record = {"workload": name + (" + bias row + SiLU, fused" if fused else ""), "description": w.description, "kernel": kernel_name,
+              "ms_per_step": ms, "steps": steps, "warmup": warmup, "value": roofline["achieved"], "unit": roofline["unit"],
+              "tflops": w.flops / (ms * 1e-3) / 1e12, "algorithmic_gb_per_s": per_set / (ms * 1e-3) / 1e9,
+              "roofline": roofline, "gpu_launches_captured": int(launches),
+              "l2": f"rotating {sets} operand sets ({sets * per_set / 1e6:.0f} MB) vs L2 126 MB",
+              "launch": "one CUDA graph of all timed launches, CUDA events around its replay", "parity": parity, "device_status": status}
+    if fused or not full_record:
+        return record
+    try:
+        e2e_steps = 20 if w.kind != "w8" else 200
+        e2e = measure_e2e(w, operands, host_inputs, e2e_steps, 3, dev, resident_weights=w.kind == "w8")
+        work = per_set / 1e9 if roofline["bound"] == "hbm" else w.flops / 1e12
+        record["e2e"] = {"value": work / (e2e["ms_per_step"] * 1e-3), "unit": roofline["unit"], "ms_per_step": e2e["ms_per_step"],
+                         "serial_ms_per_step": e2e["serial_ms_per_step"], "serial_value": work / (e2e["serial_ms_per_step"] * 1e-3),
+                         "h2d_bytes_per_step": e2e["h2d_bytes_per_step"], "d2h_bytes_per_step": e2e["d2h_bytes_per_step"], "steps": e2e_steps,
+                         "resident": e2e["resident"], "host_overhead_us_per_call": e2e["host_us_per_call"],
+                         "path": "vecops_operator_bridge_invoke_v1, pinned host buffers, copies inside the timed region"}
+    except Exception as error:  # noqa: BLE001 - a failed side measurement must not lose the kernel number
+        record["e2e"] = {"error": repr(error)}
+    del operands, prepared
+    torch.cuda.empty_cache()
+    try:
+        record["cpu_baseline"] = cpu_baseline(w)
+    except Exception as error:  # noqa: BLE001
+        record["cpu_baseline"] = {"error": repr(error)}
+    return record
 
 
 def measure_f16(steps: int, warmup: int, dev, port, peaks) -> dict:
@@ -276,7 +333,7 @@ def measure_f16(steps: int, warmup: int, dev, port, peaks) -> dict:
     return {"workload": "fp16 x fp16 -> fp16, M=N=K=4096, fp32 accumulate", "kernel": "bf16_tcgen05 (fp16 operand formats)", "ms_per_step": ms,
             "value": tflops, "unit": "TFLOP/s", "bound": "tensor", "frac_of_measured_peak": tflops / float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])),
             "l2": "rotating 4 operand sets (403 MB) vs L2 126 MB", "parity": {"rows": len(pick), "rel_fro": rel_frobenius(got, want)},
-            "device_status": take_status()}
+            "device_status": take_status(dev.index or 0)}
 
 
 def measure_pack(dev, peaks) -> dict:
@@ -361,22 +418,42 @@ def measure_sdpa(dev, port) -> dict:
     keep = (np.arange(length)[None, :] <= pick[:, None]).astype(np.uint8)
     want = port.sdpa_bf16(host[0][pick], host[1], host[2], 1.0 / np.sqrt(d), keep_mask=keep, out_bf16=True)
     got = out[torch.from_numpy(pick).to(dev)].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    # timed like every other short kernel: all launches of all timed steps in ONE CUDA graph, so that the host's
+    # launch rate (four launches per step through Python) is not what gets measured
     count = 50
-    for _ in range(20):  # warm-up
-        run()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(count):
-        run()
-    e1.record(stream)
-    torch.cuda.synchronize()
+    side = torch.cuda.Stream(dev)
+    record.stream = side.cuda_stream
+    # a second head with its own operands, result and scratch, taken in turn with the first: 2 x 105 MB of scores,
+    # probabilities and operands, more than the 126 MB L2 holds
+    q2, k2, v2 = q.clone(), k.clone(), v.clone()
+    out2, scratch2 = torch.empty_like(out), torch.empty_like(scratch)
+    other = harness.sdpa_record(q2, k2, v2, out2, 1.0 / np.sqrt(d), causal=capi.CAUSAL_BOTTOM_RIGHT, stream=side, asynchronous=True)
+    other.workspace, other.workspace_size = scratch2.data_ptr() + (-scratch2.data_ptr()) % 256, need.value
+    run_other = lambda: error.raise_for(capi.library().vecops_b200_sdpa_run(byref(other), byref(error.record)))  # noqa: E731
+    side.wait_stream(stream)
+    with torch.cuda.stream(side):
+        run()  # one-time set-up outside the capture
+        run_other()
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(count):
+                (run if i % 2 == 0 else run_other)()
+        graph.replay()  # warm-up
+        side.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(side)
+        graph.replay()
+        e1.record(side)
+        side.synchronize()
+    stream.wait_stream(side)
     ms = e0.elapsed_time(e1) / count
     flops = 4.0 * length * length * d  # both products, dense (the causal half is computed and masked)
     return {"workload": "attention, one head, Lq=Lkv=4096, D=128, bottom-right causal, bf16", "ms_per_step": ms, "launches_per_step": int(launches),
+            "launch": f"one CUDA graph of {count} steps, CUDA events around its replay", "l2": "two heads with their own operands and scratch in turn (2 x 105 MB) vs L2 126 MB",
             "dense_tflops": flops / (ms * 1e-3) / 1e12, "scratch_mb": need.value / 1e6,
             "note": "materialized strategy as in the reference: scores (67 MB f32) and probabilities (34 MB bf16) pass through device memory",
-            "parity": {"rows": len(pick), "rel_fro": rel_frobenius(bf16_bits_to_f32(got), bf16_bits_to_f32(want))}, "device_status": take_status()}
+            "parity": {"rows": len(pick), "rel_fro": rel_frobenius(bf16_bits_to_f32(got), bf16_bits_to_f32(want))}, "device_status": take_status(dev.index or 0)}
 
 
 def workloads_bf16(values):
@@ -432,15 +509,19 @@ def measure_quantized(steps: int, warmup: int, dev, port, peaks) -> dict:
               "correction_equal": bool(np.array_equal(corrections[0].cpu().numpy(), correction_host))}
     ms = time_graph(prepared, steps, warmup, dev)
     tops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
-    peak = 2.0 * float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    peak = 2.0 * float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))  # assumed: twice the measured bf16 burst figure
     return {"workload": "c3 shape, quantised form: u8 (quantised fp32) x s8 + int32 correction row, dequantised and column-scaled to bf16",
             "kernel": "i8_tcgen05", "ms_per_step": ms, "value": tops, "unit": "TOP/s", "bound": "tensor", "frac_of_measured_peak": tops / peak,
-            "quantize_rows_ms": quantize_ms, "column_correction_ms": correction_ms, "parity": parity, "device_status": take_status(),
+            "quantize_rows_ms": quantize_ms, "column_correction_ms": correction_ms,
+            "ms_per_step_with_quantize_rows": ms + quantize_ms, "value_with_quantize_rows": 2.0 * m * n * k / ((ms + quantize_ms) * 1e-3) / 1e12,
+            "note": "the activations are quantised by a pre-pass kernel, once per product; the correction row is computed once per weight matrix",
+            "parity": parity, "device_status": take_status(dev.index or 0),
             "launch": "one CUDA graph of all timed launches; two weight sets (235 MB) > L2"}
 
 
 def bridge_invoker():
-    """Returns call(a, b, c, scale, stream): one asynchronous operator-bridge invocation (the reference-facing entry)."""
+    """Returns prepare(a, b, c, scale, stream) -> call(): the call frame is built once, as a C caller keeps it on its stack,
+    and call() is ONE asynchronous vecops_operator_bridge_invoke_v1 (the reference-facing entry) over it."""
     from vecops_b200 import capi
     lib = capi.library()
     lib.vecops_b200_matmul_operator.restype = ctypes.c_uint64
@@ -449,7 +530,7 @@ def bridge_invoker():
     lib.vecops_b200_operator_workspace.argtypes = [ctypes.c_uint64, ctypes.POINTER(capi.VecopsCall), ctypes.POINTER(ctypes.c_uint64),
                                                    ctypes.POINTER(capi.VecopsError)]
     handle = lib.vecops_b200_matmul_operator()
-    scratch: dict = {}  # device workspace per call signature, sized by the operator's own query
+    invoke = lib.vecops_operator_bridge_invoke_v1
 
     import torch
 
@@ -470,8 +551,8 @@ def bridge_invoker():
         tv.flags = capi.TENSOR_READ | (capi.TENSOR_WRITE if writable else 0)
         return v
 
-    def call(a, b, c, scale, stream):
-        keep: list = []
+    def prepare(a, b, c, scale, stream):
+        keep: list = [a, b, c, scale]
         values = [value_of(a, False, keep), value_of(b, False, keep), value_of(c, True, keep)]
         if scale is not None:
             values.append(value_of(scale, False, keep))
@@ -482,83 +563,142 @@ def bridge_invoker():
         context.flags = capi.CONTEXT_FLAG_ASYNC
         frame = capi.VecopsCall(ctypes.sizeof(capi.VecopsCall), len(values), array, None, 0, ctypes.pointer(context))
         error = capi.ErrorBuffer()
-        key = (tuple(a.shape), tuple(b.shape), a.dtype, b.dtype, c.dtype, scale is not None)
-        if key not in scratch:
-            need = ctypes.c_uint64(0)
-            error.raise_for(lib.vecops_b200_operator_workspace(handle, byref(frame), byref(need), byref(error.record)))
-            scratch[key] = torch.empty(need.value, dtype=torch.uint8, device=c.device) if need.value else None
-        if scratch[key] is not None:
-            frame.workspace, frame.workspace_size = scratch[key].data_ptr(), scratch[key].numel()
-        error.raise_for(lib.vecops_operator_bridge_invoke_v1(handle, byref(frame), 0, None, byref(error.record)))
+        need = ctypes.c_uint64(0)
+        error.raise_for(lib.vecops_b200_operator_workspace(handle, byref(frame), byref(need), byref(error.record)))
+        if need.value:  # device workspace sized by the operator's own query, one per prepared call
+            scratch = torch.empty(need.value, dtype=torch.uint8, device=c.device)
+            frame.workspace, frame.workspace_size = scratch.data_ptr(), scratch.numel()
+            keep.append(scratch)
+        keep += [array, context]
+        frame_ref, error_ref = byref(frame), byref(error.record)
 
-    return call
+        def call(_keep=keep):
+            rc = invoke(handle, frame_ref, 0, None, error_ref)
+            if rc != capi.OK:
+                error.raise_for(rc)
+
+        return call
+
+    return prepare
 
 
-def measure_e2e(w, operands, host_inputs, steps: int, warmup: int, dev) -> dict:
+def async_copier():
+    """copy(dst_ptr, src_ptr, bytes, stream): cudaMemcpyAsync through the CUDA runtime the process already has loaded - what
+    a C caller of the bridge issues around its call.  (torch's Tensor.copy_ costs ~10 us of Python per copy, which would
+    be the measurement for the decode shapes.)"""
+    try:
+        runtime = ctypes.CDLL("libcudart.so.12")
+        fn = runtime.cudaMemcpyAsync
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
+        fn.restype = ctypes.c_int
+    except (OSError, AttributeError):
+        return None
+
+    def copy(dst: int, src: int, count: int, stream) -> None:
+        rc = fn(dst, src, count, 4, stream.cuda_stream)  # 4 = cudaMemcpyDefault
+        if rc != 0:
+            raise RuntimeError(f"cudaMemcpyAsync failed with code {rc}")
+
+    return copy
+
+
+def measure_e2e(w, operands, host_inputs, steps: int, warmup: int, dev, resident_weights: bool = False) -> dict:
     """The same step through the operator bridge with pinned host buffers; every step's copies are inside the timed region.
 
     Two measurements.  `serial`: copy in, run, copy out on one stream, one step after the other (the latency of a step).
     `pipelined` (the reported value): two operand sets in flight on three streams, so that the host-to-device copy of
     step i+1 and the device-to-host read of step i-1 overlap step i; still one copy-in and one read-back per step.
+    `resident_weights` (the decode shapes): the weight matrix and its scales stay on the device, as a decode loop keeps
+    them; a step copies the activations in and the result out.
     """
     import torch
     a0, b0, s0 = host_inputs
-    invoke = bridge_invoker()
+    prepare = bridge_invoker()
+    copy = async_copier()
     host_a = torch.from_numpy(a0).pin_memory()
     host_b_src = b0 if w.b_layout == "nk" else np.ascontiguousarray(b0.T)
-    host_b = torch.from_numpy(host_b_src).pin_memory()
-    host_a_raw = host_a.view(torch.int16) if host_a.dtype == torch.uint16 else host_a
-    host_b_raw = host_b.view(torch.int16) if host_b.dtype == torch.uint16 else host_b
+    host_b = None if resident_weights else torch.from_numpy(host_b_src).pin_memory()
 
-    def raw_views(o):
-        a_raw = o["a"].view(torch.int16) if o["a"].dtype == torch.bfloat16 else o["a"]
-        b_storage = o["b"] if w.b_layout == "nk" else o["b"].t()
-        return a_raw, (b_storage.view(torch.int16) if b_storage.dtype == torch.bfloat16 else b_storage)
+    def nbytes(t):
+        return t.numel() * t.element_size()
 
     lanes = []
-    for i in range(2):
+    # resident weights must still come from HBM, not from L2: rotate over every operand set the caller made
+    n_lanes = max(2, len(operands)) if resident_weights else 2
+    for i in range(n_lanes):
         if i < len(operands):
             o = operands[i]
-        else:  # the sharded configuration keeps one operand set: give the second lane its own buffers
+        else:  # a configuration that keeps one operand set: give the second lane its own buffers
             first = operands[0]
-            o = {"a": torch.empty_like(first["a"]), "b": torch.empty_like(first["b"]), "c": torch.empty_like(first["c"]), "scale": first["scale"]}
-        a_raw, b_raw = raw_views(o)
-        lanes.append({"o": o, "a_raw": a_raw, "b_raw": b_raw, "host_c": torch.empty(o["c"].shape, dtype=o["c"].dtype).pin_memory(),
+            o = {"a": torch.empty_like(first["a"]), "b": first["b"] if resident_weights else torch.empty_like(first["b"]),
+                 "c": torch.empty_like(first["c"]), "scale": first["scale"]}
+        b_storage = o["b"] if w.b_layout == "nk" else o["b"].t()  # the contiguous storage behind the [N,K] view
+        assert o["a"].is_contiguous() and b_storage.is_contiguous() and o["c"].is_contiguous()
+        lanes.append({"o": o, "a_ptr": o["a"].data_ptr(), "b_ptr": b_storage.data_ptr(), "c_ptr": o["c"].data_ptr(),
+                      "host_c": torch.empty(o["c"].shape, dtype=o["c"].dtype).pin_memory(),
                       "loaded": torch.cuda.Event(), "computed": torch.cuda.Event(), "read": torch.cuda.Event(), "used": False})
+    a_bytes, c_bytes = nbytes(host_a), nbytes(lanes[0]["host_c"])
+    b_bytes = 0 if resident_weights else nbytes(host_b)
     main = torch.cuda.current_stream(dev)
 
-    def serial_step(_):
-        lane = lanes[0]
-        lane["a_raw"].copy_(host_a_raw, non_blocking=True)
-        lane["b_raw"].copy_(host_b_raw, non_blocking=True)
-        invoke(lane["o"]["a"], lane["o"]["b"], lane["o"]["c"], lane["o"]["scale"], main)
-        lane["host_c"].copy_(lane["o"]["c"], non_blocking=True)
+    def copy_in(lane, stream):
+        if copy is not None:
+            copy(lane["a_ptr"], host_a.data_ptr(), a_bytes, stream)
+            if not resident_weights:
+                copy(lane["b_ptr"], host_b.data_ptr(), b_bytes, stream)
+        else:
+            with torch.cuda.stream(stream):
+                lane["o"]["a"].view(torch.uint8).view(-1).copy_(host_a.view(torch.uint8).view(-1), non_blocking=True)
+                if not resident_weights:
+                    storage = lane["o"]["b"] if w.b_layout == "nk" else lane["o"]["b"].t()
+                    storage.view(torch.uint8).view(-1).copy_(host_b.view(torch.uint8).view(-1), non_blocking=True)
 
-    serial_ms = time_steps(serial_step, steps, warmup, main)
+    def copy_out(lane, stream):
+        if copy is not None:
+            copy(lane["host_c"].data_ptr(), lane["c_ptr"], c_bytes, stream)
+        else:
+            with torch.cuda.stream(stream):
+                lane["host_c"].copy_(lane["o"]["c"], non_blocking=True)
 
-    copy_in, compute, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    serial_calls = [prepare(lane["o"]["a"], lane["o"]["b"], lane["o"]["c"], lane["o"]["scale"], main) for lane in lanes]
+    host_seconds = [0.0]
+
+    def serial_step(i):
+        lane = lanes[i % n_lanes]
+        copy_in(lane, main)
+        t0 = time.perf_counter()
+        serial_calls[i % n_lanes]()
+        host_seconds[0] += time.perf_counter() - t0
+        copy_out(lane, main)
+
+    for i in range(warmup):
+        serial_step(i)
+    torch.cuda.synchronize()
+    host_seconds[0] = 0.0
+    serial_ms = time_steps(serial_step, steps, 0, main)
+    host_us = host_seconds[0] / steps * 1e6
+
+    s_in, s_run, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    calls = [prepare(lane["o"]["a"], lane["o"]["b"], lane["o"]["c"], lane["o"]["scale"], s_run) for lane in lanes]
 
     def pipelined_step(i):
-        lane = lanes[i % 2]
-        with torch.cuda.stream(copy_in):
-            if lane["used"]:
-                copy_in.wait_event(lane["computed"])  # the lane's previous run has read its A and B
-            lane["a_raw"].copy_(host_a_raw, non_blocking=True)
-            lane["b_raw"].copy_(host_b_raw, non_blocking=True)
-            lane["loaded"].record(copy_in)
-        compute.wait_event(lane["loaded"])
+        lane = lanes[i % n_lanes]
         if lane["used"]:
-            compute.wait_event(lane["read"])  # the lane's previous C has reached the host
-        invoke(lane["o"]["a"], lane["o"]["b"], lane["o"]["c"], lane["o"]["scale"], compute)
-        lane["computed"].record(compute)
-        with torch.cuda.stream(copy_out):
-            copy_out.wait_event(lane["computed"])
-            lane["host_c"].copy_(lane["o"]["c"], non_blocking=True)
-            lane["read"].record(copy_out)
+            s_in.wait_event(lane["computed"])  # the lane's previous run has read its A and B
+        copy_in(lane, s_in)
+        lane["loaded"].record(s_in)
+        s_run.wait_event(lane["loaded"])
+        if lane["used"]:
+            s_run.wait_event(lane["read"])  # the lane's previous C has reached the host
+        calls[i % n_lanes]()
+        lane["computed"].record(s_run)
+        s_out.wait_event(lane["computed"])
+        copy_out(lane, s_out)
+        lane["read"].record(s_out)
         lane["used"] = True
 
     def drain():
-        for side in (copy_in, compute, copy_out):
+        for side in (s_in, s_run, s_out):
             main.wait_stream(side)
 
     for i in range(warmup):
@@ -567,7 +707,7 @@ def measure_e2e(w, operands, host_inputs, steps: int, warmup: int, dev) -> dict:
     torch.cuda.synchronize(dev)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record(main)
-    for side in (copy_in, compute, copy_out):
+    for side in (s_in, s_run, s_out):
         side.wait_event(start)
     for i in range(steps):
         pipelined_step(warmup + i)
@@ -576,50 +716,75 @@ def measure_e2e(w, operands, host_inputs, steps: int, warmup: int, dev) -> dict:
     torch.cuda.synchronize(dev)
     pipelined_ms = start.elapsed_time(stop) / steps
     # the read-back is the product's result: compare what reached the host with the device copy
-    last = lanes[(warmup + steps - 1) % 2]
+    last = lanes[(warmup + steps - 1) % n_lanes]
     if not torch.equal(last["host_c"], last["o"]["c"].cpu()):
         raise RuntimeError("end-to-end read-back differs from the device result")
-    h2d = host_a.numel() * host_a.element_size() + host_b.numel() * host_b.element_size()
-    d2h = lanes[0]["host_c"].numel() * lanes[0]["host_c"].element_size()
-    return {"ms_per_step": pipelined_ms, "serial_ms_per_step": serial_ms, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)}
+    return {"ms_per_step": pipelined_ms, "serial_ms_per_step": serial_ms, "h2d_bytes_per_step": int(a_bytes + b_bytes),
+            "d2h_bytes_per_step": int(c_bytes), "host_us_per_call": host_us,
+            "resident": "weights and scales stay on the device; a step copies the activations in and the result out" if resident_weights else "nothing: every operand is copied in every step",
+            "copies": "cudaMemcpyAsync from / to pinned host memory" + ("" if copy is not None else " (through torch)")}
 
 
-def cpu_baseline(w, steps: int = 3) -> dict:
-    """The reference's CPU matmul (or, where it cannot run, the C restatement) on a bounded sample of `w`."""
-    from oracle.checker import Port, Ref
+def cpu_sample(w, ref, cores: int):
+    """(run, rows, cols, kind, isa, note): the bounded sample of workload `w` the CPU baseline times, and how.
+
+    The reference's own code wherever it has any for the row: ops::matmul on AMX for bf16, int8 and the weight-only
+    expression, its AVX-512 fmadd leaf for fp32 (its matmul has no fp32 atom on x86).  Large problems are sampled and the
+    throughput of the sample is reported: a row block of the big bf16 GEMM, a column block of the weight-only shapes
+    (the reference's int8->bf16 conversion path is untuned and takes ~45 ms per 1024 columns)."""
+    from oracle.checker import Port
     from vecops_b200 import workloads
-    ref, why = Ref.load()
-    cores = Ref.default_threads()
-    unit = "GB/s" if w.kind == "w8" else ("TOP/s" if w.kind == "i8" else "TFLOP/s")
-    if ref is not None and w.kind in ("bf16", "i8", "w8"):
-        rows = min(w.m, 4096 if w.kind != "w8" else w.m)
-        cols = w.n if w.kind != "w8" else min(w.n, 1024 * cores)   # the reference's int8->bf16 conversion path is untuned
+    if ref is not None:
+        rows = w.m if w.flops <= 6e11 else 256
+        cols = w.n if w.kind != "w8" else min(w.n, 1024 * cores)
         a, b = workloads.make_a(w, 0, rows), workloads.make_b_nk(w, 0, cols)
         s = workloads.make_scale(w, 0, cols)
         run = {"bf16": lambda: ref.matmul_bf16(a, b, True, cores), "i8": lambda: ref.matmul_i8(a, b, cores),
-               "w8": lambda: ref.matmul_w8(a, b, s, cores)}[w.kind]
-        kind, isa = "reference", "AMX (tdpbf16ps / tdpbssd) via the reference's ops::matmul"
-    else:
-        port = Port()
-        rows, cols = min(w.m, 64), w.n
-        a, b = workloads.make_a(w, 0, rows), workloads.make_b_nk(w, 0, cols)
-        s = workloads.make_scale(w, 0, cols)
-        run = {"bf16": lambda: port.matmul_bf16(a, b), "i8": lambda: port.matmul_i8(a, b), "w8": lambda: port.matmul_w8(a, b, s),
-               "f32": lambda: port.matmul_f32(a, b)}[w.kind]
-        kind, isa = "port", f"C restatement, OpenMP ({why or 'reference has no fp32 matmul on x86'})"
-        cores = port.threads
+               "w8": lambda: ref.matmul_w8(a, b, s, cores), "f32": lambda: ref.matmul_f32_leaf(a, b, cores)}[w.kind]
+        isa = {"bf16": "AMX-BF16 (tdpbf16ps) through the reference's ops::matmul<AMX_BF16F32>",
+               "i8": "AMX-INT8 (tdpbssd) through the reference's ops::matmul<AMX_I8I32>",
+               "w8": "AMX-BF16 through the reference's ops::matmul<AMX_BF16F32> with input<bfloat16_t>(int8 W) and a per-column scale transform",
+               "f32": "AVX-512 fmadd: the reference's small_vector_dense_matmul leaf (its matmul has no fp32 atom on x86), B transposed to [N,K] beforehand"}[w.kind]
+        note = "" if (rows, cols) == (w.m, w.n) else " (throughput of the sample: the work is linear in the sampled extent)"
+        return run, rows, cols, "reference", isa, note
+    port = Port()
+    rows, cols = min(w.m, 64), w.n
+    a, b = workloads.make_a(w, 0, rows), workloads.make_b_nk(w, 0, cols)
+    s = workloads.make_scale(w, 0, cols)
+    run = {"bf16": lambda: port.matmul_bf16(a, b), "i8": lambda: port.matmul_i8(a, b), "w8": lambda: port.matmul_w8(a, b, s),
+           "f32": lambda: port.matmul_f32(a, b)}[w.kind]
+    return run, rows, cols, "port", "C restatement, OpenMP, compiler-vectorised", " (throughput of the sample)"
+
+
+def cpu_baseline(w, repeats: int = 3) -> dict:
+    """The reference's CPU matmul (or, where it cannot run, the C restatement) on a bounded sample of `w`, all host threads."""
+    from oracle.checker import Port, Ref
+    ref, why = Ref.load()
+    cores = Ref.default_threads() if ref is not None else Port().threads
+    run, rows, cols, kind, isa, note = cpu_sample(w, ref, cores)
     run()
-    best = min(_timed(run) for _ in range(steps))
+    best = min(_timed(run) for _ in range(repeats))
+    unit = "GB/s" if w.kind == "w8" else ("TOP/s" if w.kind == "i8" else "TFLOP/s")
     flops = 2.0 * rows * cols * w.k
-    value = ((cols * w.k + 2 * rows * w.k + 2 * rows * cols) / best / 1e9) if w.kind == "w8" else flops / best / 1e12
-    return {"value": value, "unit": unit, "cores": cores, "kind": kind, "isa": isa,
-            "sample": f"{rows}x{cols}x{w.k} of {w.m}x{w.n}x{w.k}, best of {steps}", "seconds": best}
+    value = ((cols * w.k + 4 * cols + 2 * rows * w.k + 2 * rows * cols) / best / 1e9) if w.kind == "w8" else flops / best / 1e12
+    record = {"value": value, "unit": unit, "cores": cores, "kind": kind, "isa": isa,
+              "sample": f"{rows}x{cols}x{w.k} of {w.m}x{w.n}x{w.k}, best of {repeats}{note}", "seconds": best,
+              "tflops": flops / best / 1e12}
+    if why:
+        record["reference_unavailable"] = why
+    return record
 
 
 def _timed(fn) -> float:
     t0 = time.perf_counter()
     fn()
     return time.perf_counter() - t0
+
+
+HEADLINE = "c5_bf16_16384x53248x8192"
+# the other single-GPU configurations, in the order they are reported: (workload, timed steps)
+CONFIGS = [("c2_bf16_4096", 200), ("c1_f32_1024", 100), ("c3_i8_4096x14336x4096", 50), ("c4_w8_m1", 200), ("c4_w8_m16", 200),
+           ("c4_w8_m128", 100)]
 
 
 def run_ours(args) -> None:
@@ -656,90 +821,96 @@ def run_ours(args) -> None:
     peaks, peak_source = measured_peaks()
     port = Port()
 
-    name = args.workload or ("c2_bf16_4096" if world == 1 else "c5_bf16_16384x53248x8192")
+    name = args.workload or HEADLINE
     w = workloads.WORKLOADS[name]
-    sharded = world > 1 or name.startswith("c5")
-    steps = args.steps if args.steps is not None else (20 if sharded else 200)
-    warmup = args.warmup if args.warmup is not None else (3 if sharded else 10)
+    if world > 1 and w.kind != "bf16":
+        raise SystemExit("only the bf16 GEMM shards over GPUs; the other configurations are single-GPU")
+    sharded = name == HEADLINE or world > 1   # the column-sharded operator (at one GPU its slab is the whole result)
+    if not sharded:
+        # any other workload alone on one GPU: the per-configuration record is the line
+        steps = args.steps if args.steps is not None else dict(CONFIGS).get(name, 100)
+        warmup = args.warmup if args.warmup is not None else 10
+        with ClockSampler(local) as clocks:
+            record = measure_single(name, steps, warmup, dev, port, peaks, peak_source)
+        e2e = record.get("e2e", {})
+        line = {"metric": METRIC, "value": record["value"], "unit": record["unit"], "n_gpus": 1, "steps": steps, "warmup": warmup,
+                "ms_per_step": record["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": {"bf16": "bf16", "i8": "int8", "w8": "bf16 x int8 weights", "f32": "f32"}[w.kind],
+                "data": "synthetic (seeded; shapes, layouts and value distributions of the named configuration)",
+                "config": {"workload": name, "description": w.description, "m": w.m, "n": w.n, "k": w.k, "parallelism": "single GPU",
+                           "l2": record["l2"], "timing": record["launch"]},
+                "roofline": record["roofline"], "cpu_baseline": record.get("cpu_baseline"), "e2e": e2e,
+                "gpu_launches": record["gpu_launches_captured"], "clocks": clocks.summary(), "parity": record["parity"],
+                "device_status": record["device_status"]}
+        print(json.dumps(line), flush=True)
+        return
+
+    steps = args.steps if args.steps is not None else 20
+    warmup = args.warmup if args.warmup is not None else 3
     stream = torch.cuda.current_stream(dev)
 
-    gather_mode = "none"
-    if sharded:
-        n0, n1 = sharding.column_partition(w.n, world, rank)
-        operands, host_inputs = device_sets(w, 1, dev, n0, n1)
-        o = operands[0]
-        prepared = [harness.PreparedMatmul(o["a"], o["b"], o["c"], None, stream=stream)]  # the slab GEMM alone (roofline, e2e)
-        full = None
-        if world == 1:
-            step_launch = prepared[0].launch  # one GPU owns every column: the slab is the result
+    gather_mode = "none: one GPU owns every column, its slab is the result"
+    n0, n1 = sharding.column_partition(w.n, world, rank)
+    operands, host_inputs = device_sets(w, 1, dev, n0, n1)
+    o = operands[0]
+    prepared = [harness.PreparedMatmul(o["a"], o["b"], o["c"], None, stream=stream)]  # the slab GEMM alone (roofline)
+    full = handle = fused = None
+    if world == 1:
+        step_launch = prepared[0].launch
+        launches_per_step = 1
+    else:
+        if args.gather in ("fused", "fused-peer"):
+            try:  # the epilogue sends each finished piece into every rank's result over NVLink
+                full, handle = sharding.symmetric_result(w.m, w.n, torch.bfloat16, dev)
+                multicast = int(getattr(handle, "multicast_ptr", 0) or 0) if args.gather == "fused" else 0
+                # every rank must take the same route
+                route = torch.tensor([1 if multicast else 0], device=dev)
+                dist.all_reduce(route, op=dist.ReduceOp.MIN)
+                if int(route.item()) == 1:
+                    # one store to the multicast address: the switch writes it into every rank's copy, own included
+                    targets = [multicast]
+                    gather_mode = "fused: epilogue multimem.st to the NVSwitch multicast address of the result (one store, every rank's copy) + one device barrier"
+                else:
+                    targets = [int(p) for p in handle.buffer_ptrs]
+                    gather_mode = "fused: epilogue TMA stores to every rank's result over NVLink peer pointers + one device barrier"
+                fused = sharding.FusedGatherGemm(o["a"], o["b"], targets, w.n, w.n, n0, torch.bfloat16, stream, multicast=len(targets) == 1)
+                fused.launch()
+                handle.barrier(channel=0)
+                torch.cuda.synchronize()
+            except Exception as error:  # symmetric memory unavailable: fall back to the library collective
+                print(f"[bench] fused gather unavailable on rank {rank}: {error!r}", file=sys.stderr)
+                fused = None
+        ok = torch.tensor([1 if fused is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 1:
+            def step_launch():
+                fused.launch()
+                handle.barrier(channel=0)
             launches_per_step = 1
         else:
             fused = None
-            if args.gather in ("fused", "fused-peer"):
-                try:  # epilogue TMA-stores each finished piece into every rank's result over NVLink
-                    full, handle = sharding.symmetric_result(w.m, w.n, torch.bfloat16, dev)
-                    multicast = int(getattr(handle, "multicast_ptr", 0) or 0) if args.gather == "fused" else 0
-                    # every rank must take the same route
-                    route = torch.tensor([1 if multicast else 0], device=dev)
-                    dist.all_reduce(route, op=dist.ReduceOp.MIN)
-                    if int(route.item()) == 1:
-                        # one store to the multicast address: the switch writes it into every rank's copy, own included
-                        targets = [multicast]
-                        gather_mode = "fused: epilogue multimem.st to the NVSwitch multicast address of the result (one store, every rank's copy) + one device barrier"
-                    else:
-                        targets = [int(p) for p in handle.buffer_ptrs]
-                        gather_mode = "fused: epilogue TMA stores to every rank's result over NVLink peer pointers + one device barrier"
-                    fused = sharding.FusedGatherGemm(o["a"], o["b"], targets, w.n, w.n, n0, torch.bfloat16, stream, multicast=len(targets) == 1)
-                    fused.launch()
-                    handle.barrier(channel=0)
-                    torch.cuda.synchronize()
-                except Exception as error:  # symmetric memory unavailable: fall back to the library collective
-                    print(f"[bench] fused gather unavailable on rank {rank}: {error!r}", file=sys.stderr)
-                    fused = None
-            ok = torch.tensor([1 if fused is not None else 0], device=dev)
-            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-            if int(ok.item()) == 1:
-                def step_launch():
-                    fused.launch()
-                    handle.barrier(channel=0)
-                launches_per_step = 1
-            else:
-                gather_mode = "nccl: all_gather_into_tensor of the slabs + placement kernel per slab"
-                full = torch.empty((w.m, w.n), dtype=torch.bfloat16, device=dev)
-                staging = torch.empty((world, w.m, n1 - n0), dtype=torch.bfloat16, device=dev)
-                place = sharding.cuda_place(stream)
+            gather_mode = "nccl: all_gather_into_tensor of the slabs + placement kernel per slab"
+            full = torch.empty((w.m, w.n), dtype=torch.bfloat16, device=dev)
+            staging = torch.empty((world, w.m, n1 - n0), dtype=torch.bfloat16, device=dev)
+            place = sharding.cuda_place(stream)
 
-                def step_launch():
-                    prepared[0].launch()
-                    sharding.gather_columns(o["c"], full, staging, world, place=place)
-                launches_per_step = 1 + world
+            def step_launch():
+                prepared[0].launch()
+                sharding.gather_columns(o["c"], full, staging, world, place=place)
+            launches_per_step = 1 + world
 
-        def step(_):
-            step_launch()
+    def step(_):
+        step_launch()
 
-        sets_note = f"operands {w.algorithmic_bytes / 1e9:.2f} GB > L2 126 MB"
-    else:
-        per_set = w.algorithmic_bytes
-        sets = 1 if per_set > 1.5 * 126e6 else int(np.ceil(1.6 * 126e6 / per_set)) + 1
-        operands, host_inputs = device_sets(w, sets, dev)
-        o = operands[0]
-
-        prepared = [harness.PreparedMatmul(x["a"], x["b"], x["c"], x["scale"], stream=stream) for x in operands]
-
-        def step(i):
-            prepared[i % sets].launch()
-
-        sets_note = f"rotating {sets} operand sets ({sets * per_set / 1e6:.0f} MB) > L2 126 MB"
-        launches_per_step = 1
+    sets_note = f"operands and result {w.algorithmic_bytes / 1e9:.2f} GB > L2 126 MB"
 
     step(0)
     torch.cuda.synchronize()
-    result_view = full[:, n0:n1] if (sharded and full is not None) else o["c"]
-    parity = parity_sample(w, host_inputs, result_view, port, rows=8 if sharded else 16)
-    if sharded and full is not None and world > 1:
+    result_view = full[:, n0:n1] if full is not None else o["c"]
+    parity = parity_sample(w, host_inputs, result_view, port, rows=8)
+    if full is not None:
         # what a PEER computed must have arrived here too: the next rank's first 256 columns, four rows
         from oracle.checker import bf16_bits_to_f32, rel_frobenius
-        from vecops_b200 import workloads
         p0, _ = sharding.column_partition(w.n, world, (rank + 1) % world)
         rows = np.array([0, w.m // 3, w.m // 2 + 1, w.m - 1])
         peer_b = workloads.make_b_nk(w, p0, p0 + 256)
@@ -768,23 +939,33 @@ def run_ours(args) -> None:
     if world > 1:
         dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
     ms = float(elapsed.item()) / steps
-    status = take_status()
+    status = take_status(local)
 
     # the GEMM kernel alone (what the roofline describes), timed live on the same stream
     def gemm_only(i):
-        prepared[i % len(prepared)].launch()
+        prepared[0].launch()
 
-    kernel_ms = time_steps(gemm_only, steps, min(warmup, 3), stream) if sharded else ms
-    local_flops = 2.0 * w.m * (o["b"].shape[0]) * w.k
-    bound, peak, nominal, unit = bound_of(w, peaks)
-    if sharded:
-        peak = float(peaks.get("bf16_tflops_sustained", peak))  # seconds-long launches run under the power cap
-    achieved = local_flops / (kernel_ms * 1e-3) / 1e12
+    kernel_ms = time_steps(gemm_only, steps, 3, stream) if world > 1 else ms
+    slab_n = o["b"].shape[0]
+    local_flops = 2.0 * w.m * slab_n * w.k
+    local_bytes = 2.0 * (w.m * w.k + slab_n * w.k + w.m * slab_n)
+    roofline = roofline_record(w, name, "gemm_tcgen05_kernel<bf16> (CTA pairs)", kernel_ms, local_flops, local_bytes, peaks, peak_source)
     value = w.flops / (ms * 1e-3) / 1e12
 
     # end to end through the operator bridge with host buffers
-    e2e_steps = max(1, min(steps, 20 if not sharded else 2))
-    e2e = measure_e2e(w, operands, host_inputs, e2e_steps, 1 if sharded else 3, dev)
+    e2e_steps = max(1, min(steps, 3))
+    if world == 1:
+        e2e = measure_e2e(w, operands, host_inputs, e2e_steps, 3, dev)
+        e2e_note = {"serial_ms_per_step": e2e["serial_ms_per_step"], "serial_value": w.flops / (e2e["serial_ms_per_step"] * 1e-3) / 1e12,
+                    "pipelining": "two operand sets in flight on copy-in / compute / read-back streams; serial_* is one step at a time on one stream",
+                    "path": "vecops_operator_bridge_invoke_v1 (Operator -> MatmulRuntimeDispatch -> CudaExecutableProvider -> descriptor.run), pinned host buffers",
+                    "resident": e2e["resident"], "copies": e2e["copies"]}
+    else:
+        e2e = measure_e2e_sharded(w, o, host_inputs, step_launch, full, n0, n1, e2e_steps, 3, dev)
+        e2e_note = {"path": "per rank: A and this rank's B slab copied in from pinned host memory, the sharded operator (slab GEMM + gather "
+                            "onto every rank + barrier), this rank's columns of the gathered result read back to the host - the whole "
+                            "result reaches the host once per step, 1/N of it per rank",
+                    "gather": "inside the timed region", "copies": e2e["copies"]}
     e2e_ms = torch.tensor([e2e["ms_per_step"]], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
@@ -792,23 +973,23 @@ def run_ours(args) -> None:
 
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if sharded else "weak", "vs_baseline": None,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded; shapes, layouts and value distributions of the named configuration)",
         "config": {"workload": name, "description": w.description, "m": w.m, "n": w.n, "k": w.k,
-                   "parallelism": f"N-sharded x{world}" if sharded else "single GPU", "gather": gather_mode,
+                   "parallelism": f"B column-sharded over {world} GPU" + ("s" if world > 1 else ""), "gather": gather_mode,
                    "l2": sets_note, "timing": "CUDA events on the launch stream, max over ranks"},
-        "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": f"{peak_source}: cuBLAS bf16 " + ("sustained" if sharded else "burst"),
-                     "frac_of_nominal": achieved / nominal, "kernel": "gemm_tcgen05_kernel<bf16>", "kernel_ms": kernel_ms,
-                     "algorithmic_flops_per_launch": local_flops, "algorithmic_bytes_per_launch": 2 * (w.m * w.k + o["b"].shape[0] * w.k + w.m * o["b"].shape[0])},
+        "roofline": roofline,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
-                "d2h_bytes_per_step": e2e["d2h_bytes_per_step"], "ms_per_step": float(e2e_ms.item()), "steps": e2e_steps,
-                "serial_ms_per_step": e2e["serial_ms_per_step"], "serial_value": w.flops / (e2e["serial_ms_per_step"] * 1e-3) / 1e12,
-                "pipelining": "two operand sets in flight on copy-in / compute / read-back streams; serial_* is one step at a time on one stream",
-                "path": "vecops_operator_bridge_invoke_v1 (Operator -> MatmulRuntimeDispatch -> CudaExecutableProvider -> descriptor.run), pinned host buffers"},
+                "d2h_bytes_per_step": e2e["d2h_bytes_per_step"], "ms_per_step": float(e2e_ms.item()), "steps": e2e_steps, **e2e_note},
         "gpu_launches": int(launches), "launches_per_step": launches_per_step, "clocks": clocks.summary(),
         "parity": parity, "device_status": status,
     }
+    if world > 1:
+        received = (world - 1) / world * w.m * w.n * 2.0
+        line["scaling_ceiling"] = {"recv_bytes_per_gpu": received, "link_gbs_measured": NVLINK_RECEIVE_GBS,
+                                   "floor_ms": received / (NVLINK_RECEIVE_GBS * 1e9) * 1e3,
+                                   "note": "gathering the result on every rank makes each GPU receive (N-1)/N of it per step; the link figure "
+                                           "is a store-only all-to-all probe on this pool, not taken in this run"}
 
     if rank == 0 and world == 1:
         try:
@@ -816,43 +997,68 @@ def run_ours(args) -> None:
         except Exception as error:  # the baseline is reported, never the reason a GPU number is lost
             line["cpu_baseline"] = {"error": repr(error)}
         if not args.no_extra and not args.workload:
-            del operands, o, prepared
+            del operands, o, prepared, host_inputs
             torch.cuda.empty_cache()
-            extras = {}
-            for extra, k_steps in [("c1_f32_1024", 100), ("c3_i8_4096x14336x4096", 50), ("c4_w8_m1", 200), ("c4_w8_m16", 200),
-                                   ("c4_w8_m128", 100)]:
+            configs = {}
+            for extra, k_steps in CONFIGS:
                 try:
-                    extras[extra] = measure_single(extra, k_steps, 5, dev, port, peaks)
-                except Exception as error:
-                    extras[extra] = {"error": repr(error)}
+                    configs[extra] = measure_single(extra, k_steps, 10, dev, port, peaks, peak_source)
+                except Exception as error:  # noqa: BLE001
+                    configs[extra] = {"error": repr(error)}
                 torch.cuda.empty_cache()
-            try:  # next-row feature: what the fused output transform costs on the headline shape
-                extras["c2_bf16_4096_fused_bias_silu"] = measure_single("c2_bf16_4096", 50, 5, dev, port, peaks, fused=True)
-            except Exception as error:
-                extras["c2_bf16_4096_fused_bias_silu"] = {"error": repr(error)}
-            torch.cuda.empty_cache()
-            try:  # next-row feature: the quantised form as the reference ships it, at C3's size
-                extras["c3_quantized_u8s8"] = measure_quantized(50, 5, dev, port, peaks)
-            except Exception as error:
-                extras["c3_quantized_u8s8"] = {"error": repr(error)}
-            try:
-                extras["attention_4096x4096x128"] = measure_sdpa(dev, port)
-            except Exception as error:  # noqa: BLE001
-                extras["attention_4096x4096x128"] = {"error": repr(error)}
-            try:
-                extras["pack_14336x4096"] = measure_pack(dev, peaks)
-            except Exception as error:  # noqa: BLE001
-                extras["pack_14336x4096"] = {"error": repr(error)}
-            try:
-                extras["c2_shape_f16"] = measure_f16(50, 5, dev, port, peaks)
-            except Exception as error:  # noqa: BLE001
-                extras["c2_shape_f16"] = {"error": repr(error)}
-            torch.cuda.empty_cache()
-            line["configs"] = extras
+            line["configs"] = configs
+            extras = {}
+            for key, measure in [
+                    ("c2_bf16_4096_fused_bias_silu", lambda: measure_single("c2_bf16_4096", 50, 5, dev, port, peaks, peak_source, fused=True)),
+                    ("c3_quantized_u8s8", lambda: measure_quantized(50, 5, dev, port, peaks)),
+                    ("attention_4096x4096x128", lambda: measure_sdpa(dev, port)),
+                    ("pack_14336x4096", lambda: measure_pack(dev, peaks)),
+                    ("c2_shape_f16", lambda: measure_f16(50, 5, dev, port, peaks))]:
+                try:  # the rows beyond the five configurations
+                    extras[key] = measure()
+                except Exception as error:  # noqa: BLE001
+                    extras[key] = {"error": repr(error)}
+                torch.cuda.empty_cache()
+            line["next_rows"] = extras
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def measure_e2e_sharded(w, o, host_inputs, step_launch, full, n0: int, n1: int, steps: int, warmup: int, dev) -> dict:
+    """One rank's share of the sharded operator end to end, one step at a time on the launch stream: copy A and this
+    rank's slab of B in from pinned host memory, run the slab GEMM with its gather (and the barrier that orders the
+    ranks), read this rank's columns of the GATHERED result back.  Every rank runs this at once."""
+    import torch
+    a0, b0, _ = host_inputs
+    copy = async_copier()
+    host_a = torch.from_numpy(a0).pin_memory()
+    host_b = torch.from_numpy(b0).pin_memory()
+    stage = torch.empty((w.m, n1 - n0), dtype=torch.bfloat16, device=dev)  # the rank's columns, made contiguous for the read-back
+    host_c = torch.empty((w.m, n1 - n0), dtype=torch.bfloat16).pin_memory()
+    main = torch.cuda.current_stream(dev)
+    a_bytes, b_bytes, c_bytes = (t.numel() * t.element_size() for t in (host_a, host_b, host_c))
+
+    def step(_):
+        if copy is not None:
+            copy(o["a"].data_ptr(), host_a.data_ptr(), a_bytes, main)
+            copy(o["b"].data_ptr(), host_b.data_ptr(), b_bytes, main)
+        else:
+            o["a"].view(torch.int16).copy_(host_a.view(torch.int16), non_blocking=True)
+            o["b"].view(torch.int16).copy_(host_b.view(torch.int16), non_blocking=True)
+        step_launch()
+        stage.copy_(full[:, n0:n1])
+        if copy is not None:
+            copy(host_c.data_ptr(), stage.data_ptr(), c_bytes, main)
+        else:
+            host_c.copy_(stage, non_blocking=True)
+
+    ms = time_steps(step, steps, warmup, main)
+    if not torch.equal(host_c, full[:, n0:n1].cpu()):
+        raise RuntimeError("end-to-end read-back differs from the gathered device result")
+    return {"ms_per_step": ms, "h2d_bytes_per_step": int(a_bytes + b_bytes), "d2h_bytes_per_step": int(c_bytes),
+            "copies": "cudaMemcpyAsync from / to pinned host memory" + ("" if copy is not None else " (through torch)")}
 
 
 # ---------------------------------------------------------------------------------------------- reference arm
@@ -865,39 +1071,30 @@ def run_reference(args) -> None:
         return
     from oracle.checker import Port, Ref
     from vecops_b200 import workloads
-    name = args.workload or ("c2_bf16_4096" if world == 1 else "c5_bf16_16384x53248x8192")
+    name = args.workload or HEADLINE
     w = workloads.WORKLOADS[name]
     steps = args.steps if args.steps is not None else 5
     warmup = args.warmup if args.warmup is not None else 1
     ref, why = Ref.load()
-    cores = Ref.default_threads()
-    if ref is not None:
-        rows = w.m if w.flops <= 2e11 else 256          # a 256-row slab of the large GEMM, all N columns
-        a, b = workloads.make_a(w, 0, rows), workloads.make_b_nk(w)
-        run = lambda: ref.matmul_bf16(a, b, True, cores)
-        kind = "reference"
-        how = f"reference ops::matmul<AMX_BF16F32>, {cores} threads each owning an N slice"
-    else:
-        port = Port()
-        rows, cores = 64, port.threads
-        a, b = workloads.make_a(w, 0, rows), workloads.make_b_nk(w)
-        run = lambda: port.matmul_bf16(a, b)
-        kind = "port"
-        how = f"C restatement with OpenMP ({why})"
+    cores = Ref.default_threads() if ref is not None else Port().threads
+    run, rows, cols, kind, isa, note = cpu_sample(w, ref, cores)
     for _ in range(warmup):
         run()
     t0 = time.perf_counter()
     for _ in range(steps):
         run()
     seconds = (time.perf_counter() - t0) / steps
-    value = 2.0 * rows * w.n * w.k / seconds / 1e12
-    sample = f"{rows} of {w.m} rows x all {w.n} columns per step" + ("" if rows == w.m else " (throughput of the sample; the full job scales linearly in M)")
-    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warmup,
-            "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "strong" if world > 1 or name.startswith("c5") else "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (same seeded inputs as the GPU arm)",
+    unit = "GB/s" if w.kind == "w8" else ("TOP/s" if w.kind == "i8" else "TFLOP/s")
+    value = ((cols * w.k + 4 * cols + 2 * rows * w.k + 2 * rows * cols) / seconds / 1e9) if w.kind == "w8" else 2.0 * rows * cols * w.k / seconds / 1e12
+    sample = f"{rows}x{cols}x{w.k} of {w.m}x{w.n}x{w.k} per step{note}"
+    how = f"{isa}; {cores} host threads each owning a slice of N" + (f" ({why})" if why else "")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "strong" if name == HEADLINE or world > 1 else "weak",
+            "vs_baseline": None, "dtype": {"bf16": "bf16", "i8": "int8", "w8": "bf16 x int8 weights", "f32": "f32"}[w.kind],
+            "data": "synthetic (same seeded inputs as the GPU arm)",
             "config": {"workload": name, "description": w.description, "m": w.m, "n": w.n, "k": w.k, "parallelism": f"{cores} host threads", "how": how},
-            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
-            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+            "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": kind, "isa": isa, "sample": sample},
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 

@@ -168,11 +168,14 @@ VECOPS_B200_EXPORT int32_t vecops_b200_matmul_run_batched(const VecopsB200Matmul
  * budget that cannot take cudaMalloc's implicit synchronisation.  `workspace` is ignored.
  *
  *   - The scratch is a fixed array of VECOPS_B200_STATIC_SCRATCH_BYTES of device memory that every GPU
- *     loading the library holds until the process exits.
- *   - Serves bf16 A[M,K] x int8 W[N,K] -> bf16|f32 C, optional column_scale, 1 <= M <= 128, K % 8 == 0,
- *     K-contiguous 16-byte aligned rows.  A problem whose scratch need (vecops_b200_matmul_workspace with
- *     kernel = W8_TCGEN05) exceeds the array is refused with INVALID_ARGUMENT; e.g. M = 64, K = 8192 fits,
- *     M = 128, K = 4096 does not.
+ *     holds, from the moment the CUDA runtime loads this library's device code on it (at the latest the
+ *     first call of this entry point there) until the process exits.
+ *   - Serves bf16 A[M,K] x int8 W[N,K] -> bf16|f32 C, optional column_scale, K % 8 == 0, K-contiguous 16-byte
+ *     aligned rows, and as many activation rows as the array has room for: the scratch need (what
+ *     vecops_b200_matmul_workspace reports with kernel = W8_TCGEN05) is 81920 * M_pad + 2 * M * K + 5632 bytes,
+ *     M_pad = M rounded up to 16, and a problem that needs more than the array holds is refused with
+ *     INVALID_ARGUMENT.  That is M <= 80 at K = 4096 and at K = 8192, M <= 96 for any K up to 2048, and never
+ *     more than 96 rows.
  *   - Every call on a device shares the array and inherits the previous call's contents (nothing needs
  *     clearing).  Calls that overlap on the GPU - two streams, or asynchronous calls not ordered by one
  *     stream - race on it: serialise them.

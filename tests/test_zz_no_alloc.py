@@ -72,3 +72,39 @@ def test_static_scratch_refuses_what_does_not_fit():
     b16 = torch.zeros((256, 4096), dtype=torch.bfloat16, device="cuda")
     problem = vecops_b200.matmul_problem(a, b16, c)
     assert entry(byref(problem), byref(error.record)) == capi.INVALID_ARGUMENT
+
+
+def test_static_scratch_allocates_nothing_and_serves_its_other_forms(port):
+    """What the entry point promises beyond the numbers: no device memory is taken by a call once the one-time set-up is
+    behind it, the fp32-output and the synchronous forms work, and inputs it cannot serve come back with a message."""
+    entry = static_scratch_entry()
+    rng = np.random.default_rng(7)
+    m, n, k = 24, 640, 1024
+    a = f32_to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32))
+    w = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    s = rng.uniform(0.001, 0.02, n).astype(np.float32)
+    da, dw, ds = to_device(a, True), to_device(w), to_device(s)
+    want = port.matmul_w8(a, w, s, False)
+    got = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    error = capi.ErrorBuffer()
+
+    # synchronous call (flags = 0), fp32 output; also the call that performs the set-up if nothing did before
+    problem = vecops_b200.matmul_problem(da, dw, got, ds, stream=torch.cuda.current_stream())
+    assert problem.flags == 0
+    error.raise_for(entry(byref(problem), byref(error.record)))
+    assert rel_frobenius(got.cpu().numpy(), want) <= TOL_BF16
+
+    # a second call takes no device memory: free memory as the driver reports it is unchanged
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    got.zero_()
+    torch.cuda.synchronize()
+    error.raise_for(entry(byref(problem), byref(error.record)))
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, "a call after the set-up must not allocate device memory"
+    assert rel_frobenius(got.cpu().numpy(), want) <= TOL_BF16
+
+    # K not a multiple of 8: not this kernel's problem, said so in words
+    odd = vecops_b200.matmul_problem(da[:, :1020], dw[:, :1020], got, ds)
+    assert entry(byref(odd), byref(error.record)) == capi.NOT_APPLICABLE
+    assert len(error.text.value) > 0

@@ -224,6 +224,7 @@ static int32_t sdpa_run_one(const VecopsB200Attention& a, VecopsError* error);
 int32_t vecops_b200_sdpa_run(const VecopsB200Attention* attention, VecopsError* error) {
   if (attention == nullptr || attention->struct_size < sizeof(VecopsB200Attention))
     return set_error(error, VECOPS_STATUS_ABI_MISMATCH, "attention record is null or too small");
+  const DeviceRestore restore;  // the heads below switch to the record's device; the caller gets its own back
   if (attention->heads <= 1) return sdpa_run_one(*attention, error);
   // one head after the other on the stream, sharing the scratch; only the last one synchronises (when the caller wants that)
   for (int64_t h = 0; h < attention->heads; ++h) {

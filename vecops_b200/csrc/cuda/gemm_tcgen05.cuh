@@ -26,9 +26,11 @@
 // on 148 SMs = 3.46 waves), the tail tiles are cut along K into S slices (S a power
 // of two) so that the last wave keeps S times as many SMs busy for 1/S of the time.
 // The S CTAs of a tile exchange fp32 (int32) partial accumulators through DEVICE
-// SCRATCH: each publishes the columns it does not own and raises a nonce-carrying
-// flag, then adds the others' partials to the columns it owns and stores those.
-// Fixed summation order, so results are reproducible.  Without scratch S = 1.
+// SCRATCH: each publishes the columns it does not own and raises a flag that carries
+// the launch's 64-bit nonce and counts its readers down, then adds the others'
+// partials to the columns it owns and stores those.  The last reader leaves the flag
+// at the bare nonce, so a captured launch can be replayed.  Fixed summation order,
+// so results are reproducible.  Without scratch S = 1.
 //
 // CTA pairs (kPair): two CTAs of a cluster, on the two SMs of one TPC, share a 256x256 tile.  Each loads its 128 rows
 // of A and its 128 of the 256 rows of B (half the shared-memory fill and L2 traffic per SM of the single-CTA form) into
@@ -423,10 +425,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
         __threadfence();
         __syncwarp();
-        if (lane == 0) st_release_gpu_u64(flags + slot_of(item.slice) * 4 + quarter, nonce);
+        // every other slice reads this slice's partial sums: the flag counts those readers down (see ptx.cuh)
+        const unsigned readers = static_cast<unsigned>(item.slices - 1);
+        if (lane == 0) st_release_gpu_u64(flags + slot_of(item.slice) * 4 + quarter, nonce + readers);
         for (int other = 0; other < item.slices; ++other) {
           if (other == item.slice) continue;
-          if (!wait_flag_u64(flags + slot_of(other) * 4 + quarter, nonce, abort_flag)) {
+          if (!wait_flag_window_u64(flags + slot_of(other) * 4 + quarter, nonce, readers, abort_flag)) {
             report_status(status, kStatusEpilogueWait);
             *abort_flag = 1;
             epilogue_ok = false;
@@ -572,6 +576,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             }
           }
         }
+      }
+      if (item.slices > 1) {
+        // this warp has read all it needs of the other slices' partial sums
+        __syncwarp();
+        if (lane == 0)
+          for (int other = 0; other < item.slices; ++other)
+            if (other != item.slice) flag_reader_done_u64(flags + slot_of(other) * 4 + quarter);
       }
       tcgen05_fence_before_sync();
       if constexpr (kPair) mbar_arrive_cluster(map_to_cta(tmem_empty_bar + 8 * acc, 0));

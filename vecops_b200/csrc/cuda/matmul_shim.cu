@@ -46,6 +46,18 @@ int32_t set_error(VecopsError* error, int32_t code, const char* format, ...) {
   return code;
 }
 
+DeviceRestore::DeviceRestore() {
+  if (cudaGetDevice(&previous) != cudaSuccess) {
+    (void)cudaGetLastError();
+    previous = -1;
+  }
+}
+
+DeviceRestore::~DeviceRestore() {
+  int now = -1;
+  if (previous >= 0 && cudaGetDevice(&now) == cudaSuccess && now != previous) cudaSetDevice(previous);
+}
+
 namespace {
 
 // ------------------------------------------------------------------ device bookkeeping
@@ -55,9 +67,21 @@ struct DeviceState {
   cudaDeviceProp prop{};
 };
 
+constexpr int kMaxDevices = 64;
 std::mutex g_mutex;
-DeviceState g_devices[64];
-uint32_t* g_status_host = nullptr;  // pinned, mapped; kernels write here only when a wait ran out
+DeviceState g_devices[kMaxDevices];
+// Pinned, mapped host memory, one word per device ordinal: kernels running on device d write word d, and only when a
+// bounded wait ran out.  Read-and-clear is an atomic exchange, so concurrent pollers cannot both see one record.
+uint32_t* g_status_host = nullptr;
+
+uint32_t* status_word_of(int device) {
+  return (g_status_host != nullptr && device >= 0 && device < kMaxDevices) ? g_status_host + device : nullptr;
+}
+
+uint32_t take_status_word(int device) {
+  uint32_t* word = status_word_of(device);
+  return word == nullptr ? 0u : __atomic_exchange_n(word, 0u, __ATOMIC_ACQ_REL);
+}
 unsigned long long* g_trace = nullptr;  // optional device buffer for kernel timelines (tuning aid), see vecops_b200_debug_set_trace
 PFN_cuTensorMapEncodeTiled_v12000 g_encode_tiled = nullptr;
 
@@ -66,7 +90,7 @@ int32_t cuda_fail(VecopsError* error, cudaError_t status, const char* what) {
 }
 
 int32_t device_state(int device, const DeviceState** out, VecopsError* error) {
-  if (device < 0 || device >= 64) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "device index %d out of range", device);
+  if (device < 0 || device >= kMaxDevices) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "device index %d out of range", device);
   std::lock_guard<std::mutex> lock(g_mutex);
   DeviceState& state = g_devices[device];
   if (!state.known) {
@@ -76,9 +100,9 @@ int32_t device_state(int device, const DeviceState** out, VecopsError* error) {
   }
   if (g_status_host == nullptr) {
     void* p = nullptr;
-    cudaError_t status = cudaHostAlloc(&p, 64, cudaHostAllocMapped | cudaHostAllocPortable);
-    if (status != cudaSuccess) return cuda_fail(error, status, "cudaHostAlloc(status word)");
-    memset(p, 0, 64);
+    cudaError_t status = cudaHostAlloc(&p, kMaxDevices * sizeof(uint32_t), cudaHostAllocMapped | cudaHostAllocPortable);
+    if (status != cudaSuccess) return cuda_fail(error, status, "cudaHostAlloc(status words)");
+    memset(p, 0, kMaxDevices * sizeof(uint32_t));
     g_status_host = static_cast<uint32_t*>(p);
   }
   if (g_encode_tiled == nullptr) {
@@ -208,7 +232,9 @@ int32_t check_problem(const VecopsB200Matmul* p, Row* row, VecopsError* error) {
   return VECOPS_STATUS_OK;
 }
 
-int32_t select_kernel(const VecopsB200Matmul& p, Row row, uint32_t* kernel, VecopsError* error) {
+// `for_query`: the answer for the selection and workspace queries - the kernel the rules prefer, whatever scratch the
+// record carries; a launch (for_query = false) takes the preferred kernel only if the scratch it cannot do without is there.
+int32_t select_kernel(const VecopsB200Matmul& p, Row row, uint32_t* kernel, VecopsError* error, bool for_query = true) {
   uint32_t wanted = p.kernel != VECOPS_B200_KERNEL_AUTO ? p.kernel : forced_by_environment();
   if (wanted != VECOPS_B200_KERNEL_AUTO) {
     if (!applicable(p, row, wanted))
@@ -234,8 +260,14 @@ int32_t select_kernel(const VecopsB200Matmul& p, Row row, uint32_t* kernel, Veco
       if (!tiny && p.k <= 32767 && applicable(p, row, VECOPS_B200_KERNEL_I8_TCGEN05)) pick = VECOPS_B200_KERNEL_I8_TCGEN05;
       break;
     case Row::W8:
-      // few activation rows: the streaming CUDA-core form; up to 128 rows: weights widened into tensor memory
-      if (p.m > 16 && p.n >= 128 && applicable(p, row, VECOPS_B200_KERNEL_W8_TCGEN05)) pick = VECOPS_B200_KERNEL_W8_TCGEN05;
+      // few activation rows: the streaming CUDA-core form; up to 128 rows: weights widened into tensor memory.  That
+      // kernel cannot run without its scratch, and the reference's matmul needs none: a call that brings no (or too
+      // small a) workspace is served by the kernels that need none instead of being refused.  (A forced kernel id is
+      // still refused by the launcher, and the workspace query keeps reporting what the preferred kernel wants.)
+      if (p.m > 16 && p.n >= 128 && applicable(p, row, VECOPS_B200_KERNEL_W8_TCGEN05) &&
+          (for_query || (p.workspace != nullptr && aligned16(p.workspace) &&
+                         p.workspace_size >= W8Tc::scratch_bytes(static_cast<int>(p.m), p.k))))
+        pick = VECOPS_B200_KERNEL_W8_TCGEN05;
       else if (p.m > 0 && p.n >= 16 && applicable(p, row, VECOPS_B200_KERNEL_W8_SMALL_M)) pick = VECOPS_B200_KERNEL_W8_SMALL_M;
       break;
     default:
@@ -559,7 +591,7 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
     if (forced > 0) raster_group = forced;
   }
   unsigned long long nonce = split > 1 ? fresh_nonce(p.workspace) : 0ull;
-  uint32_t* status_word = g_status_host;
+  uint32_t* status_word = status_word_of(device);
   unsigned long long* trace = g_trace;
   EpilogueArgs epilogue = tl_epilogue;
   void* args[] = {&map_a, &map_b, &maps, &num_dest, &col_offset, &c, &ldc, &m, &n, &k, &scale, &idesc, &store_flag,
@@ -650,9 +682,12 @@ int32_t launch_w8_stream_typed(const VecopsB200Matmul& p, const DeviceState& dev
   if (rc != VECOPS_STATUS_OK) return rc;
   const long long items = (p.n + G::kRows - 1) / G::kRows;
   const int grid = static_cast<int>(items < dev.prop.multiProcessorCount ? items : dev.prop.multiProcessorCount);
+  int device = 0;
+  cudaGetDevice(&device);
   kernel<<<grid, G::kThreads, smem, stream>>>(static_cast<const __nv_bfloat16*>(p.a), p.a_stride_m, static_cast<const int8_t*>(p.b),
                                               p.b_stride_n, p.column_scale, static_cast<OutT*>(p.c), p.c_stride_m,
-                                              static_cast<int>(p.m), static_cast<int>(p.n), static_cast<int>(p.k), tl_epilogue, g_status_host);
+                                              static_cast<int>(p.m), static_cast<int>(p.n), static_cast<int>(p.k), tl_epilogue,
+                                              status_word_of(device));
   g_launches.fetch_add(1);
   return VECOPS_STATUS_OK;
 }
@@ -812,7 +847,7 @@ int32_t launch_w8_tcgen05_typed(const VecopsB200Matmul& p, const DeviceState& de
   int m = static_cast<int>(p.m), n = static_cast<int>(p.n), k = static_cast<int>(p.k), mpad_arg = mpad;
   const float* inv = inv_scales;
   unsigned long long nonce = fresh_nonce(p.workspace);
-  uint32_t* status_word = g_status_host;
+  uint32_t* status_word = status_word_of(device);
   unsigned long long* trace = g_trace;
   EpilogueArgs epilogue = tl_epilogue;
   void* args[] = {&map_w, &map_a, &scale, &c, &ldc, &m, &n, &k, &mpad_arg, &partials, &flags, &inv, &nonce, &idesc, &epilogue, &status_word, &trace};
@@ -931,7 +966,7 @@ int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* err
   if (rc != VECOPS_STATUS_OK) return rc;
   const VecopsB200Matmul& p = *problem;
   uint32_t kernel;
-  rc = select_kernel(p, row, &kernel, error);
+  rc = select_kernel(p, row, &kernel, error, false);
   if (rc != VECOPS_STATUS_OK) return rc;
   if (p.m == 0 || p.n == 0) return VECOPS_STATUS_OK;
   if (p.c == nullptr || (p.k > 0 && (p.a == nullptr || p.b == nullptr)))
@@ -990,11 +1025,9 @@ int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* err
     cudaError_t status = cudaStreamSynchronize(stream);
     if (status != cudaSuccess) {
       rc = cuda_fail(error, status, "cudaStreamSynchronize");
-    } else if (g_status_host != nullptr && *reinterpret_cast<volatile uint32_t*>(g_status_host) != 0) {
-      const uint32_t word = *reinterpret_cast<volatile uint32_t*>(g_status_host);
-      *reinterpret_cast<volatile uint32_t*>(g_status_host) = 0;
-      rc = set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "kernel '%s': a bounded device wait ran out (status 0x%x)",
-                     kKernelNames[kernel], word);
+    } else if (const uint32_t word = take_status_word(device)) {
+      rc = set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "kernel '%s' on device %d: a bounded device wait ran out (status 0x%x)",
+                     kKernelNames[kernel], device, word);
     }
   }
   if (previous >= 0 && previous != device) cudaSetDevice(previous);
@@ -1114,10 +1147,8 @@ int32_t vecops_b200_matmul_run_batched(const VecopsB200Matmul* problem, const Ve
     cudaError_t status = cudaStreamSynchronize(static_cast<cudaStream_t>(p.stream));
     if (status != cudaSuccess) {
       rc = cuda_fail(error, status, "cudaStreamSynchronize");
-    } else if (g_status_host != nullptr && *reinterpret_cast<volatile uint32_t*>(g_status_host) != 0) {
-      const uint32_t word = *reinterpret_cast<volatile uint32_t*>(g_status_host);
-      *reinterpret_cast<volatile uint32_t*>(g_status_host) = 0;
-      rc = set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "a bounded device wait ran out in a batched launch (status 0x%x)", word);
+    } else if (const uint32_t word = take_status_word(device)) {
+      rc = set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "device %d: a bounded device wait ran out in a batched launch (status 0x%x)", device, word);
     }
     if (previous >= 0 && previous != device) cudaSetDevice(previous);
   }
@@ -1164,13 +1195,14 @@ __attribute__((visibility("default"))) void vecops_b200_debug_set_trace(void* de
 }
 
 int32_t vecops_b200_take_device_status(int32_t device_index, uint32_t* status, VecopsError* error) {
-  (void)device_index;
   if (status == nullptr) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "status output pointer is null");
   *status = 0;
-  if (g_status_host != nullptr) {
-    *status = *reinterpret_cast<volatile uint32_t*>(g_status_host);
-    *reinterpret_cast<volatile uint32_t*>(g_status_host) = 0;
+  if (device_index < 0 && cudaGetDevice(&device_index) != cudaSuccess) {
+    (void)cudaGetLastError();  // no driver, no GPU: nothing can have been recorded
+    return VECOPS_STATUS_OK;
   }
+  if (device_index >= kMaxDevices) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "device index %d out of range", device_index);
+  *status = take_status_word(device_index);
   return VECOPS_STATUS_OK;
 }
 
@@ -1229,11 +1261,8 @@ int32_t vecops_b200_matmul_allgather_run(const VecopsB200Matmul* problem, const 
   if (rc == VECOPS_STATUS_OK && (p.flags & VECOPS_B200_MATMUL_FLAG_ASYNC) == 0) {
     cudaError_t status = cudaStreamSynchronize(stream);
     if (status != cudaSuccess) rc = cuda_fail(error, status, "cudaStreamSynchronize");
-    else if (g_status_host != nullptr && *reinterpret_cast<volatile uint32_t*>(g_status_host) != 0) {
-      const uint32_t word = *reinterpret_cast<volatile uint32_t*>(g_status_host);
-      *reinterpret_cast<volatile uint32_t*>(g_status_host) = 0;
-      rc = set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "fused all-gather GEMM: a bounded device wait ran out (status 0x%x)", word);
-    }
+    else if (const uint32_t word = take_status_word(device))
+      rc = set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "fused all-gather GEMM on device %d: a bounded device wait ran out (status 0x%x)", device, word);
   }
   if (previous >= 0 && previous != device) cudaSetDevice(previous);
   return rc;

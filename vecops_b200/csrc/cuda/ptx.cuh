@@ -167,17 +167,28 @@ __device__ __forceinline__ void st_release_gpu_u64(unsigned long long* p, unsign
   asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
-// Bounded wait until *flag == value (another CTA of the same grid publishes it).
-__device__ __forceinline__ bool wait_flag_u64(const unsigned long long* flag, unsigned long long value,
-                                              volatile uint32_t* abort_flag) {
+// Flags that count their readers down, so that a launch leaves them as it found them.
+//
+// A producer publishes `base + readers`; each of the `readers` waits until the flag lies in (base, base + readers],
+// reads what the flag guards, and takes one off.  When the last reader is done the flag holds `base` again, which is
+// "not published" for the next launch that carries the same base - a replay of a captured CUDA graph, whose kernel
+// arguments (the base among them) are frozen at capture.  Scratch that was never initialised is harmless as long as
+// `base` is a fresh 64-bit random number: garbage falls inside a window of a few values with negligible probability.
+__device__ __forceinline__ bool wait_flag_window_u64(const unsigned long long* flag, unsigned long long base, unsigned readers,
+                                                     volatile uint32_t* abort_flag) {
   const long long start = clock64();
   for (;;) {
     unsigned long long seen;
     asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(flag) : "memory");
-    if (seen == value) return true;
+    if (seen - base - 1ull < static_cast<unsigned long long>(readers)) return true;
     __nanosleep(100);
     if (*abort_flag != 0 || clock64() - start > kWaitCycleBudget) return false;
   }
+}
+
+// One reader is done with what `flag` guards.
+__device__ __forceinline__ void flag_reader_done_u64(unsigned long long* flag) {
+  asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(flag), "l"(~0ull) : "memory");
 }
 
 // ---------------------------------------------------------------- programmatic dependent launch

@@ -8,13 +8,17 @@
 // lives in a fixed array inside this library instead.
 //
 // The price, stated plainly:
-//   * the array is kStaticScratchBytes (8 MiB) of device memory on EVERY GPU that loads this library, held until
-//     the process exits, whether or not this entry point is ever called;
-//   * problems whose scratch need exceeds it are refused with INVALID_ARGUMENT (nothing is truncated);
+//   * the array is kStaticScratchBytes (8 MiB) of device memory on EVERY GPU on which this library's device code
+//     is loaded, held until the process exits.  The CUDA runtime materialises it when it loads this module on a
+//     device - with lazy module loading that is at the latest this entry point's first call there, so that first
+//     call belongs in start-up code, where the 8 MiB are still to be had;
+//   * problems whose scratch need exceeds it are refused with INVALID_ARGUMENT (nothing is truncated).  The need
+//     is 81920 * M_pad + 2 * M * K + 5632 bytes with M_pad = M rounded up to 16: M <= 80 at K = 4096, M <= 96 for
+//     any K up to 2048, never more than 96 rows;
 //   * all calls on one device share the one array, which keeps the previous call's contents.  Nothing in it has
-//     to start at zero (flags carry a fresh 64-bit nonce per launch; the status word is cleared when read), but
-//     two calls that overlap on the GPU - different streams, or asynchronous calls not ordered by a stream -
-//     race on it and produce garbage.  Serialise them.
+//     to start at zero (flags carry a fresh 64-bit nonce per launch and are counted back down to it by their
+//     readers; the status word is cleared when read), but two calls that overlap on the GPU - different streams,
+//     or asynchronous calls not ordered by a stream - race on it and produce garbage.  Serialise them.
 //
 // Set-up: the first call on a device looks the array's device address up (cudaGetSymbolAddress; the array's name
 // in host code is only a host-side stand-in, never a pointer a kernel could use) and raises the kernel's
@@ -202,19 +206,18 @@ extern "C" int32_t vecops_b200_matmul_w8_static_scratch(const VecopsB200Matmul* 
     }
   }
   if (rc == VECOPS_STATUS_OK && (p.flags & VECOPS_B200_MATMUL_FLAG_ASYNC) == 0) {
-    status = cudaStreamSynchronize(stream);
+    // Did a bounded device wait run out?  The status word is read on the call's own stream, behind the kernel, so the
+    // read orders against nothing but this call (a blocking copy would go through the legacy stream and serialise
+    // against every other blocking stream of the process).
+    uint32_t word = 0;
+    status = cudaMemcpyAsync(&word, dev->status, sizeof(word), cudaMemcpyDeviceToHost, stream);
+    if (status == cudaSuccess) status = cudaStreamSynchronize(stream);
     if (status != cudaSuccess) {
-      rc = cuda_error(error, status, "cudaStreamSynchronize");
-    } else {
-      // did a bounded device wait run out?  (read and clear the status word)
-      uint32_t word = 0;
-      status = cudaMemcpy(&word, dev->status, sizeof(word), cudaMemcpyDeviceToHost);
-      if (status != cudaSuccess) {
-        rc = cuda_error(error, status, "cudaMemcpy(status word)");
-      } else if (word != 0) {
-        cudaMemset(dev->status, 0, sizeof(word));
-        rc = set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "w8_tcgen05 (static scratch): a bounded device wait ran out (status 0x%x)", word);
-      }
+      rc = cuda_error(error, status, "reading the status word behind the kernel");
+    } else if (word != 0) {
+      cudaMemsetAsync(dev->status, 0, sizeof(word), stream);
+      cudaStreamSynchronize(stream);
+      rc = set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "w8_tcgen05 (static scratch): a bounded device wait ran out (status 0x%x)", word);
     }
   }
   if (previous >= 0 && previous != device) cudaSetDevice(previous);

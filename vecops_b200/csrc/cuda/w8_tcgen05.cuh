@@ -28,8 +28,9 @@
 // reaches the tile last, adds the partials in fixed order, applies the column
 // scale once, converts and stores (vecops' split-K rule: the output transform
 // runs once, at the end, kernel/AccumulatorRoute.h:22-56).  Flags carry a
-// per-launch 64-bit nonce, so the scratch needs no clearing between launches.
-// Waits on flags are bounded.
+// 64-bit nonce and count their readers down to it, so the scratch needs no
+// clearing between launches and a captured launch can be replayed.  Waits on
+// flags are bounded.
 //
 // Warps: 0 TMA producer | 1 MMA issuer + TMEM owner | 4-7 epilogue | 8-23 widening (two groups, alternate units).
 //
@@ -138,25 +139,8 @@ __device__ __forceinline__ void umma_f16_ts_pair(uint32_t tmem_d, uint32_t tmem_
       : "memory");
 }
 
-__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
-  unsigned long long v;
-  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-
 __device__ __forceinline__ void st_release_u64(unsigned long long* p, unsigned long long v) {
   asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-
-// Bounded wait for another CTA's flag.
-__device__ __forceinline__ bool wait_flag(const unsigned long long* flag, unsigned long long nonce,
-                                          volatile uint32_t* abort_flag) {
-  const long long start = clock64();
-  while (ld_acquire_u64(flag) != nonce) {
-    __nanosleep(200);
-    if (*abort_flag != 0 || clock64() - start > kWaitCycleBudget) return false;
-  }
-  return true;
 }
 
 // Four int8 in one word -> two bf16x2 words {w0,w1}, {w2,w3}, exactly (|w| <= 128 needs 8 significant bits).  0x43xx
@@ -423,7 +407,7 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
       while (last_contributor + 1 < grid && w8tc_range_begin(total_units, grid, last_contributor + 1) < tile_end_unit) ++last_contributor;
       // a warp only needs its own 32 rows of each partner, published by the partner's warp of the same quarter
       for (int other = cta + 1; other <= last_contributor; ++other)
-        if (!wait_flag(flags + 4 * slot_of(other) + quarter, nonce, abort_flag)) return false;
+        if (!wait_flag_window_u64(flags + 4 * slot_of(other) + quarter, nonce, G::kTailParts, abort_flag)) return false;
     }
     for (int col0 = 16 * part; col0 < mpad && col0 < M; col0 += 16 * parts) {
       uint32_t v[16];
@@ -472,9 +456,15 @@ w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
       }
     }
     if (!seg.owner) {
+      // kTailParts warps of the owner read this quarter: the flag counts them down (see ptx.cuh), so that a replay of
+      // a captured launch, which carries the same nonce, finds the flag unpublished again
       __threadfence();
       __syncwarp();
-      if (lane == 0) st_release_u64(flags + 4 * slot_of(cta) + quarter, nonce);
+      if (lane == 0) st_release_u64(flags + 4 * slot_of(cta) + quarter, nonce + G::kTailParts);
+    } else if (seg.has_contributors) {
+      __syncwarp();
+      if (lane == 0)
+        for (int other = cta + 1; other <= last_contributor; ++other) flag_reader_done_u64(flags + 4 * slot_of(other) + quarter);
     }
     return true;
   };
