@@ -320,6 +320,8 @@ class Ref:
             lib.ref_f16_narrow.argtypes = [_P, _P, _I64]
         if hasattr(lib, "ref_matmul_quantized_u8s8"):
             lib.ref_matmul_quantized_u8s8.argtypes = [_I64] * 3 + [_P, _I64, _F, _F, _P, _I64, _P, _F, _P, _I64]
+        if hasattr(lib, "ref_pack_b_compensated"):
+            lib.ref_pack_b_compensated.argtypes = [_I64, _I64, _P, _I64, ctypes.c_int32, _P]
 
     def sdpa_bf16(self, q, k, v, scale, query_mask=None, key_mask=None, keep_mask=None, bias=None, causal=0):
         """The reference's own attention (materialized strategy); the four optional operands come all together or not at all."""
@@ -458,6 +460,15 @@ class Ref:
                                     n, threads)
         assert rc == 0
         return c
+
+    def pack_compensation(self, b_nk: np.ndarray, a_zero_point: int) -> np.ndarray:
+        """The compensation row the reference's ops::matmul_pack_b_compensated emits for a signed 8-bit B[N,K]
+        (ops/MatmulPack.h:28-35); its packed bytes, in the AMX tile layout, are dropped."""
+        n, k = b_nk.shape
+        out = np.full(n, 0x13579bdf, dtype=np.int32)
+        rc = self.lib.ref_pack_b_compensated(n, k, _ptr(b_nk), self._rows(b_nk), int(a_zero_point), _ptr(out))
+        assert rc == 0
+        return out
 
     def matmul_f32_leaf(self, a, b_nk, threads=1):
         m, k = a.shape

@@ -23,6 +23,7 @@
 #include "vecops/ops/Attention.h"
 #include "vecops/matmul/Quantization.h"
 #include "vecops/ops/Matmul.h"
+#include "vecops/ops/MatmulPack.h"
 
 using namespace vecops;
 using namespace vecops::meta;
@@ -298,6 +299,26 @@ int ref_matmul_f32_leaf(int64_t m, int64_t n, int64_t k, const float* a, int64_t
     kernel::matmul_details::amx::small_vector_dense_matmul<false, float, float, float>(a, lda, b + n0 * ldb, ldb, c + n0,
                                                                                        ldc, m, n1 - n0, k);
   });
+  return 0;
+}
+
+// ops::matmul_pack_b_compensated (ops/MatmulPack.h:28-35): packs a signed 8-bit B[N,K] into the AMX blocked layout and
+// emits compensation[n] = -a_zero_point * sum_k B[n,k].  The packed bytes are in the reference's own tile layout and are
+// discarded here; the compensation row does not depend on that layout and is what the caller gets.  Call form as in the
+// header's usage note and tests/ops/MatmulPackTest.cpp:157-186.
+int ref_pack_b_compensated(int64_t n, int64_t k, const int8_t* b, int64_t ldb, int32_t a_zero_point, int32_t* compensation) {
+  using Atom = matmul::AMX_I8I32<uint8_t, int8_t>;
+  if (!request_amx()) return 1;
+  auto layout = make_layout(make_shape(Any{n}, Any{k}), make_strides(Any{ldb}, cint<1>));
+  auto input_tensor = make_tensor(b, layout);
+  auto packed_layout = matmul::packed_layout<Atom, matmul::Operand::B>(layout);
+  std::vector<int8_t> packed(static_cast<size_t>(numel(packed_layout)) + 64);
+  auto* aligned = reinterpret_cast<int8_t*>((reinterpret_cast<uintptr_t>(packed.data()) + 63) & ~uintptr_t{63});
+  auto output_tensor = make_tensor(aligned, packed_layout);
+  auto compensation_tensor = make_tensor(compensation, make_layout(make_shape(Any{n})));
+  auto op = ops::matmul_pack_b_compensated(ops::MatmulPackBCompensatedConfig<Atom>{.a_zero_point = a_zero_point});
+  ExecutionSession execution{};
+  op(execution, input_tensor, output_tensor, compensation_tensor);
   return 0;
 }
 

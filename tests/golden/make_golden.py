@@ -221,6 +221,24 @@ def main() -> None:
     per_row_case("quant_per_row_seeded_37x51x128", rng.uniform(-3, 3, (m, k)).astype(np.float32), multipliers, 100,
                  rng.integers(-128, 128, (n, k), dtype=np.int8), (1.0 / multipliers).astype(np.float32), rng.uniform(0.01, 0.05, n).astype(np.float32))
 
+    # ops::matmul_pack_b_compensated (ops/MatmulPack.h:28-35): the compensation row -a_zero_point * sum_k B[n,k], which does
+    # not depend on the packed layout.  The reference test's own case (tests/ops/MatmulPackTest.cpp:354-376: N=33, K=129,
+    # values (n*17 + k*3) % 61 - 30, zero point 3, rows on a pitch of K+3) and seeded ones with extreme values and a long K
+    def compensation_case(name, b, zero_point):  # `b` may be a view with a row pitch larger than K
+        cases[name] = dict(kind="pack_comp", b=np.ascontiguousarray(b), zero_point=np.int32(zero_point),
+                           compensation=ref.pack_compensation(b, zero_point))
+
+    n, k = 33, 129
+    storage = np.full((n, k + 3), -99, dtype=np.int8)
+    storage[:, :k] = ((np.arange(n)[:, None] * 17 + np.arange(k)[None, :] * 3) % 61 - 30).astype(np.int8)
+    compensation_case("pack_comp_33x129_zp3", storage[:, :k], 3)
+    rng = np.random.default_rng(47)
+    compensation_case("pack_comp_seeded_24x4099_zp128", rng.integers(-128, 128, (24, 4099), dtype=np.int8), 128)
+    extreme = np.full((19, 512), -128, dtype=np.int8)
+    extreme[1::2] = 127
+    compensation_case("pack_comp_extremes_19x512_zp255", extreme, 255)
+    compensation_case("pack_comp_zero_point_0_16x64", rng.integers(-128, 128, (16, 64), dtype=np.int8), 0)
+
     # float16_t's widening and narrowing (util/Float16.h:272-277) over the whole sweep, as digests: the part of the
     # AMX_F16F32 row a host without AMX-FP16 can run
     patterns, floats = f16_conversion_inputs()

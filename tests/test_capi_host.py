@@ -160,3 +160,51 @@ def test_ctypes_records_match_the_header(tmp_path):
         record = getattr(capi, name)
         assert ctypes.sizeof(record) == int(size), name
         assert getattr(record, records[name]).offset == int(offset), name
+
+
+def _abi_probe_source(headers: list[str], records: dict[str, list[str]], constants: list[str]) -> str:
+    lines = ["#include <stddef.h>", "#include <stdio.h>", *[f'#include "{h}"' for h in headers], "int main(void) {"]
+    for name, fields in records.items():
+        lines.append(f'  printf("{name} size %zu\\n", sizeof({name}));')
+        lines += [f'  printf("{name}.{field} %zu\\n", offsetof({name}, {field}));' for field in fields]
+    lines += [f'  printf("{c} %lld\\n", (long long)({c}));' for c in constants]
+    return "\n".join(lines + ["  return 0;", "}", ""])
+
+
+def test_abi_records_equal_the_reference_headers(tmp_path):
+    """With the reference checkout at hand, the same probe - sizeof and offsetof of every field of every ABI record, and the
+    value of every enumerator - is compiled against this repository's headers and against the reference's own
+    (runtime/CallAbi.h, KernelAbi.h, OperatorBridgeAbi.h): the two printouts must be equal line for line."""
+    import re
+    import subprocess
+    from pathlib import Path
+
+    from oracle import build_oracle
+    reference = build_oracle.REFERENCE_ROOT / "include"
+    if not (reference / "vecops" / "runtime" / "CallAbi.h").exists():
+        pytest.skip("no reference checkout (set VECOPS_REFERENCE_ROOT)")
+    root = Path(__file__).resolve().parents[1]
+    ours = ["vecops_b200/call_abi.h", "vecops_b200/kernel_abi.h", "vecops_b200/operator_bridge.h"]
+    theirs = ["vecops/runtime/CallAbi.h", "vecops/runtime/KernelAbi.h", "vecops/runtime/OperatorBridgeAbi.h"]
+    text = "".join((root / "include" / h).read_text() for h in ours)
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    records: dict[str, list[str]] = {}
+    for match in re.finditer(r"typedef (?:struct|union) (Vecops\w+) \{(.*?)\n\} \1;", text, flags=re.S):
+        body = re.sub(r"union \{(.*?)\} (\w+);", lambda m: f"int {m.group(2)};" + "".join(
+            f"int {m.group(2)}.{inner};" for inner in re.findall(r"(\w+)\s*;", m.group(1))), match.group(2), flags=re.S)
+        records[match.group(1)] = re.findall(r"([\w.]+)\s*(?:\[\w*\])?;", body)
+    constants = [c for c in re.findall(r"\b(VECOPS_[A-Z0-9_]+)\s*=", text)]
+    constants += ["VECOPS_KERNEL_ABI_VERSION_MAJOR", "VECOPS_KERNEL_ABI_VERSION_MINOR"]
+    assert len(records) >= 12 and all(records.values()) and len(constants) >= 30
+    assert {"VecopsCall", "VecopsValue", "VecopsTensorView", "VecopsExecutionContext", "VecopsError", "VecopsKernelDescriptorV1",
+            "VecopsParameterDescriptor", "VecopsSpecializationArgument"} <= set(records)
+    assert "value.tensor" in records["VecopsValue"]
+    outputs = []
+    for tag, headers, include in (("ours", ours, root / "include"), ("reference", theirs, reference)):
+        source = tmp_path / f"probe_{tag}.c"
+        source.write_text(_abi_probe_source(headers, records, constants))
+        binary = tmp_path / f"probe_{tag}"
+        subprocess.run(["gcc", "-std=c11", f"-I{include}", str(source), "-o", str(binary)], check=True)
+        outputs.append(subprocess.run([str(binary)], check=True, capture_output=True, text=True).stdout.splitlines())
+    assert len(outputs[0]) > 100
+    assert outputs[0] == outputs[1]

@@ -92,7 +92,7 @@ def _w8_inputs(rng, m, n, k):
 
 @pytest.mark.parametrize("form", ["workspace", "static_scratch"])
 @pytest.mark.parametrize("m,n,k", [(48, 1024, 2048),    # 128 units on 128 CTAs: one unit each, fifteen contributors per tile
-                                   (100, 2048, 1024)])
+                                   (80, 2048, 1024)])   # the most activation rows the built-in scratch array holds at this K
 def test_replayed_w8_tcgen05_follows_its_inputs(port, form, m, n, k):
     rng = np.random.default_rng(17 * m + n + k)
     a = torch.zeros((m, k), dtype=torch.bfloat16, device="cuda")

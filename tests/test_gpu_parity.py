@@ -78,7 +78,7 @@ def oracle(kind, port, a, b, scale, out_bf16=True):
 def test_golden_fixtures_through_automatic_dispatch(golden):
     for name, case in golden.items():
         kind = str(case["kind"])
-        if kind in ("fused_bf16", "i8acc", "quant_u8s8", "batched_bf16", "f16_convert", "sdpa_bf16", "quant_per_row"):
+        if kind in ("fused_bf16", "i8acc", "quant_u8s8", "batched_bf16", "f16_convert", "sdpa_bf16", "quant_per_row", "pack_comp"):
             continue  # the fused forms have their own tests below; the conversion digests are the checker's own
         a, b = case["a"], case["b"]
         if kind == "i8":
@@ -945,6 +945,23 @@ def test_pack_b_compensated_emits_the_zero_point_row(port):
     _, row0 = harness.pack_operand(empty, zero_point=5)
     torch.cuda.synchronize()
     assert bool((row0 == 0).all()) and row0.numel() == 7
+
+
+def test_pack_b_compensated_golden_fixtures(golden):
+    """The compensation rows the reference's own ops::matmul_pack_b_compensated emitted, bit for bit, and the packed
+    operand beside them (every position the logical element, zero past K)."""
+    from oracle.checker import pack_rows
+    seen = 0
+    for name, case in golden.items():
+        if str(case["kind"]) != "pack_comp":
+            continue
+        b, zp = case["b"], int(case["zero_point"])
+        packed, row = harness.pack_operand(to_device(b), zero_point=zp)
+        torch.cuda.synchronize()
+        assert np.array_equal(row.cpu().numpy(), case["compensation"]), name
+        assert np.array_equal(packed.cpu().numpy(), pack_rows(b)[:, :b.shape[1]]), name
+        seen += 1
+    assert seen >= 4
 
 
 def test_pack_operator_through_the_bridge():

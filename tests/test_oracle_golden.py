@@ -43,6 +43,13 @@ def test_port_matches_golden_fixtures(port, golden):
             assert np.array_equal((got == 0).all(axis=1), (case["out"] == 0).all(axis=1)), name  # fully masked rows are exactly zero
             checked += 1
             continue
+        if kind == "pack_comp":
+            # the compensation row the reference's own ops::matmul_pack_b_compensated emitted (it does not depend on the
+            # packed layout, which is the reference's tile layout there and TMA's row layout here)
+            from oracle.checker import pack_compensation
+            assert np.array_equal(pack_compensation(case["b"], int(case["zero_point"])), case["compensation"]), name
+            checked += 1
+            continue
         if kind == "quant_per_row":
             quantized = port.quantize_rows_per_row(case["a"], case["multipliers"], float(case["zero_point"]))
             got = port.matmul_i8_dequant_rows(quantized, case["b"], case["correction"], case["row_scales"], case["column_scales"])
@@ -126,6 +133,19 @@ def test_port_against_reference_library_live(port):
     s = rng.uniform(0.001, 0.02, 64).astype(np.float32)
     got = bf16_bits_to_f32(port.matmul_w8(a[:16], w, s))
     assert rel_frobenius(got, bf16_bits_to_f32(ref.matmul_w8(a[:16], w, s))) <= TOL_BF16
+
+
+def test_pack_compensation_against_reference_library_live():
+    ref, why = Ref.load()
+    if ref is None:
+        pytest.skip(f"reference matmul cannot run on this host: {why}")
+    from oracle.checker import pack_compensation
+    rng = np.random.default_rng(21)
+    for n, k, zp in [(1, 1, 9), (17, 63, -4), (64, 1024, 77), (5, 70000, 255)]:
+        b = rng.integers(-128, 128, (n, k), dtype=np.int8)
+        assert np.array_equal(pack_compensation(b, zp), ref.pack_compensation(b, zp)), (n, k, zp)
+    padded = rng.integers(-128, 128, (12, 100), dtype=np.int8)   # rows on a pitch larger than K
+    assert np.array_equal(pack_compensation(padded[:, :90], 3), ref.pack_compensation(padded[:, :90], 3))
 
 
 def test_fp16_product_against_numpy(port):
