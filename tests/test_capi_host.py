@@ -110,10 +110,10 @@ def test_error_text_is_truncated_to_the_callers_buffer(library):
 def test_workspace_query_is_pure_host_logic(library):
     p = _problem(16, 14336, 4096, torch.bfloat16, torch.int8, torch.bfloat16)
     assert harness.workspace_bytes(p) == 0
-    # the stream-K weight-only kernel exchanges partial sums through device scratch:
-    # 160 CTA slots of [128 x 128] fp32 + flags + inverse row scales + an fp16 copy of the activations
+    # the weight-only tensor-core kernel cuts each of its 56 tiles of 256 weight rows in two along K (112 CTAs on 148 SMs)
+    # and the slices meet in device scratch: one [128 x 256] 32-bit accumulator and four flags per slice
     p = _problem(128, 14336, 4096, torch.bfloat16, torch.int8, torch.bfloat16)
-    assert harness.workspace_bytes(p) == 160 * 128 * 128 * 4 + 160 * 4 * 8 + 128 * 4 + 2 * 128 * 4096
+    assert harness.workspace_bytes(p) == 112 * (128 * 256 * 4 + 4 * 8)
 
 
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU failure mode")

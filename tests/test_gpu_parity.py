@@ -104,10 +104,14 @@ def cta_form(request, monkeypatch):
     return request.param
 
 
-@pytest.fixture(params=["single", "pair"])
+@pytest.fixture(params=["mixed", "tmem", "tmem_pair"])
 def w8_form(request, monkeypatch):
-    """The weight-only tensor-core kernel on 128-row tiles per CTA, or on 256-row tiles per CTA pair (one MMA for both)."""
-    monkeypatch.setenv("VECOPS_B200_W8TC_PAIR", "1" if request.param == "pair" else "0")
+    """The weight-only tensor-core kernel id in its forms: the default (weights widened into shared memory as the N operand of
+    the dense GEMM's MMAs, tiles cut along K), and the older one (weights widened into tensor memory as the M operand,
+    stream-K) on 128-row tiles per CTA or on 256-row tiles per CTA pair."""
+    if request.param != "mixed":
+        monkeypatch.setenv("VECOPS_B200_W8TC_FORM", "tmem")
+        monkeypatch.setenv("VECOPS_B200_W8TC_PAIR", "1" if request.param == "tmem_pair" else "0")
     return request.param
 
 
@@ -173,7 +177,28 @@ def test_w8_tcgen05_f32_out_no_scale_padded_c(port, w8_form):
     check("w8", run_case("w8", a, w, None, False, K.KERNEL_W8_TCGEN05, ldc_pad=7), port.matmul_w8(a, w, None, False))
 
 
-def test_w8_tcgen05_refuses_a_missing_workspace():
+@pytest.mark.parametrize("m,n,k", [(129, 512, 1024), (300, 1000, 520), (1024, 768, 256)])
+def test_w8_tcgen05_more_than_one_row_tile(port, m, n, k):
+    # the default form walks row tiles like the dense GEMM: M > 128 is served too (each row tile widens the weights again)
+    rng = np.random.default_rng(m + n + k)
+    a, w, s = inputs("w8", m, n, k, rng)
+    check("w8", run_case("w8", a, w, s, kernel=K.KERNEL_W8_TCGEN05), port.matmul_w8(a, w, s), f"m={m} n={n} k={k}")
+
+
+def test_w8_tcgen05_runs_whole_tiles_without_scratch(port):
+    # no workspace: the tiles are not cut along K; same result within tolerance, and with scratch the query is non-zero
+    rng = np.random.default_rng(31)
+    a, w, s = inputs("w8", 64, 1024, 2048, rng)
+    da, dw, ds = to_device(a, True), to_device(w), to_device(s)
+    c = torch.zeros((64, 1024), dtype=torch.bfloat16, device="cuda")
+    problem = vecops_b200.matmul_problem(da, dw, c, ds, kernel=K.KERNEL_W8_TCGEN05)
+    assert harness.workspace_bytes(problem) > 0 and problem.workspace is None
+    harness.run(problem)
+    check("w8", bf16_result_to_numpy(c), port.matmul_w8(a, w, s))
+
+
+def test_w8_tcgen05_older_form_refuses_a_missing_workspace(monkeypatch):
+    monkeypatch.setenv("VECOPS_B200_W8TC_FORM", "tmem")
     a = torch.zeros((32, 256), dtype=torch.bfloat16, device="cuda")
     w = torch.zeros((256, 256), dtype=torch.int8, device="cuda")
     c = torch.zeros((32, 256), dtype=torch.bfloat16, device="cuda")

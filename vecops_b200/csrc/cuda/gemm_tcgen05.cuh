@@ -39,6 +39,15 @@
 // Barriers: both CTAs' loads count bytes on the leader's `full`; the leader's commits arrive on `empty` and
 // `tmem_full` of both CTAs; both epilogues arrive on the leader's `tmem_empty`.  Loads go to one CTA each.
 //
+// Weight-only form (kW8): B is int8 in memory and bf16 in the product - vecops' input<bfloat16_t>(int8 W) - while A
+// stays the caller's bf16 activations.  256-row x 128-k units of W arrive by TMA as bytes; eight more warps widen
+// them (exactly: |w| <= 128 needs 8 significant bits) into the same 128-byte-swizzled K-major bf16 tiles the dense form
+// gets from TMA, one 64-k block at a time, and the MMA issuer runs the dense form's 128x256x16 MMAs on them: 4 KB of
+// weights per MMA, the most one CTA's instruction covers.  Everything downstream - accumulators, the K-slice exchange,
+// the fused output transform, the stores - is the dense form's.  Decode shapes have few tiles (N / 256), so every tile is
+// cut along K over the idle SMs and each CTA runs exactly ONE (tile, K slice): the grid is tiles x slices, not persistent,
+// which lets the epilogue's staging buffers lie over the drained weight ring.
+//
 // Algorithmic traffic per launch: (M*K + N*K) * sizeof(in) + M*N * sizeof(out).
 #pragma once
 
@@ -86,7 +95,27 @@ struct GemmPair : GemmTc {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarrierBytes + 1024;
 };
-static_assert(GemmPair::kSmemBytes <= 227 * 1024 && GemmTc::kSmemBytes <= 227 * 1024, "shared memory budget");
+// The weight-only form: per-CTA constants.  Shared memory: activation ring | int8 weight ring | widened weight ring |
+// barriers; the epilogue's staging buffers lie over the start of the int8 ring (free by then: one work item per CTA).
+struct GemmW8 : GemmTc {
+  static constexpr int kUnitK = 128;                  // k per unit: one TMA box of W (256 rows x 128 bytes)
+  static constexpr int kStages = 2;                   // activation units in flight (two 64-k swizzle atoms each)
+  static constexpr int kAUnitBytes = 2 * kABytes;     // 32 KB
+  static constexpr int kRawStages = 3;                // int8 weight units in flight
+  static constexpr int kRawBytes = kBlockN * kUnitK;  // 32 KB
+  static constexpr int kWideStages = 2;               // widened 64-k blocks: one being multiplied, one being written
+  static constexpr int kWideBytes = kBBytes;          // 32 KB
+  static constexpr int kConvertWarps = 8;
+  static constexpr int kThreads = 32 * (2 + kEpiWarps + kConvertWarps);
+  static constexpr int kRawOffset = kStages * kAUnitBytes;
+  static constexpr int kWideOffset = kRawOffset + kRawStages * kRawBytes;
+  static constexpr int kRingBytes = kWideOffset + kWideStages * kWideBytes;
+  static constexpr int kSmemBytes = kRingBytes + kBarrierBytes + 1024;
+  static constexpr int kExtraBarrierOffset = 128;     // raw_full[3] raw_empty[3] wide_full[2] wide_empty[2] inside the barrier block
+  static constexpr int kMinSliceUnits = 4;            // units a K slice must keep for the cut to pay
+};
+static_assert(GemmPair::kSmemBytes <= 227 * 1024 && GemmTc::kSmemBytes <= 227 * 1024 && GemmW8::kSmemBytes <= 227 * 1024, "shared memory budget");
+static_assert(GemmW8::kEpiBytes <= GemmW8::kRawStages * GemmW8::kRawBytes, "the epilogue staging buffers lie over the int8 weight ring");
 
 // Destinations of the TMA-store epilogue: map[0] is the local C, the rest are peers' C matrices.
 struct GemmStoreMaps {
@@ -195,18 +224,34 @@ __device__ __forceinline__ uint32_t pack_out16x2<__half>(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// Four int8 in one word -> two bf16x2 words {w0,w1}, {w2,w3}, exactly (|w| <= 128 needs 8 significant bits).  0x43xx
+// with bit 7 clear is 128 + (x & 127); the same word reduced to 0x4300 | (x & 128) is 128 or 256: their difference is
+// the two's-complement value.
+__device__ __forceinline__ void widen4_bf16(uint32_t packed, uint32_t& lo, uint32_t& hi) {
+  const uint32_t p0 = __byte_perm(packed, 0x43434343u, 0x4140);
+  const uint32_t p1 = __byte_perm(packed, 0x43434343u, 0x4342);
+  const uint32_t x0 = p0 & 0xff7fff7fu, c0 = p0 & 0xff80ff80u;
+  const uint32_t x1 = p1 & 0xff7fff7fu, c1 = p1 & 0xff80ff80u;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(x0), "r"(c0));
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(x1), "r"(c1));
+}
+
 // OutT: __nv_bfloat16, __half or float for kind::f16 (bf16 or fp16 operands, chosen by the instruction descriptor), int32_t for kind::i8.
-template <bool kInt8, typename OutT, bool kPair>
-__global__ void __launch_bounds__(GemmTc::kThreads, 1)
+template <bool kInt8, typename OutT, bool kPair, bool kW8 = false>
+__global__ void __launch_bounds__(kW8 ? GemmW8::kThreads : GemmTc::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const __grid_constant__ GemmStoreMaps tma_c, int num_dest, int c_col_offset, OutT* __restrict__ c,
                     long long ldc, int M, int N, int K, const float* __restrict__ column_scale, uint32_t idesc,
                     int use_tma_store, int raster_group, int split, uint32_t* __restrict__ partials, unsigned long long* __restrict__ flags,
                     unsigned long long nonce, EpilogueArgs ep, uint32_t* __restrict__ status,
                     unsigned long long* __restrict__ trace) {
-  using G = typename std::conditional<kPair, GemmPair, GemmTc>::type;
+  static_assert(!kW8 || (!kInt8 && !kPair), "the weight-only form is a single-CTA 16-bit product");
+  using G = typename std::conditional<kW8, GemmW8, typename std::conditional<kPair, GemmPair, GemmTc>::type>::type;
   constexpr int kElemBytes = kInt8 ? 1 : 2;
-  constexpr int kBlockK = G::kBlockKBytes / kElemBytes;  // elements per k-block
+  // elements of K per step of the main loop: one 128-byte swizzle atom, or - weight-only form - one unit of two
+  constexpr int kBlockK = kW8 ? GemmW8::kUnitK : G::kBlockKBytes / kElemBytes;
+  constexpr int kRingBytes = kW8 ? GemmW8::kRingBytes : G::kStages * G::kStageBytes;
+  constexpr int kMaxRounds = kW8 ? 1 : 0x7fffffff;  // the weight-only form runs one work item per CTA
   constexpr int kTileM = kPair ? 2 * G::kBlockM : G::kBlockM;  // rows of the tile a worker (CTA or pair) owns
   const uint32_t pair_rank = kPair ? cluster_cta_rank() : 0u;
   const int worker = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
@@ -216,9 +261,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t epi_base = smem_base + G::kStages * G::kStageBytes;
-  uint8_t* bar_gen = smem_gen + G::kStages * G::kStageBytes + G::kEpiBytes;
-  const uint32_t bar_base = epi_base + G::kEpiBytes;
+  const uint32_t epi_base = smem_base + (kW8 ? GemmW8::kRawOffset : kRingBytes);
+  constexpr int kBarrierOffset = kW8 ? kRingBytes : kRingBytes + G::kEpiBytes;
+  uint8_t* bar_gen = smem_gen + kBarrierOffset;
+  const uint32_t bar_base = smem_base + kBarrierOffset;
   // barrier block: full[stages] empty[stages] tmem_full[2] tmem_empty[2] | tmem slot | abort flag
   const uint32_t full_bar = bar_base;
   const uint32_t empty_bar = bar_base + 8 * G::kStages;
@@ -226,6 +272,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const uint32_t tmem_empty_bar = tmem_full_bar + 16;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_gen + 16 * G::kStages + 32);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bar_gen + 16 * G::kStages + 36);
+  // weight-only form: int8 unit landed / consumed, widened block written / multiplied
+  const uint32_t raw_full_bar = bar_base + GemmW8::kExtraBarrierOffset;
+  const uint32_t raw_empty_bar = raw_full_bar + 8 * GemmW8::kRawStages;
+  const uint32_t wide_full_bar = raw_empty_bar + 8 * GemmW8::kRawStages;
+  const uint32_t wide_empty_bar = wide_full_bar + 8 * GemmW8::kWideStages;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -255,6 +306,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar + 8 * a, 1);
       mbar_init(tmem_empty_bar + 8 * a, G::kEpiWarps * 32 * (kPair ? 2 : 1));  // the leader's collects both epilogues
+    }
+    if constexpr (kW8) {
+      for (int s = 0; s < GemmW8::kRawStages; ++s) {
+        mbar_init(raw_full_bar + 8 * s, 1);
+        mbar_init(raw_empty_bar + 8 * s, GemmW8::kConvertWarps);
+      }
+      for (int s = 0; s < GemmW8::kWideStages; ++s) {
+        mbar_init(wide_full_bar + 8 * s, GemmW8::kConvertWarps);
+        mbar_init(wide_empty_bar + 8 * s, 1);
+      }
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -289,6 +350,44 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       uint32_t phase = 0;
       bool ok = true;
       GemmItem item;
+      if constexpr (kW8) {
+        // Two independent rings, neither waiting for the other: the int8 weight units run as far ahead as their ring
+        // allows (they are what HBM latency hides behind), the activation units (from L2) follow the MMA.
+        if (gemm_item(0, num_tiles, num_kb, split, worker, workers, item)) {
+          int tm, tn;
+          tile_coords(item.tile, tiles_m, tiles_n, raster_group, tm, tn);
+          const int units = item.kb_end - item.kb_begin;
+          int raw_issued = 0, act_issued = 0, rs = 0;
+          uint32_t rphase = 0;
+          const long long started = clock64();
+          while (raw_issued < units || act_issued < units) {
+            bool progress = false;
+            if (raw_issued < units && mbar_test_wait(raw_empty_bar + 8 * rs, rphase ^ 1u)) {
+              mbar_arrive_expect_tx(raw_full_bar + 8 * rs, GemmW8::kRawBytes);
+              tma_load_2d(smem_base + GemmW8::kRawOffset + rs * GemmW8::kRawBytes, &tma_b, raw_full_bar + 8 * rs,
+                          (item.kb_begin + raw_issued) * GemmW8::kUnitK, tn * G::kBlockN);
+              if (++rs == GemmW8::kRawStages) { rs = 0; rphase ^= 1u; }
+              ++raw_issued;
+              progress = true;
+            }
+            if (act_issued < units && mbar_test_wait(empty_bar + 8 * stage, phase ^ 1u)) {
+              const uint32_t a_dst = smem_base + stage * GemmW8::kAUnitBytes;
+              const int k0 = (item.kb_begin + act_issued) * GemmW8::kUnitK;  // past K: zero-filled by TMA
+              mbar_arrive_expect_tx(full_bar + 8 * stage, GemmW8::kAUnitBytes);
+              tma_load_2d(a_dst, &tma_a, full_bar + 8 * stage, k0, tm * G::kBlockM);
+              tma_load_2d(a_dst + G::kABytes, &tma_a, full_bar + 8 * stage, k0 + 64, tm * G::kBlockM);
+              if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
+              ++act_issued;
+              progress = true;
+            }
+            if (!progress && (*abort_flag != 0 || clock64() - started > 4 * kWaitCycleBudget)) {
+              report_status(status, kStatusProducerWait);
+              *abort_flag = 1;
+              break;
+            }
+          }
+        }
+      } else
       for (int round = 0; ok && gemm_item(round, num_tiles, num_kb, split, worker, workers, item); ++round) {
         int tm, tn;
         tile_coords(item.tile, tiles_m, tiles_n, raster_group, tm, tn);
@@ -329,7 +428,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       bool ok = true;
       int tile_index = 0;
       GemmItem item;
-      for (int round = 0; ok && gemm_item(round, num_tiles, num_kb, split, worker, workers, item); ++round, ++tile_index) {
+      for (int round = 0; ok && round < kMaxRounds && gemm_item(round, num_tiles, num_kb, split, worker, workers, item); ++round, ++tile_index) {
         mark(1 + 2 * tile_index);  // MMA issuer reaches tile i
         if (!(kPair ? mbar_wait_cluster(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag)
                     : mbar_wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag))) {
@@ -339,6 +438,38 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
         tcgen05_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * G::kBlockN;
+        if constexpr (kW8) {
+          // per unit: the activation unit (two 64-k atoms) from its ring, each half against the widened block of that half
+          int ws = 0;
+          uint32_t wphase = 0;
+          for (int kb = item.kb_begin; ok && kb < item.kb_end; ++kb) {
+            if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag)) {
+              report_status(status, kStatusMmaWaitFull);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            for (int half = 0; half < 2; ++half) {
+              if (!mbar_wait(wide_full_bar + 8 * ws, wphase, abort_flag)) {
+                report_status(status, kStatusMmaWaitFull);
+                *abort_flag = 1;
+                ok = false;
+                break;
+              }
+              tcgen05_fence_after_sync();
+              const uint64_t a_desc = umma_smem_desc_sw128(smem_base + stage * GemmW8::kAUnitBytes + half * G::kABytes);
+              const uint64_t b_desc = umma_smem_desc_sw128(smem_base + GemmW8::kWideOffset + ws * GemmW8::kWideBytes);
+#pragma unroll
+              for (int kk = 0; kk < G::kBlockKBytes / 32; ++kk)
+                umma_f16(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb != item.kb_begin || half != 0 || kk != 0) ? 1u : 0u);
+              umma_commit(wide_empty_bar + 8 * ws);
+              if (++ws == GemmW8::kWideStages) { ws = 0; wphase ^= 1u; }
+            }
+            if (!ok) break;
+            umma_commit(empty_bar + 8 * stage);
+            if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
+          }
+        } else
         for (int kb = item.kb_begin; kb < item.kb_end; ++kb) {
           if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag)) {
             report_status(status, kStatusMmaWaitFull);
@@ -377,6 +508,67 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         if (acc == 0) acc_phase ^= 1u;
       }
     }
+  } else if (kW8 && warp >= 2 + G::kEpiWarps) {
+    // ------------------------------------------------------------ widening warps (weight-only form)
+    // A unit is 256 rows x 128 int8 under the 128-byte swizzle; each of its two 64-k halves becomes one 256 x 64 bf16
+    // block under the same swizzle.  A thread takes 8 weights (8 bytes in, 16 bytes out) per step.  Lane l: piece
+    // e = l % 8 of its row's 64-byte half, row (l / 8) of four; a warp-wide load covers rows {r, r+4, r+1, r+5} of an
+    // 8-row block so that each half-warp's 128 bytes fall on all 32 banks (rows r and r+4 swizzle into opposite
+    // halves of the 128-byte line), and each quarter-warp stores one whole 128-byte row.
+    GemmItem item;
+    if (gemm_item(0, num_tiles, num_kb, split, worker, workers, item)) {
+      const int cw = warp - (2 + G::kEpiWarps);
+      const int e = lane & 7, rsel = lane >> 3;
+      const int units = item.kb_end - item.kb_begin;
+      bool ok = true;
+      int ws = 0;
+      uint32_t wphase = 0;
+      for (int u = 0; ok && u < units; ++u) {
+        const int rs = u % GemmW8::kRawStages;
+        const uint32_t rphase = static_cast<uint32_t>(u / GemmW8::kRawStages) & 1u;
+        if (!mbar_wait(raw_full_bar + 8 * rs, rphase, abort_flag)) {
+          if (lane == 0) {
+            report_status(status, kStatusW8Wait);
+            *abort_flag = 1;
+          }
+          break;
+        }
+        const uint32_t raw = smem_base + GemmW8::kRawOffset + rs * GemmW8::kRawBytes + cw * 4 * 1024;  // this warp's four 8-row blocks
+        for (int half = 0; half < 2; ++half) {
+          if (!mbar_wait(wide_empty_bar + 8 * ws, wphase ^ 1u, abort_flag)) {
+            if (lane == 0) {
+              report_status(status, kStatusW8Wait);
+              *abort_flag = 1;
+            }
+            ok = false;
+            break;
+          }
+          const uint32_t wide = smem_base + GemmW8::kWideOffset + ws * GemmW8::kWideBytes + cw * 4 * 1024;
+          uint2 in[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rib = (rsel >> 1) + 4 * (rsel & 1) + 2 * (i & 1);  // row inside the 8-row block = row % 8
+            const uint32_t src = raw + (i >> 1) * 1024 + rib * 128 + (((4 * half + (e >> 1)) ^ rib) << 4) + (e & 1) * 8;
+            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(in[i].x), "=r"(in[i].y) : "r"(src));
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rib = (rsel >> 1) + 4 * (rsel & 1) + 2 * (i & 1);
+            uint32_t out[4];
+            widen4_bf16(in[i].x, out[0], out[1]);
+            widen4_bf16(in[i].y, out[2], out[3]);
+            const uint32_t dst = wide + (i >> 1) * 1024 + rib * 128 + ((e ^ rib) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]) : "memory");
+          }
+          fence_proxy_async_smem();  // the tensor core reads these stores through the async proxy
+          __syncwarp();
+          if (lane == 0) mbar_arrive(wide_full_bar + 8 * ws);
+          if (++ws == GemmW8::kWideStages) { ws = 0; wphase ^= 1u; }
+        }
+        __syncwarp();
+        if (ok && lane == 0) mbar_arrive(raw_empty_bar + 8 * rs);
+      }
+    }
   } else {
     // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
@@ -387,7 +579,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     int buf_sel = 0;
     GemmItem item;
     bool epilogue_ok = true;
-    for (int round = 0; epilogue_ok && gemm_item(round, num_tiles, num_kb, split, worker, workers, item); ++round) {
+    for (int round = 0; epilogue_ok && round < kMaxRounds && gemm_item(round, num_tiles, num_kb, split, worker, workers, item); ++round) {
       int tm, tn;
       tile_coords(item.tile, tiles_m, tiles_n, raster_group, tm, tn);
       if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag)) {
@@ -421,7 +613,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           tmem_load_32x32(taddr + chunk * 32, v);
           tmem_load_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) __stcg(my_partial + static_cast<size_t>(chunk * 32 + j) * G::kBlockM, v[j]);
+          for (int j = 0; j < 32; ++j)
+            if (row < M) __stcg(my_partial + static_cast<size_t>(chunk * 32 + j) * G::kBlockM, v[j]);  // rows past M are never stored
         }
         __threadfence();
         __syncwarp();
@@ -446,7 +639,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                                 static_cast<size_t>(first_col) * G::kBlockM + quarter * 32 + lane;
           uint32_t part[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) part[j] = __ldcg(src + static_cast<size_t>(j) * G::kBlockM);
+          for (int j = 0; j < 32; ++j) part[j] = row < M ? __ldcg(src + static_cast<size_t>(j) * G::kBlockM) : 0u;
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if constexpr (kInt8) v[j] += part[j];

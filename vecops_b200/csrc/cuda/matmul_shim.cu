@@ -180,6 +180,14 @@ bool tma_operands_ok(const VecopsB200Matmul& p, size_t elem) {
 // 128x256 tensor-core tile.
 bool area_at_most(int64_t m, int64_t n, int64_t limit) { return m > 0 && n > 0 && n <= limit / m; }
 
+// Tuning aid: VECOPS_B200_W8TC_FORM=tmem runs the weight-only tensor-core id on its older kernel (weights as the MMA's
+// M operand, widened into tensor memory, stream-K over caller scratch it cannot do without) instead of the default one
+// (weights as the N operand of the dense GEMM's MMAs, widened into shared memory).
+bool w8_tmem_form() {
+  const char* v = getenv("VECOPS_B200_W8TC_FORM");
+  return v != nullptr && strcmp(v, "tmem") == 0;
+}
+
 bool applicable(const VecopsB200Matmul& p, Row row, uint32_t kernel) {
   switch (kernel) {
     case VECOPS_B200_KERNEL_GENERIC:
@@ -196,9 +204,11 @@ bool applicable(const VecopsB200Matmul& p, Row row, uint32_t kernel) {
              aligned16(p.b) && p.a_stride_m % 8 == 0 && p.b_stride_n % 16 == 0 && p.n < (INT64_C(1) << 31) &&
              p.m < (INT64_C(1) << 31) && p.k < (INT64_C(1) << 31);
     case VECOPS_B200_KERNEL_W8_TCGEN05:
-      return row == Row::W8 && p.m >= 1 && p.m <= W8Tc::kMaxM && p.a_stride_k == 1 && p.b_stride_k == 1 && p.c_stride_n == 1 &&
-             p.k > 0 && p.k % 8 == 0 && aligned16(p.a) && aligned16(p.b) && p.a_stride_m % 8 == 0 && p.b_stride_n % 16 == 0 &&
-             p.a_stride_m >= p.k && p.b_stride_n >= p.k && p.n < (INT64_C(1) << 31) && p.k < (INT64_C(1) << 31);
+      // (the older form of this kernel, weights widened into tensor memory, serves M <= 128 only)
+      return row == Row::W8 && p.m >= 1 && (p.m <= W8Tc::kMaxM || !w8_tmem_form()) && p.a_stride_k == 1 && p.b_stride_k == 1 &&
+             p.c_stride_n == 1 && p.k > 0 && p.k % 8 == 0 && aligned16(p.a) && aligned16(p.b) && p.a_stride_m % 8 == 0 &&
+             p.b_stride_n % 16 == 0 && p.a_stride_m >= p.k && p.b_stride_n >= p.k && p.m < (INT64_C(1) << 31) &&
+             p.n < (INT64_C(1) << 31) && p.k < (INT64_C(1) << 31);
     default:
       return false;
   }
@@ -260,13 +270,13 @@ int32_t select_kernel(const VecopsB200Matmul& p, Row row, uint32_t* kernel, Veco
       if (!tiny && p.k <= 32767 && applicable(p, row, VECOPS_B200_KERNEL_I8_TCGEN05)) pick = VECOPS_B200_KERNEL_I8_TCGEN05;
       break;
     case Row::W8:
-      // few activation rows: the streaming CUDA-core form; up to 128 rows: weights widened into tensor memory.  That
-      // kernel cannot run without its scratch, and the reference's matmul needs none: a call that brings no (or too
-      // small a) workspace is served by the kernels that need none instead of being refused.  (A forced kernel id is
-      // still refused by the launcher, and the workspace query keeps reporting what the preferred kernel wants.)
+      // few activation rows: the streaming CUDA-core form; more: the tensor-core form, which uses the scratch its query
+      // reports to cut tiles along K and runs them whole without it - the reference's matmul needs no workspace, so a
+      // call that brings none is still served.  (Its older form cannot run without scratch: under that tuning switch a
+      // call without it goes to the kernels that need none; a forced kernel id is refused by the launcher.)
       if (p.m > 16 && p.n >= 128 && applicable(p, row, VECOPS_B200_KERNEL_W8_TCGEN05) &&
-          (for_query || (p.workspace != nullptr && aligned16(p.workspace) &&
-                         p.workspace_size >= W8Tc::scratch_bytes(static_cast<int>(p.m), p.k))))
+          (for_query || !w8_tmem_form() ||
+           (p.workspace != nullptr && aligned16(p.workspace) && p.workspace_size >= W8Tc::scratch_bytes(static_cast<int>(p.m), p.k))))
         pick = VECOPS_B200_KERNEL_W8_TCGEN05;
       else if (p.m > 0 && p.n >= 16 && applicable(p, row, VECOPS_B200_KERNEL_W8_SMALL_M)) pick = VECOPS_B200_KERNEL_W8_SMALL_M;
       break;
@@ -726,6 +736,120 @@ int32_t launch_w8_small(const VecopsB200Matmul& p, const DeviceState& dev, cudaS
   return VECOPS_STATUS_OK;
 }
 
+// The weight-only form of the tcgen05 GEMM: one (tile, K slice) per CTA.  Tiles are few for decode shapes (N / 256), so
+// each is cut along K into the largest power-of-two number of slices that still fits the SMs in one wave.
+struct W8MixedPlan {
+  long long tiles = 0;
+  int units = 0;   // 128-wide k units
+  int split = 1;
+  long long scratch_slots = 0;
+};
+
+W8MixedPlan plan_w8_mixed(const VecopsB200Matmul& p, size_t out_elem, int sms) {
+  using G = GemmW8;
+  W8MixedPlan plan;
+  plan.tiles = ((p.m + G::kBlockM - 1) / G::kBlockM) * ((p.n + G::kBlockN - 1) / G::kBlockN);
+  plan.units = static_cast<int>((p.k + G::kUnitK - 1) / G::kUnitK);
+  if (!tail_split_forced_off())
+    while (plan.split * 2 <= G::max_split(out_elem) && plan.tiles * (plan.split * 2) <= sms &&
+           plan.split * 2 * G::kMinSliceUnits <= plan.units)
+      plan.split *= 2;
+  if (plan.split > 1) plan.scratch_slots = plan.tiles * plan.split;
+  return plan;
+}
+
+int sm_count_for_query(const VecopsB200Matmul& p) {
+  int sms = 148;  // the part this library is built for, when no device can be asked
+  int device = p.device_index;
+  if (device < 0 && cudaGetDevice(&device) != cudaSuccess) device = -1;
+  if (device >= 0) {
+    int value = 0;
+    if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && value > 0) sms = value;
+  }
+  cudaGetLastError();  // a host without a GPU is a legal caller of the query
+  return sms;
+}
+
+uint64_t w8_mixed_scratch(const VecopsB200Matmul& p) {
+  if (p.m <= 0 || p.n <= 0 || p.k <= 0) return 0;
+  const W8MixedPlan plan = plan_w8_mixed(p, p.c_dtype == VECOPS_DTYPE_F32 ? 4 : 2, sm_count_for_query(p));
+  return plan.scratch_slots > 0 ? GemmW8::split_scratch_bytes(plan.scratch_slots) : 0;
+}
+
+template <typename OutT>
+int32_t launch_w8_mixed(const VecopsB200Matmul& p, const DeviceState& dev, cudaStream_t stream, VecopsError* error) {
+  using G = GemmW8;
+  if (dev.prop.major != 10)
+    return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "tcgen05 kernels need an sm_100 device, found sm_%d%d", dev.prop.major,
+                     dev.prop.minor);
+  int device = 0;
+  cudaGetDevice(&device);
+  auto kernel = gemm_tcgen05_kernel<false, OutT, false, true>;
+  static std::atomic<bool> raised[kMaxDevices];
+  if (device < 0 || device >= kMaxDevices || !raised[device].load()) {
+    const int32_t rc = raise_smem_limit(kernel, G::kSmemBytes, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+    if (device >= 0 && device < kMaxDevices) raised[device].store(true);
+  }
+  const W8MixedPlan plan = plan_w8_mixed(p, sizeof(OutT), dev.prop.multiProcessorCount);
+  if (plan.tiles * plan.split > 0x7fffffffLL) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "problem too large for w8_tcgen05");
+  CUtensorMap map_a, map_w;
+  GemmStoreMaps maps;
+  int32_t rc = make_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.a, p.k, p.m, p.a_stride_m * 2, 64, G::kBlockM, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.b, p.k, p.n, p.b_stride_n, G::kUnitK, G::kBlockN, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  const CUtensorMapDataType out_type = std::is_same<OutT, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const bool tma_store = !direct_epilogue_forced() && aligned16(p.c) && (p.c_stride_m * sizeof(OutT)) % 16 == 0;
+  if (tma_store) {
+    rc = make_map_2d(&maps.map[0], out_type, sizeof(OutT), p.c, p.n, p.m, p.c_stride_m * sizeof(OutT), 128 / sizeof(OutT), 32, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+  } else {
+    maps.map[0] = map_a;  // never dereferenced
+  }
+  for (int d = 1; d < GemmStoreMaps::kMax; ++d) maps.map[d] = maps.map[0];
+  int split = plan.split;
+  uint32_t* partials = nullptr;
+  unsigned long long* flags = nullptr;
+  if (split > 1) {
+    if (p.workspace == nullptr || !aligned16(p.workspace) || p.workspace_size < G::split_scratch_bytes(plan.scratch_slots)) {
+      split = 1;  // no scratch for the slices to meet in: every tile runs whole, on fewer SMs
+    } else {
+      partials = static_cast<uint32_t*>(p.workspace);
+      flags = reinterpret_cast<unsigned long long*>(static_cast<char*>(p.workspace) + G::split_flags_offset(plan.scratch_slots));
+    }
+  }
+  cudaLaunchConfig_t config = {};
+  cudaLaunchAttribute attributes[1] = {};
+  config.gridDim = dim3(static_cast<unsigned>(plan.tiles * split));
+  config.blockDim = dim3(G::kThreads);
+  config.dynamicSmemBytes = G::kSmemBytes;
+  config.stream = stream;
+  config.attrs = attributes;
+  const char* pdl = getenv("VECOPS_B200_GEMM_PDL");
+  if (pdl == nullptr || pdl[0] != '0') {
+    attributes[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[0].val.programmaticStreamSerializationAllowed = 1;
+    config.numAttrs = 1;
+  }
+  uint32_t idesc = umma_instr_desc(kUmmaAccF32, kUmmaBF16, kUmmaBF16, G::kBlockM, G::kBlockN);
+  OutT* c = static_cast<OutT*>(p.c);
+  long long ldc = p.c_stride_m;
+  int m = static_cast<int>(p.m), n = static_cast<int>(p.n), k = static_cast<int>(p.k);
+  const float* scale = p.column_scale;
+  int store_flag = tma_store ? 1 : 0, num_dest = 1, col_offset = 0, raster_group = 4;
+  unsigned long long nonce = split > 1 ? fresh_nonce(p.workspace) : 0ull;
+  uint32_t* status_word = status_word_of(device);
+  unsigned long long* trace = g_trace;
+  EpilogueArgs epilogue = tl_epilogue;
+  void* args[] = {&map_a, &map_w, &maps, &num_dest, &col_offset, &c, &ldc, &m, &n, &k, &scale, &idesc, &store_flag,
+                  &raster_group, &split, &partials, &flags, &nonce, &epilogue, &status_word, &trace};
+  cudaError_t launched = cudaLaunchKernelExC(&config, reinterpret_cast<const void*>(kernel), args);
+  if (launched != cudaSuccess) return cuda_fail(error, launched, "launch of w8_tcgen05");
+  g_launches.fetch_add(1);
+  return VECOPS_STATUS_OK;
+}
+
 // Scratch for the K slices of the tail tiles.  The grid is one CTA per SM; the SM count comes from the device the
 // problem names when one is usable, else from the part this library is built for (148).
 uint64_t tcgen05_tail_scratch(const VecopsB200Matmul& p, bool int8) {
@@ -953,7 +1077,7 @@ int32_t vecops_b200_matmul_workspace(const VecopsB200Matmul* problem, uint64_t* 
   // tcgen05 GEMMs when their last wave is cut along K.  Every other split-K meets in shared memory.
   *bytes = 0;
   if (kernel == VECOPS_B200_KERNEL_W8_TCGEN05) {
-    *bytes = W8Tc::scratch_bytes(static_cast<int>(problem->m), problem->k);
+    *bytes = w8_tmem_form() ? W8Tc::scratch_bytes(static_cast<int>(problem->m), problem->k) : w8_mixed_scratch(*problem);
   } else if (kernel == VECOPS_B200_KERNEL_BF16_TCGEN05 || kernel == VECOPS_B200_KERNEL_I8_TCGEN05) {
     *bytes = tcgen05_tail_scratch(*problem, kernel == VECOPS_B200_KERNEL_I8_TCGEN05);
   }
@@ -1010,8 +1134,12 @@ int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* err
           break;
         case VECOPS_B200_KERNEL_W8_SMALL_M: rc = launch_w8_small(p, *dev, stream, error); break;
         case VECOPS_B200_KERNEL_W8_TCGEN05:
-          rc = p.c_dtype == VECOPS_DTYPE_BF16 ? launch_w8_tcgen05_typed<__nv_bfloat16>(p, *dev, stream, error)
-                                              : launch_w8_tcgen05_typed<float>(p, *dev, stream, error);
+          if (w8_tmem_form())
+            rc = p.c_dtype == VECOPS_DTYPE_BF16 ? launch_w8_tcgen05_typed<__nv_bfloat16>(p, *dev, stream, error)
+                                                : launch_w8_tcgen05_typed<float>(p, *dev, stream, error);
+          else
+            rc = p.c_dtype == VECOPS_DTYPE_BF16 ? launch_w8_mixed<__nv_bfloat16>(p, *dev, stream, error)
+                                                : launch_w8_mixed<float>(p, *dev, stream, error);
           break;
         default: rc = set_error(error, VECOPS_STATUS_INTERNAL_ERROR, "kernel id %u has no launcher", kernel);
       }
