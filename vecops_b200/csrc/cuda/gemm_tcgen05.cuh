@@ -99,15 +99,14 @@ struct GemmPair : GemmTc {
 // barriers; the epilogue's staging buffers lie over the start of the int8 ring (free by then: one work item per CTA).
 struct GemmW8 : GemmTc {
   static constexpr int kUnitK = 128;                  // k per unit: one TMA box of W (256 rows x 128 bytes)
-  static constexpr int kStages = 2;                   // activation units in flight (two 64-k swizzle atoms each)
-  static constexpr int kAUnitBytes = 2 * kABytes;     // 32 KB
+  static constexpr int kStages = 4;                   // activation 64-k atoms in flight (16 KB each: the MMA's 128 rows)
   static constexpr int kRawStages = 3;                // int8 weight units in flight
   static constexpr int kRawBytes = kBlockN * kUnitK;  // 32 KB
   static constexpr int kWideStages = 2;               // widened 64-k blocks: one being multiplied, one being written
   static constexpr int kWideBytes = kBBytes;          // 32 KB
   static constexpr int kConvertWarps = 8;
   static constexpr int kThreads = 32 * (2 + kEpiWarps + kConvertWarps);
-  static constexpr int kRawOffset = kStages * kAUnitBytes;
+  static constexpr int kRawOffset = kStages * kABytes;
   static constexpr int kWideOffset = kRawOffset + kRawStages * kRawBytes;
   static constexpr int kRingBytes = kWideOffset + kWideStages * kWideBytes;
   static constexpr int kSmemBytes = kRingBytes + kBarrierBytes + 1024;
@@ -352,15 +351,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       GemmItem item;
       if constexpr (kW8) {
         // Two independent rings, neither waiting for the other: the int8 weight units run as far ahead as their ring
-        // allows (they are what HBM latency hides behind), the activation units (from L2) follow the MMA.
+        // allows (they are what HBM latency hides behind), the activation atoms (64 k each, from L2) follow the MMA.
         if (gemm_item(0, num_tiles, num_kb, split, worker, workers, item)) {
           int tm, tn;
           tile_coords(item.tile, tiles_m, tiles_n, raster_group, tm, tn);
           const int units = item.kb_end - item.kb_begin;
+          const int atoms = 2 * units;
           int raw_issued = 0, act_issued = 0, rs = 0;
           uint32_t rphase = 0;
           const long long started = clock64();
-          while (raw_issued < units || act_issued < units) {
+          while (raw_issued < units || act_issued < atoms) {
             bool progress = false;
             if (raw_issued < units && mbar_test_wait(raw_empty_bar + 8 * rs, rphase ^ 1u)) {
               mbar_arrive_expect_tx(raw_full_bar + 8 * rs, GemmW8::kRawBytes);
@@ -370,12 +370,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
               ++raw_issued;
               progress = true;
             }
-            if (act_issued < units && mbar_test_wait(empty_bar + 8 * stage, phase ^ 1u)) {
-              const uint32_t a_dst = smem_base + stage * GemmW8::kAUnitBytes;
-              const int k0 = (item.kb_begin + act_issued) * GemmW8::kUnitK;  // past K: zero-filled by TMA
-              mbar_arrive_expect_tx(full_bar + 8 * stage, GemmW8::kAUnitBytes);
-              tma_load_2d(a_dst, &tma_a, full_bar + 8 * stage, k0, tm * G::kBlockM);
-              tma_load_2d(a_dst + G::kABytes, &tma_a, full_bar + 8 * stage, k0 + 64, tm * G::kBlockM);
+            if (act_issued < atoms && mbar_test_wait(empty_bar + 8 * stage, phase ^ 1u)) {
+              mbar_arrive_expect_tx(full_bar + 8 * stage, G::kABytes);
+              tma_load_2d(smem_base + stage * G::kABytes, &tma_a, full_bar + 8 * stage,
+                          item.kb_begin * GemmW8::kUnitK + act_issued * 64, tm * G::kBlockM);  // past K: zero-filled by TMA
               if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
               ++act_issued;
               progress = true;
@@ -439,34 +437,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         tcgen05_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * G::kBlockN;
         if constexpr (kW8) {
-          // per unit: the activation unit (two 64-k atoms) from its ring, each half against the widened block of that half
+          // per 64-k atom: the activation atom from its ring against the widened block of the same k
           int ws = 0;
           uint32_t wphase = 0;
-          for (int kb = item.kb_begin; ok && kb < item.kb_end; ++kb) {
-            if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag)) {
+          for (int atom = 2 * item.kb_begin; ok && atom < 2 * item.kb_end; ++atom) {
+            if (!mbar_wait(wide_full_bar + 8 * ws, wphase, abort_flag) || !mbar_wait(full_bar + 8 * stage, phase, abort_flag)) {
               report_status(status, kStatusMmaWaitFull);
               *abort_flag = 1;
               ok = false;
               break;
             }
-            for (int half = 0; half < 2; ++half) {
-              if (!mbar_wait(wide_full_bar + 8 * ws, wphase, abort_flag)) {
-                report_status(status, kStatusMmaWaitFull);
-                *abort_flag = 1;
-                ok = false;
-                break;
-              }
-              tcgen05_fence_after_sync();
-              const uint64_t a_desc = umma_smem_desc_sw128(smem_base + stage * GemmW8::kAUnitBytes + half * G::kABytes);
-              const uint64_t b_desc = umma_smem_desc_sw128(smem_base + GemmW8::kWideOffset + ws * GemmW8::kWideBytes);
+            tcgen05_fence_after_sync();
+            const uint64_t a_desc = umma_smem_desc_sw128(smem_base + stage * G::kABytes);
+            const uint64_t b_desc = umma_smem_desc_sw128(smem_base + GemmW8::kWideOffset + ws * GemmW8::kWideBytes);
 #pragma unroll
-              for (int kk = 0; kk < G::kBlockKBytes / 32; ++kk)
-                umma_f16(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb != item.kb_begin || half != 0 || kk != 0) ? 1u : 0u);
-              umma_commit(wide_empty_bar + 8 * ws);
-              if (++ws == GemmW8::kWideStages) { ws = 0; wphase ^= 1u; }
-            }
-            if (!ok) break;
+            for (int kk = 0; kk < G::kBlockKBytes / 32; ++kk)
+              umma_f16(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (atom != 2 * item.kb_begin || kk != 0) ? 1u : 0u);
+            umma_commit(wide_empty_bar + 8 * ws);
             umma_commit(empty_bar + 8 * stage);
+            if (++ws == GemmW8::kWideStages) { ws = 0; wphase ^= 1u; }
             if (++stage == G::kStages) { stage = 0; phase ^= 1u; }
           }
         } else
