@@ -682,22 +682,45 @@ void launch_w8_small_typed(const VecopsB200Matmul& p, cudaStream_t stream) {
   g_launches.fetch_add(1);
 }
 
-template <int kMTiles, int kChunks, typename OutT>
+template <int kChunks, bool kRows16, typename OutT>
 int32_t launch_w8_stream_typed(const VecopsB200Matmul& p, const DeviceState& dev, cudaStream_t stream, VecopsError* error) {
   using G = W8Stream;
-  auto kernel = w8_stream_kernel<kMTiles, kChunks, OutT>;
-  const int smem = G::smem_bytes(static_cast<int>(p.k), kMTiles);
+  auto kernel = w8_stream_kernel<kChunks, kRows16, OutT>;
+  const int smem = G::smem_bytes(static_cast<int>(p.k), kRows16);
   // the attribute is per kernel instantiation and per device; setting it is cheap and idempotent
   int32_t rc = raise_smem_limit(kernel, smem, error);
   if (rc != VECOPS_STATUS_OK) return rc;
-  const long long items = (p.n + G::kRows - 1) / G::kRows;
+  // one CTA per SM, each with an equal share of W's rows (to within one row); fewer when there are not 8 rows for each
+  const long long items = (p.n + G::rows(kRows16) - 1) / G::rows(kRows16);
   const int grid = static_cast<int>(items < dev.prop.multiProcessorCount ? items : dev.prop.multiProcessorCount);
   int device = 0;
   cudaGetDevice(&device);
-  kernel<<<grid, G::kThreads, smem, stream>>>(static_cast<const __nv_bfloat16*>(p.a), p.a_stride_m, static_cast<const int8_t*>(p.b),
-                                              p.b_stride_n, p.column_scale, static_cast<OutT*>(p.c), p.c_stride_m,
-                                              static_cast<int>(p.m), static_cast<int>(p.n), static_cast<int>(p.k), tl_epilogue,
-                                              status_word_of(device));
+  cudaLaunchConfig_t config = {};
+  cudaLaunchAttribute attributes[1] = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(G::kThreads);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  config.attrs = attributes;
+  // programmatic dependent launch: barrier set-up overlaps the previous kernel's tail (VECOPS_B200_GEMM_PDL=0: the ordinary way)
+  const char* pdl = getenv("VECOPS_B200_GEMM_PDL");
+  if (pdl == nullptr || pdl[0] != '0') {
+    attributes[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[0].val.programmaticStreamSerializationAllowed = 1;
+    config.numAttrs = 1;
+  }
+  const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(p.a);
+  const int8_t* w = static_cast<const int8_t*>(p.b);
+  const float* scale = p.column_scale;
+  OutT* c = static_cast<OutT*>(p.c);
+  long long lda = p.a_stride_m, ldw = p.b_stride_n, ldc = p.c_stride_m;
+  int m = static_cast<int>(p.m), n = static_cast<int>(p.n), k = static_cast<int>(p.k);
+  EpilogueArgs epilogue = tl_epilogue;
+  uint32_t* status_word = status_word_of(device);
+  unsigned long long* trace = g_trace;
+  void* args[] = {&a, &lda, &w, &ldw, &scale, &c, &ldc, &m, &n, &k, &epilogue, &status_word, &trace};
+  const cudaError_t launched = cudaLaunchKernelExC(&config, reinterpret_cast<const void*>(kernel), args);
+  if (launched != cudaSuccess) return cuda_fail(error, launched, "launch of the streaming weight-only kernel");
   g_launches.fetch_add(1);
   return VECOPS_STATUS_OK;
 }
@@ -708,21 +731,21 @@ bool w8_stream_applicable(const VecopsB200Matmul& p, const DeviceState& dev) {
   const char* path = getenv("VECOPS_B200_W8_PATH");
   if (path != nullptr && strcmp(path, "small") == 0) return false;
   return dev.prop.major >= 9 && p.m <= 16 && p.k % W8Stream::kChunkK == 0 && p.k <= W8Stream::kMaxK &&
-         static_cast<size_t>(W8Stream::smem_bytes(static_cast<int>(p.k), 2)) <= dev.prop.sharedMemPerBlockOptin;
+         static_cast<size_t>(W8Stream::smem_bytes(static_cast<int>(p.k), p.m > 8)) <= dev.prop.sharedMemPerBlockOptin;
 }
 
 int32_t launch_w8_small(const VecopsB200Matmul& p, const DeviceState& dev, cudaStream_t stream, VecopsError* error) {
   if (p.c_stride_n != 1) return set_error(error, VECOPS_STATUS_NOT_APPLICABLE, "w8_small_m needs a row-major C");
   if (w8_stream_applicable(p, dev)) {
     const bool bf16_out = p.c_dtype == VECOPS_DTYPE_BF16;
-    const bool one_tile = p.m <= 8, one_chunk = p.k <= 2048;
-    if (one_tile && one_chunk)
-      return bf16_out ? launch_w8_stream_typed<1, 1, __nv_bfloat16>(p, dev, stream, error) : launch_w8_stream_typed<1, 1, float>(p, dev, stream, error);
-    if (one_tile)
-      return bf16_out ? launch_w8_stream_typed<1, 2, __nv_bfloat16>(p, dev, stream, error) : launch_w8_stream_typed<1, 2, float>(p, dev, stream, error);
+    const bool rows16 = p.m > 8, one_chunk = p.k <= 2048;
+    if (!rows16 && one_chunk)
+      return bf16_out ? launch_w8_stream_typed<1, false, __nv_bfloat16>(p, dev, stream, error) : launch_w8_stream_typed<1, false, float>(p, dev, stream, error);
+    if (!rows16)
+      return bf16_out ? launch_w8_stream_typed<2, false, __nv_bfloat16>(p, dev, stream, error) : launch_w8_stream_typed<2, false, float>(p, dev, stream, error);
     if (one_chunk)
-      return bf16_out ? launch_w8_stream_typed<2, 1, __nv_bfloat16>(p, dev, stream, error) : launch_w8_stream_typed<2, 1, float>(p, dev, stream, error);
-    return bf16_out ? launch_w8_stream_typed<2, 2, __nv_bfloat16>(p, dev, stream, error) : launch_w8_stream_typed<2, 2, float>(p, dev, stream, error);
+      return bf16_out ? launch_w8_stream_typed<1, true, __nv_bfloat16>(p, dev, stream, error) : launch_w8_stream_typed<1, true, float>(p, dev, stream, error);
+    return bf16_out ? launch_w8_stream_typed<2, true, __nv_bfloat16>(p, dev, stream, error) : launch_w8_stream_typed<2, true, float>(p, dev, stream, error);
   }
   if ((p.m + 31) / 32 > 65535) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "M too large for w8_small_m");
   const bool c_bf16 = p.c_dtype == VECOPS_DTYPE_BF16;

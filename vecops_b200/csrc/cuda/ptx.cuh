@@ -213,6 +213,12 @@ __device__ __forceinline__ void multimem_st_v4(void* multicast_addr, uint4 v) {
 
 // ---------------------------------------------------------------- TMA
 
+// Ask for `bytes` (a multiple of 16) of contiguous global memory at `gmem` (16-byte aligned) to be brought into L2.
+// A hint: nothing waits for it and nothing depends on it.
+__device__ __forceinline__ void prefetch_l2_bulk(const void* gmem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }

@@ -3,19 +3,18 @@
 //     C[m,n] = convert( (sum_k f32(A[m,k]) * f32(W[n,k])) * scale[n] )
 //
 // How the bytes move:
-//   * one persistent CTA per SM; work items are 16-row tiles of W (16 x K bytes,
-//     contiguous rows), taken round-robin;
-//   * a producer warp streams items into a 3-stage shared-memory ring with
-//     cp.async.bulk (one bulk copy per row, completion counted in bytes on an
-//     mbarrier), so ~190 KB per SM are in flight without holding registers;
-//   * 16 consumer warps split K: warp w owns the 128-wide k-chunks w, w+16.
-//     Its activation fragments for those chunks are loaded ONCE into registers
-//     at kernel start and reused for every item, so the inner loop touches
-//     shared memory only for weights;
-//   * per item the 16 partial 16x(8*MT) fragments meet in shared memory and are
-//     summed in fixed warp order (deterministic), scaled, converted and stored.
-//     The hand-over uses two mbarriers (partials written / partials consumed),
-//     so only the few warps that do the summing ever wait.
+//   * one persistent CTA per SM owns a contiguous range of W's rows, N / gridDim of them to within one row, so every
+//     SM streams the same number of bytes; it walks the range in items of 8 rows (8 x K bytes, contiguous rows);
+//   * a producer warp streams items into a shared-memory ring with cp.async.bulk (one bulk copy per row, completion
+//     counted in bytes on an mbarrier): five stages at K = 4096, ~160 KB per SM in flight without holding registers;
+//   * 16 consumer warps split K: warp w owns the 128-wide k-chunks w, w+16.  Its activation fragments for those
+//     chunks are loaded ONCE into registers at kernel start and reused for every item, so the inner loop touches
+//     shared memory only for weights.  The weights are the B operand of mma.m16n8k16 (eight rows of W = the n of the
+//     instruction), the activations its A operand (up to 16 rows);
+//   * per item each consumer warp leaves its 16 x 8 partial fragment in a ring of four reduction buffers and goes
+//     straight on to the next item; a summing warp of its own adds the sixteen fragments in fixed warp order
+//     (deterministic), scales, converts and stores.  No consumer ever waits for a sum.
+// The kernel is launched as a programmatic dependent: its set-up runs while the previous kernel of the stream drains.
 //
 // How the arithmetic is done.  The kernel is HBM-bound only if widening a
 // weight costs about one instruction, so the widening goes int8 -> fp16 (two
@@ -47,19 +46,29 @@ namespace vb200 {
 
 struct W8Stream {
   static constexpr int kConsumerWarps = 16;
-  static constexpr int kThreads = 32 * (1 + kConsumerWarps);
-  static constexpr int kStages = 3;
-  static constexpr int kRows = 16;
+  static constexpr int kThreads = 32 * (kConsumerWarps + 2);  // + the producer warp and the summing warp
+  // Weight rows per item.  Up to 8 activation rows the weights are the m16 operand of mma.m16n8k16 (16 rows of W per
+  // instruction, the activations its n8): half as many instructions per byte of W as the other way round, and
+  // mma.sync is slow enough on this part (one per ~30 cycles per scheduler) to be what bounds the kernel otherwise.
+  // From 9 to 16 activation rows they are its n8 operand (8 rows of W, the activations its m16).
+  __host__ __device__ static constexpr int rows(bool rows16) { return rows16 ? 8 : 16; }
   static constexpr int kChunkK = 128;
   static constexpr int kMaxK = 4096;
   static constexpr int kRowPad = 64;
-  static constexpr int kSideBytes = 16 * 16 * 4 /* row maxima */ + 16 * 4 /* inverse row scales */ + 128 /* barriers */;
-  __host__ __device__ static constexpr int stage_bytes(int K) { return kRows * (K + kRowPad); }
-  __host__ __device__ static constexpr int red_bytes(int m_tiles) { return kConsumerWarps * m_tiles * 32 * 4 * 4; }
-  __host__ __device__ static constexpr int smem_bytes(int K, int m_tiles) {
-    return kStages * stage_bytes(K) + red_bytes(m_tiles) + kSideBytes + 128;
+  static constexpr int kMaxStages = 8;
+  static constexpr int kRedStages = 2;
+  static constexpr int kRedBytes = kConsumerWarps * 32 * 16;  // 8 KB: one 16 x 8 fp32 fragment (four floats per lane) per consumer warp
+  static constexpr int kSideBytes = 16 * 16 * 4 /* row maxima */ + 16 * 4 /* inverse row scales */ + 320 /* barriers */;
+  __host__ __device__ static constexpr int stage_bytes(int K, bool rows16) { return rows(rows16) * (K + kRowPad); }
+  __host__ __device__ static constexpr int stages(int K, bool rows16) {
+    const int fit = (227 * 1024 - 256 - kRedStages * kRedBytes - kSideBytes) / stage_bytes(K, rows16);
+    return fit < kMaxStages ? fit : kMaxStages;
+  }
+  __host__ __device__ static constexpr int smem_bytes(int K, bool rows16) {
+    return stages(K, rows16) * stage_bytes(K, rows16) + kRedStages * kRedBytes + kSideBytes + 128;
   }
 };
+static_assert(W8Stream::stages(W8Stream::kMaxK, false) >= 3 && W8Stream::stages(W8Stream::kMaxK, true) >= 3, "the weight ring must hold enough bytes in flight");
 
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t smem_dst, const void* gmem_src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_dst),
@@ -92,180 +101,305 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// kMTiles: 1 (M <= 8) or 2 (M <= 16).  kChunks: k-chunks per warp, 1 (K <= 2048) or 2 (K <= 4096).
-template <int kMTiles, int kChunks, typename OutT>
+// kChunks: k-chunks per warp, 1 (K <= 2048) or 2 (K <= 4096).  kRows16: activation rows 8..15 exist (M > 8).
+template <int kChunks, bool kRows16, typename OutT>
 __global__ void __launch_bounds__(W8Stream::kThreads, 1)
 w8_stream_kernel(const __nv_bfloat16* __restrict__ a, long long lda, const int8_t* __restrict__ w, long long ldw,
                  const float* __restrict__ scale, OutT* __restrict__ c, long long ldc, int M, int N, int K, EpilogueArgs ep,
-                 uint32_t* __restrict__ status) {
+                 uint32_t* __restrict__ status, unsigned long long* __restrict__ trace) {
   using G = W8Stream;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 127u) & ~127u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  constexpr int kRows = G::rows(kRows16);  // weight rows per item
   const int pitch = K + G::kRowPad;
-  const int stage_bytes = G::kRows * pitch;
-  const int side_offset = G::kStages * stage_bytes + G::red_bytes(kMTiles);
-  float* red = reinterpret_cast<float*>(smem_gen + G::kStages * stage_bytes);
+  const int stage_bytes = kRows * pitch;
+  const int stages = G::stages(K, kRows16);
+  const int red_offset = stages * stage_bytes;
+  const int side_offset = red_offset + G::kRedStages * G::kRedBytes;
   uint32_t* row_max = reinterpret_cast<uint32_t*>(smem_gen + side_offset);          // [16 warps][16 rows]
   float* inv_row_scale = reinterpret_cast<float*>(smem_gen + side_offset + 1024);   // [16 rows]
   uint8_t* bar_gen = smem_gen + side_offset + 1024 + 64;
   const uint32_t bar_base = smem_base + side_offset + 1024 + 64;
-  const uint32_t full_bar = bar_base;                       // W stage landed            (producer -> consumers)
-  const uint32_t empty_bar = bar_base + 8 * G::kStages;     // W stage consumed          (consumers -> producer)
-  const uint32_t red_full_bar = bar_base + 16 * G::kStages; // all partial sums written  (consumers -> summing warps)
-  const uint32_t red_free_bar = red_full_bar + 8;           // partial sums consumed     (summing warps -> consumers)
-  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bar_gen + 16 * G::kStages + 16);
-  constexpr int kSumWarps = 4 * kMTiles;                    // 128 sums per m-tile, one per thread
+  const uint32_t full_bar = bar_base;                                // W stage landed                (producer -> consumers)
+  const uint32_t empty_bar = full_bar + 8 * G::kMaxStages;           // W stage consumed              (consumers -> producer)
+  const uint32_t red_full_bar = empty_bar + 8 * G::kMaxStages;       // all partial fragments written (consumers -> summing warp)
+  const uint32_t red_free_bar = red_full_bar + 8 * G::kRedStages;    // partial fragments summed      (summing warp -> consumers)
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bar_gen + 16 * G::kMaxStages + 16 * G::kRedStages);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_items = (N + G::kRows - 1) / G::kRows;
+  // optional timeline for tuning: 16 slots per CTA (nanosecond stamps and per-role wait cycles), written only when a trace buffer is given
+  auto stamp = [&](int slot) {
+    if (trace != nullptr) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      trace[blockIdx.x * 16 + slot] = now;
+    }
+  };
+  if (threadIdx.x == 0) stamp(0);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < G::kStages; ++s) {
+    for (int s = 0; s < G::kMaxStages; ++s) {
       mbar_init(full_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, G::kConsumerWarps);
     }
-    mbar_init(red_full_bar, G::kConsumerWarps);
-    mbar_init(red_free_bar, kSumWarps);
+    for (int r = 0; r < G::kRedStages; ++r) {
+      mbar_init(red_full_bar + 8 * r, G::kConsumerWarps);
+      mbar_init(red_free_bar + 8 * r, 1);
+    }
     *abort_flag = 0;
     mbar_fence_init();
   }
   __syncthreads();
+  // this CTA's rows of W: an equal share to within one row
+  const int row_begin = static_cast<int>(static_cast<long long>(N) * blockIdx.x / gridDim.x);
+  const int row_end = static_cast<int>(static_cast<long long>(N) * (blockIdx.x + 1) / gridDim.x);
+  const int num_items = (row_end - row_begin + kRows - 1) / kRows;
+  // Everything above touched only this CTA's shared memory and may run while the previous kernel of the stream drains;
+  // everything below reads or writes global memory and waits for it.  One thing is done before the wait: the rows that
+  // will fill the ring first are asked into L2.  That is a hint, not a read - nothing is consumed, and should the
+  // previous kernel still be writing those rows the copies below, issued after the wait, see its data - but HBM is idle
+  // while the previous kernel drains its last stages, and the first copies of this one then find their bytes in L2.
+  grid_launch_dependents();
+  if (warp == G::kConsumerWarps) {
+    for (int item = 0; item < stages && item < num_items; ++item) {
+      const int row = row_begin + item * kRows + lane;
+      if (lane < kRows && row < row_end) prefetch_l2_bulk(w + static_cast<long long>(row) * ldw, static_cast<uint32_t>(K));
+    }
+  }
+  grid_dependency_wait();
+
+  auto give_up = [&]() {
+    if (lane == 0) {
+      report_status(status, kStatusW8Wait);
+      *abort_flag = 1;
+    }
+  };
 
   if (warp == G::kConsumerWarps) {
     // ---------------------------------------------------------------- producer warp
     int stage = 0;
     uint32_t phase = 0;
-    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+    long long waited = 0;
+    if (lane == 0) stamp(1);
+    for (int item = 0; item < num_items; ++item) {
+      const long long t0 = trace != nullptr ? clock64() : 0;
       if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag)) {
-        if (lane == 0) {
-          report_status(status, kStatusW8Wait);
-          *abort_flag = 1;
-        }
+        give_up();
         break;
       }
-      const int row0 = item * G::kRows;
-      const int rows = min(G::kRows, N - row0);
+      if (trace != nullptr) waited += clock64() - t0;
+      const int row0 = row_begin + item * kRows;
+      const int rows = min(kRows, row_end - row0);
       if (lane == 0) mbar_arrive_expect_tx(full_bar + 8 * stage, static_cast<uint32_t>(rows) * K);
       __syncwarp();
       if (lane < rows)
         bulk_copy_g2s(smem_base + stage * stage_bytes + lane * pitch, w + static_cast<long long>(row0 + lane) * ldw,
                       static_cast<uint32_t>(K), full_bar + 8 * stage);
-      if (++stage == G::kStages) {
+      if (++stage == stages) {
         stage = 0;
         phase ^= 1u;
       }
+    }
+    if (lane == 0 && trace != nullptr) {
+      trace[blockIdx.x * 16 + 8] = static_cast<unsigned long long>(waited);
+      stamp(2);
+    }
+  } else if (warp == G::kConsumerWarps + 1) {
+    // ---------------------------------------------------------------- summing warp
+    // lane l holds, like every consumer lane, the fragment entries (m = g, n = 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)
+    const int g = lane >> 2, t = lane & 3;
+    long long waited = 0;
+    for (int item = 0; item < num_items; ++item) {
+      const int rb = item % G::kRedStages;
+      const long long t0 = trace != nullptr ? clock64() : 0;
+      if (!mbar_wait(red_full_bar + 8 * rb, static_cast<uint32_t>(item / G::kRedStages) & 1u, abort_flag)) {
+        give_up();
+        break;
+      }
+      if (trace != nullptr) waited += clock64() - t0;
+      if (item == 0 && lane == 0) stamp(6);
+      const uint32_t red = smem_base + red_offset + rb * G::kRedBytes + lane * 16;
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int q = 0; q < G::kConsumerWarps; ++q) {
+        const uint4 v = lds128(red + q * 512);
+        sum.x += __uint_as_float(v.x);
+        sum.y += __uint_as_float(v.y);
+        sum.z += __uint_as_float(v.z);
+        sum.w += __uint_as_float(v.w);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(red_free_bar + 8 * rb);
+      // fragment entries of this lane: (i = g, j = 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1), where the 16-row index i is the
+      // activation row m and the 8-column index j the weight row when the activations are the m16 operand (kRows16),
+      // and the other way round when the weights are
+      const float sums[2][2] = {{sum.x, sum.y}, {sum.z, sum.w}};
+      const int item_row0 = row_begin + item * kRows;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float out[2];
+        bool valid[2];
+        int ms[2], ns[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          ms[i] = kRows16 ? g + 8 * half : 2 * t + i;
+          ns[i] = kRows16 ? item_row0 + 2 * t + i : item_row0 + g + 8 * half;
+          valid[i] = ms[i] < M && ns[i] < row_end;
+          const float factor = (valid[i] && scale != nullptr) ? __ldg(scale + ns[i]) : 1.f;
+          // (the fused form's accumulator input joins the sum once the power of two of the row is divided out)
+          const float base = sums[half][i] * inv_row_scale[ms[i] & 15];
+          out[i] = !valid[i] ? 0.f : ep.active ? epilogue_float(base, ep, ms[i], ns[i], factor) : base * factor;
+        }
+        if constexpr (kRows16) {
+          // two neighbouring columns of one output row
+          OutT* dst = c + static_cast<long long>(ms[0]) * ldc + ns[0];
+          if constexpr (sizeof(OutT) == 2) {
+            if (valid[0] && valid[1] && (reinterpret_cast<uintptr_t>(dst) & 3u) == 0) {
+              *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(out[0], out[1]);
+              continue;
+            }
+          }
+          if (valid[0]) dst[0] = static_cast<OutT>(out[0]);
+          if (valid[1]) dst[1] = static_cast<OutT>(out[1]);
+        } else {
+          // one column of two neighbouring output rows
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+            if (valid[i]) c[static_cast<long long>(ms[i]) * ldc + ns[i]] = static_cast<OutT>(out[i]);
+        }
+      }
+    }
+    if (lane == 0 && trace != nullptr) {
+      trace[blockIdx.x * 16 + 9] = static_cast<unsigned long long>(waited);
+      stamp(7);
     }
   } else {
     // ---------------------------------------------------------------- consumer warps
     const int g = lane >> 2;
     const int t = lane & 3;
+    constexpr int kRowHalves = kRows16 ? 2 : 1;
 
-    // Activation fragments of this warp's k-chunks: bf16 from global, kept in registers as fp16.
-    uint4 act[kMTiles][kChunks][4];
-    uint32_t local_max[kMTiles];
+    // Activation fragments of this warp's k-chunks: bf16 from global, kept in registers as fp16.  For the 64 k of
+    // group gq of chunk ch, this lane holds A[g + 8*rh][k0 + 64*gq + 16*t + 0..15] as two 16-byte halves.
+    uint4 act[kChunks][2][kRowHalves][2];
+    uint32_t local_max[kRowHalves];
 #pragma unroll
-    for (int j = 0; j < kMTiles; ++j) {
-      local_max[j] = 0;
-      const int m = 8 * j + g;
+    for (int rh = 0; rh < kRowHalves; ++rh) {
+      local_max[rh] = 0;
+      const int m = g + 8 * rh;
 #pragma unroll
       for (int ch = 0; ch < kChunks; ++ch) {
         const int k0 = (warp + G::kConsumerWarps * ch) * G::kChunkK;
         const bool valid = m < M && k0 < K;
         const __nv_bfloat16* src = a + static_cast<long long>(valid ? m : 0) * lda + (valid ? k0 : 0) + 16 * t;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          // q = 0,1: k0 + 16t + [0,16);  q = 2,3: k0 + 64 + 16t + [0,16)   (8 bf16 per 16-byte load)
-          const uint4 v = valid ? __ldg(reinterpret_cast<const uint4*>(src + (q >> 1) * 64) + (q & 1)) : make_uint4(0, 0, 0, 0);
-          act[j][ch][q] = v;
-          const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+        for (int gq = 0; gq < 2; ++gq)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            local_max[j] = max(local_max[j], words[i] & 0x7fffu);
-            local_max[j] = max(local_max[j], (words[i] >> 16) & 0x7fffu);
+          for (int hv = 0; hv < 2; ++hv) {
+            const uint4 v = valid ? __ldg(reinterpret_cast<const uint4*>(src + 64 * gq) + hv) : make_uint4(0, 0, 0, 0);
+            act[ch][gq][rh][hv] = v;
+            const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              local_max[rh] = max(local_max[rh], words[i] & 0x7fffu);
+              local_max[rh] = max(local_max[rh], (words[i] >> 16) & 0x7fffu);
+            }
           }
-        }
       }
       // the four threads of a quad hold the same row
-      local_max[j] = max(local_max[j], __shfl_xor_sync(0xffffffffu, local_max[j], 1));
-      local_max[j] = max(local_max[j], __shfl_xor_sync(0xffffffffu, local_max[j], 2));
-      if (t == 0) row_max[warp * 16 + 8 * j + g] = local_max[j];
+      local_max[rh] = max(local_max[rh], __shfl_xor_sync(0xffffffffu, local_max[rh], 1));
+      local_max[rh] = max(local_max[rh], __shfl_xor_sync(0xffffffffu, local_max[rh], 2));
+      if (t == 0) row_max[warp * 16 + 8 * rh + g] = local_max[rh];
     }
-    if (kMTiles == 1 && t == 0) row_max[warp * 16 + 8 + g] = 0;
+    if (!kRows16 && t == 0) row_max[warp * 16 + 8 + g] = 0;
     // consumer-only barrier; every consumer warp reaches it exactly once, before any bounded wait
     asm volatile("bar.sync 1, %0;" ::"n"(G::kConsumerWarps * 32) : "memory");
 
-    float row_scale[kMTiles];
 #pragma unroll
-    for (int j = 0; j < kMTiles; ++j) {
-      const int m = 8 * j + g;
+    for (int rh = 0; rh < kRowHalves; ++rh) {
+      const int m = g + 8 * rh;
       uint32_t biggest = 0;
 #pragma unroll
       for (int q = 0; q < G::kConsumerWarps; ++q) biggest = max(biggest, row_max[q * 16 + m]);
       const int exponent = static_cast<int>(biggest >> 7);  // biased exponent of the largest |a| in the row
       int shift = (exponent == 0 || exponent == 255) ? 0 : (127 + 14) - exponent;
       shift = min(shift, 120);
-      row_scale[j] = __uint_as_float(static_cast<uint32_t>(shift + 127) << 23);
+      const float row_scale = __uint_as_float(static_cast<uint32_t>(shift + 127) << 23);
       if (warp == 0 && t == 0) inv_row_scale[m] = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);
 #pragma unroll
       for (int ch = 0; ch < kChunks; ++ch)
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint32_t words[4] = {act[j][ch][q].x, act[j][ch][q].y, act[j][ch][q].z, act[j][ch][q].w};
+        for (int gq = 0; gq < 2; ++gq)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float lo = __uint_as_float(words[i] << 16) * row_scale[j];
-            const float hi = __uint_as_float(words[i] & 0xffff0000u) * row_scale[j];
-            const __half2 h = __floats2half2_rn(lo, hi);
-            words[i] = *reinterpret_cast<const uint32_t*>(&h);
+          for (int hv = 0; hv < 2; ++hv) {
+            uint4& v = act[ch][gq][rh][hv];
+            uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float lo = __uint_as_float(words[i] << 16) * row_scale;
+              const float hi = __uint_as_float(words[i] & 0xffff0000u) * row_scale;
+              const __half2 h = __floats2half2_rn(lo, hi);
+              words[i] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            v = make_uint4(words[0], words[1], words[2], words[3]);
           }
-          act[j][ch][q] = make_uint4(words[0], words[1], words[2], words[3]);
-        }
     }
+    if (!kRows16 && warp == 0 && t == 0) inv_row_scale[8 + g] = 1.f;
 
     int stage = 0;
-    uint32_t phase = 0, red_phase = 0;
-    bool ok = true;
-    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
-      float acc[kMTiles][4];
-#pragma unroll
-      for (int j = 0; j < kMTiles; ++j)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
-
-      if (ok && !mbar_wait(full_bar + 8 * stage, phase, abort_flag)) {
-        if (lane == 0) {
-          report_status(status, kStatusW8Wait);
-          *abort_flag = 1;
-        }
-        ok = false;
+    uint32_t phase = 0;
+    const bool tracing = trace != nullptr && warp == 0 && lane == 0;
+    long long waited_full = 0, waited_red = 0;
+    if (tracing) stamp(3);  // activations in registers
+    const long long loop_start = tracing ? clock64() : 0;
+    for (int item = 0; item < num_items; ++item) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const long long t0 = tracing ? clock64() : 0;
+      if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag)) {
+        give_up();
+        break;
       }
-      if (!ok) break;
-      const uint32_t tile = smem_base + stage * stage_bytes;
+      if (tracing) {
+        waited_full += clock64() - t0;
+        if (item == 0) stamp(4);  // first stage landed
+      }
+      const uint32_t tile = smem_base + stage * stage_bytes + g * pitch + 16 * t;  // this lane's weight row g (and g + 8 when the weights are the m16 operand)
 #pragma unroll
       for (int ch = 0; ch < kChunks; ++ch) {
         const int k0 = (warp + G::kConsumerWarps * ch) * G::kChunkK;
         if (k0 < K) {
-          const uint32_t lo = tile + g * pitch + k0 + 16 * t;
-          const uint32_t hi = lo + 8 * pitch;
-          const uint4 wl[2] = {lds128(lo), lds128(lo + 64)};
-          const uint4 wh[2] = {lds128(hi), lds128(hi + 64)};
+          // One instruction per word of a 16-byte load: its four weights are the k pairs (2t, 2t+1) and (2t+8, 2t+9) of
+          // the fragment, and the activations of the same four k are taken for the other operand - any pairing of k
+          // works as long as both operands use it.
+          if constexpr (kRows16) {
+            const uint4 wv[2] = {lds128(tile + k0), lds128(tile + k0 + 64)};
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const uint32_t lw[4] = {wl[half].x, wl[half].y, wl[half].z, wl[half].w};
-            const uint32_t hw[4] = {wh[half].x, wh[half].y, wh[half].z, wh[half].w};
+            for (int gq = 0; gq < 2; ++gq) {
+              const uint32_t words[4] = {wv[gq].x, wv[gq].y, wv[gq].z, wv[gq].w};
 #pragma unroll
-            for (int s = 0; s < 4; ++s) {
-              uint32_t a0, a1, a2, a3;
-              dequant4_f16(lw[s], a0, a2);  // row g:   k+0,1 | k+2,3
-              dequant4_f16(hw[s], a1, a3);  // row g+8: k+0,1 | k+2,3
+              for (int j = 0; j < 4; ++j) {
+                uint32_t b0, b1;
+                dequant4_f16(words[j], b0, b1);
+                const uint4 x0 = act[ch][gq][0][j >> 1], x1 = act[ch][gq][kRowHalves - 1][j >> 1];
+                mma_f16_16816(acc, (j & 1) ? x0.z : x0.x, (j & 1) ? x1.z : x1.x, (j & 1) ? x0.w : x0.y, (j & 1) ? x1.w : x1.y, b0, b1);
+              }
+            }
+          } else {
+            const uint4 wl[2] = {lds128(tile + k0), lds128(tile + k0 + 64)};
+            const uint4 wh[2] = {lds128(tile + 8 * pitch + k0), lds128(tile + 8 * pitch + k0 + 64)};
 #pragma unroll
-              for (int j = 0; j < kMTiles; ++j) {
-                const uint4 x = act[j][ch][2 * half + (s >> 1)];
-                const uint32_t b0 = (s & 1) ? x.z : x.x;
-                const uint32_t b1 = (s & 1) ? x.w : x.y;
-                mma_f16_16816(acc[j], a0, a1, a2, a3, b0, b1);
+            for (int gq = 0; gq < 2; ++gq) {
+              const uint32_t lw[4] = {wl[gq].x, wl[gq].y, wl[gq].z, wl[gq].w};
+              const uint32_t hw[4] = {wh[gq].x, wh[gq].y, wh[gq].z, wh[gq].w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint32_t a0, a1, a2, a3;
+                dequant4_f16(lw[j], a0, a2);  // weight row g
+                dequant4_f16(hw[j], a1, a3);  // weight row g + 8
+                const uint4 x = act[ch][gq][0][j >> 1];  // activation row g: the n of the fragment
+                mma_f16_16816(acc, a0, a1, a2, a3, (j & 1) ? x.z : x.x, (j & 1) ? x.w : x.y);
               }
             }
           }
@@ -273,57 +407,33 @@ w8_stream_kernel(const __nv_bfloat16* __restrict__ a, long long lda, const int8_
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar + 8 * stage);
-      if (++stage == G::kStages) {
+      if (++stage == stages) {
         stage = 0;
         phase ^= 1u;
       }
-
-      // hand the 16 K-slices of this item to the summing warps
-      if (!mbar_wait(red_free_bar, red_phase ^ 1u, abort_flag)) {  // previous item's partials have been read
-        if (lane == 0) {
-          report_status(status, kStatusW8Wait);
-          *abort_flag = 1;
-        }
+      // leave the fragment for the summing warp and go on
+      const int rb = item % G::kRedStages;
+      const long long t1 = tracing ? clock64() : 0;
+      if (!mbar_wait(red_free_bar + 8 * rb, (static_cast<uint32_t>(item / G::kRedStages) & 1u) ^ 1u, abort_flag)) {
+        give_up();
         break;
       }
-#pragma unroll
-      for (int j = 0; j < kMTiles; ++j)
-        *reinterpret_cast<float4*>(&red[((warp * kMTiles + j) * 32 + lane) * 4]) = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+      if (tracing) waited_red += clock64() - t1;
+      const uint32_t red = smem_base + red_offset + rb * G::kRedBytes + (warp * 32 + lane) * 16;
+      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(red), "f"(acc[0]), "f"(acc[1]), "f"(acc[2]), "f"(acc[3]) : "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(red_full_bar);
-      if (warp < kSumWarps) {
-        if (!mbar_wait(red_full_bar, red_phase, abort_flag)) {
-          if (lane == 0) {
-            report_status(status, kStatusW8Wait);
-            *abort_flag = 1;
-          }
-          break;
-        }
-        const int tid = threadIdx.x;  // 0 .. 128*kMTiles-1
-        const int j = tid >> 7;
-        const int slot = tid & 127;  // = lane * 4 + e of the fragment
-        float sum = 0.f;
-#pragma unroll
-        for (int q = 0; q < G::kConsumerWarps; ++q) sum += red[(q * kMTiles + j) * 128 + slot];
-        __syncwarp();
-        if (lane == 0) mbar_arrive(red_free_bar);
-        const int fl = slot >> 2, e = slot & 3;
-        const int fg = fl >> 2, ft = fl & 3;
-        const int m = 8 * j + 2 * ft + (e & 1);
-        const int n = item * G::kRows + fg + ((e & 2) ? 8 : 0);
-        if (m < M && n < N) {
-          const float factor = scale != nullptr ? __ldg(scale + n) : 1.f;
-          // (the fused form's accumulator input joins the sum once the power of two of the row is divided out)
-          const float v = ep.active ? epilogue_float(sum * inv_row_scale[m], ep, m, n, factor) : sum * inv_row_scale[m] * factor;
-          if constexpr (sizeof(OutT) == 2) c[static_cast<long long>(m) * ldc + n] = __float2bfloat16_rn(v);
-          else c[static_cast<long long>(m) * ldc + n] = v;
-        }
-      }
-      red_phase ^= 1u;
+      if (lane == 0) mbar_arrive(red_full_bar + 8 * rb);
+    }
+    if (tracing) {
+      trace[blockIdx.x * 16 + 10] = static_cast<unsigned long long>(waited_full);
+      trace[blockIdx.x * 16 + 11] = static_cast<unsigned long long>(waited_red);
+      trace[blockIdx.x * 16 + 12] = static_cast<unsigned long long>(clock64() - loop_start);
+      stamp(5);
     }
   }
 
   __syncthreads();
+  if (threadIdx.x == 0) stamp(15);
   if (*abort_flag != 0) {
     // a wait ran out: let bulk copies still in flight land before shared memory is released
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
