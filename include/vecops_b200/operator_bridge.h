@@ -58,6 +58,14 @@ VECOPS_B200_EXPORT int32_t vecops_b200_operator_resolve(uint64_t handle, const V
 VECOPS_B200_EXPORT int32_t vecops_b200_operator_workspace(uint64_t handle, const VecopsCall* call, uint64_t* bytes,
                                                           VecopsError* error);
 
+/* How often vecops_operator_bridge_invoke_v1 took its two paths since the library was loaded (all threads): the full one -
+ * bind, validate, dispatch, resolve, then run - and the prepared one, which re-enters an executable a previous call with
+ * the same signature resolved (same operator, value kinds, tensor dtypes, devices, flags, ranks, sizes, strides and
+ * address alignment; data addresses and scalar payloads are free).  Each thread keeps its last eight signatures, as
+ * vecops' own framework bridge does (docs/Runtime.md:195-206).  VECOPS_B200_PREPARED_CALL=0 in the environment before the
+ * first call turns the prepared path off.  Either pointer may be NULL. */
+VECOPS_B200_EXPORT void vecops_b200_bridge_counters(uint64_t* slow_calls, uint64_t* prepared_calls);
+
 /* Descriptor template of one kernel variant (VecopsB200MatmulKernel id): what
  * a one-specialization artifact's vecops_kernel_query_v1 would return, with an
  * empty specialization key.  NULL for AUTO or an id out of range. */

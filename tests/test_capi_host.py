@@ -208,3 +208,85 @@ def test_abi_records_equal_the_reference_headers(tmp_path):
         outputs.append(subprocess.run([str(binary)], check=True, capture_output=True, text=True).stdout.splitlines())
     assert len(outputs[0]) > 100
     assert outputs[0] == outputs[1]
+
+
+def _frame(shapes_dtypes, base_address):
+    """A VecopsCall over fake CUDA tensors (binding and validation never touch the storage): [(shape, dtype code, writable)]."""
+    keep, values = [], []
+    for index, (shape, dtype, writable) in enumerate(shapes_dtypes):
+        sizes = (ctypes.c_int64 * len(shape))(*shape)
+        contiguous = [1] * len(shape)
+        for d in range(len(shape) - 2, -1, -1):
+            contiguous[d] = contiguous[d + 1] * shape[d + 1]
+        strides = (ctypes.c_int64 * len(shape))(*contiguous)
+        keep += [sizes, strides]
+        v = capi.VecopsValue()
+        v.struct_size = ctypes.sizeof(capi.VecopsValue)
+        v.kind = capi.VALUE_TENSOR
+        t = v.value.tensor
+        t.struct_size = ctypes.sizeof(capi.VecopsTensorView)
+        t.data, t.byte_offset = base_address + (index << 24), 0
+        t.device_type, t.device_index = capi.DEVICE_CUDA, 0
+        t.dtype, t.rank, t.sizes, t.strides = dtype, len(shape), sizes, strides
+        t.flags = capi.TENSOR_READ | (capi.TENSOR_WRITE if writable else 0)
+        values.append(v)
+    array = (capi.VecopsValue * len(values))(*values)
+    frame = capi.VecopsCall(ctypes.sizeof(capi.VecopsCall), len(values), array, None, 0, None)
+    keep.append(array)
+    return frame, keep
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="counts bridge paths on a host where every run ends in 'no device'")
+def test_bridge_re_enters_a_prepared_call_on_an_identical_signature(library):
+    """vecops' framework bridge keeps eight call signatures per thread and re-enters a resolved executable on a match
+    (docs/Runtime.md:195-206); so does this bridge.  Without a GPU every call gets as far as the artifact's run callback
+    and fails there - after binding, validation and resolution, which is all this test is about."""
+    library.vecops_b200_matmul_operator.restype = ctypes.c_uint64
+    library.vecops_operator_bridge_invoke_v1.argtypes = [ctypes.c_uint64, ctypes.POINTER(capi.VecopsCall), ctypes.c_uint32, ctypes.c_void_p,
+                                                         ctypes.POINTER(capi.VecopsError)]
+    library.vecops_b200_bridge_counters.argtypes = [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]
+    library.vecops_b200_bridge_counters.restype = None
+    handle = library.vecops_b200_matmul_operator()
+
+    def counters():
+        slow, prepared = ctypes.c_uint64(0), ctypes.c_uint64(0)
+        library.vecops_b200_bridge_counters(byref(slow), byref(prepared))
+        return slow.value, prepared.value
+
+    def invoke(frame):
+        error = capi.ErrorBuffer()
+        return library.vecops_operator_bridge_invoke_v1(handle, byref(frame), 0, None, byref(error.record)), error.text.value
+
+    decode = [((16, 4096), capi.DTYPE_BF16, False), ((14336, 4096), capi.DTYPE_I8, False), ((16, 14336), capi.DTYPE_BF16, True),
+              ((14336,), capi.DTYPE_F32, False)]
+    frame, keep = _frame(decode, 0x7f0000000000)
+    slow0, prepared0 = counters()
+    rc, text = invoke(frame)
+    assert rc == capi.EXECUTION_ERROR and b"no CPU fallback" in text
+    assert counters() == (slow0 + 1, prepared0)
+    # the same signature at other addresses: no bind, no validation, no dispatch - straight to the executable
+    other, keep2 = _frame(decode, 0x7e0000000000)
+    for step in range(3):
+        rc, text = invoke(other if step % 2 else frame)
+        assert rc == capi.EXECUTION_ERROR and b"no CPU fallback" in text
+    assert counters() == (slow0 + 1, prepared0 + 3)
+    # another M is another signature (sizes are part of it), and so is an operand that is no longer 16-byte aligned
+    longer, keep3 = _frame([((17, 4096), capi.DTYPE_BF16, False), decode[1], ((17, 14336), capi.DTYPE_BF16, True), decode[3]], 0x7f0000000000)
+    invoke(longer)
+    assert counters() == (slow0 + 2, prepared0 + 3)
+    shifted, keep4 = _frame(decode, 0x7f0000000008)
+    invoke(shifted)
+    assert counters() == (slow0 + 3, prepared0 + 3)
+    # a call the slow path refuses is not remembered: it is refused again, in words, by the slow path
+    bad, keep5 = _frame([((16, 4096), capi.DTYPE_BF16, False), ((14336, 4000), capi.DTYPE_I8, False), ((16, 14336), capi.DTYPE_BF16, True)], 0x7f0000000000)
+    for _ in range(2):
+        rc, text = invoke(bad)
+        assert rc != capi.OK and rc != capi.EXECUTION_ERROR
+    assert counters() == (slow0 + 5, prepared0 + 3)
+    # nine signatures push the first out of the thread's eight slots
+    for m in range(1, 9):
+        extra, _keep = _frame([((m, 256), capi.DTYPE_F32, False), ((64, 256), capi.DTYPE_F32, False), ((m, 64), capi.DTYPE_F32, True)], 0x7f0000000000)
+        invoke(extra)
+    slow1, prepared1 = counters()
+    invoke(frame)
+    assert counters() == (slow1 + 1, prepared1)

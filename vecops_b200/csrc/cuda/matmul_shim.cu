@@ -687,14 +687,18 @@ int32_t launch_w8_stream_typed(const VecopsB200Matmul& p, const DeviceState& dev
   using G = W8Stream;
   auto kernel = w8_stream_kernel<kChunks, kRows16, OutT>;
   const int smem = G::smem_bytes(static_cast<int>(p.k), kRows16);
-  // the attribute is per kernel instantiation and per device; setting it is cheap and idempotent
-  int32_t rc = raise_smem_limit(kernel, smem, error);
-  if (rc != VECOPS_STATUS_OK) return rc;
+  int device = 0;
+  cudaGetDevice(&device);
+  // the attribute is per kernel instantiation and per device: raised once to the most any K needs
+  static std::atomic<bool> raised[kMaxDevices];
+  if (device < 0 || device >= kMaxDevices || !raised[device].load()) {
+    const int32_t rc = raise_smem_limit(kernel, 227 * 1024, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+    if (device >= 0 && device < kMaxDevices) raised[device].store(true);
+  }
   // one CTA per SM, each with an equal share of W's rows (to within one row); fewer when there are not 8 rows for each
   const long long items = (p.n + G::rows(kRows16) - 1) / G::rows(kRows16);
   const int grid = static_cast<int>(items < dev.prop.multiProcessorCount ? items : dev.prop.multiProcessorCount);
-  int device = 0;
-  cudaGetDevice(&device);
   cudaLaunchConfig_t config = {};
   cudaLaunchAttribute attributes[1] = {};
   config.gridDim = dim3(grid);

@@ -3,6 +3,9 @@
 #include "vecops_b200/runtime/matmul_operator.h"
 
 #include <array>
+#include <atomic>
+#include <cstdlib>
+#include <string>
 #include <cstddef>
 #include <cstring>
 
@@ -729,6 +732,103 @@ std::int32_t call_from_frame(const VecopsCall* call, std::uint32_t nspec, const 
 
 }  // namespace
 
+// ---------------------------------------------------------------- prepared calls
+//
+// vecops' framework bridge keeps up to eight exact call signatures per thread: once a slow invocation has resolved and
+// validated an Executable, a call with the same signature re-enters it directly through Executable::invoke_prevalidated
+// (docs/Runtime.md:195-206).  The same here, one level down, for every caller of the C bridge.  A signature holds what
+// binding, validation, dispatch and the workspace query depend on - the operator handle, each value's kind, and for
+// tensors dtype, device, access flags, rank, every size and every stride - and leaves out what they do not: data
+// addresses and scalar payloads.  A hit skips bind_kernel_call, schema and descriptor validation, the dispatch policy,
+// the recipes and the provider; what is left is the workspace-size comparison vecops' Executable::invoke makes and the
+// artifact's run callback on the caller's own frame (the callbacks of this library read frames of 3 to 10 values
+// as they come: problem_from_frame fills in the defaults itself).
+namespace {
+
+constexpr std::size_t kSignatureWords = 96;  // ten values of rank <= 3 fit with room to spare; anything longer takes the slow path
+constexpr int kPreparedPerThread = 8;
+
+struct CallSignature {
+  std::array<std::uint64_t, kSignatureWords> words{};
+  std::size_t count = 0;
+  std::uint64_t hash = 0;
+  bool usable = false;
+};
+
+CallSignature signature_of(std::uint64_t handle, const VecopsCall* call, std::uint32_t num_specialization_values) {
+  CallSignature s;
+  if (call == nullptr || call->struct_size < sizeof(VecopsCall) || num_specialization_values != 0 ||
+      (call->num_values != 0 && call->values == nullptr))
+    return s;  // explicit specialization values, or a frame the slow path has to refuse in words
+  auto push = [&s](std::uint64_t word) {
+    if (s.count < kSignatureWords) s.words[s.count] = word;
+    ++s.count;
+  };
+  push(handle);
+  push(call->num_values);
+  for (std::uint32_t i = 0; i < call->num_values; ++i) {
+    const VecopsValue& v = call->values[i];
+    push(v.kind);
+    if (v.kind == VECOPS_VALUE_TENSOR) {
+      const VecopsTensorView& t = v.value.tensor;
+      if (t.rank > 8 || (t.rank != 0 && (t.sizes == nullptr || t.strides == nullptr))) return s;
+      push((static_cast<std::uint64_t>(t.dtype) << 32) | t.rank);
+      push((static_cast<std::uint64_t>(t.device_type) << 32) | static_cast<std::uint32_t>(t.device_index));
+      push(t.flags);
+      // the address and its byte offset are left out, but not how the address is aligned: the dispatch rules send
+      // 16-byte aligned operands to the TMA-fed kernels and others to the strided one
+      push((reinterpret_cast<std::uintptr_t>(t.data) + t.byte_offset) & 15u);
+      for (std::uint32_t d = 0; d < t.rank; ++d) {
+        push(static_cast<std::uint64_t>(t.sizes[d]));
+        push(static_cast<std::uint64_t>(t.strides[d]));
+      }
+    } else if (v.kind == VECOPS_VALUE_SCALAR) {
+      push(v.value.scalar.dtype);
+    }
+  }
+  if (s.count > kSignatureWords) return s;
+  std::uint64_t h = 0xcbf29ce484222325ULL;
+  for (std::size_t i = 0; i < s.count; ++i) h = (h ^ s.words[i]) * 0x100000001b3ULL;
+  s.hash = h;
+  s.usable = true;
+  return s;
+}
+
+struct PreparedCall {
+  CallSignature signature;
+  std::shared_ptr<Executable> executable;
+  std::uint64_t workspace_bytes = 0;
+};
+
+struct PreparedCalls {
+  std::array<PreparedCall, kPreparedPerThread> entries;
+  int next = 0;
+  const PreparedCall* find(const CallSignature& s) const {
+    for (const auto& e : entries)
+      if (e.executable != nullptr && e.signature.hash == s.hash && e.signature.count == s.count &&
+          std::memcmp(e.signature.words.data(), s.words.data(), s.count * sizeof(std::uint64_t)) == 0)
+        return &e;
+    return nullptr;
+  }
+  void remember(const CallSignature& s, std::shared_ptr<Executable> executable, std::uint64_t bytes) {
+    entries[next] = PreparedCall{s, std::move(executable), bytes};
+    next = (next + 1) % kPreparedPerThread;
+  }
+};
+
+thread_local PreparedCalls tl_prepared;
+std::atomic<std::uint64_t> g_bridge_slow{0}, g_bridge_prepared{0};
+
+bool prepared_calls_enabled() {
+  static const bool enabled = [] {
+    const char* v = std::getenv("VECOPS_B200_PREPARED_CALL");  // "0" before the first call turns the hot path off, for diagnostics
+    return !(v != nullptr && v[0] == '0');
+  }();
+  return enabled;
+}
+
+}  // namespace
+
 extern "C" {
 
 uint64_t vecops_b200_matmul_operator(void) {
@@ -745,10 +845,44 @@ int32_t vecops_operator_bridge_invoke_v1(uint64_t handle, const VecopsCall* call
                                          const VecopsSpecializationArgument* specialization_values, VecopsError* error) {
   const Operator* op = operator_of(handle);
   if (op == nullptr) return fail(error, VECOPS_STATUS_NOT_FOUND, "unknown operator handle");
+  const CallSignature signature = prepared_calls_enabled() ? signature_of(handle, call, num_specialization_values) : CallSignature{};
+  if (signature.usable) {
+    if (const PreparedCall* prepared = tl_prepared.find(signature)) {
+      // the one check of Executable::invoke that depends on what the signature leaves out (Executable.cpp:288-295)
+      if (prepared->workspace_bytes > call->workspace_size || (prepared->workspace_bytes != 0 && call->workspace == nullptr)) {
+        const std::string text = "kernel requires " + std::to_string(prepared->workspace_bytes) + " workspace bytes, but " +
+                                 std::to_string(call->workspace_size) + " were supplied";
+        return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, text.c_str());
+      }
+      g_bridge_prepared.fetch_add(1, std::memory_order_relaxed);
+      const Status status = prepared->executable->invoke_prevalidated(*call);
+      return status.ok() ? VECOPS_STATUS_OK : report(error, status);
+    }
+  }
+  g_bridge_slow.fetch_add(1, std::memory_order_relaxed);
   KernelCall kernel_call;
   if (const auto rc = call_from_frame(call, num_specialization_values, specialization_values, &kernel_call, error); rc != VECOPS_STATUS_OK) return rc;
   const Status status = op->invoke(kernel_call, call->context, call->workspace, call->workspace_size);
+  // Binding, validation and resolution have passed when the call succeeded or failed only inside the artifact's run
+  // (a device error, no device at all): the signature is worth remembering either way.
+  if (signature.usable && (status.ok() || status.code() == StatusCode::ExecutionError)) {
+    if (auto executable = op->resolve(kernel_call, call->context)) {
+      std::uint64_t bytes = 0;
+      bool sized = true;
+      if (const auto query = executable.value()->module()->descriptor().workspace) {
+        std::array<char, 256> text{};
+        VecopsError scratch{sizeof(VecopsError), 0, text.data(), text.size(), 0};
+        sized = query(call, &bytes, &scratch) == VECOPS_STATUS_OK;
+      }
+      if (sized) tl_prepared.remember(signature, std::move(executable).value(), bytes);
+    }
+  }
   return status.ok() ? VECOPS_STATUS_OK : report(error, status);
+}
+
+void vecops_b200_bridge_counters(uint64_t* slow_calls, uint64_t* prepared_calls) {
+  if (slow_calls != nullptr) *slow_calls = g_bridge_slow.load(std::memory_order_relaxed);
+  if (prepared_calls != nullptr) *prepared_calls = g_bridge_prepared.load(std::memory_order_relaxed);
 }
 
 int32_t vecops_b200_operator_resolve(uint64_t handle, const VecopsCall* call, char* key, size_t capacity, VecopsError* error) {
