@@ -291,10 +291,14 @@ def measure_single(name: str, steps: int, warmup: int, dev, port, peaks, peak_so
         e2e_steps = 20 if w.kind != "w8" else 200
         e2e = measure_e2e(w, operands, host_inputs, e2e_steps, 3, dev, resident_weights=w.kind == "w8")
         work = per_set / 1e9 if roofline["bound"] == "hbm" else w.flops / 1e12
-        record["e2e"] = {"value": work / (e2e["ms_per_step"] * 1e-3), "unit": roofline["unit"], "ms_per_step": e2e["ms_per_step"],
+        # steps of a few tens of microseconds gain nothing from three streams and their event traffic: the faster of the two ways counts
+        best_ms = min(e2e["ms_per_step"], e2e["serial_ms_per_step"])
+        record["e2e"] = {"value": work / (best_ms * 1e-3), "unit": roofline["unit"], "ms_per_step": best_ms,
+                         "pipelined_ms_per_step": e2e["ms_per_step"],
                          "serial_ms_per_step": e2e["serial_ms_per_step"], "serial_value": work / (e2e["serial_ms_per_step"] * 1e-3),
                          "h2d_bytes_per_step": e2e["h2d_bytes_per_step"], "d2h_bytes_per_step": e2e["d2h_bytes_per_step"], "steps": e2e_steps,
                          "resident": e2e["resident"], "host_overhead_us_per_call": e2e["host_us_per_call"],
+                         "bridge_calls": e2e["bridge_calls"],
                          "path": "vecops_operator_bridge_invoke_v1, pinned host buffers, copies inside the timed region"}
     except Exception as error:  # noqa: BLE001 - a failed side measurement must not lose the kernel number
         record["e2e"] = {"error": repr(error)}
@@ -719,7 +723,11 @@ def measure_e2e(w, operands, host_inputs, steps: int, warmup: int, dev, resident
     last = lanes[(warmup + steps - 1) % n_lanes]
     if not torch.equal(last["host_c"], last["o"]["c"].cpu()):
         raise RuntimeError("end-to-end read-back differs from the device result")
+    slow, prepared = ctypes.c_uint64(0), ctypes.c_uint64(0)
+    from vecops_b200 import capi
+    capi.library().vecops_b200_bridge_counters(byref(slow), byref(prepared))
     return {"ms_per_step": pipelined_ms, "serial_ms_per_step": serial_ms, "h2d_bytes_per_step": int(a_bytes + b_bytes),
+            "bridge_calls": {"full_path": slow.value, "prepared_path": prepared.value, "note": "process totals: the full path (bind, validate, dispatch, resolve) runs once per call signature, the prepared path re-enters the resolved executable"},
             "d2h_bytes_per_step": int(c_bytes), "host_us_per_call": host_us,
             "resident": "weights and scales stay on the device; a step copies the activations in and the result out" if resident_weights else "nothing: every operand is copied in every step",
             "copies": "cudaMemcpyAsync from / to pinned host memory" + ("" if copy is not None else " (through torch)")}
