@@ -26,7 +26,7 @@
 #include <string>
 
 #include "vecops_b200/matmul_cuda.h"
-#include "vecops_b200/runtime/operator.h"
+#include "vecops_b200/runtime_mirror/operator.h"
 
 namespace vecops::runtime {
 

@@ -1,3 +1,8 @@
+// RESTATED FROM vecops (include/vecops/runtime/Executable.h:54-168), not designed here.  Inside a vecops build this file is not used at all: vecops' own
+// runtime takes its place and only the matmul recipe, dispatch policy and executable provider of this library are new
+// (csrc/runtime/matmul_operator.cpp).  It exists so that the library builds and is testable standalone, with the
+// class names, signatures, checks and status texts a caller of vecops' runtime expects.
+//
 // Executable: one loaded kernel specialization, reached only through its
 // VecopsKernelDescriptorV1.  Mirrors include/vecops/runtime/Executable.h:36-168
 // and src/runtime/Executable.cpp:39-316 (descriptor validation, call
@@ -15,8 +20,8 @@
 #include <string_view>
 
 #include "vecops_b200/kernel_abi.h"
-#include "vecops_b200/runtime/status.h"
-#include "vecops_b200/runtime/values.h"
+#include "vecops_b200/runtime_mirror/status.h"
+#include "vecops_b200/runtime_mirror/values.h"
 
 namespace vecops::runtime {
 

@@ -1,3 +1,8 @@
+// RESTATED FROM vecops (include/vecops/runtime/KernelDefinition.h), not designed here.  Inside a vecops build this file is not used at all: vecops' own
+// runtime takes its place and only the matmul recipe, dispatch policy and executable provider of this library are new
+// (csrc/runtime/matmul_operator.cpp).  It exists so that the library builds and is testable standalone, with the
+// class names, signatures, checks and status texts a caller of vecops' runtime expects.
+//
 // KernelDef / KernelCall / bind_kernel_call: the declarative signature of a
 // kernel, a concrete call, and the binding that checks one against the other
 // and derives the specialization key.
@@ -24,8 +29,8 @@
 #include <variant>
 #include <vector>
 
-#include "vecops_b200/runtime/status.h"
-#include "vecops_b200/runtime/values.h"
+#include "vecops_b200/runtime_mirror/status.h"
+#include "vecops_b200/runtime_mirror/values.h"
 
 namespace vecops::runtime {
 

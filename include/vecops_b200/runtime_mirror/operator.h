@@ -1,3 +1,8 @@
+// RESTATED FROM vecops (include/vecops/runtime/Operator.h:34-293), not designed here.  Inside a vecops build this file is not used at all: vecops' own
+// runtime takes its place and only the matmul recipe, dispatch policy and executable provider of this library are new
+// (csrc/runtime/matmul_operator.cpp).  It exists so that the library builds and is testable standalone, with the
+// class names, signatures, checks and status texts a caller of vecops' runtime expects.
+//
 // Operator = schema + ordered kernel recipes + dispatch policy + executable
 // provider.  Mirrors include/vecops/runtime/Operator.h:34-293 and
 // src/runtime/Operator.cpp:162-285.
@@ -18,9 +23,9 @@
 #include <string_view>
 #include <vector>
 
-#include "vecops_b200/runtime/executable.h"
-#include "vecops_b200/runtime/kernel_def.h"
-#include "vecops_b200/runtime/schema.h"
+#include "vecops_b200/runtime_mirror/executable.h"
+#include "vecops_b200/runtime_mirror/kernel_def.h"
+#include "vecops_b200/runtime_mirror/schema.h"
 
 namespace vecops::runtime {
 

@@ -1,3 +1,8 @@
+// RESTATED FROM vecops (include/vecops/runtime/Schema.h:35-187), not designed here.  Inside a vecops build this file is not used at all: vecops' own
+// runtime takes its place and only the matmul recipe, dispatch policy and executable provider of this library are new
+// (csrc/runtime/matmul_operator.cpp).  It exists so that the library builds and is testable standalone, with the
+// class names, signatures, checks and status texts a caller of vecops' runtime expects.
+//
 // OperatorSchema: the framework-neutral signature an Operator validates every
 // call against before any recipe sees it.  Mirrors
 // include/vecops/runtime/Schema.h:35-187 and src/runtime/Schema.cpp:26-147.
@@ -12,8 +17,8 @@
 #include <variant>
 #include <vector>
 
-#include "vecops_b200/runtime/status.h"
-#include "vecops_b200/runtime/values.h"
+#include "vecops_b200/runtime_mirror/status.h"
+#include "vecops_b200/runtime_mirror/values.h"
 
 namespace vecops::runtime {
 

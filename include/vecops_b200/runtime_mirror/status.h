@@ -1,3 +1,8 @@
+// RESTATED FROM vecops (include/vecops/runtime/Status.h:49-179), not designed here.  Inside a vecops build this file is not used at all: vecops' own
+// runtime takes its place and only the matmul recipe, dispatch policy and executable provider of this library are new
+// (csrc/runtime/matmul_operator.cpp).  It exists so that the library builds and is testable standalone, with the
+// class names, signatures, checks and status texts a caller of vecops' runtime expects.
+//
 // Status and Result<T>: error transport of the operator runtime.  No exception
 // crosses a runtime call; callers branch on code().
 //

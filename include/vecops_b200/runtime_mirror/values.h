@@ -1,3 +1,8 @@
+// RESTATED FROM vecops (include/vecops/runtime/Argument.h:226-370), not designed here.  Inside a vecops build this file is not used at all: vecops' own
+// runtime takes its place and only the matmul recipe, dispatch policy and executable provider of this library are new
+// (csrc/runtime/matmul_operator.cpp).  It exists so that the library builds and is testable standalone, with the
+// class names, signatures, checks and status texts a caller of vecops' runtime expects.
+//
 // Erased call values: tensors as metadata + address, scalars in the ABI's
 // widest lane.  Mirrors include/vecops/runtime/Argument.h:46-475.
 //

@@ -32,7 +32,9 @@ def _nvcc() -> str:
 
 def _sources() -> tuple[list[Path], list[Path], list[Path]]:
     cuda = sorted((CSRC / "cuda").glob("*.cu"))
-    host = sorted((CSRC / "runtime").glob("*.cpp"))
+    # runtime/: the matmul operator, recipes, dispatch policy, provider and C bridge of this library;
+    # runtime_mirror/: vecops' runtime classes restated so that the library stands alone (unused inside a vecops build)
+    host = sorted((CSRC / "runtime").glob("*.cpp")) + sorted((CSRC / "runtime_mirror").glob("*.cpp"))
     # this file counts as an input: a change of flags rebuilds everything
     headers = sorted(CSRC.rglob("*.h")) + sorted(CSRC.rglob("*.cuh")) + sorted(INCLUDE.rglob("*.h")) + [Path(__file__)]
     return cuda, host, headers

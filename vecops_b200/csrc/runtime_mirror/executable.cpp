@@ -1,8 +1,13 @@
+// RESTATED FROM vecops (src/runtime/Executable.cpp:39-316), not designed here.  Inside a vecops build this file is not used at all: vecops' own
+// runtime takes its place and only the matmul recipe, dispatch policy and executable provider of this library are new
+// (csrc/runtime/matmul_operator.cpp).  It exists so that the library builds and is testable standalone, with the
+// class names, signatures, checks and status texts a caller of vecops' runtime expects.
+//
 // LoadedModule / Executable.  Behaviour follows src/runtime/Executable.cpp of
 // vecops: descriptor validation :39-100, per-call validation against the
 // descriptor :102-184, error text recovery :186-197, dlopen loader :208-239,
 // workspace query :260-284, guarded invoke :286-316.
-#include "vecops_b200/runtime/executable.h"
+#include "vecops_b200/runtime_mirror/executable.h"
 
 #include <dlfcn.h>
 

@@ -1,8 +1,13 @@
+// RESTATED FROM vecops (src/runtime/KernelDefinition.cpp:59-534), not designed here.  Inside a vecops build this file is not used at all: vecops' own
+// runtime takes its place and only the matmul recipe, dispatch policy and executable provider of this library are new
+// (csrc/runtime/matmul_operator.cpp).  It exists so that the library builds and is testable standalone, with the
+// class names, signatures, checks and status texts a caller of vecops' runtime expects.
+//
 // Binding of a KernelCall against a KernelDef.  Behaviour follows
 // src/runtime/KernelDefinition.cpp:59-534 of vecops (dtype spelling :59-91,
 // symbol inference :96-118, dimension checks :142-186, definition checks
 // :224-330, canonical text :332-396, two-phase bind and key :398-534).
-#include "vecops_b200/runtime/kernel_def.h"
+#include "vecops_b200/runtime_mirror/kernel_def.h"
 
 #include <bit>
 #include <cctype>

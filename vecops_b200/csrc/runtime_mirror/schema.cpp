@@ -1,6 +1,11 @@
+// RESTATED FROM vecops (src/runtime/Schema.cpp:55-147 and src/runtime/Argument.cpp:37-79), not designed here.  Inside a vecops build this file is not used at all: vecops' own
+// runtime takes its place and only the matmul recipe, dispatch policy and executable provider of this library are new
+// (csrc/runtime/matmul_operator.cpp).  It exists so that the library builds and is testable standalone, with the
+// class names, signatures, checks and status texts a caller of vecops' runtime expects.
+//
 // OperatorSchema validation and the ABI call frame.  Behaviour follows
 // src/runtime/Schema.cpp:55-147 and src/runtime/Argument.cpp:37-79 of vecops.
-#include "vecops_b200/runtime/schema.h"
+#include "vecops_b200/runtime_mirror/schema.h"
 
 #include <limits>
 
