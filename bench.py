@@ -33,7 +33,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 METRIC = "GEMM TFLOP/s (BF16/INT8) & GB/s (decode) at 1/2/4/8 B200, % of roofline"
-NOMINAL = {"bf16_tflops": 2250.0, "i8_tops": 4500.0, "hbm_gbs": 8000.0, "fp32_tflops": 74.4}  # fp32: 148 SMs x 128 FMA lanes x 2 x 1.965 GHz
+NOMINAL = {"bf16_tflops": 2250.0, "i8_tops": 4500.0, "hbm_gbs": 8000.0, "fp32_tflops": 74.4, "tf32_tflops": 1125.0}  # fp32: 148 SMs x 128 FMA lanes x 2 x 1.965 GHz
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, read from one ncu capture of that
 # workload, with the committed summary the figure was taken from.  A workload without a capture reports null.
@@ -206,8 +206,13 @@ def parity_sample(w, host_inputs, c, port, rows: int = 16) -> dict:
     return {"rows": len(pick), "rel_fro": rel_frobenius(got, bf16_bits_to_f32(want))}
 
 
-def bound_of(w, peaks, peak_source: str, kernel_ms: float) -> tuple[str, float, float, str, str]:
+def bound_of(w, peaks, peak_source: str, kernel_ms: float, kernel: str = "") -> tuple[str, float, float, str, str]:
     """(bound, peak, nominal peak, unit, where the peak comes from) of the roofline that limits workload `w`."""
+    if w.kind == "f32" and kernel == "f32_tf32x3":
+        # three tf32 products per fp32 product: the ceiling for ALGORITHMIC fp32 flops is a third of the tf32 tensor rate
+        third = NOMINAL["tf32_tflops"] / 3.0
+        return "tensor", third, third, "TFLOP/s", ("NOMINAL dense tf32 rate / 3 (three tf32 products per fp32 product; no tf32 peak is measured on this pool); "
+                                                   f"the FP32 FMA pipe's nominal rate is {NOMINAL['fp32_tflops']} TFLOP/s")
     burst = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
     sustained = float(peaks.get("bf16_tflops_sustained", burst))
     tensor, which = (burst, "burst") if kernel_ms < BURST_BELOW_MS else (sustained, "sustained")
@@ -222,7 +227,7 @@ def bound_of(w, peaks, peak_source: str, kernel_ms: float) -> tuple[str, float, 
 
 def roofline_record(w, name: str, kernel: str, kernel_ms: float, flops: float, algorithmic_bytes: float, peaks, peak_source: str) -> dict:
     """The roofline object of one kernel launch: achieved = algorithmic work per launch / measured launch time."""
-    bound, peak, nominal, unit, source = bound_of(w, peaks, peak_source, kernel_ms)
+    bound, peak, nominal, unit, source = bound_of(w, peaks, peak_source, kernel_ms, kernel)
     seconds = kernel_ms * 1e-3
     achieved = algorithmic_bytes / seconds / 1e9 if bound == "hbm" else flops / seconds / 1e12
     traffic, traffic_from = NCU_TRAFFIC.get(name, (None, None))

@@ -16,7 +16,9 @@
  * kernel/amx/Atoms.h:51-86):
  *
  *     A      B      C      scale   accumulate   vecops atom
- *     f32    f32    f32    -       f32          (AVX-512 fmadd leaf, amx/Backend.h:767-901)
+ *     f32    f32    f32    -       f32          (AVX-512 fmadd leaf, amx/Backend.h:767-901): fp32 FMAs on the CUDA cores, or -
+ *                                               when the caller brings the scratch the query reports - three tf32 products
+ *                                               of split operands on the tensor cores
  *     bf16   bf16   bf16   opt.    f32          AMX_BF16F32 with output<float>(bf16 C)
  *     bf16   bf16   f32    opt.    f32          AMX_BF16F32
  *     f16    f16    f16|f32 opt.   f32          AMX_F16F32 (Atoms.h:74-77), fp16 C through output<float>(fp16 C); same
@@ -56,8 +58,10 @@ typedef enum VecopsB200MatmulKernel {
   VECOPS_B200_KERNEL_BF16_TCGEN05 = 3, /* tcgen05 kind::f16 (bf16 or fp16 operand pairs), TMEM f32 accumulators, TMA pipeline */
   VECOPS_B200_KERNEL_I8_TCGEN05 = 4,   /* tcgen05 kind::i8, TMEM i32 accumulators, TMA pipeline */
   VECOPS_B200_KERNEL_W8_SMALL_M = 5,   /* weight-only int8, M <= 32: 128-bit loads, in-register dequant, split-K */
-  VECOPS_B200_KERNEL_W8_TCGEN05 = 6,   /* weight-only int8, M <= 128: weights widened into tensor memory, tcgen05 with W as the M operand */
-  VECOPS_B200_KERNEL_COUNT_ = 7
+  VECOPS_B200_KERNEL_W8_TCGEN05 = 6,   /* weight-only int8 on tcgen05: weights widened to bf16 on the way into the dense GEMM's MMAs */
+  VECOPS_B200_KERNEL_F32_TF32X3 = 7,   /* FP32 on tcgen05 kind::tf32: both operands split into two tf32 terms, three products summed in fp32
+                                          (about 2^-21 relative per product, inside the 1e-5 bar); needs the scratch its query reports */
+  VECOPS_B200_KERNEL_COUNT_ = 8
 } VecopsB200MatmulKernel;
 
 #define VECOPS_B200_MATMUL_FLAG_ASYNC (1u << 0) /* enqueue only; caller synchronises the stream */

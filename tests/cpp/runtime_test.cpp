@@ -257,7 +257,9 @@ void test_matmul_operator() {
     require(!refused.ok() && refused.code() == StatusCode::InvalidArgument, "invoke without the scratch is refused before run");
   }
   require(resolve_key(matmul_call(DType::Float32, DType::Float32, DType::Float32, 1024, 1024, 1024)) ==
-              "vecops::matmul;TA=f32;TB=f32;TC=f32;$0=0;$1=0;$2=0;kernel=f32_simt", "C1 resolves to the FP32 kernel");
+              "vecops::matmul;TA=f32;TB=f32;TC=f32;$0=0;$1=0;$2=0;kernel=f32_tf32x3", "C1 resolves to the split-operand tensor-core kernel");
+  require(resolve_key(matmul_call(DType::Float32, DType::Float32, DType::Float32, 128, 1024, 1024)) ==
+              "vecops::matmul;TA=f32;TB=f32;TC=f32;$0=0;$1=0;$2=0;kernel=f32_simt", "a small fp32 product resolves to the FMA kernel");
   require(resolve_key(matmul_call(DType::BFloat16, DType::BFloat16, DType::Float32, 16, 16, 35)) ==
               "vecops::matmul;TA=bf16;TB=bf16;TC=f32;$0=0;$1=0;$2=0;kernel=generic", "an unaligned K falls to the strided kernel");
 

@@ -61,7 +61,11 @@ def test_dispatch_rules_pick_the_tensor_core_kernels_for_the_benchmark_shapes(li
     for m in (1, 16):
         assert _name(vecops_b200.select_kernel(_problem(m, 14336, 4096, torch.bfloat16, torch.int8, torch.bfloat16))) == "w8_small_m"
     assert _name(vecops_b200.select_kernel(_problem(128, 14336, 4096, torch.bfloat16, torch.int8, torch.bfloat16))) == "w8_tcgen05"
-    assert _name(vecops_b200.select_kernel(_problem(1024, 1024, 1024, torch.float32, torch.float32, torch.float32))) == "f32_simt"
+    # fp32: the split-operand tensor-core route is what the rules prefer for a product this size (a launch takes it when the
+    # caller brings its scratch, the FMA kernel otherwise); small products stay on the FMA kernel
+    assert _name(vecops_b200.select_kernel(_problem(1024, 1024, 1024, torch.float32, torch.float32, torch.float32))) == "f32_tf32x3"
+    assert _name(vecops_b200.select_kernel(_problem(128, 1024, 1024, torch.float32, torch.float32, torch.float32))) == "f32_simt"
+    assert harness.workspace_bytes(_problem(1024, 1024, 1024, torch.float32, torch.float32, torch.float32)) >= 2 * 1024 * 3 * 1024 * 4
 
 
 def test_dispatch_rules_route_ragged_and_tiny_problems_to_the_strided_kernel(library):

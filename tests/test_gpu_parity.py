@@ -217,6 +217,40 @@ def test_f32_simt(port, m, n, k, b_kn):
     check("f32", run_case("f32", a, b, kernel=K.KERNEL_F32_SIMT, b_kn=b_kn), port.matmul_f32(a, b))
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (1024, 1024, 1024), (300, 520, 77), (129, 257, 1000), (64, 2048, 4096)])
+@pytest.mark.parametrize("b_kn", [True, False])
+def test_f32_tf32x3(port, m, n, k, b_kn):
+    # fp32 as three tf32 products of split operands on the tensor cores: inside the fp32 bar of 1e-5 (2e-6 to 4e-6 in fact),
+    # any K (zero-padded to k-blocks by the split), either storage of B
+    rng = np.random.default_rng(m + 2 * n + 3 * k)
+    a, b, _ = inputs("f32", m, n, k, rng)
+    got = run_case("f32", a, b, kernel=K.KERNEL_F32_TF32X3, b_kn=b_kn)
+    want = port.matmul_f32(a, b)
+    assert rel_frobenius(got, want) <= TOL_F32, f"m={m} n={n} k={k}"
+
+
+def test_f32_tf32x3_keeps_small_values_and_large_ranges(port):
+    # rows spanning many orders of magnitude: the split is per element, so no element loses bits to its neighbours
+    rng = np.random.default_rng(3)
+    m, n, k = 256, 384, 512
+    a = (rng.uniform(-1, 1, (m, k)) * 10.0 ** rng.integers(-6, 7, (m, k))).astype(np.float32)
+    b = (rng.uniform(-1, 1, (n, k)) * 10.0 ** rng.integers(-6, 7, (n, k))).astype(np.float32)
+    got = run_case("f32", a, b, kernel=K.KERNEL_F32_TF32X3)
+    assert rel_frobenius(got, port.matmul_f32(a, b)) <= TOL_F32
+    # and without the scratch the automatic choice is the FMA kernel, with it the split route: both inside the bar
+    da, db = to_device(a), to_device(b)
+    c = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    problem = harness.matmul_problem(da, db, c)
+    harness.run(problem)
+    assert rel_frobenius(c.cpu().numpy(), port.matmul_f32(a, b)) <= TOL_F32
+    scratch = harness.attach_workspace(problem, da.device)
+    assert scratch is not None
+    before = capi.library().vecops_b200_launch_count()
+    harness.run(problem)
+    assert capi.library().vecops_b200_launch_count() - before == 2  # the operand split and the product
+    assert rel_frobenius(c.cpu().numpy(), port.matmul_f32(a, b)) <= TOL_F32
+
+
 @pytest.mark.parametrize("kind", ["f32", "bf16", "i8", "w8"])
 def test_strided_kernel_on_reference_test_shapes(port, kind):
     # ragged shapes and K tails the reference exercises (tests/ops/MatmulTest.cpp:434-452)

@@ -24,7 +24,7 @@ DEVICE_CPU, DEVICE_CUDA = 1, 2
 VALUE_NONE, VALUE_TENSOR, VALUE_SCALAR = 0, 1, 2
 TENSOR_READ, TENSOR_WRITE = 1, 2
 # VecopsB200MatmulKernel
-KERNEL_AUTO, KERNEL_GENERIC, KERNEL_F32_SIMT, KERNEL_BF16_TCGEN05, KERNEL_I8_TCGEN05, KERNEL_W8_SMALL_M, KERNEL_W8_TCGEN05 = range(7)
+KERNEL_AUTO, KERNEL_GENERIC, KERNEL_F32_SIMT, KERNEL_BF16_TCGEN05, KERNEL_I8_TCGEN05, KERNEL_W8_SMALL_M, KERNEL_W8_TCGEN05, KERNEL_F32_TF32X3 = range(8)
 MATMUL_FLAG_ASYNC = 1
 CONTEXT_FLAG_ASYNC = 1 << 32
 

@@ -236,7 +236,8 @@ __device__ __forceinline__ void widen4_bf16(uint32_t packed, uint32_t& lo, uint3
 }
 
 // OutT: __nv_bfloat16, __half or float for kind::f16 (bf16 or fp16 operands, chosen by the instruction descriptor), int32_t for kind::i8.
-template <bool kInt8, typename OutT, bool kPair, bool kW8 = false>
+// kTf32: the operands are fp32 words multiplied as tf32 (kind::tf32, single CTAs only) - the building block of the split fp32 product.
+template <bool kInt8, typename OutT, bool kPair, bool kW8 = false, bool kTf32 = false>
 __global__ void __launch_bounds__(kW8 ? GemmW8::kThreads : GemmTc::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const __grid_constant__ GemmStoreMaps tma_c, int num_dest, int c_col_offset, OutT* __restrict__ c,
@@ -246,7 +247,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                     unsigned long long* __restrict__ trace) {
   static_assert(!kW8 || (!kInt8 && !kPair), "the weight-only form is a single-CTA 16-bit product");
   using G = typename std::conditional<kW8, GemmW8, typename std::conditional<kPair, GemmPair, GemmTc>::type>::type;
-  constexpr int kElemBytes = kInt8 ? 1 : 2;
+  static_assert(!kTf32 || (!kInt8 && !kPair && !kW8 && std::is_same<OutT, float>::value), "the tf32 form is a single-CTA fp32 product");
+  constexpr int kElemBytes = kInt8 ? 1 : kTf32 ? 4 : 2;
   // elements of K per step of the main loop: one 128-byte swizzle atom, or - weight-only form - one unit of two
   constexpr int kBlockK = kW8 ? GemmW8::kUnitK : G::kBlockKBytes / kElemBytes;
   constexpr int kRingBytes = kW8 ? GemmW8::kRingBytes : G::kStages * G::kStageBytes;
@@ -479,6 +481,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
               else umma_f16_pair(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accumulate);
             } else {
               if (kInt8) umma_i8(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accumulate);
+              else if (kTf32) umma_tf32(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accumulate);
               else umma_f16(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accumulate);
             }
           }

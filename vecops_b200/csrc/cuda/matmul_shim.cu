@@ -195,6 +195,10 @@ bool applicable(const VecopsB200Matmul& p, Row row, uint32_t kernel) {
     case VECOPS_B200_KERNEL_F32_SIMT:
       return row == Row::F32 && p.a_stride_k == 1 && p.c_stride_n == 1 && (p.b_stride_k == 1 || p.b_stride_n == 1) &&
              p.column_scale == nullptr;
+    case VECOPS_B200_KERNEL_F32_TF32X3:
+      // any operand strides (the split pre-pass reads them); C row-major; K small enough for the tripled reduction
+      return row == Row::F32 && p.c_stride_n == 1 && p.k > 0 && p.k < (INT64_C(1) << 29) && p.m < (INT64_C(1) << 31) &&
+             p.n < (INT64_C(1) << 31) && p.c_stride_m >= p.n && p.column_scale == nullptr;
     case VECOPS_B200_KERNEL_BF16_TCGEN05:
       return (row == Row::BF16 || row == Row::F16) && tma_operands_ok(p, 2);  // fp16 rides the same kernel: the formats are in the instruction descriptor
     case VECOPS_B200_KERNEL_I8_TCGEN05:
@@ -215,7 +219,7 @@ bool applicable(const VecopsB200Matmul& p, Row row, uint32_t kernel) {
 }
 
 const char* const kKernelNames[VECOPS_B200_KERNEL_COUNT_] = {
-    "auto", "generic", "f32_simt", "bf16_tcgen05", "i8_tcgen05", "w8_small_m", "w8_tcgen05"};
+    "auto", "generic", "f32_simt", "bf16_tcgen05", "i8_tcgen05", "w8_small_m", "w8_tcgen05", "f32_tf32x3"};
 
 uint32_t forced_by_environment() {
   const char* text = getenv("VECOPS_B200_FORCE_KERNEL");
@@ -244,6 +248,9 @@ int32_t check_problem(const VecopsB200Matmul* p, Row* row, VecopsError* error) {
 
 // `for_query`: the answer for the selection and workspace queries - the kernel the rules prefer, whatever scratch the
 // record carries; a launch (for_query = false) takes the preferred kernel only if the scratch it cannot do without is there.
+bool tf32x3_worthwhile(const VecopsB200Matmul& p);
+uint64_t tf32x3_scratch(const VecopsB200Matmul& p);
+
 int32_t select_kernel(const VecopsB200Matmul& p, Row row, uint32_t* kernel, VecopsError* error, bool for_query = true) {
   uint32_t wanted = p.kernel != VECOPS_B200_KERNEL_AUTO ? p.kernel : forced_by_environment();
   if (wanted != VECOPS_B200_KERNEL_AUTO) {
@@ -258,6 +265,11 @@ int32_t select_kernel(const VecopsB200Matmul& p, Row row, uint32_t* kernel, Veco
   switch (row) {
     case Row::F32:
       if (!tiny && applicable(p, row, VECOPS_B200_KERNEL_F32_SIMT)) pick = VECOPS_B200_KERNEL_F32_SIMT;
+      // Products big enough to pay for the operand split go to the tensor cores as three tf32 products - when the
+      // caller brings the scratch the split operands live in (the query reports it); without it the FMA kernel serves.
+      if (!tiny && tf32x3_worthwhile(p) && applicable(p, row, VECOPS_B200_KERNEL_F32_TF32X3) &&
+          (for_query || (p.workspace != nullptr && aligned16(p.workspace) && p.workspace_size >= tf32x3_scratch(p))))
+        pick = VECOPS_B200_KERNEL_F32_TF32X3;
       break;
     case Row::F16:
     case Row::BF16:
@@ -393,10 +405,10 @@ struct Tcgen05Plan {
   long long scratch_slots = 0;  // per-CTA partial accumulators the split needs
 };
 
-Tcgen05Plan plan_tcgen05(const VecopsB200Matmul& p, bool int8, size_t out_elem, int sms, int max_pairs) {
+Tcgen05Plan plan_tcgen05(const VecopsB200Matmul& p, bool int8, size_t out_elem, int sms, int max_pairs, size_t elem_override = 0) {
   using G = GemmTc;
   Tcgen05Plan plan;
-  const size_t elem = int8 ? 1 : 2;
+  const size_t elem = elem_override != 0 ? elem_override : int8 ? 1 : 2;
   plan.num_kb = static_cast<int>((p.k * elem + G::kBlockKBytes - 1) / G::kBlockKBytes);
   const long long tiles_n = (p.n + G::kBlockN - 1) / G::kBlockN;
   const long long pair_tiles = ((p.m + 2 * G::kBlockM - 1) / (2 * G::kBlockM)) * tiles_n;
@@ -481,16 +493,17 @@ int pair_capacity(int device) {
   return clusters > 0 ? clusters : 0;
 }
 
-template <bool kInt8, typename OutT>
+template <bool kInt8, typename OutT, bool kTf32 = false>
 int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaStream_t stream, VecopsError* error,
                        const GatherTargets& gather = GatherTargets()) {
   using G = GemmTc;
   if (dev.prop.major != 10)
     return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "tcgen05 kernels need an sm_100 device, found sm_%d%d", dev.prop.major,
                      dev.prop.minor);
-  constexpr size_t elem = kInt8 ? 1 : 2;
-  const bool fp16_in = !kInt8 && p.a_dtype == VECOPS_DTYPE_F16;
+  constexpr size_t elem = kInt8 ? 1 : kTf32 ? 4 : 2;
+  const bool fp16_in = !kInt8 && !kTf32 && p.a_dtype == VECOPS_DTYPE_F16;
   const CUtensorMapDataType in_type = kInt8     ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                      : kTf32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                       : fp16_in ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const CUtensorMapDataType out_type = std::is_same<OutT, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -500,7 +513,8 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
   const uint32_t box_k = G::kBlockKBytes / elem;
   int device = 0;
   cudaGetDevice(&device);
-  const Tcgen05Plan plan = plan_tcgen05(p, kInt8, sizeof(OutT), dev.prop.multiProcessorCount, pair_capacity<kInt8, OutT>(device));
+  // (the tf32 form has no CTA-pair variant)
+  const Tcgen05Plan plan = plan_tcgen05(p, kInt8, sizeof(OutT), dev.prop.multiProcessorCount, kTf32 ? 0 : pair_capacity<kInt8, OutT>(device), elem);
   CUtensorMap map_a, map_b;
   GemmStoreMaps maps;
   int32_t rc = make_map_2d(&map_a, in_type, elem, p.a, p.k, p.m, p.a_stride_m * elem, box_k, G::kBlockM, error);
@@ -541,11 +555,20 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
     idesc = umma_instr_desc(kUmmaAccS32, p.a_dtype == VECOPS_DTYPE_I8 ? kUmmaS8 : kUmmaU8,
                             p.b_dtype == VECOPS_DTYPE_I8 ? kUmmaS8 : kUmmaU8, mma_m, G::kBlockN);
   } else {
-    const uint32_t format = fp16_in ? kUmmaF16 : kUmmaBF16;
+    const uint32_t format = kTf32 ? kUmmaTF32 : fp16_in ? kUmmaF16 : kUmmaBF16;
     idesc = umma_instr_desc(kUmmaAccF32, format, format, mma_m, G::kBlockN);
   }
-  rc = prepare_gemm_kernels<kInt8, OutT>(device, error);
-  if (rc != VECOPS_STATUS_OK) return rc;
+  if constexpr (kTf32) {
+    static std::atomic<bool> raised[kMaxDevices];
+    if (device < 0 || device >= kMaxDevices || !raised[device].load()) {
+      rc = raise_smem_limit(gemm_tcgen05_kernel<false, float, false, false, true>, GemmTc::kSmemBytes, error);
+      if (rc != VECOPS_STATUS_OK) return rc;
+      if (device >= 0 && device < kMaxDevices) raised[device].store(true);
+    }
+  } else {
+    rc = prepare_gemm_kernels<kInt8, OutT>(device, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+  }
   // Tail tiles are cut along K when the caller supplied the scratch the slices meet in; without it the tail runs whole.
   int split = plan.split;
   uint32_t* partials = nullptr;
@@ -606,8 +629,10 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
   EpilogueArgs epilogue = tl_epilogue;
   void* args[] = {&map_a, &map_b, &maps, &num_dest, &col_offset, &c, &ldc, &m, &n, &k, &scale, &idesc, &store_flag,
                   &raster_group, &split, &partials, &flags, &nonce, &epilogue, &status_word, &trace};
-  const void* entry = plan.pair ? reinterpret_cast<const void*>(gemm_tcgen05_kernel<kInt8, OutT, true>)
-                                : reinterpret_cast<const void*>(gemm_tcgen05_kernel<kInt8, OutT, false>);
+  const void* entry;
+  if constexpr (kTf32) entry = reinterpret_cast<const void*>(gemm_tcgen05_kernel<false, float, false, false, true>);
+  else entry = plan.pair ? reinterpret_cast<const void*>(gemm_tcgen05_kernel<kInt8, OutT, true>)
+                         : reinterpret_cast<const void*>(gemm_tcgen05_kernel<kInt8, OutT, false>);
   cudaError_t launched = cudaLaunchKernelExC(&config, entry, args);
   if (launched != cudaSuccess) return cuda_fail(error, launched, "launch of the tcgen05 GEMM");
   g_launches.fetch_add(1);
@@ -877,6 +902,71 @@ int32_t launch_w8_mixed(const VecopsB200Matmul& p, const DeviceState& dev, cudaS
   return VECOPS_STATUS_OK;
 }
 
+// ---- FP32 on the tensor cores: three tf32 products of split operands, run as one product over a tripled K.
+// Scratch layout: A' [M, 3 Kp] f32 | B' [N, 3 Kp] f32 | the scratch the inner tcgen05 GEMM's K slices meet in.
+struct Tf32x3Plan {
+  long long kp = 0;          // K rounded up to the 32 words of a k-block
+  uint64_t a_bytes = 0, b_bytes = 0, inner = 0;
+  VecopsB200Matmul inner_problem{};
+};
+
+uint64_t align256(uint64_t v) { return (v + 255u) & ~uint64_t{255}; }
+
+Tf32x3Plan plan_tf32x3(const VecopsB200Matmul& p, int sms) {
+  Tf32x3Plan plan;
+  plan.kp = (p.k + 31) & ~INT64_C(31);
+  plan.a_bytes = align256(static_cast<uint64_t>(p.m) * 3 * plan.kp * 4);
+  plan.b_bytes = align256(static_cast<uint64_t>(p.n) * 3 * plan.kp * 4);
+  VecopsB200Matmul q = p;
+  q.k = 3 * plan.kp;
+  q.a_stride_m = q.b_stride_n = 3 * plan.kp;
+  q.a_stride_k = q.b_stride_k = 1;
+  plan.inner_problem = q;
+  const Tcgen05Plan inner = plan_tcgen05(q, false, 4, sms, 0, 4);
+  plan.inner = inner.scratch_slots > 0 ? GemmTc::split_scratch_bytes(inner.scratch_slots) : 0;
+  return plan;
+}
+
+uint64_t tf32x3_scratch(const VecopsB200Matmul& p) {
+  if (p.m <= 0 || p.n <= 0 || p.k <= 0) return 0;
+  const Tf32x3Plan plan = plan_tf32x3(p, sm_count_for_query(p));
+  return plan.a_bytes + plan.b_bytes + plan.inner;
+}
+
+// The split costs two more launches and reads and writes both operands once: it pays from a few hundred MFLOP up.
+bool tf32x3_worthwhile(const VecopsB200Matmul& p) {
+  const char* v = getenv("VECOPS_B200_F32_TF32X3");  // tuning aid: 0 = never, 1 = whenever it applies
+  if (v != nullptr && v[0] == '0') return false;
+  if (v != nullptr && v[0] == '1') return true;
+  // (up to K = 8192: the tensor core's fp32 accumulation is coarser than a chain of FMAs, and the relative error of the
+  // product, about 2e-6 at K = 1024 and 4e-6 at K = 4096, must stay inside the fp32 bar of 1e-5)
+  return p.m >= 256 && p.n >= 256 && p.k >= 256 && p.k <= 8192;
+}
+
+int32_t launch_f32_tf32x3(const VecopsB200Matmul& p, const DeviceState& dev, cudaStream_t stream, VecopsError* error) {
+  Tf32x3Plan plan = plan_tf32x3(p, dev.prop.multiProcessorCount);
+  const uint64_t need = plan.a_bytes + plan.b_bytes + plan.inner;
+  if (p.workspace == nullptr || !aligned16(p.workspace) || p.workspace_size < need)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "f32_tf32x3 needs %llu bytes of 16-byte aligned device workspace, %llu were supplied",
+                     (unsigned long long)need, (unsigned long long)p.workspace_size);
+  char* base = static_cast<char*>(p.workspace);
+  float* a_split = reinterpret_cast<float*>(base);
+  float* b_split = reinterpret_cast<float*>(base + plan.a_bytes);
+  const int kp = static_cast<int>(plan.kp), k = static_cast<int>(p.k);
+  const long long a_blocks = (kp / 32) * ((p.m + 31) / 32), b_blocks = (kp / 32) * ((p.n + 31) / 32);
+  if (a_blocks + b_blocks > 0x7fffffffLL) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "extent too large for f32_tf32x3");
+  const SplitOperand split_a{static_cast<const float*>(p.a), p.a_stride_m, p.a_stride_k, a_split, static_cast<int>(p.m)};
+  const SplitOperand split_b{static_cast<const float*>(p.b), p.b_stride_n, p.b_stride_k, b_split, static_cast<int>(p.n)};
+  f32_split3_kernel<<<static_cast<unsigned>(a_blocks + b_blocks), 256, 0, stream>>>(split_a, split_b, static_cast<int>(a_blocks), k, kp);
+  g_launches.fetch_add(1);
+  VecopsB200Matmul q = plan.inner_problem;
+  q.a = a_split;
+  q.b = b_split;
+  q.workspace = plan.inner != 0 ? base + plan.a_bytes + plan.b_bytes : nullptr;
+  q.workspace_size = plan.inner;
+  return launch_tcgen05<false, float, true>(q, dev, stream, error);
+}
+
 // Scratch for the K slices of the tail tiles.  The grid is one CTA per SM; the SM count comes from the device the
 // problem names when one is usable, else from the part this library is built for (148).
 uint64_t tcgen05_tail_scratch(const VecopsB200Matmul& p, bool int8) {
@@ -1105,6 +1195,8 @@ int32_t vecops_b200_matmul_workspace(const VecopsB200Matmul* problem, uint64_t* 
   *bytes = 0;
   if (kernel == VECOPS_B200_KERNEL_W8_TCGEN05) {
     *bytes = w8_tmem_form() ? W8Tc::scratch_bytes(static_cast<int>(problem->m), problem->k) : w8_mixed_scratch(*problem);
+  } else if (kernel == VECOPS_B200_KERNEL_F32_TF32X3) {
+    *bytes = tf32x3_scratch(*problem);
   } else if (kernel == VECOPS_B200_KERNEL_BF16_TCGEN05 || kernel == VECOPS_B200_KERNEL_I8_TCGEN05) {
     *bytes = tcgen05_tail_scratch(*problem, kernel == VECOPS_B200_KERNEL_I8_TCGEN05);
   }
@@ -1149,6 +1241,7 @@ int32_t vecops_b200_matmul_run(const VecopsB200Matmul* problem, VecopsError* err
       switch (kernel) {
         case VECOPS_B200_KERNEL_GENERIC: rc = launch_generic(p, row, stream, error); break;
         case VECOPS_B200_KERNEL_F32_SIMT: rc = launch_f32(p, stream, error); break;
+        case VECOPS_B200_KERNEL_F32_TF32X3: rc = launch_f32_tf32x3(p, *dev, stream, error); break;
         case VECOPS_B200_KERNEL_BF16_TCGEN05:
           rc = p.c_dtype == VECOPS_DTYPE_BF16  ? launch_tcgen05<false, __nv_bfloat16>(p, *dev, stream, error)
                : p.c_dtype == VECOPS_DTYPE_F16 ? launch_tcgen05<false, __half>(p, *dev, stream, error)

@@ -335,6 +335,20 @@ __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t a_desc, uint64
       : "memory");
 }
 
+// kind::tf32: fp32 words in shared memory, of which the tensor core uses sign, exponent and the top 10 mantissa bits;
+// K = 8 per instruction (32 bytes of a K-major row, as for the other kinds).
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Pair forms: issued by one thread of the leader CTA; A is 256 rows (128 per CTA), B is N rows (N/2 per CTA), each CTA
 // reading its own shared memory at the descriptor's address and accumulating its 128 rows of D in its own TMEM.
 __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,

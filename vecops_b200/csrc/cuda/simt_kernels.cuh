@@ -349,6 +349,61 @@ gemm_f32_tile8_kernel(const float* __restrict__ a, long long lda, const float* _
   }
 }
 
+// ------------------------------------------------------------------ fp32 product on the tensor cores: operand split
+//
+// An fp32 value x is the sum of two tf32 values to within 2^-22 of itself: hi = tf32(x) (round to nearest, 10 mantissa
+// bits) and lo = tf32(x - hi).  With both operands split, a.b = a_hi.b_hi + a_lo.b_hi + a_hi.b_lo up to a term of 2^-22,
+// and each of the three products is exact in the tensor core's fp32 accumulator.  The three are run as ONE product over
+// a K three times as long: this kernel writes one operand's rows as [ first | second | third ] segments, each Kp wide
+// (K rounded up to the 32 words of a k-block, zero past K) - A' = [a_hi | a_lo | a_hi], B' = [b_hi | b_hi | b_lo] - so
+// that sum_k' A'[m,k'] B'[n,k'] is the fp32 product.  Any element strides: a 32 x 32 tile goes through shared memory so
+// that both the reads (along whichever axis is contiguous) and the writes (along K) are coalesced.
+__device__ __forceinline__ float round_to_tf32(float x) {
+  uint32_t bits;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bits) : "f"(x));
+  return __uint_as_float(bits);
+}
+
+// One launch splits both operands: blocks [0, a_blocks) take A's 32 x 32 tiles, the rest B's.
+struct SplitOperand {
+  const float* src;
+  long long stride_row, stride_k;
+  float* dst;
+  int rows;
+};
+
+__global__ void __launch_bounds__(256)
+f32_split3_kernel(SplitOperand a, SplitOperand b, int a_blocks, int K, int Kp) {
+  __shared__ float tile[32][33];
+  const bool is_b = static_cast<int>(blockIdx.x) >= a_blocks;
+  const SplitOperand o = is_b ? b : a;
+  const int block = is_b ? blockIdx.x - a_blocks : blockIdx.x;
+  const int k_tiles = Kp / 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const int r0 = (block / k_tiles) * 32, k0 = (block % k_tiles) * 32;
+  const bool k_contiguous = o.stride_k == 1 || o.stride_row != 1;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int r = r0 + (k_contiguous ? ty + 8 * j : tx), k = k0 + (k_contiguous ? tx : ty + 8 * j);
+    const float v = (r < o.rows && k < K) ? __ldg(o.src + static_cast<long long>(r) * o.stride_row + static_cast<long long>(k) * o.stride_k) : 0.f;
+    if (k_contiguous) tile[ty + 8 * j][tx] = v;
+    else tile[tx][ty + 8 * j] = v;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int r = r0 + ty + 8 * j;
+    if (r >= o.rows) continue;
+    const float x = tile[ty + 8 * j][tx];
+    const float hi = round_to_tf32(x);
+    const float lo = round_to_tf32(x - hi);
+    float* row = o.dst + static_cast<long long>(r) * (3ll * Kp) + k0 + tx;
+    row[0] = hi;
+    row[Kp] = is_b ? hi : lo;
+    row[2ll * Kp] = is_b ? lo : hi;
+  }
+}
+
 // ------------------------------------------------------------------ quantise-on-load helpers
 
 // dst[m,k] = convert(src[m,k] * scale + zero_point): truncation toward zero, saturating to the 8-bit range, as vecops

@@ -17,7 +17,8 @@ namespace {
 constexpr const char* kOperatorName = "vecops::matmul";
 constexpr std::uint32_t kVariants[] = {VECOPS_B200_KERNEL_BF16_TCGEN05, VECOPS_B200_KERNEL_I8_TCGEN05,
                                        VECOPS_B200_KERNEL_W8_SMALL_M,   VECOPS_B200_KERNEL_W8_TCGEN05,
-                                       VECOPS_B200_KERNEL_F32_SIMT,     VECOPS_B200_KERNEL_GENERIC};
+                                       VECOPS_B200_KERNEL_F32_TF32X3,   VECOPS_B200_KERNEL_F32_SIMT,
+                                       VECOPS_B200_KERNEL_GENERIC};
 
 struct ErrorText {
   std::array<char, 1024> text{};
@@ -161,6 +162,7 @@ const VariantDescriptor* variant_descriptor(std::uint32_t kernel) {
       build_variant<VECOPS_B200_KERNEL_I8_TCGEN05>(i8 | u8, i8 | u8, i32 | f32 | bf16, 16, 16, 1, true, true),
       build_variant<VECOPS_B200_KERNEL_W8_SMALL_M>(bf16, i8, bf16 | f32, 8, 16, 32, true, true),
       build_variant<VECOPS_B200_KERNEL_W8_TCGEN05>(bf16, i8, bf16 | f32, 8, 16, 32, true, true),
+      build_variant<VECOPS_B200_KERNEL_F32_TF32X3>(f32, f32, f32, 1, 1, 1, false, true),
   };
   return kernel < VECOPS_B200_KERNEL_COUNT_ ? table[kernel] : nullptr;
 }
