@@ -38,11 +38,12 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, read from one ncu capture of that
 # workload, with the committed summary the figure was taken from.  A workload without a capture reports null.
 NCU_TRAFFIC = {
-    "c1_f32_1024": (8.45e6, "profiles/gemm_f32__c1_f32_1024.md"),
+    "c1_f32_1024": (25.2e6, "profiles/f32_tf32x3__c1_f32_1024.md (the GEMM launch; the split pre-pass adds 8.4 MB)"),
     "c2_bf16_4096": (99.3e6, "profiles/gemm_tcgen05_bf16__c2_bf16_4096.md"),
     "c3_i8_4096x14336x4096": (282.6e6, "profiles/gemm_tcgen05_i8__c3_i8_4096x14336x4096.md"),
-    "c4_w8_m16": (59.3e6, "profiles/w8_stream__c4_w8_m16.md"),
-    "c4_w8_m128": (63.1e6, "profiles/w8_tcgen05__c4_w8_m128.md"),
+    "c4_w8_m1": (58.9e6, "profiles/w8_stream__c4_w8_m1.md"),
+    "c4_w8_m16": (59.1e6, "profiles/w8_stream__c4_w8_m16.md"),
+    "c4_w8_m128": (60.7e6, "profiles/gemm_tcgen05_w8__c4_w8_m128.md"),
 }
 # What a GPU can receive when all eight send to all eight at once: a store-only all-to-all probe on this pool
 # (148 CTAs per GPU issuing the epilogue's own 32-row x 128-byte TMA stores to the seven peers) measured 668 GB/s per

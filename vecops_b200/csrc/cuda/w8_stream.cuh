@@ -4,16 +4,19 @@
 //
 // How the bytes move:
 //   * one persistent CTA per SM owns a contiguous range of W's rows, N / gridDim of them to within one row, so every
-//     SM streams the same number of bytes; it walks the range in items of 8 rows (8 x K bytes, contiguous rows);
+//     SM streams the same number of bytes; it walks the range in items of 16 rows (up to 8 activation rows) or 8 rows
+//     (9 to 16 activation rows), K bytes per row, rows contiguous;
 //   * a producer warp streams items into a shared-memory ring with cp.async.bulk (one bulk copy per row, completion
-//     counted in bytes on an mbarrier): five stages at K = 4096, ~160 KB per SM in flight without holding registers;
+//     counted in bytes on an mbarrier): three 16-row or six 8-row stages at K = 4096, ~195 KB per SM in flight
+//     without holding registers;
 //   * 16 consumer warps split K: warp w owns the 128-wide k-chunks w, w+16.  Its activation fragments for those
 //     chunks are loaded ONCE into registers at kernel start and reused for every item, so the inner loop touches
-//     shared memory only for weights.  The weights are the B operand of mma.m16n8k16 (eight rows of W = the n of the
-//     instruction), the activations its A operand (up to 16 rows);
-//   * per item each consumer warp leaves its 16 x 8 partial fragment in a ring of four reduction buffers and goes
-//     straight on to the next item; a summing warp of its own adds the sixteen fragments in fixed warp order
-//     (deterministic), scales, converts and stores.  No consumer ever waits for a sum.
+//     shared memory only for weights.  Up to 8 activation rows the weights are the A operand of mma.m16n8k16 (sixteen
+//     rows of W = the m of the instruction) and the activations its B operand; from 9 to 16 activation rows the
+//     weights are its B operand (eight rows of W = its n) and the activations its A operand;
+//   * per item each consumer warp leaves its 16 x 8 partial fragment in a ring of two reduction buffers and goes
+//     on to the next item; a summing warp of its own adds the sixteen fragments in fixed warp order (deterministic),
+//     scales, converts and stores.  A consumer waits for a sum only when it is two items ahead of the summing warp.
 // The kernel is launched as a programmatic dependent: its set-up runs while the previous kernel of the stream drains.
 //
 // How the arithmetic is done.  The kernel is HBM-bound only if widening a
