@@ -331,7 +331,18 @@ VECOPS_B200_EXPORT int32_t vecops_b200_matmul_pack_b_compensated(const VecopsB20
  * Q [Lq,Dqk], K [Lkv,Dqk], V [Lkv,Dv] bf16 with element strides, out [Lq,Dv] f32 or bf16.  Masks are bytes (non-zero
  * keeps; the reference takes bool tensors), bias is f32; each may be NULL.  Device scratch (scores, probabilities, the
  * packed V^T and the products' own scratch) is the caller's: ask vecops_b200_sdpa_workspace, pass 256-byte aligned memory.
- * Not a fused attention kernel: the score matrix makes one round trip through device memory. */
+ * Two strategies, as in the reference (SDPAStrategy, SDPA.h:21-25): `streaming` - one kernel over all heads, the keys walked
+ * tile by tile with a running maximum and sum (SparseFlashAttention.h:360-545), nothing of size Lq x Lkv in device memory;
+ * it serves bf16 operands with head dims up to 128 and K-contiguous, 16-byte aligned rows of Q and K - and `materialized`
+ * (the composition above, any strides).  `automatic` takes streaming whenever it can serve the call; the workspace query
+ * and the run make the same choice.  Results of the two differ by the rounding of p (normalised before the bf16 rounding
+ * in one, after it in the other), inside the 1e-3 bar of the bf16 rows. */
+typedef enum VecopsB200SdpaStrategy {
+  VECOPS_B200_SDPA_AUTOMATIC = 0,
+  VECOPS_B200_SDPA_MATERIALIZED = 1,
+  VECOPS_B200_SDPA_STREAMING = 2 /* NOT_APPLICABLE when the call cannot be served by it */
+} VecopsB200SdpaStrategy;
+
 typedef struct VecopsB200Attention {
   uint32_t struct_size;
   uint32_t causal;            /* 0 none, 1 top left (key <= query), 2 bottom right (key <= query + Lkv - Lq) */
@@ -358,10 +369,11 @@ typedef struct VecopsB200Attention {
   uint64_t workspace_size;
   void* stream;
   int32_t device_index;
-  uint32_t reserved;
+  uint32_t strategy;          /* VecopsB200SdpaStrategy; 0 = automatic */
   /* Several heads in one call: head h reads q + h*q_stride_head (elements) and so on; a stride of 0 shares the operand
    * between heads (grouped-query K and V, one mask for all).  heads <= 1 means one head and the strides are ignored.
-   * The heads run one after the other on the stream and share the scratch, which is sized for one head. */
+   * The streaming strategy runs all heads in one launch; the materialized one runs them one after the other on the
+   * stream, sharing scratch sized for one head. */
   int64_t heads;
   int64_t q_stride_head, k_stride_head, v_stride_head, out_stride_head;
   int64_t query_mask_stride_head, key_mask_stride_head, keep_stride_head, bias_stride_head;

@@ -139,6 +139,8 @@ class Port:
         self.lib.oracle_matmul_f16_fused.argtypes = [_I64] * 3 + [_P, _I64, _I64, _P, _I64, _I64, _P, _I64, _I64, _F, _P, c_int, _F, _F, _P,
                                                                  _I64, _I64, c_int]
         self.lib.oracle_sdpa_bf16.argtypes = [_I64] * 4 + [_P, _I64, _P, _I64, _P, _I64, _P, _P, _P, _I64, _P, _I64, c_int, _F, _P, _I64, c_int]
+        self.lib.oracle_sdpa_bf16_streaming.argtypes = ([_I64] * 4 + [_P, _I64, _P, _I64, _P, _I64, _P, _P, _P, _I64, _P, _I64, c_int, _F, _I64, _I64,
+                                                         _P, _I64, c_int])
         self.lib.oracle_quantize_rows_per_row.argtypes = [_I64, _I64, _P, _I64, _I64, _P, _F, _P, _I64, _I64, c_int]
         self.lib.oracle_matmul_i8_dequant_rows.argtypes = [_I64] * 3 + [_P, _I64, _I64, c_int, _P, _I64, _I64, c_int, _P, _I64, _I64, _P, _P, _P,
                                                                        _I64, _I64, c_int]
@@ -234,6 +236,23 @@ class Port:
                                   _ptr(keep_mask), lkv, _ptr(bias), lkv, int(causal), float(scale), _ptr(out), dv, int(out_bf16))
         return out
 
+    def sdpa_bf16_streaming(self, q, k, v, scale, query_mask=None, key_mask=None, keep_mask=None, bias=None, causal=0, out_bf16=False,
+                            block=128, chunk_blocks=0):
+        """The same head by the streaming strategy: keys in blocks of `block`, probabilities rounded to bf16 before the
+        normalisation; `chunk_blocks` > 0 cuts the keys into chunks of that many blocks whose states are merged at the end."""
+        q, k, v = (np.ascontiguousarray(x) for x in (q, k, v))
+        lq, dqk = q.shape
+        lkv, dv = v.shape
+        out = np.empty((lq, dv), dtype=np.uint16 if out_bf16 else np.float32)
+        keep_mask = None if keep_mask is None else np.ascontiguousarray(keep_mask, dtype=np.uint8)
+        bias = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+        query_mask = None if query_mask is None else np.ascontiguousarray(query_mask, dtype=np.uint8)
+        key_mask = None if key_mask is None else np.ascontiguousarray(key_mask, dtype=np.uint8)
+        self.lib.oracle_sdpa_bf16_streaming(lq, lkv, dqk, dv, _ptr(q), dqk, _ptr(k), dqk, _ptr(v), dv, _ptr(query_mask), _ptr(key_mask),
+                                            _ptr(keep_mask), lkv, _ptr(bias), lkv, int(causal), float(scale), int(block), int(chunk_blocks),
+                                            _ptr(out), dv, int(out_bf16))
+        return out
+
     def matmul_f32_fused(self, a, b_nk, cin=None, alpha=1.0, scale=None, act=ACT_NONE, lo=0.0, hi=0.0):
         m, k = a.shape
         n = b_nk.shape[0]
@@ -315,6 +334,8 @@ class Ref:
             lib.ref_matmul_quantized_per_row.argtypes = [_I64] * 3 + [_P, _I64, _P, ctypes.c_int32, _P, _I64, _P, _P, _P, _P, _I64]
         if hasattr(lib, "ref_sdpa_bf16"):
             lib.ref_sdpa_bf16.argtypes = [_I64] * 4 + [_P] * 7 + [c_int, ctypes.c_float, _P]
+        if hasattr(lib, "ref_sdpa_bf16_streaming"):
+            lib.ref_sdpa_bf16_streaming.argtypes = [_I64] * 4 + [_P] * 7 + [c_int, ctypes.c_float, _P]
         if hasattr(lib, "ref_f16_widen"):
             lib.ref_f16_widen.argtypes = [_P, _P, _I64]
             lib.ref_f16_narrow.argtypes = [_P, _P, _I64]
@@ -323,16 +344,17 @@ class Ref:
         if hasattr(lib, "ref_pack_b_compensated"):
             lib.ref_pack_b_compensated.argtypes = [_I64, _I64, _P, _I64, ctypes.c_int32, _P]
 
-    def sdpa_bf16(self, q, k, v, scale, query_mask=None, key_mask=None, keep_mask=None, bias=None, causal=0):
-        """The reference's own attention (materialized strategy); the four optional operands come all together or not at all."""
+    def sdpa_bf16(self, q, k, v, scale, query_mask=None, key_mask=None, keep_mask=None, bias=None, causal=0, streaming=False):
+        """The reference's own attention (materialized strategy, or streaming over key blocks of 128); the four optional
+        operands come all together or not at all."""
         q, k, v = (np.ascontiguousarray(x) for x in (q, k, v))
         lq, dqk = q.shape
         lkv, dv = v.shape
         out = np.full((lq, dv), -99.0, dtype=np.float32)
         optional = [None if x is None else np.ascontiguousarray(x, dtype=t)
                     for x, t in ((query_mask, np.uint8), (key_mask, np.uint8), (keep_mask, np.uint8), (bias, np.float32))]
-        rc = self.lib.ref_sdpa_bf16(lq, lkv, dqk, dv, _ptr(q), _ptr(k), _ptr(v), *[_ptr(x) for x in optional], int(causal), float(scale),
-                                    _ptr(out))
+        door = self.lib.ref_sdpa_bf16_streaming if streaming else self.lib.ref_sdpa_bf16
+        rc = door(lq, lkv, dqk, dv, _ptr(q), _ptr(k), _ptr(v), *[_ptr(x) for x in optional], int(causal), float(scale), _ptr(out))
         assert rc == 0, rc
         return out
 

@@ -414,6 +414,85 @@ void oracle_sdpa_bf16(int64_t lq, int64_t lkv, int64_t dqk, int64_t dv, const ui
   }
 }
 
+/* The same attention by the streaming strategy (include/vecops/ops/details/attention/SparseFlashAttention.h:360-545 walked
+ * over every key/value block, as ScaledDotProductAttention does for SDPAStrategy::streaming, :993-1010): per query row a
+ * running maximum m, a running sum l and an unnormalised fp32 accumulator O; per block of `block` keys
+ *   m' = max(m, block maximum);  a block with nothing kept (or m' = -inf) contributes zero probabilities and alpha = 1;
+ *   alpha = 0 when m = -inf, exp(m - m') when the block raised the maximum, else 1;
+ *   p = exp(s - m'), summed UNROUNDED into l = alpha * l + sum, then rounded to the probability type (bf16);
+ *   O = alpha * O + p.V_block;   out = O / l when l > 0, else 0.
+ * `chunk_blocks` > 0 restates what a GPU launch does when it cuts a row's keys into chunks of that many blocks handled by
+ * different SMs: every chunk runs the recurrence from (m = -inf, l = 0, O = 0) and the chunk states are merged with the same
+ * rule, (m, l, O) = (max m_c, sum l_c exp(m_c - m), sum O_c exp(m_c - m)), before the division.  0 = one chunk. */
+void oracle_sdpa_bf16_streaming(int64_t lq, int64_t lkv, int64_t dqk, int64_t dv, const uint16_t* q, int64_t sq, const uint16_t* k,
+                                int64_t sk, const uint16_t* v, int64_t sv, const uint8_t* query_mask, const uint8_t* key_mask,
+                                const uint8_t* keep_mask, int64_t keep_sr, const float* bias, int64_t bias_sr, int causal, float scale,
+                                int64_t block, int64_t chunk_blocks, void* out, int64_t so, int out_is_bf16) {
+  if (block < 1) block = 128;
+  const int64_t blocks = (lkv + block - 1) / block;
+  if (chunk_blocks < 1 || chunk_blocks > blocks) chunk_blocks = blocks > 0 ? blocks : 1;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < lq; ++i) {
+    float* s = (float*)malloc((size_t)block * sizeof(float));
+    double* acc = (double*)malloc((size_t)(dv > 0 ? dv : 1) * sizeof(double));      /* the chunk in hand */
+    double* merged = (double*)calloc((size_t)(dv > 0 ? dv : 1), sizeof(double));   /* chunks merged so far */
+    float merged_m = -INFINITY;
+    double merged_l = 0.0;
+    const int64_t last_key = causal == 1 ? i : (causal == 2 ? i + (lkv - lq) : lkv - 1);
+    const int query_active = query_mask == NULL || query_mask[i] != 0;
+    for (int64_t first = 0; first < blocks; first += chunk_blocks) {
+      float m = -INFINITY;
+      double l = 0.0;
+      for (int64_t d = 0; d < dv; ++d) acc[d] = 0.0;
+      for (int64_t b = first; b < blocks && b < first + chunk_blocks; ++b) {
+        const int64_t j0 = b * block, j1 = j0 + block < lkv ? j0 + block : lkv;
+        float block_max = -INFINITY;
+        for (int64_t j = j0; j < j1; ++j) {
+          double sum = 0.0;
+          for (int64_t d = 0; d < dqk; ++d) sum += (double)bf16_to_f32(q[i * sq + d]) * (double)bf16_to_f32(k[j * sk + d]);
+          float value = (float)sum * scale;
+          if (bias) value += bias[i * bias_sr + j];
+          const int keep = query_active && j <= last_key && (key_mask == NULL || key_mask[j] != 0) &&
+                           (keep_mask == NULL || keep_mask[i * keep_sr + j] != 0);
+          s[j - j0] = keep ? value : -INFINITY;
+          if (s[j - j0] > block_max) block_max = s[j - j0];
+        }
+        const float next = m > block_max ? m : block_max;
+        if (next == -INFINITY) continue;  /* nothing kept so far: zero probabilities, alpha = 1 */
+        const double alpha = m == -INFINITY ? 0.0 : exp((double)m - (double)next);
+        double block_sum = 0.0;
+        for (int64_t d = 0; d < dv; ++d) acc[d] *= alpha;
+        for (int64_t j = j0; j < j1; ++j) {
+          const float pj = s[j - j0] == -INFINITY ? 0.f : (float)exp((double)s[j - j0] - (double)next);
+          block_sum += pj;
+          const double rounded = (double)bf16_to_f32(f32_to_bf16(pj));
+          for (int64_t d = 0; d < dv; ++d) acc[d] += rounded * (double)bf16_to_f32(v[j * sv + d]);
+        }
+        l = alpha * l + block_sum;
+        m = next;
+      }
+      /* merge the chunk into what the earlier chunks left */
+      const float top = merged_m > m ? merged_m : m;
+      if (top != -INFINITY) {
+        const double w_old = merged_m == -INFINITY ? 0.0 : exp((double)merged_m - (double)top);
+        const double w_new = m == -INFINITY ? 0.0 : exp((double)m - (double)top);
+        merged_l = merged_l * w_old + l * w_new;
+        for (int64_t d = 0; d < dv; ++d) merged[d] = merged[d] * w_old + acc[d] * w_new;
+        merged_m = top;
+      }
+    }
+    const double reciprocal = merged_l > 0.0 ? 1.0 / merged_l : 0.0;
+    for (int64_t d = 0; d < dv; ++d) {
+      const float value = (float)(merged[d] * reciprocal);
+      if (out_is_bf16) ((uint16_t*)out)[i * so + d] = f32_to_bf16(value);
+      else ((float*)out)[i * so + d] = value;
+    }
+    free(s);
+    free(acc);
+    free(merged);
+  }
+}
+
 #ifdef _OPENMP
 #include <omp.h>
 int oracle_threads(void) { return omp_get_max_threads(); }

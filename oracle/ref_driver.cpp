@@ -336,11 +336,11 @@ void ref_f16_narrow(const float* src, uint16_t* dst, int64_t count) {
 // The reference's scaled dot-product attention for one head (ops/details/attention/SDPA.h:72-84), materialized strategy:
 // Q[Lq,Dqk], K[Lkv,Dqk], V[Lkv,Dv] bf16, out[Lq,Dv] f32.  Call forms as in tests/ops/AttentionTest.cpp:238-241 (plain) and
 // :603-607 (query mask, key mask, keep mask, bias - all four or none).  causal: 0 none, 1 top_left, 2 bottom_right.
-template <ops::AttentionCausalMode Causal>
+template <ops::AttentionCausalMode Causal, ops::SDPAStrategy Strategy = ops::SDPAStrategy::materialized, int KeyValueBlock = 32>
 static int ref_sdpa_typed(int64_t lq, int64_t lkv, int64_t dqk, int64_t dv, const uint16_t* q, const uint16_t* k, const uint16_t* v,
                           const uint8_t* query_mask, const uint8_t* key_mask, const uint8_t* keep_mask, const float* bias, float scale,
                           float* out) {
-  using Config = ops::AttentionConfig<ops::MatmulConfig<matmul::AMX_BF16F32>, 32, 32, Causal, ops::SDPAStrategy::materialized>;
+  using Config = ops::AttentionConfig<ops::MatmulConfig<matmul::AMX_BF16F32>, 32, KeyValueBlock, Causal, Strategy>;
   auto qt = make_tensor(reinterpret_cast<const bfloat16_t*>(q), make_shape(Any{lq}, Any{dqk}));
   auto kt = make_tensor(reinterpret_cast<const bfloat16_t*>(k), make_shape(Any{lkv}, Any{dqk}));
   auto vt = make_tensor(reinterpret_cast<const bfloat16_t*>(v), make_shape(Any{lkv}, Any{dv}));
@@ -374,6 +374,23 @@ int ref_sdpa_bf16(int64_t lq, int64_t lkv, int64_t dqk, int64_t dv, const uint16
   if (causal == 1) return ref_sdpa_typed<ops::AttentionCausalMode::top_left>(lq, lkv, dqk, dv, q, k, v, query_mask, key_mask, keep_mask, bias, scale, out);
   if (causal == 2) return ref_sdpa_typed<ops::AttentionCausalMode::bottom_right>(lq, lkv, dqk, dv, q, k, v, query_mask, key_mask, keep_mask, bias, scale, out);
   return ref_sdpa_typed<ops::AttentionCausalMode::none>(lq, lkv, dqk, dv, q, k, v, query_mask, key_mask, keep_mask, bias, scale, out);
+}
+
+// The same call with the streaming strategy (SDPA.h:21-25; SparseFlashAttention.h:360-545 over every key/value block):
+// keys walked in blocks of 128 with a running maximum and sum, probabilities rounded to bf16 before normalisation.
+int ref_sdpa_bf16_streaming(int64_t lq, int64_t lkv, int64_t dqk, int64_t dv, const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                            const uint8_t* query_mask, const uint8_t* key_mask, const uint8_t* keep_mask, const float* bias, int causal,
+                            float scale, float* out) {
+  if (!request_amx()) return 1;
+  if ((query_mask == nullptr) != (key_mask == nullptr) || (query_mask == nullptr) != (keep_mask == nullptr) ||
+      (query_mask == nullptr) != (bias == nullptr))
+    return 2;
+  constexpr auto streaming = ops::SDPAStrategy::streaming;
+  if (causal == 1)
+    return ref_sdpa_typed<ops::AttentionCausalMode::top_left, streaming, 128>(lq, lkv, dqk, dv, q, k, v, query_mask, key_mask, keep_mask, bias, scale, out);
+  if (causal == 2)
+    return ref_sdpa_typed<ops::AttentionCausalMode::bottom_right, streaming, 128>(lq, lkv, dqk, dv, q, k, v, query_mask, key_mask, keep_mask, bias, scale, out);
+  return ref_sdpa_typed<ops::AttentionCausalMode::none, streaming, 128>(lq, lkv, dqk, dv, q, k, v, query_mask, key_mask, keep_mask, bias, scale, out);
 }
 
 }  // extern "C"

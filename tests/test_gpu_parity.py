@@ -1073,52 +1073,87 @@ def test_pack_operator_through_the_bridge():
 
 # ------------------------------------------------------------------ the caller one step up: scaled dot-product attention
 
-def _sdpa_gpu(case_or_kwargs, out_dtype=torch.float32):
+SDPA_STRATEGIES = [capi.SDPA_MATERIALIZED, capi.SDPA_STREAMING]
+
+
+def _launches() -> int:
+    capi.library().vecops_b200_launch_count.restype = ctypes.c_uint64
+    return capi.library().vecops_b200_launch_count()
+
+
+def _sdpa_gpu(case_or_kwargs, out_dtype=torch.float32, strategy=capi.SDPA_AUTOMATIC):
     c = case_or_kwargs
     q, k, v = (to_device(c[name], bf16=True) for name in ("q", "k", "v"))
     out = torch.full((q.shape[0], v.shape[1]), -99, dtype=out_dtype, device="cuda")
     optional = {name: to_device(np.ascontiguousarray(c[name])) for name in ("query_mask", "key_mask", "keep_mask", "bias") if c.get(name) is not None}
-    harness.sdpa(q, k, v, out, float(c["scale"]), causal=int(c.get("causal", 0)), **optional)
+    harness.sdpa(q, k, v, out, float(c["scale"]), causal=int(c.get("causal", 0)), strategy=strategy, **optional)
     torch.cuda.synchronize()
     return bf16_bits_to_f32(bf16_result_to_numpy(out)) if out_dtype == torch.bfloat16 else out.cpu().numpy()
 
 
-def test_sdpa_golden_fixtures(golden):
-    # outputs of the reference's own scaled_dot_product_attention on its tests' operand patterns and on seeded cases
+def _stream_cut(lq, lkv, causal, asked):
+    """128-key tiles per work item the streaming launch uses when VECOPS_B200_SDPA_CHUNK_TILES asks for `asked`: a query
+    block's keys are never cut into more than 32 chunks, and a chunk is never longer than the block with the most keys."""
+    last = lkv - 1 if causal == 0 else min(lkv - 1, lq - 1 + (lkv - lq if causal == 2 else 0))
+    most = max(1, last // 128 + 1) if last >= 0 else 1
+    return min(max(asked, -(-most // 32)), most)
+
+
+def _sdpa_want(port, strategy, q, k, v, scale, cut=0, **kwargs):
+    """The checker's result for the strategy: the two differ in where probabilities are rounded to bf16 (2e-3 .. 4e-3 apart,
+    as the reference's own two strategies are), so each kernel is held to the restatement of ITS strategy - for the
+    streaming one with the same cut of the keys into chunks."""
+    if strategy == capi.SDPA_STREAMING:
+        return port.sdpa_bf16_streaming(q, k, v, scale, chunk_blocks=cut, **kwargs)
+    return port.sdpa_bf16(q, k, v, scale, **kwargs)
+
+
+@pytest.mark.parametrize("strategy,cut", [(capi.SDPA_MATERIALIZED, 0), (capi.SDPA_STREAMING, 1000), (capi.SDPA_STREAMING, 1)])
+def test_sdpa_golden_fixtures(golden, port, monkeypatch, strategy, cut):
+    # outputs of the reference's own scaled_dot_product_attention, by its materialized and by its streaming strategy, on
+    # its tests' operand patterns and on seeded cases
+    monkeypatch.setenv("VECOPS_B200_SDPA_CHUNK_TILES", str(cut))
     seen = 0
     for name, case in golden.items():
         if str(case["kind"]) != "sdpa_bf16":
             continue
-        got = _sdpa_gpu(case)
-        assert rel_frobenius(got, case["out"]) <= TOL_BF16, name
-        assert np.array_equal((got == 0).all(axis=1), (case["out"] == 0).all(axis=1)), name  # fully masked rows are exactly zero
+        got = _sdpa_gpu(case, strategy=strategy)
+        want = case["out"] if strategy == capi.SDPA_MATERIALIZED else case["out_streaming"]
+        if cut == 1:  # every 128-key tile on its own SM, merged at the end: the reference has no such cut, the restatement does
+            optional = {n: case[n] for n in ("query_mask", "key_mask", "keep_mask", "bias") if case.get(n) is not None}
+            want = port.sdpa_bf16_streaming(case["q"], case["k"], case["v"], float(case["scale"]), causal=int(case["causal"]), chunk_blocks=1, **optional)
+        assert rel_frobenius(got, want) <= TOL_BF16, name
+        assert np.array_equal((got == 0).all(axis=1), (want == 0).all(axis=1)), name  # fully masked rows are exactly zero
         seen += 1
     assert seen >= 6
 
 
 @pytest.mark.parametrize("lq,lkv,dqk,dv,causal", [(512, 768, 64, 64, 0), (1024, 1024, 128, 128, 2), (300, 520, 72, 40, 1), (1, 2048, 128, 128, 0),
                                                     (257, 129, 64, 96, 2), (40, 9000, 64, 64, 0)])  # the last: rows too long for registers
-def test_sdpa_against_the_checker(port, lq, lkv, dqk, dv, causal):
+@pytest.mark.parametrize("strategy", SDPA_STRATEGIES)
+def test_sdpa_against_the_checker(port, monkeypatch, lq, lkv, dqk, dv, causal, strategy):
     # sizes at which both products run on the tensor-core kernels (and ragged ones that do not)
+    monkeypatch.setenv("VECOPS_B200_SDPA_CHUNK_TILES", "2")
+    cut = _stream_cut(lq, lkv, causal, 2)
     rng = np.random.default_rng(lq + lkv)
     case = dict(q=f32_to_bf16_bits(rng.standard_normal((lq, dqk)).astype(np.float32)),
                 k=f32_to_bf16_bits(rng.standard_normal((lkv, dqk)).astype(np.float32)),
                 v=f32_to_bf16_bits(rng.standard_normal((lkv, dv)).astype(np.float32)), scale=1.0 / np.sqrt(dqk), causal=causal)
     rows = np.unique(np.concatenate([np.linspace(0, lq - 1, 24).astype(np.int64), np.arange(max(0, lq - 3), lq)]))
-    got = _sdpa_gpu(case)
+    got = _sdpa_gpu(case, strategy=strategy)
     # rows of attention are independent: the checker runs on a sample of query rows (causal cuts are per row, so the
     # sample keeps its row indices through a keep mask instead)
     last = np.arange(lq)[:, None] + (0 if causal == 1 else lkv - lq)
     keep = np.ones((lq, lkv), np.uint8) if causal == 0 else (np.arange(lkv)[None, :] <= last).astype(np.uint8)
-    want = port.sdpa_bf16(case["q"][rows], case["k"], case["v"], case["scale"], keep_mask=keep[rows])
+    want = _sdpa_want(port, strategy, case["q"][rows], case["k"], case["v"], case["scale"], cut, keep_mask=keep[rows])
     assert rel_frobenius(got[rows], want) <= TOL_BF16
     # with every optional operand, bf16 out
     case.update(query_mask=(rng.random(lq) > 0.1).astype(np.uint8), key_mask=(rng.random(lkv) > 0.1).astype(np.uint8),
                 keep_mask=(rng.random((lq, lkv)) > 0.05).astype(np.uint8), bias=rng.uniform(-1, 1, (lq, lkv)).astype(np.float32))
-    got = _sdpa_gpu(case, torch.bfloat16)
+    got = _sdpa_gpu(case, torch.bfloat16, strategy=strategy)
     combined = (keep & case["keep_mask"])[rows]
-    want = port.sdpa_bf16(case["q"][rows], case["k"], case["v"], case["scale"], query_mask=case["query_mask"][rows], key_mask=case["key_mask"],
-                          keep_mask=combined, bias=case["bias"][rows], out_bf16=True)
+    want = _sdpa_want(port, strategy, case["q"][rows], case["k"], case["v"], case["scale"], cut, query_mask=case["query_mask"][rows],
+                      key_mask=case["key_mask"], keep_mask=combined, bias=case["bias"][rows], out_bf16=True)
     assert rel_frobenius(got[rows], bf16_bits_to_f32(want)) <= 3e-3  # one more bf16 rounding of the output on both sides
 
 
@@ -1136,7 +1171,56 @@ def test_sdpa_degenerate_extents_and_refusals():
     assert capi.library().vecops_b200_sdpa_run(byref(record), byref(error.record)) == capi.INVALID_ARGUMENT  # no scratch given
 
 
-def test_sdpa_heads_in_one_call(port):
+def test_sdpa_strategy_choice():
+    """Automatic takes the streaming kernel (a pack of V and one launch for all heads) whenever it can serve the call and the
+    composition through the matmul path (four launches per head) otherwise; a forced streaming call that cannot be
+    served says so instead of running something else."""
+    q = torch.randn((3, 256, 64), device="cuda").to(torch.bfloat16)
+    out = torch.empty((3, 256, 64), dtype=torch.float32, device="cuda")
+    before = _launches()
+    harness.sdpa(q, q, q, out, 0.125)
+    assert _launches() - before == 3 + 1  # V of each head transposed, one attention launch
+    before = _launches()
+    harness.sdpa(q, q, q, out, 0.125, strategy=capi.SDPA_MATERIALIZED)
+    assert _launches() - before == 3 * 4
+    strided = torch.randn((64, 256), device="cuda").to(torch.bfloat16).t()  # [256, 64] with the head dim strided
+    out2 = torch.empty((256, 64), dtype=torch.float32, device="cuda")
+    before = _launches()
+    harness.sdpa(strided, strided, strided, out2, 0.125)
+    assert _launches() - before == 4
+    with pytest.raises(capi.VecopsB200Error) as info:
+        harness.sdpa(strided, strided, strided, out2, 0.125, strategy=capi.SDPA_STREAMING)
+    assert info.value.code == capi.NOT_APPLICABLE
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("lq,lkv,d,causal,heads", [(4096, 4096, 128, 2, 1),   # every query block's keys cut into chunks that meet in scratch
+                                                   (128, 8192, 64, 0, 2),     # one query block per head, 32 chunks each (decode-like)
+                                                   (1000, 3000, 128, 1, 3)])  # ragged edges, top-left cut: late blocks see few keys
+def test_sdpa_streaming_chunks_merge(port, monkeypatch, lq, lkv, d, causal, heads):
+    monkeypatch.setenv("VECOPS_B200_SDPA_CHUNK_TILES", "4")
+    cut = _stream_cut(lq, lkv, causal, 4)
+    rng = np.random.default_rng(lq + lkv + heads)
+    qh = f32_to_bf16_bits(rng.standard_normal((heads, lq, d)).astype(np.float32))
+    kh = f32_to_bf16_bits(rng.standard_normal((heads, lkv, d)).astype(np.float32))
+    vh = f32_to_bf16_bits(rng.standard_normal((heads, lkv, d)).astype(np.float32))
+    out = torch.full((heads, lq, d), -99, dtype=torch.float32, device="cuda")
+    scale = 1.0 / np.sqrt(d)
+    for repeat in range(2):  # the second call finds the first one's counters and partial records in its scratch
+        harness.sdpa(to_device(qh, bf16=True), to_device(kh, bf16=True), to_device(vh, bf16=True), out, scale, causal=causal,
+                     strategy=capi.SDPA_STREAMING)
+        torch.cuda.synchronize()
+        rows = np.unique(np.concatenate([np.linspace(0, lq - 1, 20).astype(np.int64), np.arange(max(0, lq - 2), lq)]))
+        last = np.arange(lq)[:, None] + (0 if causal == 1 else lkv - lq)
+        keep = np.ones((lq, lkv), np.uint8) if causal == 0 else (np.arange(lkv)[None, :] <= last).astype(np.uint8)
+        for h in range(heads):
+            want = port.sdpa_bf16_streaming(qh[h][rows], kh[h], vh[h], scale, keep_mask=keep[rows], chunk_blocks=cut)
+            assert rel_frobenius(out[h].cpu().numpy()[rows], want) <= TOL_BF16, (repeat, h)
+
+
+@pytest.mark.parametrize("strategy", SDPA_STRATEGIES)
+def test_sdpa_heads_in_one_call(port, monkeypatch, strategy):
+    monkeypatch.setenv("VECOPS_B200_SDPA_CHUNK_TILES", "1000")  # 160 keys: two tiles, kept together
     # [heads, L, D] operands; K and V shared by pairs of heads (grouped-query: head stride via expanded views), one mask for all
     rng = np.random.default_rng(77)
     heads, lq, lkv, d = 4, 96, 160, 64
@@ -1149,17 +1233,17 @@ def test_sdpa_heads_in_one_call(port):
     k = to_device(kh, bf16=True).repeat_interleave(2, dim=0)       # heads 0,1 -> group 0; heads 2,3 -> group 1
     v = to_device(vh, bf16=True).repeat_interleave(2, dim=0)
     out = torch.full((heads, lq, d), -99, dtype=torch.float32, device="cuda")
-    harness.sdpa(q, k, v, out, 0.125, key_mask=to_device(key_mask), bias=to_device(bias), causal=capi.CAUSAL_BOTTOM_RIGHT)
+    harness.sdpa(q, k, v, out, 0.125, key_mask=to_device(key_mask), bias=to_device(bias), causal=capi.CAUSAL_BOTTOM_RIGHT, strategy=strategy)
     torch.cuda.synchronize()
     for h in range(heads):
-        want = port.sdpa_bf16(qh[h], kh[h // 2], vh[h // 2], 0.125, key_mask=key_mask, bias=bias[h], causal=2)
+        want = _sdpa_want(port, strategy, qh[h], kh[h // 2], vh[h // 2], 0.125, key_mask=key_mask, bias=bias[h], causal=2)
         assert rel_frobenius(out[h].cpu().numpy(), want) <= TOL_BF16, h
     # a head stride of 0 shares K and V between all heads
     shared_k, shared_v = to_device(kh[:1], bf16=True).expand(heads, lkv, d), to_device(vh[:1], bf16=True).expand(heads, lkv, d)
-    harness.sdpa(q, shared_k, shared_v, out, 0.125)
+    harness.sdpa(q, shared_k, shared_v, out, 0.125, strategy=strategy)
     torch.cuda.synchronize()
     for h in (0, heads - 1):
-        assert rel_frobenius(out[h].cpu().numpy(), port.sdpa_bf16(qh[h], kh[0], vh[0], 0.125)) <= TOL_BF16, h
+        assert rel_frobenius(out[h].cpu().numpy(), _sdpa_want(port, strategy, qh[h], kh[0], vh[0], 0.125)) <= TOL_BF16, h
 
 
 
@@ -1295,8 +1379,8 @@ def test_torch_ops_reach_the_kernels(port):
     q, kk, v = (f32_to_bf16_bits(rng.standard_normal((heads, length, d)).astype(np.float32)) for _ in range(3))
     out = ops.sdpa(to_device(q, bf16=True), to_device(kk, bf16=True), to_device(v, bf16=True), 0.125, capi.CAUSAL_BOTTOM_RIGHT, None, None, torch.float32)
     torch.cuda.synchronize()
-    for h in range(heads):
-        assert rel_frobenius(out[h].cpu().numpy(), port.sdpa_bf16(q[h], kk[h], v[h], 0.125, causal=2)) <= TOL_BF16
+    for h in range(heads):  # six tiles on 148 SMs: the automatic cut is one tile per work item, and the restatement gets the same
+        assert rel_frobenius(out[h].cpu().numpy(), port.sdpa_bf16_streaming(q[h], kk[h], v[h], 0.125, causal=2, chunk_blocks=_stream_cut(length, length, 2, 1))) <= TOL_BF16
     # a captured CUDA graph replays the operator
     static_c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
     ops.matmul_out(da, db, static_c)  # warm-up outside the capture (first-use set-up)

@@ -41,6 +41,13 @@ def test_port_matches_golden_fixtures(port, golden):
                                  case.get("keep_mask"), case.get("bias"), int(case["causal"]))
             assert rel_frobenius(got, case["out"]) <= 1e-5, name  # the reference's fast exp is the only difference
             assert np.array_equal((got == 0).all(axis=1), (case["out"] == 0).all(axis=1)), name  # fully masked rows are exactly zero
+            # ... and of its streaming strategy (key blocks of 128, probabilities rounded before the normalisation)
+            streamed = port.sdpa_bf16_streaming(case["q"], case["k"], case["v"], float(case["scale"]), case.get("query_mask"),
+                                                case.get("key_mask"), case.get("keep_mask"), case.get("bias"), int(case["causal"]))
+            assert rel_frobenius(streamed, case["out_streaming"]) <= 1e-5, name
+            assert np.array_equal((streamed == 0).all(axis=1), (case["out_streaming"] == 0).all(axis=1)), name
+            # the two strategies round probabilities at different scalings: they agree to a few 1e-3, not to 1e-5
+            assert 1e-4 < rel_frobenius(case["out_streaming"], case["out"]) < 5e-3, name
             checked += 1
             continue
         if kind == "pack_comp":

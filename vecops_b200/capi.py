@@ -105,12 +105,13 @@ class VecopsB200Attention(Structure):
                 ("query_mask", c_void_p), ("key_mask", c_void_p), ("keep_mask", c_void_p), ("keep_stride_row", c_int64),
                 ("keep_stride_col", c_int64), ("bias", c_void_p), ("bias_stride_row", c_int64), ("bias_stride_col", c_int64),
                 ("scale", c_float), ("flags", c_uint32), ("workspace", c_void_p), ("workspace_size", c_uint64), ("stream", c_void_p),
-                ("device_index", c_int32), ("reserved", c_uint32), ("heads", c_int64), ("q_stride_head", c_int64), ("k_stride_head", c_int64),
+                ("device_index", c_int32), ("strategy", c_uint32), ("heads", c_int64), ("q_stride_head", c_int64), ("k_stride_head", c_int64),
                 ("v_stride_head", c_int64), ("out_stride_head", c_int64), ("query_mask_stride_head", c_int64),
                 ("key_mask_stride_head", c_int64), ("keep_stride_head", c_int64), ("bias_stride_head", c_int64)]
 
 
 CAUSAL_NONE, CAUSAL_TOP_LEFT, CAUSAL_BOTTOM_RIGHT = 0, 1, 2
+SDPA_AUTOMATIC, SDPA_MATERIALIZED, SDPA_STREAMING = 0, 1, 2  # VecopsB200SdpaStrategy
 
 
 class VecopsB200Gather(Structure):

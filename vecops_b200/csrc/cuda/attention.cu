@@ -1,7 +1,10 @@
-// Scaled dot-product attention for one head, built the way vecops builds it: two products through the matmul
-// entry points with a row softmax between them (include/vecops/ops/details/attention/SDPA.h:305-383, the
-// "materialized" strategy).  The caller one step above the matmul path - not a fused attention kernel: the score
-// matrix makes one round trip through device memory.
+// Scaled dot-product attention, the caller one step above the matmul path, in vecops' two strategies
+// (include/vecops/ops/details/attention/SDPA.h:21-25):
+//   * streaming: one kernel over all heads (sdpa_stream.cuh) after V has been transposed by the pack kernel; nothing of
+//     size Lq x Lkv exists in device memory.  Taken whenever the operands allow (head dims up to 128, TMA-addressable
+//     Q and K);
+//   * materialized, built the way vecops builds it: two products through the matmul entry points with a row softmax
+//     between them (SDPA.h:305-383); the score matrix makes one round trip through device memory.  Serves the rest.
 //
 //   S = Q.K^T            vecops_b200_matmul_run, bf16 x bf16 -> f32            (tcgen05 when the operands allow)
 //   P = softmax rows     sdpa_softmax_kernel: scale, bias, masks, causal cut, exp, normalise, round to bf16
@@ -11,9 +14,15 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <atomic>
 
 #include "vecops_b200/matmul_cuda.h"
 
+#include "sdpa_stream.cuh"
+#include "shim_device.h"
 #include "shim_util.h"
 
 using namespace vb200;
@@ -206,6 +215,193 @@ int32_t plan_of(const VecopsB200Attention& a, char* base, Plan* out, VecopsError
   return VECOPS_STATUS_OK;
 }
 
+
+// ---------------------------------------------------------------- streaming strategy
+
+struct StreamPlan {
+  int q_blocks = 0, tiles_per_chunk = 1, max_chunks = 1;
+  int value_slabs = 1;  // transposed copies of V: one per head, or one for all when the heads share V
+  int64_t pitch = 0;    // elements per row of a transposed V
+  uint64_t slab_bytes = 0, partials_at = 0, counters_at = 0, total = 0;
+};
+
+uint32_t strategy_of(const VecopsB200Attention& a) {
+  if (a.strategy != VECOPS_B200_SDPA_AUTOMATIC) return a.strategy;
+  const char* forced = getenv("VECOPS_B200_SDPA");
+  if (forced != nullptr && strcmp(forced, "materialized") == 0) return VECOPS_B200_SDPA_MATERIALIZED;
+  if (forced != nullptr && strcmp(forced, "streaming") == 0) return VECOPS_B200_SDPA_STREAMING;
+  return VECOPS_B200_SDPA_AUTOMATIC;
+}
+
+bool tma_addressable(const void* base, int64_t stride_row, int64_t stride_col, int64_t stride_head, int64_t heads) {
+  return stride_col == 1 && stride_row > 0 && stride_row % 8 == 0 && (reinterpret_cast<uintptr_t>(base) & 15u) == 0 &&
+         (heads <= 1 || (stride_head >= 0 && stride_head % 8 == 0));
+}
+
+// What the streaming kernel can serve; `why` names the first obstacle.
+bool stream_applicable(const VecopsB200Attention& a, const char** why) {
+  const int64_t heads = a.heads <= 1 ? 1 : a.heads;
+  const char* reason = nullptr;
+  if (a.qkv_dtype != VECOPS_DTYPE_BF16) reason = "q, k, v must be bf16";
+  else if (a.lq < 1 || a.lkv < 1) reason = "no queries or no keys";
+  else if (a.dqk < 1 || a.dqk > SdpaStream::kMaxHeadDim || a.dv < 1 || a.dv > SdpaStream::kMaxHeadDim) reason = "head dims must be 1..128";
+  else if (heads > 65535 || (a.lq + SdpaStream::kBlockQ - 1) / SdpaStream::kBlockQ > 65535) reason = "too many heads or query blocks for one grid";
+  else if (!tma_addressable(a.q, a.q_stride_row, a.q_stride_col, a.q_stride_head, heads)) reason = "q is not K-contiguous on 16-byte aligned rows";
+  else if (!tma_addressable(a.k, a.k_stride_row, a.k_stride_col, a.k_stride_head, heads)) reason = "k is not K-contiguous on 16-byte aligned rows";
+  if (why != nullptr) *why = reason;
+  return reason == nullptr;
+}
+
+int32_t plan_stream(const VecopsB200Attention& a, int sms, uint64_t scratch_limit, StreamPlan* out, VecopsError* error) {
+  using G = SdpaStream;
+  StreamPlan p;
+  const int64_t heads = a.heads <= 1 ? 1 : a.heads;
+  p.q_blocks = static_cast<int>((a.lq + G::kBlockQ - 1) / G::kBlockQ);
+  p.value_slabs = (heads > 1 && a.v_stride_head != 0) ? static_cast<int>(heads) : 1;
+  uint64_t packed_bytes = 0;
+  const int32_t rc = vecops_b200_matmul_packed_layout(VECOPS_DTYPE_BF16, a.dv, a.lkv, &p.pitch, &packed_bytes, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  p.slab_bytes = round_up(packed_bytes, 256);
+  // 128-key tiles per query block after the causal cut, over all heads
+  const int64_t shift = a.causal == 2 ? a.lkv - a.lq : 0;
+  int64_t total_tiles = 0, most = 0;
+  for (int b = 0; b < p.q_blocks; ++b) {
+    const int64_t last_row = (b + 1 < p.q_blocks ? static_cast<int64_t>(b + 1) * G::kBlockQ : a.lq) - 1;
+    int64_t last_key = a.causal != 0 ? last_row + shift : a.lkv - 1;
+    if (last_key > a.lkv - 1) last_key = a.lkv - 1;
+    const int64_t tiles = last_key < 0 ? 0 : last_key / G::kBlockKv + 1;
+    total_tiles += tiles;
+    if (tiles > most) most = tiles;
+  }
+  total_tiles *= heads;
+  // Fill the SMs once: a work item gets about total / SMs tiles; a block is never cut into more than kMaxChunks
+  int64_t per_chunk = (total_tiles + sms - 1) / sms;
+  if (per_chunk < 1) per_chunk = 1;
+  if (per_chunk * G::kMaxChunks < most) per_chunk = (most + G::kMaxChunks - 1) / G::kMaxChunks;
+  if (per_chunk > most) per_chunk = most > 0 ? most : 1;
+  // VECOPS_B200_SDPA_CHUNK_TILES=n: tiles per work item fixed by hand (tuning aid; tests use it to hold cut and uncut
+  // launches to the restatement with the same cut).  Still never more than kMaxChunks chunks per block.
+  if (const char* forced = getenv("VECOPS_B200_SDPA_CHUNK_TILES")) {
+    const long long asked = atoll(forced);
+    if (asked >= 1) per_chunk = asked > most ? (most > 0 ? most : 1) : asked;
+    if (per_chunk * G::kMaxChunks < most) per_chunk = (most + G::kMaxChunks - 1) / G::kMaxChunks;
+  }
+  auto layout = [&](int64_t chunk_tiles) {
+    p.tiles_per_chunk = static_cast<int>(chunk_tiles);
+    p.max_chunks = most > 0 ? static_cast<int>((most + chunk_tiles - 1) / chunk_tiles) : 1;
+    p.partials_at = p.slab_bytes * p.value_slabs;
+    const uint64_t partial_bytes =
+        p.max_chunks > 1 ? static_cast<uint64_t>(heads) * p.q_blocks * p.max_chunks * G::kPartialFloats * sizeof(float) : 0;
+    p.counters_at = p.partials_at + partial_bytes;
+    p.total = p.counters_at + (p.max_chunks > 1 ? round_up(static_cast<uint64_t>(heads) * p.q_blocks * 8, 256) : 0);
+  };
+  layout(per_chunk);
+  // a caller whose scratch was sized for another SM count still runs: uncut blocks need no partial records
+  if (scratch_limit != 0 && p.total > scratch_limit) layout(most > 0 ? most : 1);
+  *out = p;
+  return VECOPS_STATUS_OK;
+}
+
+int32_t sdpa_run_streaming(const VecopsB200Attention& a, VecopsError* error) {
+  using G = SdpaStream;
+  if (a.out == nullptr || a.q == nullptr || a.k == nullptr || a.v == nullptr)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "sdpa: null operand");
+  if (vecops_b200_device_count() == 0)
+    return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "no usable CUDA device; there is no CPU fallback");
+  int device = a.device_index;
+  if (device >= 0) {
+    const cudaError_t status = cudaSetDevice(device);
+    if (status != cudaSuccess) return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "cudaSetDevice(%d): %s", device, cudaGetErrorString(status));
+  } else {
+    cudaGetDevice(&device);
+  }
+  int sms = 0, major = 0;
+  uint32_t* status_word = nullptr;
+  int32_t rc = shim_device_facts(device, &sms, &major, &status_word, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  if (major != 10) return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "the streaming attention kernel needs an sm_100 device, found sm_%dx", major);
+  StreamPlan plan;
+  rc = plan_stream(a, sms, a.workspace_size, &plan, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  if (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & 255u) != 0 || a.workspace_size < plan.total)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "sdpa needs %llu bytes of 256-byte aligned device scratch (vecops_b200_sdpa_workspace)",
+                     (unsigned long long)plan.total);
+  const int64_t heads = a.heads <= 1 ? 1 : a.heads;
+  char* base = static_cast<char*>(a.workspace);
+  cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
+
+  // V^T per head (or once): B of the second product is V^T, rows along V's columns, keys contiguous
+  for (int slab = 0; slab < plan.value_slabs; ++slab) {
+    VecopsB200Pack pack{};
+    pack.struct_size = sizeof(VecopsB200Pack);
+    pack.operand = 1;
+    pack.rows = a.dv, pack.k = a.lkv;
+    pack.src = static_cast<const char*>(a.v) + static_cast<int64_t>(slab) * a.v_stride_head * 2;
+    pack.src_stride_row = a.v_stride_col, pack.src_stride_k = a.v_stride_row;
+    pack.src_dtype = pack.dst_dtype = VECOPS_DTYPE_BF16;
+    pack.dst = base + plan.slab_bytes * slab;
+    pack.dst_size = plan.slab_bytes;
+    pack.device_index = a.device_index;
+    pack.stream = a.stream;
+    rc = vecops_b200_matmul_pack(&pack, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+  }
+
+  CUtensorMap map_q, map_k, map_vt;
+  auto operand_map = [&](CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t stride_row, int64_t stride_head, bool per_head) {
+    const uint64_t dims[3] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows), per_head ? static_cast<uint64_t>(heads) : 1};
+    const uint64_t strides[2] = {static_cast<uint64_t>(stride_row) * 2,
+                                 per_head ? static_cast<uint64_t>(stride_head) * 2 : static_cast<uint64_t>(stride_row) * 2 * static_cast<uint64_t>(rows)};
+    const uint32_t box[3] = {64, 128, 1};
+    return shim_encode_map(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, ptr, dims, strides, box, error);
+  };
+  const bool q_per_head = heads > 1 && a.q_stride_head != 0, k_per_head = heads > 1 && a.k_stride_head != 0;
+  rc = operand_map(&map_q, a.q, a.lq, a.dqk, a.q_stride_row, a.q_stride_head, q_per_head);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  rc = operand_map(&map_k, a.k, a.lkv, a.dqk, a.k_stride_row, a.k_stride_head, k_per_head);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  rc = operand_map(&map_vt, base, a.dv, a.lkv, plan.pitch, static_cast<int64_t>(plan.slab_bytes / 2), plan.value_slabs > 1);
+  if (rc != VECOPS_STATUS_OK) return rc;
+
+  SdpaStreamParams p{};
+  p.lq = static_cast<int>(a.lq), p.lkv = static_cast<int>(a.lkv), p.dqk = static_cast<int>(a.dqk), p.dv = static_cast<int>(a.dv);
+  p.causal = static_cast<int>(a.causal);
+  p.tiles_per_chunk = plan.tiles_per_chunk;
+  p.q_head = q_per_head ? 1 : 0, p.k_head = k_per_head ? 1 : 0, p.v_head = plan.value_slabs > 1 ? 1 : 0;
+  p.scale = a.scale;
+  p.out = a.out, p.out_sr = a.out_stride_row, p.out_sc = a.out_stride_col, p.out_sh = heads > 1 ? a.out_stride_head : 0;
+  p.out_bf16 = a.out_dtype == VECOPS_DTYPE_BF16 ? 1 : 0;
+  p.query_mask = a.query_mask, p.query_mask_sh = heads > 1 ? a.query_mask_stride_head : 0;
+  p.key_mask = a.key_mask, p.key_mask_sh = heads > 1 ? a.key_mask_stride_head : 0;
+  p.keep_mask = a.keep_mask, p.keep_sr = a.keep_stride_row, p.keep_sc = a.keep_stride_col, p.keep_sh = heads > 1 ? a.keep_stride_head : 0;
+  p.bias = a.bias, p.bias_sr = a.bias_stride_row, p.bias_sc = a.bias_stride_col, p.bias_sh = heads > 1 ? a.bias_stride_head : 0;
+  p.partials = reinterpret_cast<float*>(base + plan.partials_at);
+  p.counters = reinterpret_cast<unsigned long long*>(base + plan.counters_at);
+  p.nonce = static_cast<uint32_t>(shim_nonce(a.workspace)) | 1u;
+  p.status = status_word;
+
+  const bool plain = a.key_mask == nullptr && a.keep_mask == nullptr && a.bias == nullptr;
+  auto kernel = plain ? &sdpa_stream_kernel<true> : &sdpa_stream_kernel<false>;
+  static std::atomic<bool> raised[2][64];
+  if (device < 0 || device >= 64 || !raised[plain][device].load()) {
+    const cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::kSmemBytes);
+    if (status != cudaSuccess) return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "cudaFuncSetAttribute(sdpa_stream): %s", cudaGetErrorString(status));
+    if (device >= 0 && device < 64) raised[plain][device].store(true);
+  }
+  const dim3 grid(static_cast<unsigned>(plan.max_chunks), static_cast<unsigned>(plan.q_blocks), static_cast<unsigned>(heads));
+  kernel<<<grid, G::kThreads, G::kSmemBytes, stream>>>(map_q, map_k, map_vt, p);
+  g_launches.fetch_add(1);
+  cudaError_t status = cudaGetLastError();
+  if (status != cudaSuccess) return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "sdpa_stream launch: %s", cudaGetErrorString(status));
+  if ((a.flags & VECOPS_B200_MATMUL_FLAG_ASYNC) == 0) {
+    status = cudaStreamSynchronize(stream);
+    if (status != cudaSuccess) return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "cudaStreamSynchronize: %s", cudaGetErrorString(status));
+    if (const uint32_t word = shim_take_status(device))
+      return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "sdpa_stream on device %d: a bounded device wait ran out (status 0x%x)", device, word);
+  }
+  return VECOPS_STATUS_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -213,6 +409,22 @@ extern "C" {
 int32_t vecops_b200_sdpa_workspace(const VecopsB200Attention* attention, uint64_t* bytes, VecopsError* error) {
   if (attention == nullptr || attention->struct_size < sizeof(VecopsB200Attention) || bytes == nullptr)
     return set_error(error, VECOPS_STATUS_ABI_MISMATCH, "attention record is null or too small, or no output pointer");
+  const uint32_t strategy = strategy_of(*attention);
+  const char* why = nullptr;
+  if (strategy > VECOPS_B200_SDPA_STREAMING) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "sdpa: unknown strategy %u", strategy);
+  if (strategy != VECOPS_B200_SDPA_MATERIALIZED && stream_applicable(*attention, &why)) {
+    // the SM count of the device the record names, or of a B200 when no device can be asked
+    int sms = 148, device = attention->device_index;
+    if (vecops_b200_device_count() > 0 && (device >= 0 || cudaGetDevice(&device) == cudaSuccess)) {
+      int asked = 0;
+      if (shim_device_facts(device, &asked, nullptr, nullptr, nullptr) == VECOPS_STATUS_OK && asked > 0) sms = asked;
+    }
+    StreamPlan stream;
+    const int32_t rc = plan_stream(*attention, sms, 0, &stream, error);
+    if (rc == VECOPS_STATUS_OK) *bytes = stream.total;
+    return rc;
+  }
+  if (strategy == VECOPS_B200_SDPA_STREAMING) return set_error(error, VECOPS_STATUS_NOT_APPLICABLE, "sdpa: the streaming strategy cannot serve this call: %s", why);
   Plan plan;
   const int32_t rc = plan_of(*attention, nullptr, &plan, error);
   if (rc == VECOPS_STATUS_OK) *bytes = plan.total;
@@ -225,6 +437,20 @@ int32_t vecops_b200_sdpa_run(const VecopsB200Attention* attention, VecopsError* 
   if (attention == nullptr || attention->struct_size < sizeof(VecopsB200Attention))
     return set_error(error, VECOPS_STATUS_ABI_MISMATCH, "attention record is null or too small");
   const DeviceRestore restore;  // the heads below switch to the record's device; the caller gets its own back
+  const uint32_t strategy = strategy_of(*attention);
+  if (strategy > VECOPS_B200_SDPA_STREAMING) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "sdpa: unknown strategy %u", strategy);
+  if (strategy != VECOPS_B200_SDPA_MATERIALIZED) {
+    const char* why = nullptr;
+    if (stream_applicable(*attention, &why)) {
+      if (attention->out_dtype != VECOPS_DTYPE_F32 && attention->out_dtype != VECOPS_DTYPE_BF16)
+        return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "sdpa serves bf16 q, k, v with an f32 or bf16 output");
+      if (attention->causal > 2) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "sdpa: causal is 0 (none), 1 (top left) or 2 (bottom right)");
+      if (attention->dv == 0) return VECOPS_STATUS_OK;
+      return sdpa_run_streaming(*attention, error);  // all heads in one launch
+    }
+    if (strategy == VECOPS_B200_SDPA_STREAMING)
+      return set_error(error, VECOPS_STATUS_NOT_APPLICABLE, "sdpa: the streaming strategy cannot serve this call: %s", why);
+  }
   if (attention->heads <= 1) return sdpa_run_one(*attention, error);
   // one head after the other on the stream, sharing the scratch; only the last one synchronises (when the caller wants that)
   for (int64_t h = 0; h < attention->heads; ++h) {

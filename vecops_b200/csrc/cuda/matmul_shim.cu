@@ -24,6 +24,7 @@
 #include "w8_small_m.cuh"
 #include "w8_stream.cuh"
 #include "w8_tcgen05.cuh"
+#include "shim_device.h"
 #include "shim_util.h"
 
 namespace vb200 {
@@ -1168,6 +1169,38 @@ int32_t launch_f32(const VecopsB200Matmul& p, cudaStream_t stream, VecopsError* 
 }
 
 }  // namespace
+
+int32_t shim_encode_map(CUtensorMap* out, CUtensorMapDataType dtype, uint32_t rank, const void* base, const uint64_t* dims,
+                        const uint64_t* strides_bytes, const uint32_t* box, VecopsError* error) {
+  if (rank < 2 || rank > 3) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "tensor map rank %u not served", rank);
+  if (g_encode_tiled == nullptr) return set_error(error, VECOPS_STATUS_LOAD_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t d[3] = {dims[0], dims[1], rank > 2 ? dims[2] : 1};
+  cuuint64_t s[2] = {strides_bytes[0], rank > 2 ? strides_bytes[1] : 0};
+  cuuint32_t b[3] = {box[0], box[1], rank > 2 ? box[2] : 1};
+  cuuint32_t e[3] = {1, 1, 1};
+  const CUresult result = g_encode_tiled(out, dtype, rank, const_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (result != CUDA_SUCCESS)
+    return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "cuTensorMapEncodeTiled failed (%d) for dims=(%llu,%llu,%llu) strides=(%llu,%llu)",
+                     static_cast<int>(result), (unsigned long long)d[0], (unsigned long long)d[1], (unsigned long long)d[2],
+                     (unsigned long long)s[0], (unsigned long long)s[1]);
+  return VECOPS_STATUS_OK;
+}
+
+int32_t shim_device_facts(int device, int* sm_count, int* major, uint32_t** status_word, VecopsError* error) {
+  const DeviceState* dev = nullptr;
+  const int32_t rc = device_state(device, &dev, error);
+  if (rc != VECOPS_STATUS_OK) return rc;
+  if (sm_count != nullptr) *sm_count = dev->prop.multiProcessorCount;
+  if (major != nullptr) *major = dev->prop.major;
+  if (status_word != nullptr) *status_word = status_word_of(device);
+  return VECOPS_STATUS_OK;
+}
+
+uint64_t shim_nonce(const void* salt) { return fresh_nonce(salt); }
+
+uint32_t shim_take_status(int device) { return take_status_word(device); }
+
 }  // namespace vb200
 
 using namespace vb200;

@@ -202,13 +202,15 @@ def pack_operand(view, dtype=None, operand: int = 1, zero_point: int | None = No
 
 
 def sdpa_record(q, k, v, out, scale: float, query_mask=None, key_mask=None, keep_mask=None, bias=None, causal: int = 0, stream=None,
-                asynchronous: bool = False) -> capi.VecopsB200Attention:
+                asynchronous: bool = False, strategy: int = 0) -> capi.VecopsB200Attention:
     """Describe scaled dot-product attention: q [Lq,Dqk], k [Lkv,Dqk], v [Lkv,Dv] bf16, out [Lq,Dv] f32 or bf16; masks
     uint8 / bool tensors (non-zero keeps), bias float32 [Lq,Lkv].  With a leading head axis on q, k, v and out (and
-    optionally on the masks and the bias) the heads run one after the other; `.expand`ed views share an operand."""
+    optionally on the masks and the bias) all heads are served by the call; `.expand`ed views share an operand.
+    `strategy`: capi.SDPA_AUTOMATIC (streaming kernel when it can serve the call), SDPA_MATERIALIZED or SDPA_STREAMING."""
     a = capi.VecopsB200Attention()
     a.struct_size = ctypes.sizeof(capi.VecopsB200Attention)
     a.causal = causal
+    a.strategy = strategy
     if q.dim() == 3:  # [heads, L, D]; expanded views (head stride 0) share an operand between heads
         a.heads = out.shape[0]
         a.q_stride_head, a.k_stride_head, a.v_stride_head, a.out_stride_head = q.stride(0), k.stride(0), v.stride(0), out.stride(0)
@@ -245,7 +247,7 @@ def sdpa_record(q, k, v, out, scale: float, query_mask=None, key_mask=None, keep
 
 
 def sdpa(q, k, v, out, scale: float, **kwargs) -> None:
-    """Run one head of attention on the GPU through the C ABI (two products through the matmul path around a row softmax)."""
+    """Run attention on the GPU through the C ABI (the streaming kernel, or two products through the matmul path around a row softmax)."""
     import torch
     kwargs.setdefault("stream", torch.cuda.current_stream(out.device) if out.is_cuda else None)
     record = sdpa_record(q, k, v, out, scale, **kwargs)
