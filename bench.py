@@ -401,54 +401,58 @@ def measure_pack(dev, peaks) -> dict:
             "timing": "a CUDA graph of 12 launches (three source/destination sets in rotation), 20 warm-up replays, 5 timed", "cases": out}
 
 
-def measure_sdpa(dev, port) -> dict:
-    """The caller one step up: one head of attention, Lq = Lkv = 4096, D = 128, bottom-right causal, bf16 in and out - two
-    products through the matmul path around a row softmax (not a fused attention kernel: the scores make a round trip)."""
+def measure_sdpa_case(dev, port, heads: int, length: int, d: int, strategy: int, sets: int, own_scratch: bool) -> dict:
+    """Attention over `heads` heads of Lq = Lkv = `length`, head dim `d`, bottom-right causal, bf16 in and out, through
+    vecops_b200_sdpa_run with the given strategy.  All launches of all timed steps are ONE CUDA graph (the host's launch rate
+    is not what gets measured); `sets` operand sets are taken in turn so that no step finds its operands in the 126 MB L2."""
     import torch
     from oracle.checker import bf16_bits_to_f32, rel_frobenius
     from vecops_b200 import capi, harness
-    length, d = 4096, 128
     rng = np.random.default_rng(9)
-    host = [workloads_bf16(rng.standard_normal((length, d)).astype(np.float32)) for _ in range(3)]
-    q, k, v = (torch.from_numpy(x).to(dev).view(torch.bfloat16) for x in host)
-    out = torch.empty((length, d), dtype=torch.bfloat16, device=dev)
+    scale = 1.0 / np.sqrt(d)
+    host = [workloads_bf16(rng.standard_normal((heads, length, d)).astype(np.float32)) for _ in range(3)]
     stream = torch.cuda.current_stream(dev)
-    record = harness.sdpa_record(q, k, v, out, 1.0 / np.sqrt(d), causal=capi.CAUSAL_BOTTOM_RIGHT, stream=stream, asynchronous=True)
-    need = ctypes.c_uint64(0)
     error = capi.ErrorBuffer()
-    error.raise_for(capi.library().vecops_b200_sdpa_workspace(byref(record), byref(need), byref(error.record)))
-    scratch = torch.empty(need.value + 256, dtype=torch.uint8, device=dev)
-    record.workspace, record.workspace_size = scratch.data_ptr() + (-scratch.data_ptr()) % 256, need.value
-    run = lambda: error.raise_for(capi.library().vecops_b200_sdpa_run(byref(record), byref(error.record)))  # noqa: E731
+    records, keep_alive = [], []
+    need = ctypes.c_uint64(0)
+    shared = None
+    for index in range(sets):
+        q, k, v = (torch.from_numpy(x).to(dev).view(torch.bfloat16) for x in host)
+        out = torch.empty((heads, length, d), dtype=torch.bfloat16, device=dev)
+        record = harness.sdpa_record(q, k, v, out, scale, causal=capi.CAUSAL_BOTTOM_RIGHT, stream=stream, asynchronous=True, strategy=strategy)
+        error.raise_for(capi.library().vecops_b200_sdpa_workspace(byref(record), byref(need), byref(error.record)))
+        if own_scratch or shared is None:
+            shared = torch.empty(need.value + 256, dtype=torch.uint8, device=dev)
+        record.workspace, record.workspace_size = shared.data_ptr() + (-shared.data_ptr()) % 256, need.value
+        records.append(record)
+        keep_alive.append((q, k, v, out, shared))
+    run = lambda r: error.raise_for(capi.library().vecops_b200_sdpa_run(byref(r), byref(error.record)))  # noqa: E731
     before = capi.library().vecops_b200_launch_count()
-    run()
+    run(records[0])
     launches = capi.library().vecops_b200_launch_count() - before
     torch.cuda.synchronize()
+    chosen, tiles = harness.sdpa_plan(records[0])
     pick = np.unique(np.linspace(0, length - 1, 8).astype(np.int64))
     keep = (np.arange(length)[None, :] <= pick[:, None]).astype(np.uint8)
-    want = port.sdpa_bf16(host[0][pick], host[1], host[2], 1.0 / np.sqrt(d), keep_mask=keep, out_bf16=True)
-    got = out[torch.from_numpy(pick).to(dev)].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
-    # timed like every other short kernel: all launches of all timed steps in ONE CUDA graph, so that the host's
-    # launch rate (four launches per step through Python) is not what gets measured
-    count = 50
+    last = heads - 1
+    if chosen == capi.SDPA_STREAMING:  # held to the restatement of ITS strategy, keys cut into chunks as the launch cuts them
+        want = port.sdpa_bf16_streaming(host[0][last][pick], host[1][last], host[2][last], scale, keep_mask=keep, out_bf16=True, chunk_blocks=tiles)
+    else:
+        want = port.sdpa_bf16(host[0][last][pick], host[1][last], host[2][last], scale, keep_mask=keep, out_bf16=True)
+    got = keep_alive[0][3][last][torch.from_numpy(pick).to(dev)].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    count = max(sets, 24 // max(1, heads // 8) if heads > 1 else 48)
     side = torch.cuda.Stream(dev)
-    record.stream = side.cuda_stream
-    # a second head with its own operands, result and scratch, taken in turn with the first: 2 x 105 MB of scores,
-    # probabilities and operands, more than the 126 MB L2 holds
-    q2, k2, v2 = q.clone(), k.clone(), v.clone()
-    out2, scratch2 = torch.empty_like(out), torch.empty_like(scratch)
-    other = harness.sdpa_record(q2, k2, v2, out2, 1.0 / np.sqrt(d), causal=capi.CAUSAL_BOTTOM_RIGHT, stream=side, asynchronous=True)
-    other.workspace, other.workspace_size = scratch2.data_ptr() + (-scratch2.data_ptr()) % 256, need.value
-    run_other = lambda: error.raise_for(capi.library().vecops_b200_sdpa_run(byref(other), byref(error.record)))  # noqa: E731
+    for record in records:
+        record.stream = side.cuda_stream
     side.wait_stream(stream)
     with torch.cuda.stream(side):
-        run()  # one-time set-up outside the capture
-        run_other()
+        for record in records:  # one-time set-up outside the capture
+            run(record)
         side.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=side):
             for i in range(count):
-                (run if i % 2 == 0 else run_other)()
+                run(records[i % sets])
         graph.replay()  # warm-up
         side.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -458,12 +462,30 @@ def measure_sdpa(dev, port) -> dict:
         side.synchronize()
     stream.wait_stream(side)
     ms = e0.elapsed_time(e1) / count
-    flops = 4.0 * length * length * d  # both products, dense (the causal half is computed and masked)
-    return {"workload": "attention, one head, Lq=Lkv=4096, D=128, bottom-right causal, bf16", "ms_per_step": ms, "launches_per_step": int(launches),
-            "launch": f"one CUDA graph of {count} steps, CUDA events around its replay", "l2": "two heads with their own operands and scratch in turn (2 x 105 MB) vs L2 126 MB",
-            "dense_tflops": flops / (ms * 1e-3) / 1e12, "scratch_mb": need.value / 1e6,
-            "note": "materialized strategy as in the reference: scores (67 MB f32) and probabilities (34 MB bf16) pass through device memory",
+    dense = 4.0 * heads * length * length * d  # both products over the whole square
+    needed = dense * (length + 1) / (2.0 * length)  # what the causal cut leaves
+    names = {capi.SDPA_MATERIALIZED: "materialized", capi.SDPA_STREAMING: "streaming"}
+    operand_mb = 4 * heads * length * d * 2 / 1e6
+    return {"strategy": names[chosen], "heads": heads, "ms_per_step": ms, "launches_per_step": int(launches),
+            "tiles_per_work_item": int(tiles), "dense_tflops": dense / (ms * 1e-3) / 1e12, "causal_tflops": needed / (ms * 1e-3) / 1e12,
+            "scratch_mb": need.value / 1e6,
+            "l2": f"{sets} operand sets of {operand_mb:.1f} MB" + (f" with {need.value / 1e6:.0f} MB of scratch each" if own_scratch else "") + " in turn vs L2 126 MB",
+            "launch": f"one CUDA graph of {count} steps, CUDA events around its replay",
             "parity": {"rows": len(pick), "rel_fro": rel_frobenius(bf16_bits_to_f32(got), bf16_bits_to_f32(want))}, "device_status": take_status(dev.index or 0)}
+
+
+def measure_sdpa(dev, port) -> dict:
+    """The caller one step up: attention at Lq = Lkv = 4096, D = 128, bottom-right causal, bf16 - one head by both of the
+    reference's strategies (streaming: one kernel, nothing of size Lq x Lkv in memory; materialized: two products
+    through the matmul path around a row softmax, scores making a round trip), and 32 heads by the streaming one."""
+    from vecops_b200 import capi
+    one = measure_sdpa_case(dev, port, 1, 4096, 128, capi.SDPA_AUTOMATIC, sets=48, own_scratch=False)
+    old = measure_sdpa_case(dev, port, 1, 4096, 128, capi.SDPA_MATERIALIZED, sets=2, own_scratch=True)
+    many = measure_sdpa_case(dev, port, 32, 4096, 128, capi.SDPA_AUTOMATIC, sets=2, own_scratch=False)
+    return {"workload": "attention, one head, Lq=Lkv=4096, D=128, bottom-right causal, bf16", **one,
+            "materialized": old, "heads_32": many,
+            "note": "automatic takes the streaming kernel; `materialized` is the same call forced onto the composition through "
+                    "the matmul path (scores 67 MB f32 and probabilities 34 MB bf16 pass through device memory)"}
 
 
 def workloads_bf16(values):

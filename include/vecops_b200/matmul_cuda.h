@@ -381,6 +381,12 @@ typedef struct VecopsB200Attention {
 
 VECOPS_B200_EXPORT int32_t vecops_b200_sdpa_workspace(const VecopsB200Attention* attention, uint64_t* bytes, VecopsError* error);
 VECOPS_B200_EXPORT int32_t vecops_b200_sdpa_run(const VecopsB200Attention* attention, VecopsError* error);
+/* Pure host logic: which strategy the run takes for this record (MATERIALIZED or STREAMING) and, for streaming, how many
+ * 128-key tiles one work item walks (a query block whose keys span more tiles is cut into chunks that different SMs
+ * handle and merge; the cut changes at which running maximum probabilities are rounded to bf16, so a restatement that
+ * is to agree beyond 1e-3 needs it).  With workspace_size = 0 the plan is the one the workspace query sized. */
+VECOPS_B200_EXPORT int32_t vecops_b200_sdpa_plan(const VecopsB200Attention* attention, uint32_t* strategy, uint32_t* tiles_per_item,
+                                                 VecopsError* error);
 
 /* Strided gather of column slabs: dst[M, ldd] columns [col0, col0+cols) <-
  * src[M, cols] (row pitch lds), `elem_size` bytes per element.  Used after the

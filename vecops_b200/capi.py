@@ -173,6 +173,7 @@ def library() -> ctypes.CDLL:
         lib.vecops_b200_matmul_pack_b_compensated.argtypes = [POINTER(VecopsB200Pack), c_int32, c_void_p, e]
         lib.vecops_b200_sdpa_workspace.argtypes = [POINTER(VecopsB200Attention), POINTER(c_uint64), e]
         lib.vecops_b200_sdpa_run.argtypes = [POINTER(VecopsB200Attention), e]
+        lib.vecops_b200_sdpa_plan.argtypes = [POINTER(VecopsB200Attention), POINTER(c_uint32), POINTER(c_uint32), e]
         lib.vecops_b200_matmul_allgather_run.argtypes = [POINTER(VecopsB200Matmul), POINTER(VecopsB200Gather), e]
         lib.vecops_b200_kernel_name.argtypes = [c_uint32]
         lib.vecops_b200_kernel_name.restype = c_char_p

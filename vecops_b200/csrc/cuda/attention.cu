@@ -220,9 +220,11 @@ int32_t plan_of(const VecopsB200Attention& a, char* base, Plan* out, VecopsError
 
 struct StreamPlan {
   int q_blocks = 0, tiles_per_chunk = 1, max_chunks = 1;
+  int uniform_chunks = 0;     // chunks per query block when every block has the same number, else 0
+  int64_t items_per_head = 0; // work items (query block x chunk) of one head
   int value_slabs = 1;  // transposed copies of V: one per head, or one for all when the heads share V
   int64_t pitch = 0;    // elements per row of a transposed V
-  uint64_t slab_bytes = 0, partials_at = 0, counters_at = 0, total = 0;
+  uint64_t slab_bytes = 0, partials_at = 0, total = 0;
 };
 
 uint32_t strategy_of(const VecopsB200Attention& a) {
@@ -245,7 +247,7 @@ bool stream_applicable(const VecopsB200Attention& a, const char** why) {
   if (a.qkv_dtype != VECOPS_DTYPE_BF16) reason = "q, k, v must be bf16";
   else if (a.lq < 1 || a.lkv < 1) reason = "no queries or no keys";
   else if (a.dqk < 1 || a.dqk > SdpaStream::kMaxHeadDim || a.dv < 1 || a.dv > SdpaStream::kMaxHeadDim) reason = "head dims must be 1..128";
-  else if (heads > 65535 || (a.lq + SdpaStream::kBlockQ - 1) / SdpaStream::kBlockQ > 65535) reason = "too many heads or query blocks for one grid";
+  else if (heads > 65535 || (a.lq + SdpaStream::kBlockQ - 1) / SdpaStream::kBlockQ > (1 << 20)) reason = "too many heads or query blocks for one grid";
   else if (!tma_addressable(a.q, a.q_stride_row, a.q_stride_col, a.q_stride_head, heads)) reason = "q is not K-contiguous on 16-byte aligned rows";
   else if (!tma_addressable(a.k, a.k_stride_row, a.k_stride_col, a.k_stride_head, heads)) reason = "k is not K-contiguous on 16-byte aligned rows";
   if (why != nullptr) *why = reason;
@@ -264,12 +266,15 @@ int32_t plan_stream(const VecopsB200Attention& a, int sms, uint64_t scratch_limi
   p.slab_bytes = round_up(packed_bytes, 256);
   // 128-key tiles per query block after the causal cut, over all heads
   const int64_t shift = a.causal == 2 ? a.lkv - a.lq : 0;
-  int64_t total_tiles = 0, most = 0;
-  for (int b = 0; b < p.q_blocks; ++b) {
+  auto tiles_of = [&](int b) {
     const int64_t last_row = (b + 1 < p.q_blocks ? static_cast<int64_t>(b + 1) * G::kBlockQ : a.lq) - 1;
     int64_t last_key = a.causal != 0 ? last_row + shift : a.lkv - 1;
     if (last_key > a.lkv - 1) last_key = a.lkv - 1;
-    const int64_t tiles = last_key < 0 ? 0 : last_key / G::kBlockKv + 1;
+    return last_key < 0 ? int64_t{0} : last_key / G::kBlockKv + 1;
+  };
+  int64_t total_tiles = 0, most = 0;
+  for (int b = 0; b < p.q_blocks; ++b) {
+    const int64_t tiles = tiles_of(b);
     total_tiles += tiles;
     if (tiles > most) most = tiles;
   }
@@ -289,11 +294,19 @@ int32_t plan_stream(const VecopsB200Attention& a, int sms, uint64_t scratch_limi
   auto layout = [&](int64_t chunk_tiles) {
     p.tiles_per_chunk = static_cast<int>(chunk_tiles);
     p.max_chunks = most > 0 ? static_cast<int>((most + chunk_tiles - 1) / chunk_tiles) : 1;
+    p.items_per_head = 0;
+    int64_t fewest = p.max_chunks;
+    for (int b = 0; b < p.q_blocks; ++b) {
+      const int64_t tiles = tiles_of(b);
+      const int64_t chunks = tiles > 0 ? (tiles + chunk_tiles - 1) / chunk_tiles : 1;
+      p.items_per_head += chunks;
+      if (chunks < fewest) fewest = chunks;
+    }
+    p.uniform_chunks = fewest == p.max_chunks ? p.max_chunks : 0;
     p.partials_at = p.slab_bytes * p.value_slabs;
     const uint64_t partial_bytes =
         p.max_chunks > 1 ? static_cast<uint64_t>(heads) * p.q_blocks * p.max_chunks * G::kPartialFloats * sizeof(float) : 0;
-    p.counters_at = p.partials_at + partial_bytes;
-    p.total = p.counters_at + (p.max_chunks > 1 ? round_up(static_cast<uint64_t>(heads) * p.q_blocks * 8, 256) : 0);
+    p.total = p.partials_at + partial_bytes;
   };
   layout(per_chunk);
   // a caller whose scratch was sized for another SM count still runs: uncut blocks need no partial records
@@ -367,6 +380,7 @@ int32_t sdpa_run_streaming(const VecopsB200Attention& a, VecopsError* error) {
   p.lq = static_cast<int>(a.lq), p.lkv = static_cast<int>(a.lkv), p.dqk = static_cast<int>(a.dqk), p.dv = static_cast<int>(a.dv);
   p.causal = static_cast<int>(a.causal);
   p.tiles_per_chunk = plan.tiles_per_chunk;
+  p.q_blocks = plan.q_blocks, p.max_chunks = plan.max_chunks, p.uniform_chunks = plan.uniform_chunks;
   p.q_head = q_per_head ? 1 : 0, p.k_head = k_per_head ? 1 : 0, p.v_head = plan.value_slabs > 1 ? 1 : 0;
   p.scale = a.scale;
   p.out = a.out, p.out_sr = a.out_stride_row, p.out_sc = a.out_stride_col, p.out_sh = heads > 1 ? a.out_stride_head : 0;
@@ -376,23 +390,42 @@ int32_t sdpa_run_streaming(const VecopsB200Attention& a, VecopsError* error) {
   p.keep_mask = a.keep_mask, p.keep_sr = a.keep_stride_row, p.keep_sc = a.keep_stride_col, p.keep_sh = heads > 1 ? a.keep_stride_head : 0;
   p.bias = a.bias, p.bias_sr = a.bias_stride_row, p.bias_sc = a.bias_stride_col, p.bias_sh = heads > 1 ? a.bias_stride_head : 0;
   p.partials = reinterpret_cast<float*>(base + plan.partials_at);
-  p.counters = reinterpret_cast<unsigned long long*>(base + plan.counters_at);
-  p.nonce = static_cast<uint32_t>(shim_nonce(a.workspace)) | 1u;
   p.status = status_word;
+  p.trace = shim_trace();
 
   const bool plain = a.key_mask == nullptr && a.keep_mask == nullptr && a.bias == nullptr;
-  auto kernel = plain ? &sdpa_stream_kernel<true> : &sdpa_stream_kernel<false>;
-  static std::atomic<bool> raised[2][64];
-  if (device < 0 || device >= 64 || !raised[plain][device].load()) {
+  // (the timeline variant is its own instantiation: its bookkeeping costs registers the plain one needs)
+  auto kernel = p.trace != nullptr ? (plain ? &sdpa_stream_kernel<true, true> : &sdpa_stream_kernel<false, true>)
+                                   : (plain ? &sdpa_stream_kernel<true, false> : &sdpa_stream_kernel<false, false>);
+  static std::atomic<bool> raised[4][64];
+  const int variant = (plain ? 1 : 0) + (p.trace != nullptr ? 2 : 0);
+  if (device < 0 || device >= 64 || !raised[variant][device].load()) {
     const cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::kSmemBytes);
     if (status != cudaSuccess) return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "cudaFuncSetAttribute(sdpa_stream): %s", cudaGetErrorString(status));
-    if (device >= 0 && device < 64) raised[plain][device].store(true);
+    if (device >= 0 && device < 64) raised[variant][device].store(true);
   }
-  const dim3 grid(static_cast<unsigned>(plan.max_chunks), static_cast<unsigned>(plan.q_blocks), static_cast<unsigned>(heads));
+  const dim3 grid(static_cast<unsigned>(plan.items_per_head), static_cast<unsigned>(heads), 1);
   kernel<<<grid, G::kThreads, G::kSmemBytes, stream>>>(map_q, map_k, map_vt, p);
   g_launches.fetch_add(1);
   cudaError_t status = cudaGetLastError();
   if (status != cudaSuccess) return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "sdpa_stream launch: %s", cudaGetErrorString(status));
+  if (plan.max_chunks > 1) {
+    // the chunks of the blocks that were cut meet here: launched as a programmatic dependent, so its CTAs are resident
+    // when the last work item finishes
+    cudaLaunchConfig_t config = {};
+    cudaLaunchAttribute attribute[1] = {};
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.gridDim = dim3(static_cast<unsigned>(plan.q_blocks) * 4, static_cast<unsigned>(heads), 1);
+    config.blockDim = dim3(kMergeThreads);
+    config.stream = stream;
+    config.attrs = attribute;
+    const char* pdl = getenv("VECOPS_B200_GEMM_PDL");  // =0: an ordinary launch behind the kernel that writes the records
+    config.numAttrs = (pdl != nullptr && pdl[0] == '0') ? 0 : 1;
+    status = cudaLaunchKernelEx(&config, sdpa_merge_kernel, p);
+    g_launches.fetch_add(1);
+    if (status != cudaSuccess) return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "sdpa_merge launch: %s", cudaGetErrorString(status));
+  }
   if ((a.flags & VECOPS_B200_MATMUL_FLAG_ASYNC) == 0) {
     status = cudaStreamSynchronize(stream);
     if (status != cudaSuccess) return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "cudaStreamSynchronize: %s", cudaGetErrorString(status));
@@ -432,6 +465,32 @@ int32_t vecops_b200_sdpa_workspace(const VecopsB200Attention* attention, uint64_
 }
 
 static int32_t sdpa_run_one(const VecopsB200Attention& a, VecopsError* error);
+
+int32_t vecops_b200_sdpa_plan(const VecopsB200Attention* attention, uint32_t* strategy, uint32_t* tiles_per_item, VecopsError* error) {
+  if (attention == nullptr || attention->struct_size < sizeof(VecopsB200Attention) || strategy == nullptr || tiles_per_item == nullptr)
+    return set_error(error, VECOPS_STATUS_ABI_MISMATCH, "attention record is null or too small, or no output pointer");
+  const uint32_t asked = strategy_of(*attention);
+  if (asked > VECOPS_B200_SDPA_STREAMING) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "sdpa: unknown strategy %u", asked);
+  const char* why = nullptr;
+  *tiles_per_item = 0;
+  if (asked != VECOPS_B200_SDPA_MATERIALIZED && stream_applicable(*attention, &why)) {
+    int sms = 148, device = attention->device_index;
+    if (vecops_b200_device_count() > 0 && (device >= 0 || cudaGetDevice(&device) == cudaSuccess)) {
+      int count = 0;
+      if (shim_device_facts(device, &count, nullptr, nullptr, nullptr) == VECOPS_STATUS_OK && count > 0) sms = count;
+    }
+    StreamPlan stream;
+    const int32_t rc = plan_stream(*attention, sms, attention->workspace_size, &stream, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+    *strategy = VECOPS_B200_SDPA_STREAMING;
+    *tiles_per_item = static_cast<uint32_t>(stream.tiles_per_chunk);
+    return VECOPS_STATUS_OK;
+  }
+  if (asked == VECOPS_B200_SDPA_STREAMING)
+    return set_error(error, VECOPS_STATUS_NOT_APPLICABLE, "sdpa: the streaming strategy cannot serve this call: %s", why);
+  *strategy = VECOPS_B200_SDPA_MATERIALIZED;
+  return VECOPS_STATUS_OK;
+}
 
 int32_t vecops_b200_sdpa_run(const VecopsB200Attention* attention, VecopsError* error) {
   if (attention == nullptr || attention->struct_size < sizeof(VecopsB200Attention))

@@ -1201,6 +1201,8 @@ uint64_t shim_nonce(const void* salt) { return fresh_nonce(salt); }
 
 uint32_t shim_take_status(int device) { return take_status_word(device); }
 
+unsigned long long* shim_trace() { return g_trace; }
+
 }  // namespace vb200
 
 using namespace vb200;

@@ -23,4 +23,7 @@ uint64_t shim_nonce(const void* salt);
 // Reads and clears the device's status word (0 = no bounded wait ran out since the last read).
 uint32_t shim_take_status(int device);
 
+// The device buffer kernels write their optional timelines to (a tuning aid; null unless one was registered).
+unsigned long long* shim_trace();
+
 }  // namespace vb200

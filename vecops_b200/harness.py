@@ -246,6 +246,14 @@ def sdpa_record(q, k, v, out, scale: float, query_mask=None, key_mask=None, keep
     return a
 
 
+def sdpa_plan(record: capi.VecopsB200Attention) -> tuple[int, int]:
+    """(strategy, 128-key tiles per work item) the library takes for the record; pure host logic."""
+    strategy, tiles = ctypes.c_uint32(0), ctypes.c_uint32(0)
+    error = capi.ErrorBuffer()
+    error.raise_for(capi.library().vecops_b200_sdpa_plan(byref(record), byref(strategy), byref(tiles), byref(error.record)))
+    return strategy.value, tiles.value
+
+
 def sdpa(q, k, v, out, scale: float, **kwargs) -> None:
     """Run attention on the GPU through the C ABI (the streaming kernel, or two products through the matmul path around a row softmax)."""
     import torch
