@@ -1166,9 +1166,16 @@ def test_sdpa_degenerate_extents_and_refusals():
     harness.sdpa(q[:0], q, q, out[:0], 1.0)  # no query: nothing to write
     with pytest.raises(capi.VecopsB200Error):
         harness.sdpa(q.float(), q.float(), q.float(), out, 1.0)  # fp32 q, k, v are not served
-    record = harness.sdpa_record(q, q, q, out, 1.0)
+    record = harness.sdpa_record(q, q, q, out, 1.0, strategy=capi.SDPA_MATERIALIZED)
     error = capi.ErrorBuffer()
     assert capi.library().vecops_b200_sdpa_run(byref(record), byref(error.record)) == capi.INVALID_ARGUMENT  # no scratch given
+    # the streaming kernel needs scratch only where it cuts a query block's keys into chunks, and does not cut without it
+    k = torch.randn((1024, 8), device="cuda").to(torch.bfloat16)
+    record = harness.sdpa_record(q, k, k, out, 1.0, strategy=capi.SDPA_STREAMING)
+    assert harness.sdpa_plan(record) == (capi.SDPA_STREAMING, 1)
+    assert capi.library().vecops_b200_sdpa_run(byref(record), byref(error.record)) == capi.OK
+    reference = torch.softmax((q.float() @ k.float().t()), dim=1) @ k.float()
+    assert torch.allclose(out, reference, atol=2e-2)
 
 
 def test_sdpa_strategy_choice():
@@ -1179,7 +1186,7 @@ def test_sdpa_strategy_choice():
     out = torch.empty((3, 256, 64), dtype=torch.float32, device="cuda")
     before = _launches()
     harness.sdpa(q, q, q, out, 0.125)
-    assert _launches() - before == 3 + 1 + 1  # V of each head transposed, the attention launch, the merge of the key chunks
+    assert _launches() - before == 1 + 1  # the attention launch for all heads, the merge of the key chunks
     before = _launches()
     harness.sdpa(q, q, q, out, 0.125, strategy=capi.SDPA_MATERIALIZED)
     assert _launches() - before == 3 * 4

@@ -1,8 +1,9 @@
 // Scaled dot-product attention, the caller one step above the matmul path, in vecops' two strategies
 // (include/vecops/ops/details/attention/SDPA.h:21-25):
-//   * streaming: one kernel over all heads (sdpa_stream.cuh) after V has been transposed by the pack kernel; nothing of
-//     size Lq x Lkv exists in device memory.  Taken whenever the operands allow (head dims up to 128, TMA-addressable
-//     Q and K);
+//   * streaming: one kernel over all heads (sdpa_stream.cuh), then - when query blocks were cut into key chunks to fill
+//     the SMs - a small kernel that merges the chunks; nothing of size Lq x Lkv exists in device memory.  Taken
+//     whenever the operands allow (head dims up to 128, TMA-addressable Q and K; a V that TMA cannot address is
+//     re-pitched into scratch first);
 //   * materialized, built the way vecops builds it: two products through the matmul entry points with a row softmax
 //     between them (SDPA.h:305-383); the score matrix makes one round trip through device memory.  Serves the rest.
 //
@@ -222,8 +223,10 @@ struct StreamPlan {
   int q_blocks = 0, tiles_per_chunk = 1, max_chunks = 1;
   int uniform_chunks = 0;     // chunks per query block when every block has the same number, else 0
   int64_t items_per_head = 0; // work items (query block x chunk) of one head
-  int value_slabs = 1;  // transposed copies of V: one per head, or one for all when the heads share V
-  int64_t pitch = 0;    // elements per row of a transposed V
+  // V is read where it lies when TMA can address it; otherwise a re-pitched copy per head (or one, when the heads share
+  // V) is made in scratch first: rows of `pitch` elements, zero past Dv
+  int value_slabs = 0;
+  int64_t pitch = 0;
   uint64_t slab_bytes = 0, partials_at = 0, total = 0;
 };
 
@@ -259,11 +262,13 @@ int32_t plan_stream(const VecopsB200Attention& a, int sms, uint64_t scratch_limi
   StreamPlan p;
   const int64_t heads = a.heads <= 1 ? 1 : a.heads;
   p.q_blocks = static_cast<int>((a.lq + G::kBlockQ - 1) / G::kBlockQ);
-  p.value_slabs = (heads > 1 && a.v_stride_head != 0) ? static_cast<int>(heads) : 1;
-  uint64_t packed_bytes = 0;
-  const int32_t rc = vecops_b200_matmul_packed_layout(VECOPS_DTYPE_BF16, a.dv, a.lkv, &p.pitch, &packed_bytes, error);
-  if (rc != VECOPS_STATUS_OK) return rc;
-  p.slab_bytes = round_up(packed_bytes, 256);
+  if (!tma_addressable(a.v, a.v_stride_row, a.v_stride_col, a.v_stride_head, heads)) {
+    p.value_slabs = (heads > 1 && a.v_stride_head != 0) ? static_cast<int>(heads) : 1;
+    uint64_t packed_bytes = 0;
+    const int32_t rc = vecops_b200_matmul_packed_layout(VECOPS_DTYPE_BF16, a.lkv, a.dv, &p.pitch, &packed_bytes, error);
+    if (rc != VECOPS_STATUS_OK) return rc;
+    p.slab_bytes = round_up(packed_bytes, 256);
+  }
   // 128-key tiles per query block after the causal cut, over all heads
   const int64_t shift = a.causal == 2 ? a.lkv - a.lq : 0;
   auto tiles_of = [&](int b) {
@@ -309,8 +314,8 @@ int32_t plan_stream(const VecopsB200Attention& a, int sms, uint64_t scratch_limi
     p.total = p.partials_at + partial_bytes;
   };
   layout(per_chunk);
-  // a caller whose scratch was sized for another SM count still runs: uncut blocks need no partial records
-  if (scratch_limit != 0 && p.total > scratch_limit) layout(most > 0 ? most : 1);
+  // a caller that brings no scratch, or scratch sized for another SM count, still runs: uncut blocks need no records
+  if (p.total > scratch_limit) layout(most > 0 ? most : 1);
   *out = p;
   return VECOPS_STATUS_OK;
 }
@@ -334,23 +339,22 @@ int32_t sdpa_run_streaming(const VecopsB200Attention& a, VecopsError* error) {
   if (rc != VECOPS_STATUS_OK) return rc;
   if (major != 10) return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "the streaming attention kernel needs an sm_100 device, found sm_%dx", major);
   StreamPlan plan;
-  rc = plan_stream(a, sms, a.workspace_size, &plan, error);
+  rc = plan_stream(a, sms, a.workspace != nullptr && (reinterpret_cast<uintptr_t>(a.workspace) & 255u) == 0 ? a.workspace_size : 0, &plan, error);
   if (rc != VECOPS_STATUS_OK) return rc;
-  if (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & 255u) != 0 || a.workspace_size < plan.total)
+  if (plan.total != 0 && (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & 255u) != 0 || a.workspace_size < plan.total))
     return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "sdpa needs %llu bytes of 256-byte aligned device scratch (vecops_b200_sdpa_workspace)",
                      (unsigned long long)plan.total);
   const int64_t heads = a.heads <= 1 ? 1 : a.heads;
   char* base = static_cast<char*>(a.workspace);
   cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
 
-  // V^T per head (or once): B of the second product is V^T, rows along V's columns, keys contiguous
   for (int slab = 0; slab < plan.value_slabs; ++slab) {
     VecopsB200Pack pack{};
     pack.struct_size = sizeof(VecopsB200Pack);
     pack.operand = 1;
-    pack.rows = a.dv, pack.k = a.lkv;
+    pack.rows = a.lkv, pack.k = a.dv;
     pack.src = static_cast<const char*>(a.v) + static_cast<int64_t>(slab) * a.v_stride_head * 2;
-    pack.src_stride_row = a.v_stride_col, pack.src_stride_k = a.v_stride_row;
+    pack.src_stride_row = a.v_stride_row, pack.src_stride_k = a.v_stride_col;
     pack.src_dtype = pack.dst_dtype = VECOPS_DTYPE_BF16;
     pack.dst = base + plan.slab_bytes * slab;
     pack.dst_size = plan.slab_bytes;
@@ -359,8 +363,7 @@ int32_t sdpa_run_streaming(const VecopsB200Attention& a, VecopsError* error) {
     rc = vecops_b200_matmul_pack(&pack, error);
     if (rc != VECOPS_STATUS_OK) return rc;
   }
-
-  CUtensorMap map_q, map_k, map_vt;
+  CUtensorMap map_q, map_k, map_v;
   auto operand_map = [&](CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t stride_row, int64_t stride_head, bool per_head) {
     const uint64_t dims[3] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows), per_head ? static_cast<uint64_t>(heads) : 1};
     const uint64_t strides[2] = {static_cast<uint64_t>(stride_row) * 2,
@@ -373,7 +376,9 @@ int32_t sdpa_run_streaming(const VecopsB200Attention& a, VecopsError* error) {
   if (rc != VECOPS_STATUS_OK) return rc;
   rc = operand_map(&map_k, a.k, a.lkv, a.dqk, a.k_stride_row, a.k_stride_head, k_per_head);
   if (rc != VECOPS_STATUS_OK) return rc;
-  rc = operand_map(&map_vt, base, a.dv, a.lkv, plan.pitch, static_cast<int64_t>(plan.slab_bytes / 2), plan.value_slabs > 1);
+  const bool v_per_head = heads > 1 && a.v_stride_head != 0;
+  if (plan.value_slabs > 0) rc = operand_map(&map_v, base, a.lkv, a.dv, plan.pitch, static_cast<int64_t>(plan.slab_bytes / 2), v_per_head);
+  else rc = operand_map(&map_v, a.v, a.lkv, a.dv, a.v_stride_row, a.v_stride_head, v_per_head);
   if (rc != VECOPS_STATUS_OK) return rc;
 
   SdpaStreamParams p{};
@@ -381,7 +386,7 @@ int32_t sdpa_run_streaming(const VecopsB200Attention& a, VecopsError* error) {
   p.causal = static_cast<int>(a.causal);
   p.tiles_per_chunk = plan.tiles_per_chunk;
   p.q_blocks = plan.q_blocks, p.max_chunks = plan.max_chunks, p.uniform_chunks = plan.uniform_chunks;
-  p.q_head = q_per_head ? 1 : 0, p.k_head = k_per_head ? 1 : 0, p.v_head = plan.value_slabs > 1 ? 1 : 0;
+  p.q_head = q_per_head ? 1 : 0, p.k_head = k_per_head ? 1 : 0, p.v_head = v_per_head ? 1 : 0;
   p.scale = a.scale;
   p.out = a.out, p.out_sr = a.out_stride_row, p.out_sc = a.out_stride_col, p.out_sh = heads > 1 ? a.out_stride_head : 0;
   p.out_bf16 = a.out_dtype == VECOPS_DTYPE_BF16 ? 1 : 0;
@@ -405,7 +410,7 @@ int32_t sdpa_run_streaming(const VecopsB200Attention& a, VecopsError* error) {
     if (device >= 0 && device < 64) raised[variant][device].store(true);
   }
   const dim3 grid(static_cast<unsigned>(plan.items_per_head), static_cast<unsigned>(heads), 1);
-  kernel<<<grid, G::kThreads, G::kSmemBytes, stream>>>(map_q, map_k, map_vt, p);
+  kernel<<<grid, G::kThreads, G::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
   g_launches.fetch_add(1);
   cudaError_t status = cudaGetLastError();
   if (status != cudaSuccess) return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "sdpa_stream launch: %s", cudaGetErrorString(status));
@@ -453,7 +458,7 @@ int32_t vecops_b200_sdpa_workspace(const VecopsB200Attention* attention, uint64_
       if (shim_device_facts(device, &asked, nullptr, nullptr, nullptr) == VECOPS_STATUS_OK && asked > 0) sms = asked;
     }
     StreamPlan stream;
-    const int32_t rc = plan_stream(*attention, sms, 0, &stream, error);
+    const int32_t rc = plan_stream(*attention, sms, UINT64_MAX, &stream, error);
     if (rc == VECOPS_STATUS_OK) *bytes = stream.total;
     return rc;
   }
@@ -480,7 +485,7 @@ int32_t vecops_b200_sdpa_plan(const VecopsB200Attention* attention, uint32_t* st
       if (shim_device_facts(device, &count, nullptr, nullptr, nullptr) == VECOPS_STATUS_OK && count > 0) sms = count;
     }
     StreamPlan stream;
-    const int32_t rc = plan_stream(*attention, sms, attention->workspace_size, &stream, error);
+    const int32_t rc = plan_stream(*attention, sms, attention->workspace_size != 0 ? attention->workspace_size : UINT64_MAX, &stream, error);
     if (rc != VECOPS_STATUS_OK) return rc;
     *strategy = VECOPS_B200_SDPA_STREAMING;
     *tiles_per_item = static_cast<uint32_t>(stream.tiles_per_chunk);

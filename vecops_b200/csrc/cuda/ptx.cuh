@@ -436,6 +436,20 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr) {
   return desc;
 }
 
+// The same for an MN-major operand under the 128-byte swizzle: rows of 128 bytes hold 64 consecutive elements along M
+// (or N) for one k, eight consecutive k make a 1024-byte swizzle atom.  `k_group_bytes` is the distance between groups
+// of eight k (stride byte offset), `mn_group_bytes` the distance between groups of 64 elements along M/N (leading byte
+// offset).  This is how a row-major [K, N] tile that TMA loaded as boxes of 64 columns lies in shared memory.
+__device__ __forceinline__ uint64_t umma_smem_desc_sw128_mn(uint32_t smem_addr, uint32_t mn_group_bytes, uint32_t k_group_bytes) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);
+  desc |= static_cast<uint64_t>((mn_group_bytes >> 4) & 0x3fffu) << 16;
+  desc |= static_cast<uint64_t>((k_group_bytes >> 4) & 0x3fffu) << 32;
+  desc |= static_cast<uint64_t>(1) << 46;
+  desc |= static_cast<uint64_t>(2) << 61;
+  return desc;
+}
+
 // Operand element formats of the instruction descriptor.
 enum : uint32_t {
   kUmmaF16 = 0,
@@ -453,8 +467,8 @@ enum : uint32_t {
 // format, [10,13) B format, 15/16 A/B major (0 = K), [17,23) N >> 3,
 // [24,29) M >> 4.
 __host__ __device__ constexpr uint32_t umma_instr_desc(uint32_t acc_format, uint32_t a_format, uint32_t b_format,
-                                                       uint32_t m, uint32_t n) {
-  return (acc_format << 4) | (a_format << 7) | (b_format << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+                                                       uint32_t m, uint32_t n, bool b_mn_major = false) {
+  return (acc_format << 4) | (a_format << 7) | (b_format << 10) | (b_mn_major ? (1u << 16) : 0u) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 }  // namespace vb200

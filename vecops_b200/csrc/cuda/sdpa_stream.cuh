@@ -10,8 +10,8 @@
 //   * a work item is one block of 128 query rows of one head against a chunk of consecutive 128-key tiles; a query
 //     block whose keys are cut into several chunks (few query blocks, many SMs) leaves each chunk's (O, m, l) in device
 //     scratch, and sdpa_merge_kernel, launched behind this one, merges them by the same rule on all SMs at once;
-//   * warp 0 streams K tiles and V^T tiles (V transposed once by the pack kernel: tcgen05 wants both operands
-//     K-contiguous) through TMA into two-stage rings; Q is loaded once;
+//   * warp 0 streams K tiles and V tiles through TMA into two-stage rings; Q is loaded once.  V is used as it lies in
+//     memory, [key][head dim]: the second product takes it as an N-major operand, nothing is transposed;
 //   * warp 1 issues tcgen05.mma: S_j = Q.K_j^T into one of two 128x128 fp32 accumulators in tensor memory, and
 //     O_j = P_j.V_j into one of two more.  S_{j+1} is issued before P_j is needed, so it overlaps the softmax of tile j;
 //     the K ring and the V ring are released separately (K after the scores, V after the product);
@@ -44,7 +44,7 @@ struct SdpaStream {
   static constexpr int kKOffset = kQOffset + kQBytes;
   static constexpr int kKBytes = 2 * kAtomBytes;  // 128 keys x 128 head dims
   static constexpr int kVOffset = kKOffset + kStages * kKBytes;
-  static constexpr int kVBytes = 2 * kAtomBytes;  // 128 head dims x 128 keys (V transposed)
+  static constexpr int kVBytes = 2 * kAtomBytes;  // 128 keys x 128 head dims, as V lies in memory: two boxes of 64 head dims
   static constexpr int kPOffset = kVOffset + kStages * kVBytes;
   static constexpr int kPBytes = 2 * kAtomBytes;  // 128 query rows x 128 keys, one buffer: free again when the product that read it is
   static constexpr int kBarrierOffset = kPOffset + kPBytes;
@@ -104,7 +104,7 @@ __device__ __forceinline__ float exp2_approx(float x) {
 template <bool kPlain, bool kTrace = false>
 __global__ void __launch_bounds__(SdpaStream::kThreads, 1)
 sdpa_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_vt, const SdpaStreamParams p) {
+                   const __grid_constant__ CUtensorMap map_v, const SdpaStreamParams p) {
   using G = SdpaStream;
   // ---------------------------------------------------------------- which work item
   // The grid's x extent counts the work items of one head, query blocks with the most keys first, a block's chunks next
@@ -184,7 +184,7 @@ sdpa_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     mbar_fence_init();
     tma_prefetch_descriptor(&map_q);
     tma_prefetch_descriptor(&map_k);
-    tma_prefetch_descriptor(&map_vt);
+    tma_prefetch_descriptor(&map_v);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), G::kTmemColumns);
@@ -228,8 +228,8 @@ sdpa_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           const int s = v_issued & 1;
           const int key0 = (tile_begin + v_issued) * G::kBlockKv;
           mbar_arrive_expect_tx(v_full + 8 * s, G::kVBytes);
-          tma_load_3d(smem_base + G::kVOffset + s * G::kVBytes, &map_vt, v_full + 8 * s, key0, 0, head * p.v_head);
-          tma_load_3d(smem_base + G::kVOffset + s * G::kVBytes + G::kAtomBytes, &map_vt, v_full + 8 * s, key0 + 64, 0, head * p.v_head);
+          tma_load_3d(smem_base + G::kVOffset + s * G::kVBytes, &map_v, v_full + 8 * s, 0, key0, head * p.v_head);
+          tma_load_3d(smem_base + G::kVOffset + s * G::kVBytes + G::kAtomBytes, &map_v, v_full + 8 * s, 64, key0, head * p.v_head);  // past Dv: zero-filled
           ++v_issued;
           progress = true;
         }
@@ -246,6 +246,7 @@ sdpa_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0 && ntiles > 0) {
       constexpr uint32_t idesc = umma_instr_desc(kUmmaAccF32, kUmmaBF16, kUmmaBF16, 128, 128);
+      constexpr uint32_t idesc_pv = umma_instr_desc(kUmmaAccF32, kUmmaBF16, kUmmaBF16, 128, 128, true);  // B = V, N-major
       const int q_steps = (p.dqk + 15) / 16;  // 16 head dims per instruction; what lies past Dqk is zero in both operands
       bool ok = true;
       // S_i = Q . K_i^T into S[i % 2]
@@ -284,8 +285,9 @@ sdpa_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
         for (int ks = 0; ks < G::kBlockKv / 16; ++ks) {
           const uint64_t a_desc = umma_smem_desc_sw128(smem_base + G::kPOffset + (ks >> 2) * G::kAtomBytes) + 2 * (ks & 3);
-          const uint64_t b_desc = umma_smem_desc_sw128(smem_base + G::kVOffset + s * G::kVBytes + (ks >> 2) * G::kAtomBytes) + 2 * (ks & 3);
-          umma_f16(tmem_base + 256 + s * 128, a_desc, b_desc, idesc, ks > 0 ? 1u : 0u);
+          // V as it lies in memory, [key][head dim]: the N-major operand.  16 keys per instruction = 16 rows of 128 bytes.
+          const uint64_t b_desc = umma_smem_desc_sw128_mn(smem_base + G::kVOffset + s * G::kVBytes + ks * 16 * 128, G::kAtomBytes, 1024);
+          umma_f16(tmem_base + 256 + s * 128, a_desc, b_desc, idesc_pv, ks > 0 ? 1u : 0u);
         }
         umma_commit(o_full + 8 * s);
         umma_commit(v_empty + 8 * s);
