@@ -13,13 +13,14 @@
 //   * warp 0 streams K tiles and V tiles through TMA into two-stage rings; Q is loaded once.  V is used as it lies in
 //     memory, [key][head dim]: the second product takes it as an N-major operand, nothing is transposed;
 //   * warp 1 issues tcgen05.mma: S_j = Q.K_j^T into one of two 128x128 fp32 accumulators in tensor memory, and
-//     O_j = P_j.V_j into one of two more.  S_{j+1} is issued before P_j is needed, so it overlaps the softmax of tile j;
+//     O += P_j.V_j into a third.  S_{j+1} is issued before P_j is needed, so it overlaps the softmax of tile j;
 //     the K ring and the V ring are released separately (K after the scores, V after the product);
 //   * sixteen softmax warps, four threads per query row (row = tensor-memory lane; each takes 32 of the tile's 128 keys and
-//     32 of the output columns): they read S_j once into registers, agree on the row maximum through shared memory, add
-//     alpha * O + O_{j-1} in registers - so no accumulator is ever rescaled in tensor memory - and write P_j as bf16 into
-//     shared memory in the 128-byte-swizzled K-major layout the MMA reads.  Scores are kept in units of log2(e), so a
-//     probability is one subtraction and one ex2.
+//     32 of the output columns): they read S_j once into registers, agree on the row maximum through shared memory and
+//     write P_j as bf16 into shared memory in the 128-byte-swizzled K-major layout the MMA reads.  O accumulates in
+//     tensor memory over all tiles; a warp multiplies its rows of O by alpha there (load, scale, store) only when one of
+//     them got a new maximum - alpha = 1 changes nothing - which for typical scores is the first few tiles.  Scores
+//     are kept in units of log2(e), so a probability is one subtraction and one ex2.
 // Every wait is bounded; a wait that runs out reports a status code and the CTA tears down normally.
 #pragma once
 
@@ -56,7 +57,7 @@ struct SdpaStream {
   static constexpr int kSmemBytes = kExchangeOffset + kExchangeBytes + kAlignSlack;
   static constexpr int kSoftmaxWarps = 4 * kSplit;
   static constexpr int kThreads = 32 * (2 + kSoftmaxWarps);
-  static constexpr int kTmemColumns = 512;  // S at columns 0 and 128, O at 256 and 384
+  static constexpr int kTmemColumns = 512;  // S at columns 0 and 128, O at 256 (allocations are powers of two)
   static constexpr int kPartialFloats = kBlockQ * kMaxHeadDim + 2 * kBlockQ;  // O, then m, then l
   static constexpr int kMaxChunks = 32;  // chunks a query block's keys are cut into at most (the grid's x extent)
 };
@@ -149,9 +150,8 @@ sdpa_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const uint32_t v_empty = bar_base + 56;   // [2] the product that read it done   (MMA -> TMA)
   const uint32_t s_full = bar_base + 72;    // [2] S_j in tensor memory            (MMA -> softmax)
   const uint32_t s_free = bar_base + 88;    // [2] S_j in the softmax registers    (softmax -> MMA)
-  const uint32_t o_full = bar_base + 104;   // [2] O_j in tensor memory, P_j read  (MMA -> softmax)
-  const uint32_t o_free = bar_base + 120;   // [2] O_j added                       (softmax -> MMA)
-  const uint32_t p_full = bar_base + 136;   //     P_j in shared memory            (softmax -> MMA)
+  const uint32_t pv_done = bar_base + 104;  //     O += P_j.V_j done, P_j read      (MMA -> softmax)
+  const uint32_t p_full = bar_base + 112;   //     P_j in shared memory, O rescaled (softmax -> MMA)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + G::kBarrierOffset + 160);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + G::kBarrierOffset + 164);
 
@@ -176,9 +176,8 @@ sdpa_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       mbar_init(v_empty + 8 * s, 1);
       mbar_init(s_full + 8 * s, 1);
       mbar_init(s_free + 8 * s, G::kSoftmaxWarps);
-      mbar_init(o_full + 8 * s, 1);
-      mbar_init(o_free + 8 * s, G::kSoftmaxWarps);
     }
+    mbar_init(pv_done, 1);
     mbar_init(p_full, G::kSoftmaxWarps);
     *abort_flag = 0;
     mbar_fence_init();
@@ -276,8 +275,7 @@ sdpa_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (i + 1 < ntiles && !issue_scores(i + 1)) break;
         const int s = i & 1;
         const uint32_t parity = static_cast<uint32_t>(i >> 1) & 1u;
-        if (!mbar_wait(p_full, static_cast<uint32_t>(i) & 1u, abort_flag) || !mbar_wait(o_free + 8 * s, parity ^ 1u, abort_flag) ||
-            !mbar_wait(v_full + 8 * s, parity, abort_flag)) {
+        if (!mbar_wait(p_full, static_cast<uint32_t>(i) & 1u, abort_flag) || !mbar_wait(v_full + 8 * s, parity, abort_flag)) {
           give_up(kStatusMmaWaitTmem);
           break;
         }
@@ -287,9 +285,9 @@ sdpa_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           const uint64_t a_desc = umma_smem_desc_sw128(smem_base + G::kPOffset + (ks >> 2) * G::kAtomBytes) + 2 * (ks & 3);
           // V as it lies in memory, [key][head dim]: the N-major operand.  16 keys per instruction = 16 rows of 128 bytes.
           const uint64_t b_desc = umma_smem_desc_sw128_mn(smem_base + G::kVOffset + s * G::kVBytes + ks * 16 * 128, G::kAtomBytes, 1024);
-          umma_f16(tmem_base + 256 + s * 128, a_desc, b_desc, idesc_pv, ks > 0 ? 1u : 0u);
+          umma_f16(tmem_base + 256, a_desc, b_desc, idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);  // O accumulates over the tiles
         }
-        umma_commit(o_full + 8 * s);
+        umma_commit(pv_done);
         umma_commit(v_empty + 8 * s);
       }
     }
@@ -334,10 +332,7 @@ sdpa_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     // this thread's 32 keys inside P: atom = 64 keys, then four 16-byte pieces of the row, swizzled by the row
     const uint32_t p_row = smem_base + G::kPOffset + (part >> 1) * G::kAtomBytes + (row_local >> 3) * 1024 + (row_local & 7) * 128;
     float* row_max_of = reinterpret_cast<float*>(smem_gen + G::kExchangeOffset);  // [tile parity][part][row]
-    float o[kCols];
-#pragma unroll
-    for (int d = 0; d < kCols; ++d) o[d] = 0.f;
-    float m = negative_infinity, l = 0.f, alpha_pending = 1.f;
+    float m = negative_infinity, l = 0.f;
     bool ok = true;
     const bool tracing = kTrace && trace != nullptr && warp == 2 && lane == 0;
     long long spent[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -354,24 +349,14 @@ sdpa_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       if (lane == 0) give_up(code);
       ok = false;
     };
-    // O = alpha * O + O_j, the product of tile j read from tensor memory; P is free again once the product is there
-    auto take_product = [&](int j, float alpha) {
-      const int s = j & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(o_full + 8 * s, static_cast<uint32_t>(j >> 1) & 1u, abort_flag))) {  // (warp-wide loads follow)
+    const uint32_t o_base = lane_base + 256;  // this thread's 32 columns of O in tensor memory
+    // The product of tile j is in O and P is free again.  (Warp-wide: tensor-memory accesses follow.)
+    auto product_done = [&](int j) {
+      if (!__all_sync(0xffffffffu, mbar_wait(pv_done, static_cast<uint32_t>(j) & 1u, abort_flag))) {
         fail(kStatusEpilogueWait);
         return;
       }
-      lap(5);  // waiting for the product
       tcgen05_fence_after_sync();
-      uint32_t v[kCols];
-      tmem_load_32x32(lane_base + 256 + s * 128, v);
-      tmem_load_wait();
-      lap(6);  // reading it
-#pragma unroll
-      for (int e = 0; e < kCols; ++e) o[e] = fmaf(o[e], alpha, __uint_as_float(v[e]));
-      tcgen05_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(o_free + 8 * s);
     };
     if (tracing) mark = clock64();
     for (int i = 0; i < ntiles; ++i) {
@@ -419,9 +404,23 @@ sdpa_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       // nothing kept so far: every p is 0 and alpha is 1 (the reference's "block not valid" branch)
       const float m_use = m_new == negative_infinity ? 0.f : m_new;
       const float alpha = m_new == negative_infinity ? 1.f : exp2_approx(m - m_new);  // m = -inf: 0
-      if (ok) {
-        // the product of the tile before this one: issued while this tile's scores were read, and what frees P
-        if (i > 0) take_product(i - 1, alpha_pending);
+      if (ok && i > 0) {
+        // The product of the tile before this one has to be done before P is written again - and before O is rescaled,
+        // which happens only when some row of this warp got a new maximum (alpha = 1 leaves O as it is, exactly); with
+        // typical scores the maximum settles after a few tiles and most tiles skip this.
+        product_done(i - 1);
+        lap(5);  // waiting for the product
+        if (ok && __any_sync(0xffffffffu, alpha != 1.f)) {
+          uint32_t v[kCols];
+          tmem_load_32x32(o_base, v);
+          tmem_load_wait();
+#pragma unroll
+          for (int e = 0; e < kCols; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+          tmem_store_32x32(o_base, v);
+          tmem_store_wait();
+          tcgen05_fence_before_sync();  // ... before the arrival below lets the next product accumulate into it
+          lap(6);  // rescaling O
+        }
       }
       if (ok) {
         // p = exp(s - m'), summed unrounded, stored as bf16 where the MMA reads its A operand
@@ -446,11 +445,23 @@ sdpa_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (lane == 0) mbar_arrive(p_full);
         lap(4);  // exponentials, probabilities to shared memory
       }
-      alpha_pending = alpha;
       m = m_new;
     }
     if (tracing) stamp(3);
-    if (ok && ntiles > 0) take_product(ntiles - 1, alpha_pending);
+    // O leaves tensor memory once, at the end
+    float o[kCols];
+#pragma unroll
+    for (int d = 0; d < kCols; ++d) o[d] = 0.f;
+    if (ok && ntiles > 0) {
+      product_done(ntiles - 1);
+      if (ok) {
+        uint32_t v[kCols];
+        tmem_load_32x32(o_base, v);
+        tmem_load_wait();
+#pragma unroll
+        for (int e = 0; e < kCols; ++e) o[e] = __uint_as_float(v[e]);
+      }
+    }
     if (tracing) {
       lap(7);
       stamp(4);
