@@ -218,6 +218,11 @@ VECOPS_B200_EXPORT int32_t vecops_b200_device_info(int32_t device_index, VecopsB
 /* Kernels launched by this library since load (all devices, all threads). */
 VECOPS_B200_EXPORT uint64_t vecops_b200_launch_count(void);
 
+/* Waits for everything enqueued on `stream` (a cudaStream_t; NULL = the default stream) - what a caller of the
+ * enqueue-only entry points above (quantisers, correction row, pack) does before reading results on the host, without
+ * linking the CUDA runtime itself. */
+VECOPS_B200_EXPORT int32_t vecops_b200_stream_synchronize(void* stream, VecopsError* error);
+
 /* Device-side wait diagnostics.  Every mbarrier wait in the tensor-core
  * kernels is bounded; a wait that runs out records where it gave up and the
  * kernel returns.  Synchronous runs check this themselves and report

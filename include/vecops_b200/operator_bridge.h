@@ -42,6 +42,15 @@ VECOPS_B200_EXPORT uint64_t vecops_b200_matmul_operator(void);
  * vecops_b200_matmul_packed_layout's layout (ops/MatmulPack.h:93-131, :28-35). */
 VECOPS_B200_EXPORT uint64_t vecops_b200_matmul_pack_operator(int32_t compensated);
 
+/* Handles of the operators either side of the matmul path (0 for an unknown `which`):
+ *   0  vecops::matmul_batched                values = {a[B,M,K], b[B,N,K], c[B,M,N][, column_scale[N]]}; an operand every entry
+ *                                            shares comes as a view with batch stride 0 (tests/ops/MatmulBatchTest.cpp:96-131)
+ *   1  vecops::scaled_dot_product_attention  values = {q[H,Lq,D], k[H,Lkv,D], v[H,Lkv,Dv], out[H,Lq,Dv], scale, causal[, key_mask[Lkv]
+ *                                            [, bias[H,Lq,Lkv]]]}; scratch of vecops_b200_operator_workspace bytes in the frame
+ *                                            (ops/details/attention/SDPA.h:72-84)
+ *   2  vecops::quantize_rows_per_row         values = {src[M,K], multipliers[M], dst[M,K][, zero_point]} (matmul/Quantization.h:76-140) */
+VECOPS_B200_EXPORT uint64_t vecops_b200_caller_operator(uint32_t which);
+
 /* Validate, resolve and run one call: values = {a, b, c[, column_scale]}.
  * Replaces vecops_operator_bridge_invoke_v1 (OperatorBridgeAbi.h:156-158). */
 VECOPS_B200_EXPORT int32_t vecops_operator_bridge_invoke_v1(uint64_t handle, const VecopsCall* call,

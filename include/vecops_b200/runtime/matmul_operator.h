@@ -83,6 +83,18 @@ private:
 [[nodiscard]] KernelDef matmul_pack_b_compensated_kernel_def();
 [[nodiscard]] std::shared_ptr<Operator> make_matmul_pack_operator(bool compensated = false);
 
+// The callers and data formats either side of the path, as operators (csrc/runtime/caller_operators.cpp):
+//   vecops::matmul_batched                a[B,M,K], b[B,N,K], c[B,M,N], column_scale[N]?     (tests/ops/MatmulBatchTest.cpp:96-131)
+//   vecops::scaled_dot_product_attention  q[H,Lq,D], k[H,Lkv,D], v[H,Lkv,Dv], out[H,Lq,Dv], scale, causal, key_mask[Lkv]?, bias[H,Lq,Lkv]?
+//   vecops::quantize_rows_per_row         src[M,K], multipliers[M], dst[M,K], zero_point     (matmul/Quantization.h:76-140)
+[[nodiscard]] std::shared_ptr<Operator> make_matmul_batched_operator();
+[[nodiscard]] std::shared_ptr<Operator> make_attention_operator();
+[[nodiscard]] std::shared_ptr<Operator> make_quantize_rows_per_row_operator();
+// Bridge handles kCallerHandleBase + {0, 1, 2} name the three; null for anything else.
+inline constexpr std::uint64_t kCallerHandleBase = 0x6d61746d756c0010ULL;
+[[nodiscard]] const Operator* caller_operator_of(std::uint64_t handle);
+[[nodiscard]] const KernelDef* caller_kernel_def_of(std::uint64_t handle);
+
 // Static descriptor template of one variant (specialization_key left empty).
 [[nodiscard]] const VecopsKernelDescriptorV1* matmul_descriptor_template(std::uint32_t kernel);
 

@@ -294,3 +294,33 @@ def test_bridge_re_enters_a_prepared_call_on_an_identical_signature(library):
     slow1, prepared1 = counters()
     invoke(frame)
     assert counters() == (slow1 + 1, prepared1)
+
+
+def test_caller_operators_bind_and_fail_loudly_without_a_gpu(library):
+    """The operators either side of the matmul path (rank-3 matmul, attention, the per-row quantiser) are reachable through
+    the bridge: handles exist, frames bind and resolve on the host, and a frame of the wrong shape names its fault."""
+    library.vecops_b200_caller_operator.restype = ctypes.c_uint64
+    library.vecops_b200_caller_operator.argtypes = [ctypes.c_uint32]
+    library.vecops_operator_bridge_invoke_v1.argtypes = [ctypes.c_uint64, ctypes.POINTER(capi.VecopsCall), ctypes.c_uint32, ctypes.c_void_p,
+                                                         ctypes.POINTER(capi.VecopsError)]
+    library.vecops_b200_operator_resolve.argtypes = [ctypes.c_uint64, ctypes.POINTER(capi.VecopsCall), ctypes.c_char_p, ctypes.c_size_t,
+                                                     ctypes.POINTER(capi.VecopsError)]
+    handles = [library.vecops_b200_caller_operator(i) for i in range(3)]
+    assert all(handles) and len(set(handles)) == 3 and library.vecops_b200_caller_operator(7) == 0
+    batched = handles[0]
+    frame, keep = _frame([((3, 16, 64), capi.DTYPE_BF16, False), ((3, 32, 64), capi.DTYPE_BF16, False), ((3, 16, 32), capi.DTYPE_F32, True)],
+                         0x7f0000000000)
+    key = ctypes.create_string_buffer(256)
+    error = capi.ErrorBuffer()
+    assert library.vecops_b200_operator_resolve(batched, byref(frame), key, 256, byref(error.record)) == capi.OK, error.text.value
+    assert key.value.decode().startswith("vecops::matmul_batched;TA=bf16;TB=bf16;TC=f32")
+    if not torch.cuda.is_available():
+        rc = library.vecops_operator_bridge_invoke_v1(batched, byref(frame), 0, None, byref(error.record))
+        assert rc == capi.EXECUTION_ERROR and b"no CPU fallback" in error.text.value
+    # extents that disagree are named, and a rank-2 frame belongs to the plain matmul operator
+    wrong, keep2 = _frame([((3, 16, 64), capi.DTYPE_BF16, False), ((3, 32, 48), capi.DTYPE_BF16, False), ((3, 16, 32), capi.DTYPE_F32, True)],
+                          0x7f0000000000)
+    error = capi.ErrorBuffer()
+    assert library.vecops_operator_bridge_invoke_v1(batched, byref(wrong), 0, None, byref(error.record)) != capi.OK
+    flat, keep3 = _frame([((16, 64), capi.DTYPE_BF16, False), ((32, 64), capi.DTYPE_BF16, False), ((16, 32), capi.DTYPE_F32, True)], 0x7f0000000000)
+    assert library.vecops_operator_bridge_invoke_v1(batched, byref(flat), 0, None, byref(capi.ErrorBuffer().record)) != capi.OK

@@ -1225,6 +1225,90 @@ def test_sdpa_streaming_chunks_merge(port, monkeypatch, lq, lkv, d, causal, head
             assert rel_frobenius(out[h].cpu().numpy()[rows], want) <= TOL_BF16, (repeat, h)
 
 
+def _frame_of(values, keep, workspace=None):
+    array = (capi.VecopsValue * len(values))(*values)
+    context = capi.VecopsExecutionContext()
+    context.struct_size = ctypes.sizeof(context)
+    context.stream = None
+    keep.extend([array, context, workspace])
+    return capi.VecopsCall(ctypes.sizeof(capi.VecopsCall), len(values), array, workspace.data_ptr() if workspace is not None else None,
+                           workspace.numel() if workspace is not None else 0, ctypes.pointer(context))
+
+
+def _none_value():
+    v = capi.VecopsValue()
+    v.struct_size = ctypes.sizeof(capi.VecopsValue)
+    v.kind = capi.VALUE_NONE
+    return v
+
+
+def test_callers_through_the_operator_layer(port, golden, monkeypatch):
+    """Rank-3 matmul, attention and the per-row quantiser as operators behind vecops_operator_bridge_invoke_v1: the same
+    frames, keys and errors as the matmul operator's, held to the reference-made fixtures."""
+    lib, _ = bridge_lib()
+    lib.vecops_b200_caller_operator.restype = ctypes.c_uint64
+    lib.vecops_b200_caller_operator.argtypes = [ctypes.c_uint32]
+    lib.vecops_b200_operator_workspace.argtypes = [ctypes.c_uint64, ctypes.POINTER(capi.VecopsCall), ctypes.POINTER(ctypes.c_uint64),
+                                                   ctypes.POINTER(capi.VecopsError)]
+    batched, attention, quantize = (lib.vecops_b200_caller_operator(i) for i in range(3))
+    assert batched and attention and quantize and lib.vecops_b200_caller_operator(3) == 0
+    error = capi.ErrorBuffer()
+    key = ctypes.create_string_buffer(256)
+    # rank-3 matmul: the reference's own batch fixtures, shared weights as a stride-0 view
+    for name, case in golden.items():
+        if str(case["kind"]) != "batched_bf16":
+            continue
+        if "bias" in case:
+            continue  # (an accumulator input is the fused form's: the C entry point takes it, this operator does not)
+        batch = case["c"].shape[0]
+        a = to_device(case["a"], bf16=True)
+        b = to_device(case["b"], bf16=True)
+        a = a.expand(batch, *a.shape) if a.dim() == 2 else a
+        b = b.expand(batch, *b.shape) if b.dim() == 2 else b
+        c = torch.full((batch, a.shape[1], b.shape[1]), -5.0, dtype=torch.float32, device="cuda")
+        keep = []
+        call = _frame_of([_tensor_value(a, keep=keep), _tensor_value(b, keep=keep), _tensor_value(c, True, keep=keep)], keep)
+        error.raise_for(lib.vecops_b200_operator_resolve(batched, byref(call), key, 256, byref(error.record)))
+        assert key.value.decode().startswith("vecops::matmul_batched;TA=bf16;TB=bf16;TC=f32"), key.value
+        error.raise_for(lib.vecops_operator_bridge_invoke_v1(batched, byref(call), 0, None, byref(error.record)))
+        torch.cuda.synchronize()
+        assert rel_frobenius(c.cpu().numpy(), case["c"]) <= TOL_BF16, name
+    # a rank-2 operand is not this operator's
+    keep = []
+    flat = torch.zeros((4, 8), dtype=torch.bfloat16, device="cuda")
+    call = _frame_of([_tensor_value(flat, keep=keep), _tensor_value(flat, keep=keep), _tensor_value(flat, True, keep=keep)], keep)
+    assert lib.vecops_operator_bridge_invoke_v1(batched, byref(call), 0, None, byref(capi.ErrorBuffer().record)) != capi.OK
+    # attention: one fixture with masks and bias as a single head, scratch as the workspace query sizes it
+    monkeypatch.setenv("VECOPS_B200_SDPA_CHUNK_TILES", "1000")
+    case = golden["sdpa_masks_130x257x64x64"]
+    q, k, v = (to_device(case[n], bf16=True).unsqueeze(0) for n in ("q", "k", "v"))
+    out = torch.full((1, q.shape[1], v.shape[2]), -5.0, dtype=torch.float32, device="cuda")
+    key_mask, bias = to_device(case["key_mask"]), to_device(case["bias"]).unsqueeze(0)
+    keep = []
+    values = [_tensor_value(q, keep=keep), _tensor_value(k, keep=keep), _tensor_value(v, keep=keep), _tensor_value(out, True, keep=keep),
+              _scalar_value(capi.DTYPE_F32, float(case["scale"])), _scalar_value(capi.DTYPE_I32, int(case["causal"])),
+              _tensor_value(key_mask, keep=keep), _tensor_value(bias, keep=keep)]
+    call = _frame_of(values, keep)
+    need = ctypes.c_uint64(0)
+    error.raise_for(lib.vecops_b200_operator_workspace(attention, byref(call), byref(need), byref(error.record)))
+    scratch = torch.empty(max(need.value, 1), dtype=torch.uint8, device="cuda")
+    call = _frame_of(values, keep, scratch if need.value else None)
+    error.raise_for(lib.vecops_operator_bridge_invoke_v1(attention, byref(call), 0, None, byref(error.record)))
+    torch.cuda.synchronize()
+    want = port.sdpa_bf16_streaming(case["q"], case["k"], case["v"], float(case["scale"]), key_mask=case["key_mask"], bias=case["bias"],
+                                    causal=int(case["causal"]))
+    assert rel_frobenius(out[0].cpu().numpy(), want) <= TOL_BF16
+    # the per-row quantiser: the reference's own per-token fixture, bit for bit
+    case = next(c for c in golden.values() if str(c["kind"]) == "quant_per_row")
+    src, multipliers = to_device(case["a"]), to_device(case["multipliers"])
+    dst = torch.zeros(case["a"].shape, dtype=torch.uint8, device="cuda")
+    keep = []
+    call = _frame_of([_tensor_value(src, keep=keep), _tensor_value(multipliers, keep=keep), _tensor_value(dst, True, keep=keep),
+                      _scalar_value(capi.DTYPE_F32, float(case["zero_point"]))], keep)
+    error.raise_for(lib.vecops_operator_bridge_invoke_v1(quantize, byref(call), 0, None, byref(error.record)))
+    assert np.array_equal(dst.cpu().numpy(), port.quantize_rows_per_row(case["a"], case["multipliers"], float(case["zero_point"])))
+
+
 @pytest.mark.parametrize("strategy", SDPA_STRATEGIES)
 def test_sdpa_heads_in_one_call(port, monkeypatch, strategy):
     monkeypatch.setenv("VECOPS_B200_SDPA_CHUNK_TILES", "1000")  # 160 keys: two tiles, kept together

@@ -180,6 +180,7 @@ def library() -> ctypes.CDLL:
         lib.vecops_b200_device_count.restype = c_int32
         lib.vecops_b200_device_info.argtypes = [c_int32, POINTER(VecopsB200DeviceInfo), e]
         lib.vecops_b200_launch_count.restype = c_uint64
+        lib.vecops_b200_stream_synchronize.argtypes = [c_void_p, e]
         lib.vecops_b200_take_device_status.argtypes = [c_int32, POINTER(c_uint32), e]
         lib.vecops_b200_place_columns.argtypes = [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
                                                   c_uint32, c_void_p, e]

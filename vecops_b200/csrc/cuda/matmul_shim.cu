@@ -1477,6 +1477,13 @@ __attribute__((visibility("default"))) void vecops_b200_debug_set_trace(void* de
   g_trace = static_cast<unsigned long long*>(device_buffer);
 }
 
+int32_t vecops_b200_stream_synchronize(void* stream, VecopsError* error) {
+  if (vecops_b200_device_count() == 0) return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "no usable CUDA device; there is no CPU fallback");
+  const cudaError_t status = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (status != cudaSuccess) return cuda_fail(error, status, "cudaStreamSynchronize");
+  return VECOPS_STATUS_OK;
+}
+
 int32_t vecops_b200_take_device_status(int32_t device_index, uint32_t* status, VecopsError* error) {
   if (status == nullptr) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "status output pointer is null");
   *status = 0;

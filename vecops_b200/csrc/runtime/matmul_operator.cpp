@@ -682,7 +682,7 @@ const Operator* operator_of(std::uint64_t handle) {
   if (handle == kMatmulHandle) return matmul_operator().get();
   if (handle == kPackHandle) return pack_operator(false).get();
   if (handle == kPackCompensatedHandle) return pack_operator(true).get();
-  return nullptr;
+  return caller_operator_of(handle);  // batched matmul, attention, per-row quantiser
 }
 
 std::int32_t report(VecopsError* error, const Status& status) {
@@ -904,13 +904,15 @@ int32_t vecops_b200_operator_resolve(uint64_t handle, const VecopsCall* call, ch
 }
 
 int32_t vecops_b200_operator_workspace(uint64_t handle, const VecopsCall* call, uint64_t* bytes, VecopsError* error) {
-  if (handle != kMatmulHandle) return fail(error, VECOPS_STATUS_NOT_FOUND, "unknown operator handle");
+  const Operator* op = handle == kMatmulHandle ? matmul_operator().get() : caller_operator_of(handle);
+  const KernelDef* caller_definition = handle == kMatmulHandle ? nullptr : caller_kernel_def_of(handle);
+  if (op == nullptr || (handle != kMatmulHandle && caller_definition == nullptr)) return fail(error, VECOPS_STATUS_NOT_FOUND, "unknown operator handle");
   if (bytes == nullptr) return fail(error, VECOPS_STATUS_INVALID_ARGUMENT, "bytes output pointer is null");
   KernelCall kernel_call;
   if (const auto rc = call_from_frame(call, 0, nullptr, &kernel_call, error); rc != VECOPS_STATUS_OK) return rc;
-  auto executable = matmul_operator()->resolve(kernel_call, call->context);
+  auto executable = op->resolve(kernel_call, call->context);
   if (!executable) return report(error, executable.status());
-  auto bound = bind_kernel_call(matmul_kernel_def(), kernel_call);
+  auto bound = caller_definition != nullptr ? bind_kernel_call(*caller_definition, kernel_call) : bind_kernel_call(matmul_kernel_def(), kernel_call);
   if (!bound) return report(error, bound.status());
   auto size = executable.value()->workspace_size(bound.value().arguments, call->context);
   if (!size) return report(error, size.status());
