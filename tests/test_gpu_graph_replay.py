@@ -150,3 +150,47 @@ def test_automatic_weight_only_dispatch_runs_without_a_workspace(port):
         torch.cuda.synchronize()
         assert rel_frobenius(bf16_bits_to_f32(bf16_result_to_numpy(c)), want) <= TOL_BF16, f"workspace={with_workspace}"
         del scratch
+
+
+def test_replayed_streaming_attention_follows_its_inputs(port):
+    """The streaming attention kernel and the merge of its key chunks (a programmatic dependent) captured once and replayed
+    with new operands: the chunk records in scratch are rewritten by every launch and nothing else lives there."""
+    rng = np.random.default_rng(11)
+    heads, lq, lkv, d = 2, 384, 1024, 64
+    q = torch.zeros((heads, lq, d), dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros((heads, lkv, d), dtype=torch.bfloat16, device="cuda")
+    v = torch.zeros((heads, lkv, d), dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros((heads, lq, d), dtype=torch.float32, device="cuda")
+    holder = {}
+
+    def launch(stream):
+        record = harness.sdpa_record(q, k, v, out, 0.125, causal=capi.CAUSAL_BOTTOM_RIGHT, stream=stream, asynchronous=True,
+                                     strategy=capi.SDPA_STREAMING)
+        if "scratch" not in holder:
+            need = ctypes.c_uint64(0)
+            error = capi.ErrorBuffer()
+            error.raise_for(capi.library().vecops_b200_sdpa_workspace(byref(record), byref(need), byref(error.record)))
+            assert need.value > 0, "this shape is expected to be cut into key chunks"
+            holder["scratch"] = torch.empty(need.value + 256, dtype=torch.uint8, device="cuda")
+            holder["need"] = need.value
+            holder["tiles"] = harness.sdpa_plan(record)[1]
+        scratch = holder["scratch"]
+        record.workspace, record.workspace_size = scratch.data_ptr() + (-scratch.data_ptr()) % 256, holder["need"]
+        error = capi.ErrorBuffer()
+        error.raise_for(capi.library().vecops_b200_sdpa_run(byref(record), byref(error.record)))
+
+    graph = _capture(launch)
+    rows = np.unique(np.linspace(0, lq - 1, 10).astype(np.int64))
+    last = np.arange(lq)[:, None] + (lkv - lq)
+    keep = (np.arange(lkv)[None, :] <= last).astype(np.uint8)
+    for replay in range(REPLAYS):
+        host = [f32_to_bf16_bits(rng.standard_normal(t.shape).astype(np.float32)) for t in (q, k, v)]
+        for tensor, values in zip((q, k, v), host):
+            tensor.copy_(torch.from_numpy(values).cuda().view(torch.bfloat16))
+        out.fill_(-7)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert _status() == 0
+        for head in range(heads):
+            want = port.sdpa_bf16_streaming(host[0][head][rows], host[1][head], host[2][head], 0.125, keep_mask=keep[rows], chunk_blocks=holder["tiles"])
+            assert rel_frobenius(out[head].cpu().numpy()[rows], want) <= TOL_BF16, f"replay {replay} head {head}"
