@@ -182,6 +182,42 @@ def time_graph(prepared, steps: int, warmup: int, dev) -> float:
     return start.elapsed_time(stop) / steps
 
 
+def size_matched_read(byte_count: float, sets: int, steps: int, warmup: int, dev) -> dict:
+    """Context for an HBM-bound roofline fraction: a library reduction (torch fp32 sum) over buffers of the same byte count,
+    rotated and timed exactly as the kernel is.  The measured HBM peak comes from a copy of gigabytes; a launch that moves
+    tens of megabytes spends a large part of its few microseconds filling and draining the memory system, and this figure
+    says how much of the peak a plain read of that size reaches.  A yardstick only: nothing on the product path calls it."""
+    import torch
+    count = int(byte_count) // 4
+    buffers = [torch.ones(count, dtype=torch.float32, device=dev) for _ in range(sets)]
+    outs = [torch.empty(1, dtype=torch.float32, device=dev) for _ in range(sets)]
+    stream = torch.cuda.Stream(dev)
+
+    def capture(launches: int):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(launches):
+                torch.sum(buffers[i % sets], dim=(0,), keepdim=True, out=outs[i % sets])
+        return graph
+
+    with torch.cuda.stream(stream):
+        torch.sum(buffers[0], dim=(0,), keepdim=True, out=outs[0])
+        stream.synchronize()
+    warm, timed = capture(max(warmup, 3)), capture(steps)
+    with torch.cuda.stream(stream):
+        warm.replay()
+        stream.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        timed.replay()
+        stop.record(stream)
+        stream.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    del buffers, outs
+    return {"kernel": "torch.sum over fp32, one launch per buffer", "bytes_per_launch": count * 4, "ms_per_launch": ms,
+            "gb_per_s": count * 4 / (ms * 1e-3) / 1e9, "sets": sets}
+
+
 def take_status(device: int = 0) -> int:
     from vecops_b200 import capi
     status = ctypes.c_uint32(0)
@@ -293,6 +329,14 @@ def measure_single(name: str, steps: int, warmup: int, dev, port, peaks, peak_so
               "launch": "one CUDA graph of all timed launches, CUDA events around its replay", "parity": parity, "device_status": status}
     if fused or not full_record:
         return record
+    if roofline["bound"] == "hbm":
+        try:
+            read = size_matched_read(per_set, sets, steps, warmup, dev)
+            read["frac_of_peak"] = read["gb_per_s"] / roofline["peak"]
+            read["kernel_vs_read"] = roofline["achieved"] / read["gb_per_s"]
+            roofline["size_matched_read"] = read
+        except Exception as error:  # noqa: BLE001 - context only
+            roofline["size_matched_read"] = {"error": repr(error)}
     try:
         e2e_steps = 20 if w.kind != "w8" else 200
         e2e = measure_e2e(w, operands, host_inputs, e2e_steps, 3, dev, resident_weights=w.kind == "w8")
@@ -1134,6 +1178,39 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def measure_w8_size_curve(dev, peaks, steps: int = 60, warmup: int = 6) -> dict:
+    """The weight-only streaming kernel at K=4096 over growing N (C4's N and 2, 4, 8, 16 times it), M=1 and M=16, each beside a
+    library read of the same bytes: how much of the HBM-bound gap at C4 is the size of one launch and how much the kernel."""
+    import torch
+    from vecops_b200 import harness
+    k, rows = 4096, []
+    stream = torch.cuda.current_stream(dev)
+    for n in (14336, 28672, 57344, 114688, 229376):
+        sets = max(2, int(np.ceil(260e6 / (n * k))) + 1)
+        weights = [torch.randint(-127, 128, (n, k), dtype=torch.int8, device=dev) for _ in range(sets)]
+        scale = torch.rand(n, device=dev) * 0.02 + 0.001
+        row = {"n": n, "k": k, "weight_bytes": n * k, "sets": sets}
+        for m in (1, 16):
+            a = torch.randn(m, k, device=dev).to(torch.bfloat16)
+            outs = [torch.empty(m, n, dtype=torch.bfloat16, device=dev) for _ in range(sets)]
+            prepared = [harness.PreparedMatmul(a, weights[i], outs[i], scale, stream=stream) for i in range(sets)]
+            prepared[0].launch()
+            torch.cuda.synchronize()
+            ms = time_graph(prepared, steps, warmup, dev)
+            want = (a.float() @ weights[0].float().t()) * scale
+            algorithmic = n * k + 4 * n + 2 * m * k + 2 * m * n
+            gbs = algorithmic / (ms * 1e-3) / 1e9
+            row[f"m{m}"] = {"us": ms * 1e3, "gb_per_s": gbs, "frac_of_peak": gbs / peaks["hbm_gbs"],
+                            "rel_fro_vs_torch_f32": ((outs[0].float() - want).norm() / want.norm()).item(), "device_status": take_status(dev.index or 0)}
+            del prepared, outs
+        read = size_matched_read(n * k, sets, steps, warmup, dev)
+        row["read_of_the_same_bytes"] = {"us": read["ms_per_launch"] * 1e3, "gb_per_s": read["gb_per_s"], "frac_of_peak": read["gb_per_s"] / peaks["hbm_gbs"]}
+        rows.append(row)
+        del weights
+        torch.cuda.empty_cache()
+    return {"kernel": "w8_stream_kernel", "peak_gb_per_s": peaks["hbm_gbs"], "rows": rows}
+
+
 def run_extra(which: str) -> None:
     """One of the extra measurements alone, on cuda:0."""
     import torch
@@ -1143,7 +1220,8 @@ def run_extra(which: str) -> None:
     peaks, _ = measured_peaks()
     port = Port()
     record = {"attention": lambda: measure_sdpa(dev, port), "pack": lambda: measure_pack(dev, peaks),
-              "f16": lambda: measure_f16(50, 5, dev, port, peaks), "quantized": lambda: measure_quantized(50, 5, dev, port, peaks)}[which]()
+              "f16": lambda: measure_f16(50, 5, dev, port, peaks), "quantized": lambda: measure_quantized(50, 5, dev, port, peaks),
+              "w8-size-curve": lambda: measure_w8_size_curve(dev, peaks)}[which]()
     print(json.dumps({"extra": which, **record}), flush=True)
 
 
@@ -1157,7 +1235,7 @@ def main() -> None:
     parser.add_argument("--gather", choices=["fused", "fused-peer", "nccl"], default="fused",
                         help="how the sharded GEMM's output is gathered: fused = epilogue stores through the NVSwitch multicast address when "
                              "there is one, else to every rank's peer pointer; fused-peer = peer pointers only; nccl = library collective")
-    parser.add_argument("--extra", choices=["attention", "pack", "f16", "quantized"], default=None,
+    parser.add_argument("--extra", choices=["attention", "pack", "f16", "quantized", "w8-size-curve"], default=None,
                         help="run ONLY this one of the extra single-GPU measurements and print its record (for profiling that kernel)")
     parser.add_argument("--no-extra", action="store_true", help="skip the brief measurements of the other single-GPU configurations")
     args = parser.parse_args()
