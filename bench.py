@@ -4,8 +4,9 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--no-extra]
 
 Headline workload at EVERY N (1, 2, 4, 8): the large BF16 GEMM M=16384 N=53248 K=8192, B column-sharded over the ranks
-(one process per GPU, launched by torch.distributed.run), A replicated, the output gathered on every rank by the GEMM's
-own epilogue - strong scaling, so the per-N values form one curve.  It fits one GPU (2.9 GB), where the slab is the
+(one process per GPU, launched by torch.distributed.run), A replicated, the output gathered on every rank - by the GEMM's
+own epilogue, or by copies that run behind the next step's GEMM, whichever a ten-step trial on the machine finds faster
+(`--gather`; the trial times are in the line) - strong scaling, so the per-N values form one curve.  It fits one GPU (2.9 GB), where the slab is the
 whole result.  At N = 1 the other single-GPU configurations (BF16 4096^3, FP32 1024^3, INT8 4096x14336x4096, the three
 weight-only decode shapes) are measured too and reported under "configs", each with its own `roofline`,
 `cpu_baseline` and `e2e` record.
@@ -934,41 +935,100 @@ def run_ours(args) -> None:
     operands, host_inputs = device_sets(w, 1, dev, n0, n1)
     o = operands[0]
     prepared = [harness.PreparedMatmul(o["a"], o["b"], o["c"], None, stream=stream)]  # the slab GEMM alone (roofline)
-    full = handle = fused = None
+    full = pipe = full_of = None
+    trials = {}
+    step_join = lambda: None  # noqa: E731 - only the pipelined gather has work in flight on a second stream
     if world == 1:
         step_launch = prepared[0].launch
         launches_per_step = 1
     else:
-        if args.gather in ("fused", "fused-peer"):
-            try:  # the epilogue sends each finished piece into every rank's result over NVLink
-                full, handle = sharding.symmetric_result(w.m, w.n, torch.bfloat16, dev)
-                multicast = int(getattr(handle, "multicast_ptr", 0) or 0) if args.gather == "fused" else 0
-                # every rank must take the same route
-                route = torch.tensor([1 if multicast else 0], device=dev)
-                dist.all_reduce(route, op=dist.ReduceOp.MIN)
-                if int(route.item()) == 1:
-                    # one store to the multicast address: the switch writes it into every rank's copy, own included
-                    targets = [multicast]
-                    gather_mode = "fused: epilogue multimem.st to the NVSwitch multicast address of the result (one store, every rank's copy) + one device barrier"
-                else:
-                    targets = [int(p) for p in handle.buffer_ptrs]
-                    gather_mode = "fused: epilogue TMA stores to every rank's result over NVLink peer pointers + one device barrier"
-                fused = sharding.FusedGatherGemm(o["a"], o["b"], targets, w.n, w.n, n0, torch.bfloat16, stream, multicast=len(targets) == 1)
-                fused.launch()
-                handle.barrier(channel=0)
+        def fused_route(allow_multicast: bool):
+            """The gather inside the GEMM's epilogue: each finished piece goes into every rank's result over NVLink."""
+            result, hdl = sharding.symmetric_result(w.m, w.n, torch.bfloat16, dev)
+            multicast = int(getattr(hdl, "multicast_ptr", 0) or 0) if allow_multicast else 0
+            same = torch.tensor([1 if multicast else 0], device=dev)  # every rank must take the same route
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            if int(same.item()) == 1:
+                # one store to the multicast address: the switch writes it into every rank's copy, own included
+                targets = [multicast]
+                mode = "fused: epilogue multimem.st to the NVSwitch multicast address of the result (one store, every rank's copy) + one device barrier"
+            else:
+                targets = [int(p) for p in hdl.buffer_ptrs]
+                mode = "fused: epilogue TMA stores to every rank's result over NVLink peer pointers + one device barrier"
+            gemm = sharding.FusedGatherGemm(o["a"], o["b"], targets, w.n, w.n, n0, torch.bfloat16, stream, multicast=len(targets) == 1)
+
+            def launch():
+                gemm.launch()
+                hdl.barrier(channel=0)
+            return {"launch": launch, "join": lambda: None, "full": lambda: result, "mode": mode, "launches_per_step": 1,
+                    "buffers": result, "pipe": None, "keep": (gemm, hdl)}
+
+        def pipelined_route(by_kernel: bool):
+            """The slab stored locally, pushed to the peers on a second stream behind the next step's GEMM."""
+            results, hdl = sharding.symmetric_result(w.m, w.n, torch.bfloat16, dev, copies=2)
+            lanes = 1 if by_kernel else int(os.environ.get("VECOPS_B200_PUSH_LANES", "1"))
+            gemm = sharding.PipelinedGatherGemm(o["a"], o["b"], results, [int(p) for p in hdl.buffer_ptrs], rank, n0,
+                                                barrier=lambda: hdl.barrier(channel=0), compute_stream=stream,
+                                                route=capi.PUSH_KERNEL if by_kernel else capi.PUSH_COPY_ENGINE, lanes=lanes)
+            mode = ("pipelined: the slab GEMM stores into this rank's copy of the result; on a second stream "
+                    + ("push_columns_kernel stores the slab" if by_kernel else f"the copy engines copy the slab (one strided copy per peer, {lanes} at a time)")
+                    + " into every peer's copy over NVLink + one device barrier, while the next step's GEMM runs (two copies of the result, alternating)")
+            return {"launch": gemm.launch, "join": gemm.join, "full": lambda: results[(gemm.steps - 1) & 1], "mode": mode,
+                    "launches_per_step": 2 if by_kernel else 1, "buffers": results, "pipe": gemm, "keep": (hdl,)}
+
+        makers = {"fused": lambda: fused_route(True), "fused-peer": lambda: fused_route(False),
+                  "pipelined": lambda: pipelined_route(True), "pipelined-ce": lambda: pipelined_route(False)}
+        # auto: both ways of hiding the gather are tried for a few steps on this machine and the faster one is measured
+        wanted = ["fused", "pipelined-ce"] if args.gather == "auto" else [args.gather] if args.gather in makers else []
+        routes, trials = {}, {}
+        for key in wanted:
+            try:
+                route = makers[key]()
+                route["launch"]()
+                route["join"]()
                 torch.cuda.synchronize()
+                built = 1
             except Exception as error:  # symmetric memory unavailable: fall back to the library collective
-                print(f"[bench] fused gather unavailable on rank {rank}: {error!r}", file=sys.stderr)
-                fused = None
-        ok = torch.tensor([1 if fused is not None else 0], device=dev)
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        if int(ok.item()) == 1:
-            def step_launch():
-                fused.launch()
-                handle.barrier(channel=0)
-            launches_per_step = 1
+                print(f"[bench] gather route {key} unavailable on rank {rank}: {error!r}", file=sys.stderr)
+                built = 0
+            ok = torch.tensor([built], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 1:
+                routes[key] = route
+        if len(routes) > 1:
+            for key, route in routes.items():
+                def trial_step(_i, route=route):
+                    route["launch"]()
+                torch.cuda.synchronize()
+                dist.barrier()
+                for i in range(2):
+                    trial_step(i)
+                route["join"]()
+                torch.cuda.synchronize()
+                dist.barrier()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record(stream)
+                for i in range(10):
+                    trial_step(i)
+                route["join"]()
+                t1.record(stream)
+                torch.cuda.synchronize()
+                took = torch.tensor([t0.elapsed_time(t1) / 10], dtype=torch.float64, device=dev)
+                dist.all_reduce(took, op=dist.ReduceOp.MAX)
+                trials[key] = float(took.item())
+        if routes:
+            chosen_key = min(routes, key=lambda k: trials.get(k, 0.0))
+            chosen = routes[chosen_key]
+            step_launch, step_join, pipe = chosen["launch"], chosen["join"], chosen["pipe"]
+            gather_mode, launches_per_step = chosen["mode"], chosen["launches_per_step"]
+            # nothing a trial step left behind may pass for the checked step's result
+            torch.cuda.synchronize()
+            dist.barrier()
+            chosen["buffers"].zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            full_of = chosen["full"]
         else:
-            fused = None
             gather_mode = "nccl: all_gather_into_tensor of the slabs + placement kernel per slab"
             full = torch.empty((w.m, w.n), dtype=torch.bfloat16, device=dev)
             staging = torch.empty((world, w.m, n1 - n0), dtype=torch.bfloat16, device=dev)
@@ -978,6 +1038,7 @@ def run_ours(args) -> None:
                 prepared[0].launch()
                 sharding.gather_columns(o["c"], full, staging, world, place=place)
             launches_per_step = 1 + world
+            full_of = lambda: full  # noqa: E731
 
     def step(_):
         step_launch()
@@ -985,7 +1046,10 @@ def run_ours(args) -> None:
     sets_note = f"operands and result {w.algorithmic_bytes / 1e9:.2f} GB > L2 126 MB"
 
     step(0)
+    step_join()
     torch.cuda.synchronize()
+    if full_of is not None:
+        full = full_of()
     result_view = full[:, n0:n1] if full is not None else o["c"]
     parity = parity_sample(w, host_inputs, result_view, port, rows=8)
     if full is not None:
@@ -999,6 +1063,7 @@ def run_ours(args) -> None:
 
     for i in range(warmup):
         step(i)
+    step_join()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -1009,6 +1074,7 @@ def run_ours(args) -> None:
         start.record(stream)
         for i in range(steps):
             step(warmup + i)
+        step_join()  # the last step's gather has landed on every rank before the clock stops
         stop.record(stream)
         torch.cuda.synchronize()
     if world > 1:
@@ -1026,6 +1092,17 @@ def run_ours(args) -> None:
         prepared[0].launch()
 
     kernel_ms = time_steps(gemm_only, steps, 3, stream) if world > 1 else ms
+    gather_alone = None
+    if pipe is not None:
+        # the transfer by itself: this rank's slab to every peer + the barrier, nothing else running, max over ranks
+        torch.cuda.synchronize()
+        dist.barrier()
+        gather_ms = torch.tensor([time_steps(lambda i: pipe.gather_alone(i & 1), steps, 3, pipe.send)], dtype=torch.float64, device=dev)
+        dist.all_reduce(gather_ms, op=dist.ReduceOp.MAX)
+        slab_bytes = 2.0 * w.m * (n1 - n0)
+        gather_alone = {"note": "with the SMs idle; inside the pipelined step the same transfers have measured faster",
+                        "ms": float(gather_ms.item()), "sent_bytes_per_gpu": slab_bytes * (world - 1),
+                        "gb_per_s_per_direction": slab_bytes * (world - 1) / (float(gather_ms.item()) * 1e-3) / 1e9}
     slab_n = o["b"].shape[0]
     local_flops = 2.0 * w.m * slab_n * w.k
     local_bytes = 2.0 * (w.m * w.k + slab_n * w.k + w.m * slab_n)
@@ -1041,7 +1118,10 @@ def run_ours(args) -> None:
                     "path": "vecops_operator_bridge_invoke_v1 (Operator -> MatmulRuntimeDispatch -> CudaExecutableProvider -> descriptor.run), pinned host buffers",
                     "resident": e2e["resident"], "copies": e2e["copies"]}
     else:
-        e2e = measure_e2e_sharded(w, o, host_inputs, step_launch, full, n0, n1, e2e_steps, 3, dev)
+        def whole_step():  # end to end is one step at a time: the gather is waited for before the read-back
+            step_launch()
+            step_join()
+        e2e = measure_e2e_sharded(w, o, host_inputs, whole_step, full_of, n0, n1, e2e_steps, 3, dev)
         e2e_note = {"path": "per rank: A and this rank's B slab copied in from pinned host memory, the sharded operator (slab GEMM + gather "
                             "onto every rank + barrier), this rank's columns of the gathered result read back to the host - the whole "
                             "result reaches the host once per step, 1/N of it per rank",
@@ -1064,6 +1144,10 @@ def run_ours(args) -> None:
         "gpu_launches": int(launches), "launches_per_step": launches_per_step, "clocks": clocks.summary(),
         "parity": parity, "device_status": status,
     }
+    if gather_alone is not None:
+        line["gather_alone"] = gather_alone
+    if trials:
+        line["config"]["gather_trials_ms_per_step"] = trials  # ten steps of each route before the measured run; the faster one was taken
     if world > 1:
         received = (world - 1) / world * w.m * w.n * 2.0
         line["scaling_ceiling"] = {"recv_bytes_per_gpu": received, "link_gbs_measured": NVLINK_RECEIVE_GBS,
@@ -1107,7 +1191,7 @@ def run_ours(args) -> None:
 
 
 def measure_e2e_sharded(w, o, host_inputs, step_launch, full, n0: int, n1: int, steps: int, warmup: int, dev) -> dict:
-    """One rank's share of the sharded operator end to end, one step at a time on the launch stream: copy A and this
+    """(`full` is a callable returning the gathered result of the step just run.)  One rank's share of the sharded operator end to end, one step at a time on the launch stream: copy A and this
     rank's slab of B in from pinned host memory, run the slab GEMM with its gather (and the barrier that orders the
     ranks), read this rank's columns of the GATHERED result back.  Every rank runs this at once."""
     import torch
@@ -1128,14 +1212,14 @@ def measure_e2e_sharded(w, o, host_inputs, step_launch, full, n0: int, n1: int, 
             o["a"].view(torch.int16).copy_(host_a.view(torch.int16), non_blocking=True)
             o["b"].view(torch.int16).copy_(host_b.view(torch.int16), non_blocking=True)
         step_launch()
-        stage.copy_(full[:, n0:n1])
+        stage.copy_(full()[:, n0:n1])
         if copy is not None:
             copy(host_c.data_ptr(), stage.data_ptr(), c_bytes, main)
         else:
             host_c.copy_(stage, non_blocking=True)
 
     ms = time_steps(step, steps, warmup, main)
-    if not torch.equal(host_c, full[:, n0:n1].cpu()):
+    if not torch.equal(host_c, full()[:, n0:n1].cpu()):
         raise RuntimeError("end-to-end read-back differs from the gathered device result")
     return {"ms_per_step": ms, "h2d_bytes_per_step": int(a_bytes + b_bytes), "d2h_bytes_per_step": int(c_bytes),
             "copies": "cudaMemcpyAsync from / to pinned host memory" + ("" if copy is not None else " (through torch)")}
@@ -1232,9 +1316,12 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=None)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--workload", default=None, help="override the workload (a name from vecops_b200.workloads.WORKLOADS)")
-    parser.add_argument("--gather", choices=["fused", "fused-peer", "nccl"], default="fused",
-                        help="how the sharded GEMM's output is gathered: fused = epilogue stores through the NVSwitch multicast address when "
-                             "there is one, else to every rank's peer pointer; fused-peer = peer pointers only; nccl = library collective")
+    parser.add_argument("--gather", choices=["auto", "fused", "fused-peer", "pipelined", "pipelined-ce", "nccl"], default="auto",
+                        help="how the sharded GEMM's output is gathered: auto = fused and pipelined-ce are both tried for ten steps and the "
+                             "faster one is measured; fused = epilogue stores through the NVSwitch multicast address when "
+                             "there is one, else to every rank's peer pointer; fused-peer = peer pointers only; pipelined = the slab is stored "
+                             "locally and pushed to the peers by this library's kernel on a second stream, behind the next step's GEMM "
+                             "(pipelined-ce: by the copy engines); nccl = library collective")
     parser.add_argument("--extra", choices=["attention", "pack", "f16", "quantized", "w8-size-curve"], default=None,
                         help="run ONLY this one of the extra single-GPU measurements and print its record (for profiling that kernel)")
     parser.add_argument("--no-extra", action="store_true", help="skip the brief measurements of the other single-GPU configurations")

@@ -401,6 +401,22 @@ VECOPS_B200_EXPORT int32_t vecops_b200_place_columns(void* dst, int64_t ldd, int
                                                      int64_t lds, int64_t rows, int64_t cols, uint32_t elem_size,
                                                      void* stream, VecopsError* error);
 
+/* The gather of a column-sharded product as a step of its own, for callers that run it BEHIND the next product
+ * (the slab GEMM stores locally at full speed; this call, on a second stream ordered after it by an event, sends the
+ * slab while the next GEMM computes).  Columns [col0, col0 + cols) of the local result src[rows, ld] are written to
+ * the same columns of every destination in `dst` - the peers' copies of the result, `count` <= 8 pointers this
+ * process can store through (symmetric memory, CUDA IPC), visited in the order given (start at the next rank so that
+ * no two senders begin on the same receiver).  Only stores cross GPUs.  Asynchronous on `stream`; the caller orders
+ * the ranks afterwards (a barrier on that stream) before anyone reads.
+ *   VECOPS_B200_PUSH_KERNEL       this library's kernel: every 16-byte piece is read once and stored to every destination
+ *                                 (16-byte aligned bases, pitch, col0 and cols);
+ *   VECOPS_B200_PUSH_COPY_ENGINE  one strided cudaMemcpy2DAsync per destination: no SM is used. */
+#define VECOPS_B200_PUSH_KERNEL 0u
+#define VECOPS_B200_PUSH_COPY_ENGINE 1u
+VECOPS_B200_EXPORT int32_t vecops_b200_push_columns(const void* src, void* const* dst, int32_t count, int64_t ld, int64_t col0,
+                                                    int64_t rows, int64_t cols, uint32_t elem_size, uint32_t route, void* stream,
+                                                    VecopsError* error);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

@@ -324,3 +324,23 @@ def test_caller_operators_bind_and_fail_loudly_without_a_gpu(library):
     assert library.vecops_operator_bridge_invoke_v1(batched, byref(wrong), 0, None, byref(error.record)) != capi.OK
     flat, keep3 = _frame([((16, 64), capi.DTYPE_BF16, False), ((32, 64), capi.DTYPE_BF16, False), ((16, 32), capi.DTYPE_F32, True)], 0x7f0000000000)
     assert library.vecops_operator_bridge_invoke_v1(batched, byref(flat), 0, None, byref(capi.ErrorBuffer().record)) != capi.OK
+
+
+def test_push_columns_checks_its_arguments_and_fails_loudly_without_a_gpu(library):
+    # argument checks come first and need no device; a well-formed push on a box without a GPU is an error, never a host copy
+    addresses = (ctypes.c_void_p * 2)(0x7f0000100000, 0x7f0000200000)
+    source = ctypes.c_void_p(0x7f0000000000)
+
+    def push(count=2, ld=1024, col0=256, rows=64, cols=256, elem=2, route=capi.PUSH_KERNEL, dst=addresses):
+        error = capi.ErrorBuffer()
+        return library.vecops_b200_push_columns(source, dst, count, ld, col0, rows, cols, elem, route, None, byref(error.record)), error.text.value
+
+    assert push(count=9)[0] == capi.INVALID_ARGUMENT
+    assert push(col0=900)[0] == capi.INVALID_ARGUMENT            # the slab would leave the row
+    assert push(route=5)[0] == capi.INVALID_ARGUMENT
+    assert push(dst=(ctypes.c_void_p * 2)(0x7f0000100000, 0x7f0000000000))[0] == capi.INVALID_ARGUMENT  # the source among the destinations
+    assert push(rows=0)[0] == capi.OK
+    if library.vecops_b200_device_count() == 0:
+        for route in (capi.PUSH_KERNEL, capi.PUSH_COPY_ENGINE):
+            rc, text = push(route=route)
+            assert rc == capi.EXECUTION_ERROR and b"no CPU fallback" in text

@@ -282,6 +282,60 @@ def test_fused_allgather_epilogue_stores_the_slab_into_every_destination(port, c
             assert bool((t[:, :col0] == -3).all()) and bool((t[:, col0 + n:] == -3).all())
 
 
+@pytest.mark.parametrize("route,lanes", [(K.PUSH_KERNEL, 1), (K.PUSH_COPY_ENGINE, 1), (K.PUSH_COPY_ENGINE, 2), (K.PUSH_KERNEL, 2)])
+def test_pipelined_gather_pushes_the_slab_behind_the_next_product(port, route, lanes):
+    # One GPU stands in for three ranks: rank 1's double-buffered result and two "peers'" results are three local
+    # tensors, the barrier is a no-op.  After every step the copy it filled must hold the slab at [col0, col0 + n) in
+    # the rank's own result AND in both peers', nothing else may have been touched, and five steps in a row (each
+    # result copy reused twice) must give the product of THAT step's operands.
+    from vecops_b200 import sharding
+    rng = np.random.default_rng(89)
+    m, n, k, n_total, col0 = 384, 512, 256, 1536, 512
+    a, b, _ = inputs("bf16", m, n, k, rng)
+    da, db = to_device(a, True), to_device(b, True)
+    results = [torch.full((2, m, n_total), -3.0, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    bases = [t.data_ptr() for t in results]  # indexed by rank: this rank is 1
+    gemm = sharding.PipelinedGatherGemm(da, db, results[1], bases, rank=1, col0=col0, barrier=lambda: None, route=route, lanes=lanes)
+    before = capi.library().vecops_b200_launch_count()
+    for step in range(5):
+        if step == 3:  # new operand values in place: later steps must follow them
+            a2, b2, _ = inputs("bf16", m, n, k, np.random.default_rng(90))
+            gemm.join()
+            torch.cuda.synchronize()
+            da.copy_(to_device(a2, True))
+            db.copy_(to_device(b2, True))
+            a, b = a2, b2
+        half = gemm.launch()
+        assert half == step % 2
+        gemm.join()
+        torch.cuda.synchronize()
+        want = port.matmul_bf16(a, b, None, True)
+        for t in results:
+            check("bf16", bf16_result_to_numpy(t[half][:, col0:col0 + n]), want)
+            assert bool((t[half][:, :col0] == -3).all()) and bool((t[half][:, col0 + n:] == -3).all())
+    expected = 5 * (1 + (lanes if route == K.PUSH_KERNEL else 0))  # the GEMM, and one push kernel per lane
+    assert capi.library().vecops_b200_launch_count() - before == expected
+    status, error = ctypes.c_uint32(1), capi.ErrorBuffer()
+    error.raise_for(capi.library().vecops_b200_take_device_status(0, ctypes.byref(status), ctypes.byref(error.record)))
+    assert status.value == 0
+
+
+def test_push_columns_refuses_what_it_cannot_send():
+    src = torch.zeros((8, 64), dtype=torch.bfloat16, device="cuda")
+    dst = torch.zeros((8, 64), dtype=torch.bfloat16, device="cuda")
+    error = capi.ErrorBuffer()
+    lib = capi.library()
+    one = (ctypes.c_void_p * 1)(dst.data_ptr())
+    same = (ctypes.c_void_p * 1)(src.data_ptr())
+    nine = (ctypes.c_void_p * 9)(*[dst.data_ptr()] * 9)
+    assert lib.vecops_b200_push_columns(src.data_ptr(), nine, 9, 64, 0, 8, 64, 2, K.PUSH_KERNEL, None, ctypes.byref(error.record)) == capi.INVALID_ARGUMENT
+    assert lib.vecops_b200_push_columns(src.data_ptr(), same, 1, 64, 0, 8, 64, 2, K.PUSH_KERNEL, None, ctypes.byref(error.record)) == capi.INVALID_ARGUMENT
+    assert lib.vecops_b200_push_columns(src.data_ptr(), one, 1, 64, 32, 8, 64, 2, K.PUSH_KERNEL, None, ctypes.byref(error.record)) == capi.INVALID_ARGUMENT
+    assert lib.vecops_b200_push_columns(src.data_ptr(), one, 1, 64, 4, 8, 8, 2, K.PUSH_KERNEL, None, ctypes.byref(error.record)) == capi.INVALID_ARGUMENT  # 8-byte offset
+    assert lib.vecops_b200_push_columns(src.data_ptr(), one, 1, 64, 0, 8, 64, 2, 7, None, ctypes.byref(error.record)) == capi.INVALID_ARGUMENT
+    assert lib.vecops_b200_push_columns(src.data_ptr(), one, 1, 64, 0, 0, 64, 2, K.PUSH_KERNEL, None, ctypes.byref(error.record)) == capi.OK
+
+
 def test_int32_accumulators_wrap_like_the_reference(port):
     # K = 262145 of 127*127 (and 255*255) overflows int32 and must wrap (tests/ops/MatmulTest.cpp:1025-1055)
     k = 262145

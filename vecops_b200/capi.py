@@ -119,6 +119,7 @@ class VecopsB200Gather(Structure):
                 ("col0", c_int64), ("flags", c_uint32), ("reserved", c_uint32)]
 
 
+PUSH_KERNEL, PUSH_COPY_ENGINE = 0, 1
 GATHER_MULTICAST = 1
 
 
@@ -184,5 +185,7 @@ def library() -> ctypes.CDLL:
         lib.vecops_b200_take_device_status.argtypes = [c_int32, POINTER(c_uint32), e]
         lib.vecops_b200_place_columns.argtypes = [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
                                                   c_uint32, c_void_p, e]
+        lib.vecops_b200_push_columns.argtypes = [c_void_p, POINTER(c_void_p), c_int32, c_int64, c_int64, c_int64, c_int64,
+                                                 c_uint32, c_uint32, c_void_p, e]
         _LIB = lib
     return _LIB

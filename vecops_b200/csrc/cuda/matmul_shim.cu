@@ -1660,4 +1660,66 @@ int32_t vecops_b200_place_columns(void* dst, int64_t ldd, int64_t col0, const vo
   return VECOPS_STATUS_OK;
 }
 
+int32_t vecops_b200_push_columns(const void* src, void* const* dst, int32_t count, int64_t ld, int64_t col0, int64_t rows,
+                                 int64_t cols, uint32_t elem_size, uint32_t route, void* stream, VecopsError* error) {
+  if (rows == 0 || cols == 0 || count == 0) return VECOPS_STATUS_OK;
+  if (src == nullptr || dst == nullptr || count < 0 || count > 8 || rows < 0 || cols < 0 || col0 < 0 || elem_size == 0 ||
+      col0 + cols > ld)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "push_columns: null pointer, more than 8 destinations or a bad extent");
+  if (route != VECOPS_B200_PUSH_KERNEL && route != VECOPS_B200_PUSH_COPY_ENGINE)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "push_columns: unknown route");
+  const int64_t e = elem_size;
+  bool aligned = aligned16(src) && (ld * e) % 16 == 0 && (col0 * e) % 16 == 0 && (cols * e) % 16 == 0;
+  for (int d = 0; d < count; ++d) {
+    if (dst[d] == nullptr || dst[d] == src)
+      return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "push_columns: a destination is null or is the source itself");
+    aligned = aligned && aligned16(dst[d]);
+  }
+  if (route == VECOPS_B200_PUSH_KERNEL && !aligned)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "push_columns needs 16-byte aligned slabs and pitches");
+  if (vecops_b200_device_count() == 0)
+    return set_error(error, VECOPS_STATUS_EXECUTION_ERROR, "no usable CUDA device; there is no CPU fallback");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (route == VECOPS_B200_PUSH_COPY_ENGINE) {
+    // one strided copy per destination, in the caller's order, on the caller's stream
+    for (int d = 0; d < count; ++d) {
+      cudaError_t status = cudaMemcpy2DAsync(static_cast<char*>(dst[d]) + col0 * e, static_cast<size_t>(ld * e),
+                                             static_cast<const char*>(src) + col0 * e, static_cast<size_t>(ld * e),
+                                             static_cast<size_t>(cols * e), static_cast<size_t>(rows), cudaMemcpyDefault, s);
+      if (status != cudaSuccess) return cuda_fail(error, status, "push_columns copy");
+    }
+    return VECOPS_STATUS_OK;
+  }
+  PushTargets targets{};
+  targets.count = count;
+  for (int d = 0; d < count; ++d) targets.dst[d] = static_cast<uint4*>(dst[d]);
+  // At most one CTA per SM (see the kernel): a second one would keep a GEMM's CTAs off the SM until the push had finished.
+  // A kernel without shared memory would also ask for the L1-heavy split of the SM's unified memory, which an SM cannot
+  // hold together with the GEMM's split: prefer the shared one.
+  static std::atomic<unsigned> configured{0};
+  static int sm_count[32] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  if (device < 0 || device >= 32) device = 0;
+  if (!(configured.load() & (1u << device))) {
+    cudaFuncSetAttribute(push_columns_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaDeviceGetAttribute(&sm_count[device], cudaDevAttrMultiProcessorCount, device);
+    configured.fetch_or(1u << device);
+  }
+  long long limit = sm_count[device] > 0 ? sm_count[device] : 148;
+  if (const char* text = std::getenv("VECOPS_B200_PUSH_BLOCKS")) {
+    const long long asked = std::atoll(text);
+    if (asked >= 1 && asked <= limit) limit = asked;
+  }
+  if (rows > 0x7fffffff || cols * e / 16 > 0x7fffffff)
+    return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "push_columns: extent too large");
+  const int blocks = static_cast<int>(rows < limit ? rows : limit);
+  push_columns_kernel<<<blocks, 256, 0, s>>>(static_cast<const uint4*>(src), targets, ld * e / 16, col0 * e / 16,
+                                             static_cast<int>(rows), static_cast<int>(cols * e / 16));
+  g_launches.fetch_add(1);
+  cudaError_t status = cudaGetLastError();
+  if (status != cudaSuccess) return cuda_fail(error, status, "push_columns launch");
+  return VECOPS_STATUS_OK;
+}
+
 }  // extern "C"

@@ -538,4 +538,38 @@ __global__ void place_columns_kernel(uint4* __restrict__ dst, long long dst_pitc
   }
 }
 
+// Up to eight destinations of one push, passed by value.
+struct PushTargets {
+  uint4* dst[8];
+  int count;
+};
+
+// Columns [col0, col0 + cols) of src[rows, pitch] go to the same position of every destination: each 16-byte piece is
+// read once and stored `count` times.  A CTA takes whole rows; four pieces per thread are in flight before the first
+// store leaves.  Only stores reach the destinations.
+//
+// Sized to run BESIDE a tensor-core GEMM that fills the SMs: that kernel's CTA leaves 1.7 KB of an SM's shared memory
+// (every CTA reserves 1 KB even when it declares none) and 2560 registers in two of the SM's four register
+// partitions, so exactly one CTA of 256 threads at no more than 40 registers fits next to it - hence 256 threads,
+// 32 registers, and a grid of at most one CTA per SM.
+__global__ void __launch_bounds__(256, 8) push_columns_kernel(const uint4* __restrict__ src, PushTargets targets, long long pitch16,
+                                                              long long col0_16, int rows, int cols16) {
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const long long row_at = r * pitch16 + col0_16;
+    const uint4* from = src + row_at;
+    for (int j0 = threadIdx.x; j0 < cols16; j0 += 4 * 256) {
+      uint4 piece[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (j0 + u * 256 < cols16) piece[u] = __ldcs(from + j0 + u * 256);
+      for (int d = 0; d < targets.count; ++d) {
+        uint4* to = targets.dst[d] + row_at;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (j0 + u * 256 < cols16) to[j0 + u * 256] = piece[u];
+      }
+    }
+  }
+}
+
 }  // namespace vb200

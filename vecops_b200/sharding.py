@@ -113,10 +113,104 @@ class FusedGatherGemm:
             self.error.raise_for(rc)
 
 
-def symmetric_result(m: int, n: int, dtype, device, group=None):
-    """Allocate the full [M, N] result in symmetric memory; returns (tensor, handle) with handle.buffer_ptrs = every rank's copy."""
+class PipelinedGatherGemm:
+    """The column-sharded product with its gather run BEHIND the next product.
+
+    Two copies of the full [M, N] result live in symmetric memory and steps alternate between them.  Step i: the slab
+    GEMM stores this rank's columns into its own copy at full speed (compute stream); an event later, on a second
+    stream, the slab is pushed to the same columns of every peer's copy (vecops_b200_push_columns, peers visited from
+    the next rank on) and one device barrier orders the ranks - while the compute stream is already running the GEMM
+    of step i+1.  A copy is written again two steps later, after its own push and barrier have finished.
+
+    `results` is the symmetric [2, M, N] tensor, `peer_bases` every rank's base address of it as seen from here
+    (handle.buffer_ptrs), `barrier` a callable that enqueues the ranks' device barrier on the CURRENT torch stream.
+    """
+
+    def __init__(self, a, b_slab, results, peer_bases, rank: int, col0: int, barrier: Callable, compute_stream=None,
+                 route: int = 0, lanes: int = 1) -> None:
+        import ctypes
+
+        import torch
+
+        from . import capi, harness
+        if results.dim() != 3 or results.shape[0] != 2:
+            raise ValueError("results must be [2, M, N]")
+        world = len(peer_bases)
+        m, n_total = results.shape[1], results.shape[2]
+        n = b_slab.shape[0]
+        self.device = a.device
+        self.compute = compute_stream if compute_stream is not None else torch.cuda.current_stream(a.device)
+        self.send = torch.cuda.Stream(a.device)
+        self.results, self.barrier, self.route = results, barrier, route
+        self.prepared = [harness.PreparedMatmul(a, b_slab, results[half][:, col0:col0 + n], None, stream=self.compute) for half in (0, 1)]
+        half_bytes = m * n_total * results.element_size()
+        order = [(rank + 1 + j) % world for j in range(world - 1)]
+        self.peers = [(ctypes.c_void_p * max(1, len(order)))(*[int(peer_bases[r]) + half * half_bytes for r in order]) for half in (0, 1)]
+        self.count = len(order)
+        # `lanes` > 1: the peers are dealt over that many side streams, so that copies to different peers overlap
+        self.lanes = max(1, min(lanes, self.count))
+        self.single = [[(ctypes.c_void_p * 1)(int(peer_bases[r]) + half * half_bytes) for r in order] for half in (0, 1)]
+        self.lane_streams = [torch.cuda.Stream(a.device) for _ in range(self.lanes)] if self.lanes > 1 else []
+        self.fork = torch.cuda.Event()
+        self.lane_done = [torch.cuda.Event() for _ in self.lane_streams]
+        self.shape = (n_total, col0, m, n, results.element_size())
+        self.computed = [torch.cuda.Event(), torch.cuda.Event()]
+        self.gathered = [torch.cuda.Event(), torch.cuda.Event()]
+        self.steps = 0
+        self.error = capi.ErrorBuffer()
+        self._push = capi.library().vecops_b200_push_columns
+
+    def launch(self) -> int:
+        """Enqueue one step; returns which copy of the result it fills (complete on every rank once `join` has been
+        waited for, or once the NEXT step using that copy starts)."""
+        half = self.steps & 1
+        if self.steps >= 2:
+            self.compute.wait_event(self.gathered[half])  # the push that read this copy two steps ago has finished
+        self.prepared[half].launch()
+        self.computed[half].record(self.compute)
+        self.send.wait_event(self.computed[half])
+        self.gather_alone(half)
+        self.gathered[half].record(self.send)
+        self.steps += 1
+        return half
+
+    def gather_alone(self, half: int = 0) -> None:
+        """Enqueue only the push and the barrier of one copy on the send stream (for timing the transfer by itself)."""
+        import ctypes
+
+        import torch
+        ld, col0, rows, cols, elem = self.shape
+        source, error = self.results[half].data_ptr(), ctypes.byref(self.error.record)
+
+        def push(pointers, count, stream):
+            rc = self._push(source, pointers, count, ld, col0, rows, cols, elem, self.route, stream.cuda_stream, error)
+            if rc != 0:
+                self.error.raise_for(rc)
+
+        if self.count and self.lanes <= 1:
+            push(self.peers[half], self.count, self.send)
+        elif self.count:
+            self.fork.record(self.send)
+            for lane, stream in enumerate(self.lane_streams):
+                stream.wait_event(self.fork)
+                for j in range(lane, self.count, self.lanes):
+                    push(self.single[half][j], 1, stream)
+                self.lane_done[lane].record(stream)
+                self.send.wait_event(self.lane_done[lane])
+        with torch.cuda.stream(self.send):
+            self.barrier()
+
+    def join(self) -> None:
+        """The compute stream waits for the gather of the last step enqueued."""
+        if self.steps:
+            self.compute.wait_event(self.gathered[(self.steps - 1) & 1])
+
+
+def symmetric_result(m: int, n: int, dtype, device, group=None, copies: int = 0):
+    """Allocate the full [M, N] result (or `copies` of it, [copies, M, N]) in symmetric memory; returns (tensor, handle)
+    with handle.buffer_ptrs = every rank's base address of it."""
     import torch.distributed as dist
     import torch.distributed._symmetric_memory as symm_mem
-    tensor = symm_mem.empty((m, n), dtype=dtype, device=device)
+    tensor = symm_mem.empty((copies, m, n) if copies else (m, n), dtype=dtype, device=device)
     handle = symm_mem.rendezvous(tensor, group if group is not None else dist.group.WORLD)
     return tensor, handle
