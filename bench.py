@@ -934,6 +934,25 @@ def run_ours(args) -> None:
     n0, n1 = sharding.column_partition(w.n, world, rank)
     operands, host_inputs = device_sets(w, 1, dev, n0, n1)
     o = operands[0]
+    a_peers = None
+    if world > 1:
+        # A lives in symmetric memory, so that the end-to-end step can copy in ONE row slice of A per rank and replicate
+        # it over NVLink instead of pulling the whole of A over every rank's PCIe link
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            a_sym = symm_mem.empty(tuple(o["a"].shape), dtype=o["a"].dtype, device=dev)
+            a_handle = symm_mem.rendezvous(a_sym, dist.group.WORLD)
+            a_sym.copy_(o["a"])
+            o["a"] = a_sym
+            a_peers = {"handle": a_handle, "bases": [int(p) for p in a_handle.buffer_ptrs], "rank": rank, "world": world}
+            built = 1
+        except Exception as error:
+            print(f"[bench] symmetric A unavailable on rank {rank}: {error!r}", file=sys.stderr)
+            built = 0
+        same = torch.tensor([built], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        if int(same.item()) == 0:
+            a_peers = None
     prepared = [harness.PreparedMatmul(o["a"], o["b"], o["c"], None, stream=stream)]  # the slab GEMM alone (roofline)
     full = pipe = full_of = None
     trials = {}
@@ -1110,7 +1129,7 @@ def run_ours(args) -> None:
     value = w.flops / (ms * 1e-3) / 1e12
 
     # end to end through the operator bridge with host buffers
-    e2e_steps = max(1, min(steps, 12 if world == 1 else 3))  # enough steps that filling the three-stream pipeline is not a third of the figure
+    e2e_steps = max(1, min(steps, 12 if world == 1 else 8))  # enough steps that filling the three-stream pipeline is not a third of the figure
     if world == 1:
         e2e = measure_e2e(w, operands, host_inputs, e2e_steps, 3, dev)
         e2e_note = {"serial_ms_per_step": e2e["serial_ms_per_step"], "serial_value": w.flops / (e2e["serial_ms_per_step"] * 1e-3) / 1e12,
@@ -1121,10 +1140,10 @@ def run_ours(args) -> None:
         def whole_step():  # end to end is one step at a time: the gather is waited for before the read-back
             step_launch()
             step_join()
-        e2e = measure_e2e_sharded(w, o, host_inputs, whole_step, full_of, n0, n1, e2e_steps, 3, dev)
-        e2e_note = {"path": "per rank: A and this rank's B slab copied in from pinned host memory, the sharded operator (slab GEMM + gather "
-                            "onto every rank + barrier), this rank's columns of the gathered result read back to the host - the whole "
-                            "result reaches the host once per step, 1/N of it per rank",
+        e2e = measure_e2e_sharded(w, o, host_inputs, whole_step, full_of, n0, n1, e2e_steps, 3, dev, a_peers)
+        e2e_note = {"path": "per rank: " + e2e["a_route"] + " and this rank's B slab copied in from pinned host memory, the sharded operator "
+                            "(slab GEMM + gather onto every rank + barrier), this rank's columns of the gathered result read back to the "
+                            "host - the whole result reaches the host once per step, 1/N of it per rank",
                     "gather": "inside the timed region", "copies": e2e["copies"]}
     e2e_ms = torch.tensor([e2e["ms_per_step"]], dtype=torch.float64, device=dev)
     if world > 1:
@@ -1190,38 +1209,97 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
-def measure_e2e_sharded(w, o, host_inputs, step_launch, full, n0: int, n1: int, steps: int, warmup: int, dev) -> dict:
-    """(`full` is a callable returning the gathered result of the step just run.)  One rank's share of the sharded operator end to end, one step at a time on the launch stream: copy A and this
-    rank's slab of B in from pinned host memory, run the slab GEMM with its gather (and the barrier that orders the
-    ranks), read this rank's columns of the GATHERED result back.  Every rank runs this at once."""
+def measure_e2e_sharded(w, o, host_inputs, step_launch, full, n0: int, n1: int, steps: int, warmup: int, dev, a_peers=None) -> dict:
+    """One rank's share of the sharded operator end to end; every rank runs this at once.  Copy in from pinned host memory,
+    run the slab GEMM with its gather (and the barrier that orders the ranks), read this rank's columns of the GATHERED
+    result back - on a second stream, so that a step's read-back overlaps the next step's copy-in; the clock stops when the
+    last result is on the host.  `full` is a callable returning the gathered result of the step
+    just run.
+
+    The inputs of a step are A, once, and B, once.  With `a_peers` (A in symmetric memory) each rank copies in its 1/N
+    row slice of A and its slab of B, pushes the slice into every peer's A over NVLink (copy engines) and a device barrier
+    orders the ranks before the GEMM: A crosses PCIe once per step in total, not once per rank.  Without it every rank
+    pulls the whole of A over its own link."""
     import torch
+    from vecops_b200 import capi
     a0, b0, _ = host_inputs
     copy = async_copier()
-    host_a = torch.from_numpy(a0).pin_memory()
+    main = torch.cuda.current_stream(dev)
+    k_bytes = o["a"].shape[1] * o["a"].element_size()
+    if a_peers is not None and copy is not None:
+        rank, world = a_peers["rank"], a_peers["world"]
+        r0, r1 = w.m * rank // world, w.m * (rank + 1) // world
+        order = [(rank + 1 + j) % world for j in range(world - 1)]
+        peers = (ctypes.c_void_p * len(order))(*[a_peers["bases"][r] + r0 * k_bytes for r in order])
+        error = capi.ErrorBuffer()
+        push = capi.library().vecops_b200_push_columns
+        a_route = f"rows [{r0}, {r1}) of A (1/{world} of it; the slice is then pushed into every peer's A over NVLink by the copy engines, one device barrier)"
+    else:
+        a_peers, r0, r1 = None, 0, w.m
+        a_route = "the whole of A"
+    host_a = torch.from_numpy(np.ascontiguousarray(a0[r0:r1])).pin_memory()
     host_b = torch.from_numpy(b0).pin_memory()
     stage = torch.empty((w.m, n1 - n0), dtype=torch.bfloat16, device=dev)  # the rank's columns, made contiguous for the read-back
     host_c = torch.empty((w.m, n1 - n0), dtype=torch.bfloat16).pin_memory()
-    main = torch.cuda.current_stream(dev)
     a_bytes, b_bytes, c_bytes = (t.numel() * t.element_size() for t in (host_a, host_b, host_c))
+    a_slice_ptr = o["a"].data_ptr() + r0 * k_bytes
+    # the read-back of a step runs on a second stream, so that it shares the PCIe link (full duplex) with the next step's copy-in
+    side = torch.cuda.Stream(dev)
+    staged, read = torch.cuda.Event(), torch.cuda.Event()
+    state = {"used": False}
 
     def step(_):
         if copy is not None:
-            copy(o["a"].data_ptr(), host_a.data_ptr(), a_bytes, main)
+            copy(a_slice_ptr, host_a.data_ptr(), a_bytes, main)
             copy(o["b"].data_ptr(), host_b.data_ptr(), b_bytes, main)
         else:
             o["a"].view(torch.int16).copy_(host_a.view(torch.int16), non_blocking=True)
             o["b"].view(torch.int16).copy_(host_b.view(torch.int16), non_blocking=True)
+        if a_peers is not None:
+            rc = push(a_slice_ptr, peers, len(order), o["a"].shape[1], 0, r1 - r0, o["a"].shape[1], o["a"].element_size(),
+                      capi.PUSH_COPY_ENGINE, main.cuda_stream, byref(error.record))
+            if rc != 0:
+                error.raise_for(rc)
+            a_peers["handle"].barrier(channel=0)  # every rank's slice has landed in this rank's A
         step_launch()
+        if state["used"]:
+            main.wait_event(read)  # the previous step's read-back has left `stage`
         stage.copy_(full()[:, n0:n1])
+        staged.record(main)
+        side.wait_event(staged)
         if copy is not None:
-            copy(host_c.data_ptr(), stage.data_ptr(), c_bytes, main)
+            copy(host_c.data_ptr(), stage.data_ptr(), c_bytes, side)
         else:
-            host_c.copy_(stage, non_blocking=True)
+            with torch.cuda.stream(side):
+                host_c.copy_(stage, non_blocking=True)
+        read.record(side)
+        state["used"] = True
 
-    ms = time_steps(step, steps, warmup, main)
+    def timed(count: int) -> float:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(main)
+        for i in range(count):
+            step(i)
+        main.wait_event(read)  # the last result has reached the host before the clock stops
+        stop.record(main)
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / count
+
+    if a_peers is not None:
+        # the replication itself is checked: A is cleared on the device, one step rebuilds it from the ranks' slices
+        torch.cuda.synchronize()
+        a_peers["handle"].barrier(channel=0)
+        o["a"].zero_()
+        torch.cuda.synchronize()
+        a_peers["handle"].barrier(channel=0)
+        torch.cuda.synchronize()
+    timed(warmup)
+    ms = timed(steps)
     if not torch.equal(host_c, full()[:, n0:n1].cpu()):
         raise RuntimeError("end-to-end read-back differs from the gathered device result")
-    return {"ms_per_step": ms, "h2d_bytes_per_step": int(a_bytes + b_bytes), "d2h_bytes_per_step": int(c_bytes),
+    if a_peers is not None and not torch.equal(o["a"].view(torch.int16).cpu(), torch.from_numpy(a0.view(np.int16) if a0.dtype != np.int16 else a0)):
+        raise RuntimeError("A rebuilt from the ranks' row slices differs from the host's A")
+    return {"ms_per_step": ms, "h2d_bytes_per_step": int(a_bytes + b_bytes), "d2h_bytes_per_step": int(c_bytes), "a_route": a_route,
             "copies": "cudaMemcpyAsync from / to pinned host memory" + ("" if copy is not None else " (through torch)")}
 
 
