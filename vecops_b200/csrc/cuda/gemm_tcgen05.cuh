@@ -580,12 +580,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         break;
       }
       tcgen05_fence_after_sync();
+      const bool timeline = round == 0 && item.slices > 1 && warp == 2 && lane == 0;  // the exchange of a launch whose only round is split
+      if (timeline) mark(3);
       const int row0 = tm * kTileM + static_cast<int>(pair_rank) * G::kBlockM + quarter * 32;
       const int row = row0 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * G::kBlockN;
       constexpr int kSlabs = G::kBlockN / kOutCols;
       int slab_begin = 0, slab_end = kSlabs;
-      // partial accumulators of one split tile: [slice][column][row] 32-bit words, rows contiguous
+      // partial accumulators of one split tile: [slice][column][row] 32-bit words, rows contiguous: the 32 lanes of a
+      // warp write (and read) one column's 128 contiguous bytes per instruction.  (The transposed layout - a thread's 32
+      // columns contiguous, 16-byte accesses - was measured: every instruction then touches 32 lines, and the exchange
+      // took twice as long.)
       const size_t tile_words = static_cast<size_t>(G::kBlockN) * G::kBlockM;
       uint32_t* my_partial = nullptr;
       // scratch slot of slice `s` of this tile (of this CTA's half of it, for a pair)
@@ -598,30 +603,43 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         slab_begin = kSlabs * item.slice / item.slices;
         slab_end = kSlabs * (item.slice + 1) / item.slices;
         my_partial = partials + slot_of(item.slice) * tile_words + quarter * 32 + lane;
-        for (int chunk = 0; chunk < G::kBlockN / 32; ++chunk) {
+        auto goes_out = [&](int chunk) {  // warp-uniform: the chunk belongs to another slice's columns
           const int owner_slab = chunk * 32 / kOutCols;
-          if (owner_slab >= slab_begin && owner_slab < slab_end) continue;
-          uint32_t v[32];
-          tmem_load_32x32(taddr + chunk * 32, v);
-          tmem_load_wait();
+          return owner_slab < slab_begin || owner_slab >= slab_end;
+        };
+        auto store_chunk = [&](int chunk, const uint32_t (&v)[32]) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (row < M) __stcg(my_partial + static_cast<size_t>(chunk * 32 + j) * G::kBlockM, v[j]);  // rows past M are never stored
+          for (int j = 0; j < 32; ++j) __stcg(my_partial + static_cast<size_t>(chunk * 32 + j) * G::kBlockM, v[j]);
+        };
+        // two chunks per tensor-memory wait: the second read-back overlaps the first chunk's stores
+        for (int chunk = 0; chunk < G::kBlockN / 32; chunk += 2) {
+          const bool first = goes_out(chunk), second = goes_out(chunk + 1);
+          if (!first && !second) continue;
+          uint32_t v0[32], v1[32];
+          if (first) tmem_load_32x32(taddr + chunk * 32, v0);
+          if (second) tmem_load_32x32(taddr + (chunk + 1) * 32, v1);
+          tmem_load_wait();
+          if (row < M) {  // rows past M are never stored
+            if (first) store_chunk(chunk, v0);
+            if (second) store_chunk(chunk + 1, v1);
+          }
         }
         __threadfence();
         __syncwarp();
+        if (timeline) mark(4);
         // every other slice reads this slice's partial sums: the flag counts those readers down (see ptx.cuh)
         const unsigned readers = static_cast<unsigned>(item.slices - 1);
         if (lane == 0) st_release_gpu_u64(flags + slot_of(item.slice) * 4 + quarter, nonce + readers);
-        for (int other = 0; other < item.slices; ++other) {
-          if (other == item.slice) continue;
-          if (!wait_flag_window_u64(flags + slot_of(other) * 4 + quarter, nonce, readers, abort_flag)) {
-            report_status(status, kStatusEpilogueWait);
-            *abort_flag = 1;
-            epilogue_ok = false;
-          }
+        // lane s polls slice s's flag: all the flags are waited for at once, not one round trip after the other
+        const bool polls = lane < item.slices && lane != item.slice;
+        const bool seen = !polls || wait_flag_window_u64(flags + slot_of(lane) * 4 + quarter, nonce, readers, abort_flag);
+        if (!__all_sync(0xffffffffu, seen)) {
+          report_status(status, kStatusEpilogueWait);
+          *abort_flag = 1;
+          epilogue_ok = false;
         }
         if (!epilogue_ok) break;
+        if (timeline) mark(5);
       }
       // adds the other slices' partial sums of 32 columns starting at `first_col` (column inside the tile)
       auto add_partials = [&](uint32_t (&v)[32], int first_col) {
@@ -764,6 +782,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       }
       if (item.slices > 1) {
         // this warp has read all it needs of the other slices' partial sums
+        if (timeline) mark(6);
         __syncwarp();
         if (lane == 0)
           for (int other = 0; other < item.slices; ++other)
