@@ -982,10 +982,11 @@ def run_ours(args) -> None:
             return {"launch": launch, "join": lambda: None, "full": lambda: result, "mode": mode, "launches_per_step": 1,
                     "buffers": result, "pipe": None, "keep": (gemm, hdl)}
 
-        def pipelined_route(by_kernel: bool):
-            """The slab stored locally, pushed to the peers on a second stream behind the next step's GEMM."""
+        def pipelined_route(by_kernel: bool, lanes: int = 1):
+            """The slab stored locally, pushed to the peers on a second stream behind the next step's GEMM (`lanes`:
+            how many of the copy-engine copies to different peers are in flight at once, each on a stream of its own)."""
             results, hdl = sharding.symmetric_result(w.m, w.n, torch.bfloat16, dev, copies=2)
-            lanes = 1 if by_kernel else int(os.environ.get("VECOPS_B200_PUSH_LANES", "1"))
+            lanes = 1 if by_kernel else int(os.environ.get("VECOPS_B200_PUSH_LANES", str(lanes)))
             gemm = sharding.PipelinedGatherGemm(o["a"], o["b"], results, [int(p) for p in hdl.buffer_ptrs], rank, n0,
                                                 barrier=lambda: hdl.barrier(channel=0), compute_stream=stream,
                                                 route=capi.PUSH_KERNEL if by_kernel else capi.PUSH_COPY_ENGINE, lanes=lanes)
@@ -997,7 +998,9 @@ def run_ours(args) -> None:
 
         makers = {"fused": lambda: fused_route(True), "fused-peer": lambda: fused_route(False),
                   "pipelined": lambda: pipelined_route(True), "pipelined-ce": lambda: pipelined_route(False)}
-        # auto: both ways of hiding the gather are tried for a few steps on this machine and the faster one is measured
+        # auto: both ways of hiding the gather are tried for a few steps on this machine and the faster one is measured.
+        # (Copies to several peers in flight at once, VECOPS_B200_PUSH_LANES > 1, are not a candidate: 3 % faster than one
+        # at a time in one 8-GPU run, 15-25 % slower in every 4-GPU run and twice as slow in another 8-GPU run.)
         wanted = ["fused", "pipelined-ce"] if args.gather == "auto" else [args.gather] if args.gather in makers else []
         routes, trials = {}, {}
         for key in wanted:
