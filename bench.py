@@ -48,8 +48,10 @@ NCU_TRAFFIC = {
 }
 # What a GPU can receive when all eight send to all eight at once: a store-only all-to-all probe on this pool
 # (148 CTAs per GPU issuing the epilogue's own 32-row x 128-byte TMA stores to the seven peers) measured 668 GB/s per
-# direction per GPU.  Not measured in this run; it bounds "result gathered on every rank" from below.
+# direction per GPU; a copy-engine copy between two GPUs 770.  Not measured in this run; they bound "result gathered on
+# every rank" from below (the pipelined gather has run ten steps at 685 GB/s into every GPU, between the two).
 NVLINK_RECEIVE_GBS = 668.0
+NVLINK_PEER_COPY_GBS = 770.0
 BURST_BELOW_MS = 5.0  # kernels shorter than this are held to the burst cuBLAS figure, longer ones to the sustained one
 
 
@@ -1174,8 +1176,11 @@ def run_ours(args) -> None:
         received = (world - 1) / world * w.m * w.n * 2.0
         line["scaling_ceiling"] = {"recv_bytes_per_gpu": received, "link_gbs_measured": NVLINK_RECEIVE_GBS,
                                    "floor_ms": received / (NVLINK_RECEIVE_GBS * 1e9) * 1e3,
-                                   "note": "gathering the result on every rank makes each GPU receive (N-1)/N of it per step; the link figure "
-                                           "is a store-only all-to-all probe on this pool, not taken in this run"}
+                                   "peer_copy_gbs_measured": NVLINK_PEER_COPY_GBS,
+                                   "floor_ms_at_peer_copy_rate": received / (NVLINK_PEER_COPY_GBS * 1e9) * 1e3,
+                                   "achieved_gbs_into_every_gpu": received / (ms * 1e-3) / 1e9,
+                                   "note": "gathering the result on every rank makes each GPU receive (N-1)/N of it per step; the link figures "
+                                           "are a store-only all-to-all probe and a copy between two GPUs on this pool, not taken in this run"}
 
     if rank == 0 and world == 1:
         try:
