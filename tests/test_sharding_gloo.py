@@ -27,6 +27,19 @@ def test_partition_covers_all_columns_in_whole_tiles():
         sharding.column_partition(10, 2, 2)
 
 
+def test_peer_order_gives_every_receiver_one_sender_per_phase():
+    # the pipelined gather sends a rank's slab to its peers one after the other: in phase j the senders must hit
+    # distinct receivers, nobody sends to itself, and over all phases everybody reaches everybody else once
+    for world in (1, 2, 3, 4, 8):
+        orders = [sharding.peer_order(r, world) for r in range(world)]
+        for r, order in enumerate(orders):
+            assert sorted(order) == [p for p in range(world) if p != r]
+        for phase in range(world - 1):
+            assert sorted(order[phase] for order in orders) == list(range(world))
+    with pytest.raises(ValueError):
+        sharding.peer_order(2, 2)
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -113,6 +113,14 @@ class FusedGatherGemm:
             self.error.raise_for(rc)
 
 
+def peer_order(rank: int, world: int) -> list[int]:
+    """The order in which `rank` sends to its peers: from the next rank on, wrapping round.  In phase j every rank r
+    sends to (r + 1 + j) mod world, so each receiver has exactly one sender per phase when the ranks run in step."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} of {world}")
+    return [(rank + 1 + j) % world for j in range(world - 1)]
+
+
 class PipelinedGatherGemm:
     """The column-sharded product with its gather run BEHIND the next product.
 
@@ -144,7 +152,7 @@ class PipelinedGatherGemm:
         self.results, self.barrier, self.route = results, barrier, route
         self.prepared = [harness.PreparedMatmul(a, b_slab, results[half][:, col0:col0 + n], None, stream=self.compute) for half in (0, 1)]
         half_bytes = m * n_total * results.element_size()
-        order = [(rank + 1 + j) % world for j in range(world - 1)]
+        order = peer_order(rank, world)
         self.peers = [(ctypes.c_void_p * max(1, len(order)))(*[int(peer_bases[r]) + half * half_bytes for r in order]) for half in (0, 1)]
         self.count = len(order)
         # `lanes` > 1: the peers are dealt over that many side streams, so that copies to different peers overlap
