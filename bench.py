@@ -1355,7 +1355,9 @@ def measure_w8_size_curve(dev, peaks, steps: int = 60, warmup: int = 6) -> dict:
     from vecops_b200 import harness
     k, rows = 4096, []
     stream = torch.cuda.current_stream(dev)
-    for n in (14336, 28672, 57344, 114688, 229376):
+    # VECOPS_B200_SIZE_CURVE_MULTIPLES="16" (or "1,4"): only these multiples of C4's N, e.g. to profile one size
+    multiples = [int(x) for x in os.environ.get("VECOPS_B200_SIZE_CURVE_MULTIPLES", "1,2,4,8,16").split(",") if x.strip()]
+    for n in [14336 * f for f in multiples]:
         sets = max(2, int(np.ceil(260e6 / (n * k))) + 1)
         weights = [torch.randint(-127, 128, (n, k), dtype=torch.int8, device=dev) for _ in range(sets)]
         scale = torch.rand(n, device=dev) * 0.02 + 0.001
