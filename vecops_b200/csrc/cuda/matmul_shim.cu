@@ -954,7 +954,8 @@ int32_t launch_f32_tf32x3(const VecopsB200Matmul& p, const DeviceState& dev, cud
   float* a_split = reinterpret_cast<float*>(base);
   float* b_split = reinterpret_cast<float*>(base + plan.a_bytes);
   const int kp = static_cast<int>(plan.kp), k = static_cast<int>(p.k);
-  const long long a_blocks = (kp / 32) * ((p.m + 31) / 32), b_blocks = (kp / 32) * ((p.n + 31) / 32);
+  const long long k_groups = (kp / 32 + kSplitTiles - 1) / kSplitTiles;
+  const long long a_blocks = k_groups * ((p.m + 31) / 32), b_blocks = k_groups * ((p.n + 31) / 32);
   if (a_blocks + b_blocks > 0x7fffffffLL) return set_error(error, VECOPS_STATUS_INVALID_ARGUMENT, "extent too large for f32_tf32x3");
   const SplitOperand split_a{static_cast<const float*>(p.a), p.a_stride_m, p.a_stride_k, a_split, static_cast<int>(p.m)};
   const SplitOperand split_b{static_cast<const float*>(p.b), p.b_stride_n, p.b_stride_k, b_split, static_cast<int>(p.n)};

@@ -372,35 +372,56 @@ struct SplitOperand {
   int rows;
 };
 
+// One CTA takes kSplitTiles consecutive 32 x 32 tiles along k of one 32-row block and has all their loads in flight
+// before the first store: with one tile per CTA the launch was two waves of CTAs each waiting out one DRAM latency.
+constexpr int kSplitTiles = 4;
+
 __global__ void __launch_bounds__(256)
 f32_split3_kernel(SplitOperand a, SplitOperand b, int a_blocks, int K, int Kp) {
-  __shared__ float tile[32][33];
+  __shared__ float tile[kSplitTiles][32][33];
   const bool is_b = static_cast<int>(blockIdx.x) >= a_blocks;
   const SplitOperand o = is_b ? b : a;
   const int block = is_b ? blockIdx.x - a_blocks : blockIdx.x;
   const int k_tiles = Kp / 32;
+  const int k_groups = (k_tiles + kSplitTiles - 1) / kSplitTiles;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
-  const int r0 = (block / k_tiles) * 32, k0 = (block % k_tiles) * 32;
+  const int r0 = (block / k_groups) * 32, kt0 = (block % k_groups) * kSplitTiles;
   const bool k_contiguous = o.stride_k == 1 || o.stride_row != 1;
+  float v[kSplitTiles][4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int r = r0 + (k_contiguous ? ty + 8 * j : tx), k = k0 + (k_contiguous ? tx : ty + 8 * j);
-    const float v = (r < o.rows && k < K) ? __ldg(o.src + static_cast<long long>(r) * o.stride_row + static_cast<long long>(k) * o.stride_k) : 0.f;
-    if (k_contiguous) tile[ty + 8 * j][tx] = v;
-    else tile[tx][ty + 8 * j] = v;
+  for (int t = 0; t < kSplitTiles; ++t) {
+    const int k0 = (kt0 + t) * 32;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int r = r0 + (k_contiguous ? ty + 8 * j : tx), k = k0 + (k_contiguous ? tx : ty + 8 * j);
+      v[t][j] = (r < o.rows && k < K) ? __ldg(o.src + static_cast<long long>(r) * o.stride_row + static_cast<long long>(k) * o.stride_k) : 0.f;
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < kSplitTiles; ++t) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (k_contiguous) tile[t][ty + 8 * j][tx] = v[t][j];
+      else tile[t][tx][ty + 8 * j] = v[t][j];
+    }
   }
   __syncthreads();
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int r = r0 + ty + 8 * j;
-    if (r >= o.rows) continue;
-    const float x = tile[ty + 8 * j][tx];
-    const float hi = round_to_tf32(x);
-    const float lo = round_to_tf32(x - hi);
-    float* row = o.dst + static_cast<long long>(r) * (3ll * Kp) + k0 + tx;
-    row[0] = hi;
-    row[Kp] = is_b ? hi : lo;
-    row[2ll * Kp] = is_b ? lo : hi;
+  for (int t = 0; t < kSplitTiles; ++t) {
+    const int k0 = (kt0 + t) * 32;
+    if (k0 >= Kp) break;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int r = r0 + ty + 8 * j;
+      if (r >= o.rows) continue;
+      const float x = tile[t][ty + 8 * j][tx];
+      const float hi = round_to_tf32(x);
+      const float lo = round_to_tf32(x - hi);
+      float* row = o.dst + static_cast<long long>(r) * (3ll * Kp) + k0 + tx;
+      row[0] = hi;
+      row[Kp] = is_b ? hi : lo;
+      row[2ll * Kp] = is_b ? lo : hi;
+    }
   }
 }
 
