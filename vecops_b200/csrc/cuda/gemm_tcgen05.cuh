@@ -408,8 +408,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             tma_load_2d_pair(b_dst, &tma_b, leader_full, kb * kBlockK, tn * G::kBlockN + static_cast<int>(pair_rank) * GemmPair::kBRows);
           } else {
             mbar_arrive_expect_tx(full_bar + 8 * stage, G::kStageBytes);
-            tma_load_2d(a_dst, &tma_a, full_bar + 8 * stage, kb * kBlockK, tm * G::kBlockM);
-            tma_load_2d(b_dst, &tma_b, full_bar + 8 * stage, kb * kBlockK, tn * G::kBlockN);
+            int a_k = kb * kBlockK, b_k = kb * kBlockK;
+            if constexpr (kTf32) {
+              // the split fp32 product: k runs over three terms, a_hi.b_hi, a_lo.b_hi, a_hi.b_lo, of operands stored
+              // as [hi | lo]
+              const int term_kb = num_kb / 3, term = kb / term_kb, within = (kb - term * term_kb) * kBlockK;
+              a_k = (term == 1 ? term_kb * kBlockK : 0) + within;
+              b_k = (term == 2 ? term_kb * kBlockK : 0) + within;
+            }
+            tma_load_2d(a_dst, &tma_a, full_bar + 8 * stage, a_k, tm * G::kBlockM);
+            tma_load_2d(b_dst, &tma_b, full_bar + 8 * stage, b_k, tn * G::kBlockN);
           }
           if (++stage == G::kStages) {
             stage = 0;

@@ -518,9 +518,11 @@ int32_t launch_tcgen05(const VecopsB200Matmul& p, const DeviceState& dev, cudaSt
   const Tcgen05Plan plan = plan_tcgen05(p, kInt8, sizeof(OutT), dev.prop.multiProcessorCount, kTf32 ? 0 : pair_capacity<kInt8, OutT>(device), elem);
   CUtensorMap map_a, map_b;
   GemmStoreMaps maps;
-  int32_t rc = make_map_2d(&map_a, in_type, elem, p.a, p.k, p.m, p.a_stride_m * elem, box_k, G::kBlockM, error);
+  // the split fp32 form walks three terms of k over operands stored as two ([hi | lo]): the maps cover what is stored
+  const long long stored_k = kTf32 ? p.k / 3 * 2 : p.k;
+  int32_t rc = make_map_2d(&map_a, in_type, elem, p.a, stored_k, p.m, p.a_stride_m * elem, box_k, G::kBlockM, error);
   if (rc != VECOPS_STATUS_OK) return rc;
-  rc = make_map_2d(&map_b, in_type, elem, p.b, p.k, p.n, p.b_stride_n * elem, box_k, plan.pair ? GemmPair::kBRows : G::kBlockN, error);
+  rc = make_map_2d(&map_b, in_type, elem, p.b, stored_k, p.n, p.b_stride_n * elem, box_k, plan.pair ? GemmPair::kBRows : G::kBlockN, error);
   if (rc != VECOPS_STATUS_OK) return rc;
   bool tma_store;
   int num_dest = 1;
@@ -904,7 +906,7 @@ int32_t launch_w8_mixed(const VecopsB200Matmul& p, const DeviceState& dev, cudaS
 }
 
 // ---- FP32 on the tensor cores: three tf32 products of split operands, run as one product over a tripled K.
-// Scratch layout: A' [M, 3 Kp] f32 | B' [N, 3 Kp] f32 | the scratch the inner tcgen05 GEMM's K slices meet in.
+// Scratch layout: A' [M, 2 Kp] f32 ([hi | lo]) | B' [N, 2 Kp] f32 | the scratch the inner tcgen05 GEMM's K slices meet in.
 struct Tf32x3Plan {
   long long kp = 0;          // K rounded up to the 32 words of a k-block
   uint64_t a_bytes = 0, b_bytes = 0, inner = 0;
@@ -916,11 +918,12 @@ uint64_t align256(uint64_t v) { return (v + 255u) & ~uint64_t{255}; }
 Tf32x3Plan plan_tf32x3(const VecopsB200Matmul& p, int sms) {
   Tf32x3Plan plan;
   plan.kp = (p.k + 31) & ~INT64_C(31);
-  plan.a_bytes = align256(static_cast<uint64_t>(p.m) * 3 * plan.kp * 4);
-  plan.b_bytes = align256(static_cast<uint64_t>(p.n) * 3 * plan.kp * 4);
+  // each operand is stored once as [hi | lo], 2 * kp wide; the GEMM walks 3 * kp of k and its producer picks the term
+  plan.a_bytes = align256(static_cast<uint64_t>(p.m) * 2 * plan.kp * 4);
+  plan.b_bytes = align256(static_cast<uint64_t>(p.n) * 2 * plan.kp * 4);
   VecopsB200Matmul q = p;
   q.k = 3 * plan.kp;
-  q.a_stride_m = q.b_stride_n = 3 * plan.kp;
+  q.a_stride_m = q.b_stride_n = 2 * plan.kp;
   q.a_stride_k = q.b_stride_k = 1;
   plan.inner_problem = q;
   const Tcgen05Plan inner = plan_tcgen05(q, false, 4, sms, 0, 4);

@@ -354,9 +354,9 @@ gemm_f32_tile8_kernel(const float* __restrict__ a, long long lda, const float* _
 // An fp32 value x is the sum of two tf32 values to within 2^-22 of itself: hi = tf32(x) (round to nearest, 10 mantissa
 // bits) and lo = tf32(x - hi).  With both operands split, a.b = a_hi.b_hi + a_lo.b_hi + a_hi.b_lo up to a term of 2^-22,
 // and each of the three products is exact in the tensor core's fp32 accumulator.  The three are run as ONE product over
-// a K three times as long: this kernel writes one operand's rows as [ first | second | third ] segments, each Kp wide
-// (K rounded up to the 32 words of a k-block, zero past K) - A' = [a_hi | a_lo | a_hi], B' = [b_hi | b_hi | b_lo] - so
-// that sum_k' A'[m,k'] B'[n,k'] is the fp32 product.  Any element strides: a 32 x 32 tile goes through shared memory so
+// a K three times as long: this kernel writes each operand's rows once as [ hi | lo ], each half Kp wide (K rounded up
+// to the 32 words of a k-block, zero past K), and the GEMM's producer walks k' over the three terms - A's halves in the
+// order hi, lo, hi against B's hi, hi, lo - so that what is summed is the fp32 product.  Any element strides: a 32 x 32 tile goes through shared memory so
 // that both the reads (along whichever axis is contiguous) and the writes (along K) are coalesced.
 __device__ __forceinline__ float round_to_tf32(float x) {
   uint32_t bits;
@@ -417,10 +417,9 @@ f32_split3_kernel(SplitOperand a, SplitOperand b, int a_blocks, int K, int Kp) {
       const float x = tile[t][ty + 8 * j][tx];
       const float hi = round_to_tf32(x);
       const float lo = round_to_tf32(x - hi);
-      float* row = o.dst + static_cast<long long>(r) * (3ll * Kp) + k0 + tx;
+      float* row = o.dst + static_cast<long long>(r) * (2ll * Kp) + k0 + tx;  // [hi | lo], each Kp wide
       row[0] = hi;
-      row[Kp] = is_b ? hi : lo;
-      row[2ll * Kp] = is_b ? lo : hi;
+      row[Kp] = lo;
     }
   }
 }
