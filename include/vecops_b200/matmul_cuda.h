@@ -406,8 +406,9 @@ VECOPS_B200_EXPORT int32_t vecops_b200_place_columns(void* dst, int64_t ldd, int
  * slab while the next GEMM computes).  Columns [col0, col0 + cols) of the local result src[rows, ld] are written to
  * the same columns of every destination in `dst` - the peers' copies of the result, `count` <= 8 pointers this
  * process can store through (symmetric memory, CUDA IPC), visited in the order given (start at the next rank so that
- * no two senders begin on the same receiver).  Only stores cross GPUs.  Asynchronous on `stream`; the caller orders
- * the ranks afterwards (a barrier on that stream) before anyone reads.
+ * no two senders begin on the same receiver).  Only stores cross GPUs.  Asynchronous on `stream`, which belongs to the
+ * device `src` lives on - the calling thread's current device; the caller orders the ranks afterwards (a barrier on
+ * that stream) before anyone reads.
  *   VECOPS_B200_PUSH_KERNEL       this library's kernel: every 16-byte piece is read once and stored to every destination
  *                                 (16-byte aligned bases, pitch, col0 and cols);
  *   VECOPS_B200_PUSH_COPY_ENGINE  one strided cudaMemcpy2DAsync per destination: no SM is used. */
